@@ -1,0 +1,275 @@
+/*
+ * b200nn - fixed library of hand-written sm_100a kernels behind a C ABI.
+ *
+ * This is the device side of the CUDA backend for the PyTorch-IR compiler: the
+ * Python host (cuda_compiler / cuda_runtime) lowers an IR subgraph to a list of
+ * calls into this library and issues them through ctypes.  The reference
+ * backend has no native boundary of its own - it JIT-compiles CUDA C strings with
+ * NVRTC through CuPy and calls cuBLAS via cupy.matmul - so every entry point
+ * below cites the reference kernel template or executor dispatch it replaces.
+ *
+ * Conventions
+ *   - every call returns 0 on success or a negative B200_E* code; the message is
+ *     available from b200_last_error() (thread local);
+ *   - calls only enqueue work on `stream` (a cudaStream_t passed as void*); they
+ *     never synchronise, never allocate device memory and never free it, so a
+ *     sequence of calls can be captured into a CUDA graph;
+ *   - device pointers are plain pointers; sizes are element counts unless a name
+ *     says bytes; `dtype` arguments take the B200_* codes below;
+ *   - strided operands are described by b200_tensor (element strides).
+ */
+#ifndef B200NN_H
+#define B200NN_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200NN_VERSION 1
+
+/* status codes */
+#define B200_OK 0
+#define B200_EINVAL (-1)   /* bad argument (shape, dtype, null pointer)        */
+#define B200_EALIGN (-2)   /* pointer or stride not aligned as the kernel needs */
+#define B200_ELAUNCH (-3)  /* the CUDA runtime refused the launch               */
+#define B200_ENOTSUP (-4)  /* combination not implemented                       */
+#define B200_ELIMIT (-5)   /* size beyond a documented maximum                  */
+
+/* element types */
+#define B200_F32 0
+#define B200_F16 1
+#define B200_BF16 2
+#define B200_I32 3
+#define B200_I64 4
+#define B200_U8 5
+
+#define B200_MAX_DIMS 6
+
+typedef struct b200_tensor {
+  void* data;
+  int32_t dtype;
+  int32_t ndim;
+  int64_t shape[B200_MAX_DIMS];
+  int64_t stride[B200_MAX_DIMS]; /* in elements; 0 = broadcast */
+} b200_tensor;
+
+int b200_version(void);
+const char* b200_last_error(void);
+/* sm count, compute capability and opt-in shared memory of device `dev`. */
+int b200_device_info(int dev, int* sm_count, int* cc_major, int* cc_minor, int64_t* smem_optin_bytes);
+
+/* ------------------------------------------------------------------------- *
+ * Fused elementwise chains.
+ * Replaces the NVRTC-generated `fused_ew_<i>` kernels
+ * (cuda_compiler/cuda_codegen.py:47-142, launched at
+ * cuda_runtime/cuda_executor.py:358-376).  The reference emits one __half
+ * kernel per chain and indexes every operand with the flat output index; here a
+ * chain is a short program interpreted per element in fp32, operands may be
+ * broadcast/strided, and every intermediate is rounded to the dtype the IR gives
+ * it, which is what ATen does op by op.
+ * ------------------------------------------------------------------------- */
+enum b200_ew_opcode {
+  B200_EW_RELU = 1, B200_EW_SILU, B200_EW_NEG, B200_EW_RSQRT, B200_EW_COS, B200_EW_SIN,
+  B200_EW_ADD, B200_EW_MUL, B200_EW_DIV, B200_EW_SUB,
+  B200_EW_ADD_S, B200_EW_MUL_S, B200_EW_DIV_S, B200_EW_POW_S, B200_EW_SUB_S, B200_EW_CAST,
+  B200_EW_SIGMOID, B200_EW_EXP, B200_EW_SQRT, B200_EW_TANH, B200_EW_GELU, B200_EW_RSUB_S, B200_EW_MAX, B200_EW_MIN
+};
+
+#define B200_EW_MAX_INPUTS 4
+#define B200_EW_MAX_OPS 12
+
+typedef struct b200_ew_op {
+  int32_t opcode;      /* b200_ew_opcode */
+  int32_t a;           /* operand slot: 0..3 = inputs, 4+i = result of op i */
+  int32_t b;           /* second operand slot (binary ops), else -1 */
+  int32_t round_dtype; /* B200_F32/F16/BF16: dtype the result is rounded to */
+  float imm;           /* scalar for the *_S opcodes */
+} b200_ew_op;
+
+/* out[i] = chain(in0[i], in1[i], ...).  Inputs must already be expressed in the
+ * output's index space (same ndim and shape, stride 0 where broadcast). */
+int b200_ew_chain(const b200_tensor* out, const b200_tensor* ins, int n_in,
+                  const b200_ew_op* ops, int n_ops, void* stream);
+
+/* Strided gather copy with dtype conversion: out[idx] = (out dtype) in[idx].
+ * Replaces transpose_kernel / slice_kernel / expand_kernel / cat_2_kernel
+ * (cuda_compiler/cuda_templates.py:164-302), which the reference executor
+ * substitutes with CuPy views and implicit copies
+ * (cuda_runtime/cuda_executor.py:596-649). */
+int b200_strided_copy(const b200_tensor* out, const b200_tensor* in, void* stream);
+
+/* full_kernel (cuda_templates.py:304-313): fill `n` elements with `value`. */
+int b200_fill(void* out, int64_t n, double value, int dtype, void* stream);
+
+/* ------------------------------------------------------------------------- *
+ * Row reductions.
+ * ------------------------------------------------------------------------- */
+/* rmsnorm_kernel (cuda_templates.py:458-506; matcher
+ * cuda_compiler/subgraph_analyzer.py:667-756): y = x * rsqrt(mean(x^2)+eps) * w.
+ * fp32 math.  With round_mid != 0 the normalised value is rounded to the
+ * activation dtype before the multiply by w, as the unfused ATen chain does.
+ * x, y: [rows, cols] with row strides in elements; w: [cols]. */
+int b200_rmsnorm(const void* x, const void* w, void* y, int64_t rows, int64_t cols,
+                 int64_t x_row_stride, int64_t y_row_stride, float eps, int dtype,
+                 int round_mid, void* stream);
+
+/* softmax_kernel / masked_softmax_kernel (cuda_templates.py:9-80, 525-594;
+ * dispatch cuda_executor.py:378-427): y = softmax(x*scale + mask) over the last
+ * axis.  x and y are contiguous [d0, d1, d2, cols]; the additive mask (may be
+ * NULL) is addressed as mask[i0*ms0 + i1*ms1 + i2*ms2 + c], so [B,1,T,S],
+ * [B,1,1,S] and full-shape masks all work (the reference indexes the mask with
+ * the flat score index and cannot broadcast).  fp32 math; with round_steps != 0
+ * the product x*scale and the sum with the mask are each rounded to `in_dtype`,
+ * as the unfused ATen ops would. */
+int b200_softmax(const void* x, const void* mask, void* y, int64_t d0, int64_t d1, int64_t d2,
+                 int64_t cols, int64_t ms0, int64_t ms1, int64_t ms2, float scale, int in_dtype,
+                 int mask_dtype, int out_dtype, int round_steps, void* stream);
+
+/* mean_last_dim_kernel (cuda_templates.py:82-97): y[r] = mean(x[r, :]). */
+int b200_mean_last_dim(const void* x, void* y, int64_t rows, int64_t cols, int in_dtype,
+                       int out_dtype, void* stream);
+
+/* ------------------------------------------------------------------------- *
+ * Indexing (bit-exact).
+ * ------------------------------------------------------------------------- */
+/* embedding_kernel (cuda_templates.py:99-112; step subgraph_analyzer.py:381-393):
+ * out[s, :] = table[ids[s], :].  ids are int64 or int32 as given (the reference
+ * casts to int32 on device each call, cuda_executor.py:535).  Rows are copied
+ * as raw bytes; an id outside [0, vocab) yields a zero row. */
+int b200_embedding(const void* table, const void* ids, void* out, int64_t n_ids, int64_t vocab,
+                   int64_t row_bytes, int ids_dtype, void* stream);
+
+/* index_copy_kernel (cuda_templates.py:134-162; step subgraph_analyzer.py:411-428):
+ * dst viewed as [outer, dim_size, inner]; dst[o, index[l], :] = src[o, l, :].
+ * When base != dst the whole of base is copied to dst first (the reference's
+ * out-of-place semantics); when base == dst only the indexed rows are written.
+ * src may be strided: src element (o, l, i) is at o*src_outer_stride +
+ * l*src_index_stride + i (inner is contiguous). */
+int b200_index_copy(const void* base, void* dst, const void* src, const void* index,
+                    int64_t outer, int64_t dim_size, int64_t inner, int64_t n_index,
+                    int64_t src_outer_stride, int64_t src_index_stride, int elem_bytes,
+                    int index_dtype, void* stream);
+
+/* Greedy token choice: out[r] = argmax(x[r, :]) as int64 (lowest index wins ties).
+ * Not a reference kernel: the reference downloads logits and uses numpy on the
+ * host (benchmarks/benchmark_qwen.py). */
+int b200_argmax_rows(const void* x, int64_t* out, int64_t rows, int64_t cols, int64_t row_stride,
+                     int dtype, void* stream);
+
+/* ------------------------------------------------------------------------- *
+ * Rotary embedding.
+ * ------------------------------------------------------------------------- */
+/* rope_kernel (cuda_templates.py:114-132; correct math metal_kernels/rope.metal:34-44):
+ * cos/sin tables [n_pos, head_dim] with angle = fp32(pos) * inv_freq[d mod head_dim/2]. */
+int b200_rope_table(const float* inv_freq, const void* positions, void* cos_out, void* sin_out,
+                    int64_t n_pos, int head_dim, int pos_dtype, int out_dtype, void* stream);
+
+/* Fused rotate, replacing the mul/slice/neg/cat/mul/add chain the reference runs
+ * as 7 elementwise and copy steps per tensor (math: metal_kernels/rope_rotate.metal:41-61):
+ * y = x*cos + rotate_half(x)*sin for x [batch, heads, seq, head_dim] (arbitrary
+ * strides, head_dim contiguous), cos/sin [batch, seq, head_dim].  Each product
+ * and the sum are rounded to `dtype`, as the unfused chain does.
+ * If kv_cache != NULL the result is written there instead of y, at row
+ * cache_pos[s] of a [batch, heads, cache_len, head_dim] cache (the index_copy the
+ * graph applies next). */
+int b200_rope_rotate(const b200_tensor* x, const void* cos_t, const void* sin_t, void* y,
+                     void* kv_cache, const void* cache_pos, int64_t cache_len, int pos_dtype,
+                     void* stream);
+
+/* ------------------------------------------------------------------------- *
+ * Pooling / normalisation for the CNN path (NCHW logical shape, any strides, so
+ * channels-last storage is simply a stride pattern).
+ * ------------------------------------------------------------------------- */
+/* max_pool2d_kernel (cuda_templates.py:315-352). */
+int b200_max_pool2d(const b200_tensor* x, const b200_tensor* y, int kh, int kw, int sh, int sw,
+                    int ph, int pw, void* stream);
+/* adaptive_avg_pool2d_kernel (cuda_templates.py:354-383); fp32 sum / count. */
+int b200_adaptive_avg_pool2d(const b200_tensor* x, const b200_tensor* y, void* stream);
+/* batch_norm_kernel (cuda_templates.py:432-456), inference statistics. */
+int b200_batch_norm(const b200_tensor* x, const b200_tensor* y, const void* gamma, const void* beta,
+                    const void* mean, const void* var, float eps, int param_dtype, int relu,
+                    void* stream);
+/* Weight preparation, run once per weight set: folds inference batch-norm into
+ * the preceding convolution (math of npu_runtime/weight_loader.py:74-99) and
+ * repacks OIHW weights to [O, KH, KW, I_pad] in the compute dtype.
+ * w_out: [O, KH*KW*I_pad]; bias_out: fp32 [O].  gamma..var and conv_bias may be NULL. */
+int b200_conv_weight_prep(const void* w, const void* conv_bias, const void* gamma, const void* beta,
+                          const void* mean, const void* var, void* w_out, float* bias_out,
+                          int O, int I, int KH, int KW, int I_pad, float eps, int w_dtype,
+                          int param_dtype, int out_dtype, void* stream);
+
+/* ------------------------------------------------------------------------- *
+ * Dense contractions.
+ * ------------------------------------------------------------------------- */
+/* epilogue flags */
+#define B200_EPI_RELU 1
+#define B200_EPI_SILU_MUL 2 /* out = silu(acc) * aux (aux shaped like out) */
+
+/* CUBLASStep("gemm") (subgraph_analyzer.py:168-224, dispatch cuda_executor.py:182-208,
+ * which calls cupy.matmul and a separate bias-add kernel):
+ *   out[M,N] = epi( A[M,K] * W[N,K]^T + bias[N] + residual[M,N] )
+ * A, W, out, residual share `dtype` (f16/bf16), fp32 accumulation; bias dtype is
+ * `bias_dtype`.  lda/ldw/ldo/ldr are row strides in elements.  Any M; skinny M
+ * (decode) takes a weight-streaming split-K path that uses `workspace`
+ * (fp32 [M*N] + a counter block, see b200_linear_workspace_bytes). */
+int b200_linear(const void* A, const void* W, const void* bias, const void* residual, void* out,
+                int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldw, int64_t ldo, int64_t ldr,
+                int dtype, int bias_dtype, int epilogue, const void* aux, int64_t ldaux,
+                void* workspace, int64_t workspace_bytes, void* stream);
+int64_t b200_linear_workspace_bytes(int64_t M, int64_t N, int64_t K);
+
+/* CUBLASStep("gemm_batched") and plain 2-D matmul (subgraph_analyzer.py:206-224,
+ * dispatch cuda_executor.py:210-218): out[b1,b2,M,N] = A[b1,b2,M,K] @ B[b1,b2,K,N] with
+ * independent element strides for every axis of every operand (0 = broadcast), so
+ * transposed and expanded operands need no materialised copy.  fp32 accumulate. */
+int b200_matmul_strided(const void* A, const void* B, void* out, int64_t b1, int64_t b2, int64_t M,
+                        int64_t N, int64_t K, const int64_t a_strides[4], const int64_t b_strides[4],
+                        const int64_t o_strides[4], int dtype, void* stream);
+
+/* CUBLASStep("conv2d") (subgraph_analyzer.py:226-254; dispatch
+ * cuda_executor.py:275-356, a host-side im2col loop + cupy.matmul): implicit-GEMM
+ * convolution over channels-last activations.
+ *   x: [N, H, W, C] (C contiguous), w: [O, KH, KW, C_pad] from b200_conv_weight_prep,
+ *   y / residual: [N, Ho, Wo, O];  y = epi(conv(x, w) + bias + residual).
+ * groups must be 1. */
+int b200_conv2d_nhwc(const void* x, const void* w, const float* bias, const void* residual, void* y,
+                     int N, int H, int W, int C, int C_pad, int O, int KH, int KW, int sh, int sw,
+                     int ph, int pw, int Ho, int Wo, int dtype, int epilogue, void* stream);
+
+/* ------------------------------------------------------------------------- *
+ * Attention.
+ * ------------------------------------------------------------------------- */
+/* Decode attention over a static KV cache, replacing CUBLASStep("gemm_gqa") x2 plus
+ * the scale / mask-add / softmax steps between them (subgraph_analyzer.py:819-861,
+ * dispatch cuda_executor.py:226-273).
+ *   q:   [B, Hq, D]   (one query token per sequence, D = 128)
+ *   k,v: [B, Hkv, S, D] caches, row stride D, head stride S*D
+ *   mask:[B, S] additive (the graph's attention_mask [B,1,1,S]); NULL = none
+ *   out: [B, Hq, D]
+ * Split-KV: partial (max, sum, acc) per split go to `workspace` and are merged by a
+ * second kernel.  Key blocks whose mask entries are all <= -1e30 are skipped, which
+ * leaves the result unchanged because their softmax weight underflows to 0. */
+int b200_attn_decode(const void* q, const void* k, const void* v, const void* mask, void* out,
+                     int64_t B, int Hq, int Hkv, int64_t S, int D, int64_t q_batch_stride,
+                     int64_t kv_batch_stride, int64_t kv_head_stride, int64_t mask_batch_stride,
+                     float scale, int dtype, void* workspace, int64_t workspace_bytes, void* stream);
+int64_t b200_attn_decode_workspace_bytes(int64_t B, int Hq, int Hkv, int64_t S, int D);
+
+/* Prefill attention, replacing CUBLASStep("gemm_batched") x2 with the softmax
+ * between them and the materialised expand/transpose copies
+ * (subgraph_analyzer.py:206-215; cuda_executor.py:210-218):
+ *   q: [B, Hq, T, D] with strides (q_b, q_h, q_t, 1); k,v: [B, Hkv, S, D] likewise;
+ *   mask: additive, addressed mask[b*mask_b + t*mask_t + s]; out: [B, T, Hq, D]
+ *   contiguous (the layout the following o_proj consumes). */
+int b200_attn_prefill(const void* q, const void* k, const void* v, const void* mask, void* out,
+                      int64_t B, int Hq, int Hkv, int64_t T, int64_t S, int D,
+                      const int64_t q_strides[3], const int64_t k_strides[3], const int64_t v_strides[3],
+                      int64_t mask_b, int64_t mask_t, float scale, int dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200NN_H */

@@ -1,0 +1,411 @@
+// Fused attention for head_dim 128 on the warp-level tensor-core path.
+//
+// One warp owns a 16-row score tile: 16 query positions of one head (prefill) or
+// the group of query heads that share one KV head, padded to 16 (decode).  K and V
+// rows go from global memory straight into MMA fragments with 16-byte loads:
+//   * S = Q K^T: inside every 32-wide slice of the head dim, thread t of a quad owns
+//     dims 8t..8t+7 for both Q and K - a consistent permutation of the contraction
+//     index, so the dot products are unchanged;
+//   * O = P V: thread (g, t) loads dims 8g..8g+7 (+64) of keys {2t, 2t+1, 2t+8, 2t+9}
+//     and assembles the B fragments with byte permutes; output column "g" of MMA
+//     tile j therefore is head dim 8g + j, which the store undoes.
+// Softmax is the usual online form in fp32; P is rounded to the activation dtype
+// for the second MMA, as the unfused graph rounds the probabilities.
+#include "mma.cuh"
+
+namespace b200 {
+
+constexpr int HD = 128;          // head dim
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr float MASKED = -1e30f; // additive mask values at or below this are "masked out"
+
+template <typename T> struct AttnWarp {
+  uint32_t q[4][2][4];  // [32-dim slice][row half g / g+8][4 x 32-bit]
+  float o[2][8][4];     // [64-dim half][tile j][c0..c3]
+  float m[2], l[2];     // running max / sum for rows g and g+8
+
+  __device__ __forceinline__ void init() {
+#pragma unroll
+    for (int a = 0; a < 2; ++a)
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[a][j][e] = 0.f;
+    m[0] = m[1] = -INFINITY;
+    l[0] = l[1] = 0.f;
+  }
+
+  // q_lo / q_hi: rows g and g+8 (nullptr -> zero row)
+  __device__ __forceinline__ void load_q(const T* q_lo, const T* q_hi, int t) {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const uint4 lo = q_lo ? *reinterpret_cast<const uint4*>(q_lo + 32 * c + 8 * t) : make_uint4(0, 0, 0, 0);
+      const uint4 hi = q_hi ? *reinterpret_cast<const uint4*>(q_hi + 32 * c + 8 * t) : make_uint4(0, 0, 0, 0);
+      q[c][0][0] = lo.x; q[c][0][1] = lo.y; q[c][0][2] = lo.z; q[c][0][3] = lo.w;
+      q[c][1][0] = hi.x; q[c][1][1] = hi.y; q[c][1][2] = hi.z; q[c][1][3] = hi.w;
+    }
+  }
+
+  // One block of 16 keys starting at row `kb`.  k_base/v_base point at key 0 of this
+  // (batch, kv head); key stride in elements.  add[j][e]: additive mask (already in
+  // the score domain) for rows (g, g+8) x keys (8j+2t, 8j+2t+1): index [j][2*half+e].
+  __device__ __forceinline__ void step(const T* k_base, const T* v_base, int64_t k_stride, int64_t v_stride, int64_t kb,
+                                       int64_t n_keys, float scale, const float (&add)[2][4], int g, int t) {
+    const uint4 zero4 = make_uint4(0, 0, 0, 0);
+    // ---- issue all loads for this block -----------------------------------------
+    uint4 kf[2][4];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int64_t key = kb + 8 * j + g;
+      const T* kr = k_base + key * k_stride + 8 * t;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) kf[j][c] = key < n_keys ? ld_global_nc_v4(kr + 32 * c) : zero4;
+    }
+    uint4 vf[2][4];  // [64-dim half][key slot 2t, 2t+1, 2t+8, 2t+9]
+#pragma unroll
+    for (int s = 0; s < 4; ++s) {
+      const int64_t key = kb + 2 * t + (s & 1) + 8 * (s >> 1);
+      const T* vr = v_base + key * v_stride + 8 * g;
+#pragma unroll
+      for (int a = 0; a < 2; ++a) vf[a][s] = key < n_keys ? ld_global_nc_v4(vr + 64 * a) : zero4;
+    }
+    // ---- S = Q K^T ---------------------------------------------------------------
+    float s[2][4];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const uint32_t a1[4] = {q[c][0][0], q[c][1][0], q[c][0][1], q[c][1][1]};
+        const uint32_t a2[4] = {q[c][0][2], q[c][1][2], q[c][0][3], q[c][1][3]};
+        const uint32_t b1[2] = {kf[j][c].x, kf[j][c].y};
+        const uint32_t b2[2] = {kf[j][c].z, kf[j][c].w};
+        MmaType<T>::mma(s[j], a1, b1);
+        MmaType<T>::mma(s[j], a2, b2);
+      }
+    }
+    // ---- online softmax ------------------------------------------------------------
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int64_t key = kb + 8 * j + 2 * t + (e & 1);
+        const float v = key < n_keys ? s[j][e] * scale + add[j][e] : -INFINITY;
+        s[j][e] = v;
+        mx[e >> 1] = fmaxf(mx[e >> 1], v);
+      }
+    float corr[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+      const float m_new = fmaxf(m[h], mx[h]);
+      const float m_use = m_new == -INFINITY ? 0.f : m_new;
+      corr[h] = exp2f((m[h] - m_use) * LOG2E);  // m = -inf -> 0
+      m[h] = m_new;
+      float rs = 0.f;
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const float p = exp2f((s[j][2 * h + e] - m_use) * LOG2E);
+          s[j][2 * h + e] = p;
+          rs += p;
+        }
+      rs += __shfl_xor_sync(0xffffffffu, rs, 1);
+      rs += __shfl_xor_sync(0xffffffffu, rs, 2);
+      l[h] = l[h] * corr[h] + rs;
+    }
+    // ---- O = O * corr + P V -----------------------------------------------------------
+    const uint32_t pa[4] = {pack2<T>(s[0][0], s[0][1]), pack2<T>(s[0][2], s[0][3]), pack2<T>(s[1][0], s[1][1]),
+                            pack2<T>(s[1][2], s[1][3])};
+#pragma unroll
+    for (int a = 0; a < 2; ++a) {
+      const uint32_t* r0 = reinterpret_cast<const uint32_t*>(&vf[a][0]);
+      const uint32_t* r1 = reinterpret_cast<const uint32_t*>(&vf[a][1]);
+      const uint32_t* r2 = reinterpret_cast<const uint32_t*>(&vf[a][2]);
+      const uint32_t* r3 = reinterpret_cast<const uint32_t*>(&vf[a][3]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint32_t sel = (j & 1) ? 0x7632u : 0x5410u;
+        const uint32_t b[2] = {__byte_perm(r0[j >> 1], r1[j >> 1], sel), __byte_perm(r2[j >> 1], r3[j >> 1], sel)};
+        o[a][j][0] *= corr[0]; o[a][j][1] *= corr[0];
+        o[a][j][2] *= corr[1]; o[a][j][3] *= corr[1];
+        MmaType<T>::mma(o[a][j], pa, b);
+      }
+    }
+  }
+};
+
+// head dim held in o[a][j][2*h + e]  (h: row half) for thread (g, t)
+__device__ __forceinline__ int out_dim(int a, int j, int e, int t) { return 64 * a + 8 * (2 * t + e) + j; }
+
+// ===========================================================================
+// Decode: one query token, G = Hq / Hkv query heads share each KV head.
+// grid = (splits, Hkv, B), 128 threads.  Partials: acc [B][Hkv][splits][G][HD] fp32,
+// then ml [B][Hkv][splits][G][2] fp32 (max, sum).
+// ===========================================================================
+struct DecodeParams {
+  const void* q; const void* k; const void* v; const void* mask;
+  float* part_acc; float* part_ml;
+  int64_t B, S;
+  int Hq, Hkv, G;
+  int64_t q_bs, kv_bs, kv_hs, mask_bs;
+  int split_len, splits;
+  float scale;
+  int mask_dtype;
+};
+
+constexpr int DEC_MAX_BLOCKS = 128;  // 16-key blocks per split (split_len <= 2048)
+
+template <typename T>
+__global__ void __launch_bounds__(128) attn_decode_kernel(const __grid_constant__ DecodeParams p) {
+  __shared__ uint32_t valid[DEC_MAX_BLOCKS / 32];
+  __shared__ float s_acc[8][HD];
+  __shared__ float s_m[4][8], s_l[4][8];
+
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+  const int split = blockIdx.x, hk = blockIdx.y;
+  const int64_t b = blockIdx.z;
+  const int64_t s_begin = static_cast<int64_t>(split) * p.split_len;
+  const int64_t s_end = min(p.S, s_begin + p.split_len);
+  const int nblk = static_cast<int>((s_end - s_begin + 15) / 16);
+
+  // ---- which 16-key blocks have at least one unmasked key ---------------------------
+  if (threadIdx.x < DEC_MAX_BLOCKS / 32) valid[threadIdx.x] = 0u;
+  for (int i = threadIdx.x; i < 8 * HD; i += 128) (&s_acc[0][0])[i] = 0.f;
+  __syncthreads();
+  if (p.mask) {
+    for (int64_t key = s_begin + threadIdx.x; key < s_end; key += 128) {
+      const float mv = load_as_f32(p.mask, b * p.mask_bs + key, p.mask_dtype);
+      if (mv > MASKED) {
+        const int blk = static_cast<int>((key - s_begin) >> 4);
+        atomicOr(&valid[blk >> 5], 1u << (blk & 31));
+      }
+    }
+  } else {
+    for (int blk = threadIdx.x; blk < nblk; blk += 128) atomicOr(&valid[blk >> 5], 1u << (blk & 31));
+  }
+  __syncthreads();
+
+  AttnWarp<T> w;
+  w.init();
+  const T* qb = static_cast<const T*>(p.q) + b * p.q_bs + static_cast<int64_t>(hk) * p.G * HD;
+  w.load_q(g < p.G ? qb + g * HD : nullptr, (g + 8) < p.G ? qb + (g + 8) * HD : nullptr, t);
+  const T* kbase = static_cast<const T*>(p.k) + b * p.kv_bs + hk * p.kv_hs;
+  const T* vbase = static_cast<const T*>(p.v) + b * p.kv_bs + hk * p.kv_hs;
+
+  for (int blk = warp; blk < nblk; blk += 4) {
+    if (!((valid[blk >> 5] >> (blk & 31)) & 1u)) continue;
+    const int64_t kb = s_begin + 16 * blk;
+    float add[2][4];
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int64_t key = kb + 8 * j + 2 * t + e;
+        const float mv = (p.mask && key < s_end) ? load_as_f32(p.mask, b * p.mask_bs + key, p.mask_dtype) : 0.f;
+        add[j][e] = mv;
+        add[j][2 + e] = mv;
+      }
+    w.step(kbase, vbase, HD, HD, kb, s_end, p.scale, add, g, t);
+  }
+
+  // ---- merge the four warps (rows 0..7 only: G <= 8 lives in the g half) --------------
+  if (t == 0) { s_m[warp][g] = w.m[0]; s_l[warp][g] = w.l[0]; }
+  __syncthreads();
+  float m_all = fmaxf(fmaxf(s_m[0][g], s_m[1][g]), fmaxf(s_m[2][g], s_m[3][g]));
+  const float m_use = m_all == -INFINITY ? 0.f : m_all;
+  const float f = exp2f((w.m[0] - m_use) * LOG2E);
+  if (g < p.G) {
+#pragma unroll
+    for (int a = 0; a < 2; ++a)
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) atomicAdd(&s_acc[g][out_dim(a, j, e, t)], w.o[a][j][e] * f);
+  }
+  __syncthreads();
+  const int64_t pidx = ((b * p.Hkv + hk) * p.splits + split) * p.G;
+  for (int i = threadIdx.x; i < p.G * HD; i += 128) p.part_acc[pidx * HD + i] = (&s_acc[0][0])[i];
+  if (threadIdx.x < p.G) {
+    const int r = threadIdx.x;
+    const float mr = fmaxf(fmaxf(s_m[0][r], s_m[1][r]), fmaxf(s_m[2][r], s_m[3][r]));
+    const float mu = mr == -INFINITY ? 0.f : mr;
+    float lr = 0.f;
+#pragma unroll
+    for (int wi = 0; wi < 4; ++wi) lr += s_l[wi][r] * exp2f((s_m[wi][r] - mu) * LOG2E);
+    p.part_ml[(pidx + r) * 2] = mr;
+    p.part_ml[(pidx + r) * 2 + 1] = lr;
+  }
+}
+
+// grid = B*Hq blocks of 128 threads (one per head dim)
+template <typename T>
+__global__ void __launch_bounds__(128) attn_decode_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
+                                                                T* __restrict__ out, int Hq, int Hkv, int G, int splits) {
+  const int64_t bh = blockIdx.x, b = bh / Hq;
+  const int h = static_cast<int>(bh % Hq), hk = h / G, r = h % G;
+  const int64_t base = (b * Hkv + hk) * splits;
+  float m_all = -INFINITY;
+  for (int s = 0; s < splits; ++s) m_all = fmaxf(m_all, part_ml[((base + s) * G + r) * 2]);
+  const float m_use = m_all == -INFINITY ? 0.f : m_all;
+  float acc = 0.f, l = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const int64_t i = (base + s) * G + r;
+    const float f = exp2f((part_ml[i * 2] - m_use) * LOG2E);
+    l += part_ml[i * 2 + 1] * f;
+    acc += part_acc[i * HD + threadIdx.x] * f;
+  }
+  out[bh * HD + threadIdx.x] = from_f32<T>(l > 0.f ? acc / l : 0.f);
+}
+
+// ===========================================================================
+// Prefill: grid = (ceil(T/64), Hq, B), 4 warps x 16 query rows, all keys streamed.
+// ===========================================================================
+struct PrefillParams {
+  const void* q; const void* k; const void* v; const void* mask; void* out;
+  int64_t B, T, S;
+  int Hq, Hkv;
+  int64_t qs[3], ks[3], vs[3];
+  int64_t mask_b, mask_t;
+  float scale;
+  int mask_dtype;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(128) attn_prefill_kernel(const __grid_constant__ PrefillParams p) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+  const int h = blockIdx.y, hk = h / (p.Hq / p.Hkv);
+  const int64_t b = blockIdx.z;
+  const int64_t row0 = static_cast<int64_t>(blockIdx.x) * 64 + warp * 16;
+  if (row0 >= p.T) return;
+  const int64_t r_lo = row0 + g, r_hi = row0 + g + 8;
+  const T* qb = static_cast<const T*>(p.q) + b * p.qs[0] + h * p.qs[1];
+  AttnWarp<T> w;
+  w.init();
+  w.load_q(r_lo < p.T ? qb + r_lo * p.qs[2] : nullptr, r_hi < p.T ? qb + r_hi * p.qs[2] : nullptr, t);
+  const T* kbase = static_cast<const T*>(p.k) + b * p.ks[0] + hk * p.ks[1];
+  const T* vbase = static_cast<const T*>(p.v) + b * p.vs[0] + hk * p.vs[1];
+  const int64_t mrow[2] = {b * p.mask_b + min(r_lo, p.T - 1) * p.mask_t, b * p.mask_b + min(r_hi, p.T - 1) * p.mask_t};
+
+  for (int64_t kb = 0; kb < p.S; kb += 16) {
+    float add[2][4];
+    bool any = !p.mask;
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int64_t key = kb + 8 * j + 2 * t + (e & 1);
+        float mv = 0.f;
+        if (p.mask && key < p.S) {
+          mv = load_as_f32(p.mask, mrow[e >> 1] + key, p.mask_dtype);
+          any = any || mv > MASKED;
+        }
+        add[j][e] = mv;
+      }
+    if (!__any_sync(0xffffffffu, any)) continue;  // whole 16x16 tile masked out
+    w.step(kbase, vbase, p.ks[2], p.vs[2], kb, p.S, p.scale, add, g, t);
+  }
+
+  // out[b][row][h][:]
+  T* ob = static_cast<T*>(p.out) + (b * p.T * p.Hq + h) * HD;
+#pragma unroll
+  for (int hh = 0; hh < 2; ++hh) {
+    const int64_t row = hh ? r_hi : r_lo;
+    if (row >= p.T) continue;
+    const float inv = w.l[hh] > 0.f ? 1.f / w.l[hh] : 0.f;
+    T* orow = ob + row * p.Hq * HD;
+#pragma unroll
+    for (int a = 0; a < 2; ++a)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        float vals[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) vals[j] = w.o[a][j][2 * hh + e] * inv;
+        *reinterpret_cast<uint4*>(orow + 64 * a + 8 * (2 * t + e)) = pack8<T>(vals);
+      }
+  }
+}
+
+struct DecodePlan { int split_len; int splits; };
+
+static DecodePlan plan_decode(int64_t B, int Hkv, int64_t S) {
+  const int64_t want = 2 * 148;  // fixed so that the workspace size does not depend on the device
+  int len = 256;
+  while (len > 64 && B * Hkv * ceil_div(S, len) < want) len >>= 1;
+  DecodePlan d;
+  d.split_len = len;
+  d.splits = static_cast<int>(ceil_div(S, len));
+  return d;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int64_t b200_attn_decode_workspace_bytes(int64_t B, int Hq, int Hkv, int64_t S, int D) {
+  if (B <= 0 || Hkv <= 0 || Hq <= 0 || S <= 0) return 0;
+  const DecodePlan d = plan_decode(B, Hkv, S);
+  const int G = Hq / Hkv;
+  return B * Hkv * d.splits * G * (static_cast<int64_t>(D) + 2) * 4;
+}
+
+extern "C" int b200_attn_decode(const void* q, const void* k, const void* v, const void* mask, void* out, int64_t B, int Hq,
+                                int Hkv, int64_t S, int D, int64_t q_batch_stride, int64_t kv_batch_stride,
+                                int64_t kv_head_stride, int64_t mask_batch_stride, float scale, int dtype, void* workspace,
+                                int64_t workspace_bytes, void* stream) {
+  B200_CHECK_ARG(q && k && v && out && B >= 0 && Hq > 0 && Hkv > 0 && S > 0, "b200_attn_decode: bad arguments");
+  B200_CHECK_ARG(D == HD, "b200_attn_decode: head_dim %d not supported (128 only)", D);
+  B200_CHECK_ARG(Hq % Hkv == 0 && Hq / Hkv <= 8, "b200_attn_decode: query heads per KV head must divide and be <= 8");
+  B200_CHECK_ARG(B <= 65535 && Hkv <= 65535, "b200_attn_decode: batch or head count too large");
+  if (B == 0) return B200_OK;
+  if (!(aligned16(q) && aligned16(k) && aligned16(v) && q_batch_stride % 8 == 0 && kv_batch_stride % 8 == 0 && kv_head_stride % 8 == 0))
+    B200_FAIL(B200_EALIGN, "b200_attn_decode: operands must be 16-byte aligned with strides multiple of 8");
+  const DecodePlan d = plan_decode(B, Hkv, S);
+  const int64_t need = b200_attn_decode_workspace_bytes(B, Hq, Hkv, S, D);
+  if (!workspace || workspace_bytes < need)
+    B200_FAIL(B200_EINVAL, "b200_attn_decode: workspace of %lld bytes required (got %lld)", (long long)need, (long long)workspace_bytes);
+  DecodeParams p;
+  p.q = q; p.k = k; p.v = v; p.mask = mask;
+  p.G = Hq / Hkv;
+  p.part_acc = static_cast<float*>(workspace);
+  p.part_ml = p.part_acc + B * Hkv * d.splits * p.G * HD;
+  p.B = B; p.S = S; p.Hq = Hq; p.Hkv = Hkv;
+  p.q_bs = q_batch_stride; p.kv_bs = kv_batch_stride; p.kv_hs = kv_head_stride; p.mask_bs = mask_batch_stride;
+  p.split_len = d.split_len; p.splits = d.splits; p.scale = scale; p.mask_dtype = dtype;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  dim3 grid(static_cast<unsigned>(d.splits), static_cast<unsigned>(Hkv), static_cast<unsigned>(B));
+  B200_DISPATCH_HALF(dtype, T, {
+    attn_decode_kernel<T><<<grid, 128, 0, st>>>(p);
+    attn_decode_merge_kernel<T><<<static_cast<unsigned>(B * Hq), 128, 0, st>>>(p.part_acc, p.part_ml, static_cast<T*>(out), Hq, Hkv,
+                                                                               p.G, d.splits);
+  });
+  B200_CHECK_LAUNCH("attn_decode_kernel");
+  return B200_OK;
+}
+
+extern "C" int b200_attn_prefill(const void* q, const void* k, const void* v, const void* mask, void* out, int64_t B, int Hq,
+                                 int Hkv, int64_t T, int64_t S, int D, const int64_t q_strides[3], const int64_t k_strides[3],
+                                 const int64_t v_strides[3], int64_t mask_b, int64_t mask_t, float scale, int dtype,
+                                 void* stream) {
+  B200_CHECK_ARG(q && k && v && out && B >= 0 && Hq > 0 && Hkv > 0 && T >= 0 && S > 0 && q_strides && k_strides && v_strides,
+                 "b200_attn_prefill: bad arguments");
+  B200_CHECK_ARG(D == HD, "b200_attn_prefill: head_dim %d not supported (128 only)", D);
+  B200_CHECK_ARG(Hq % Hkv == 0, "b200_attn_prefill: Hq must be a multiple of Hkv");
+  B200_CHECK_ARG(B <= 65535 && Hq <= 65535, "b200_attn_prefill: batch or head count too large");
+  if (B == 0 || T == 0) return B200_OK;
+  bool ok = aligned16(q) && aligned16(k) && aligned16(v) && aligned16(out);
+  for (int i = 0; i < 3; ++i) ok = ok && q_strides[i] % 8 == 0 && k_strides[i] % 8 == 0 && v_strides[i] % 8 == 0;
+  if (!ok) B200_FAIL(B200_EALIGN, "b200_attn_prefill: operands must be 16-byte aligned with strides multiple of 8");
+  PrefillParams p;
+  p.q = q; p.k = k; p.v = v; p.mask = mask; p.out = out; p.B = B; p.T = T; p.S = S; p.Hq = Hq; p.Hkv = Hkv;
+  for (int i = 0; i < 3; ++i) { p.qs[i] = q_strides[i]; p.ks[i] = k_strides[i]; p.vs[i] = v_strides[i]; }
+  p.mask_b = mask_b; p.mask_t = mask_t; p.scale = scale; p.mask_dtype = dtype;
+  dim3 grid(static_cast<unsigned>(ceil_div(T, 64)), static_cast<unsigned>(Hq), static_cast<unsigned>(B));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  B200_DISPATCH_HALF(dtype, T_, { attn_prefill_kernel<T_><<<grid, 128, 0, st>>>(p); });
+  B200_CHECK_LAUNCH("attn_prefill_kernel");
+  return B200_OK;
+}

@@ -1,0 +1,196 @@
+// Gather / scatter kernels (embedding, KV-cache index_copy) and rotary embedding.
+// Gathers and scatters move raw bytes, so their results are bit-exact.
+#include "common.cuh"
+
+namespace b200 {
+
+// out[s, :] = table[ids[s], :], rows as raw bytes.  blockDim.x threads walk one row.
+template <bool VEC16>
+__global__ void __launch_bounds__(256) embedding_kernel(const uint8_t* __restrict__ table, const void* __restrict__ ids,
+                                                        uint8_t* __restrict__ out, int64_t vocab, int64_t row_bytes,
+                                                        int ids_dtype) {
+  const int64_t s = blockIdx.x;
+  const int64_t id = load_index(ids, s, ids_dtype);
+  const bool ok = id >= 0 && id < vocab;
+  const uint8_t* src = table + (ok ? id : 0) * row_bytes;
+  uint8_t* dst = out + s * row_bytes;
+  if (VEC16) {
+    const int64_t n = row_bytes >> 4;
+    for (int64_t i = threadIdx.x; i < n; i += blockDim.x)
+      reinterpret_cast<uint4*>(dst)[i] = ok ? ld_global_nc_v4(reinterpret_cast<const uint4*>(src) + i) : make_uint4(0, 0, 0, 0);
+  } else {
+    for (int64_t i = threadIdx.x; i < row_bytes; i += blockDim.x) dst[i] = ok ? src[i] : uint8_t(0);
+  }
+}
+
+// dst[o, index[l], :] = src[o, l, :]; one block per (o, l) row.
+template <bool VEC16>
+__global__ void __launch_bounds__(128) index_copy_rows_kernel(uint8_t* __restrict__ dst, const uint8_t* __restrict__ src,
+                                                              const void* __restrict__ index, int64_t dim_size,
+                                                              int64_t inner_bytes, int64_t n_index, int64_t src_outer_bytes,
+                                                              int64_t src_index_bytes, int index_dtype) {
+  const int64_t o = blockIdx.x / n_index, l = blockIdx.x % n_index;
+  int64_t pos = load_index(index, l, index_dtype);
+  if (pos < 0) pos += dim_size;
+  if (pos < 0 || pos >= dim_size) return;  // out-of-range index: leave the destination untouched
+  const uint8_t* s = src + o * src_outer_bytes + l * src_index_bytes;
+  uint8_t* d = dst + (o * dim_size + pos) * inner_bytes;
+  if (VEC16) {
+    const int64_t n = inner_bytes >> 4;
+    for (int64_t i = threadIdx.x; i < n; i += blockDim.x) reinterpret_cast<uint4*>(d)[i] = reinterpret_cast<const uint4*>(s)[i];
+  } else {
+    for (int64_t i = threadIdx.x; i < inner_bytes; i += blockDim.x) d[i] = s[i];
+  }
+}
+
+// cos/sin tables: angle = fp32(position) * inv_freq[d mod half] as one fp32 product.
+template <typename TO>
+__global__ void __launch_bounds__(128) rope_table_kernel(const float* __restrict__ inv_freq, const void* __restrict__ positions,
+                                                         TO* __restrict__ cos_out, TO* __restrict__ sin_out, int64_t n_pos,
+                                                         int head_dim, int pos_dtype) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n_pos * head_dim) return;
+  const int64_t p = i / head_dim;
+  const int d = static_cast<int>(i % head_dim);
+  const float pos = pos_dtype == B200_F32 ? static_cast<const float*>(positions)[p]
+                                          : static_cast<float>(load_index(positions, p, pos_dtype));
+  const float ang = __fmul_rn(pos, inv_freq[d % (head_dim >> 1)]);
+  cos_out[i] = from_f32<TO>(cosf(ang));
+  sin_out[i] = from_f32<TO>(sinf(ang));
+}
+
+struct RopeParams {
+  const void* x;
+  const void* cos_t;
+  const void* sin_t;
+  void* y;
+  void* cache;
+  const void* cache_pos;
+  int64_t B, H, T;
+  int D;
+  int64_t xs[3];  // element strides of x over (b, h, t); D is contiguous
+  int64_t cache_len;
+  int pos_dtype;
+};
+
+// One thread per 8 consecutive head dims.
+template <typename T>
+__global__ void __launch_bounds__(128) rope_rotate_kernel(const __grid_constant__ RopeParams p) {
+  const int packs = p.D >> 3, half_packs = packs >> 1;
+  const int64_t gid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t total = p.B * p.H * p.T * packs;
+  if (gid >= total) return;
+  const int pk = static_cast<int>(gid % packs);
+  int64_t r = gid / packs;
+  const int64_t t = r % p.T; r /= p.T;
+  const int64_t h = r % p.H;
+  const int64_t b = r / p.H;
+  const T* xr = static_cast<const T*>(p.x) + b * p.xs[0] + h * p.xs[1] + t * p.xs[2];
+  const int64_t tab = (b * p.T + t) * p.D;
+  float xv[8], ov[8], c[8], s[8];
+  unpack8<T>(*(reinterpret_cast<const uint4*>(xr) + pk), xv);
+  const int opk = pk < half_packs ? pk + half_packs : pk - half_packs;
+  unpack8<T>(*(reinterpret_cast<const uint4*>(xr) + opk), ov);
+  unpack8<T>(__ldg(reinterpret_cast<const uint4*>(static_cast<const T*>(p.cos_t) + tab) + pk), c);
+  unpack8<T>(__ldg(reinterpret_cast<const uint4*>(static_cast<const T*>(p.sin_t) + tab) + pk), s);
+  const float sign = pk < half_packs ? -1.f : 1.f;
+  float out[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const float a = round_as<T>(xv[k] * c[k]);
+    const float rb = round_as<T>(sign * ov[k] * s[k]);
+    out[k] = a + rb;
+  }
+  T* dst;
+  if (p.cache) {
+    int64_t pos = load_index(p.cache_pos, t, p.pos_dtype);
+    if (pos < 0) pos += p.cache_len;
+    if (pos < 0 || pos >= p.cache_len) return;
+    dst = static_cast<T*>(p.cache) + ((b * p.H + h) * p.cache_len + pos) * p.D;
+  } else {
+    dst = static_cast<T*>(p.y) + ((b * p.H + h) * p.T + t) * p.D;
+  }
+  reinterpret_cast<uint4*>(dst)[pk] = pack8<T>(out);
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_embedding(const void* table, const void* ids, void* out, int64_t n_ids, int64_t vocab,
+                              int64_t row_bytes, int ids_dtype, void* stream) {
+  B200_CHECK_ARG(table && ids && out && n_ids >= 0 && vocab > 0 && row_bytes > 0, "b200_embedding: bad arguments");
+  B200_CHECK_ARG(ids_dtype == B200_I64 || ids_dtype == B200_I32, "b200_embedding: ids must be int32/int64");
+  if (n_ids == 0) return B200_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const bool vec = row_bytes % 16 == 0 && aligned16(table) && aligned16(out);
+  const int threads = row_bytes >= 16 * 256 ? 256 : (row_bytes >= 16 * 64 ? 64 : 32);
+  if (vec) embedding_kernel<true><<<static_cast<unsigned>(n_ids), threads, 0, st>>>(
+        static_cast<const uint8_t*>(table), ids, static_cast<uint8_t*>(out), vocab, row_bytes, ids_dtype);
+  else embedding_kernel<false><<<static_cast<unsigned>(n_ids), threads, 0, st>>>(
+        static_cast<const uint8_t*>(table), ids, static_cast<uint8_t*>(out), vocab, row_bytes, ids_dtype);
+  B200_CHECK_LAUNCH("embedding_kernel");
+  return B200_OK;
+}
+
+extern "C" int b200_index_copy(const void* base, void* dst, const void* src, const void* index, int64_t outer,
+                               int64_t dim_size, int64_t inner, int64_t n_index, int64_t src_outer_stride,
+                               int64_t src_index_stride, int elem_bytes, int index_dtype, void* stream) {
+  B200_CHECK_ARG(base && dst && src && index && outer >= 0 && dim_size > 0 && inner > 0 && n_index >= 0 && elem_bytes > 0,
+                 "b200_index_copy: bad arguments");
+  B200_CHECK_ARG(index_dtype == B200_I64 || index_dtype == B200_I32, "b200_index_copy: index must be int32/int64");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (base != dst) {
+    cudaError_t e = cudaMemcpyAsync(dst, base, static_cast<size_t>(outer * dim_size * inner) * elem_bytes,
+                                    cudaMemcpyDeviceToDevice, st);
+    if (e != cudaSuccess) B200_FAIL(B200_ELAUNCH, "b200_index_copy: %s", cudaGetErrorString(e));
+  }
+  if (outer == 0 || n_index == 0) return B200_OK;
+  const int64_t inner_bytes = inner * elem_bytes, so = src_outer_stride * elem_bytes, si = src_index_stride * elem_bytes;
+  const bool vec = inner_bytes % 16 == 0 && so % 16 == 0 && si % 16 == 0 && aligned16(dst) && aligned16(src);
+  const unsigned grid = static_cast<unsigned>(outer * n_index);
+  const int threads = inner_bytes >= 16 * 128 ? 128 : 32;
+  if (vec) index_copy_rows_kernel<true><<<grid, threads, 0, st>>>(static_cast<uint8_t*>(dst), static_cast<const uint8_t*>(src),
+                                                                  index, dim_size, inner_bytes, n_index, so, si, index_dtype);
+  else index_copy_rows_kernel<false><<<grid, threads, 0, st>>>(static_cast<uint8_t*>(dst), static_cast<const uint8_t*>(src),
+                                                               index, dim_size, inner_bytes, n_index, so, si, index_dtype);
+  B200_CHECK_LAUNCH("index_copy_rows_kernel");
+  return B200_OK;
+}
+
+extern "C" int b200_rope_table(const float* inv_freq, const void* positions, void* cos_out, void* sin_out, int64_t n_pos,
+                               int head_dim, int pos_dtype, int out_dtype, void* stream) {
+  B200_CHECK_ARG(inv_freq && positions && cos_out && sin_out && n_pos >= 0 && head_dim > 0 && head_dim % 2 == 0,
+                 "b200_rope_table: bad arguments");
+  if (n_pos == 0) return B200_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const unsigned grid = static_cast<unsigned>(ceil_div(n_pos * head_dim, 128));
+  B200_DISPATCH_FLOAT(out_dtype, T, {
+    rope_table_kernel<T><<<grid, 128, 0, st>>>(inv_freq, positions, static_cast<T*>(cos_out), static_cast<T*>(sin_out), n_pos,
+                                               head_dim, pos_dtype);
+  });
+  B200_CHECK_LAUNCH("rope_table_kernel");
+  return B200_OK;
+}
+
+extern "C" int b200_rope_rotate(const b200_tensor* x, const void* cos_t, const void* sin_t, void* y, void* kv_cache,
+                                const void* cache_pos, int64_t cache_len, int pos_dtype, void* stream) {
+  B200_CHECK_ARG(x && x->data && x->ndim == 4 && cos_t && sin_t && (y || kv_cache), "b200_rope_rotate: bad arguments");
+  B200_CHECK_ARG(x->stride[3] == 1 && x->shape[3] % 16 == 0, "b200_rope_rotate: head_dim must be contiguous and a multiple of 16");
+  B200_CHECK_ARG(!kv_cache || cache_pos, "b200_rope_rotate: cache write needs cache_pos");
+  RopeParams p;
+  p.x = x->data; p.cos_t = cos_t; p.sin_t = sin_t; p.y = y; p.cache = kv_cache; p.cache_pos = cache_pos;
+  p.B = x->shape[0]; p.H = x->shape[1]; p.T = x->shape[2]; p.D = static_cast<int>(x->shape[3]);
+  for (int i = 0; i < 3; ++i) p.xs[i] = x->stride[i];
+  p.cache_len = cache_len; p.pos_dtype = pos_dtype;
+  const bool ok = aligned16(x->data) && aligned16(cos_t) && aligned16(sin_t) && aligned16(kv_cache ? kv_cache : y) &&
+                  p.xs[0] % 8 == 0 && p.xs[1] % 8 == 0 && p.xs[2] % 8 == 0;
+  if (!ok) B200_FAIL(B200_EALIGN, "b200_rope_rotate: operands must be 16-byte aligned with strides multiple of 8");
+  const int64_t total = p.B * p.H * p.T * (p.D >> 3);
+  if (total == 0) return B200_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const unsigned grid = static_cast<unsigned>(ceil_div(total, 128));
+  B200_DISPATCH_HALF(x->dtype, T, { rope_rotate_kernel<T><<<grid, 128, 0, st>>>(p); });
+  B200_CHECK_LAUNCH("rope_rotate_kernel");
+  return B200_OK;
+}
