@@ -157,6 +157,9 @@ class IRInterpreter:
             cos, sin = _rope_tables(ins[0], ins[1], _TORCH_DTYPES[outs[0]["dtype"]])
             env[outs[0]["name"]], env[outs[1]["name"]] = cos, sin
             return
+        if op == "aten.detach_.default":  # in-place detach is refused on views; the value is the same
+            env[outs[0]["name"]] = ins[0].detach()
+            return
         fn = _resolve_op(op)
         if fn is None:
             raise ValueError(f"oracle: unknown op_type {op!r}")

@@ -1,0 +1,430 @@
+"""Run a ``CUDAProgram`` on one B200.
+
+Interface of the reference executor (cuda_runtime/cuda_executor.py:66-176):
+``CUDAExecutor(program)`` does all one-time work, ``run(inputs, weights)`` takes
+name -> ``CUDABuffer`` dicts (weights keyed by placeholder) and returns
+``{output name: CUDABuffer}``.
+
+What happens inside is different.  The reference walks ~1.3 k Python dispatches per
+decode token (NVRTC kernels and ``cupy.matmul``).  Here
+
+1. *bind*: every step is turned once into ``(entry point, argument tuple)`` with all
+   device pointers resolved - intermediates live at fixed offsets of one arena,
+   inputs and weights at the addresses of the caller's buffers;
+2. *launch*: the first run issues the calls one by one through ctypes; the
+   second run with the same buffer addresses captures them into a CUDA graph, and
+   every later run is a single graph replay;
+3. weights are prepared once per weight set (dtype narrowing, batch-norm folding
+   and channels-last repacking of convolution filters) by library kernels.
+
+Outputs are views into the arena, or - for an in-place ``index_copy`` - the caller's
+own input buffer; they stay valid until the next ``run`` (the reference reuses its
+pool the same way, cuda_executor.py:90-95).  Not re-entrant; one executor per GPU.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from typing import Any
+
+from cuda_compiler.cuda_codegen import EW_OPCODES
+from cuda_compiler.cuda_program import AliasStep, CUDAProgram, TensorView
+from cuda_runtime import native
+from cuda_runtime.native import DTYPE_BYTES, DTYPE_CODES
+
+try:
+    import torch
+except ImportError:  # pragma: no cover
+    torch = None
+
+
+class _Plan:
+    """Launch list bound to one set of buffer addresses."""
+
+    def __init__(self):
+        self.launches: list[tuple[Any, tuple]] = []   # (cfunc, args without the trailing stream)
+        self.keepalive: list[Any] = []
+        self.outputs: dict[str, Any] = {}
+        self.graph = None
+        self.runs = 0
+        self.n_kernels = 0
+
+
+class CUDAExecutor:
+    def __init__(self, program: CUDAProgram, device_id: int = 0, use_cuda_graph: bool = True):
+        if torch is None:
+            raise RuntimeError("PyTorch is not installed; it provides device memory for the CUDA executor")
+        self._lib = native.load()
+        self._device = native.device_string(device_id)
+        self._on_gpu = self._device.startswith("cuda")
+        if self._on_gpu and not torch.cuda.is_available():
+            raise RuntimeError("no CUDA device is available")
+        self._program = program
+        self._compute_dtype = program.compute_dtype
+        self._use_graph = use_cuda_graph and self._on_gpu
+        self._allocs = {a.name: a for a in program.buffer_allocations}
+        self._input_names = [s.name for s in program.input_specs]
+        self._input_set = set(self._input_names)
+        # zero-filled once: padding channels rely on it, everything else is overwritten before use
+        self._arena = torch.zeros(max(int(program.arena_bytes), 256), dtype=torch.uint8, device=self._device)
+        ws_lin = ws_att = 0
+        for step in program.steps:
+            p = getattr(step, "params", None) or {}
+            if p.get("op") == "linear" and p.get("workspace"):
+                ws_lin = max(ws_lin, int(self._lib.b200_linear_workspace_bytes(p["M"], p["N"], p["K"])))
+            if p.get("op") == "attention" and p.get("workspace"):
+                ws_att = max(ws_att, int(self._lib.b200_attn_decode_workspace_bytes(p["B"], p["Hq"], p["Hkv"], p["S"], p["D"])))
+        # split-K partial sums must start at zero; the kernel restores zeros before it exits
+        self._ws = {"__ws_splitk": torch.zeros(max(ws_lin, 256), dtype=torch.uint8, device=self._device),
+                    "__ws_attn": torch.empty(max(ws_att, 256), dtype=torch.uint8, device=self._device)}
+        self._weights_id = None
+        self._weights_len = -1
+        self._weight_tensors: dict[str, Any] = {}
+        self._weight_cache: dict[tuple[str, str], Any] = {}
+        self._prepared: dict[str, Any] = {}
+        self._plans: dict[tuple, _Plan] = {}
+        self.last_launch_count = 0
+
+    # ------------------------------------------------------------------ public
+    def run(self, inputs: dict[str, Any], weights: dict[str, Any]) -> dict[str, Any]:
+        from cuda_runtime.cuda_backend import CUDABuffer
+
+        if self._weights_id != id(weights) or len(weights) != self._weights_len:
+            self._load_weights(weights)
+        tensors = {n: inputs[n].native_handle for n in self._input_names if n in inputs}
+        key = tuple((n, t.data_ptr(), t.dtype) for n, t in tensors.items())
+        plan = self._plans.get(key)
+        if plan is None:
+            if len(self._plans) >= 8:
+                self._plans.pop(next(iter(self._plans)))
+            plan = self._bind(tensors)
+            self._plans[key] = plan
+        self._launch(plan)
+        self.last_launch_count = plan.n_kernels
+        return {name: CUDABuffer(t, logical_shape=tuple(t.shape)) for name, t in plan.outputs.items()}
+
+    # --------------------------------------------------------------- launching
+    def _stream_ptr(self) -> int:
+        return torch.cuda.current_stream().cuda_stream if self._on_gpu else 0
+
+    def _issue(self, plan: _Plan, stream: int) -> None:
+        for fn, args in plan.launches:
+            rc = fn(*args, stream)
+            if rc != 0:
+                native.check(rc, getattr(fn, "__name__", "call"))
+
+    def _launch(self, plan: _Plan) -> None:
+        plan.runs += 1
+        if plan.graph is not None:
+            plan.graph.replay()
+            return
+        if self._use_graph and plan.runs == 2:
+            graph = torch.cuda.CUDAGraph()
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.graph(graph, stream=side):
+                self._issue(plan, torch.cuda.current_stream().cuda_stream)
+            plan.graph = graph
+            graph.replay()
+            return
+        self._issue(plan, self._stream_ptr())
+
+    # ----------------------------------------------------------------- weights
+    def _load_weights(self, weights: dict[str, Any]) -> None:
+        self._weights_id = id(weights)
+        self._weights_len = len(weights)
+        self._weight_tensors = {n: b.native_handle for n, b in weights.items()}
+        self._weight_cache.clear()
+        self._prepared.clear()
+        self._plans.clear()
+        for key, const in (self._program.constants or {}).items():
+            for ph, k in self._program.weight_name_mapping.items():
+                if k == key and ph not in self._weight_tensors:
+                    self._weight_tensors[ph] = torch.tensor(const.get("data", []), dtype=getattr(torch, const["dtype"]),
+                                                            device=self._device).reshape(const["shape"])
+        stream = self._stream_ptr()
+        for prep in self._program.weight_preps:
+            if prep.kind == "conv_fold":
+                self._prep_conv(prep, stream)
+            else:
+                raise RuntimeError(f"unknown weight preparation {prep.kind}")
+
+    def _raw_weight(self, name: str):
+        t = self._weight_tensors.get(name)
+        if t is None:
+            raise RuntimeError(f"weight '{name}' was not provided to CUDAExecutor.run")
+        return t
+
+    def _weight(self, name: str, dtype: str):
+        """Weight ``name`` in ``dtype``; narrowed/widened once on the device if the
+        upload has another floating type."""
+        t = self._raw_weight(name)
+        want = getattr(torch, dtype)
+        if t.dtype == want and t.is_contiguous():
+            return t
+        cached = self._weight_cache.get((name, dtype))
+        if cached is None:
+            src = t if t.is_contiguous() else t.contiguous()
+            cached = torch.empty(src.shape, dtype=want, device=self._device)
+            self._convert(src, cached)
+            self._weight_cache[(name, dtype)] = cached
+        return cached
+
+    def _convert(self, src, dst) -> None:
+        """dst = cast(src) through the library's strided copy (both contiguous)."""
+        n = src.numel()
+        if n == 0:
+            return
+        a = native.make_tensor(dst.data_ptr(), str(dst.dtype).replace("torch.", ""), (n,), (1,))
+        b = native.make_tensor(src.data_ptr(), str(src.dtype).replace("torch.", ""), (n,), (1,))
+        native.check(self._lib.b200_strided_copy(C.byref(a), C.byref(b), self._stream_ptr()), "weight cast")
+
+    def _prep_conv(self, prep, stream: int) -> None:
+        p = prep.params
+        w = self._raw_weight(prep.inputs[0])
+        opt = [self._raw_weight(n) if n is not None else None for n in prep.inputs[1:]]
+        params = [t for t in opt if t is not None]
+        pdt = params[0].dtype if params else torch.float32
+        if any(t.dtype != pdt for t in params):
+            raise RuntimeError("convolution bias and batch-norm parameters must share one dtype")
+        out_dt = getattr(torch, p["dtype"])
+        wout = torch.empty(p["O"] * p["KH"] * p["KW"] * p["I_pad"], dtype=out_dt, device=self._device)
+        bout = torch.empty(p["O"], dtype=torch.float32, device=self._device)
+        name = lambda t: str(t.dtype).replace("torch.", "")
+        ptr = lambda t: t.data_ptr() if t is not None else None
+        wc = w if w.is_contiguous() else w.contiguous()
+        native.check(self._lib.b200_conv_weight_prep(
+            wc.data_ptr(), ptr(opt[0]), ptr(opt[1]), ptr(opt[2]), ptr(opt[3]), ptr(opt[4]), wout.data_ptr(), bout.data_ptr(),
+            p["O"], p["I"], p["KH"], p["KW"], p["I_pad"], float(p["eps"]), DTYPE_CODES[name(wc)],
+            DTYPE_CODES[name(params[0])] if params else 0, DTYPE_CODES[p["dtype"]], stream), "conv weight prep")
+        self._prepared[prep.outputs[0]] = wout
+        self._prepared[prep.outputs[1]] = bout
+
+    # ----------------------------------------------------------------- binding
+    def _bind(self, inputs: dict[str, Any]) -> _Plan:
+        plan = _Plan()
+        self._cur_inputs = inputs
+        self._cur_plan = plan
+        self._staged: dict[str, Any] = {}
+        for step in self._program.steps:
+            if isinstance(step, AliasStep):
+                continue
+            p = step.params
+            getattr(self, "_bind_" + p["op"])(plan, step, p)
+        plan.n_kernels = len(plan.launches) + sum(1 for s in self._program.steps
+                                                   if getattr(s, "params", None) and s.params.get("op") == "attention" and s.params["decode"])
+        for spec in self._program.output_specs:
+            view = self._program.views.get(spec.name)
+            if view is None:
+                continue
+            plan.outputs[spec.name] = self._as_torch(view)
+        return plan
+
+    def _base(self, view: TensorView, any_dtype: bool = False):
+        """(device address of element 0 of the view's buffer, dtype actually stored there)."""
+        name = view.buffer
+        alloc = self._allocs.get(name)
+        if alloc is not None and name not in self._ws:
+            return self._arena.data_ptr() + alloc.offset, view.dtype
+        if name in self._ws:
+            return self._ws[name].data_ptr(), view.dtype
+        if name in self._input_set:
+            t = self._cur_inputs.get(name)
+            if t is None:
+                raise RuntimeError(f"graph input '{name}' was not provided to CUDAExecutor.run")
+            have = str(t.dtype).replace("torch.", "")
+            if have == "bool":
+                have = "uint8"
+            if have == view.dtype or any_dtype:
+                if not t.is_contiguous():
+                    raise RuntimeError(f"graph input '{name}' must be contiguous")
+                return t.data_ptr(), have
+            staged = self._staged.get(name)
+            if staged is None:  # per-run conversion into the dtype the kernels expect
+                staged = torch.empty(t.shape, dtype=getattr(torch, view.dtype), device=self._device)
+                self._staged[name] = staged
+                n = t.numel()
+                a = native.make_tensor(staged.data_ptr(), view.dtype, (n,), (1,))
+                b = native.make_tensor(t.data_ptr(), have, (n,), (1,))
+                self._cur_plan.keepalive += [a, b, staged]
+                self._cur_plan.launches.append((self._lib.b200_strided_copy, (C.byref(a), C.byref(b))))
+            return staged.data_ptr(), view.dtype
+        if name in self._prepared:
+            return self._prepared[name].data_ptr(), view.dtype
+        return self._weight(name, view.dtype).data_ptr(), view.dtype
+
+    def _ptr(self, view: TensorView | None) -> int | None:
+        if view is None:
+            return None
+        base, _ = self._base(view)
+        return base + view.offset * DTYPE_BYTES[view.dtype]
+
+    def _wptr(self, name: str | None, dtype: str | None = None) -> int | None:
+        if name is None:
+            return None
+        view = self._program.views[name]
+        return self._ptr(view if dtype is None else TensorView(view.buffer, view.offset, view.shape, view.strides, dtype))
+
+    def _tensor(self, plan: _Plan, view: TensorView, any_dtype: bool = False):
+        base, dtype = self._base(view, any_dtype)
+        t = native.make_tensor(base + view.offset * DTYPE_BYTES[dtype], dtype, view.shape, view.strides)
+        plan.keepalive.append(t)
+        return t
+
+    def _as_torch(self, view: TensorView):
+        base, dtype = self._base(view)
+        name = view.buffer
+        if name in self._input_set and name not in self._staged:
+            root = self._cur_inputs[name]
+        elif name in self._staged:
+            root = self._staged[name]
+        elif name in self._allocs and name not in self._ws:
+            a = self._allocs[name]
+            root = self._arena[a.offset:a.offset + a.size_bytes].view(getattr(torch, dtype))
+        elif name in self._prepared:
+            root = self._prepared[name]
+        else:
+            root = self._weight(name, view.dtype)
+        flat = root.reshape(-1)  # as_strided offsets are absolute in the storage
+        return torch.as_strided(flat, tuple(view.shape), tuple(view.strides), flat.storage_offset() + view.offset)
+
+    # one binder per library entry point --------------------------------------------
+    def _bind_ew_chain(self, plan, step, p):
+        out = self._tensor(plan, p["out_view"])
+        ins = (native.Tensor * len(p["in_views"]))()
+        for i, v in enumerate(p["in_views"]):
+            base, dtype = self._base(v, any_dtype=True)
+            ins[i] = native.make_tensor(base + v.offset * DTYPE_BYTES[dtype], dtype, v.shape, v.strides)
+        ops = (native.EwOp * len(p["program"]))()
+        for i, (name, a, b, rd, imm) in enumerate(p["program"]):
+            ops[i] = native.EwOp(EW_OPCODES[name], a, b, DTYPE_CODES[rd], float(imm))
+        plan.keepalive += [ins, ops]
+        plan.launches.append((self._lib.b200_ew_chain, (C.byref(out), ins, len(p["in_views"]), ops, len(p["program"]))))
+
+    def _bind_strided_copy(self, plan, step, p):
+        dst = self._tensor(plan, p["out_view"])
+        src = self._tensor(plan, p["in_view"], any_dtype=True)
+        plan.launches.append((self._lib.b200_strided_copy, (C.byref(dst), C.byref(src))))
+
+    def _bind_fill(self, plan, step, p):
+        y = p["y"]
+        plan.launches.append((self._lib.b200_fill, (self._ptr(y), y.numel, float(p["fill_value"]), DTYPE_CODES[y.dtype])))
+
+    def _bind_rmsnorm(self, plan, step, p):
+        x, y = p["x"], p["y"]
+        plan.launches.append((self._lib.b200_rmsnorm, (self._ptr(x), self._wptr(p["w"], x.dtype), self._ptr(y), p["rows"], p["cols"],
+                                                       x.strides[0] if p["rows"] > 1 else p["cols"], p["cols"], float(p["eps"]),
+                                                       DTYPE_CODES[x.dtype], int(p["round_mid"]))))
+
+    def _bind_softmax(self, plan, step, p):
+        x, y, m = p["x"], p["y"], p["mask"]
+        d0, d1, d2 = p["dims"]
+        ms = p["mask_strides"]
+        plan.launches.append((self._lib.b200_softmax, (self._ptr(x), self._ptr(m), self._ptr(y), d0, d1, d2, p["cols"], ms[0], ms[1],
+                                                       ms[2], float(p["scale"]), DTYPE_CODES[x.dtype],
+                                                       DTYPE_CODES[m.dtype] if m is not None else 0, DTYPE_CODES[y.dtype],
+                                                       int(p["round_steps"]))))
+
+    def _bind_mean_last_dim(self, plan, step, p):
+        x, y = p["x"], p["y"]
+        plan.launches.append((self._lib.b200_mean_last_dim, (self._ptr(x), self._ptr(y), p["rows"], p["cols"], DTYPE_CODES[x.dtype],
+                                                             DTYPE_CODES[y.dtype])))
+
+    def _bind_argmax(self, plan, step, p):
+        x, y = p["x"], p["y"]
+        plan.launches.append((self._lib.b200_argmax_rows, (self._ptr(x), self._ptr(y), p["rows"], p["cols"], p["cols"],
+                                                           DTYPE_CODES[x.dtype])))
+
+    def _bind_embedding(self, plan, step, p):
+        ids, y = p["ids"], p["y"]
+        base, ids_dtype = self._base(ids, any_dtype=True)
+        if ids_dtype not in ("int64", "int32"):
+            raise RuntimeError(f"embedding indices arrived as {ids_dtype}; upload them as int64/int32")
+        row_bytes = p["embed_dim"] * DTYPE_BYTES[y.dtype]
+        plan.launches.append((self._lib.b200_embedding, (self._wptr(p["table"], y.dtype), base + ids.offset * DTYPE_BYTES[ids_dtype],
+                                                         self._ptr(y), p["seq_len"], p["vocab"], row_bytes, DTYPE_CODES[ids_dtype])))
+
+    def _index_ptr(self, view: TensorView):
+        base, dtype = self._base(view, any_dtype=True)
+        if dtype not in ("int64", "int32"):
+            raise RuntimeError(f"index tensor '{view.buffer}' arrived as {dtype}; upload it as int64/int32")
+        return base + view.offset * DTYPE_BYTES[dtype], DTYPE_CODES[dtype]
+
+    def _bind_index_copy(self, plan, step, p):
+        base, dst, src = p["base"], p["dst"], p["src"]
+        iptr, idt = self._index_ptr(p["index"])
+        plan.launches.append((self._lib.b200_index_copy, (self._ptr(base), self._ptr(dst), self._ptr(src), iptr, p["outer_size"],
+                                                          p["dim_size"], p["inner_size"], p["num_indices"], src.strides[0],
+                                                          src.strides[1], DTYPE_BYTES[dst.dtype], idt)))
+
+    def _bind_rope_table(self, plan, step, p):
+        pptr, pdt = self._index_ptr(p["pos"])
+        plan.launches.append((self._lib.b200_rope_table, (self._wptr(p["inv_freq"], "float32"), pptr, self._ptr(p["cos"]),
+                                                          self._ptr(p["sin"]), p["seq_len"], p["head_dim"], pdt,
+                                                          DTYPE_CODES[p["cos"].dtype])))
+
+    def _bind_rope_rotate(self, plan, step, p):
+        x = self._tensor(plan, p["x"])
+        plan.launches.append((self._lib.b200_rope_rotate, (C.byref(x), self._ptr(p["cos"]), self._ptr(p["sin"]), self._ptr(p["y"]),
+                                                           None, None, 0, 0)))
+
+    def _bind_max_pool2d(self, plan, step, p):
+        x, y = self._tensor(plan, p["x"]), self._tensor(plan, p["y"])
+        plan.launches.append((self._lib.b200_max_pool2d, (C.byref(x), C.byref(y), p["kernel_h"], p["kernel_w"], p["stride_h"],
+                                                          p["stride_w"], p["pad_h"], p["pad_w"])))
+
+    def _bind_adaptive_avg_pool2d(self, plan, step, p):
+        x, y = self._tensor(plan, p["x"]), self._tensor(plan, p["y"])
+        plan.launches.append((self._lib.b200_adaptive_avg_pool2d, (C.byref(x), C.byref(y))))
+
+    def _bind_batch_norm(self, plan, step, p):
+        x, y = self._tensor(plan, p["x"]), self._tensor(plan, p["y"])
+        pd = "float32"
+        g = lambda n: self._weight(n, pd).data_ptr() if n is not None else None
+        plan.launches.append((self._lib.b200_batch_norm, (C.byref(x), C.byref(y), g(p["gamma"]), g(p["beta"]), g(p["mean"]), g(p["var"]),
+                                                          float(p["eps"]), DTYPE_CODES[pd], int(p["relu"]))))
+
+    def _bind_linear(self, plan, step, p):
+        x, y = p["x"], p["y"]
+        dt = y.dtype
+        res, aux = p["residual"], p["aux"]
+        epi = (native.EPI_RELU if p["relu"] else 0) | (native.EPI_SILU_MUL if aux is not None else 0)
+        ws = self._ws["__ws_splitk"] if p["workspace"] else None
+        ld = lambda v: (v.strides[0] if v.shape[0] > 1 else v.shape[1]) if v is not None else 0
+        plan.launches.append((self._lib.b200_linear, (
+            self._ptr(x), self._wptr(p["w"], dt), self._wptr(p["bias"], dt), self._ptr(res), self._ptr(y), p["M"], p["N"], p["K"],
+            ld(x), p["K"], ld(y), ld(res), DTYPE_CODES[dt], DTYPE_CODES[dt], epi, self._ptr(aux), ld(aux),
+            ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0)))
+
+    def _bind_matmul(self, plan, step, p):
+        a, b, y = p["a"], p["b"], p["y"]
+        arr = lambda v: (C.c_int64 * 4)(*v.strides)
+        sa, sb, so = arr(a), arr(b), arr(y)
+        plan.keepalive += [sa, sb, so]
+        plan.launches.append((self._lib.b200_matmul_strided, (self._ptr(a), self._ptr(b), self._ptr(y), p["b1"], p["b2"], p["M"], p["N"],
+                                                              p["K"], sa, sb, so, DTYPE_CODES[y.dtype])))
+
+    def _bind_conv2d(self, plan, step, p):
+        x, y, res = p["x"], p["y"], p["residual"]
+        epi = native.EPI_RELU if p["relu"] else 0
+        plan.launches.append((self._lib.b200_conv2d_nhwc, (
+            self._ptr(x), self._prepared[p["w_prepared"]].data_ptr(), self._prepared[p["bias_prepared"]].data_ptr(), self._ptr(res),
+            self._ptr(y), p["batch"], p["in_h"], p["in_w"], p["c_pad"], p["c_pad"], p["out_channels"], p["kernel_h"], p["kernel_w"],
+            p["stride_h"], p["stride_w"], p["pad_h"], p["pad_w"], p["out_h"], p["out_w"], DTYPE_CODES[y.dtype], epi)))
+
+    def _bind_attention(self, plan, step, p):
+        q, k, v, m, y = p["q"], p["k"], p["v"], p["mask"], p["y"]
+        dt = DTYPE_CODES[y.dtype]
+        if p["decode"]:
+            ws = self._ws["__ws_attn"]
+            plan.launches.append((self._lib.b200_attn_decode, (
+                self._ptr(q), self._ptr(k), self._ptr(v), self._ptr(m), self._ptr(y), p["B"], p["Hq"], p["Hkv"], p["S"], p["D"],
+                q.strides[0], k.strides[0], k.strides[1], m.strides[0] if m is not None else 0, float(p["scale"]), dt,
+                ws.data_ptr(), ws.numel())))
+            return
+        arr = lambda t: (C.c_int64 * 3)(*t.strides[:3])
+        qs, ks, vs = arr(q), arr(k), arr(v)
+        plan.keepalive += [qs, ks, vs]
+        plan.launches.append((self._lib.b200_attn_prefill, (
+            self._ptr(q), self._ptr(k), self._ptr(v), self._ptr(m), self._ptr(y), p["B"], p["Hq"], p["Hkv"], p["T"], p["S"], p["D"],
+            qs, ks, vs, m.strides[0] if m is not None else 0, m.strides[2] if m is not None else 0, float(p["scale"]), dt)))

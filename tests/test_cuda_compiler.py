@@ -1,0 +1,187 @@
+"""Offline compiler tests (no GPU, no native library): op tables, pattern fusion,
+lowering, arena planning.  Structure follows the reference's
+tests/test_cuda_compiler.py; assertions about NVRTC source text do not apply
+because no source is generated."""
+
+import model_zoo as mz
+import torch
+from cuda_compiler import compile_subgraph, get_cuda_supported_ops, is_cuda_op_supported
+from cuda_compiler.cuda_codegen import generate_fused_kernel, is_fusible_elementwise
+from cuda_compiler.cuda_program import AliasStep, CUBLASStep, CUDAProgram, FusedKernelStep, ReductionKernelStep, SpecialKernelStep
+from cuda_compiler.op_classify import OpCategory, classify_op
+from cuda_compiler.subgraph_analyzer import analyze_subgraph
+from helpers import graph, masked_softmax_graph, node, rmsnorm_graph, rope_graph, silu_mul_graph, ts
+from ir_export import extract_ir
+from npu_compiler import load_ir_from_dict
+
+REFERENCE_SUPPORTED = [
+    "aten.conv2d.default", "aten.relu.default", "aten.relu_.default", "aten.batch_norm.default", "aten.max_pool2d.default",
+    "aten.adaptive_avg_pool2d.default", "aten.linear.default", "aten.matmul.default", "aten.addmm.default", "aten.t.default",
+    "aten.add.Tensor", "aten.add_.Tensor", "aten.mul.Tensor", "aten.div.Tensor", "aten.silu.default", "aten.neg.default",
+    "aten.rsqrt.default", "aten.cos.default", "aten.sin.default", "aten.pow.Tensor_Scalar", "aten.embedding.default",
+    "aten.transpose.int", "aten.cat.default", "aten.slice.Tensor", "aten.expand.default", "aten.index_copy.default",
+    "aten.softmax.int", "aten.mean.dim", "aten.full.default", "aten.reshape.default", "aten.view.default",
+    "aten.flatten.using_ints", "aten.contiguous.default", "aten.unsqueeze.default", "aten.alias.default", "aten.detach_.default",
+    "aten.to.dtype", "aten.dropout.default", "<built-in function getitem>", "aten._assert_tensor_metadata.default",
+    "wrap_with_set_grad_enabled",
+]
+
+
+def steps_of(ir, kind):
+    return [s for s in analyze_subgraph(load_ir_from_dict(ir)) if isinstance(s, kind)]
+
+
+def test_classification_matches_reference_table():
+    assert classify_op("aten.matmul.default") == OpCategory.ANCHOR_BLAS
+    assert classify_op("aten.linear.default") == OpCategory.ANCHOR_BLAS
+    assert classify_op("aten.conv2d.default") == OpCategory.ANCHOR_BLAS
+    for op in ("aten.relu.default", "aten.silu.default", "aten.add.Tensor", "aten.mul.Tensor"):
+        assert classify_op(op) == OpCategory.ELEMENTWISE
+    assert classify_op("aten.softmax.int") == OpCategory.REDUCTION
+    assert classify_op("aten.reshape.default") == OpCategory.SHAPE_ALIAS
+    assert classify_op("aten.view.default") == OpCategory.SHAPE_ALIAS
+    assert classify_op("aten.embedding.default") == OpCategory.SPECIAL
+    assert classify_op("aten._assert_tensor_metadata.default") == OpCategory.NOOP
+    assert classify_op("aten.never_heard_of.default") == OpCategory.SPECIAL
+
+
+def test_support_set_covers_the_reference_set():
+    ops = get_cuda_supported_ops()
+    assert all(op in ops for op in REFERENCE_SUPPORTED) and len(ops) >= 30
+    assert is_cuda_op_supported("aten.conv2d.default") and is_cuda_op_supported("aten.silu.default", {})
+    assert not is_cuda_op_supported("aten.some_weird_op.default")
+
+
+def test_single_relu_is_one_fused_step():
+    ir = graph([node("relu", "aten.relu.default", [ts("x", [1, 256])], [ts("y", [1, 256])])], [ts("x", [1, 256])], [ts("y", [1, 256])])
+    fused = steps_of(ir, FusedKernelStep)
+    assert len(fused) == 1 and fused[0].total_elements == 256
+
+
+def test_silu_mul_fuses():
+    fused = steps_of(silu_mul_graph(1, 256, "float32"), FusedKernelStep)
+    assert len(fused) == 1 and "silu" in fused[0].kernel_name
+    assert [op[0] for op in fused[0].params["program"]] == ["SILU", "MUL"]
+
+
+def test_linear_breaks_chains_and_absorbs_following_relu():
+    n = [node("relu1", "aten.relu.default", [ts("x", [1, 256])], [ts("r", [1, 256])]),
+         node("linear", "aten.linear.default", [ts("r", [1, 256]), ts("w", [128, 256])], [ts("l", [1, 128])]),
+         node("relu2", "aten.relu.default", [ts("l", [1, 128])], [ts("y", [1, 128])])]
+    ir = graph(n, [ts("x", [1, 256])], [ts("y", [1, 128])], [ts("w", [128, 256])])
+    blas, fused = steps_of(ir, CUBLASStep), steps_of(ir, FusedKernelStep)
+    assert len(blas) == 1 and blas[0].params["relu"]       # the reference leaves relu2 as a second fused kernel
+    assert len(fused) == 1
+
+
+def test_multi_consumer_is_a_fusion_barrier():
+    n = [node("relu", "aten.relu.default", [ts("x", [1, 256])], [ts("r", [1, 256])]),
+         node("add", "aten.add.Tensor", [ts("r", [1, 256]), ts("r", [1, 256])], [ts("y", [1, 256])])]
+    assert len(steps_of(graph(n, [ts("x", [1, 256])], [ts("y", [1, 256])]), FusedKernelStep)) == 2
+
+
+def test_reshape_is_alias():
+    ir = graph([node("reshape", "aten.reshape.default", [ts("x", [2, 128])], [ts("y", [256])], shape=[256])], [ts("x", [2, 128])], [ts("y", [256])])
+    assert len(steps_of(ir, AliasStep)) == 1 and len(analyze_subgraph(load_ir_from_dict(ir))) == 1
+
+
+def test_softmax_and_embedding_steps():
+    ir = graph([node("softmax", "aten.softmax.int", [ts("x", [4, 128])], [ts("y", [4, 128])], dim=-1)], [ts("x", [4, 128])], [ts("y", [4, 128])])
+    red = steps_of(ir, ReductionKernelStep)
+    assert len(red) == 1 and red[0].kernel_name == "softmax_kernel" and red[0].params["rows"] == 4
+    ir = graph([node("embed", "aten.embedding.default", [ts("weight", [1000, 256]), ts("indices", [4], "int64")], [ts("y", [4, 256])])],
+               [ts("indices", [4], "int64")], [ts("y", [4, 256])], [ts("weight", [1000, 256])])
+    sp = steps_of(ir, SpecialKernelStep)
+    assert len(sp) == 1 and sp[0].kernel_name == "embedding_kernel" and sp[0].params["embed_dim"] == 256
+
+
+def test_conv_step_and_weight_prep():
+    ir = graph([node("conv", "aten.conv2d.default", [ts("x", [1, 8, 8, 8]), ts("w", [16, 8, 3, 3])], [ts("y", [1, 16, 6, 6])],
+                     stride=[1, 1], padding=[0, 0], groups=1)], [ts("x", [1, 8, 8, 8])], [ts("y", [1, 16, 6, 6])], [ts("w", [16, 8, 3, 3])])
+    prog = compile_subgraph(ir)
+    blas = [s for s in prog.steps if isinstance(s, CUBLASStep)]
+    assert len(blas) == 1 and blas[0].blas_type == "conv2d" and blas[0].params["out_h"] == 6
+    assert len(prog.weight_preps) == 1 and prog.weight_preps[0].kind == "conv_fold"
+    # channels-last output: NCHW shape, C has stride 1
+    assert prog.views["y"].strides[1] == 1
+
+
+def test_rmsnorm_chain_becomes_one_kernel():
+    for dtype in ("float32", "bfloat16"):
+        steps = analyze_subgraph(load_ir_from_dict(rmsnorm_graph(3, 256, dtype)))
+        rms = [s for s in steps if isinstance(s, ReductionKernelStep) and s.kernel_name == "rmsnorm_kernel"]
+        assert len(rms) == 1 and rms[0].params["cols"] == 256 and abs(rms[0].params["eps"] - 1e-6) < 1e-12
+        assert not [s for s in steps if isinstance(s, FusedKernelStep)]
+
+
+def test_masked_softmax_fusion_with_broadcast_mask():
+    red = steps_of(masked_softmax_graph(12, 128), ReductionKernelStep)
+    assert len(red) == 1 and red[0].kernel_name == "masked_softmax_kernel"
+    assert red[0].params["rows"] == 12 * 128 and red[0].params["cols"] == 128
+    assert red[0].params["mask_strides"][1:] == (0, 128)  # head axis broadcast, one row per query
+
+
+def test_rope_chain_becomes_table_plus_rotate():
+    steps = analyze_subgraph(load_ir_from_dict(rope_graph(12, 16)))
+    names = [s.kernel_name for s in steps if isinstance(s, SpecialKernelStep)]
+    assert names == ["rope_kernel", "rope_rotate_kernel"] and not [s for s in steps if isinstance(s, FusedKernelStep)]
+
+
+def test_codegen_helpers_keep_reference_names():
+    assert is_fusible_elementwise("aten.relu.default") and is_fusible_elementwise("aten.add.Tensor")
+    assert not is_fusible_elementwise("aten.matmul.default")
+    g = load_ir_from_dict(silu_mul_graph(1, 8, "float32"))
+    text = generate_fused_kernel("fused_silu_mul", g.nodes, ["gate", "up"], "y")
+    assert "fused_silu_mul" in text and "exp" in text and "*" in text
+
+
+def test_buffer_plan_reuses_memory():
+    prog = compile_subgraph(extract_ir(mz.resnet(18, device="meta"), (torch.zeros(1, 3, 64, 64, device="meta"),), "r18"))
+    assert isinstance(prog, CUDAProgram)
+    total = sum(a.size_bytes for a in prog.buffer_allocations)
+    assert 0 < prog.arena_bytes < total
+    live = [a for a in prog.buffer_allocations if a.size_bytes and a.offset >= 0]
+    for i, a in enumerate(live):
+        for b in live[i + 1:]:
+            overlap_mem = a.offset < b.offset + b.size_bytes and b.offset < a.offset + a.size_bytes
+            overlap_time = not (a.last_step < b.first_step or b.last_step < a.first_step)
+            assert not (overlap_mem and overlap_time), (a, b)
+
+
+def test_resnet_block_compiles_to_two_convs_with_fused_epilogues():
+    prog = compile_subgraph(extract_ir(mz.resnet(18, device="meta"), (torch.zeros(1, 3, 64, 64, device="meta"),), "r18"))
+    convs = [s for s in prog.steps if isinstance(s, CUBLASStep) and s.blas_type == "conv2d"]
+    assert len(convs) == 20 and all(c.params["bn_folded"] for c in convs)
+    assert sum(1 for c in convs if c.params["residual"] is not None) == 8
+    assert not [s for s in prog.steps if isinstance(s, ReductionKernelStep) and s.kernel_name == "batch_norm_kernel"]
+    assert prog.compute_dtype == "float16"
+
+
+def test_qwen_mlp_pattern_at_real_sizes():
+    x, f32 = ts("x", [1, 1536]), "float32"
+    n = [node("gate", "aten.linear.default", [x, ts("gate_w", [8960, 1536])], [ts("g", [1, 8960])]),
+         node("up", "aten.linear.default", [x, ts("up_w", [8960, 1536])], [ts("u", [1, 8960])]),
+         node("silu", "aten.silu.default", [ts("g", [1, 8960])], [ts("s", [1, 8960])]),
+         node("mul", "aten.mul.Tensor", [ts("s", [1, 8960]), ts("u", [1, 8960])], [ts("m", [1, 8960])]),
+         node("down", "aten.linear.default", [ts("m", [1, 8960]), ts("down_w", [1536, 8960])], [ts("y", [1, 1536])])]
+    ir = graph(n, [x], [ts("y", [1, 1536])], [ts("gate_w", [8960, 1536]), ts("up_w", [8960, 1536]), ts("down_w", [1536, 8960])])
+    prog = compile_subgraph(ir)
+    blas = [s for s in prog.steps if isinstance(s, CUBLASStep)]
+    assert len(blas) == 3 and sum(1 for b in blas if b.params["aux"] is not None) == 1   # silu*up rides in the gate GEMM
+    assert not [s for s in prog.steps if isinstance(s, FusedKernelStep)]
+
+
+def test_qwen_decode_layer_plan():
+    L = 2
+    cfg = mz.qwen2_config(num_layers=L)
+    ir = extract_ir(mz.QwenDecodeWrapper(mz.qwen2_model(cfg), L), mz.qwen2_example_inputs(cfg, 2, 1, 256), "qd")
+    prog = compile_subgraph(ir)
+    assert prog.compute_dtype == "bfloat16"
+    kinds = [getattr(s, "kernel_name", None) or s.blas_type for s in prog.steps if not isinstance(s, AliasStep)]
+    assert kinds.count("attention") == L and kinds.count("rmsnorm_kernel") == 2 * L + 1
+    assert kinds.count("gemm") == 7 * L + 1 and kinds.count("index_copy_kernel") == 2 * L
+    assert len(prog.donated_inputs) == 2 * L
+    assert all(s.params["in_place"] for s in prog.steps if getattr(s, "kernel_name", "") == "index_copy_kernel")
+    # without donation the cache is copied, as in the reference
+    prog2 = compile_subgraph(ir, donate_inputs=False)
+    assert not prog2.donated_inputs

@@ -1,0 +1,175 @@
+"""Whole host pipeline on CPU: IR -> patterns -> lowering -> arena -> argument binding
+-> outputs, with the native library replaced by the torch stand-in
+(tests/fake_b200nn.py) and the oracle as the checker.  These tests prove the host
+logic (views, offsets, strides, operand order), not the CUDA kernels."""
+
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import model_zoo as mz
+from helpers import graph, masked_softmax_graph, node, np_inputs, rmsnorm_graph, rope_graph, run_backend, silu_mul_graph, to_f32, ts
+from ir_export import extract_ir
+from oracle.ir_interpreter import IRInterpreter, cpu_executor_factory, torch_to_numpy
+
+GOLDEN = Path(__file__).parent / "golden"
+
+
+def oracle(ir, weights, inputs):
+    return {k: to_f32(v) for k, v in IRInterpreter(ir, weights).execute(inputs).items()}
+
+
+def assert_bf16_close(got, gold_bits, max_fraction=0.01):
+    """bf16 results of a floating-point path: at most one unit in the last place, on few elements."""
+    a = got.view(np.uint16).astype(np.int32)
+    b = np.asarray(gold_bits).astype(np.int32)
+    diff = np.abs(a - b)
+    assert diff.max() <= 1 and (diff != 0).mean() <= max_fraction, (diff.max(), (diff != 0).mean())
+
+
+def rand(shape, dtype=torch.bfloat16, seed=0, scale=1.0):
+    return (torch.randn(*shape, generator=torch.Generator().manual_seed(seed)) * scale).to(dtype)
+
+
+@pytest.mark.parametrize("rows", [1, 5, 128])
+def test_rmsnorm_graph(fake_native, rows):
+    ir = rmsnorm_graph(rows, 1536)
+    x, w = rand((rows, 1536)), (1 + 0.02 * rand((1536,), seed=1).float()).bfloat16()
+    out, _ = run_backend(ir, {"w": torch_to_numpy(w)}, {"x": torch_to_numpy(x)})
+    ref = oracle(ir, {"w": w}, {"x": x})
+    np.testing.assert_allclose(to_f32(out["y"]), ref["y"], rtol=2e-2, atol=1e-2)
+    assert fake_native.calls == ["rmsnorm"]
+
+
+def test_silu_mul_graph(fake_native):
+    ir = silu_mul_graph(7, 8960)
+    g, u = rand((7, 8960)), rand((7, 8960), seed=1)
+    out, _ = run_backend(ir, {}, {"gate": torch_to_numpy(g), "up": torch_to_numpy(u)})
+    np.testing.assert_allclose(to_f32(out["y"]), oracle(ir, {}, {"gate": g, "up": u})["y"], rtol=2e-2, atol=1e-2)
+
+
+def test_masked_softmax_graph(fake_native):
+    T = 40
+    ir = masked_softmax_graph(12, T)
+    s, m = rand((1, 12, T, T)), mz.causal_mask(1, T, T, 0)
+    out, _ = run_backend(ir, {}, {"scores": torch_to_numpy(s), "mask": torch_to_numpy(m)})
+    np.testing.assert_allclose(to_f32(out["y"]), oracle(ir, {}, {"scores": s, "mask": m})["y"], rtol=2e-2, atol=2e-3)
+    assert fake_native.calls == ["softmax"]
+
+
+def test_rope_graph(fake_native):
+    T = 24
+    ir = rope_graph(12, T)
+    x = rand((1, 12, T, 128))
+    pos = torch.arange(T)[None] + 1000
+    inv = 1.0 / (1e6 ** (torch.arange(0, 128, 2).float() / 128))
+    out, _ = run_backend(ir, {"inv_freq": inv.numpy()}, {"x": torch_to_numpy(x), "position_ids": pos.numpy()})
+    ref = oracle(ir, {"inv_freq": inv}, {"x": x, "position_ids": pos})
+    np.testing.assert_allclose(to_f32(out["y"]), ref["y"], rtol=2e-2, atol=2e-2)
+    assert fake_native.calls == ["rope_table", "rope_rotate"]
+
+
+def test_unfused_lowering_matches_too(fake_native):
+    """fuse=False exercises the generic per-op path (views, chains, strided copies)."""
+    T = 8
+    ir = rope_graph(4, T)
+    x = rand((1, 4, T, 128))
+    pos = torch.arange(T)[None]
+    inv = 1.0 / (1e6 ** (torch.arange(0, 128, 2).float() / 128))
+    out, _ = run_backend(ir, {"inv_freq": inv.numpy()}, {"x": torch_to_numpy(x), "position_ids": pos.numpy()}, {"fuse": False})
+    ref = oracle(ir, {"inv_freq": inv}, {"x": x, "position_ids": pos})
+    np.testing.assert_allclose(to_f32(out["y"]), ref["y"], rtol=2e-2, atol=2e-2)
+    assert "rope_rotate" not in fake_native.calls and "strided_copy" in fake_native.calls
+
+
+def test_embedding_and_index_copy_are_bit_exact(fake_native):
+    V, D, S = 300, 64, 16
+    n = [node("emb", "aten.embedding.default", [ts("table", [V, D], "bfloat16"), ts("ids", [2, 3], "int64")], [ts("emb", [2, 3, D], "bfloat16")]),
+         node("ic", "aten.index_copy.default", [ts("cache", [2, 2, S, D], "bfloat16"), ts("pos", [1], "int64"), ts("src", [2, 2, 1, D], "bfloat16")],
+              [ts("ic", [2, 2, S, D], "bfloat16")], dim=2)]
+    ir = graph(n, [ts("ids", [2, 3], "int64"), ts("cache", [2, 2, S, D], "bfloat16"), ts("pos", [1], "int64"), ts("src", [2, 2, 1, D], "bfloat16")],
+               [ts("emb", [2, 3, D], "bfloat16"), ts("ic", [2, 2, S, D], "bfloat16")], [ts("table", [V, D], "bfloat16")])
+    table, cache, src = rand((V, D)), rand((2, 2, S, D), seed=1), rand((2, 2, 1, D), seed=2)
+    ids, pos = torch.tensor([[0, 299, 7], [151, 151, 2]]), torch.tensor([5])
+    ins = {"ids": ids.numpy(), "cache": torch_to_numpy(cache), "pos": pos.numpy(), "src": torch_to_numpy(src)}
+    out, _ = run_backend(ir, {"table": torch_to_numpy(table)}, ins)
+    ref = IRInterpreter(ir, {"table": table}).execute({"ids": ids, "cache": cache, "pos": pos, "src": src})
+    for k in ("emb", "ic"):
+        np.testing.assert_array_equal(out[k].view(np.uint16), ref[k].view(torch.uint16).numpy())
+
+
+def test_resnet18_golden(fake_native):
+    fx = np.load(GOLDEN / "resnet18_b2_64.npz")
+    m = mz.resnet(18, seed=0)
+    ir = extract_ir(m, (torch.from_numpy(fx["x"]),), "resnet18")
+    out, dag = run_backend(ir, mz.state_dict_numpy(m.state_dict()), {"x": fx["x"]})
+    got = to_f32(out[ir["graph_outputs"][0]["name"]])
+    np.testing.assert_allclose(got, fx["logits"], rtol=0, atol=1e-1)  # the reference's ResNet-18 tolerance
+    assert (np.argsort(-got, 1)[:, :5] == np.argsort(-fx["logits"], 1)[:, :5]).all()
+    assert fake_native.calls.count("conv2d") == 20 and "batch_norm" not in fake_native.calls
+
+
+def test_qwen_tiny_golden_prefill_then_decode(fake_native):
+    from golden.make_golden import tiny_qwen
+
+    fx = np.load(GOLDEN / "qwen_tiny.npz")
+    cfg, sd, model = tiny_qwen()
+    T, S, L = int(fx["T"]), int(fx["S"]), cfg.num_hidden_layers
+    w = mz.state_dict_numpy(sd)
+    irp = extract_ir(mz.QwenPrefillWrapper(model), mz.qwen2_example_inputs(cfg, 1, T, None, device="cpu"), "p")
+    ins = np_inputs(irp, (torch.from_numpy(fx["ids"]), mz.causal_mask(1, T, T, 0), torch.arange(T)[None], torch.arange(T)))
+    pre, _ = run_backend(irp, w, ins)
+    names = [o["name"] for o in irp["graph_outputs"]]
+    gold = torch.from_numpy(fx["prefill_logits"]).view(torch.bfloat16).float().numpy()
+    got = to_f32(pre[names[0]])
+    assert np.abs(got - gold).max() < 0.1
+    assert (got[0, -1].argmax() == gold[0, -1].argmax())
+    assert_bf16_close(pre[names[1]], fx["prefill_k0"])  # K of layer 0: norm + GEMM + rope, last-bit differences only
+    # decode on top of the prefilled cache
+    kv = []
+    for n in names[1:]:
+        buf = np.zeros((1, 1, S, 128), dtype=pre[n].dtype)
+        buf[:, :, :T] = pre[n]
+        kv.append(buf)
+    ird = extract_ir(mz.QwenDecodeWrapper(model, L), mz.qwen2_example_inputs(cfg, 1, 1, S, device="cpu"), "d")
+    dins = dict(zip([s["name"] for s in ird["graph_inputs"]],
+                    [fx["next_id"], torch_to_numpy(mz.causal_mask(1, 1, S, T)), np.array([[T]]), np.array([T])] + kv))
+    dec, _ = run_backend(ird, w, dins)
+    dn = [o["name"] for o in ird["graph_outputs"]]
+    gold = torch.from_numpy(fx["decode_logits"]).view(torch.bfloat16).float().numpy()
+    got = to_f32(dec[dn[0]])
+    assert np.abs(got - gold).max() < 0.1 and got.argmax() == gold.argmax()
+    assert_bf16_close(dec[dn[1]], fx["decode_k0"])
+    assert fake_native.calls.count("attn_decode") == L and fake_native.calls.count("attn_prefill") == L
+
+
+def test_mixed_partitions_use_the_injected_cpu_executor(fake_native):
+    from cuda_compiler import compile_subgraph
+    from cuda_runtime import CUDABackend
+    from npu_compiler import partition
+    from npu_runtime import DAGExecutor
+
+    n = [node("a", "aten.relu.default", [ts("x", [2, 8])], [ts("a", [2, 8])]),
+         node("b", "aten.neg.default", [ts("a", [2, 8])], [ts("b", [2, 8])]),
+         node("c", "aten.add.Tensor", [ts("b", [2, 8]), ts("a", [2, 8])], [ts("c", [2, 8])])]
+    ir = graph(n, [ts("x", [2, 8])], [ts("c", [2, 8])])
+    plan = partition(ir, lambda op, attrs=None: op != "aten.neg.default")
+    dag = DAGExecutor(plan, CUDABackend(), compile_subgraph, cpu_executor_factory=cpu_executor_factory)
+    x = np.random.RandomState(0).randn(2, 8).astype(np.float32)
+    out = dag.execute({"x": x}, weights={})
+    c = out["c"] if isinstance(out["c"], np.ndarray) else out["c"].to_numpy()
+    np.testing.assert_allclose(c.astype(np.float32), np.zeros((2, 8)), atol=1e-3)  # relu(x) - relu(x)
+
+
+def test_cpu_partition_without_interpreter_raises(fake_native):
+    from cuda_compiler import compile_subgraph
+    from cuda_runtime import CUDABackend
+    from npu_compiler import partition
+    from npu_runtime import DAGExecutor
+
+    ir = graph([node("b", "aten.neg.default", [ts("x", [2])], [ts("b", [2])])], [ts("x", [2])], [ts("b", [2])])
+    dag = DAGExecutor(partition(ir, lambda *a: False), CUDABackend(), compile_subgraph)
+    with pytest.raises(RuntimeError, match="torch_ir"):
+        dag.execute({"x": np.zeros(2, np.float32)}, weights={})

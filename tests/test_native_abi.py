@@ -1,0 +1,84 @@
+"""The shared library builds, loads, and exports exactly what include/b200nn.h declares.
+No compute call is made here (no GPU)."""
+
+import re
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def declared_symbols():
+    text = (ROOT / "include" / "b200nn.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(b200_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_and_binding_agree():
+    from cuda_runtime import native
+
+    assert declared_symbols() == sorted(native.SIGNATURES)
+
+
+def test_library_exports_every_declared_symbol(native_lib):
+    for name in declared_symbols():
+        assert hasattr(native_lib, name), name
+    assert native_lib.b200_version() == 1
+
+
+def test_host_only_entry_points(native_lib):
+    # workspace sizing is pure host arithmetic
+    assert native_lib.b200_linear_workspace_bytes(1, 1536, 1536) > 0
+    assert native_lib.b200_linear_workspace_bytes(512, 1536, 1536) == 0
+    assert native_lib.b200_attn_decode_workspace_bytes(64, 12, 2, 4352, 128) == 64 * 2 * 17 * 6 * 130 * 4
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    from cuda_runtime import native
+
+    monkeypatch.setenv("B200NN_LIBRARY", str(tmp_path / "nope.so"))
+    monkeypatch.setattr(native, "_lib", None)
+    with pytest.raises(RuntimeError, match="no fallback"):
+        native.load()
+
+
+def test_backend_without_gpu_raises_runtime_error(native_lib):
+    import torch
+
+    from cuda_runtime import CUDABackend, CUDABuffer
+    from npu_runtime.backend import Backend, DeviceBuffer
+
+    assert issubclass(CUDABackend, Backend) and issubclass(CUDABuffer, DeviceBuffer)
+    if not torch.cuda.is_available():
+        with pytest.raises(RuntimeError):
+            CUDABackend()
+
+
+def test_buffer_semantics_on_the_cpu_seam(fake_native):
+    import ml_dtypes
+
+    from cuda_runtime import CUDABackend, CUDABuffer
+    from npu_compiler import TensorSpec
+
+    be = CUDABackend()
+    assert be.name == "cuda"
+    a = np.arange(12, dtype=np.float32).reshape(3, 4)
+    buf = be.allocate_buffer(a)
+    assert buf.shape == (3, 4) and buf.dtype == np.float32 and buf.size_bytes == 48
+    np.testing.assert_array_equal(buf.to_numpy(), a)
+    z = be.allocate_zeros((2, 5))
+    assert z.dtype == np.float16 and not z.to_numpy().any()
+    # the DAG executor pre-allocates fp16 zeros for every input, ids included: writes must retype
+    ids = np.array([[151935, 70000]], dtype=np.int64)
+    z.write_from_numpy(ids, spec=TensorSpec("input_ids", [1, 2], "int64"))
+    assert z.dtype == np.int64 and z.shape == (1, 2)
+    np.testing.assert_array_equal(z.to_numpy(), ids)
+    # bf16 travels as bit patterns
+    b = np.array([1.0, 3.0e-6, -2.5], dtype=ml_dtypes.bfloat16)
+    bb = CUDABuffer.from_numpy(b)
+    assert bb.dtype == ml_dtypes.bfloat16
+    np.testing.assert_array_equal(bb.to_numpy().view(np.uint16), b.view(np.uint16))
+    np.testing.assert_array_equal(bb.to_numpy(dtype=np.float32), b.astype(np.float32))
+    be.synchronize()
