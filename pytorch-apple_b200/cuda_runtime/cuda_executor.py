@@ -103,6 +103,29 @@ class CUDAExecutor:
         self.last_launch_count = plan.n_kernels
         return {name: CUDABuffer(t, logical_shape=tuple(t.shape)) for name, t in plan.outputs.items()}
 
+    def profile(self, inputs: dict[str, Any], weights: dict[str, Any]) -> list[tuple[str, float]]:
+        """Run once without a CUDA graph, bracketing every library call with CUDA events on
+        the launching stream.  Returns ``[(entry point, milliseconds), ...]`` in issue order.
+        (The reference's profiler times whole runs with a host clock, npu_runtime/profiler.py:23-49.)"""
+        if not self._on_gpu:
+            raise RuntimeError("profile() needs a CUDA device")
+        if self._weights_id != id(weights) or len(weights) != self._weights_len:
+            self._load_weights(weights)
+        tensors = {n: inputs[n].native_handle for n in self._input_names if n in inputs}
+        plan = self._bind(tensors)
+        stream = torch.cuda.current_stream()
+        events = []
+        for fn, args in plan.launches:
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            rc = fn(*args, stream.cuda_stream)
+            b.record(stream)
+            if rc != 0:
+                native.check(rc, fn.__name__)
+            events.append((fn.__name__, a, b))
+        stream.synchronize()
+        return [(name, a.elapsed_time(b)) for name, a, b in events]
+
     # --------------------------------------------------------------- launching
     def _stream_ptr(self) -> int:
         return torch.cuda.current_stream().cuda_stream if self._on_gpu else 0

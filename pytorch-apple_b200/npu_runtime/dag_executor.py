@@ -153,7 +153,8 @@ class DAGExecutor:
                 arr = weights.get(placeholder)
             if arr is None:
                 continue
-            out[placeholder] = self.backend.allocate_buffer(arr, spec=spec)
+            # a weight that already lives on the device is used as it is
+            out[placeholder] = arr if isinstance(arr, DeviceBuffer) else self.backend.allocate_buffer(arr, spec=spec)
         return out
 
     def load_weights(self, weights: dict[str, np.ndarray]) -> None:
@@ -168,12 +169,11 @@ class DAGExecutor:
                 self._npu_weight_cache[pid] = self._upload_weights(weights, self.npu_programs[pid])
             else:
                 self._cpu_runners[pid] = self._cpu_factory(step.nodes, weights, self._weight_name_mapping)
-        if not self._npu_input_buffers:
-            for pid, program in self.npu_programs.items():
-                self._npu_input_buffers[pid] = {
-                    spec.name: self.backend.allocate_zeros(tuple(spec.shape), dtype=np.dtype(np.float16))
-                    for spec in program.input_specs
-                }
+        # Staging buffers for host inputs are created on first use (the reference allocates
+        # one per program input up front, dag_executor.py:101-116, which for a decode graph
+        # would duplicate the whole device-resident KV cache).
+        for pid in self.npu_programs:
+            self._npu_input_buffers.setdefault(pid, {})
 
     # -- execution -------------------------------------------------------
     def execute(self, inputs: dict[str, Any], weights: dict[str, np.ndarray] | None = None) -> dict[str, Any]:
@@ -194,18 +194,17 @@ class DAGExecutor:
     def _run_npu(self, part: Partition, pool: dict) -> None:
         pid = part.partition_id
         program = self.npu_programs[pid]
-        staged = self._npu_input_buffers.get(pid, {})
+        staged = self._npu_input_buffers.setdefault(pid, {})
         dev_inputs: dict[str, DeviceBuffer] = {}
         for spec in program.input_specs:
             val = pool.get(spec.name)
             if val is None:
                 continue
             if isinstance(val, np.ndarray):
-                if spec.name in staged:
-                    staged[spec.name].write_from_numpy(val, spec=spec)
-                    dev_inputs[spec.name] = staged[spec.name]
-                else:
-                    dev_inputs[spec.name] = self.backend.allocate_buffer(val, alloc_shape=spec.alloc_shape, spec=spec)
+                if spec.name not in staged:
+                    staged[spec.name] = self.backend.allocate_zeros(tuple(spec.shape), dtype=np.dtype(np.float16))
+                staged[spec.name].write_from_numpy(val, spec=spec)
+                dev_inputs[spec.name] = staged[spec.name]
             else:
                 dev_inputs[spec.name] = val
         pool.update(self._npu_executors[pid].run(dev_inputs, self._npu_weight_cache.get(pid, {})))

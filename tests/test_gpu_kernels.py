@@ -1,0 +1,374 @@
+"""Parity of every CUDA kernel with a CPU statement of the same op, called through the
+C ABI (ctypes on raw device pointers), on seeded inputs.  Integer/byte work must be
+bit-exact; floating point uses the op-level tolerance of the reference's CUDA tests
+(rtol 5e-2 / atol 1e-2, tests/test_cuda_executor.py:150-319), tightened where bf16 allows."""
+
+import ctypes as C
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DT = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2, torch.int32: 3, torch.int64: 4, torch.uint8: 5}
+
+
+@pytest.fixture(scope="module")
+def lib(native_lib):
+    assert torch.cuda.is_available()
+    torch.cuda.set_device(0)
+    return native_lib
+
+
+def ok(lib, rc):
+    assert rc == 0, lib.b200_last_error().decode()
+    torch.cuda.synchronize()
+
+
+def stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def gen(shape, dtype=torch.bfloat16, seed=0, scale=1.0):
+    return (torch.randn(*shape, generator=torch.Generator().manual_seed(seed)) * scale).to(dtype)
+
+
+def bt(t):
+    from cuda_runtime import native
+
+    return native.make_tensor(t.data_ptr(), str(t.dtype).replace("torch.", ""), tuple(t.shape), tuple(t.stride()))
+
+
+def close(got, ref, rtol=2e-2, atol=1e-2):
+    np.testing.assert_allclose(got.float().cpu().numpy(), ref.float().cpu().numpy(), rtol=rtol, atol=atol)
+
+
+# ------------------------------------------------------------------ linear
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("M,N,K,bias,res,relu,silu", [
+    (1, 1536, 1536, True, False, False, False),
+    (1, 1536, 8960, False, True, False, False),
+    (8, 8960, 1536, False, False, False, True),
+    (64, 256, 1536, True, False, False, False),
+    (3, 1000, 512, True, False, True, False),
+    (7, 130, 72, True, True, True, False),
+    (65, 1536, 1536, True, True, False, False),
+    (512, 8960, 1536, False, False, False, True),
+    (300, 1000, 2048, True, False, True, False),
+    (128, 151936 // 8, 1536, False, False, False, False),
+])
+def test_linear(lib, dtype, M, N, K, bias, res, relu, silu):
+    a, w = gen((M, K), dtype), gen((N, K), dtype, 1, 0.05)
+    b = gen((N,), dtype, 2) if bias else None
+    r = gen((M, N), dtype, 3) if res else None
+    u = gen((M, N), dtype, 4) if silu else None
+    ref = a.float() @ w.float().t()
+    if bias:
+        ref = ref + b.float()
+    if res:
+        ref = ref.to(dtype).float() + r.float()
+    if relu:
+        ref = torch.relu(ref)
+    if silu:
+        s = ref.to(dtype).float()
+        ref = torch.nn.functional.silu(s).to(dtype).float() * u.float()
+    A, W = a.cuda(), w.cuda()
+    Bv, Rv, Uv = (t.cuda() if t is not None else None for t in (b, r, u))
+    out = torch.full((M, N), float("nan"), dtype=dtype, device="cuda")
+    nbytes = lib.b200_linear_workspace_bytes(M, N, K)
+    ws = torch.zeros(max(nbytes, 16), dtype=torch.uint8, device="cuda")
+    p = lambda t: t.data_ptr() if t is not None else None
+    for _ in range(2):  # second call checks that the split-K workspace was left clean
+        out.fill_(float("nan"))
+        ok(lib, lib.b200_linear(p(A), p(W), p(Bv), p(Rv), p(out), M, N, K, K, K, N, N, DT[dtype], DT[dtype],
+                                (1 if relu else 0) | (2 if silu else 0), p(Uv), N, p(ws), ws.numel(), stream()))
+        close(out, ref, rtol=2e-2, atol=2e-2 * max(1.0, math.sqrt(K) * 0.05))
+    assert not ws.any()
+
+
+def test_linear_rejects_unaligned(lib):
+    a = torch.zeros(4, 12, dtype=torch.bfloat16, device="cuda")
+    rc = lib.b200_linear(a.data_ptr(), a.data_ptr(), None, None, a.data_ptr(), 4, 4, 12, 12, 12, 4, 0, 2, 2, 0, None, 0, None, 0, stream())
+    assert rc == -2 and b"multiples of 8" in lib.b200_last_error()
+
+
+# ------------------------------------------------------------------ conv
+@pytest.mark.parametrize("N,C,H,O,k,s,p,res,relu", [
+    (2, 8, 56, 64, 7, 2, 3, False, True),     # stem after channel padding 3 -> 8
+    (1, 64, 56, 64, 3, 1, 1, True, True),
+    (2, 64, 56, 128, 3, 2, 1, False, True),
+    (2, 64, 56, 128, 1, 2, 0, False, False),
+    (3, 256, 14, 1024, 1, 1, 0, True, True),
+    (1, 512, 7, 512, 3, 1, 1, False, True),
+])
+def test_conv2d_nhwc(lib, N, C, H, O, k, s, p, res, relu):
+    dtype = torch.float16
+    x = gen((N, C, H, H), dtype)
+    w = gen((O, C, k, k), torch.float32, 1, math.sqrt(2.0 / (C * k * k)))
+    gamma, beta = torch.rand(O) + 0.5, torch.randn(O) * 0.1
+    mean, var = torch.randn(O) * 0.1, torch.rand(O) + 0.5
+    Ho = (H + 2 * p - k) // s + 1
+    r = gen((N, O, Ho, Ho), dtype, 5) if res else None
+    ref = torch.nn.functional.conv2d(x.float(), w, None, s, p)
+    ref = torch.nn.functional.batch_norm(ref, mean, var, gamma, beta, False, 0.0, 1e-5)
+    if res:
+        ref = ref + r.float()
+    if relu:
+        ref = torch.relu(ref)
+    xd = x.cuda().contiguous(memory_format=torch.channels_last)
+    wd = torch.empty(O * k * k * C, dtype=dtype, device="cuda")
+    bd = torch.empty(O, dtype=torch.float32, device="cuda")
+    prm = [t.cuda() for t in (gamma, beta, mean, var)]
+    wc = w.cuda()
+    ok(lib, lib.b200_conv_weight_prep(wc.data_ptr(), None, *[t.data_ptr() for t in prm], wd.data_ptr(), bd.data_ptr(), O, C, k, k, C,
+                                      1e-5, 0, 0, 1, stream()))
+    y = torch.empty(N, O, Ho, Ho, dtype=dtype, device="cuda").contiguous(memory_format=torch.channels_last)
+    rd = r.cuda().contiguous(memory_format=torch.channels_last) if res else None
+    ok(lib, lib.b200_conv2d_nhwc(xd.data_ptr(), wd.data_ptr(), bd.data_ptr(), rd.data_ptr() if res else None, y.data_ptr(), N, H, H, C, C,
+                                 O, k, k, s, s, p, p, Ho, Ho, 1, 1 if relu else 0, stream()))
+    close(y, ref, rtol=2e-2, atol=3e-2)
+
+
+# ------------------------------------------------------------------ attention
+def attn_ref(q, k, v, mask, scale, dtype):
+    G = q.shape[1] // k.shape[1]
+    k, v = k.float().repeat_interleave(G, 1), v.float().repeat_interleave(G, 1)
+    s = q.float() @ k.transpose(-1, -2) * scale
+    if mask is not None:
+        s = s + mask.float()
+    return torch.softmax(s, -1) @ v
+
+
+@pytest.mark.parametrize("B,S,valid", [(1, 4352, 4097), (8, 4352, 4100), (3, 80, 37), (2, 272, 272), (64, 512, 300)])
+def test_attn_decode(lib, B, S, valid):
+    import model_zoo as mz
+
+    dtype, Hq, Hkv, D = torch.bfloat16, 12, 2, 128
+    q, k, v = gen((B, Hq, 1, D), dtype), gen((B, Hkv, S, D), dtype, 1), gen((B, Hkv, S, D), dtype, 2)
+    mask = mz.causal_mask(B, 1, S, valid - 1)
+    ref = attn_ref(q, k, v, mask, D ** -0.5, dtype)[:, :, 0]
+    Q, K, V, M = q.cuda(), k.cuda(), v.cuda(), mask.cuda()
+    out = torch.empty(B, Hq, D, dtype=dtype, device="cuda")
+    ws = torch.empty(lib.b200_attn_decode_workspace_bytes(B, Hq, Hkv, S, D), dtype=torch.uint8, device="cuda")
+    ok(lib, lib.b200_attn_decode(Q.data_ptr(), K.data_ptr(), V.data_ptr(), M.data_ptr(), out.data_ptr(), B, Hq, Hkv, S, D, Hq * D,
+                                 Hkv * S * D, S * D, S, D ** -0.5, 2, ws.data_ptr(), ws.numel(), stream()))
+    close(out, ref, rtol=2e-2, atol=5e-3)
+    # no mask = attend to everything
+    ok(lib, lib.b200_attn_decode(Q.data_ptr(), K.data_ptr(), V.data_ptr(), None, out.data_ptr(), B, Hq, Hkv, S, D, Hq * D,
+                                 Hkv * S * D, S * D, 0, D ** -0.5, 2, ws.data_ptr(), ws.numel(), stream()))
+    close(out, attn_ref(q, k, v, None, D ** -0.5, dtype)[:, :, 0], rtol=2e-2, atol=5e-3)
+
+
+@pytest.mark.parametrize("B,T", [(1, 512), (2, 48), (1, 100)])
+def test_attn_prefill(lib, B, T):
+    import model_zoo as mz
+
+    dtype, Hq, Hkv, D = torch.bfloat16, 12, 2, 128
+    q = gen((B, T, Hq, D), dtype).transpose(1, 2)          # the layout the graph produces: a transposed view
+    k, v = gen((B, Hkv, T, D), dtype, 1), gen((B, T, Hkv, D), dtype, 2).transpose(1, 2)
+    mask = mz.causal_mask(1, T, T, 0)
+    ref = attn_ref(q, k, v, mask, D ** -0.5, dtype).transpose(1, 2)
+    Q, K, V, M = (t.cuda() for t in (q.transpose(1, 2).contiguous(), k, v.transpose(1, 2).contiguous(), mask))
+    Q, V = Q.transpose(1, 2), V.transpose(1, 2)
+    out = torch.empty(B, T, Hq, D, dtype=dtype, device="cuda")
+    st = lambda t: (C.c_int64 * 3)(*t.stride()[:3])
+    ok(lib, lib.b200_attn_prefill(Q.data_ptr(), K.data_ptr(), V.data_ptr(), M.data_ptr(), out.data_ptr(), B, Hq, Hkv, T, T, D,
+                                  st(Q), st(K), st(V), 0, T, D ** -0.5, 2, stream()))
+    close(out, ref, rtol=2e-2, atol=5e-3)
+
+
+# ------------------------------------------------------------------ bandwidth kernels
+@pytest.mark.parametrize("rows,cols", [(1, 1536), (128, 1536), (2048, 1536), (5, 4096), (3, 100)])
+def test_rmsnorm(lib, rows, cols):
+    for dtype in (torch.bfloat16, torch.float16):
+        x, w = gen((rows, cols), dtype), (1 + 0.02 * gen((cols,), torch.float32, 1)).to(dtype)
+        n = (x.float() * torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + 1e-6)).to(dtype)
+        ref = (w.float() * n.float()).to(dtype)
+        X, W = x.cuda(), w.cuda()
+        Y = torch.empty_like(X)
+        ok(lib, lib.b200_rmsnorm(X.data_ptr(), W.data_ptr(), Y.data_ptr(), rows, cols, cols, cols, 1e-6, DT[dtype], 1, stream()))
+        got, r = Y.cpu(), ref
+        ulp = (got.view(torch.int16).int() - r.view(torch.int16).int()).abs()
+        assert ulp.max() <= 1 and (ulp != 0).float().mean() < 0.02   # fp32 reduction order only
+
+
+@pytest.mark.parametrize("T", [1, 128, 1000, 2048])
+def test_masked_softmax(lib, T):
+    import model_zoo as mz
+
+    dtype = torch.bfloat16
+    H = 12 if T <= 1000 else 3
+    x, mask = gen((1, H, T, T), dtype), mz.causal_mask(1, T, T, 0)
+    ref = torch.softmax((x.float() + mask.float()).to(dtype).float(), -1)
+    X, M = x.cuda(), mask.cuda()
+    Y = torch.empty_like(X)
+    ok(lib, lib.b200_softmax(X.data_ptr(), M.data_ptr(), Y.data_ptr(), 1, H, T, T, 0, 0, T, 1.0, 2, 2, 2, 1, stream()))
+    close(Y, ref, rtol=1e-2, atol=2e-3)
+    assert not Y.float().triu(1).any()            # masked positions are exactly zero
+    Yf = torch.empty(1, H, T, T, dtype=torch.float32, device="cuda")
+    ok(lib, lib.b200_softmax(X.data_ptr(), None, Yf.data_ptr(), 1, H, T, T, 0, 0, 0, 0.5, 2, 0, 0, 0, stream()))
+    close(Yf, torch.softmax(x.float() * 0.5, -1), rtol=1e-3, atol=1e-5)
+
+
+def test_softmax_full_size_properties(lib):
+    """[12, 8192, 8192] causal: too large for the CPU oracle in a test, so check what must
+    hold: rows sum to 1, masked columns are 0, row 0 is one-hot."""
+    T, H = 8192, 12
+    x = torch.randn(1, H, T, T, device="cuda", dtype=torch.bfloat16, generator=torch.Generator("cuda").manual_seed(0))
+    mask = torch.full((T, T), torch.finfo(torch.bfloat16).min, device="cuda", dtype=torch.bfloat16).triu(1)[None, None]
+    y = torch.empty_like(x)
+    ok(lib, lib.b200_softmax(x.data_ptr(), mask.data_ptr(), y.data_ptr(), 1, H, T, T, 0, 0, T, 1.0, 2, 2, 2, 1, stream()))
+    for h in (0, H - 1):
+        sums = y[0, h].float().sum(-1)
+        assert (sums - 1).abs().max() < 2e-2
+        assert not y[0, h].triu(1).any()
+        assert y[0, h, 0, 0] == 1
+
+
+@pytest.mark.parametrize("T", [1, 128, 2048])
+def test_silu_mul_and_add_relu_chains(lib, T):
+    from cuda_runtime import native
+
+    dtype = torch.bfloat16
+    g, u = gen((T, 8960), dtype), gen((T, 8960), dtype, 1)
+    G, U = g.cuda(), u.cuda()
+    Y = torch.empty_like(G)
+    ins = (native.Tensor * 2)(bt(G), bt(U))
+    ops = (native.EwOp * 2)(native.EwOp(2, 0, -1, 2, 0.0), native.EwOp(8, 4, 1, 2, 0.0))
+    out = bt(Y)
+    ok(lib, lib.b200_ew_chain(C.byref(out), ins, 2, ops, 2, stream()))
+    ref = (torch.nn.functional.silu(g.float()).to(dtype).float() * u.float()).to(dtype)
+    close(Y, ref, rtol=1e-2, atol=1e-2)
+    ops = (native.EwOp * 2)(native.EwOp(7, 0, 1, 2, 0.0), native.EwOp(1, 4, -1, 2, 0.0))
+    ok(lib, lib.b200_ew_chain(C.byref(out), ins, 2, ops, 2, stream()))
+    assert torch.equal(Y.cpu(), torch.relu((g.float() + u.float()).to(dtype)))
+
+
+def test_ew_chain_broadcast_and_strided(lib):
+    from cuda_runtime import native
+
+    x = gen((2, 5, 7, 16), torch.float16).cuda()
+    b = gen((1, 5, 1, 1), torch.float32, 1).cuda()
+    xt = x.permute(0, 2, 3, 1)                                  # channels-last style view
+    y = torch.empty(2, 7, 16, 5, dtype=torch.float16, device="cuda")
+    ins = (native.Tensor * 2)(bt(xt), bt(b.permute(0, 2, 3, 1).expand(2, 7, 16, 5)))
+    ops = (native.EwOp * 3)(native.EwOp(8, 0, 1, 0, 0.0), native.EwOp(11, 4, -1, 0, 0.25), native.EwOp(3, 5, -1, 1, 0.0))
+    out = bt(y)
+    ok(lib, lib.b200_ew_chain(C.byref(out), ins, 2, ops, 3, stream()))
+    ref = -(xt.float() * b.permute(0, 2, 3, 1) + 0.25)
+    close(y, ref, rtol=2e-3, atol=2e-3)
+
+
+@pytest.mark.parametrize("T", [1, 128, 2048])
+def test_rope_table_and_rotate(lib, T):
+    dtype, H, D = torch.bfloat16, 12, 128
+    inv = 1.0 / (1e6 ** (torch.arange(0, D, 2).float() / D))
+    pos = torch.arange(T) + 4096
+    ang = torch.cat([pos.float()[:, None] * inv[None]] * 2, -1)
+    cos, sin = ang.cos().to(dtype), ang.sin().to(dtype)
+    INV, POS = inv.cuda(), pos.cuda()
+    Cd, Sd = torch.empty(T, D, dtype=dtype, device="cuda"), torch.empty(T, D, dtype=dtype, device="cuda")
+    ok(lib, lib.b200_rope_table(INV.data_ptr(), POS.data_ptr(), Cd.data_ptr(), Sd.data_ptr(), T, D, 4, 2, stream()))
+    for got, ref in ((Cd, cos), (Sd, sin)):
+        ulp = (got.cpu().view(torch.int16).int() - ref.view(torch.int16).int()).abs()
+        assert ulp.max() <= 1 and (ulp != 0).float().mean() < 0.01
+    x = gen((1, T, H, D), dtype).transpose(1, 2)
+    xf = x.float()
+    rot = torch.cat([-xf[..., D // 2:], xf[..., : D // 2]], -1)
+    ref = ((xf * cos.float()).to(dtype).float() + (rot * sin.float()).to(dtype).float()).to(dtype)
+    X = x.transpose(1, 2).contiguous().cuda().transpose(1, 2)
+    Y = torch.empty(1, H, T, D, dtype=dtype, device="cuda")
+    xs = bt(X)
+    ok(lib, lib.b200_rope_rotate(C.byref(xs), cos.cuda().data_ptr(), sin.cuda().data_ptr(), Y.data_ptr(), None, None, 0, 0, stream()))
+    assert torch.equal(Y.cpu(), ref)
+
+
+def test_embedding_is_bit_exact(lib):
+    V, D = 151936, 1536
+    table = torch.randn(V, D, generator=torch.Generator().manual_seed(0)).bfloat16()
+    ids = torch.tensor([0, V - 1, 70000, 65505, 2049, 151935, 1, 1], dtype=torch.int64)
+    Tb, I = table.cuda(), ids.cuda()
+    out = torch.empty(len(ids), D, dtype=torch.bfloat16, device="cuda")
+    ok(lib, lib.b200_embedding(Tb.data_ptr(), I.data_ptr(), out.data_ptr(), len(ids), V, D * 2, 4, stream()))
+    assert torch.equal(out.cpu().view(torch.int16), table[ids].view(torch.int16))
+    I32 = ids.int().cuda()
+    ok(lib, lib.b200_embedding(Tb.data_ptr(), I32.data_ptr(), out.data_ptr(), len(ids), V, D * 2, 3, stream()))
+    assert torch.equal(out.cpu().view(torch.int16), table[ids].view(torch.int16))
+    ok(lib, lib.b200_embedding(Tb.data_ptr(), I.data_ptr(), out.data_ptr(), 0, V, D * 2, 4, stream()))  # empty gather
+
+
+@pytest.mark.parametrize("in_place", [True, False])
+def test_index_copy_is_bit_exact(lib, in_place):
+    B, H, S, D = 3, 2, 4352, 128
+    cache, src = gen((B, H, S, D)), gen((B, 1, H, D), seed=1).transpose(1, 2)   # src is a strided view, as in the graph
+    pos = torch.tensor([4100])
+    ref = cache.index_copy(2, pos, src)
+    Cc, Sc, P = cache.cuda(), src.transpose(1, 2).contiguous().cuda().transpose(1, 2), pos.cuda()
+    dst = Cc if in_place else torch.zeros_like(Cc)
+    ok(lib, lib.b200_index_copy(Cc.data_ptr(), dst.data_ptr(), Sc.data_ptr(), P.data_ptr(), B * H, S, D, 1, D, D * H, 2, 4, stream()))
+    assert torch.equal(dst.cpu().view(torch.int16), ref.view(torch.int16))
+
+
+def test_strided_copy_transpose_cast_and_pad(lib):
+    x = gen((2, 3, 20, 20), torch.float32)
+    X = x.cuda()
+    full = torch.zeros(2, 20, 20, 8, dtype=torch.float16, device="cuda")
+    dst = full.permute(0, 3, 1, 2)[:, :3]                       # NCHW-shaped window of an NHWC8 buffer
+    a, b = bt(dst), bt(X)
+    ok(lib, lib.b200_strided_copy(C.byref(a), C.byref(b), stream()))
+    assert torch.equal(full[..., :3].cpu(), x.permute(0, 2, 3, 1).half()) and not full[..., 3:].any()
+    y = gen((4, 6, 128), torch.bfloat16).cuda()
+    z = torch.empty(6, 4, 128, dtype=torch.bfloat16, device="cuda")
+    a, b = bt(z), bt(y.transpose(0, 1))
+    ok(lib, lib.b200_strided_copy(C.byref(a), C.byref(b), stream()))
+    assert torch.equal(z, y.transpose(0, 1).contiguous())
+
+
+def test_pooling_and_batchnorm(lib):
+    x = gen((2, 64, 112, 112), torch.float16)
+    for cl in (True, False):
+        X = x.cuda().contiguous(memory_format=torch.channels_last) if cl else x.cuda()
+        Y = torch.empty(2, 64, 56, 56, dtype=torch.float16, device="cuda")
+        Y = Y.contiguous(memory_format=torch.channels_last) if cl else Y
+        a, b = bt(X), bt(Y)
+        ok(lib, lib.b200_max_pool2d(C.byref(a), C.byref(b), 3, 3, 2, 2, 1, 1, stream()))
+        assert torch.equal(Y.cpu(), torch.nn.functional.max_pool2d(x.float(), 3, 2, 1).half())
+        Z = torch.empty(2, 64, 1, 1, dtype=torch.float16, device="cuda")
+        c = bt(Z)
+        ok(lib, lib.b200_adaptive_avg_pool2d(C.byref(a), C.byref(c), stream()))
+        close(Z, x.float().mean((2, 3), keepdim=True), rtol=2e-3, atol=2e-3)
+    g, be, m, v = (torch.rand(64) + 0.5).cuda(), torch.randn(64).cuda(), torch.randn(64).cuda(), (torch.rand(64) + 0.5).cuda()
+    X = x.cuda()
+    Y = torch.empty_like(X)
+    a, b = bt(X), bt(Y)
+    ok(lib, lib.b200_batch_norm(C.byref(a), C.byref(b), g.data_ptr(), be.data_ptr(), m.data_ptr(), v.data_ptr(), 1e-5, 0, 0, stream()))
+    close(Y, torch.nn.functional.batch_norm(x.float(), m.cpu(), v.cpu(), g.cpu(), be.cpu(), False, 0.0, 1e-5), rtol=2e-3, atol=4e-3)
+
+
+def test_matmul_strided_and_mean_and_fill(lib):
+    a, b = gen((2, 3, 20, 24), torch.bfloat16), gen((2, 1, 17, 24), torch.bfloat16, 1)
+    A, B = a.cuda(), b.cuda()
+    Bt = B.transpose(2, 3).expand(2, 3, 24, 17)
+    out = torch.empty(2, 3, 20, 17, dtype=torch.bfloat16, device="cuda")
+    arr = lambda t: (C.c_int64 * 4)(*t.stride())
+    ok(lib, lib.b200_matmul_strided(A.data_ptr(), Bt.data_ptr(), out.data_ptr(), 2, 3, 20, 17, 24, arr(A), arr(Bt), arr(out), 2, stream()))
+    close(out, a.float() @ b.float().transpose(2, 3), rtol=1e-2, atol=5e-2)
+    x = gen((50, 333), torch.float32).cuda()
+    y = torch.empty(50, dtype=torch.float32, device="cuda")
+    ok(lib, lib.b200_mean_last_dim(x.data_ptr(), y.data_ptr(), 50, 333, 0, 0, stream()))
+    close(y, x.mean(-1), rtol=1e-5, atol=1e-6)
+    z = torch.empty(1000, dtype=torch.bfloat16, device="cuda")
+    ok(lib, lib.b200_fill(z.data_ptr(), 1000, -2.5, 2, stream()))
+    assert (z == -2.5).all()
+
+
+def test_argmax_rows_matches_and_breaks_ties_low(lib):
+    x = gen((9, 151936), torch.bfloat16)
+    x[3, 77] = x[3, 150000] = 50.0
+    X = x.cuda()
+    out = torch.empty(9, dtype=torch.int64, device="cuda")
+    ok(lib, lib.b200_argmax_rows(X.data_ptr(), out.data_ptr(), 9, 151936, 151936, 2, stream()))
+    ref = torch.tensor([int(np.flatnonzero(r == r.max())[0]) for r in x.float().numpy()])
+    assert torch.equal(out.cpu(), ref) and out[3] == 77
