@@ -281,7 +281,8 @@ def test_rope_table_and_rotate(lib, T):
     X = x.transpose(1, 2).contiguous().cuda().transpose(1, 2)
     Y = torch.empty(1, H, T, D, dtype=dtype, device="cuda")
     xs = bt(X)
-    ok(lib, lib.b200_rope_rotate(C.byref(xs), cos.cuda().data_ptr(), sin.cuda().data_ptr(), Y.data_ptr(), None, None, 0, 0, stream()))
+    cos_d, sin_d = cos.cuda(), sin.cuda()
+    ok(lib, lib.b200_rope_rotate(C.byref(xs), cos_d.data_ptr(), sin_d.data_ptr(), Y.data_ptr(), None, None, 0, 0, stream()))
     assert torch.equal(Y.cpu(), ref)
 
 
