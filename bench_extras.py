@@ -1,0 +1,112 @@
+"""Secondary workloads reported next to the headline decode number (``"also"`` in the
+benchmark's JSON line): Qwen2.5-1.5B-architecture decode at B=1 and B=8, prefill of a
+512-token prompt, and ResNet-50 fp16 inference at batch 1 / 32 / 256.  All are timed with
+CUDA events over device-resident inputs, after warm-up, as whole-graph replays.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+import model_zoo as mz
+from ir_export import extract_ir
+
+CACHE_LEN, PREFILLED = 4352, 4096
+
+
+def _time_runs(fn, warmup: int, iters: int) -> float:
+    """median milliseconds of ``fn()``"""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b))
+    return float(np.median(times))
+
+
+def _dag(ir, weights, device):
+    from cuda_compiler import compile_subgraph, is_cuda_op_supported
+    from cuda_runtime import CUDABackend
+    from npu_compiler import partition
+    from npu_runtime import DAGExecutor
+
+    dag = DAGExecutor(partition(ir, is_cuda_op_supported), CUDABackend(device.index), compile_subgraph)
+    dag.load_weights(weights)
+    pid = next(iter(dag.npu_programs))
+    return dag, dag._npu_executors[pid], dag._npu_weight_cache[pid]
+
+
+def qwen_decode(cfg, sd, device, B: int, hbm_gbs: float) -> dict:
+    from bench import decode_bytes_per_step
+    from cuda_runtime import CUDABuffer
+
+    L = cfg.num_hidden_layers
+    ir = extract_ir(mz.QwenDecodeWrapper(mz.qwen2_model(cfg), L), mz.qwen2_example_inputs(cfg, B, 1, CACHE_LEN), "qwen2_decode")
+    _, ex, w = _dag(ir, {k: CUDABuffer(v) for k, v in sd.items()}, device)
+    g = torch.Generator(device=device).manual_seed(7)
+    names = [s["name"] for s in ir["graph_inputs"]]
+    feed = {"input_ids": CUDABuffer(torch.randint(0, cfg.vocab_size, (B, 1), device=device, generator=g)),
+            "attention_mask": CUDABuffer(mz.causal_mask(B, 1, CACHE_LEN, PREFILLED).to(device)),
+            "position_ids": CUDABuffer(torch.full((B, 1), PREFILLED, device=device)),
+            "cache_position": CUDABuffer(torch.tensor([PREFILLED], device=device))}
+    for n in names[4:]:
+        feed[n] = CUDABuffer((torch.randn(B, cfg.num_key_value_heads, CACHE_LEN, 128, generator=g, device=device) * 0.5).bfloat16())
+    ms = _time_runs(lambda: ex.run(feed, w), 5, 30)
+    bts = decode_bytes_per_step(cfg, B, PREFILLED + 1)["total"]
+    return {"tokens_per_s": B / (ms / 1e3), "ms_per_step": ms, "algorithmic_bytes": int(bts),
+            "hbm_frac": bts / (ms * 1e-3) / 1e9 / hbm_gbs, "launches": ex.last_launch_count}
+
+
+def qwen_prefill(cfg, sd, device, T: int, tflops_peak: float) -> dict:
+    from cuda_runtime import CUDABuffer
+
+    ir = extract_ir(mz.QwenPrefillWrapper(mz.qwen2_model(cfg)), mz.qwen2_example_inputs(cfg, 1, T, None), "qwen2_prefill")
+    _, ex, w = _dag(ir, {k: CUDABuffer(v) for k, v in sd.items()}, device)
+    g = torch.Generator(device=device).manual_seed(7)
+    feed = {"input_ids": CUDABuffer(torch.randint(0, cfg.vocab_size, (1, T), device=device, generator=g)),
+            "attention_mask": CUDABuffer(mz.causal_mask(1, T, T, 0).to(device)),
+            "position_ids": CUDABuffer(torch.arange(T, device=device)[None]),
+            "cache_position": CUDABuffer(torch.arange(T, device=device))}
+    ms = _time_runs(lambda: ex.run(feed, w), 3, 10)
+    H, I, V, L = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size, cfg.num_hidden_layers
+    kvd = cfg.num_key_value_heads * 128
+    flops = 2 * T * (L * (H * H * 2 + 2 * kvd * H + 3 * H * I) + V * H) + L * cfg.num_attention_heads * 4 * T * T * 128
+    return {"ms": ms, "tflops": flops / (ms * 1e-3) / 1e12, "tensor_frac": flops / (ms * 1e-3) / 1e12 / tflops_peak,
+            "algorithmic_flops": int(flops), "launches": ex.last_launch_count, "tokens": T}
+
+
+def resnet50(device, batch: int, tflops_peak: float) -> dict:
+    from cuda_runtime import CUDABuffer
+
+    m = mz.resnet(50, seed=0)
+    ir = extract_ir(mz.resnet(50, device="meta"), (torch.zeros(batch, 3, 224, 224, device="meta"),), "resnet50")
+    _, ex, w = _dag(ir, mz.state_dict_numpy(m.state_dict()), device)
+    x = torch.randn(batch, 3, 224, 224, device=device, generator=torch.Generator(device=device).manual_seed(0)).half()
+    feed = {ir["graph_inputs"][0]["name"]: CUDABuffer(x)}
+    ms = _time_runs(lambda: ex.run(feed, w), 5, 20)
+    flops = 8.178e9 * batch
+    return {"images_per_s": batch / (ms / 1e3), "ms": ms, "tflops": flops / (ms * 1e-3) / 1e12,
+            "tensor_frac": flops / (ms * 1e-3) / 1e12 / tflops_peak, "launches": ex.last_launch_count}
+
+
+def run(cfg, sd, device) -> dict:
+    from bench import measured_peaks
+
+    hbm, tf, which = measured_peaks()
+    out = {"peaks": {"hbm_gbs": hbm, "bf16_tflops": tf, "source": which}}
+    for B in (1, 8):
+        out[f"qwen_decode_b{B}"] = qwen_decode(cfg, sd, device, B, hbm)
+        torch.cuda.empty_cache()
+    out["qwen_prefill_t512"] = qwen_prefill(cfg, sd, device, 512, tf)
+    torch.cuda.empty_cache()
+    for b in (1, 32, 256):
+        out[f"resnet50_b{b}"] = resnet50(device, b, tf)
+        torch.cuda.empty_cache()
+    return out

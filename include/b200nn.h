@@ -58,6 +58,10 @@ typedef struct b200_tensor {
 
 int b200_version(void);
 const char* b200_last_error(void);
+/* Diagnostic: the kernels' bounded waits (mbarrier waits of the tcgen05 GEMM) record a
+ * non-zero code in a device variable when they give up instead of hanging.  Reads (and
+ * optionally clears) it; this call synchronises the device. */
+int b200_debug_device_error(int* code, int clear);
 /* sm count, compute capability and opt-in shared memory of device `dev`. */
 int b200_device_info(int dev, int* sm_count, int* cc_major, int* cc_minor, int64_t* smem_optin_bytes);
 

@@ -5,6 +5,7 @@
 //   * gemm_skinny_kernel - M <= 64 (decode): weights streamed once from HBM straight into
 //                         MMA fragments (no shared memory), split-K across CTAs;
 //   * matmul_strided_kernel - fully strided batched fallback on CUDA cores.
+#include "gemm_tc5.cuh"
 #include "mma.cuh"
 
 namespace b200 {
@@ -509,6 +510,11 @@ extern "C" int b200_linear(const void* A, const void* W, const void* bias, const
     B200_CHECK_LAUNCH("gemm_skinny_kernel");
     return B200_OK;
   }
+  {
+    Tc5Args t{A, W, bias, residual, aux, out, M, N, K, lda, ldw, ldo, ldr, ldaux, dtype, bias_dtype, epilogue};
+    const int rc = linear_tc5(t, st);
+    if (rc != B200_ENOTSUP) return rc;
+  }
   GemmParams p;
   p.A = A; p.W = W; p.bias = bias; p.residual = residual; p.aux = aux; p.out = out;
   p.M = M; p.N = N; p.K = K; p.lda = lda; p.ldw = ldw; p.ldo = ldo; p.ldr = ldr; p.ldaux = ldaux;
@@ -527,13 +533,20 @@ extern "C" int b200_conv2d_nhwc(const void* x, const void* w, const float* bias,
   B200_CHECK_ARG(!(epilogue & B200_EPI_SILU_MUL), "b200_conv2d_nhwc: unsupported epilogue");
   if (!(aligned16(x) && aligned16(w))) B200_FAIL(B200_EALIGN, "b200_conv2d_nhwc: x and w must be 16-byte aligned");
   if (N == 0) return B200_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (KH == 1 && KW == 1 && sh == 1 && sw == 1 && ph == 0 && pw == 0 && static_cast<int64_t>(N) * Ho * Wo > 64) {
+    // a 1x1 stride-1 convolution over channels-last data is a plain GEMM over [N*H*W, C]
+    const int64_t rows = static_cast<int64_t>(N) * Ho * Wo;
+    Tc5Args t{x, w, bias, residual, nullptr, y, rows, O, C, C, C, O, O, 0, dtype, B200_F32, epilogue};
+    const int rc = linear_tc5(t, st);
+    if (rc != B200_ENOTSUP) return rc;
+  }
   GemmParams p;
   p.A = x; p.W = w; p.bias = bias; p.residual = residual; p.aux = nullptr; p.out = y;
   p.M = static_cast<int64_t>(N) * Ho * Wo; p.N = O; p.K = static_cast<int64_t>(KH) * KW * C;
   p.lda = 0; p.ldw = p.K; p.ldo = O; p.ldr = O; p.ldaux = 0;
   p.bias_dtype = B200_F32; p.epilogue = epilogue;
   p.g = ConvGeom{H, W, C, KH, KW, sh, sw, ph, pw, Ho, Wo};
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
   B200_DISPATCH_HALF(dtype, T, { return launch_tile_auto<T, true>(p, st); });
   return B200_OK;
 }

@@ -1,0 +1,241 @@
+// tcgen05 GEMM for large M:  out[M,N] = epi(A[M,K] * W[N,K]^T + bias + residual).
+//
+// One CTA computes a 128 x BN tile.  Warp 0 streams 128x64 (A) and BNx64 (W) tiles
+// through a ring of shared-memory stages with TMA (128-byte swizzle, no multicast);
+// warp 1 issues tcgen05.mma (M=128, N=BN, K=16) from shared-memory descriptors into a
+// tensor-memory accumulator and releases stages with tcgen05.commit; warps 2-5 read the
+// accumulator back with tcgen05.ld (each warp owns the 32 TMEM lanes of its quarter),
+// apply the epilogue in fp32 and store.  Every barrier wait is bounded: on a timeout the
+// CTA records an error code in `g_tc5_error`, drains its own copies and exits.
+#include "gemm_tc5.cuh"
+#include "tc5.cuh"
+
+namespace b200 {
+
+__device__ int g_tc5_error = 0;
+
+namespace {
+
+constexpr int BM = 128, BK = 64, ST = 5;
+constexpr int A_STAGE = BM * BK * 2;
+
+struct Tc5Params {
+  const void* bias; const void* residual; const void* aux; void* out;
+  int64_t M, N, K, ldo, ldr, ldaux;
+  int bias_dtype, epilogue;
+};
+
+template <typename T> struct AbFormat;
+template <> struct AbFormat<__half> { static constexpr int value = 0; };
+template <> struct AbFormat<__nv_bfloat16> { static constexpr int value = 1; };
+
+template <typename T, int BN>
+__global__ void __launch_bounds__(192, 1) gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                          const __grid_constant__ CUtensorMap map_w, const Tc5Params p) {
+  constexpr int B_STAGE = BN * BK * 2, STAGE = A_STAGE + B_STAGE;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  __shared__ __align__(8) uint64_t full_bar[ST], empty_bar[ST], acc_bar;
+  __shared__ uint32_t tmem_holder;
+  __shared__ int failed;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  const int KB = static_cast<int>((p.K + BK - 1) / BK);
+
+  if (threadIdx.x == 0) {
+    failed = 0;
+    for (int s = 0; s < ST; ++s) { tc5::mbar_init(&full_bar[s], 1); tc5::mbar_init(&empty_bar[s], 1); }
+    tc5::mbar_init(&acc_bar, 1);
+    tc5::fence_barrier_init();
+    tc5::prefetch_tensormap(&map_a);
+    tc5::prefetch_tensormap(&map_w);
+  }
+  if (warp == 1) { tc5::tmem_alloc(&tmem_holder, BN); tc5::tmem_relinquish(); }
+  tc5::tc_fence_before();
+  __syncthreads();
+  tc5::tc_fence_after();
+  const uint32_t tmem_base = tmem_holder;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int issued = 0;
+      for (int kb = 0; kb < KB; ++kb) {
+        const int s = kb % ST;
+        const uint32_t ph = (kb / ST) & 1;
+        if (!tc5::mbar_wait(&empty_bar[s], ph ^ 1)) { failed = 1; atomicExch(&g_tc5_error, 1); break; }
+        if (*reinterpret_cast<volatile int*>(&failed)) break;
+        tc5::mbar_arrive_expect_tx(&full_bar[s], STAGE);
+        tc5::tma_load_2d(smem + s * STAGE, &map_a, &full_bar[s], kb * BK, m0);
+        tc5::tma_load_2d(smem + s * STAGE + A_STAGE, &map_w, &full_bar[s], kb * BK, n0);
+        issued = kb + 1;
+      }
+      if (*reinterpret_cast<volatile int*>(&failed)) {  // wait (bounded) for our own copies still in flight
+        for (int kb = issued > ST ? issued - ST : 0; kb < issued; ++kb) tc5::mbar_wait(&full_bar[kb % ST], (kb / ST) & 1);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = tc5::umma_idesc(BM, BN, AbFormat<T>::value);
+      for (int kb = 0; kb < KB; ++kb) {
+        const int s = kb % ST;
+        const uint32_t ph = (kb / ST) & 1;
+        if (!tc5::mbar_wait(&full_bar[s], ph)) { failed = 1; atomicExch(&g_tc5_error, 2); break; }
+        tc5::tc_fence_after();
+        const uint32_t a_addr = tc5::smem_addr(smem + s * STAGE), b_addr = a_addr + A_STAGE;
+        const uint64_t da = tc5::umma_desc_sw128(a_addr), db = tc5::umma_desc_sw128(b_addr);
+#pragma unroll
+        for (int k = 0; k < BK / 16; ++k)  // 16 elements = 32 bytes = 2 descriptor address units
+          tc5::umma_f16(tmem_base, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+        tc5::umma_commit(&empty_bar[s]);
+      }
+      tc5::umma_commit(&acc_bar);
+    }
+  } else {
+    const int q = warp & 3;  // warps 2,3,4,5 -> TMEM lane quarters 2,3,0,1
+    bool ok = true;
+    if (lane == 0) ok = tc5::mbar_wait(&acc_bar, 0);
+    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+    if (!ok) { if (lane == 0) { failed = 1; atomicExch(&g_tc5_error, 3); } }
+    ok = ok && !*reinterpret_cast<volatile int*>(&failed);
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok) {
+      tc5::tc_fence_after();
+      const int64_t m = m0 + q * 32 + lane;
+      T* __restrict__ out = static_cast<T*>(p.out);
+      const T* __restrict__ res = static_cast<const T*>(p.residual);
+      const T* __restrict__ aux = static_cast<const T*>(p.aux);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        float v[32];
+        __syncwarp();  // tcgen05.ld is warp-collective; lanes that skipped the stores rejoin here
+        tc5::tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + c * 32, v);
+        const int64_t n = n0 + c * 32;
+        if (m >= p.M || n >= p.N) continue;
+        const int cnt = static_cast<int>(p.N - n < 32 ? p.N - n : 32);
+        if (p.bias) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) if (i < cnt) v[i] += load_as_f32(p.bias, n + i, p.bias_dtype);
+        }
+        if (res) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) if (i < cnt) v[i] = round_as<T>(v[i]) + to_f32<T>(res[m * p.ldr + n + i]);
+        }
+        if (p.epilogue & B200_EPI_RELU) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = fmaxf(v[i], 0.f);
+        }
+        if (p.epilogue & B200_EPI_SILU_MUL) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) if (i < cnt) {
+            const float s = round_as<T>(v[i]);
+            v[i] = round_as<T>(s / (1.f + expf(-s))) * to_f32<T>(aux[m * p.ldaux + n + i]);
+          }
+        }
+        T* o = out + m * p.ldo + n;
+        if (cnt == 32 && (reinterpret_cast<uintptr_t>(o) & 15u) == 0) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            float f[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) f[i] = v[8 * j + i];
+            reinterpret_cast<uint4*>(o)[j] = pack8<T>(f);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) if (i < cnt) o[i] = from_f32<T>(v[i]);
+        }
+      }
+      tc5::tc_fence_before();
+    }
+  }
+  __syncthreads();
+  if (warp == 1) { tc5::tc_fence_after(); tc5::tmem_dealloc(tmem_base, BN); }
+}
+
+// ---- host side -----------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &p, 12000, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// [rows, K] row-major with row stride `ld` elements -> map with a (64 x box_rows) box, 128-byte swizzle.
+bool make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t K, int64_t ld, int box_rows, int dtype) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
+  const cuuint32_t box[2] = {BK, static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUtensorMapDataType dt = dtype == B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  return fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <typename T, int BN> int launch(const Tc5Args& a, cudaStream_t st) {
+  constexpr int SMEM = ST * (A_STAGE + BN * BK * 2) + 1024;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(gemm_tc5_kernel<T, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) {
+      cudaGetLastError();
+      return B200_ENOTSUP;
+    }
+    configured = true;
+  }
+  CUtensorMap ma, mw;
+  if (!make_map(&ma, a.A, a.M, a.K, a.lda, BM, a.dtype) || !make_map(&mw, a.W, a.N, a.K, a.ldw, BN, a.dtype)) return B200_ENOTSUP;
+  Tc5Params p{a.bias, a.residual, a.aux, a.out, a.M, a.N, a.K, a.ldo, a.ldr, a.ldaux, a.bias_dtype, a.epilogue};
+  dim3 grid(static_cast<unsigned>(ceil_div(a.N, BN)), static_cast<unsigned>(ceil_div(a.M, BM)));
+  gemm_tc5_kernel<T, BN><<<grid, 192, SMEM, st>>>(ma, mw, p);
+  B200_CHECK_LAUNCH("gemm_tc5_kernel");
+  return B200_OK;
+}
+
+}  // namespace
+
+bool tc5_enabled() {
+  static int state = -1;
+  if (state < 0) {
+    const char* e = getenv("B200NN_DISABLE_TC5");
+    state = (e && e[0] == '1') ? 0 : 1;
+  }
+  return state == 1;
+}
+
+int linear_tc5(const Tc5Args& a, cudaStream_t st) {
+  if (!tc5_enabled()) return B200_ENOTSUP;
+  if (a.dtype != B200_BF16 && a.dtype != B200_F16) return B200_ENOTSUP;
+  if (a.K % 8 || a.lda % 8 || a.ldw % 8 || !aligned16(a.A) || !aligned16(a.W)) return B200_ENOTSUP;
+  if (a.M >= (1ll << 31) || a.N >= (1ll << 31) || a.K >= (1ll << 31)) return B200_ENOTSUP;
+  // narrower tiles when 128-wide ones would leave most SMs idle
+  const bool narrow = ceil_div(a.N, 128) * ceil_div(a.M, BM) < sm_count();
+  if (a.dtype == B200_BF16) return narrow ? launch<__nv_bfloat16, 64>(a, st) : launch<__nv_bfloat16, 128>(a, st);
+  return narrow ? launch<__half, 64>(a, st) : launch<__half, 128>(a, st);
+}
+
+}  // namespace b200
+
+extern "C" int b200_debug_device_error(int* code, int clear) {
+  int v = 0;
+  cudaError_t e = cudaMemcpyFromSymbol(&v, b200::g_tc5_error, sizeof(int));
+  if (e != cudaSuccess) B200_FAIL(B200_ELAUNCH, "b200_debug_device_error: %s", cudaGetErrorString(e));
+  if (code) *code = v;
+  if (clear && v) {
+    v = 0;
+    cudaMemcpyToSymbol(b200::g_tc5_error, &v, sizeof(int));
+  }
+  return B200_OK;
+}

@@ -86,6 +86,27 @@ def test_linear(lib, dtype, M, N, K, bias, res, relu, silu):
                                 (1 if relu else 0) | (2 if silu else 0), p(Uv), N, p(ws), ws.numel(), stream()))
         close(out, ref, rtol=2e-2, atol=2e-2 * max(1.0, math.sqrt(K) * 0.05))
     assert not ws.any()
+    code = C.c_int(-1)
+    ok(lib, lib.b200_debug_device_error(C.byref(code), 1))
+    assert code.value == 0, f"a bounded wait in the tcgen05 GEMM gave up (code {code.value})"
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (129, 200, 72), (1000, 1536, 1536), (512, 151936, 1536)])
+def test_linear_tcgen05_shapes(lib, M, N, K):
+    """Large-M linears take the tcgen05/TMEM path: tile edges, K tails and a very wide N."""
+    dtype = torch.bfloat16
+    a, w = gen((M, K), dtype), gen((N, K), dtype, 1, 0.05)
+    A, W = a.cuda(), w.cuda()
+    out = torch.full((M, N), float("nan"), dtype=dtype, device="cuda")
+    ok(lib, lib.b200_linear(A.data_ptr(), W.data_ptr(), None, None, out.data_ptr(), M, N, K, K, K, N, 0, 2, 2, 0, None, 0, None, 0, stream()))
+    ref = (A.float() @ W.float().t())           # fp32 GEMM on the device as the large-size reference
+    err = (out.float() - ref).abs().max().item()
+    assert err <= 2e-2 * max(1.0, math.sqrt(K) * 0.05) + 1e-2 * ref.abs().max().item(), err
+    if N <= 2048:
+        close(out, a.float() @ w.float().t(), rtol=2e-2, atol=2e-2 * max(1.0, math.sqrt(K) * 0.05))
+    code = C.c_int(-1)
+    ok(lib, lib.b200_debug_device_error(C.byref(code), 1))
+    assert code.value == 0
 
 
 def test_linear_rejects_unaligned(lib):
