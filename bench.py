@@ -101,6 +101,20 @@ class ClockSampler:
             self.result = {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def max_over_ranks(values, world: int, device=None):
+    """Slowest rank decides: element-wise MAX of per-rank timings over the process group."""
+    if world <= 1:
+        return [float(v) for v in values]
+    t = torch.tensor(list(values), device=device, dtype=torch.float64)
+    torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    return [float(v) for v in t]
+
+
+def whole_job_throughput(world: int, units_per_rank_per_step: int, steps: int, ms: float) -> float:
+    """Units all ranks processed divided by the (max-over-ranks) time."""
+    return world * units_per_rank_per_step * steps / (ms / 1e3)
+
+
 # ---------------------------------------------------------------------------------------
 def decode_bytes_per_step(cfg, B: int, L: int) -> dict:
     """Algorithmic HBM bytes of one decode step: every weight once (tied head counted once,
@@ -247,18 +261,15 @@ def run_b200(args, rank: int, world: int, device):
     bts = decode_bytes_per_step(cfg, B, L_valid)
     hbm, _, which = measured_peaks()
 
-    if world > 1:
-        t = torch.tensor([ms, e2e_ms], device=device, dtype=torch.float64)
-        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
-        ms, e2e_ms = float(t[0]), float(t[1])
+    ms, e2e_ms = max_over_ranks([ms, e2e_ms], world, device)
     line = {
-        "metric": METRIC, "value": world * B * K / (ms / 1e3), "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
+        "metric": METRIC, "value": whole_job_throughput(world, B, K, ms), "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
         "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": f"Qwen2.5-1.5B-arch greedy decode, {args.layers} layers, B={B} sequences per GPU, KV cache {CACHE_LEN} rows "
                                f"with {PREFILLED} filled, lock-step positions from {PREFILLED}", "batch_per_gpu": B,
                    "cache_len": CACHE_LEN, "prefilled": PREFILLED, "parallelism": f"replicas x{world}, batch sharded, no collective",
                    "l2_policy": "inputs larger than L2: every step streams 3.1 GB of weights and the KV cache"},
-        "e2e": {"value": world * B * K / (e2e_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
+        "e2e": {"value": whole_job_throughput(world, B, K, e2e_ms), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
                 "ms_per_step": e2e_ms / K, "api": "DAGExecutor.execute(host inputs) -> argmax -> to_numpy()"},
         "gpu_launches": int(launches_per_step * K),
         "clocks": clocks.result,
