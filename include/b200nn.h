@@ -183,6 +183,17 @@ int b200_rope_rotate(const b200_tensor* x, const void* cos_t, const void* sin_t,
                      void* kv_cache, const void* cache_pos, int64_t cache_len, int pos_dtype,
                      void* stream);
 
+/* The three per-token steps between the QKV projection and decode attention in one
+ * launch: RoPE on q -> q_out [B,Hq,T,D] dense; RoPE on k -> key cache row cache_pos[t];
+ * v -> value cache row cache_pos[t] (caches [B,Hkv,cache_len,D], updated in place).
+ * Replaces two rotate chains and two index_copy_kernel launches
+ * (cuda_templates.py:114-162; steps subgraph_analyzer.py:395-428).  q, k, v are
+ * [B,H,T,D] views with arbitrary strides over (b,h,t); cos/sin are [B,T,D]. */
+int b200_qkv_rope_cache(const b200_tensor* q, const b200_tensor* k, const b200_tensor* v,
+                        const void* cos_t, const void* sin_t, void* q_out, void* k_cache,
+                        void* v_cache, const void* cache_pos, int64_t cache_len, int pos_dtype,
+                        void* stream);
+
 /* ------------------------------------------------------------------------- *
  * Pooling / normalisation for the CNN path (NCHW logical shape, any strides, so
  * channels-last storage is simply a stride pattern).

@@ -53,7 +53,7 @@ template <typename T> struct AttnWarp {
                                        int64_t n_keys, float scale, const float (&add)[2][4], int g, int t) {
     const uint4 zero4 = make_uint4(0, 0, 0, 0);
     // ---- issue all loads for this block -----------------------------------------
-    uint4 kf[2][4];
+    uint4 kf[2][4];  // [key tile][32-dim slice]
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
       const int64_t key = kb + 8 * j + g;
@@ -69,6 +69,12 @@ template <typename T> struct AttnWarp {
 #pragma unroll
       for (int a = 0; a < 2; ++a) vf[a][s] = key < n_keys ? ld_global_nc_v4(vr + 64 * a) : zero4;
     }
+    compute(kf, vf, kb, n_keys, scale, add, t);
+  }
+
+  // Same block, fragments already in registers (from global memory or from a shared-memory stage).
+  __device__ __forceinline__ void compute(const uint4 (&kf)[2][4], const uint4 (&vf)[2][4], int64_t kb, int64_t n_keys, float scale,
+                                          const float (&add)[2][4], int t) {
     // ---- S = Q K^T ---------------------------------------------------------------
     float s[2][4];
 #pragma unroll
@@ -159,9 +165,20 @@ struct DecodeParams {
 
 constexpr int DEC_MAX_BLOCKS = 128;  // 16-key blocks per split (split_len <= 2048)
 
+constexpr int DEC_STAGES = 3;                  // per-warp cp.async ring depth
+constexpr int DEC_STAGE_BYTES = 2 * 16 * HD * 2;  // 16 keys of K and of V
+constexpr int DEC_SMEM = 4 * DEC_STAGES * DEC_STAGE_BYTES;
+constexpr int DEC_MAX_SPLIT = 256;             // keys per split (mask values of a split are staged in shared memory)
+
+// Each warp streams its own 16-key blocks through a private 3-stage ring of shared memory
+// filled with cp.async (two blocks, 16 KB, in flight per warp while a third is consumed).
+// Rows are stored with an XOR on the 16-byte chunk index chosen so that the fragment reads
+// below are bank-conflict free: K rows use chunk ^ 4*(row&1), V rows chunk ^ 2*((row>>1)&3).
 template <typename T>
-__global__ void __launch_bounds__(128) attn_decode_kernel(const __grid_constant__ DecodeParams p) {
+__global__ void __launch_bounds__(128, 2) attn_decode_kernel(const __grid_constant__ DecodeParams p) {
+  extern __shared__ __align__(128) uint8_t dsm[];
   __shared__ uint32_t valid[DEC_MAX_BLOCKS / 32];
+  __shared__ float s_mask[DEC_MAX_SPLIT];
   __shared__ float s_acc[8][HD];
   __shared__ float s_m[4][8], s_l[4][8];
 
@@ -172,20 +189,17 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const __grid_constant_
   const int64_t s_end = min(p.S, s_begin + p.split_len);
   const int nblk = static_cast<int>((s_end - s_begin + 15) / 16);
 
-  // ---- which 16-key blocks have at least one unmasked key ---------------------------
+  // ---- mask values of this split; which 16-key blocks have at least one unmasked key ----
   if (threadIdx.x < DEC_MAX_BLOCKS / 32) valid[threadIdx.x] = 0u;
   for (int i = threadIdx.x; i < 8 * HD; i += 128) (&s_acc[0][0])[i] = 0.f;
   __syncthreads();
-  if (p.mask) {
-    for (int64_t key = s_begin + threadIdx.x; key < s_end; key += 128) {
-      const float mv = load_as_f32(p.mask, b * p.mask_bs + key, p.mask_dtype);
-      if (mv > MASKED) {
-        const int blk = static_cast<int>((key - s_begin) >> 4);
-        atomicOr(&valid[blk >> 5], 1u << (blk & 31));
-      }
-    }
-  } else {
-    for (int blk = threadIdx.x; blk < nblk; blk += 128) atomicOr(&valid[blk >> 5], 1u << (blk & 31));
+  for (int i = threadIdx.x; i < nblk * 16; i += 128) {
+    const int64_t key = s_begin + i;
+    float mv = 0.f;
+    if (key >= s_end) mv = -INFINITY;
+    else if (p.mask) mv = load_as_f32(p.mask, b * p.mask_bs + key, p.mask_dtype);
+    s_mask[i] = mv;
+    if (mv > MASKED) atomicOr(&valid[i >> 9], 1u << ((i >> 4) & 31));
   }
   __syncthreads();
 
@@ -193,24 +207,80 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const __grid_constant_
   w.init();
   const T* qb = static_cast<const T*>(p.q) + b * p.q_bs + static_cast<int64_t>(hk) * p.G * HD;
   w.load_q(g < p.G ? qb + g * HD : nullptr, (g + 8) < p.G ? qb + (g + 8) * HD : nullptr, t);
-  const T* kbase = static_cast<const T*>(p.k) + b * p.kv_bs + hk * p.kv_hs;
-  const T* vbase = static_cast<const T*>(p.v) + b * p.kv_bs + hk * p.kv_hs;
+  const T* kbase = static_cast<const T*>(p.k) + b * p.kv_bs + hk * p.kv_hs + s_begin * HD;
+  const T* vbase = static_cast<const T*>(p.v) + b * p.kv_bs + hk * p.kv_hs + s_begin * HD;
+  const uint32_t ring = smem_u32(dsm) + warp * (DEC_STAGES * DEC_STAGE_BYTES);
 
-  for (int blk = warp; blk < nblk; blk += 4) {
-    if (!((valid[blk >> 5] >> (blk & 31)) & 1u)) continue;
-    const int64_t kb = s_begin + 16 * blk;
+  auto is_valid = [&](int blk) { return ((valid[blk >> 5] >> (blk & 31)) & 1u) != 0u; };
+  auto next_valid = [&](int blk) {  // first valid block of this warp at or after blk (stride 4)
+    while (blk < nblk && !is_valid(blk)) blk += 4;
+    return blk;
+  };
+  // copy block `blk` (16 keys x 256 B of K and of V) into ring stage `st`
+  auto issue = [&](int blk, int st) {
+    const uint32_t sk = ring + st * DEC_STAGE_BYTES, sv = sk + 16 * HD * 2;
+    const int64_t key0 = static_cast<int64_t>(blk) * 16;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int idx = i * 32 + lane, r = idx >> 4, ch = idx & 15;
+      const bool ok = s_begin + key0 + r < s_end;
+      const int64_t off = (key0 + r) * HD + ch * 8;
+      cp_async16(sk + r * 256 + ((ch ^ (4 * (r & 1))) << 4), ok ? static_cast<const void*>(kbase + off) : static_cast<const void*>(kbase), ok ? 16 : 0);
+      cp_async16(sv + r * 256 + ((ch ^ (2 * ((r >> 1) & 3))) << 4), ok ? static_cast<const void*>(vbase + off) : static_cast<const void*>(vbase), ok ? 16 : 0);
+    }
+  };
+
+  int fetch = next_valid(warp);   // next block to copy
+  int st_fetch = 0;
+#pragma unroll
+  for (int i = 0; i < DEC_STAGES - 1; ++i) {
+    if (fetch < nblk) { issue(fetch, st_fetch); fetch = next_valid(fetch + 4); }
+    cp_async_commit();
+    st_fetch = (st_fetch + 1) % DEC_STAGES;
+  }
+  int st_use = 0;
+  for (int blk = next_valid(warp); blk < nblk; blk = next_valid(blk + 4)) {
+    cp_async_wait<DEC_STAGES - 2>();
+    __syncwarp();   // every lane's copies for this stage have landed; the stage consumed last time is free
+    if (fetch < nblk) { issue(fetch, st_fetch); fetch = next_valid(fetch + 4); }
+    cp_async_commit();
+    st_fetch = (st_fetch + 1) % DEC_STAGES;
+
+    const uint32_t sk = ring + st_use * DEC_STAGE_BYTES, sv = sk + 16 * HD * 2;
+    uint4 kf[2][4], vf[2][4];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int r = 8 * j + g;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int ch = 4 * c + t;
+        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(kf[j][c].x), "=r"(kf[j][c].y), "=r"(kf[j][c].z), "=r"(kf[j][c].w)
+                     : "r"(sk + r * 256 + ((ch ^ (4 * (r & 1))) << 4)));
+      }
+    }
+#pragma unroll
+    for (int s = 0; s < 4; ++s) {
+      const int r = 2 * t + (s & 1) + 8 * (s >> 1);
+#pragma unroll
+      for (int a = 0; a < 2; ++a) {
+        const int ch = g + 8 * a;
+        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(vf[a][s].x), "=r"(vf[a][s].y), "=r"(vf[a][s].z), "=r"(vf[a][s].w)
+                     : "r"(sv + r * 256 + ((ch ^ (2 * t)) << 4)));
+      }
+    }
     float add[2][4];
 #pragma unroll
     for (int j = 0; j < 2; ++j)
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
-        const int64_t key = kb + 8 * j + 2 * t + e;
-        const float mv = (p.mask && key < s_end) ? load_as_f32(p.mask, b * p.mask_bs + key, p.mask_dtype) : 0.f;
+        const float mv = s_mask[blk * 16 + 8 * j + 2 * t + e];
         add[j][e] = mv;
         add[j][2 + e] = mv;
       }
-    w.step(kbase, vbase, HD, HD, kb, s_end, p.scale, add, g, t);
+    w.compute(kf, vf, s_begin + static_cast<int64_t>(blk) * 16, s_end, p.scale, add, t);
+    st_use = (st_use + 1) % DEC_STAGES;
   }
+  cp_async_wait<0>();
 
   // ---- merge the four warps (rows 0..7 only: G <= 8 lives in the g half) --------------
   if (t == 0) { s_m[warp][g] = w.m[0]; s_l[warp][g] = w.l[0]; }
@@ -378,7 +448,13 @@ extern "C" int b200_attn_decode(const void* q, const void* k, const void* v, con
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   dim3 grid(static_cast<unsigned>(d.splits), static_cast<unsigned>(Hkv), static_cast<unsigned>(B));
   B200_DISPATCH_HALF(dtype, T, {
-    attn_decode_kernel<T><<<grid, 128, 0, st>>>(p);
+    static bool configured = false;
+    if (!configured) {
+      cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM);
+      if (e != cudaSuccess) B200_FAIL(B200_ELAUNCH, "attn_decode_kernel attribute: %s", cudaGetErrorString(e));
+      configured = true;
+    }
+    attn_decode_kernel<T><<<grid, 128, DEC_SMEM, st>>>(p);
     attn_decode_merge_kernel<T><<<static_cast<unsigned>(B * Hq), 128, 0, st>>>(p.part_acc, p.part_ml, static_cast<T*>(out), Hq, Hkv,
                                                                                p.G, d.splits);
   });

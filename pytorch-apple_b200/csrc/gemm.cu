@@ -467,11 +467,20 @@ static SkinnyPlan plan_skinny(int64_t M, int64_t N, int64_t K) {
 
 using namespace b200;
 
-extern "C" int64_t b200_linear_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+static int64_t skinny_workspace_bytes(int64_t M, int64_t N, int64_t K) {
   if (M > 64 || M <= 0) return 0;
   const SkinnyPlan s = plan_skinny(M, N, K);
   if (s.splits <= 1) return 0;
   return s.row_blocks * SK_ROWS * s.mpad * 4 + s.row_blocks * 4 + 256;
+}
+
+// Which kernel family serves a linear of M rows: up to 16 rows the register-streaming
+// split-K kernel, above that the tcgen05 tiles (which also split K for narrow outputs).
+static bool prefers_skinny(int64_t M) { return M <= 16; }
+
+extern "C" int64_t b200_linear_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+  const int64_t a = skinny_workspace_bytes(M, N, K), b = linear_tc5_workspace_bytes(M, N, K);
+  return a > b ? a : b;
 }
 
 extern "C" int b200_linear(const void* A, const void* W, const void* bias, const void* residual, void* out, int64_t M,
@@ -484,6 +493,11 @@ extern "C" int b200_linear(const void* A, const void* W, const void* bias, const
   if (!(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0 && aligned16(A) && aligned16(W)))
     B200_FAIL(B200_EALIGN, "b200_linear: K, lda, ldw must be multiples of 8 and A, W 16-byte aligned");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (!prefers_skinny(M)) {
+    Tc5Args t{A, W, bias, residual, aux, out, M, N, K, lda, ldw, ldo, ldr, ldaux, dtype, bias_dtype, epilogue, workspace, workspace_bytes};
+    const int rc = linear_tc5(t, st);
+    if (rc != B200_ENOTSUP) return rc;
+  }
   if (M <= 64) {
     const SkinnyPlan s = plan_skinny(M, N, K);
     SkinnyParams p;
@@ -492,7 +506,7 @@ extern "C" int b200_linear(const void* A, const void* W, const void* bias, const
     p.bias_dtype = bias_dtype; p.epilogue = epilogue; p.splits = s.splits; p.k_per_split = s.k_per_split;
     p.ws = nullptr; p.ctr = nullptr;
     if (s.splits > 1) {
-      const int64_t need = b200_linear_workspace_bytes(M, N, K);
+      const int64_t need = skinny_workspace_bytes(M, N, K);
       if (!workspace || workspace_bytes < need || !aligned16(workspace))
         B200_FAIL(B200_EINVAL, "b200_linear: workspace of %lld bytes required (got %lld)", (long long)need, (long long)workspace_bytes);
       p.ws = static_cast<float*>(workspace);
@@ -509,11 +523,6 @@ extern "C" int b200_linear(const void* A, const void* W, const void* bias, const
     });
     B200_CHECK_LAUNCH("gemm_skinny_kernel");
     return B200_OK;
-  }
-  {
-    Tc5Args t{A, W, bias, residual, aux, out, M, N, K, lda, ldw, ldo, ldr, ldaux, dtype, bias_dtype, epilogue};
-    const int rc = linear_tc5(t, st);
-    if (rc != B200_ENOTSUP) return rc;
   }
   GemmParams p;
   p.A = A; p.W = W; p.bias = bias; p.residual = residual; p.aux = aux; p.out = out;
@@ -537,7 +546,7 @@ extern "C" int b200_conv2d_nhwc(const void* x, const void* w, const float* bias,
   if (KH == 1 && KW == 1 && sh == 1 && sw == 1 && ph == 0 && pw == 0 && static_cast<int64_t>(N) * Ho * Wo > 64) {
     // a 1x1 stride-1 convolution over channels-last data is a plain GEMM over [N*H*W, C]
     const int64_t rows = static_cast<int64_t>(N) * Ho * Wo;
-    Tc5Args t{x, w, bias, residual, nullptr, y, rows, O, C, C, C, O, O, 0, dtype, B200_F32, epilogue};
+    Tc5Args t{x, w, bias, residual, nullptr, y, rows, O, C, C, C, O, O, 0, dtype, B200_F32, epilogue, nullptr, 0};
     const int rc = linear_tc5(t, st);
     if (rc != B200_ENOTSUP) return rc;
   }

@@ -16,35 +16,87 @@ __device__ int g_tc5_error = 0;
 
 namespace {
 
-constexpr int BM = 128, BK = 64, ST = 5;
+constexpr int BM = 128, BK = 64;
 constexpr int A_STAGE = BM * BK * 2;
+template <int BN> struct Cfg { static constexpr int ST = BN == 128 ? 3 : 4; };  // two CTAs per SM either way
 
 struct Tc5Params {
   const void* bias; const void* residual; const void* aux; void* out;
-  int64_t M, N, K, ldo, ldr, ldaux;
-  int bias_dtype, epilogue;
+  float* ws;            // split-K partial sums, fp32 [M][ws_pitch]; zero on entry, zero on exit
+  unsigned int* ctr;    // one arrival counter per output tile; zero on entry and exit
+  int64_t M, N, K, ldo, ldr, ldaux, ws_pitch;
+  int bias_dtype, epilogue, splits, kb_per_split;
 };
 
 template <typename T> struct AbFormat;
 template <> struct AbFormat<__half> { static constexpr int value = 0; };
 template <> struct AbFormat<__nv_bfloat16> { static constexpr int value = 1; };
 
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+__device__ __forceinline__ void epilogue_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+// bias / residual / activation on 32 consecutive outputs of row m starting at column n, then store
+template <typename T>
+__device__ __forceinline__ void finish_row(const Tc5Params& p, float (&v)[32], int64_t m, int64_t n) {
+  const int cnt = static_cast<int>(p.N - n < 32 ? p.N - n : 32);
+  const T* __restrict__ res = static_cast<const T*>(p.residual);
+  const T* __restrict__ aux = static_cast<const T*>(p.aux);
+  if (p.bias) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) if (i < cnt) v[i] += load_as_f32(p.bias, n + i, p.bias_dtype);
+  }
+  if (res) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) if (i < cnt) v[i] = round_as<T>(v[i]) + to_f32<T>(res[m * p.ldr + n + i]);
+  }
+  if (p.epilogue & B200_EPI_RELU) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = fmaxf(v[i], 0.f);
+  }
+  if (p.epilogue & B200_EPI_SILU_MUL) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) if (i < cnt) {
+      const float s = round_as<T>(v[i]);
+      v[i] = round_as<T>(s / (1.f + expf(-s))) * to_f32<T>(aux[m * p.ldaux + n + i]);
+    }
+  }
+  T* o = static_cast<T*>(p.out) + m * p.ldo + n;
+  if (cnt == 32 && (reinterpret_cast<uintptr_t>(o) & 15u) == 0) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float f[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[i] = v[8 * j + i];
+      reinterpret_cast<uint4*>(o)[j] = pack8<T>(f);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) if (i < cnt) o[i] = from_f32<T>(v[i]);
+  }
+}
+
 template <typename T, int BN>
-__global__ void __launch_bounds__(192, 1) gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a,
+__global__ void __launch_bounds__(192, 2) gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a,
                                                           const __grid_constant__ CUtensorMap map_w, const Tc5Params p) {
+  constexpr int ST = Cfg<BN>::ST;
   constexpr int B_STAGE = BN * BK * 2, STAGE = A_STAGE + B_STAGE;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   __shared__ __align__(8) uint64_t full_bar[ST], empty_bar[ST], acc_bar;
   __shared__ uint32_t tmem_holder;
-  __shared__ int failed;
+  __shared__ int failed, is_last;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
   const int KB = static_cast<int>((p.K + BK - 1) / BK);
+  const int kb0 = blockIdx.z * p.kb_per_split;
+  const int nkb = min(KB, kb0 + p.kb_per_split) - kb0;   // >= 1 by construction of the grid
 
   if (threadIdx.x == 0) {
     failed = 0;
+    is_last = 0;
     for (int s = 0; s < ST; ++s) { tc5::mbar_init(&full_bar[s], 1); tc5::mbar_init(&empty_bar[s], 1); }
     tc5::mbar_init(&acc_bar, 1);
     tc5::fence_barrier_init();
@@ -60,33 +112,33 @@ __global__ void __launch_bounds__(192, 1) gemm_tc5_kernel(const __grid_constant_
   if (warp == 0) {
     if (lane == 0) {
       int issued = 0;
-      for (int kb = 0; kb < KB; ++kb) {
-        const int s = kb % ST;
-        const uint32_t ph = (kb / ST) & 1;
+      for (int i = 0; i < nkb; ++i) {
+        const int s = i % ST;
+        const uint32_t ph = (i / ST) & 1;
         if (!tc5::mbar_wait(&empty_bar[s], ph ^ 1)) { failed = 1; atomicExch(&g_tc5_error, 1); break; }
         if (*reinterpret_cast<volatile int*>(&failed)) break;
         tc5::mbar_arrive_expect_tx(&full_bar[s], STAGE);
-        tc5::tma_load_2d(smem + s * STAGE, &map_a, &full_bar[s], kb * BK, m0);
-        tc5::tma_load_2d(smem + s * STAGE + A_STAGE, &map_w, &full_bar[s], kb * BK, n0);
-        issued = kb + 1;
+        tc5::tma_load_2d(smem + s * STAGE, &map_a, &full_bar[s], (kb0 + i) * BK, m0);
+        tc5::tma_load_2d(smem + s * STAGE + A_STAGE, &map_w, &full_bar[s], (kb0 + i) * BK, n0);
+        issued = i + 1;
       }
       if (*reinterpret_cast<volatile int*>(&failed)) {  // wait (bounded) for our own copies still in flight
-        for (int kb = issued > ST ? issued - ST : 0; kb < issued; ++kb) tc5::mbar_wait(&full_bar[kb % ST], (kb / ST) & 1);
+        for (int i = issued > ST ? issued - ST : 0; i < issued; ++i) tc5::mbar_wait(&full_bar[i % ST], (i / ST) & 1);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc = tc5::umma_idesc(BM, BN, AbFormat<T>::value);
-      for (int kb = 0; kb < KB; ++kb) {
-        const int s = kb % ST;
-        const uint32_t ph = (kb / ST) & 1;
+      for (int i = 0; i < nkb; ++i) {
+        const int s = i % ST;
+        const uint32_t ph = (i / ST) & 1;
         if (!tc5::mbar_wait(&full_bar[s], ph)) { failed = 1; atomicExch(&g_tc5_error, 2); break; }
         tc5::tc_fence_after();
         const uint32_t a_addr = tc5::smem_addr(smem + s * STAGE), b_addr = a_addr + A_STAGE;
         const uint64_t da = tc5::umma_desc_sw128(a_addr), db = tc5::umma_desc_sw128(b_addr);
 #pragma unroll
         for (int k = 0; k < BK / 16; ++k)  // 16 elements = 32 bytes = 2 descriptor address units
-          tc5::umma_f16(tmem_base, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+          tc5::umma_f16(tmem_base, da + 2 * k, db + 2 * k, idesc, (i | k) != 0);
         tc5::umma_commit(&empty_bar[s]);
       }
       tc5::umma_commit(&acc_bar);
@@ -96,57 +148,56 @@ __global__ void __launch_bounds__(192, 1) gemm_tc5_kernel(const __grid_constant_
     bool ok = true;
     if (lane == 0) ok = tc5::mbar_wait(&acc_bar, 0);
     ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-    if (!ok) { if (lane == 0) { failed = 1; atomicExch(&g_tc5_error, 3); } }
+    if (!ok && lane == 0) { failed = 1; atomicExch(&g_tc5_error, 3); }
     ok = ok && !*reinterpret_cast<volatile int*>(&failed);
     ok = __all_sync(0xffffffffu, ok);
+    const int64_t m = m0 + q * 32 + lane;
+    const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
     if (ok) {
       tc5::tc_fence_after();
-      const int64_t m = m0 + q * 32 + lane;
-      T* __restrict__ out = static_cast<T*>(p.out);
-      const T* __restrict__ res = static_cast<const T*>(p.residual);
-      const T* __restrict__ aux = static_cast<const T*>(p.aux);
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         float v[32];
         __syncwarp();  // tcgen05.ld is warp-collective; lanes that skipped the stores rejoin here
-        tc5::tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + c * 32, v);
+        tc5::tmem_ld_32x32(t_row + c * 32, v);
         const int64_t n = n0 + c * 32;
-        if (m >= p.M || n >= p.N) continue;
-        const int cnt = static_cast<int>(p.N - n < 32 ? p.N - n : 32);
-        if (p.bias) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) if (i < cnt) v[i] += load_as_f32(p.bias, n + i, p.bias_dtype);
-        }
-        if (res) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) if (i < cnt) v[i] = round_as<T>(v[i]) + to_f32<T>(res[m * p.ldr + n + i]);
-        }
-        if (p.epilogue & B200_EPI_RELU) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = fmaxf(v[i], 0.f);
-        }
-        if (p.epilogue & B200_EPI_SILU_MUL) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) if (i < cnt) {
-            const float s = round_as<T>(v[i]);
-            v[i] = round_as<T>(s / (1.f + expf(-s))) * to_f32<T>(aux[m * p.ldaux + n + i]);
-          }
-        }
-        T* o = out + m * p.ldo + n;
-        if (cnt == 32 && (reinterpret_cast<uintptr_t>(o) & 15u) == 0) {
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            float f[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) f[i] = v[8 * j + i];
-            reinterpret_cast<uint4*>(o)[j] = pack8<T>(f);
-          }
+        if (m >= p.M) continue;
+        if (p.splits == 1) {
+          if (n < p.N) finish_row<T>(p, v, m, n);
         } else {
+          float* w = p.ws + m * p.ws_pitch + n;
 #pragma unroll
-          for (int i = 0; i < 32; ++i) if (i < cnt) o[i] = from_f32<T>(v[i]);
+          for (int j = 0; j < 8; ++j) red_add_v4(w + 4 * j, v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
         }
       }
       tc5::tc_fence_before();
+    }
+    if (p.splits > 1) {  // uniform for the whole grid: the four epilogue warps meet on named barrier 1
+      __threadfence();
+      epilogue_bar();
+      if (warp == 2 && lane == 0) {
+        const unsigned int tile = blockIdx.y * gridDim.x + blockIdx.x;
+        const unsigned int ticket = atomicAdd(p.ctr + tile, 1u);
+        is_last = ticket == static_cast<unsigned int>(p.splits) - 1u;
+        if (is_last) p.ctr[tile] = 0u;
+      }
+      epilogue_bar();
+      if (*reinterpret_cast<volatile int*>(&is_last) && m < p.M) {
+        __threadfence();
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          const int64_t n = n0 + c * 32;
+          float v[32];
+          float4* w = reinterpret_cast<float4*>(p.ws + m * p.ws_pitch + n);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float4 t = __ldcg(w + j);
+            __stcg(w + j, make_float4(0.f, 0.f, 0.f, 0.f));
+            v[4 * j] = t.x; v[4 * j + 1] = t.y; v[4 * j + 2] = t.z; v[4 * j + 3] = t.w;
+          }
+          if (n < p.N) finish_row<T>(p, v, m, n);
+        }
+      }
     }
   }
   __syncthreads();
@@ -185,8 +236,33 @@ bool make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t K, int64
             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <typename T, int BN> int launch(const Tc5Args& a, cudaStream_t st) {
-  constexpr int SMEM = ST * (A_STAGE + BN * BK * 2) + 1024;
+struct Tc5Plan { int bn, splits, kb_per_split; int64_t tiles_n, tiles_m, ws_pitch; };
+
+Tc5Plan plan_tc5(int64_t M, int64_t N, int64_t K) {
+  Tc5Plan pl;
+  const int64_t tm = ceil_div(M, BM);
+  // 64-wide tiles whenever 128-wide ones would not give every SM a tile (148 SMs; fixed so that
+  // the workspace size does not depend on the device the plan is made on)
+  pl.bn = ceil_div(N, 128) * tm < 148 ? 64 : 128;
+  pl.tiles_n = ceil_div(N, pl.bn);
+  pl.tiles_m = tm;
+  const int64_t tiles = pl.tiles_n * tm, KB = ceil_div(K, BK);
+  int64_t splits = 1;
+  if (tiles < 100) {
+    splits = ceil_div(148, tiles);
+    const int64_t by_traffic = K / (8 * (M < BM ? M : BM));   // partial sums stay well below the weight bytes
+    if (splits > by_traffic) splits = by_traffic;
+    if (splits > KB / 4) splits = KB / 4;                        // at least 4 k-blocks per CTA
+    if (splits < 1) splits = 1;
+  }
+  pl.kb_per_split = static_cast<int>(ceil_div(KB, splits));
+  pl.splits = static_cast<int>(ceil_div(KB, pl.kb_per_split));
+  pl.ws_pitch = pl.tiles_n * pl.bn;
+  return pl;
+}
+
+template <typename T, int BN> int launch(const Tc5Args& a, const Tc5Plan& pl, cudaStream_t st) {
+  constexpr int SMEM = Cfg<BN>::ST * (A_STAGE + BN * BK * 2) + 1024;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(gemm_tc5_kernel<T, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) {
@@ -197,8 +273,18 @@ template <typename T, int BN> int launch(const Tc5Args& a, cudaStream_t st) {
   }
   CUtensorMap ma, mw;
   if (!make_map(&ma, a.A, a.M, a.K, a.lda, BM, a.dtype) || !make_map(&mw, a.W, a.N, a.K, a.ldw, BN, a.dtype)) return B200_ENOTSUP;
-  Tc5Params p{a.bias, a.residual, a.aux, a.out, a.M, a.N, a.K, a.ldo, a.ldr, a.ldaux, a.bias_dtype, a.epilogue};
-  dim3 grid(static_cast<unsigned>(ceil_div(a.N, BN)), static_cast<unsigned>(ceil_div(a.M, BM)));
+  Tc5Params p;
+  p.bias = a.bias; p.residual = a.residual; p.aux = a.aux; p.out = a.out;
+  p.M = a.M; p.N = a.N; p.K = a.K; p.ldo = a.ldo; p.ldr = a.ldr; p.ldaux = a.ldaux; p.ws_pitch = pl.ws_pitch;
+  p.bias_dtype = a.bias_dtype; p.epilogue = a.epilogue; p.splits = pl.splits; p.kb_per_split = pl.kb_per_split;
+  p.ws = nullptr; p.ctr = nullptr;
+  if (pl.splits > 1) {
+    const int64_t need = linear_tc5_workspace_bytes(a.M, a.N, a.K);
+    if (!a.workspace || a.workspace_bytes < need || !aligned16(a.workspace)) return B200_ENOTSUP;
+    p.ws = static_cast<float*>(a.workspace);
+    p.ctr = reinterpret_cast<unsigned int*>(static_cast<uint8_t*>(a.workspace) + a.M * pl.ws_pitch * 4);
+  }
+  dim3 grid(static_cast<unsigned>(pl.tiles_n), static_cast<unsigned>(pl.tiles_m), static_cast<unsigned>(pl.splits));
   gemm_tc5_kernel<T, BN><<<grid, 192, SMEM, st>>>(ma, mw, p);
   B200_CHECK_LAUNCH("gemm_tc5_kernel");
   return B200_OK;
@@ -215,15 +301,22 @@ bool tc5_enabled() {
   return state == 1;
 }
 
+int64_t linear_tc5_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  const Tc5Plan pl = plan_tc5(M, N, K);
+  if (pl.splits <= 1) return 0;
+  return M * pl.ws_pitch * 4 + pl.tiles_n * pl.tiles_m * 4 + 256;
+}
+
 int linear_tc5(const Tc5Args& a, cudaStream_t st) {
   if (!tc5_enabled()) return B200_ENOTSUP;
   if (a.dtype != B200_BF16 && a.dtype != B200_F16) return B200_ENOTSUP;
   if (a.K % 8 || a.lda % 8 || a.ldw % 8 || !aligned16(a.A) || !aligned16(a.W)) return B200_ENOTSUP;
   if (a.M >= (1ll << 31) || a.N >= (1ll << 31) || a.K >= (1ll << 31)) return B200_ENOTSUP;
-  // narrower tiles when 128-wide ones would leave most SMs idle
-  const bool narrow = ceil_div(a.N, 128) * ceil_div(a.M, BM) < sm_count();
-  if (a.dtype == B200_BF16) return narrow ? launch<__nv_bfloat16, 64>(a, st) : launch<__nv_bfloat16, 128>(a, st);
-  return narrow ? launch<__half, 64>(a, st) : launch<__half, 128>(a, st);
+  const Tc5Plan pl = plan_tc5(a.M, a.N, a.K);
+  if (pl.tiles_m > 65535 || pl.splits > 65535) return B200_ENOTSUP;
+  if (a.dtype == B200_BF16) return pl.bn == 64 ? launch<__nv_bfloat16, 64>(a, pl, st) : launch<__nv_bfloat16, 128>(a, pl, st);
+  return pl.bn == 64 ? launch<__half, 64>(a, pl, st) : launch<__half, 128>(a, pl, st);
 }
 
 }  // namespace b200

@@ -8,11 +8,15 @@ struct Tc5Args {
   const void* A; const void* W; const void* bias; const void* residual; const void* aux; void* out;
   int64_t M, N, K, lda, ldw, ldo, ldr, ldaux;
   int dtype, bias_dtype, epilogue;
+  void* workspace;          // zero-initialised scratch for split-K (may be null when not needed)
+  int64_t workspace_bytes;
 };
 
 // out = epi(A W^T + bias + residual) on the tcgen05 path.  Returns B200_ENOTSUP when the
 // operands do not meet the TMA alignment rules (the caller then uses the mma.sync tiles).
 int linear_tc5(const Tc5Args& a, cudaStream_t stream);
 bool tc5_enabled();
+// Scratch bytes linear_tc5 needs for (M, N, K); 0 when the plan does not split K.
+int64_t linear_tc5_workspace_bytes(int64_t M, int64_t N, int64_t K);
 
 }  // namespace b200

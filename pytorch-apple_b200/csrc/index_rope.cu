@@ -113,9 +113,93 @@ __global__ void __launch_bounds__(128) rope_rotate_kernel(const __grid_constant_
   reinterpret_cast<uint4*>(dst)[pk] = pack8<T>(out);
 }
 
+struct QkvPostParams {
+  const void* x[3];     // q, k, v: [B, H, T, D] views, D contiguous
+  int64_t xs[3][3];     // element strides over (b, h, t)
+  const void* cos_t; const void* sin_t;
+  void* q_out; void* k_cache; void* v_cache;
+  const void* cache_pos;
+  int64_t B, T, cache_len;
+  int Hq, Hkv, D, pos_dtype;
+};
+
+// One launch for the three per-token steps between the QKV projection and attention:
+// RoPE on q (to a dense [B,Hq,T,D] buffer), RoPE on k written straight into the key cache
+// at row cache_pos[t], and v copied into the value cache at the same row.
+template <typename T>
+__global__ void __launch_bounds__(128) qkv_rope_cache_kernel(const __grid_constant__ QkvPostParams p) {
+  const int packs = p.D >> 3, half_packs = packs >> 1, H = p.Hq + 2 * p.Hkv;
+  const int64_t gid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (gid >= p.B * H * p.T * packs) return;
+  const int pk = static_cast<int>(gid % packs);
+  int64_t r = gid / packs;
+  const int64_t t = r % p.T; r /= p.T;
+  int h = static_cast<int>(r % H);
+  const int64_t b = r / H;
+  const int which = h < p.Hq ? 0 : (h < p.Hq + p.Hkv ? 1 : 2);
+  if (which == 1) h -= p.Hq;
+  if (which == 2) h -= p.Hq + p.Hkv;
+  const T* xr = static_cast<const T*>(p.x[which]) + b * p.xs[which][0] + h * p.xs[which][1] + t * p.xs[which][2];
+  uint4 result;
+  if (which == 2) {
+    result = *(reinterpret_cast<const uint4*>(xr) + pk);
+  } else {
+    const int64_t tab = (b * p.T + t) * p.D;
+    float xv[8], ov[8], c[8], s[8], out[8];
+    unpack8<T>(*(reinterpret_cast<const uint4*>(xr) + pk), xv);
+    unpack8<T>(*(reinterpret_cast<const uint4*>(xr) + (pk < half_packs ? pk + half_packs : pk - half_packs)), ov);
+    unpack8<T>(__ldg(reinterpret_cast<const uint4*>(static_cast<const T*>(p.cos_t) + tab) + pk), c);
+    unpack8<T>(__ldg(reinterpret_cast<const uint4*>(static_cast<const T*>(p.sin_t) + tab) + pk), s);
+    const float sign = pk < half_packs ? -1.f : 1.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) out[k] = round_as<T>(xv[k] * c[k]) + round_as<T>(sign * ov[k] * s[k]);
+    result = pack8<T>(out);
+  }
+  T* dst;
+  if (which == 0) {
+    dst = static_cast<T*>(p.q_out) + ((b * p.Hq + h) * p.T + t) * p.D;
+  } else {
+    int64_t pos = load_index(p.cache_pos, t, p.pos_dtype);
+    if (pos < 0) pos += p.cache_len;
+    if (pos < 0 || pos >= p.cache_len) return;
+    dst = static_cast<T*>(which == 1 ? p.k_cache : p.v_cache) + ((b * p.Hkv + h) * p.cache_len + pos) * p.D;
+  }
+  reinterpret_cast<uint4*>(dst)[pk] = result;
+}
+
 }  // namespace b200
 
 using namespace b200;
+
+extern "C" int b200_qkv_rope_cache(const b200_tensor* q, const b200_tensor* k, const b200_tensor* v, const void* cos_t,
+                                   const void* sin_t, void* q_out, void* k_cache, void* v_cache, const void* cache_pos,
+                                   int64_t cache_len, int pos_dtype, void* stream) {
+  B200_CHECK_ARG(q && k && v && q->data && k->data && v->data && cos_t && sin_t && q_out && k_cache && v_cache && cache_pos,
+                 "b200_qkv_rope_cache: bad arguments");
+  B200_CHECK_ARG(q->ndim == 4 && k->ndim == 4 && v->ndim == 4 && q->dtype == k->dtype && k->dtype == v->dtype,
+                 "b200_qkv_rope_cache: q, k, v must be 4-D tensors of one dtype");
+  QkvPostParams p;
+  const b200_tensor* ts[3] = {q, k, v};
+  bool ok = aligned16(cos_t) && aligned16(sin_t) && aligned16(q_out) && aligned16(k_cache) && aligned16(v_cache);
+  for (int i = 0; i < 3; ++i) {
+    p.x[i] = ts[i]->data;
+    ok = ok && aligned16(ts[i]->data) && ts[i]->stride[3] == 1;
+    for (int d = 0; d < 3; ++d) { p.xs[i][d] = ts[i]->stride[d]; ok = ok && ts[i]->stride[d] % 8 == 0; }
+  }
+  B200_CHECK_ARG(k->shape[1] == v->shape[1] && q->shape[0] == k->shape[0] && q->shape[2] == k->shape[2] && q->shape[3] == k->shape[3] &&
+                 v->shape[0] == k->shape[0] && v->shape[2] == k->shape[2] && v->shape[3] == k->shape[3] && q->shape[3] % 16 == 0,
+                 "b200_qkv_rope_cache: shape mismatch");
+  if (!ok) B200_FAIL(B200_EALIGN, "b200_qkv_rope_cache: operands must be 16-byte aligned with strides multiple of 8");
+  p.cos_t = cos_t; p.sin_t = sin_t; p.q_out = q_out; p.k_cache = k_cache; p.v_cache = v_cache; p.cache_pos = cache_pos;
+  p.B = q->shape[0]; p.T = q->shape[2]; p.cache_len = cache_len;
+  p.Hq = static_cast<int>(q->shape[1]); p.Hkv = static_cast<int>(k->shape[1]); p.D = static_cast<int>(q->shape[3]); p.pos_dtype = pos_dtype;
+  const int64_t total = p.B * (p.Hq + 2 * p.Hkv) * p.T * (p.D >> 3);
+  if (total == 0) return B200_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  B200_DISPATCH_HALF(q->dtype, T, { qkv_rope_cache_kernel<T><<<static_cast<unsigned>(ceil_div(total, 128)), 128, 0, st>>>(p); });
+  B200_CHECK_LAUNCH("qkv_rope_cache_kernel");
+  return B200_OK;
+}
 
 extern "C" int b200_embedding(const void* table, const void* ids, void* out, int64_t n_ids, int64_t vocab,
                               int64_t row_bytes, int ids_dtype, void* stream) {

@@ -468,6 +468,82 @@ def apply_patterns(nodes: list[OpNode], graph: IRGraph, families) -> list[OpNode
     return nodes
 
 
+def group_linears(nodes: list[OpNode], graph: IRGraph) -> list[OpNode]:
+    """Linears that read the same activation (q/k/v projections) become one GEMM over the
+    row-concatenated weights; the member outputs turn into column slices of its result.
+    The fused node takes the place of the first member: its operands (the shared input and
+    graph-level weights) are all defined there."""
+    weight_names = {w.name for w in graph.weights} | set(graph.weight_name_mapping)
+    groups: dict[tuple, list[OpNode]] = {}
+    for n in nodes:
+        if n.op_type != "aten.linear.default" or len(n.inputs) not in (2, 3) or len(n.outputs) != 1:
+            continue
+        if any(t.name not in weight_names for t in n.inputs[1:]):
+            continue
+        x, w = n.inputs[0], n.inputs[1]
+        key = (x.name, len(n.inputs), w.shape[1], w.dtype, n.outputs[0].dtype, tuple(n.outputs[0].shape[:-1]))
+        groups.setdefault(key, []).append(n)
+    replace: dict[int, OpNode] = {}
+    drop: set[int] = set()
+    for members in groups.values():
+        if len(members) < 2:
+            continue
+        first = members[0]
+        inputs = [first.inputs[0]]
+        for m in members:
+            inputs += list(m.inputs[1:])
+        macro = OpNode(name=f"linear_group__{first.name}", op_type="b200.linear_group", inputs=inputs,
+                       outputs=[m.outputs[0] for m in members],
+                       attrs={"has_bias": len(first.inputs) == 3, "n_parts": len(members), "_orig": members})
+        replace[id(first)] = macro
+        drop.update(id(m) for m in members[1:])
+    if not replace:
+        return nodes
+    return [replace.get(id(n), n) for n in nodes if id(n) not in drop]
+
+
+def fuse_qkv_post(nodes: list[OpNode], graph: IRGraph) -> list[OpNode]:
+    """rope(q), rope(k) -> index_copy into the key cache, v -> index_copy into the value
+    cache: one launch.  Runs after the rope pattern, on ``b200.rope_rotate`` nodes."""
+    gi = GraphIndex.build(nodes, graph)
+    replace: dict[int, OpNode] = {}
+    drop: set[int] = set()
+    for ic_k in nodes:
+        if ic_k.op_type != "aten.index_copy.default" or id(ic_k) in drop or len(ic_k.inputs) != 3:
+            continue
+        cache_k, index, src = ic_k.inputs
+        if len(cache_k.shape) != 4 or _norm_dim(ic_k.attrs.get("dim", 0), 4) != 2:
+            continue
+        rk = gi.prod(src.name, "b200.rope_rotate")
+        if rk is None or gi.sole_consumer(src.name) is not ic_k or id(rk) in drop:
+            continue
+        k, cos_u, sin_u = rk.inputs
+        rq = next((n for n in nodes if n.op_type == "b200.rope_rotate" and n is not rk and id(n) not in drop
+                   and n.inputs[1].name == cos_u.name and n.inputs[2].name == sin_u.name
+                   and n.inputs[0].shape[0] == k.shape[0] and n.inputs[0].shape[2:] == k.shape[2:]), None)
+        if rq is None:
+            continue
+        ic_v = None
+        for n in nodes[gi.position[id(ic_k)] + 1: gi.position[id(ic_k)] + 4]:
+            if (n.op_type == "aten.index_copy.default" and len(n.inputs) == 3 and n.inputs[1].name == index.name
+                    and list(n.inputs[0].shape) == list(cache_k.shape) and list(n.inputs[2].shape) == list(k.shape)
+                    and _norm_dim(n.attrs.get("dim", 0), 4) == 2 and gi.prod(n.inputs[2].name, "b200.rope_rotate") is None):
+                ic_v = n
+                break
+        if ic_v is None or k.shape[2] != index.shape[0]:
+            continue
+        matched = sorted([rq, rk, ic_k, ic_v], key=lambda n: gi.position[id(n)])
+        macro = _macro("b200.qkv_post", matched[-1], [rq.inputs[0], k, ic_v.inputs[2], cos_u, sin_u, cache_k, ic_v.inputs[0], index],
+                       [rq.outputs[0], ic_k.outputs[0], ic_v.outputs[0]], {"dim": 2}, matched)
+        if not _acceptable(gi, matched, macro):
+            continue
+        replace[id(matched[-1])] = macro
+        drop.update(id(n) for n in matched[:-1])
+    if not replace:
+        return nodes
+    return [replace.get(id(n), n) for n in nodes if id(n) not in drop]
+
+
 DEFAULT_FAMILIES = [
     ({"aten.pow.Tensor_Scalar"}, match_rmsnorm),
     (ADD_OPS, match_rope_rotate),

@@ -44,6 +44,8 @@ from cuda_compiler.patterns import (
     PASSTHROUGH_OPS,
     GraphIndex,
     apply_patterns,
+    fuse_qkv_post,
+    group_linears,
 )
 from npu_compiler.ir_reader import IRGraph, OpNode, TensorSpec
 
@@ -182,6 +184,8 @@ class _Lowering:
         nodes = [n for n in self.graph.nodes if n.op_type not in NOOP_OPS]
         if self.fuse:
             nodes = apply_patterns(nodes, self.graph, DEFAULT_FAMILIES)
+            nodes = group_linears(nodes, self.graph)
+            nodes = fuse_qkv_post(nodes, self.graph)
         self.gi = GraphIndex.build(nodes, self.graph)
         self._chain_done: set[int] = set()
         for node in nodes:
@@ -614,6 +618,40 @@ class _Lowering:
                                     params={"op": "rope_rotate", "x": xv, "cos": cv, "sin": sv, "y": o}),
                   [x.name, cos_u.name, sin_u.name, out.name])
 
+    def lower_qkv_post(self, node: OpNode) -> None:
+        q, k, v, cos_u, sin_u, cache_k, cache_v, index = node.inputs
+        q_out, kc_out, vc_out = node.outputs
+        dt = self.sd(q_out.dtype)
+        views = [self.view(t.name) for t in (q, k, v)]
+        cv, sv = self.view(cos_u.name), self.view(sin_u.name)
+        B, Hq, T, D = views[0].shape
+
+        def table_ok(t: TensorView) -> bool:
+            return t.dtype == dt and t.strides[3] == 1 and (T == 1 or t.strides[2] == D) and (B == 1 or t.strides[0] == T * D) and t.offset % 8 == 0
+
+        def donatable(c) -> bool:
+            cvw = self.view(c.name)
+            return (self.donate and c.name in self.external and c.name not in self.weight_names and cvw.is_contiguous()
+                    and cvw.dtype == dt and len(self.gi.consumers.get(c.name, [])) == 1)
+
+        ok = dt in ("float16", "bfloat16") and D % 16 == 0 and table_ok(cv) and table_ok(sv) and donatable(cache_k) and donatable(cache_v)
+        ok = ok and all(t.dtype == dt and t.strides[3] == 1 and t.offset % 8 == 0 and all(s % 8 == 0 for s in t.strides[:3]) for t in views)
+        if not ok:
+            return self.lower_original(node)
+        idx = self.contiguous(index.name)
+        qo = self.alloc(q_out.name, q_out.shape, dt)
+        for c, o in ((cache_k, kc_out), (cache_v, vc_out)):
+            base = self.view(c.name)
+            self.out.views[o.name] = TensorView(base.buffer, base.offset, tuple(o.shape), V.contiguous_strides(o.shape), base.dtype)
+            self.out.donated[o.name] = c.name
+        names = [t.name for t in (q, k, v, cos_u, sin_u, cache_k, cache_v)] + [idx]
+        self.emit(SpecialKernelStep("qkv_rope_cache_kernel", "rope(q); key cache[pos] = rope(k); value cache[pos] = v  (in place)",
+                                    names, q_out.name, output_buffer_names=[q_out.name, kc_out.name, vc_out.name],
+                                    params={"op": "qkv_post", "q": views[0], "k": views[1], "v": views[2], "cos": cv, "sin": sv, "q_out": qo,
+                                            "k_cache": self.view(cache_k.name), "v_cache": self.view(cache_v.name), "index": self.view(idx),
+                                            "cache_len": cache_k.shape[2], "in_place": True}),
+                  names + [q_out.name, kc_out.name, vc_out.name])
+
     # -- dense contractions -----------------------------------------------------------------
     def lower_blas(self, node: OpNode) -> None:
         op = node.op_type
@@ -646,6 +684,36 @@ class _Lowering:
         aux = extra.pop(0) if a["silu_mul"] else None
         self._linear(node, node.inputs[:n_base], node.outputs[0], has_bias=a["has_bias"], residual=residual, aux=aux,
                      relu=a["relu"])
+
+    def lower_linear_group(self, node: OpNode) -> None:
+        """q/k/v-style projections of one activation as a single GEMM over concatenated weights."""
+        a = node.attrs
+        per = 2 if a["has_bias"] else 1
+        x = node.inputs[0]
+        ws = [node.inputs[1 + per * i] for i in range(a["n_parts"])]
+        bs = [node.inputs[2 + per * i] for i in range(a["n_parts"])] if a["has_bias"] else []
+        outs = node.outputs
+        dt = self.sd(outs[0].dtype)
+        if dt not in ("float16", "bfloat16") or self.view(x.name).dtype != dt:
+            return self.lower_original(node)
+        rows = [int(w.shape[0]) for w in ws]
+        K, n_total = int(ws[0].shape[1]), sum(rows)
+        wp, bp = f"{node.name}__w", f"{node.name}__b"
+        self.out.weight_preps.append(WeightPrep("concat_rows", [w.name for w in ws], [wp], {"rows": rows, "cols": K, "dtype": dt}))
+        self.out.views[wp] = TensorView(wp, 0, (n_total, K), (K, 1), dt)
+        if bs:
+            self.out.weight_preps.append(WeightPrep("concat_rows", [b.name for b in bs], [bp], {"rows": rows, "cols": 1, "dtype": dt}))
+            self.out.views[bp] = TensorView(bp, 0, (n_total,), (1,), dt)
+        merged = TensorSpec(f"{node.name}__out", list(outs[0].shape[:-1]) + [n_total], outs[0].dtype)
+        fake_ins = [x, TensorSpec(wp, [n_total, K], ws[0].dtype)] + ([TensorSpec(bp, [n_total], bs[0].dtype)] if bs else [])
+        self._linear(node, fake_ins, merged, has_bias=bool(bs))
+        full = self.view(merged.name)
+        nd = len(full.shape)
+        at = 0
+        for o, n in zip(outs, rows):
+            self.out.views[o.name] = V.slice_(full, nd - 1, at, at + n, 1)
+            self.emit(AliasStep(merged.name, o.name, list(full.shape), list(o.shape)), [merged.name, o.name])
+            at += n
 
     def _linear(self, node, ins, out: TensorSpec, has_bias: bool, residual=None, aux=None, relu=False) -> None:
         x, w = ins[0].name, ins[1].name

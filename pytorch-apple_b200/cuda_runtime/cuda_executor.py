@@ -169,6 +169,8 @@ class CUDAExecutor:
         for prep in self._program.weight_preps:
             if prep.kind == "conv_fold":
                 self._prep_conv(prep, stream)
+            elif prep.kind == "concat_rows":
+                self._prep_concat(prep)
             else:
                 raise RuntimeError(f"unknown weight preparation {prep.kind}")
 
@@ -201,6 +203,22 @@ class CUDAExecutor:
         a = native.make_tensor(dst.data_ptr(), str(dst.dtype).replace("torch.", ""), (n,), (1,))
         b = native.make_tensor(src.data_ptr(), str(src.dtype).replace("torch.", ""), (n,), (1,))
         native.check(self._lib.b200_strided_copy(C.byref(a), C.byref(b), self._stream_ptr()), "weight cast")
+
+    def _prep_concat(self, prep) -> None:
+        """Row-wise concatenation of weights (merged q/k/v projection), in the compute dtype."""
+        p = prep.params
+        dt = getattr(torch, p["dtype"])
+        cols = p["cols"]
+        out = torch.empty(sum(p["rows"]) * cols, dtype=dt, device=self._device)
+        at = 0
+        for name, rows in zip(prep.inputs, p["rows"]):
+            src = self._raw_weight(name)
+            src = src if src.is_contiguous() else src.contiguous()
+            if src.numel() != rows * cols:
+                raise RuntimeError(f"weight '{name}' has {src.numel()} elements, expected {rows * cols}")
+            self._convert(src.reshape(-1), out[at:at + rows * cols])
+            at += rows * cols
+        self._prepared[prep.outputs[0]] = out
 
     def _prep_conv(self, prep, stream: int) -> None:
         p = prep.params
@@ -390,6 +408,13 @@ class CUDAExecutor:
         x = self._tensor(plan, p["x"])
         plan.launches.append((self._lib.b200_rope_rotate, (C.byref(x), self._ptr(p["cos"]), self._ptr(p["sin"]), self._ptr(p["y"]),
                                                            None, None, 0, 0)))
+
+    def _bind_qkv_post(self, plan, step, p):
+        q, k, v = (self._tensor(plan, p[n]) for n in ("q", "k", "v"))
+        iptr, idt = self._index_ptr(p["index"])
+        plan.launches.append((self._lib.b200_qkv_rope_cache, (C.byref(q), C.byref(k), C.byref(v), self._ptr(p["cos"]), self._ptr(p["sin"]),
+                                                              self._ptr(p["q_out"]), self._ptr(p["k_cache"]), self._ptr(p["v_cache"]), iptr,
+                                                              p["cache_len"], idt)))
 
     def _bind_max_pool2d(self, plan, step, p):
         x, y = self._tensor(plan, p["x"]), self._tensor(plan, p["y"])

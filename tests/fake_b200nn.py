@@ -214,6 +214,27 @@ class FakeLibrary:
         _raw(y, dt, [B, H, T, D], [H * T * D, T * D, D, 1]).copy_(r)
         return 0
 
+    def b200_qkv_rope_cache(self, q, k, v, cos_t, sin_t, q_out, k_cache, v_cache, cache_pos, cache_len, pos_dtype, stream):
+        self.calls.append("qkv_rope_cache")
+        Q, K, Vv = _t(q), _t(k), _t(v)
+        dt = Q.dtype
+        B, Hq, T, D = Q.shape
+        Hkv = K.shape[1]
+        c = _raw(cos_t, dt, [B, 1, T, D], [T * D, T * D, D, 1]).float()
+        s = _raw(sin_t, dt, [B, 1, T, D], [T * D, T * D, D, 1]).float()
+
+        def rope(x):
+            xf = x.float()
+            rot = torch.cat([-xf[..., D // 2:], xf[..., :D // 2]], -1)
+            return ((xf * c).to(dt).float() + (rot * s).to(dt).float()).to(dt)
+
+        _raw(q_out, dt, [B, Hq, T, D], [Hq * T * D, T * D, D, 1]).copy_(rope(Q))
+        pos = _flat(cache_pos, pos_dtype, T).long()
+        cs = [Hkv * cache_len * D, cache_len * D, D, 1]
+        _raw(k_cache, dt, [B, Hkv, cache_len, D], cs)[:, :, pos] = rope(K)
+        _raw(v_cache, dt, [B, Hkv, cache_len, D], cs)[:, :, pos] = Vv
+        return 0
+
     # -- CNN ops --------------------------------------------------------------------
     def b200_max_pool2d(self, x, y, kh, kw, sh, sw, ph, pw, stream):
         self.calls.append("max_pool2d")

@@ -179,9 +179,14 @@ def test_qwen_decode_layer_plan():
     assert prog.compute_dtype == "bfloat16"
     kinds = [getattr(s, "kernel_name", None) or s.blas_type for s in prog.steps if not isinstance(s, AliasStep)]
     assert kinds.count("attention") == L and kinds.count("rmsnorm_kernel") == 2 * L + 1
-    assert kinds.count("gemm") == 7 * L + 1 and kinds.count("index_copy_kernel") == 2 * L
+    assert kinds.count("gemm") == 5 * L + 1                    # q, k, v share one GEMM
+    assert kinds.count("qkv_rope_cache_kernel") == L           # rope(q), rope(k) + key write, value write: one launch
+    assert kinds.count("index_copy_kernel") == 0 and kinds.count("rope_rotate_kernel") == 0
     assert len(prog.donated_inputs) == 2 * L
-    assert all(s.params["in_place"] for s in prog.steps if getattr(s, "kernel_name", "") == "index_copy_kernel")
+    per_layer = (len(kinds) - 4) / L                           # minus embedding, rope table, final norm, lm_head
+    assert per_layer == 9
     # without donation the cache is copied, as in the reference
     prog2 = compile_subgraph(ir, donate_inputs=False)
     assert not prog2.donated_inputs
+    kinds2 = [getattr(s, "kernel_name", None) or s.blas_type for s in prog2.steps if not isinstance(s, AliasStep)]
+    assert kinds2.count("index_copy_kernel") == 2 * L and kinds2.count("rope_rotate_kernel") == 2 * L

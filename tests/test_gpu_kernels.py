@@ -212,7 +212,8 @@ def test_rmsnorm(lib, rows, cols):
         ok(lib, lib.b200_rmsnorm(X.data_ptr(), W.data_ptr(), Y.data_ptr(), rows, cols, cols, cols, 1e-6, DT[dtype], 1, stream()))
         got, r = Y.cpu(), ref
         ulp = (got.view(torch.int16).int() - r.view(torch.int16).int()).abs()
-        assert ulp.max() <= 1 and (ulp != 0).float().mean() < 0.02   # fp32 reduction order only
+        # fp32 reduction order only: two roundings, so rarely 2 units in the last place
+        assert ulp.max() <= 2 and (ulp != 0).float().mean() < 0.02 and (ulp > 1).float().mean() < 1e-4
 
 
 @pytest.mark.parametrize("T", [1, 128, 1000, 2048])
@@ -305,6 +306,42 @@ def test_rope_table_and_rotate(lib, T):
     cos_d, sin_d = cos.cuda(), sin.cuda()
     ok(lib, lib.b200_rope_rotate(C.byref(xs), cos_d.data_ptr(), sin_d.data_ptr(), Y.data_ptr(), None, None, 0, 0, stream()))
     assert torch.equal(Y.cpu(), ref)
+
+
+@pytest.mark.parametrize("B,T", [(1, 1), (8, 1), (2, 5)])
+def test_qkv_rope_cache_fused(lib, B, T):
+    """rope(q), rope(k) -> key cache row, v -> value cache row in one launch, from column
+    slices of one merged projection buffer (the layout the compiler produces)."""
+    dtype, Hq, Hkv, D, S = torch.bfloat16, 12, 2, 128, 64
+    N = (Hq + 2 * Hkv) * D
+    qkv = gen((B, T, N), dtype)
+    pos = torch.arange(T) + 17
+    inv = 1.0 / (1e6 ** (torch.arange(0, D, 2).float() / D))
+    ang = torch.cat([pos.float()[:, None] * inv[None]] * 2, -1)
+    cos = ang.cos().to(dtype)[None].expand(B, T, D).contiguous()
+    sin = ang.sin().to(dtype)[None].expand(B, T, D).contiguous()
+    kc, vc = gen((B, Hkv, S, D), dtype, 1), gen((B, Hkv, S, D), dtype, 2)
+
+    def heads(lo, n):  # [B,T,n*D] column slice -> [B,n,T,D] view
+        return qkv[..., lo:lo + n * D].view(B, T, n, D).transpose(1, 2)
+
+    def rope(x):
+        xf = x.float()
+        rot = torch.cat([-xf[..., D // 2:], xf[..., : D // 2]], -1)
+        return ((xf * cos[:, None].float()).to(dtype).float() + (rot * sin[:, None].float()).to(dtype).float()).to(dtype)
+
+    q, k, v = heads(0, Hq), heads(Hq * D, Hkv), heads((Hq + Hkv) * D, Hkv)
+    ref_q = rope(q)
+    ref_k, ref_v = kc.clone(), vc.clone()
+    ref_k[:, :, pos] = rope(k)
+    ref_v[:, :, pos] = v
+    QKV, KC, VC, CO, SI, P = qkv.cuda(), kc.cuda(), vc.cuda(), cos.cuda(), sin.cuda(), pos.cuda()
+    dv = lambda lo, n: QKV[..., lo:lo + n * D].view(B, T, n, D).transpose(1, 2)
+    tq, tk, tv = bt(dv(0, Hq)), bt(dv(Hq * D, Hkv)), bt(dv((Hq + Hkv) * D, Hkv))
+    qo = torch.empty(B, Hq, T, D, dtype=dtype, device="cuda")
+    ok(lib, lib.b200_qkv_rope_cache(C.byref(tq), C.byref(tk), C.byref(tv), CO.data_ptr(), SI.data_ptr(), qo.data_ptr(), KC.data_ptr(),
+                                    VC.data_ptr(), P.data_ptr(), S, 4, stream()))
+    assert torch.equal(qo.cpu(), ref_q) and torch.equal(KC.cpu(), ref_k) and torch.equal(VC.cpu(), ref_v)
 
 
 def test_embedding_is_bit_exact(lib):
