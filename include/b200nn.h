@@ -222,6 +222,11 @@ int b200_conv_weight_prep(const void* w, const void* conv_bias, const void* gamm
 /* epilogue flags */
 #define B200_EPI_RELU 1
 #define B200_EPI_SILU_MUL 2 /* out = silu(acc) * aux (aux shaped like out) */
+/* Gated MLP in one GEMM: W holds the gate and up projections interleaved in blocks of 64
+ * rows ([128j, 128j+64) gate rows 64j.., [128j+64, 128j+128) up rows 64j..); N counts
+ * the merged rows (a multiple of 128) and out has N/2 columns:
+ * out[:, 64j+c] = silu(acc[:, 128j+c]) * acc[:, 128j+64+c]. */
+#define B200_EPI_GLU 4
 
 /* CUBLASStep("gemm") (subgraph_analyzer.py:168-224, dispatch cuda_executor.py:182-208,
  * which calls cupy.matmul and a separate bias-add kernel):

@@ -372,6 +372,19 @@ __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant_
   if (!finish) return;
   __syncthreads();
 
+  if (p.epilogue & B200_EPI_GLU) {
+    // rows 0..63 of this block are gate features, rows 64..127 the matching up features
+    if (threadIdx.x >= 64) return;
+    const int64_t ng = n_blk + threadIdx.x, no = static_cast<int64_t>(blockIdx.x) * 64 + threadIdx.x;
+    const float bg = p.bias ? load_as_f32(p.bias, ng, p.bias_dtype) : 0.f;
+    const float bu = p.bias ? load_as_f32(p.bias, ng + 64, p.bias_dtype) : 0.f;
+    T* __restrict__ og = static_cast<T*>(p.out);
+    for (int64_t m = 0; m < p.M; ++m) {
+      const float s = round_as<T>(stage[threadIdx.x][m] + bg);
+      og[m * p.ldo + no] = from_f32<T>(round_as<T>(s / (1.f + expf(-s))) * round_as<T>(stage[threadIdx.x + 64][m] + bu));
+    }
+    return;
+  }
   // epilogue: thread r owns output feature n_blk + r, walks the batch rows
   const int64_t n = n_blk + threadIdx.x;
   if (n >= p.N) return;
@@ -489,6 +502,8 @@ extern "C" int b200_linear(const void* A, const void* W, const void* bias, const
                            int64_t workspace_bytes, void* stream) {
   B200_CHECK_ARG(A && W && out && M >= 0 && N > 0 && K > 0, "b200_linear: bad arguments");
   B200_CHECK_ARG(!(epilogue & B200_EPI_SILU_MUL) || aux, "b200_linear: silu_mul epilogue needs aux");
+  B200_CHECK_ARG(!(epilogue & B200_EPI_GLU) || (N % 128 == 0 && !residual && !(epilogue & ~B200_EPI_GLU)),
+                 "b200_linear: the gated epilogue needs N %% 128 == 0 and excludes residual / other epilogues");
   if (M == 0) return B200_OK;
   if (!(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0 && aligned16(A) && aligned16(W)))
     B200_FAIL(B200_EALIGN, "b200_linear: K, lda, ldw must be multiples of 8 and A, W 16-byte aligned");
@@ -524,6 +539,7 @@ extern "C" int b200_linear(const void* A, const void* W, const void* bias, const
     B200_CHECK_LAUNCH("gemm_skinny_kernel");
     return B200_OK;
   }
+  if (epilogue & B200_EPI_GLU) B200_FAIL(B200_ENOTSUP, "b200_linear: the gated epilogue needs the tcgen05 path (operands aligned, B200NN_DISABLE_TC5 unset)");
   GemmParams p;
   p.A = A; p.W = W; p.bias = bias; p.residual = residual; p.aux = aux; p.out = out;
   p.M = M; p.N = N; p.K = K; p.lda = lda; p.ldw = ldw; p.ldo = ldo; p.ldr = ldr; p.ldaux = ldaux;

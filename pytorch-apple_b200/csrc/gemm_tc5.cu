@@ -77,6 +77,32 @@ __device__ __forceinline__ void finish_row(const Tc5Params& p, float (&v)[32], i
   }
 }
 
+// gated-MLP epilogue: 32 gate accumulators and the 32 matching up accumulators of row m
+template <typename T>
+__device__ __forceinline__ void finish_glu(const Tc5Params& p, float (&vg)[32], float (&vu)[32], int64_t m, int64_t n_merged, int64_t n_out) {
+  float v[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    float g = vg[i], u = vu[i];
+    if (p.bias) { g += load_as_f32(p.bias, n_merged + i, p.bias_dtype); u += load_as_f32(p.bias, n_merged + 64 + i, p.bias_dtype); }
+    const float s = round_as<T>(g);
+    v[i] = round_as<T>(s / (1.f + expf(-s))) * round_as<T>(u);
+  }
+  T* o = static_cast<T*>(p.out) + m * p.ldo + n_out;
+  if ((reinterpret_cast<uintptr_t>(o) & 15u) == 0) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float f[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[i] = v[8 * j + i];
+      reinterpret_cast<uint4*>(o)[j] = pack8<T>(f);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) o[i] = from_f32<T>(v[i]);
+  }
+}
+
 template <typename T, int BN>
 __global__ void __launch_bounds__(192, 2) gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a,
                                                           const __grid_constant__ CUtensorMap map_w, const Tc5Params p) {
@@ -153,7 +179,19 @@ __global__ void __launch_bounds__(192, 2) gemm_tc5_kernel(const __grid_constant_
     ok = __all_sync(0xffffffffu, ok);
     const int64_t m = m0 + q * 32 + lane;
     const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
-    if (ok) {
+    const bool glu = (p.epilogue & B200_EPI_GLU) != 0;  // host guarantees BN == 128 and N % 128 == 0
+    if (ok && glu && p.splits == 1) {
+      tc5::tc_fence_after();
+#pragma unroll 1
+      for (int c = 0; c < 2; ++c) {
+        float vg[32], vu[32];
+        __syncwarp();
+        tc5::tmem_ld_32x32(t_row + c * 32, vg);
+        tc5::tmem_ld_32x32(t_row + 64 + c * 32, vu);
+        if (m < p.M) finish_glu<T>(p, vg, vu, m, n0 + c * 32, n0 / 2 + c * 32);
+      }
+      tc5::tc_fence_before();
+    } else if (ok) {
       tc5::tc_fence_after();
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
@@ -182,19 +220,31 @@ __global__ void __launch_bounds__(192, 2) gemm_tc5_kernel(const __grid_constant_
         if (is_last) p.ctr[tile] = 0u;
       }
       epilogue_bar();
-      if (*reinterpret_cast<volatile int*>(&is_last) && m < p.M) {
+      auto take = [&](int64_t n, float (&v)[32]) {  // read 32 summed partials and leave zeros behind
+        float4* w = reinterpret_cast<float4*>(p.ws + m * p.ws_pitch + n);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float4 t = __ldcg(w + j);
+          __stcg(w + j, make_float4(0.f, 0.f, 0.f, 0.f));
+          v[4 * j] = t.x; v[4 * j + 1] = t.y; v[4 * j + 2] = t.z; v[4 * j + 3] = t.w;
+        }
+      };
+      if (*reinterpret_cast<volatile int*>(&is_last) && m < p.M && glu) {
+        __threadfence();
+#pragma unroll 1
+        for (int c = 0; c < 2; ++c) {
+          float vg[32], vu[32];
+          take(n0 + c * 32, vg);
+          take(n0 + 64 + c * 32, vu);
+          finish_glu<T>(p, vg, vu, m, n0 + c * 32, n0 / 2 + c * 32);
+        }
+      } else if (*reinterpret_cast<volatile int*>(&is_last) && m < p.M) {
         __threadfence();
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
           const int64_t n = n0 + c * 32;
           float v[32];
-          float4* w = reinterpret_cast<float4*>(p.ws + m * p.ws_pitch + n);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const float4 t = __ldcg(w + j);
-            __stcg(w + j, make_float4(0.f, 0.f, 0.f, 0.f));
-            v[4 * j] = t.x; v[4 * j + 1] = t.y; v[4 * j + 2] = t.z; v[4 * j + 3] = t.w;
-          }
+          take(n, v);
           if (n < p.N) finish_row<T>(p, v, m, n);
         }
       }
@@ -238,12 +288,12 @@ bool make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t K, int64
 
 struct Tc5Plan { int bn, splits, kb_per_split; int64_t tiles_n, tiles_m, ws_pitch; };
 
-Tc5Plan plan_tc5(int64_t M, int64_t N, int64_t K) {
+Tc5Plan plan_tc5(int64_t M, int64_t N, int64_t K, bool glu = false) {
   Tc5Plan pl;
   const int64_t tm = ceil_div(M, BM);
   // 64-wide tiles whenever 128-wide ones would not give every SM a tile (148 SMs; fixed so that
   // the workspace size does not depend on the device the plan is made on)
-  pl.bn = ceil_div(N, 128) * tm < 148 ? 64 : 128;
+  pl.bn = (!glu && ceil_div(N, 128) * tm < 148) ? 64 : 128;   // the gated epilogue pairs columns c and c+64 of a 128-wide tile
   pl.tiles_n = ceil_div(N, pl.bn);
   pl.tiles_m = tm;
   const int64_t tiles = pl.tiles_n * tm, KB = ceil_div(K, BK);
@@ -279,7 +329,7 @@ template <typename T, int BN> int launch(const Tc5Args& a, const Tc5Plan& pl, cu
   p.bias_dtype = a.bias_dtype; p.epilogue = a.epilogue; p.splits = pl.splits; p.kb_per_split = pl.kb_per_split;
   p.ws = nullptr; p.ctr = nullptr;
   if (pl.splits > 1) {
-    const int64_t need = linear_tc5_workspace_bytes(a.M, a.N, a.K);
+    const int64_t need = a.M * pl.ws_pitch * 4 + pl.tiles_n * pl.tiles_m * 4 + 256;
     if (!a.workspace || a.workspace_bytes < need || !aligned16(a.workspace)) return B200_ENOTSUP;
     p.ws = static_cast<float*>(a.workspace);
     p.ctr = reinterpret_cast<unsigned int*>(static_cast<uint8_t*>(a.workspace) + a.M * pl.ws_pitch * 4);
@@ -303,9 +353,15 @@ bool tc5_enabled() {
 
 int64_t linear_tc5_workspace_bytes(int64_t M, int64_t N, int64_t K) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
-  const Tc5Plan pl = plan_tc5(M, N, K);
-  if (pl.splits <= 1) return 0;
-  return M * pl.ws_pitch * 4 + pl.tiles_n * pl.tiles_m * 4 + 256;
+  int64_t need = 0;
+  for (int glu = 0; glu < 2; ++glu) {  // the caller does not say which epilogue it will ask for
+    if (glu && N % 128) continue;
+    const Tc5Plan pl = plan_tc5(M, N, K, glu != 0);
+    if (pl.splits <= 1) continue;
+    const int64_t b = M * pl.ws_pitch * 4 + pl.tiles_n * pl.tiles_m * 4 + 256;
+    need = b > need ? b : need;
+  }
+  return need;
 }
 
 int linear_tc5(const Tc5Args& a, cudaStream_t st) {
@@ -313,7 +369,9 @@ int linear_tc5(const Tc5Args& a, cudaStream_t st) {
   if (a.dtype != B200_BF16 && a.dtype != B200_F16) return B200_ENOTSUP;
   if (a.K % 8 || a.lda % 8 || a.ldw % 8 || !aligned16(a.A) || !aligned16(a.W)) return B200_ENOTSUP;
   if (a.M >= (1ll << 31) || a.N >= (1ll << 31) || a.K >= (1ll << 31)) return B200_ENOTSUP;
-  const Tc5Plan pl = plan_tc5(a.M, a.N, a.K);
+  const bool glu = (a.epilogue & B200_EPI_GLU) != 0;
+  if (glu && (a.N % 128 || (a.epilogue & ~B200_EPI_GLU) || a.residual)) return B200_ENOTSUP;
+  const Tc5Plan pl = plan_tc5(a.M, a.N, a.K, glu);
   if (pl.tiles_m > 65535 || pl.splits > 65535) return B200_ENOTSUP;
   if (a.dtype == B200_BF16) return pl.bn == 64 ? launch<__nv_bfloat16, 64>(a, pl, st) : launch<__nv_bfloat16, 128>(a, pl, st);
   return pl.bn == 64 ? launch<__half, 64>(a, pl, st) : launch<__half, 128>(a, pl, st);

@@ -368,7 +368,7 @@ def match_linear_epilogue(gi: GraphIndex, lin: OpNode):
     out = lin.outputs[0]
     matched = [lin]
     inputs = list(lin.inputs)
-    attrs = {"has_bias": len(lin.inputs) > 2, "residual": False, "relu": False, "silu_mul": False}
+    attrs = {"has_bias": len(lin.inputs) > 2, "residual": False, "relu": False, "silu_mul": False, "glu": False}
     nxt = gi.sole_consumer(out.name)
     if nxt is not None and nxt.op_type in ADD_OPS and len(nxt.inputs) == 2 and nxt.attrs.get("alpha", 1) in (1, 1.0):
         res = _other_input(nxt, out.name)
@@ -387,11 +387,21 @@ def match_linear_epilogue(gi: GraphIndex, lin: OpNode):
         up = _other_input(mul, nxt.outputs[0].name) if mul is not None else None
         if up is not None and list(up.shape) == list(out.shape) and up.dtype == out.dtype:
             matched += [nxt, mul]
-            inputs.append(up)
-            attrs["silu_mul"] = True
             out = mul.outputs[0]
+            # gate and up read the same activation: one GEMM over interleaved weights
+            upl = gi.prod(up.name, "aten.linear.default")
+            if (upl is not None and len(upl.inputs) == 2 and len(lin.inputs) == 2 and upl.inputs[0].name == lin.inputs[0].name
+                    and gi.sole_consumer(up.name) is mul and list(upl.inputs[1].shape) == list(lin.inputs[1].shape)
+                    and lin.inputs[1].shape[0] % 64 == 0 and gi.prod(lin.inputs[1].name) is None and gi.prod(upl.inputs[1].name) is None):
+                matched.insert(0, upl)
+                inputs.append(upl.inputs[1])
+                attrs["glu"] = True
+            else:
+                inputs.append(up)
+                attrs["silu_mul"] = True
     if len(matched) == 1:
         return None
+    matched.sort(key=lambda n: gi.position[id(n)])
     return matched, _macro("b200.linear", matched[-1], inputs, [out], attrs, matched)
 
 

@@ -678,6 +678,8 @@ class _Lowering:
 
     def lower_linear(self, node: OpNode) -> None:  # b200.linear macro
         a = node.attrs
+        if a.get("glu"):
+            return self._linear_glu(node)
         n_base = 3 if a["has_bias"] else 2
         extra = list(node.inputs[n_base:])
         residual = extra.pop(0) if a["residual"] else None
@@ -715,7 +717,20 @@ class _Lowering:
             self.emit(AliasStep(merged.name, o.name, list(full.shape), list(o.shape)), [merged.name, o.name])
             at += n
 
-    def _linear(self, node, ins, out: TensorSpec, has_bias: bool, residual=None, aux=None, relu=False) -> None:
+    def _linear_glu(self, node: OpNode) -> None:
+        """silu(x Wg^T) * (x Wu^T) as one GEMM over gate/up rows interleaved in blocks of 64."""
+        x, wg, wu = node.inputs
+        out = node.outputs[0]
+        dt = self.sd(out.dtype)
+        inter, K = int(wg.shape[0]), int(wg.shape[1])
+        if dt not in ("float16", "bfloat16") or self.view(x.name).dtype != dt or K % 8:
+            return self.lower_original(node)
+        wp = f"{node.name}__w"
+        self.out.weight_preps.append(WeightPrep("interleave_rows", [wg.name, wu.name], [wp], {"rows": inter, "cols": K, "block": 64, "dtype": dt}))
+        self.out.views[wp] = TensorView(wp, 0, (2 * inter, K), (K, 1), dt)
+        self._linear(node, [x, TensorSpec(wp, [2 * inter, K], wg.dtype)], out, has_bias=False, glu=True)
+
+    def _linear(self, node, ins, out: TensorSpec, has_bias: bool, residual=None, aux=None, relu=False, glu=False) -> None:
         x, w = ins[0].name, ins[1].name
         bias = ins[2].name if has_bias else None
         dt = self.sd(out.dtype)
@@ -726,15 +741,16 @@ class _Lowering:
             raise ValueError(f"linear input {x} is {xv.dtype}, expected {dt}")
         xn, x2 = self.as_2d(x)
         M, K = x2.shape
-        N = self.view(w).shape[0]
+        N = self.view(w).shape[0]          # rows of W (gate and up rows together for the gated form)
+        n_out = N // 2 if glu else N
         if x2.strides[0] % 8 or x2.offset % 8:
             xn = self.contiguous(xn, "aligned")
             x2 = V.try_reshape(self.view(xn), (M, K))
         o = self.alloc(out.name, out.shape, dt)
-        o2 = V.try_reshape(o, (M, N))
+        o2 = V.try_reshape(o, (M, n_out))
         names = [xn, w]
         p = {"op": "linear", "x": x2, "w": w, "bias": bias, "y": o2, "M": M, "N": N, "K": K, "transpose_b": True,
-             "has_bias": has_bias, "relu": bool(relu), "residual": None, "aux": None, "workspace": None}
+             "has_bias": has_bias, "relu": bool(relu), "residual": None, "aux": None, "workspace": None, "glu": bool(glu)}
         if bias:
             names.append(bias)
         for key, t in (("residual", residual), ("aux", aux)):
@@ -744,13 +760,13 @@ class _Lowering:
                     raise ValueError(f"linear epilogue operand {t.name} has dtype {t2.dtype}, expected {dt}")
                 p[key] = t2
                 names.append(tn)
-        if M <= 64:
+        if M <= 128:
             p["workspace"] = "__ws_splitk"
             names.append("__ws_splitk")
             self.out.buffers.setdefault("__ws_splitk", BufferAllocation("__ws_splitk", [0], "uint8", 0, persistent=True))
             p["workspace_key"] = (M, N, K)
         desc = "x @ W^T" + (" + b" if has_bias else "") + (" + residual" if residual is not None else "") + \
-               (" -> relu" if relu else "") + (" -> silu(.) * up" if aux is not None else "")
+               (" -> relu" if relu else "") + (" -> silu(.) * up" if aux is not None else "") + (" -> silu(gate) * up, interleaved rows" if glu else "")
         self.emit(CUBLASStep("gemm", names, out.name, p), names + [out.name])
         self.out.steps[-1].params["source"] = desc
 

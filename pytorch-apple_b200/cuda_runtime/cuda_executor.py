@@ -171,6 +171,8 @@ class CUDAExecutor:
                 self._prep_conv(prep, stream)
             elif prep.kind == "concat_rows":
                 self._prep_concat(prep)
+            elif prep.kind == "interleave_rows":
+                self._prep_interleave(prep)
             else:
                 raise RuntimeError(f"unknown weight preparation {prep.kind}")
 
@@ -218,6 +220,22 @@ class CUDAExecutor:
                 raise RuntimeError(f"weight '{name}' has {src.numel()} elements, expected {rows * cols}")
             self._convert(src.reshape(-1), out[at:at + rows * cols])
             at += rows * cols
+        self._prepared[prep.outputs[0]] = out
+
+    def _prep_interleave(self, prep) -> None:
+        """Gate and up projection rows interleaved in blocks (gated-MLP GEMM), in the compute dtype."""
+        p = prep.params
+        rows, cols, blk = p["rows"], p["cols"], p["block"]
+        out = torch.empty(2 * rows * cols, dtype=getattr(torch, p["dtype"]), device=self._device)
+        for half, name in enumerate(prep.inputs):
+            src = self._raw_weight(name)
+            src = src if src.is_contiguous() else src.contiguous()
+            if src.numel() != rows * cols:
+                raise RuntimeError(f"weight '{name}' has {src.numel()} elements, expected {rows * cols}")
+            dst = native.make_tensor(out.data_ptr() + half * blk * cols * out.element_size(), p["dtype"], (rows // blk, blk, cols),
+                                     (2 * blk * cols, cols, 1))
+            s_t = native.make_tensor(src.data_ptr(), str(src.dtype).replace("torch.", ""), (rows // blk, blk, cols), (blk * cols, cols, 1))
+            native.check(self._lib.b200_strided_copy(C.byref(dst), C.byref(s_t), self._stream_ptr()), "weight interleave")
         self._prepared[prep.outputs[0]] = out
 
     def _prep_conv(self, prep, stream: int) -> None:
@@ -436,7 +454,7 @@ class CUDAExecutor:
         x, y = p["x"], p["y"]
         dt = y.dtype
         res, aux = p["residual"], p["aux"]
-        epi = (native.EPI_RELU if p["relu"] else 0) | (native.EPI_SILU_MUL if aux is not None else 0)
+        epi = (native.EPI_RELU if p["relu"] else 0) | (native.EPI_SILU_MUL if aux is not None else 0) | (native.EPI_GLU if p.get("glu") else 0)
         ws = self._ws["__ws_splitk"] if p["workspace"] else None
         ld = lambda v: (v.strides[0] if v.shape[0] > 1 else v.shape[1]) if v is not None else 0
         plan.launches.append((self._lib.b200_linear, (

@@ -21,6 +21,7 @@ DTYPE_BYTES = {"float32": 4, "float16": 2, "bfloat16": 2, "int32": 4, "int64": 8
 
 EPI_RELU = 1
 EPI_SILU_MUL = 2
+EPI_GLU = 4
 
 
 class Tensor(C.Structure):

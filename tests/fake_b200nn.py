@@ -74,7 +74,7 @@ class FakeLibrary:
         return self._err
 
     def b200_linear_workspace_bytes(self, M, N, K):
-        return 256 if M <= 64 else 0
+        return 256 if M <= 128 else 0
 
     def b200_attn_decode_workspace_bytes(self, B, Hq, Hkv, S, D):
         return 256
@@ -283,6 +283,12 @@ class FakeLibrary:
         r = a @ w.t()
         if _addr(bias):
             r = r + _flat(bias, bias_dtype, N).float()
+        if epilogue & 4:  # gated MLP: gate/up rows interleaved in blocks of 64
+            r = r.reshape(M, N // 128, 2, 64)
+            g, u = r[:, :, 0].to(dt).float(), r[:, :, 1].to(dt).float()
+            r = ((g / (1 + torch.exp(-g))).to(dt).float() * u).reshape(M, N // 2)
+            _raw(out, dt, [M, N // 2], [ldo, 1]).copy_(r.to(dt))
+            return 0
         if _addr(residual):
             r = r.to(dt).float() + _raw(residual, dt, [M, N], [ldr, 1]).float()
         if epilogue & 1:

@@ -167,7 +167,9 @@ def test_qwen_mlp_pattern_at_real_sizes():
     ir = graph(n, [x], [ts("y", [1, 1536])], [ts("gate_w", [8960, 1536]), ts("up_w", [8960, 1536]), ts("down_w", [1536, 8960])])
     prog = compile_subgraph(ir)
     blas = [s for s in prog.steps if isinstance(s, CUBLASStep)]
-    assert len(blas) == 3 and sum(1 for b in blas if b.params["aux"] is not None) == 1   # silu*up rides in the gate GEMM
+    # gate and up share one GEMM over interleaved rows with the silu*up epilogue; down is the second
+    assert len(blas) == 2 and blas[0].params["glu"] and blas[0].params["N"] == 2 * 8960 and blas[1].params["K"] == 8960
+    assert [p.kind for p in prog.weight_preps] == ["interleave_rows"]
     assert not [s for s in prog.steps if isinstance(s, FusedKernelStep)]
 
 
@@ -179,12 +181,12 @@ def test_qwen_decode_layer_plan():
     assert prog.compute_dtype == "bfloat16"
     kinds = [getattr(s, "kernel_name", None) or s.blas_type for s in prog.steps if not isinstance(s, AliasStep)]
     assert kinds.count("attention") == L and kinds.count("rmsnorm_kernel") == 2 * L + 1
-    assert kinds.count("gemm") == 5 * L + 1                    # q, k, v share one GEMM
+    assert kinds.count("gemm") == 4 * L + 1                    # qkv, o_proj, gate+up, down
     assert kinds.count("qkv_rope_cache_kernel") == L           # rope(q), rope(k) + key write, value write: one launch
     assert kinds.count("index_copy_kernel") == 0 and kinds.count("rope_rotate_kernel") == 0
     assert len(prog.donated_inputs) == 2 * L
     per_layer = (len(kinds) - 4) / L                           # minus embedding, rope table, final norm, lm_head
-    assert per_layer == 9
+    assert per_layer == 8
     # without donation the cache is copied, as in the reference
     prog2 = compile_subgraph(ir, donate_inputs=False)
     assert not prog2.donated_inputs

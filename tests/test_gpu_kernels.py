@@ -109,6 +109,25 @@ def test_linear_tcgen05_shapes(lib, M, N, K):
     assert code.value == 0
 
 
+@pytest.mark.parametrize("M,I,K", [(1, 8960, 1536), (8, 8960, 1536), (64, 8960, 1536), (512, 8960, 1536), (40, 256, 72)])
+def test_linear_gated_mlp_epilogue(lib, M, I, K):
+    """silu(x Wg^T) * (x Wu^T) from one GEMM over gate/up rows interleaved in blocks of 64."""
+    dtype = torch.bfloat16
+    x, wg, wu = gen((M, K), dtype), gen((I, K), dtype, 1, 0.05), gen((I, K), dtype, 2, 0.05)
+    g = (x.float() @ wg.float().t()).to(dtype).float()
+    u = (x.float() @ wu.float().t()).to(dtype).float()
+    ref = torch.nn.functional.silu(g).to(dtype).float() * u
+    merged = torch.stack([wg.view(I // 64, 64, K), wu.view(I // 64, 64, K)], 1).reshape(2 * I, K).contiguous()
+    X, W = x.cuda(), merged.cuda()
+    out = torch.full((M, I), float("nan"), dtype=dtype, device="cuda")
+    ws = torch.zeros(max(lib.b200_linear_workspace_bytes(M, 2 * I, K), 16), dtype=torch.uint8, device="cuda")
+    for _ in range(2):
+        ok(lib, lib.b200_linear(X.data_ptr(), W.data_ptr(), None, None, out.data_ptr(), M, 2 * I, K, K, K, I, 0, 2, 2, 4, None, 0,
+                                ws.data_ptr(), ws.numel(), stream()))
+        close(out, ref, rtol=3e-2, atol=3e-2 * max(1.0, math.sqrt(K) * 0.05))
+    assert not ws.any()
+
+
 def test_linear_rejects_unaligned(lib):
     a = torch.zeros(4, 12, dtype=torch.bfloat16, device="cuda")
     rc = lib.b200_linear(a.data_ptr(), a.data_ptr(), None, None, a.data_ptr(), 4, 4, 12, 12, 12, 4, 0, 2, 2, 0, None, 0, None, 0, stream())
