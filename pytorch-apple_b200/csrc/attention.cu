@@ -193,6 +193,7 @@ __global__ void __launch_bounds__(128, 2) attn_decode_kernel(const __grid_consta
   if (threadIdx.x < DEC_MAX_BLOCKS / 32) valid[threadIdx.x] = 0u;
   for (int i = threadIdx.x; i < 8 * HD; i += 128) (&s_acc[0][0])[i] = 0.f;
   __syncthreads();
+  pdl_wait();   // q, the new cache rows and the mask come from the kernels before this one
   for (int i = threadIdx.x; i < nblk * 16; i += 128) {
     const int64_t key = s_begin + i;
     float mv = 0.f;
@@ -281,6 +282,7 @@ __global__ void __launch_bounds__(128, 2) attn_decode_kernel(const __grid_consta
     st_use = (st_use + 1) % DEC_STAGES;
   }
   cp_async_wait<0>();
+  pdl_trigger();
 
   // ---- merge the four warps (rows 0..7 only: G <= 8 lives in the g half) --------------
   if (t == 0) { s_m[warp][g] = w.m[0]; s_l[warp][g] = w.l[0]; }
@@ -317,6 +319,8 @@ __global__ void __launch_bounds__(128) attn_decode_merge_kernel(const float* __r
                                                                 T* __restrict__ out, int Hq, int Hkv, int G, int splits) {
   const int64_t bh = blockIdx.x, b = bh / Hq;
   const int h = static_cast<int>(bh % Hq), hk = h / G, r = h % G;
+  pdl_wait();
+  pdl_trigger();
   const int64_t base = (b * Hkv + hk) * splits;
   float m_all = -INFINITY;
   for (int s = 0; s < splits; ++s) m_all = fmaxf(m_all, part_ml[((base + s) * G + r) * 2]);
@@ -454,9 +458,9 @@ extern "C" int b200_attn_decode(const void* q, const void* k, const void* v, con
       if (e != cudaSuccess) B200_FAIL(B200_ELAUNCH, "attn_decode_kernel attribute: %s", cudaGetErrorString(e));
       configured = true;
     }
-    attn_decode_kernel<T><<<grid, 128, DEC_SMEM, st>>>(p);
-    attn_decode_merge_kernel<T><<<static_cast<unsigned>(B * Hq), 128, 0, st>>>(p.part_acc, p.part_ml, static_cast<T*>(out), Hq, Hkv,
-                                                                               p.G, d.splits);
+    launch_pdl(attn_decode_kernel<T>, grid, dim3(128), DEC_SMEM, st, p);
+    launch_pdl(attn_decode_merge_kernel<T>, dim3(static_cast<unsigned>(B * Hq)), dim3(128), 0, st, static_cast<const float*>(p.part_acc),
+               static_cast<const float*>(p.part_ml), static_cast<T*>(out), Hq, Hkv, p.G, d.splits);
   });
   B200_CHECK_LAUNCH("attn_decode_kernel");
   return B200_OK;

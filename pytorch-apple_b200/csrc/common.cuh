@@ -15,6 +15,33 @@ namespace b200 {
 // ---- host-side error plumbing ------------------------------------------------
 void set_error(const char* fmt, ...);
 int sm_count();  // SM count of the current device (cached per device)
+bool pdl_enabled();  // programmatic dependent launch for the decode-path kernels (B200NN_PDL=0 turns it off)
+
+// ---- programmatic dependent launch ---------------------------------------------
+// A kernel launched through launch_pdl may start while its predecessor in the stream is
+// still draining; it must execute pdl_wait() before it touches memory the predecessor
+// writes (the wait returns once the predecessor grid has completed and flushed).
+// pdl_trigger() lets the successor's blocks be scheduled early.  Both are no-ops for a
+// plain launch.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr = {};
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  if (pdl_enabled()) {
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+  }
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 
 #define B200_FAIL(code, ...)        \
   do {                              \

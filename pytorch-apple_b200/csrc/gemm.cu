@@ -247,6 +247,7 @@ __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant_
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
+  pdl_wait();
   const int64_t n_blk = static_cast<int64_t>(blockIdx.x) * SK_ROWS;
   const int64_t k_begin = static_cast<int64_t>(blockIdx.y) * p.k_per_split;
   const int64_t k_end = min(p.K, k_begin + p.k_per_split);
@@ -320,6 +321,7 @@ __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant_
     compute(w1, k + 32);
   }
 
+  pdl_trigger();
   // acc[i][j][2h+e] = partial out[m = 8j + 2t + e][n = n_blk + warp*32 + 16i + g + 8h]
   bool finish = true;
   if (p.splits > 1) {
@@ -530,10 +532,10 @@ extern "C" int b200_linear(const void* A, const void* W, const void* bias, const
     dim3 grid(static_cast<unsigned>(s.row_blocks), static_cast<unsigned>(s.splits));
     B200_DISPATCH_HALF(dtype, T, {
       switch (s.mpad) {
-        case 8: gemm_skinny_kernel<T, 1><<<grid, 128, 0, st>>>(p); break;
-        case 16: gemm_skinny_kernel<T, 2><<<grid, 128, 0, st>>>(p); break;
-        case 32: gemm_skinny_kernel<T, 4><<<grid, 128, 0, st>>>(p); break;
-        default: gemm_skinny_kernel<T, 8><<<grid, 128, 0, st>>>(p); break;
+        case 8: launch_pdl(gemm_skinny_kernel<T, 1>, grid, dim3(128), 0, st, p); break;
+        case 16: launch_pdl(gemm_skinny_kernel<T, 2>, grid, dim3(128), 0, st, p); break;
+        case 32: launch_pdl(gemm_skinny_kernel<T, 4>, grid, dim3(128), 0, st, p); break;
+        default: launch_pdl(gemm_skinny_kernel<T, 8>, grid, dim3(128), 0, st, p); break;
       }
     });
     B200_CHECK_LAUNCH("gemm_skinny_kernel");

@@ -134,6 +134,7 @@ __global__ void __launch_bounds__(192, 2) gemm_tc5_kernel(const __grid_constant_
   __syncthreads();
   tc5::tc_fence_after();
   const uint32_t tmem_base = tmem_holder;
+  pdl_wait();   // barriers, tensor memory and descriptors are set up; operands come from earlier kernels
 
   if (warp == 0) {
     if (lane == 0) {
@@ -152,6 +153,7 @@ __global__ void __launch_bounds__(192, 2) gemm_tc5_kernel(const __grid_constant_
         for (int i = issued > ST ? issued - ST : 0; i < issued; ++i) tc5::mbar_wait(&full_bar[i % ST], (i / ST) & 1);
       }
     }
+    pdl_trigger();   // every warp triggers once its part of the main loop is over
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc = tc5::umma_idesc(BM, BN, AbFormat<T>::value);
@@ -169,6 +171,7 @@ __global__ void __launch_bounds__(192, 2) gemm_tc5_kernel(const __grid_constant_
       }
       tc5::umma_commit(&acc_bar);
     }
+    pdl_trigger();
   } else {
     const int q = warp & 3;  // warps 2,3,4,5 -> TMEM lane quarters 2,3,0,1
     bool ok = true;
@@ -177,6 +180,7 @@ __global__ void __launch_bounds__(192, 2) gemm_tc5_kernel(const __grid_constant_
     if (!ok && lane == 0) { failed = 1; atomicExch(&g_tc5_error, 3); }
     ok = ok && !*reinterpret_cast<volatile int*>(&failed);
     ok = __all_sync(0xffffffffu, ok);
+    pdl_trigger();
     const int64_t m = m0 + q * 32 + lane;
     const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
     const bool glu = (p.epilogue & B200_EPI_GLU) != 0;  // host guarantees BN == 128 and N % 128 == 0
@@ -335,7 +339,7 @@ template <typename T, int BN> int launch(const Tc5Args& a, const Tc5Plan& pl, cu
     p.ctr = reinterpret_cast<unsigned int*>(static_cast<uint8_t*>(a.workspace) + a.M * pl.ws_pitch * 4);
   }
   dim3 grid(static_cast<unsigned>(pl.tiles_n), static_cast<unsigned>(pl.tiles_m), static_cast<unsigned>(pl.splits));
-  gemm_tc5_kernel<T, BN><<<grid, 192, SMEM, st>>>(ma, mw, p);
+  launch_pdl(gemm_tc5_kernel<T, BN>, grid, dim3(192), SMEM, st, ma, mw, p);
   B200_CHECK_LAUNCH("gemm_tc5_kernel");
   return B200_OK;
 }

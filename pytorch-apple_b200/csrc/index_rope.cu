@@ -130,6 +130,8 @@ template <typename T>
 __global__ void __launch_bounds__(128) qkv_rope_cache_kernel(const __grid_constant__ QkvPostParams p) {
   const int packs = p.D >> 3, half_packs = packs >> 1, H = p.Hq + 2 * p.Hkv;
   const int64_t gid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  pdl_wait();
+  pdl_trigger();
   if (gid >= p.B * H * p.T * packs) return;
   const int pk = static_cast<int>(gid % packs);
   int64_t r = gid / packs;
@@ -196,7 +198,7 @@ extern "C" int b200_qkv_rope_cache(const b200_tensor* q, const b200_tensor* k, c
   const int64_t total = p.B * (p.Hq + 2 * p.Hkv) * p.T * (p.D >> 3);
   if (total == 0) return B200_OK;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  B200_DISPATCH_HALF(q->dtype, T, { qkv_rope_cache_kernel<T><<<static_cast<unsigned>(ceil_div(total, 128)), 128, 0, st>>>(p); });
+  B200_DISPATCH_HALF(q->dtype, T, { launch_pdl(qkv_rope_cache_kernel<T>, dim3(static_cast<unsigned>(ceil_div(total, 128))), dim3(128), 0, st, p); });
   B200_CHECK_LAUNCH("qkv_rope_cache_kernel");
   return B200_OK;
 }

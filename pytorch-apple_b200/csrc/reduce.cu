@@ -15,6 +15,8 @@ __global__ void __launch_bounds__(128) rmsnorm_warp_kernel(const T* __restrict__
                                                            int round_mid) {
   const int lane = threadIdx.x & 31;
   const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  pdl_wait();
+  pdl_trigger();
   if (row >= rows) return;
   const int npack = cols >> 3;
   const uint4* xr = reinterpret_cast<const uint4*>(x + row * xs);
@@ -202,6 +204,8 @@ __global__ void __launch_bounds__(1024) argmax_rows_kernel(const T* __restrict__
                                                            int64_t row_stride) {
   __shared__ float s_val[32];
   __shared__ int64_t s_idx[32];
+  pdl_wait();
+  pdl_trigger();
   const T* xr = x + static_cast<int64_t>(blockIdx.x) * row_stride;
   float best = -INFINITY;
   int64_t bidx = INT64_MAX;
@@ -260,9 +264,9 @@ extern "C" int b200_rmsnorm(const void* x, const void* w, void* y, int64_t rows,
     if (vec) {
       const int grid = static_cast<int>(ceil_div(rows, 4));
       if (cols <= 1024)
-        rmsnorm_warp_kernel<T, 4><<<grid, 128, 0, st>>>(xp, wp, yp, rows, (int)cols, x_row_stride, y_row_stride, eps, round_mid);
+        launch_pdl(rmsnorm_warp_kernel<T, 4>, dim3(grid), dim3(128), 0, st, xp, wp, yp, rows, (int)cols, x_row_stride, y_row_stride, eps, round_mid);
       else
-        rmsnorm_warp_kernel<T, 8><<<grid, 128, 0, st>>>(xp, wp, yp, rows, (int)cols, x_row_stride, y_row_stride, eps, round_mid);
+        launch_pdl(rmsnorm_warp_kernel<T, 8>, dim3(grid), dim3(128), 0, st, xp, wp, yp, rows, (int)cols, x_row_stride, y_row_stride, eps, round_mid);
     } else {
       rmsnorm_block_kernel<T><<<static_cast<int>(rows), 256, 0, st>>>(xp, wp, yp, cols, x_row_stride, y_row_stride, eps, round_mid);
     }
@@ -325,7 +329,7 @@ extern "C" int b200_argmax_rows(const void* x, int64_t* out, int64_t rows, int64
   if (rows == 0) return B200_OK;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   B200_DISPATCH_FLOAT(dtype, T, {
-    argmax_rows_kernel<T><<<static_cast<int>(rows), 1024, 0, st>>>(static_cast<const T*>(x), out, cols, row_stride);
+    launch_pdl(argmax_rows_kernel<T>, dim3(static_cast<unsigned>(rows)), dim3(1024), 0, st, static_cast<const T*>(x), out, cols, row_stride);
   });
   B200_CHECK_LAUNCH("argmax_rows_kernel");
   return B200_OK;

@@ -1,5 +1,6 @@
 // Library-wide host helpers: thread-local error string, device queries.
 #include <stdarg.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 
@@ -24,6 +25,15 @@ int sm_count() {
     cached[dev] = n;
   }
   return cached[dev];
+}
+
+bool pdl_enabled() {
+  static int state = -1;
+  if (state < 0) {
+    const char* e = getenv("B200NN_PDL");
+    state = (e && e[0] == '0') ? 0 : 1;
+  }
+  return state == 1;
 }
 
 }  // namespace b200
