@@ -26,6 +26,8 @@ struct Tc5Params {
   unsigned int* ctr;    // one arrival counter per output tile; zero on entry and exit
   int64_t M, N, K, ldo, ldr, ldaux, ws_pitch;
   int bias_dtype, epilogue, splits, kb_per_split;
+  const void* x;   // convolution input (implicit-GEMM mode only)
+  Tc5Conv g;
 };
 
 template <typename T> struct AbFormat;
@@ -103,7 +105,18 @@ __device__ __forceinline__ void finish_glu(const Tc5Params& p, float (&vg)[32], 
   }
 }
 
-template <typename T, int BN>
+__device__ __forceinline__ void cp_async16_zfill(uint32_t smem_dst, const void* gptr, int src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_dst), "l"(gptr), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tc5::smem_addr(bar)) : "memory");
+}
+
+// CONV = false: A tiles arrive by TMA.  CONV = true (implicit-GEMM convolution): the four
+// epilogue warps, idle during the main loop, gather the A tile - one output pixel per
+// thread, 128 bytes of channels per k-block - with zero-filling cp.async into the same
+// 128-byte-swizzled layout TMA would produce, and signal the stage's barrier themselves.
+template <typename T, int BN, bool CONV>
 __global__ void __launch_bounds__(192, 2) gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a,
                                                           const __grid_constant__ CUtensorMap map_w, const Tc5Params p) {
   constexpr int ST = Cfg<BN>::ST;
@@ -123,7 +136,7 @@ __global__ void __launch_bounds__(192, 2) gemm_tc5_kernel(const __grid_constant_
   if (threadIdx.x == 0) {
     failed = 0;
     is_last = 0;
-    for (int s = 0; s < ST; ++s) { tc5::mbar_init(&full_bar[s], 1); tc5::mbar_init(&empty_bar[s], 1); }
+    for (int s = 0; s < ST; ++s) { tc5::mbar_init(&full_bar[s], CONV ? 129 : 1); tc5::mbar_init(&empty_bar[s], 1); }
     tc5::mbar_init(&acc_bar, 1);
     tc5::fence_barrier_init();
     tc5::prefetch_tensormap(&map_a);
@@ -144,8 +157,8 @@ __global__ void __launch_bounds__(192, 2) gemm_tc5_kernel(const __grid_constant_
         const uint32_t ph = (i / ST) & 1;
         if (!tc5::mbar_wait(&empty_bar[s], ph ^ 1)) { failed = 1; atomicExch(&g_tc5_error, 1); break; }
         if (*reinterpret_cast<volatile int*>(&failed)) break;
-        tc5::mbar_arrive_expect_tx(&full_bar[s], STAGE);
-        tc5::tma_load_2d(smem + s * STAGE, &map_a, &full_bar[s], (kb0 + i) * BK, m0);
+        tc5::mbar_arrive_expect_tx(&full_bar[s], CONV ? B_STAGE : STAGE);
+        if (!CONV) tc5::tma_load_2d(smem + s * STAGE, &map_a, &full_bar[s], (kb0 + i) * BK, m0);
         tc5::tma_load_2d(smem + s * STAGE + A_STAGE, &map_w, &full_bar[s], (kb0 + i) * BK, n0);
         issued = i + 1;
       }
@@ -174,6 +187,44 @@ __global__ void __launch_bounds__(192, 2) gemm_tc5_kernel(const __grid_constant_
     pdl_trigger();
   } else {
     const int q = warp & 3;  // warps 2,3,4,5 -> TMEM lane quarters 2,3,0,1
+    if (CONV) {
+      // ---- A-operand gather: this thread owns tile row q*32+lane (the pixel it will also finish) ----
+      constexpr int LAG = 2;   // k-blocks of copies kept in flight per thread
+      const int row = q * 32 + lane;
+      const int64_t mrow = static_cast<int64_t>(m0) + row;
+      const bool row_ok = mrow < p.M;
+      const int64_t mm = row_ok ? mrow : 0;
+      const int ow = static_cast<int>(mm % p.g.Wo), oh = static_cast<int>((mm / p.g.Wo) % p.g.Ho);
+      const int64_t img = mm / (static_cast<int64_t>(p.g.Wo) * p.g.Ho);
+      const int ih0 = oh * p.g.sh - p.g.ph, iw0 = ow * p.g.sw - p.g.pw;
+      const T* xb = static_cast<const T*>(p.x) + img * p.g.H * p.g.W * p.g.C;
+      const int cpb = p.g.C / BK;   // k-blocks per filter tap
+      const uint32_t row_off = row * 128, swz = row & 7;
+      bool alive = true;
+      for (int i = 0; i < nkb + LAG; ++i) {
+        if (i < nkb && alive) {
+          const int s = i % ST;
+          if (!tc5::mbar_wait(&empty_bar[s], ((i / ST) & 1) ^ 1)) { failed = 1; atomicExch(&g_tc5_error, 4); alive = false; }
+          if (alive) {
+            const int kb = kb0 + i, tap = kb / cpb, c0 = (kb - tap * cpb) * BK;
+            const int r = tap / p.g.KW, sx = tap - r * p.g.KW;
+            const int ih = ih0 + r, iw = iw0 + sx;
+            const bool in = row_ok && ih >= 0 && ih < p.g.H && iw >= 0 && iw < p.g.W;
+            const T* src = in ? xb + (static_cast<int64_t>(ih) * p.g.W + iw) * p.g.C + c0 : static_cast<const T*>(p.x);
+            const uint32_t dst = tc5::smem_addr(smem + s * STAGE) + row_off;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) cp_async16_zfill(dst + ((j ^ swz) << 4), src + (in ? j * 8 : 0), in ? 16 : 0);
+          }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        if (i >= LAG && alive) {
+          asm volatile("cp.async.wait_group %0;" ::"n"(LAG) : "memory");
+          tc5::fence_proxy_async();          // generic-proxy writes -> visible to the tensor core's async-proxy reads
+          mbar_arrive(&full_bar[(i - LAG) % ST]);
+        }
+      }
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
     bool ok = true;
     if (lane == 0) ok = tc5::mbar_wait(&acc_bar, 0);
     ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
@@ -315,19 +366,23 @@ Tc5Plan plan_tc5(int64_t M, int64_t N, int64_t K, bool glu = false) {
   return pl;
 }
 
-template <typename T, int BN> int launch(const Tc5Args& a, const Tc5Plan& pl, cudaStream_t st) {
+template <typename T, int BN, bool CONV> int launch(const Tc5Args& a, const Tc5Plan& pl, cudaStream_t st, const Tc5Conv* g = nullptr) {
   constexpr int SMEM = Cfg<BN>::ST * (A_STAGE + BN * BK * 2) + 1024;
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(gemm_tc5_kernel<T, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) {
+    if (cudaFuncSetAttribute(gemm_tc5_kernel<T, BN, CONV>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) {
       cudaGetLastError();
       return B200_ENOTSUP;
     }
     configured = true;
   }
   CUtensorMap ma, mw;
-  if (!make_map(&ma, a.A, a.M, a.K, a.lda, BM, a.dtype) || !make_map(&mw, a.W, a.N, a.K, a.ldw, BN, a.dtype)) return B200_ENOTSUP;
+  if (!make_map(&mw, a.W, a.N, a.K, a.ldw, BN, a.dtype)) return B200_ENOTSUP;
+  if (CONV) ma = mw;   // unused in implicit-GEMM mode
+  else if (!make_map(&ma, a.A, a.M, a.K, a.lda, BM, a.dtype)) return B200_ENOTSUP;
   Tc5Params p;
+  p.x = a.A;
+  p.g = g ? *g : Tc5Conv{};
   p.bias = a.bias; p.residual = a.residual; p.aux = a.aux; p.out = a.out;
   p.M = a.M; p.N = a.N; p.K = a.K; p.ldo = a.ldo; p.ldr = a.ldr; p.ldaux = a.ldaux; p.ws_pitch = pl.ws_pitch;
   p.bias_dtype = a.bias_dtype; p.epilogue = a.epilogue; p.splits = pl.splits; p.kb_per_split = pl.kb_per_split;
@@ -339,7 +394,7 @@ template <typename T, int BN> int launch(const Tc5Args& a, const Tc5Plan& pl, cu
     p.ctr = reinterpret_cast<unsigned int*>(static_cast<uint8_t*>(a.workspace) + a.M * pl.ws_pitch * 4);
   }
   dim3 grid(static_cast<unsigned>(pl.tiles_n), static_cast<unsigned>(pl.tiles_m), static_cast<unsigned>(pl.splits));
-  launch_pdl(gemm_tc5_kernel<T, BN>, grid, dim3(192), SMEM, st, ma, mw, p);
+  launch_pdl(gemm_tc5_kernel<T, BN, CONV>, grid, dim3(192), SMEM, st, ma, mw, p);
   B200_CHECK_LAUNCH("gemm_tc5_kernel");
   return B200_OK;
 }
@@ -377,8 +432,25 @@ int linear_tc5(const Tc5Args& a, cudaStream_t st) {
   if (glu && (a.N % 128 || (a.epilogue & ~B200_EPI_GLU) || a.residual)) return B200_ENOTSUP;
   const Tc5Plan pl = plan_tc5(a.M, a.N, a.K, glu);
   if (pl.tiles_m > 65535 || pl.splits > 65535) return B200_ENOTSUP;
-  if (a.dtype == B200_BF16) return pl.bn == 64 ? launch<__nv_bfloat16, 64>(a, pl, st) : launch<__nv_bfloat16, 128>(a, pl, st);
-  return pl.bn == 64 ? launch<__half, 64>(a, pl, st) : launch<__half, 128>(a, pl, st);
+  if (a.dtype == B200_BF16) return pl.bn == 64 ? launch<__nv_bfloat16, 64, false>(a, pl, st) : launch<__nv_bfloat16, 128, false>(a, pl, st);
+  return pl.bn == 64 ? launch<__half, 64, false>(a, pl, st) : launch<__half, 128, false>(a, pl, st);
+}
+
+int conv_tc5(const Tc5Args& a, const Tc5Conv& g, cudaStream_t st) {
+  if (!tc5_enabled()) return B200_ENOTSUP;
+  if (a.dtype != B200_BF16 && a.dtype != B200_F16) return B200_ENOTSUP;
+  if (g.C % BK || a.K != static_cast<int64_t>(g.KH) * g.KW * g.C || a.ldw % 8 || !aligned16(a.A) || !aligned16(a.W)) return B200_ENOTSUP;
+  if (a.M >= (1ll << 31) || a.N >= (1ll << 31) || (a.epilogue & ~B200_EPI_RELU)) return B200_ENOTSUP;
+  Tc5Plan pl;
+  pl.bn = a.N >= 128 ? 128 : 64;
+  pl.tiles_n = ceil_div(a.N, pl.bn);
+  pl.tiles_m = ceil_div(a.M, BM);
+  pl.splits = 1;
+  pl.kb_per_split = static_cast<int>(a.K / BK);
+  pl.ws_pitch = pl.tiles_n * pl.bn;
+  if (pl.tiles_m > 65535) return B200_ENOTSUP;
+  if (a.dtype == B200_BF16) return pl.bn == 64 ? launch<__nv_bfloat16, 64, true>(a, pl, st, &g) : launch<__nv_bfloat16, 128, true>(a, pl, st, &g);
+  return pl.bn == 64 ? launch<__half, 64, true>(a, pl, st, &g) : launch<__half, 128, true>(a, pl, st, &g);
 }
 
 }  // namespace b200

@@ -12,6 +12,16 @@ struct Tc5Args {
   int64_t workspace_bytes;
 };
 
+// Geometry of an NHWC convolution run as an implicit GEMM (A rows are output pixels,
+// k runs over (filter row, filter column, channel)).
+struct Tc5Conv {
+  int H, W, C, KH, KW, sh, sw, ph, pw, Ho, Wo;
+};
+
+// y = epi(conv(x, w) + bias + residual) on the tcgen05 path; needs C % 64 == 0.
+// Args: A = x [N,H,W,C], W = packed weights [O, KH*KW*C], M = N*Ho*Wo, N = O, K = KH*KW*C.
+int conv_tc5(const Tc5Args& a, const Tc5Conv& g, cudaStream_t stream);
+
 // out = epi(A W^T + bias + residual) on the tcgen05 path.  Returns B200_ENOTSUP when the
 // operands do not meet the TMA alignment rules (the caller then uses the mma.sync tiles).
 int linear_tc5(const Tc5Args& a, cudaStream_t stream);
