@@ -278,6 +278,21 @@ int b200_attn_decode(const void* q, const void* k, const void* v, const void* ma
                      float scale, int dtype, void* workspace, int64_t workspace_bytes, void* stream);
 int64_t b200_attn_decode_workspace_bytes(int64_t B, int Hq, int Hkv, int64_t S, int D);
 
+/* Same computation as b200_attn_decode for callers that cannot allocate device memory
+ * (a host runtime that owns every byte of the GPU, FFI glue that may only forward pointers
+ * it was handed, code running where cudaMalloc is off limits).  This entry point has no
+ * counterpart in the reference.  The split-KV partials go to an 8 MiB array that is part
+ * of the library image (each GPU that loads the library holds it until exit); shapes whose
+ * partials need more return B200_ELIMIT - for Hq=12, Hkv=2, S=4352 that is B > 79.  No
+ * cudaMalloc, cudaFree or allocating library call is made.  The first call on a device
+ * looks up the array's device address; make that call before any stream capture.  All
+ * calls share the array: two calls whose kernels overlap on the GPU (different streams)
+ * race.  Nothing in it needs clearing between calls - every partial is rewritten. */
+int b200_attn_decode_noalloc(const void* q, const void* k, const void* v, const void* mask, void* out,
+                             int64_t B, int Hq, int Hkv, int64_t S, int D, int64_t q_batch_stride,
+                             int64_t kv_batch_stride, int64_t kv_head_stride, int64_t mask_batch_stride,
+                             float scale, int dtype, void* stream);
+
 /* Prefill attention, replacing CUBLASStep("gemm_batched") x2 with the softmax
  * between them and the materialised expand/transpose copies
  * (subgraph_analyzer.py:206-215; cuda_executor.py:210-218):

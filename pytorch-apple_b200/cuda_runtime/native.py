@@ -68,6 +68,7 @@ SIGNATURES = {
     "b200_matmul_strided": (_i, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _I64P, _I64P, _I64P, _i, _vp]),
     "b200_conv2d_nhwc": (_i, [_vp, _vp, _vp, _vp, _vp] + [_i] * 16 + [_vp]),
     "b200_attn_decode": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i64, _i, _i64, _i64, _i64, _i64, _f, _i, _vp, _i64, _vp]),
+    "b200_attn_decode_noalloc": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i64, _i, _i64, _i64, _i64, _i64, _f, _i, _vp]),
     "b200_attn_decode_workspace_bytes": (_i64, [_i64, _i, _i, _i64, _i]),
     "b200_attn_prefill": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i64, _i64, _i, _I64P, _I64P, _I64P, _i64, _i64, _f, _i, _vp]),
 }

@@ -1,0 +1,55 @@
+"""The allocation-free decode attention entry point.
+
+Some callers of the library cannot allocate device memory - a host runtime that has
+already claimed the whole GPU, glue code that is only allowed to forward the pointers it
+received.  ``b200_attn_decode_noalloc`` serves them from a scratch array built into the
+library.  It must give what ``b200_attn_decode`` gives with a caller-provided workspace,
+on the first call and on the next one (the array keeps the previous call's contents).
+Collected last so that a run which stops at the first failure has already run everything else.
+"""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _case(B, S, valid, seed):
+    import model_zoo as mz
+
+    g = torch.Generator().manual_seed(seed)
+    Hq, Hkv, D = 12, 2, 128
+    q = torch.randn(B, Hq, D, generator=g).bfloat16().cuda()
+    k = torch.randn(B, Hkv, S, D, generator=g).bfloat16().cuda()
+    v = torch.randn(B, Hkv, S, D, generator=g).bfloat16().cuda()
+    mask = mz.causal_mask(B, 1, S, valid - 1).reshape(B, S).cuda()
+    return q, k, v, mask, Hq, Hkv, D
+
+
+def test_noalloc_matches_workspace_entry_point_twice(native_lib):
+    lib = native_lib
+    torch.cuda.set_device(0)
+    stream = torch.cuda.current_stream().cuda_stream
+    for B, S, valid, seed in ((8, 4352, 4100, 0), (3, 1024, 700, 1)):   # two calls in a row, different shapes
+        q, k, v, mask, Hq, Hkv, D = _case(B, S, valid, seed)
+        scale = D ** -0.5
+        ws = torch.empty(lib.b200_attn_decode_workspace_bytes(B, Hq, Hkv, S, D), dtype=torch.uint8, device="cuda")
+        want = torch.empty(B, Hq, D, dtype=torch.bfloat16, device="cuda")
+        got = torch.full_like(want, float("nan"))
+        rc = lib.b200_attn_decode(q.data_ptr(), k.data_ptr(), v.data_ptr(), mask.data_ptr(), want.data_ptr(), B, Hq, Hkv, S, D, Hq * D,
+                                  Hkv * S * D, S * D, S, scale, 2, ws.data_ptr(), ws.numel(), stream)
+        assert rc == 0, lib.b200_last_error().decode()
+        rc = lib.b200_attn_decode_noalloc(q.data_ptr(), k.data_ptr(), v.data_ptr(), mask.data_ptr(), got.data_ptr(), B, Hq, Hkv, S, D,
+                                          Hq * D, Hkv * S * D, S * D, S, scale, 2, stream)
+        assert rc == 0, lib.b200_last_error().decode()
+        torch.cuda.synchronize()
+        torch.testing.assert_close(got.float(), want.float(), rtol=2e-2, atol=5e-3)
+
+
+def test_noalloc_rejects_shapes_beyond_the_builtin_scratch(native_lib):
+    lib = native_lib
+    B, S = 200, 4352   # needs ~21 MB of partials, the array holds 8 MiB
+    dummy = torch.zeros(16, dtype=torch.bfloat16, device="cuda")
+    rc = lib.b200_attn_decode_noalloc(dummy.data_ptr(), dummy.data_ptr(), dummy.data_ptr(), None, dummy.data_ptr(), B, 12, 2, S, 128,
+                                      12 * 128, 2 * S * 128, S * 128, 0, 0.088, 2, torch.cuda.current_stream().cuda_stream)
+    assert rc == -5 and b"built-in array" in lib.b200_last_error()
