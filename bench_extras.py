@@ -6,11 +6,19 @@ CUDA events over device-resident inputs, after warm-up, as whole-graph replays.
 
 from __future__ import annotations
 
+import sys
+from pathlib import Path
+
 import numpy as np
 import torch
 
-import model_zoo as mz
-from ir_export import extract_ir
+_ROOT = Path(__file__).resolve().parent
+for _p in (_ROOT / "pytorch-apple_b200", _ROOT):
+    if str(_p) not in sys.path:
+        sys.path.insert(0, str(_p))
+
+import model_zoo as mz  # noqa: E402
+from ir_export import extract_ir  # noqa: E402
 
 CACHE_LEN, PREFILLED = 4352, 4096
 
@@ -110,3 +118,31 @@ def run(cfg, sd, device) -> dict:
         out[f"resnet50_b{b}"] = resnet50(device, b, tf)
         torch.cuda.empty_cache()
     return out
+
+
+if __name__ == "__main__":
+    # Stand-alone runs of one secondary workload, e.g. for profiling a small case:
+    #   python bench_extras.py qwen_prefill --layers 2
+    #   python bench_extras.py resnet50 --batch 256
+    #   python bench_extras.py qwen_decode --layers 2 --batch 1
+    import argparse
+    import json
+
+    from bench import measured_peaks
+
+    ap = argparse.ArgumentParser()
+    ap.add_argument("workload", choices=["qwen_prefill", "qwen_decode", "resnet50"])
+    ap.add_argument("--layers", type=int, default=28)
+    ap.add_argument("--batch", type=int, default=64)
+    ap.add_argument("--tokens", type=int, default=512)
+    a = ap.parse_args()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    hbm, tf, _ = measured_peaks()
+    if a.workload == "resnet50":
+        print(json.dumps(resnet50(dev, a.batch, tf)))
+    else:
+        cfg = mz.qwen2_config(num_layers=a.layers)
+        sd = mz.qwen2_weights(cfg, seed=0, device=str(dev))
+        res = qwen_prefill(cfg, sd, dev, a.tokens, tf) if a.workload == "qwen_prefill" else qwen_decode(cfg, sd, dev, a.batch, hbm)
+        print(json.dumps(res))

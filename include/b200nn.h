@@ -227,6 +227,9 @@ int b200_conv_weight_prep(const void* w, const void* conv_bias, const void* gamm
  * the merged rows (a multiple of 128) and out has N/2 columns:
  * out[:, 64j+c] = silu(acc[:, 128j+c]) * acc[:, 128j+64+c]. */
 #define B200_EPI_GLU 4
+/* Hint: W is a constant of the stream (a model weight), so the kernel may begin fetching it
+ * before the previous kernel in the stream has finished (programmatic dependent launch). */
+#define B200_EPI_W_STATIC 8
 
 /* CUBLASStep("gemm") (subgraph_analyzer.py:168-224, dispatch cuda_executor.py:182-208,
  * which calls cupy.matmul and a separate bias-add kernel):
@@ -283,7 +286,7 @@ int64_t b200_attn_decode_workspace_bytes(int64_t B, int Hq, int Hkv, int64_t S, 
  * it was handed, code running where cudaMalloc is off limits).  This entry point has no
  * counterpart in the reference.  The split-KV partials go to an 8 MiB array that is part
  * of the library image (each GPU that loads the library holds it until exit); shapes whose
- * partials need more return B200_ELIMIT - for Hq=12, Hkv=2, S=4352 that is B > 79.  No
+ * partials need more return B200_ELIMIT - for Hq=12, Hkv=2, S=4352 that is B > 149.  No
  * cudaMalloc, cudaFree or allocating library call is made.  The first call on a device
  * looks up the array's device address; make that call before any stream capture.  All
  * calls share the array: two calls whose kernels overlap on the GPU (different streams)

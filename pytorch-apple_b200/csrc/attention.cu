@@ -168,7 +168,7 @@ constexpr int DEC_MAX_BLOCKS = 128;  // 16-key blocks per split (split_len <= 20
 constexpr int DEC_STAGES = 3;                  // per-warp cp.async ring depth
 constexpr int DEC_STAGE_BYTES = 2 * 16 * HD * 2;  // 16 keys of K and of V
 constexpr int DEC_SMEM = 4 * DEC_STAGES * DEC_STAGE_BYTES;
-constexpr int DEC_MAX_SPLIT = 256;             // keys per split (mask values of a split are staged in shared memory)
+constexpr int DEC_MAX_SPLIT = 512;             // keys per split (mask values of a split are staged in shared memory)
 
 // Each warp streams its own 16-key blocks through a private 3-stage ring of shared memory
 // filled with cp.async (two blocks, 16 KB, in flight per warp while a third is consumed).
@@ -189,20 +189,10 @@ __global__ void __launch_bounds__(128, 2) attn_decode_kernel(const __grid_consta
   const int64_t s_end = min(p.S, s_begin + p.split_len);
   const int nblk = static_cast<int>((s_end - s_begin + 15) / 16);
 
-  // ---- mask values of this split; which 16-key blocks have at least one unmasked key ----
   if (threadIdx.x < DEC_MAX_BLOCKS / 32) valid[threadIdx.x] = 0u;
   for (int i = threadIdx.x; i < 8 * HD; i += 128) (&s_acc[0][0])[i] = 0.f;
-  __syncthreads();
+  pdl_trigger();
   pdl_wait();   // q, the new cache rows and the mask come from the kernels before this one
-  for (int i = threadIdx.x; i < nblk * 16; i += 128) {
-    const int64_t key = s_begin + i;
-    float mv = 0.f;
-    if (key >= s_end) mv = -INFINITY;
-    else if (p.mask) mv = load_as_f32(p.mask, b * p.mask_bs + key, p.mask_dtype);
-    s_mask[i] = mv;
-    if (mv > MASKED) atomicOr(&valid[i >> 9], 1u << ((i >> 4) & 31));
-  }
-  __syncthreads();
 
   AttnWarp<T> w;
   w.init();
@@ -212,11 +202,6 @@ __global__ void __launch_bounds__(128, 2) attn_decode_kernel(const __grid_consta
   const T* vbase = static_cast<const T*>(p.v) + b * p.kv_bs + hk * p.kv_hs + s_begin * HD;
   const uint32_t ring = smem_u32(dsm) + warp * (DEC_STAGES * DEC_STAGE_BYTES);
 
-  auto is_valid = [&](int blk) { return ((valid[blk >> 5] >> (blk & 31)) & 1u) != 0u; };
-  auto next_valid = [&](int blk) {  // first valid block of this warp at or after blk (stride 4)
-    while (blk < nblk && !is_valid(blk)) blk += 4;
-    return blk;
-  };
   // copy block `blk` (16 keys x 256 B of K and of V) into ring stage `st`
   auto issue = [&](int blk, int st) {
     const uint32_t sk = ring + st * DEC_STAGE_BYTES, sv = sk + 16 * HD * 2;
@@ -231,58 +216,80 @@ __global__ void __launch_bounds__(128, 2) attn_decode_kernel(const __grid_consta
     }
   };
 
-  int fetch = next_valid(warp);   // next block to copy
-  int st_fetch = 0;
-#pragma unroll
-  for (int i = 0; i < DEC_STAGES - 1; ++i) {
-    if (fetch < nblk) { issue(fetch, st_fetch); fetch = next_valid(fetch + 4); }
-    cp_async_commit();
-    st_fetch = (st_fetch + 1) % DEC_STAGES;
+  // The first two blocks of every warp are fetched before the mask has been looked at (they
+  // are almost always needed); this hides the mask scan behind the first copies.
+  int cur = warp < nblk ? warp : -1, nxt = warp + 4 < nblk ? warp + 4 : -1;
+  if (cur >= 0) issue(cur, 0);
+  cp_async_commit();
+  if (nxt >= 0) issue(nxt, 1);
+  cp_async_commit();
+  int st_fetch = 2, st_use = 0;
+
+  // ---- mask values of this split; which 16-key blocks have at least one unmasked key ----
+  __syncthreads();
+  for (int i = threadIdx.x; i < nblk * 16; i += 128) {
+    const int64_t key = s_begin + i;
+    float mv = 0.f;
+    if (key >= s_end) mv = -INFINITY;
+    else if (p.mask) mv = load_as_f32(p.mask, b * p.mask_bs + key, p.mask_dtype);
+    s_mask[i] = mv;
+    if (mv > MASKED) atomicOr(&valid[i >> 9], 1u << ((i >> 4) & 31));
   }
-  int st_use = 0;
-  for (int blk = next_valid(warp); blk < nblk; blk = next_valid(blk + 4)) {
+  __syncthreads();
+
+  auto is_valid = [&](int blk) { return ((valid[blk >> 5] >> (blk & 31)) & 1u) != 0u; };
+  auto next_valid = [&](int blk) {  // first valid block of this warp at or after blk (stride 4)
+    while (blk < nblk && !is_valid(blk)) blk += 4;
+    return blk;
+  };
+  int fetch = next_valid(warp + 8);   // next block to copy
+  while (cur >= 0) {
     cp_async_wait<DEC_STAGES - 2>();
     __syncwarp();   // every lane's copies for this stage have landed; the stage consumed last time is free
-    if (fetch < nblk) { issue(fetch, st_fetch); fetch = next_valid(fetch + 4); }
+    int fetched = -1;
+    if (fetch < nblk) { issue(fetch, st_fetch); fetched = fetch; fetch = next_valid(fetch + 4); }
     cp_async_commit();
     st_fetch = (st_fetch + 1) % DEC_STAGES;
 
-    const uint32_t sk = ring + st_use * DEC_STAGE_BYTES, sv = sk + 16 * HD * 2;
-    uint4 kf[2][4], vf[2][4];
+    if (is_valid(cur)) {
+      const uint32_t sk = ring + st_use * DEC_STAGE_BYTES, sv = sk + 16 * HD * 2;
+      uint4 kf[2][4], vf[2][4];
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {
-      const int r = 8 * j + g;
+      for (int j = 0; j < 2; ++j) {
+        const int r = 8 * j + g;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const int ch = 4 * c + t;
-        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(kf[j][c].x), "=r"(kf[j][c].y), "=r"(kf[j][c].z), "=r"(kf[j][c].w)
-                     : "r"(sk + r * 256 + ((ch ^ (4 * (r & 1))) << 4)));
+        for (int c = 0; c < 4; ++c) {
+          const int ch = 4 * c + t;
+          asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(kf[j][c].x), "=r"(kf[j][c].y), "=r"(kf[j][c].z), "=r"(kf[j][c].w)
+                       : "r"(sk + r * 256 + ((ch ^ (4 * (r & 1))) << 4)));
+        }
       }
+#pragma unroll
+      for (int s = 0; s < 4; ++s) {
+        const int r = 2 * t + (s & 1) + 8 * (s >> 1);
+#pragma unroll
+        for (int a = 0; a < 2; ++a) {
+          const int ch = g + 8 * a;
+          asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(vf[a][s].x), "=r"(vf[a][s].y), "=r"(vf[a][s].z), "=r"(vf[a][s].w)
+                       : "r"(sv + r * 256 + ((ch ^ (2 * t)) << 4)));
+        }
+      }
+      float add[2][4];
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const float mv = s_mask[cur * 16 + 8 * j + 2 * t + e];
+          add[j][e] = mv;
+          add[j][2 + e] = mv;
+        }
+      w.compute(kf, vf, s_begin + static_cast<int64_t>(cur) * 16, s_end, p.scale, add, t);
     }
-#pragma unroll
-    for (int s = 0; s < 4; ++s) {
-      const int r = 2 * t + (s & 1) + 8 * (s >> 1);
-#pragma unroll
-      for (int a = 0; a < 2; ++a) {
-        const int ch = g + 8 * a;
-        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(vf[a][s].x), "=r"(vf[a][s].y), "=r"(vf[a][s].z), "=r"(vf[a][s].w)
-                     : "r"(sv + r * 256 + ((ch ^ (2 * t)) << 4)));
-      }
-    }
-    float add[2][4];
-#pragma unroll
-    for (int j = 0; j < 2; ++j)
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const float mv = s_mask[blk * 16 + 8 * j + 2 * t + e];
-        add[j][e] = mv;
-        add[j][2 + e] = mv;
-      }
-    w.compute(kf, vf, s_begin + static_cast<int64_t>(blk) * 16, s_end, p.scale, add, t);
     st_use = (st_use + 1) % DEC_STAGES;
+    cur = nxt;
+    nxt = fetched;
   }
   cp_async_wait<0>();
-  pdl_trigger();
 
   // ---- merge the four warps (rows 0..7 only: G <= 8 lives in the g half) --------------
   if (t == 0) { s_m[warp][g] = w.m[0]; s_l[warp][g] = w.l[0]; }
@@ -407,6 +414,12 @@ struct DecodePlan { int split_len; int splits; };
 
 static DecodePlan plan_decode(int64_t B, int Hkv, int64_t S) {
   const int64_t want = 2 * 148;  // fixed so that the workspace size does not depend on the device
+  if (B * Hkv * ceil_div(S, 512) >= 4 * 148) {  // plenty of work: longer splits amortise the per-split prologue
+    DecodePlan big;
+    big.split_len = 512;
+    big.splits = static_cast<int>(ceil_div(S, 512));
+    return big;
+  }
   int len = 256;
   while (len > 64 && B * Hkv * ceil_div(S, len) < want) len >>= 1;
   DecodePlan d;

@@ -247,6 +247,7 @@ __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant_
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
+  pdl_trigger();
   pdl_wait();
   const int64_t n_blk = static_cast<int64_t>(blockIdx.x) * SK_ROWS;
   const int64_t k_begin = static_cast<int64_t>(blockIdx.y) * p.k_per_split;
@@ -321,7 +322,6 @@ __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant_
     compute(w1, k + 32);
   }
 
-  pdl_trigger();
   // acc[i][j][2h+e] = partial out[m = 8j + 2t + e][n = n_blk + warp*32 + 16i + g + 8h]
   bool finish = true;
   if (p.splits > 1) {
@@ -504,7 +504,7 @@ extern "C" int b200_linear(const void* A, const void* W, const void* bias, const
                            int64_t workspace_bytes, void* stream) {
   B200_CHECK_ARG(A && W && out && M >= 0 && N > 0 && K > 0, "b200_linear: bad arguments");
   B200_CHECK_ARG(!(epilogue & B200_EPI_SILU_MUL) || aux, "b200_linear: silu_mul epilogue needs aux");
-  B200_CHECK_ARG(!(epilogue & B200_EPI_GLU) || (N % 128 == 0 && !residual && !(epilogue & ~B200_EPI_GLU)),
+  B200_CHECK_ARG(!(epilogue & B200_EPI_GLU) || (N % 128 == 0 && !residual && !(epilogue & ~(B200_EPI_GLU | B200_EPI_W_STATIC))),
                  "b200_linear: the gated epilogue needs N %% 128 == 0 and excludes residual / other epilogues");
   if (M == 0) return B200_OK;
   if (!(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0 && aligned16(A) && aligned16(W)))
@@ -564,7 +564,7 @@ extern "C" int b200_conv2d_nhwc(const void* x, const void* w, const float* bias,
   if (KH == 1 && KW == 1 && sh == 1 && sw == 1 && ph == 0 && pw == 0 && static_cast<int64_t>(N) * Ho * Wo > 64) {
     // a 1x1 stride-1 convolution over channels-last data is a plain GEMM over [N*H*W, C]
     const int64_t rows = static_cast<int64_t>(N) * Ho * Wo;
-    Tc5Args t{x, w, bias, residual, nullptr, y, rows, O, C, C, C, O, O, 0, dtype, B200_F32, epilogue, nullptr, 0};
+    Tc5Args t{x, w, bias, residual, nullptr, y, rows, O, C, C, C, O, O, 0, dtype, B200_F32, epilogue | B200_EPI_W_STATIC, nullptr, 0};
     const int rc = linear_tc5(t, st);
     if (rc != B200_ENOTSUP) return rc;
   }

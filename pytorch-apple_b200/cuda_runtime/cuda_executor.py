@@ -455,6 +455,8 @@ class CUDAExecutor:
         dt = y.dtype
         res, aux = p["residual"], p["aux"]
         epi = (native.EPI_RELU if p["relu"] else 0) | (native.EPI_SILU_MUL if aux is not None else 0) | (native.EPI_GLU if p.get("glu") else 0)
+        if p["w"] in self._weight_tensors or p["w"] in self._prepared:
+            epi |= native.EPI_W_STATIC   # model weight: may be prefetched ahead of the previous kernel's completion
         ws = self._ws["__ws_splitk"] if p["workspace"] else None
         ld = lambda v: (v.strides[0] if v.shape[0] > 1 else v.shape[1]) if v is not None else 0
         plan.launches.append((self._lib.b200_linear, (

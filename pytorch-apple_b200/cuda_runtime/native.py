@@ -22,6 +22,7 @@ DTYPE_BYTES = {"float32": 4, "float16": 2, "bfloat16": 2, "int32": 4, "int64": 8
 EPI_RELU = 1
 EPI_SILU_MUL = 2
 EPI_GLU = 4
+EPI_W_STATIC = 8
 
 
 class Tensor(C.Structure):
