@@ -150,7 +150,7 @@ __device__ __forceinline__ int out_dim(int a, int j, int e, int t) { return 64 *
 // ===========================================================================
 // Decode: one query token, G = Hq / Hkv query heads share each KV head.
 // grid = (splits, Hkv, B), 128 threads.  Partials: acc [B][Hkv][splits][G][HD] fp32,
-// then ml [B][Hkv][splits][G][2] fp32 (max, sum).
+// then ml [B][Hkv][splits][G][2] fp32 (running max in the log2 domain, sum).
 // ===========================================================================
 struct DecodeParams {
   const void* q; const void* k; const void* v; const void* mask;
@@ -169,17 +169,30 @@ constexpr int DEC_STAGES = 3;                  // per-warp cp.async ring depth
 constexpr int DEC_STAGE_BYTES = 2 * 16 * HD * 2;  // 16 keys of K and of V
 constexpr int DEC_SMEM = 4 * DEC_STAGES * DEC_STAGE_BYTES;
 constexpr int DEC_MAX_SPLIT = 512;             // keys per split (mask values of a split are staged in shared memory)
+constexpr int DEC_ACC_PITCH = HD + 4;          // row pitch of the cross-warp accumulator (spreads the heads over banks)
 
+// The decode kernel works on the transposed problem, so that the (at most 8) query heads of a
+// KV group sit on the 8-wide N side of the m16n8k16 MMA and no tensor-core row is wasted:
+//   S^T[16 keys x 8 heads] = K[16 x 128] Q^T        A = K rows from shared memory (ldmatrix),
+//                                                   B = Q^T, 16 registers loaded once;
+//   O^T[128 dims x 8 heads] += V^T[128 x 16] P^T    A = V^T via ldmatrix.trans,
+//                                                   B = P^T, the S^T accumulators transposed
+//                                                       in registers with movmatrix.
+// Thread (g = lane / 4, t = lane % 4) owns heads 2t, 2t+1: scores of keys g and g+8, and
+// output dims 16j+g, 16j+g+8.  Running max and sum are kept in the log2 domain; the sum is
+// a per-thread partial (its keys only) until the end; the output accumulators are rescaled
+// only when some head's running max moved.
+//
 // Each warp streams its own 16-key blocks through a private 3-stage ring of shared memory
 // filled with cp.async (two blocks, 16 KB, in flight per warp while a third is consumed).
-// Rows are stored with an XOR on the 16-byte chunk index chosen so that the fragment reads
-// below are bank-conflict free: K rows use chunk ^ 4*(row&1), V rows chunk ^ 2*((row>>1)&3).
+// 16-byte chunk c of row r is stored at chunk c ^ (r & 7), which makes every ldmatrix
+// (8 rows x 16 bytes, rows 256 bytes apart) bank-conflict free.
 template <typename T>
 __global__ void __launch_bounds__(128, 2) attn_decode_kernel(const __grid_constant__ DecodeParams p) {
-  extern __shared__ __align__(128) uint8_t dsm[];
+  extern __shared__ __align__(1024) uint8_t dsm[];
   __shared__ uint32_t valid[DEC_MAX_BLOCKS / 32];
   __shared__ float s_mask[DEC_MAX_SPLIT];
-  __shared__ float s_acc[8][HD];
+  __shared__ float s_acc[8][DEC_ACC_PITCH];
   __shared__ float s_m[4][8], s_l[4][8];
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
@@ -187,32 +200,47 @@ __global__ void __launch_bounds__(128, 2) attn_decode_kernel(const __grid_consta
   const int64_t b = blockIdx.z;
   const int64_t s_begin = static_cast<int64_t>(split) * p.split_len;
   const int64_t s_end = min(p.S, s_begin + p.split_len);
-  const int nblk = static_cast<int>((s_end - s_begin + 15) / 16);
+  const int n_keys = static_cast<int>(s_end - s_begin);
+  const int nblk = (n_keys + 15) / 16;
 
   if (threadIdx.x < DEC_MAX_BLOCKS / 32) valid[threadIdx.x] = 0u;
-  for (int i = threadIdx.x; i < 8 * HD; i += 128) (&s_acc[0][0])[i] = 0.f;
+  for (int i = threadIdx.x; i < 8 * DEC_ACC_PITCH; i += 128) (&s_acc[0][0])[i] = 0.f;
   pdl_trigger();
   pdl_wait();   // q, the new cache rows and the mask come from the kernels before this one
 
-  AttnWarp<T> w;
-  w.init();
-  const T* qb = static_cast<const T*>(p.q) + b * p.q_bs + static_cast<int64_t>(hk) * p.G * HD;
-  w.load_q(g < p.G ? qb + g * HD : nullptr, (g + 8) < p.G ? qb + (g + 8) * HD : nullptr, t);
-  const T* kbase = static_cast<const T*>(p.k) + b * p.kv_bs + hk * p.kv_hs + s_begin * HD;
-  const T* vbase = static_cast<const T*>(p.v) + b * p.kv_bs + hk * p.kv_hs + s_begin * HD;
+  // ---- per-lane addressing -------------------------------------------------------------
+  // cp.async: lane copies chunk (lane & 15) of rows 2i + (lane >> 4), i = 0..7
+  const int hi = lane >> 4, ch = lane & 15;
+  const uint32_t cp_off = hi * 256 + ((ch ^ hi) << 4);   // chunk ^ (row & 7) = (ch ^ hi) ^ (2i & 7)
+  const T* k_lane = static_cast<const T*>(p.k) + b * p.kv_bs + hk * p.kv_hs + (s_begin + hi) * HD + ch * 8;
+  const T* v_lane = static_cast<const T*>(p.v) + b * p.kv_bs + hk * p.kv_hs + (s_begin + hi) * HD + ch * 8;
+  // ldmatrix: lane supplies one row address of 8x8 matrix (lane >> 3)
+  const int mi = lane >> 3, mr = lane & 7;
+  const uint32_t k_off = (8 * (mi & 1) + mr) * 256 + (((mi >> 1) ^ mr) << 4);   // ^ (ks << 5) selects dims 16ks..16ks+15
+  const uint32_t v_off = (8 * (mi >> 1) + mr) * 256 + (((mi & 1) ^ mr) << 4);   // ^ (j << 5) selects dims 16j..16j+15
   const uint32_t ring = smem_u32(dsm) + warp * (DEC_STAGES * DEC_STAGE_BYTES);
 
   // copy block `blk` (16 keys x 256 B of K and of V) into ring stage `st`
   auto issue = [&](int blk, int st) {
-    const uint32_t sk = ring + st * DEC_STAGE_BYTES, sv = sk + 16 * HD * 2;
-    const int64_t key0 = static_cast<int64_t>(blk) * 16;
+    const uint32_t sk = ring + st * DEC_STAGE_BYTES + cp_off;
+    const T* ks = k_lane + static_cast<int64_t>(blk) * 16 * HD;
+    const T* vs = v_lane + static_cast<int64_t>(blk) * 16 * HD;
+    const int rows_left = n_keys - blk * 16;
+    if (rows_left >= 16) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int idx = i * 32 + lane, r = idx >> 4, ch = idx & 15;
-      const bool ok = s_begin + key0 + r < s_end;
-      const int64_t off = (key0 + r) * HD + ch * 8;
-      cp_async16(sk + r * 256 + ((ch ^ (4 * (r & 1))) << 4), ok ? static_cast<const void*>(kbase + off) : static_cast<const void*>(kbase), ok ? 16 : 0);
-      cp_async16(sv + r * 256 + ((ch ^ (2 * ((r >> 1) & 3))) << 4), ok ? static_cast<const void*>(vbase + off) : static_cast<const void*>(vbase), ok ? 16 : 0);
+      for (int i = 0; i < 8; ++i) {
+        const uint32_t d = (sk ^ (((2 * i) & 7) << 4)) + i * 512;
+        cp_async16(d, ks + i * 2 * HD, 16);
+        cp_async16(d + 16 * HD * 2, vs + i * 2 * HD, 16);
+      }
+    } else {   // rows past the end are zero-filled (their probabilities are zero, but 0 * garbage must stay 0)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const uint32_t d = (sk ^ (((2 * i) & 7) << 4)) + i * 512;
+        const bool ok = 2 * i + hi < rows_left;
+        cp_async16(d, ok ? ks + i * 2 * HD : k_lane, ok ? 16 : 0);
+        cp_async16(d + 16 * HD * 2, ok ? vs + i * 2 * HD : v_lane, ok ? 16 : 0);
+      }
     }
   };
 
@@ -225,17 +253,33 @@ __global__ void __launch_bounds__(128, 2) attn_decode_kernel(const __grid_consta
   cp_async_commit();
   int st_fetch = 2, st_use = 0;
 
-  // ---- mask values of this split; which 16-key blocks have at least one unmasked key ----
+  // Q^T fragments: head g, dims 16ks + 2t, +1 and 16ks + 2t + 8, +9
+  uint32_t qf[8][2];
+  {
+    const T* qr = static_cast<const T*>(p.q) + b * p.q_bs + (static_cast<int64_t>(hk) * p.G + g) * HD + 2 * t;
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      qf[ks][0] = g < p.G ? *reinterpret_cast<const uint32_t*>(qr + 16 * ks) : 0u;
+      qf[ks][1] = g < p.G ? *reinterpret_cast<const uint32_t*>(qr + 16 * ks + 8) : 0u;
+    }
+  }
+
+  // ---- mask values of this split (log2 domain); which 16-key blocks have an unmasked key ----
   __syncthreads();
   for (int i = threadIdx.x; i < nblk * 16; i += 128) {
-    const int64_t key = s_begin + i;
     float mv = 0.f;
-    if (key >= s_end) mv = -INFINITY;
-    else if (p.mask) mv = load_as_f32(p.mask, b * p.mask_bs + key, p.mask_dtype);
-    s_mask[i] = mv;
+    if (i >= n_keys) mv = -INFINITY;
+    else if (p.mask) mv = load_as_f32(p.mask, b * p.mask_bs + s_begin + i, p.mask_dtype);
+    s_mask[i] = mv * LOG2E;
     if (mv > MASKED) atomicOr(&valid[i >> 9], 1u << ((i >> 4) & 31));
   }
   __syncthreads();
+
+  float o[8][4];   // [dim tile j][dims 16j+g (0,1) / 16j+g+8 (2,3)  x  heads 2t (0,2) / 2t+1 (1,3)]
+#pragma unroll
+  for (int j = 0; j < 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+  const float sl = p.scale * LOG2E;
 
   auto is_valid = [&](int blk) { return ((valid[blk >> 5] >> (blk & 31)) & 1u) != 0u; };
   auto next_valid = [&](int blk) {  // first valid block of this warp at or after blk (stride 4)
@@ -253,37 +297,46 @@ __global__ void __launch_bounds__(128, 2) attn_decode_kernel(const __grid_consta
 
     if (is_valid(cur)) {
       const uint32_t sk = ring + st_use * DEC_STAGE_BYTES, sv = sk + 16 * HD * 2;
-      uint4 kf[2][4], vf[2][4];
+      // ---- S^T = K Q^T (two accumulators halve the dependent chain) ----
+      float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        const int r = 8 * j + g;
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          const int ch = 4 * c + t;
-          asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(kf[j][c].x), "=r"(kf[j][c].y), "=r"(kf[j][c].z), "=r"(kf[j][c].w)
-                       : "r"(sk + r * 256 + ((ch ^ (4 * (r & 1))) << 4)));
-        }
+      for (int ks = 0; ks < 8; ks += 2) {
+        uint32_t a0[4], a1[4];
+        ldmatrix_x4(a0, sk + (k_off ^ (ks << 5)));
+        ldmatrix_x4(a1, sk + (k_off ^ ((ks + 1) << 5)));
+        MmaType<T>::mma(sa, a0, qf[ks]);
+        MmaType<T>::mma(sb, a1, qf[ks + 1]);
       }
+      const float mk0 = s_mask[cur * 16 + g], mk1 = s_mask[cur * 16 + g + 8];
+      const float v0 = fmaf(sa[0] + sb[0], sl, mk0), v1 = fmaf(sa[1] + sb[1], sl, mk0);   // key g:   heads 2t, 2t+1
+      const float v2 = fmaf(sa[2] + sb[2], sl, mk1), v3 = fmaf(sa[3] + sb[3], sl, mk1);   // key g+8: heads 2t, 2t+1
+      // ---- online softmax over the 16 keys (lanes that differ in g) ----
+      float mx0 = fmaxf(v0, v2), mx1 = fmaxf(v1, v3);
 #pragma unroll
-      for (int s = 0; s < 4; ++s) {
-        const int r = 2 * t + (s & 1) + 8 * (s >> 1);
-#pragma unroll
-        for (int a = 0; a < 2; ++a) {
-          const int ch = g + 8 * a;
-          asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(vf[a][s].x), "=r"(vf[a][s].y), "=r"(vf[a][s].z), "=r"(vf[a][s].w)
-                       : "r"(sv + r * 256 + ((ch ^ (2 * t)) << 4)));
-        }
+      for (int off = 4; off < 32; off <<= 1) {
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
       }
-      float add[2][4];
+      const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+      if (__any_sync(0xffffffffu, mn0 > m0 || mn1 > m1)) {
+        const float c0 = ex2_approx(m0 - (mn0 == -INFINITY ? 0.f : mn0)), c1 = ex2_approx(m1 - (mn1 == -INFINITY ? 0.f : mn1));
 #pragma unroll
-      for (int j = 0; j < 2; ++j)
+        for (int j = 0; j < 8; ++j) { o[j][0] *= c0; o[j][1] *= c1; o[j][2] *= c0; o[j][3] *= c1; }
+        l0 *= c0; l1 *= c1;
+        m0 = mn0; m1 = mn1;
+      }
+      const float u0 = m0 == -INFINITY ? 0.f : m0, u1 = m1 == -INFINITY ? 0.f : m1;
+      const float p0 = ex2_approx(v0 - u0), p1 = ex2_approx(v1 - u1), p2 = ex2_approx(v2 - u0), p3 = ex2_approx(v3 - u1);
+      l0 += p0 + p2;
+      l1 += p1 + p3;
+      // ---- O^T += V^T P^T ----
+      const uint32_t pb[2] = {movmatrix_trans(pack2<T>(p0, p1)), movmatrix_trans(pack2<T>(p2, p3))};
 #pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const float mv = s_mask[cur * 16 + 8 * j + 2 * t + e];
-          add[j][e] = mv;
-          add[j][2 + e] = mv;
-        }
-      w.compute(kf, vf, s_begin + static_cast<int64_t>(cur) * 16, s_end, p.scale, add, t);
+      for (int j = 0; j < 8; ++j) {
+        uint32_t a[4];
+        ldmatrix_x4_trans(a, sv + (v_off ^ (j << 5)));
+        MmaType<T>::mma(o[j], a, pb);
+      }
     }
     st_use = (st_use + 1) % DEC_STAGES;
     cur = nxt;
@@ -291,31 +344,36 @@ __global__ void __launch_bounds__(128, 2) attn_decode_kernel(const __grid_consta
   }
   cp_async_wait<0>();
 
-  // ---- merge the four warps (rows 0..7 only: G <= 8 lives in the g half) --------------
-  if (t == 0) { s_m[warp][g] = w.m[0]; s_l[warp][g] = w.l[0]; }
+  // ---- merge the four warps ------------------------------------------------------------
+#pragma unroll
+  for (int off = 4; off < 32; off <<= 1) {
+    l0 += __shfl_xor_sync(0xffffffffu, l0, off);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, off);
+  }
+  if (g == 0) { s_m[warp][2 * t] = m0; s_m[warp][2 * t + 1] = m1; s_l[warp][2 * t] = l0; s_l[warp][2 * t + 1] = l1; }
   __syncthreads();
-  float m_all = fmaxf(fmaxf(s_m[0][g], s_m[1][g]), fmaxf(s_m[2][g], s_m[3][g]));
-  const float m_use = m_all == -INFINITY ? 0.f : m_all;
-  const float f = exp2f((w.m[0] - m_use) * LOG2E);
-  if (g < p.G) {
+  {
+    const int h0 = 2 * t, h1 = 2 * t + 1;
+    const float ma0 = fmaxf(fmaxf(s_m[0][h0], s_m[1][h0]), fmaxf(s_m[2][h0], s_m[3][h0]));
+    const float ma1 = fmaxf(fmaxf(s_m[0][h1], s_m[1][h1]), fmaxf(s_m[2][h1], s_m[3][h1]));
+    const float f0 = ex2_approx(m0 - (ma0 == -INFINITY ? 0.f : ma0)), f1 = ex2_approx(m1 - (ma1 == -INFINITY ? 0.f : ma1));
 #pragma unroll
-    for (int a = 0; a < 2; ++a)
-#pragma unroll
-      for (int j = 0; j < 8; ++j)
-#pragma unroll
-        for (int e = 0; e < 2; ++e) atomicAdd(&s_acc[g][out_dim(a, j, e, t)], w.o[a][j][e] * f);
+    for (int j = 0; j < 8; ++j) {
+      if (h0 < p.G) { atomicAdd(&s_acc[h0][16 * j + g], o[j][0] * f0); atomicAdd(&s_acc[h0][16 * j + g + 8], o[j][2] * f0); }
+      if (h1 < p.G) { atomicAdd(&s_acc[h1][16 * j + g], o[j][1] * f1); atomicAdd(&s_acc[h1][16 * j + g + 8], o[j][3] * f1); }
+    }
   }
   __syncthreads();
   const int64_t pidx = ((b * p.Hkv + hk) * p.splits + split) * p.G;
-  for (int i = threadIdx.x; i < p.G * HD; i += 128) p.part_acc[pidx * HD + i] = (&s_acc[0][0])[i];
+  for (int i = threadIdx.x; i < p.G * HD; i += 128) p.part_acc[pidx * HD + i] = s_acc[i >> 7][i & (HD - 1)];
   if (threadIdx.x < p.G) {
     const int r = threadIdx.x;
-    const float mr = fmaxf(fmaxf(s_m[0][r], s_m[1][r]), fmaxf(s_m[2][r], s_m[3][r]));
-    const float mu = mr == -INFINITY ? 0.f : mr;
+    const float mr_ = fmaxf(fmaxf(s_m[0][r], s_m[1][r]), fmaxf(s_m[2][r], s_m[3][r]));
+    const float mu = mr_ == -INFINITY ? 0.f : mr_;
     float lr = 0.f;
 #pragma unroll
-    for (int wi = 0; wi < 4; ++wi) lr += s_l[wi][r] * exp2f((s_m[wi][r] - mu) * LOG2E);
-    p.part_ml[(pidx + r) * 2] = mr;
+    for (int wi = 0; wi < 4; ++wi) lr += s_l[wi][r] * ex2_approx(s_m[wi][r] - mu);
+    p.part_ml[(pidx + r) * 2] = mr_;      // log2 domain
     p.part_ml[(pidx + r) * 2 + 1] = lr;
   }
 }
@@ -335,7 +393,7 @@ __global__ void __launch_bounds__(128) attn_decode_merge_kernel(const float* __r
   float acc = 0.f, l = 0.f;
   for (int s = 0; s < splits; ++s) {
     const int64_t i = (base + s) * G + r;
-    const float f = exp2f((part_ml[i * 2] - m_use) * LOG2E);
+    const float f = ex2_approx(part_ml[i * 2] - m_use);   // maxima are stored in the log2 domain
     l += part_ml[i * 2 + 1] * f;
     acc += part_acc[i * HD + threadIdx.x] * f;
   }

@@ -10,6 +10,8 @@
 #include "gemm_tc5.cuh"
 #include "tc5.cuh"
 
+#include <stdlib.h>
+
 namespace b200 {
 
 __device__ int g_tc5_error = 0;
@@ -25,12 +27,23 @@ constexpr int BM = 128, BK = 64;
 //      rows; the upper half is whatever follows in shared memory and only feeds accumulator
 //      rows that are never stored), which halves the stage size: two CTAs per SM, so the
 //      next GEMM in the stream can already sit on the SM and prefetch its weights.
+//   3  as 2, but one CTA per SM with a ring twice as deep (more bytes in flight per CTA).
 template <int BN, int MODE> struct Cfg {
-  static constexpr int AROWS = MODE == 2 ? 64 : 128;
+  static constexpr int AROWS = MODE >= 2 ? 64 : 128;
   static constexpr int A_STAGE = AROWS * BK * 2;
-  static constexpr int ST = MODE == 0 ? (BN == 128 ? 3 : 4) : MODE == 1 ? (BN == 128 ? 6 : 8) : (BN == 128 ? 4 : 6);
-  static constexpr int CTAS = MODE == 1 ? 1 : 2;
+  static constexpr int ST = MODE == 0 ? (BN == 128 ? 3 : 4) : MODE == 1 ? (BN == 128 ? 6 : 8) : MODE == 2 ? (BN == 128 ? 4 : 6) : (BN == 128 ? 8 : 12);
+  static constexpr int CTAS = (MODE == 1 || MODE == 3) ? 1 : 2;
 };
+
+int env_int(const char* name, int dflt) {
+  const char* e = getenv(name);
+  return e && e[0] ? atoi(e) : dflt;
+}
+// decode (M <= 64) tuning: ring depth / CTAs per SM, and how many CTAs split-K aims for
+int decode_deep() { static int v = env_int("B200NN_TC5_DECODE_DEEP", 0); return v; }
+int split_target() { static int v = env_int("B200NN_TC5_SPLIT_CTAS", 148); return v; }
+int split_traffic_div() { static int v = env_int("B200NN_TC5_SPLIT_TRAFFIC", 8); return v; }
+int split_min_kb() { static int v = env_int("B200NN_TC5_SPLIT_MIN_KB", 4); return v; }
 
 struct Tc5Params {
   const void* bias; const void* residual; const void* aux; void* out;
@@ -556,10 +569,10 @@ Tc5Plan plan_tc5(int64_t M, int64_t N, int64_t K, bool glu = false) {
   const int64_t tiles = pl.tiles_n * tm, KB = ceil_div(K, BK);
   int64_t splits = 1;
   if (tiles < 100) {
-    splits = ceil_div(148, tiles);
-    const int64_t by_traffic = K / (8 * (M < BM ? M : BM));   // partial sums stay well below the weight bytes
+    splits = split_target() == 148 ? ceil_div(148, tiles) : split_target() / tiles;
+    const int64_t by_traffic = K / (split_traffic_div() * (M < BM ? M : BM));   // partial sums stay below the weight bytes
     if (splits > by_traffic) splits = by_traffic;
-    if (splits > KB / 4) splits = KB / 4;                        // at least 4 k-blocks per CTA
+    if (splits > KB / split_min_kb()) splits = KB / split_min_kb();             // at least this many k-blocks per CTA
     if (splits < 1) splits = 1;
   }
   pl.kb_per_split = static_cast<int>(ceil_div(KB, splits));
@@ -694,6 +707,10 @@ int linear_tc5(const Tc5Args& a, cudaStream_t st) {
   if (const int bn = persistent_bn(a.M, a.N, glu)) return dispatch_persistent<false>(bn, a, st, nullptr);
   const Tc5Plan pl = plan_tc5(a.M, a.N, a.K, glu);
   if (pl.tiles_m > 65535 || pl.splits > 65535) return B200_ENOTSUP;
+  if (pl.tiles_m == 1 && a.M <= 64 && decode_deep()) {
+    if (a.dtype == B200_BF16) return pl.bn == 64 ? launch<__nv_bfloat16, 64, false, 3>(a, pl, st) : launch<__nv_bfloat16, 128, false, 3>(a, pl, st);
+    return pl.bn == 64 ? launch<__half, 64, false, 3>(a, pl, st) : launch<__half, 128, false, 3>(a, pl, st);
+  }
   if (pl.tiles_m == 1 && a.M <= 64) {
     if (a.dtype == B200_BF16) return pl.bn == 64 ? launch<__nv_bfloat16, 64, false, 2>(a, pl, st) : launch<__nv_bfloat16, 128, false, 2>(a, pl, st);
     return pl.bn == 64 ? launch<__half, 64, false, 2>(a, pl, st) : launch<__half, 128, false, 2>(a, pl, st);

@@ -760,11 +760,11 @@ class _Lowering:
                     raise ValueError(f"linear epilogue operand {t.name} has dtype {t2.dtype}, expected {dt}")
                 p[key] = t2
                 names.append(tn)
-        if M <= 128:
-            p["workspace"] = "__ws_splitk"
-            names.append("__ws_splitk")
-            self.out.buffers.setdefault("__ws_splitk", BufferAllocation("__ws_splitk", [0], "uint8", 0, persistent=True))
-            p["workspace_key"] = (M, N, K)
+        # split-K scratch (sized by the library for the largest (M, N, K) of the program; shared, self-cleaning)
+        p["workspace"] = "__ws_splitk"
+        names.append("__ws_splitk")
+        self.out.buffers.setdefault("__ws_splitk", BufferAllocation("__ws_splitk", [0], "uint8", 0, persistent=True))
+        p["workspace_key"] = (M, N, K)
         desc = "x @ W^T" + (" + b" if has_bias else "") + (" + residual" if residual is not None else "") + \
                (" -> relu" if relu else "") + (" -> silu(.) * up" if aux is not None else "") + (" -> silu(gate) * up, interleaved rows" if glu else "")
         self.emit(CUBLASStep("gemm", names, out.name, p), names + [out.name])
