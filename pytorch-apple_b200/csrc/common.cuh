@@ -91,6 +91,11 @@ __device__ __forceinline__ float round_to(float v, int dt) {
 }
 template <typename T> __device__ __forceinline__ float round_as(float v) { return to_f32<T>(from_f32<T>(v)); }
 
+// x * sigmoid(x) on the special-function units, branch-free (the IEEE division and expf
+// carry slow-path branches that keep the compiler from interleaving independent elements).
+// The result feeds a 16-bit rounding, which absorbs the ~2^-21 relative error.
+__device__ __forceinline__ float silu_f32(float x) { return __fdividef(x, 1.f + __expf(-x)); }
+
 __device__ __forceinline__ float load_as_f32(const void* p, int64_t i, int dt) {
   switch (dt) {
     case B200_F32: return static_cast<const float*>(p)[i];

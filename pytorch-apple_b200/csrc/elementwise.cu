@@ -136,7 +136,7 @@ template <typename T, int KIND> __device__ __forceinline__ float flat_eval(float
   if (KIND == FLAT_RELU) return a != a ? a : fmaxf(a, 0.f);
   if (KIND == FLAT_ADD) return a + b;
   if (KIND == FLAT_ADD_RELU) { float s = round_as<T>(a + b); return s != s ? s : fmaxf(s, 0.f); }
-  if (KIND == FLAT_SILU_MUL) { float s = round_as<T>(a / (1.f + expf(-a))); return s * b; }
+  if (KIND == FLAT_SILU_MUL) { float s = round_as<T>(silu_f32(a)); return s * b; }
   if (KIND == FLAT_MUL) return a * b;
   if (KIND == FLAT_MUL_S) return a * imm;
   if (KIND == FLAT_ADD_S) return a + imm;

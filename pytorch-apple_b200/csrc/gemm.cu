@@ -8,6 +8,8 @@
 #include "gemm_tc5.cuh"
 #include "mma.cuh"
 
+#include <stdlib.h>
+
 namespace b200 {
 
 // ===========================================================================
@@ -193,8 +195,8 @@ __global__ void __launch_bounds__(256) gemm_tile_kernel(const __grid_constant__ 
         if (p.epilogue & B200_EPI_RELU) { v0 = fmaxf(v0, 0.f); v1 = fmaxf(v1, 0.f); }
         if (p.epilogue & B200_EPI_SILU_MUL) {
           const float s0 = round_as<T>(v0), s1 = round_as<T>(v1);
-          v0 = round_as<T>(s0 / (1.f + expf(-s0))) * to_f32<T>(aux[m * p.ldaux + n]);
-          if (n1) v1 = round_as<T>(s1 / (1.f + expf(-s1))) * to_f32<T>(aux[m * p.ldaux + n + 1]);
+          v0 = round_as<T>(silu_f32(s0)) * to_f32<T>(aux[m * p.ldaux + n]);
+          if (n1) v1 = round_as<T>(silu_f32(s1)) * to_f32<T>(aux[m * p.ldaux + n + 1]);
         }
         T* o = out + m * p.ldo + n;
         if (n1 && ((reinterpret_cast<uintptr_t>(o) & 3u) == 0)) {
@@ -383,7 +385,7 @@ __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant_
     T* __restrict__ og = static_cast<T*>(p.out);
     for (int64_t m = 0; m < p.M; ++m) {
       const float s = round_as<T>(stage[threadIdx.x][m] + bg);
-      og[m * p.ldo + no] = from_f32<T>(round_as<T>(s / (1.f + expf(-s))) * round_as<T>(stage[threadIdx.x + 64][m] + bu));
+      og[m * p.ldo + no] = from_f32<T>(round_as<T>(silu_f32(s)) * round_as<T>(stage[threadIdx.x + 64][m] + bu));
     }
     return;
   }
@@ -400,7 +402,7 @@ __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant_
     if (p.epilogue & B200_EPI_RELU) v = fmaxf(v, 0.f);
     if (p.epilogue & B200_EPI_SILU_MUL) {
       const float s = round_as<T>(v);
-      v = round_as<T>(s / (1.f + expf(-s))) * to_f32<T>(aux[m * p.ldaux + n]);
+      v = round_as<T>(silu_f32(s)) * to_f32<T>(aux[m * p.ldaux + n]);
     }
     out[m * p.ldo + n] = from_f32<T>(v);
   }
@@ -491,7 +493,17 @@ static int64_t skinny_workspace_bytes(int64_t M, int64_t N, int64_t K) {
 
 // Which kernel family serves a linear of M rows: up to 16 rows the register-streaming
 // split-K kernel, above that the tcgen05 tiles (which also split K for narrow outputs).
-static bool prefers_skinny(int64_t M) { return M <= 16; }
+static bool prefers_skinny(int64_t M) {
+  // Rows up to which the mma.sync weight-streaming kernel is tried before the tcgen05 path.
+  // Default 0: the tcgen05 kernel (activation rows padded into its 64-row tile) measured faster
+  // for every decode batch size; the skinny kernel remains the fallback for unaligned operands.
+  static int limit = -1;
+  if (limit < 0) {
+    const char* e = getenv("B200NN_SKINNY_MAX_M");
+    limit = e && e[0] ? atoi(e) : 0;
+  }
+  return M <= limit;
+}
 
 extern "C" int64_t b200_linear_workspace_bytes(int64_t M, int64_t N, int64_t K) {
   const int64_t a = skinny_workspace_bytes(M, N, K), b = linear_tc5_workspace_bytes(M, N, K);

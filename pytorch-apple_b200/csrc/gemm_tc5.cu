@@ -8,6 +8,7 @@
 // apply the epilogue in fp32 and store.  Every barrier wait is bounded: on a timeout the
 // CTA records an error code in `g_tc5_error`, drains its own copies and exits.
 #include "gemm_tc5.cuh"
+#include "mma.cuh"
 #include "tc5.cuh"
 
 #include <stdlib.h>
@@ -44,89 +45,177 @@ int decode_deep() { static int v = env_int("B200NN_TC5_DECODE_DEEP", 0); return 
 int split_target() { static int v = env_int("B200NN_TC5_SPLIT_CTAS", 148); return v; }
 int split_traffic_div() { static int v = env_int("B200NN_TC5_SPLIT_TRAFFIC", 8); return v; }
 int split_min_kb() { static int v = env_int("B200NN_TC5_SPLIT_MIN_KB", 4); return v; }
+int prefer_bn128() { static int v = env_int("B200NN_TC5_PREFER_BN128", 0); return v; }
+
+// Phase time stamps for tuning, compiled in only with -DB200NN_TC5_TRACE (never in the shipped
+// library): every CTA of the one-tile kernel records %globaltimer at fixed points into
+// g_tc5_trace[launch slot][CTA][point]; b200_debug_tc5_trace copies the table to the host.
+#ifdef B200NN_TC5_TRACE
+constexpr int TR_SLOTS = 64, TR_CTAS = 320, TR_N = 14;
+__device__ unsigned long long g_tc5_trace[TR_SLOTS][TR_CTAS][TR_N];
+int g_trace_counter = 0;   // host side: launches so far
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+#define TC5_STAMP(i)                                                                              \
+  do {                                                                                            \
+    const int cta_ = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);              \
+    if (cta_ < TR_CTAS) g_tc5_trace[p.trace_slot][cta_][i] = globaltimer_ns();                   \
+  } while (0)
+#else
+#define TC5_STAMP(i)
+#endif
 
 struct Tc5Params {
   const void* bias; const void* residual; const void* aux; void* out;
-  float* ws;            // split-K partial sums, fp32 [M][ws_pitch]; zero on entry, zero on exit
-  unsigned int* ctr;    // one arrival counter per output tile; zero on entry and exit
-  int64_t M, N, K, ldo, ldr, ldaux, ws_pitch;
+  int64_t M, N, K, ldo, ldr, ldaux;
   int bias_dtype, epilogue, splits, kb_per_split;
   const void* x;   // convolution input (implicit-GEMM mode only)
   Tc5Conv g;
+  int trace_slot;  // used by the tracing build only
 };
 
 template <typename T> struct AbFormat;
 template <> struct AbFormat<__half> { static constexpr int value = 0; };
 template <> struct AbFormat<__nv_bfloat16> { static constexpr int value = 1; };
 
-__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
-}
-__device__ __forceinline__ void epilogue_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
-// bias / residual / activation on 32 consecutive outputs of row m starting at column n, then store
-template <typename T>
-__device__ __forceinline__ void finish_row(const Tc5Params& p, float (&v)[32], int64_t m, int64_t n) {
-  const int cnt = static_cast<int>(p.N - n < 32 ? p.N - n : 32);
-  const T* __restrict__ res = static_cast<const T*>(p.residual);
-  const T* __restrict__ aux = static_cast<const T*>(p.aux);
-  if (p.bias) {
+// The epilogue code runs once or a few times per CTA, so it is written as short rolled loops
+// over 16-column units: straight-line code unrolled over a whole tile row costs more in
+// instruction fetch (cold instruction cache on every SM) than in execution.
+
+// v[i] += bias[n + i]
+template <int CNT>
+__device__ __forceinline__ void add_bias(const Tc5Params& p, float (&v)[CNT], int64_t n, int cnt) {
+  if (!p.bias) return;
+  if (p.bias_dtype == B200_F32) {
+    const float* __restrict__ bp = static_cast<const float*>(p.bias) + n;
 #pragma unroll
-    for (int i = 0; i < 32; ++i) if (i < cnt) v[i] += load_as_f32(p.bias, n + i, p.bias_dtype);
+    for (int i = 0; i < CNT; ++i) if (i < cnt) v[i] += bp[i];
+  } else if (p.bias_dtype == B200_BF16) {
+    const __nv_bfloat16* __restrict__ bp = static_cast<const __nv_bfloat16*>(p.bias) + n;
+#pragma unroll
+    for (int i = 0; i < CNT; ++i) if (i < cnt) v[i] += __bfloat162float(bp[i]);
+  } else if (p.bias_dtype == B200_F16) {
+    const __half* __restrict__ bp = static_cast<const __half*>(p.bias) + n;
+#pragma unroll
+    for (int i = 0; i < CNT; ++i) if (i < cnt) v[i] += __half2float(bp[i]);
+  } else {
+#pragma unroll 1
+    for (int i = 0; i < cnt; ++i) v[i] += load_as_f32(p.bias, n + i, p.bias_dtype);
   }
-  if (res) {
+}
+
+// CNT (8 or 16) consecutive values of row `row` of a [*, ld] matrix of T starting at column n
+template <typename T, int CNT>
+__device__ __forceinline__ void load_cols(const T* __restrict__ base, int64_t ld, int64_t row, int64_t n, int cnt, float (&f)[CNT]) {
+  const T* src = base + row * ld + n;
+  if (cnt == CNT && (reinterpret_cast<uintptr_t>(src) & 15u) == 0) {
 #pragma unroll
-    for (int i = 0; i < 32; ++i) if (i < cnt) v[i] = round_as<T>(v[i]) + to_f32<T>(res[m * p.ldr + n + i]);
+    for (int j = 0; j < CNT / 8; ++j) {
+      float t[8];
+      unpack8<T>(reinterpret_cast<const uint4*>(src)[j], t);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[8 * j + i] = t[i];
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < CNT; ++i) f[i] = i < cnt ? to_f32<T>(src[i]) : 0.f;
+  }
+}
+
+template <typename T, int CNT>
+__device__ __forceinline__ void store_cols(T* __restrict__ dst, const float (&v)[CNT], int cnt) {
+  if (cnt == CNT && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+#pragma unroll
+    for (int j = 0; j < CNT / 8; ++j) {
+      float f[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[i] = v[8 * j + i];
+      reinterpret_cast<uint4*>(dst)[j] = pack8<T>(f);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < CNT; ++i) if (i < cnt) dst[i] = from_f32<T>(v[i]);
+  }
+}
+
+// bias / residual / activation on CNT consecutive outputs of row m starting at column n, then store
+template <typename T, int CNT>
+__device__ __forceinline__ void finish_cols(const Tc5Params& p, float (&v)[CNT], int64_t m, int64_t n) {
+  const int cnt = static_cast<int>(p.N - n < CNT ? p.N - n : CNT);
+  add_bias<CNT>(p, v, n, cnt);
+  if (p.residual) {
+    float r[CNT];
+    load_cols<T, CNT>(static_cast<const T*>(p.residual), p.ldr, m, n, cnt, r);
+#pragma unroll
+    for (int i = 0; i < CNT; ++i) v[i] = round_as<T>(v[i]) + r[i];
   }
   if (p.epilogue & B200_EPI_RELU) {
 #pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = fmaxf(v[i], 0.f);
+    for (int i = 0; i < CNT; ++i) v[i] = fmaxf(v[i], 0.f);
   }
   if (p.epilogue & B200_EPI_SILU_MUL) {
+    float x[CNT];
+    load_cols<T, CNT>(static_cast<const T*>(p.aux), p.ldaux, m, n, cnt, x);
 #pragma unroll
-    for (int i = 0; i < 32; ++i) if (i < cnt) {
-      const float s = round_as<T>(v[i]);
-      v[i] = round_as<T>(s / (1.f + expf(-s))) * to_f32<T>(aux[m * p.ldaux + n + i]);
+    for (int i = 0; i < CNT; ++i) v[i] = round_as<T>(silu_f32(round_as<T>(v[i]))) * x[i];
+  }
+  store_cols<T, CNT>(static_cast<T*>(p.out) + m * p.ldo + n, v, cnt);
+}
+
+// gated-MLP epilogue: CNT gate accumulators (merged columns n_merged..) and the matching up
+// accumulators (merged columns n_merged + 64 ..) of row m -> CNT outputs starting at column n_out
+template <typename T, int CNT>
+__device__ __forceinline__ void finish_glu_cols(const Tc5Params& p, float (&g)[CNT], float (&u)[CNT], int64_t m, int64_t n_merged, int64_t n_out) {
+  add_bias<CNT>(p, g, n_merged, CNT);
+  add_bias<CNT>(p, u, n_merged + 64, CNT);
+#pragma unroll
+  for (int i = 0; i < CNT; ++i) g[i] = round_as<T>(silu_f32(round_as<T>(g[i]))) * round_as<T>(u[i]);
+  store_cols<T, CNT>(static_cast<T*>(p.out) + m * p.ldo + n_out, g, CNT);
+}
+
+// four consecutive outputs of row m starting at column n (split-K final pass)
+template <typename T>
+__device__ __forceinline__ void finish4(const Tc5Params& p, const float4& acc, int64_t m, int64_t n) {
+  float v[4] = {acc.x, acc.y, acc.z, acc.w};
+  const int cnt = static_cast<int>(p.N - n < 4 ? p.N - n : 4);
+  add_bias<4>(p, v, n, cnt);
+  const T* __restrict__ res = static_cast<const T*>(p.residual);
+  const T* __restrict__ aux = static_cast<const T*>(p.aux);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if (i < cnt) {
+      if (res) v[i] = round_as<T>(v[i]) + to_f32<T>(res[m * p.ldr + n + i]);
+      if (p.epilogue & B200_EPI_RELU) v[i] = fmaxf(v[i], 0.f);
+      if (p.epilogue & B200_EPI_SILU_MUL) v[i] = round_as<T>(silu_f32(round_as<T>(v[i]))) * to_f32<T>(aux[m * p.ldaux + n + i]);
     }
   }
   T* o = static_cast<T*>(p.out) + m * p.ldo + n;
-  if (cnt == 32 && (reinterpret_cast<uintptr_t>(o) & 15u) == 0) {
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      float f[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) f[i] = v[8 * j + i];
-      reinterpret_cast<uint4*>(o)[j] = pack8<T>(f);
-    }
+  if (cnt == 4 && (reinterpret_cast<uintptr_t>(o) & 7u) == 0) {
+    *reinterpret_cast<uint2*>(o) = make_uint2(pack2<T>(v[0], v[1]), pack2<T>(v[2], v[3]));
   } else {
 #pragma unroll
-    for (int i = 0; i < 32; ++i) if (i < cnt) o[i] = from_f32<T>(v[i]);
+    for (int i = 0; i < 4; ++i) if (i < cnt) o[i] = from_f32<T>(v[i]);
   }
 }
 
-// gated-MLP epilogue: 32 gate accumulators and the 32 matching up accumulators of row m
+// four gate accumulators and the matching up accumulators of row m (split-K final pass)
 template <typename T>
-__device__ __forceinline__ void finish_glu(const Tc5Params& p, float (&vg)[32], float (&vu)[32], int64_t m, int64_t n_merged, int64_t n_out) {
-  float v[32];
+__device__ __forceinline__ void finish_glu4(const Tc5Params& p, const float4& gate, const float4& up, int64_t m, int64_t n_merged, int64_t n_out) {
+  float g[4] = {gate.x, gate.y, gate.z, gate.w}, u[4] = {up.x, up.y, up.z, up.w};
+  add_bias<4>(p, g, n_merged, 4);
+  add_bias<4>(p, u, n_merged + 64, 4);
 #pragma unroll
-  for (int i = 0; i < 32; ++i) {
-    float g = vg[i], u = vu[i];
-    if (p.bias) { g += load_as_f32(p.bias, n_merged + i, p.bias_dtype); u += load_as_f32(p.bias, n_merged + 64 + i, p.bias_dtype); }
-    const float s = round_as<T>(g);
-    v[i] = round_as<T>(s / (1.f + expf(-s))) * round_as<T>(u);
-  }
+  for (int i = 0; i < 4; ++i) g[i] = round_as<T>(silu_f32(round_as<T>(g[i]))) * round_as<T>(u[i]);
   T* o = static_cast<T*>(p.out) + m * p.ldo + n_out;
-  if ((reinterpret_cast<uintptr_t>(o) & 15u) == 0) {
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      float f[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) f[i] = v[8 * j + i];
-      reinterpret_cast<uint4*>(o)[j] = pack8<T>(f);
-    }
+  if ((reinterpret_cast<uintptr_t>(o) & 7u) == 0) {
+    *reinterpret_cast<uint2*>(o) = make_uint2(pack2<T>(g[0], g[1]), pack2<T>(g[2], g[3]));
   } else {
 #pragma unroll
-    for (int i = 0; i < 32; ++i) o[i] = from_f32<T>(v[i]);
+    for (int i = 0; i < 4; ++i) o[i] = from_f32<T>(g[i]);
   }
 }
 
@@ -150,17 +239,23 @@ __global__ void __launch_bounds__(192, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(cons
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   __shared__ __align__(8) uint64_t full_bar[ST], empty_bar[ST], acc_bar;
   __shared__ uint32_t tmem_holder;
-  __shared__ int failed, is_last;
+  __shared__ int failed;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
   const int KB = static_cast<int>((p.K + BK - 1) / BK);
   const int kb0 = blockIdx.z * p.kb_per_split;
   const int nkb = min(KB, kb0 + p.kb_per_split) - kb0;   // >= 1 by construction of the grid
+  // single-row-tile shapes and split-K stage the accumulator through shared memory (see the end of the kernel)
+  const bool staged = !CONV && (MODE >= 1 || p.splits > 1);   // MODE >= 1: known at compile time, the direct epilogue is dropped
+  const bool glu = (p.epilogue & B200_EPI_GLU) != 0;       // host guarantees BN == 128 and N % 128 == 0
+  const int rows_valid = static_cast<int>(p.M - m0 < BM ? p.M - m0 : BM);
+  constexpr int PART_PITCH = BN + 4;                      // floats; rows 16 bytes apart in bank space
+  float* part = reinterpret_cast<float*>(smem);
 
   if (threadIdx.x == 0) {
+    TC5_STAMP(0);
     failed = 0;
-    is_last = 0;
     for (int s = 0; s < ST; ++s) { tc5::mbar_init(&full_bar[s], CONV ? 129 : 1); tc5::mbar_init(&empty_bar[s], 1); }
     tc5::mbar_init(&acc_bar, 1);
     tc5::fence_barrier_init();
@@ -176,6 +271,7 @@ __global__ void __launch_bounds__(192, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(cons
 
   if (warp == 0) {
     if (lane == 0) {
+      TC5_STAMP(1);
       // Weights that no kernel of this stream writes can be fetched before the predecessor has
       // finished: fill the ring with weight tiles first, then wait, then add the activation tiles.
       int pre = 0;
@@ -187,6 +283,7 @@ __global__ void __launch_bounds__(192, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(cons
         }
       }
       pdl_wait();
+      TC5_STAMP(2);
       int issued = pre;
       for (int i = 0; i < nkb; ++i) {
         const int s = i % ST;
@@ -211,6 +308,7 @@ __global__ void __launch_bounds__(192, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(cons
         const int s = i % ST;
         const uint32_t ph = (i / ST) & 1;
         if (!tc5::mbar_wait(&full_bar[s], ph)) { failed = 1; atomicExch(&g_tc5_error, 2); break; }
+        if (i == 0) TC5_STAMP(3);
         tc5::tc_fence_after();
         const uint32_t a_addr = tc5::smem_addr(smem + s * STAGE), b_addr = a_addr + A_STAGE;
         const uint64_t da = tc5::umma_desc_sw128(a_addr), db = tc5::umma_desc_sw128(b_addr);
@@ -220,6 +318,7 @@ __global__ void __launch_bounds__(192, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(cons
         tc5::umma_commit(&empty_bar[s]);
       }
       tc5::umma_commit(&acc_bar);
+      TC5_STAMP(4);
     }
   } else {
     pdl_wait();   // residual, bias, split-K scratch and convolution inputs come from earlier kernels
@@ -268,80 +367,139 @@ __global__ void __launch_bounds__(192, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(cons
     if (!ok && lane == 0) { failed = 1; atomicExch(&g_tc5_error, 3); }
     ok = ok && !*reinterpret_cast<volatile int*>(&failed);
     ok = __all_sync(0xffffffffu, ok);
+    if (threadIdx.x == 64) TC5_STAMP(5);
     const int64_t m = m0 + q * 32 + lane;
     const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
-    const bool glu = (p.epilogue & B200_EPI_GLU) != 0;  // host guarantees BN == 128 and N % 128 == 0
-    if (ok && glu && p.splits == 1) {
+    if (ok && staged) {
+      // ---- accumulator -> fp32 tile in shared memory (the ring is free: every stage was consumed) ----
+      tc5::tc_fence_after();
+      if (q * 32 < rows_valid) {   // warp-uniform: this lane quarter holds rows that exist
+        float* prow = part + (q * 32 + lane) * PART_PITCH;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 16) {
+          float v[16];
+          tc5::tmem_ld_32x16(t_row + c, v);
+          tc5::tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 4; ++j) *reinterpret_cast<float4*>(prow + c + 4 * j) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+        }
+      }
+      tc5::tc_fence_before();
+    } else if (ok && glu) {
       tc5::tc_fence_after();
 #pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
-        float vg[32], vu[32];
+      for (int c = 0; c < 64; c += 16) {   // gate columns c..c+15 pair with up columns 64+c..
+        float vg[16], vu[16];
         __syncwarp();
-        tc5::tmem_ld_32x32(t_row + c * 32, vg);
-        tc5::tmem_ld_32x32(t_row + 64 + c * 32, vu);
-        if (m < p.M) finish_glu<T>(p, vg, vu, m, n0 + c * 32, n0 / 2 + c * 32);
+        tc5::tmem_ld_32x16(t_row + c, vg);
+        tc5::tmem_ld_32x16(t_row + 64 + c, vu);
+        tc5::tmem_ld_wait();
+        if (m < p.M) finish_glu_cols<T, 16>(p, vg, vu, m, n0 + c, n0 / 2 + c);
       }
       tc5::tc_fence_before();
     } else if (ok) {
       tc5::tc_fence_after();
+      float va[16], vb[16];   // two 16-column units in flight: the next tcgen05.ld runs under the current unit's stores
+      tc5::tmem_ld_32x16(t_row, va);
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        float v[32];
-        __syncwarp();  // tcgen05.ld is warp-collective; lanes that skipped the stores rejoin here
-        tc5::tmem_ld_32x32(t_row + c * 32, v);
-        const int64_t n = n0 + c * 32;
-        if (m >= p.M) continue;
-        if (p.splits == 1) {
-          if (n < p.N) finish_row<T>(p, v, m, n);
-        } else {
-          float* w = p.ws + m * p.ws_pitch + n;
-#pragma unroll
-          for (int j = 0; j < 8; ++j) red_add_v4(w + 4 * j, v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-        }
+      for (int c = 0; c < BN; c += 32) {
+        tc5::tmem_ld_wait();
+        tc5::tmem_ld_32x16(t_row + c + 16, vb);
+        if (m < p.M && n0 + c < p.N) finish_cols<T, 16>(p, va, m, n0 + c);
+        __syncwarp();   // tcgen05.ld is warp-collective; lanes that skipped the stores rejoin here
+        tc5::tmem_ld_wait();
+        if (c + 32 < BN) tc5::tmem_ld_32x16(t_row + c + 32, va);
+        if (m < p.M && n0 + c + 16 < p.N) finish_cols<T, 16>(p, vb, m, n0 + c + 16);
+        __syncwarp();
       }
       tc5::tc_fence_before();
     }
-    if (p.splits > 1) {  // uniform for the whole grid: the four epilogue warps meet on named barrier 1
-      __threadfence();
-      epilogue_bar();
-      if (warp == 2 && lane == 0) {
-        const unsigned int tile = blockIdx.y * gridDim.x + blockIdx.x;
-        const unsigned int ticket = atomicAdd(p.ctr + tile, 1u);
-        is_last = ticket == static_cast<unsigned int>(p.splits) - 1u;
-        if (is_last) p.ctr[tile] = 0u;
-      }
-      epilogue_bar();
-      auto take = [&](int64_t n, float (&v)[32]) {  // read 32 summed partials and leave zeros behind
-        float4* w = reinterpret_cast<float4*>(p.ws + m * p.ws_pitch + n);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const float4 t = __ldcg(w + j);
-          __stcg(w + j, make_float4(0.f, 0.f, 0.f, 0.f));
-          v[4 * j] = t.x; v[4 * j + 1] = t.y; v[4 * j + 2] = t.z; v[4 * j + 3] = t.w;
-        }
-      };
-      if (*reinterpret_cast<volatile int*>(&is_last) && m < p.M && glu) {
-        __threadfence();
+    if (threadIdx.x == 64) TC5_STAMP(6);
+  }
+
+  // ---- staged epilogue: the tile (or, with split-K, this CTA's partial tile) sits in shared
+  // memory as fp32.  The split-K CTAs of one output tile form a thread-block cluster along z:
+  // after a cluster barrier each CTA sums its share of the tile over all ranks through
+  // distributed shared memory, in rank order (deterministic), and finishes those outputs.
+  // No global scratch, no atomics.  Every thread of every CTA takes both cluster barriers.
+  if (staged) {
+    __syncwarp();
+    if (p.splits > 1) tc5::cluster_sync();
+    else __syncthreads();
+    if (threadIdx.x == 64) TC5_STAMP(7);
+    if (!*reinterpret_cast<volatile int*>(&failed)) {
+      if (threadIdx.x == 64) TC5_STAMP(11);
+      // All 192 threads walk the tile as float4 units in row-major order (coalesced stores).  The
+      // loop body is kept short: it runs a handful of times per thread, so its cost is mostly
+      // instruction count, not throughput.
+      constexpr int LOG_UNITS = BN == 64 ? 4 : 5;              // float4 units per tile row (staged tiles are 64 or 128 wide)
+      const int log_pr = glu ? 4 : LOG_UNITS;                  // gated: the 16 units of gate columns, each paired with +64
+      const int total = rows_valid << log_pr;
+      const int nsp = p.splits;
+      const int share = (total + nsp - 1) / nsp;
+      const int rank = nsp > 1 ? static_cast<int>(tc5::cluster_ctarank()) : 0;
+      const int end = min(total, (rank + 1) * share);
+      const uint32_t part_addr = tc5::smem_addr(part);
+      T* const outp = static_cast<T*>(p.out);
+      const T* const resp = static_cast<const T*>(p.residual);
+      const bool relu = (p.epilogue & B200_EPI_RELU) != 0;
+      const int bias_kind = !p.bias ? 0 : p.bias_dtype == B200_F32 ? 1 : p.bias_dtype == AbFormat<T>::value + 1 ? 2 : 3;
+      const bool vec_ok = (reinterpret_cast<uintptr_t>(outp) & 7u) == 0 && (p.ldo & 3) == 0 && bias_kind < 3 &&
+                          (!resp || ((reinterpret_cast<uintptr_t>(resp) & 7u) == 0 && (p.ldr & 3) == 0)) && !(p.epilogue & B200_EPI_SILU_MUL);
+      if (threadIdx.x == 64) TC5_STAMP(12);
 #pragma unroll 1
-        for (int c = 0; c < 2; ++c) {
-          float vg[32], vu[32];
-          take(n0 + c * 32, vg);
-          take(n0 + 64 + c * 32, vu);
-          finish_glu<T>(p, vg, vu, m, n0 + c * 32, n0 / 2 + c * 32);
-        }
-      } else if (*reinterpret_cast<volatile int*>(&is_last) && m < p.M) {
-        __threadfence();
+      for (int idx = rank * share + static_cast<int>(threadIdx.x); idx < end; idx += 192) {
+        const int r = idx >> log_pr, col = (idx & ((1 << log_pr) - 1)) << 2;
+        const uint32_t off = part_addr + static_cast<uint32_t>(r * PART_PITCH + col) * 4u;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f), up = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (nsp == 1) {
+          acc = *reinterpret_cast<const float4*>(part + r * PART_PITCH + col);
+          if (glu) up = *reinterpret_cast<const float4*>(part + r * PART_PITCH + col + 64);
+        } else {
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          const int64_t n = n0 + c * 32;
-          float v[32];
-          take(n, v);
-          if (n < p.N) finish_row<T>(p, v, m, n);
+          for (int sidx = 0; sidx < nsp; ++sidx) {
+            const uint32_t ra = tc5::map_to_rank(off, sidx);
+            const float4 t = tc5::ld_cluster_f4(ra);
+            acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w;
+            if (glu) {
+              const float4 u = tc5::ld_cluster_f4(ra + 256);
+              up.x += u.x; up.y += u.y; up.z += u.z; up.w += u.w;
+            }
+          }
+        }
+        const int64_t mm = static_cast<int64_t>(m0) + r;
+        const int64_t n = static_cast<int64_t>(n0) + col;
+        if (glu) {
+          finish_glu4<T>(p, acc, up, mm, n, n0 / 2 + col);
+        } else if (vec_ok && n + 4 <= p.N) {
+          if (bias_kind == 1) {
+            const float* bp = static_cast<const float*>(p.bias) + n;
+            acc.x += bp[0]; acc.y += bp[1]; acc.z += bp[2]; acc.w += bp[3];
+          } else if (bias_kind == 2) {
+            const T* bp = static_cast<const T*>(p.bias) + n;
+            acc.x += to_f32<T>(bp[0]); acc.y += to_f32<T>(bp[1]); acc.z += to_f32<T>(bp[2]); acc.w += to_f32<T>(bp[3]);
+          }
+          if (resp) {
+            const uint2 raw = *reinterpret_cast<const uint2*>(resp + mm * p.ldr + n);
+            float r0, r1, r2, r3;
+            unpack2<T>(raw.x, r0, r1);
+            unpack2<T>(raw.y, r2, r3);
+            acc.x = round_as<T>(acc.x) + r0; acc.y = round_as<T>(acc.y) + r1; acc.z = round_as<T>(acc.z) + r2; acc.w = round_as<T>(acc.w) + r3;
+          }
+          if (relu) { acc.x = fmaxf(acc.x, 0.f); acc.y = fmaxf(acc.y, 0.f); acc.z = fmaxf(acc.z, 0.f); acc.w = fmaxf(acc.w, 0.f); }
+          *reinterpret_cast<uint2*>(outp + mm * p.ldo + n) = make_uint2(pack2<T>(acc.x, acc.y), pack2<T>(acc.z, acc.w));
+        } else if (n < p.N) {
+          finish4<T>(p, acc, mm, n);
         }
       }
     }
+    if (threadIdx.x == 64) TC5_STAMP(9);
+    __syncwarp();
+    if (p.splits > 1) tc5::cluster_sync();   // nobody leaves while a peer may still read its tile
+    if (threadIdx.x == 64) TC5_STAMP(10);
   }
   __syncthreads();
+  if (threadIdx.x == 0) TC5_STAMP(8);
   if (warp == 1) { tc5::tc_fence_after(); tc5::tmem_dealloc(tmem_base, BN); }
 }
 
@@ -452,24 +610,25 @@ __global__ void __launch_bounds__(CONV ? 320 : 192, 1) gemm_tc5p_kernel(const __
       const uint32_t t_row = tmem_base + b * BN + (static_cast<uint32_t>(q * 32) << 16);
       if (glu) {
 #pragma unroll 1
-        for (int h = 0; h < BN / 128; ++h)
-#pragma unroll 1
-          for (int c = 0; c < 2; ++c) {
-            float vg[32], vu[32];
-            __syncwarp();
-            tc5::tmem_ld_32x32(t_row + h * 128 + c * 32, vg);
-            tc5::tmem_ld_32x32(t_row + h * 128 + 64 + c * 32, vu);
-            const int64_t nm = static_cast<int64_t>(n0) + h * 128 + c * 32;
-            if (m < p.M && nm < p.N) finish_glu<T>(p, vg, vu, m, nm, (static_cast<int64_t>(n0) + h * 128) / 2 + c * 32);
-          }
+        for (int c = 0; c < BN / 2; c += 16) {   // c counts gate columns: block h = c / 64 of 128 merged columns
+          float vg[16], vu[16];
+          const int col = (c >> 6) * 128 + (c & 63);
+          __syncwarp();
+          tc5::tmem_ld_32x16(t_row + col, vg);
+          tc5::tmem_ld_32x16(t_row + col + 64, vu);
+          tc5::tmem_ld_wait();
+          const int64_t nm = static_cast<int64_t>(n0) + col;
+          if (m < p.M && nm < p.N) finish_glu_cols<T, 16>(p, vg, vu, m, nm, (static_cast<int64_t>(n0) + (c >> 6) * 128) / 2 + (c & 63));
+        }
       } else {
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          float v[32];
+        for (int c = 0; c < BN; c += 16) {
+          float v[16];
           __syncwarp();
-          tc5::tmem_ld_32x32(t_row + c * 32, v);
-          const int64_t n = static_cast<int64_t>(n0) + c * 32;
-          if (m < p.M && n < p.N) finish_row<T>(p, v, m, n);
+          tc5::tmem_ld_32x16(t_row + c, v);
+          tc5::tmem_ld_wait();
+          const int64_t n = static_cast<int64_t>(n0) + c;
+          if (m < p.M && n < p.N) finish_cols<T, 16>(p, v, m, n);
         }
       }
       tc5::tc_fence_before();
@@ -556,29 +715,45 @@ bool make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t K, int64
             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-struct Tc5Plan { int bn, splits, kb_per_split; int64_t tiles_n, tiles_m, ws_pitch; };
+struct Tc5Plan { int bn, splits, kb_per_split; int64_t tiles_n, tiles_m; };
 
-Tc5Plan plan_tc5(int64_t M, int64_t N, int64_t K, bool glu = false) {
+constexpr int MAX_SPLITS = 8;   // portable cluster size
+
+Tc5Plan plan_for_bn(int bn, int64_t M, int64_t N, int64_t K) {
   Tc5Plan pl;
   const int64_t tm = ceil_div(M, BM);
-  // 64-wide tiles whenever 128-wide ones would not give every SM a tile (148 SMs; fixed so that
-  // the workspace size does not depend on the device the plan is made on)
-  pl.bn = (!glu && ceil_div(N, 128) * tm < 148) ? 64 : 128;   // the gated epilogue pairs columns c and c+64 of a 128-wide tile
+  pl.bn = bn;
   pl.tiles_n = ceil_div(N, pl.bn);
   pl.tiles_m = tm;
   const int64_t tiles = pl.tiles_n * tm, KB = ceil_div(K, BK);
   int64_t splits = 1;
   if (tiles < 100) {
-    splits = split_target() == 148 ? ceil_div(148, tiles) : split_target() / tiles;
+    // one CTA per SM in the deep decode mode, otherwise two may share an SM
+    splits = (decode_deep() && M <= 64) ? split_target() / tiles : ceil_div(split_target(), tiles);
     const int64_t by_traffic = K / (split_traffic_div() * (M < BM ? M : BM));   // partial sums stay below the weight bytes
     if (splits > by_traffic) splits = by_traffic;
     if (splits > KB / split_min_kb()) splits = KB / split_min_kb();             // at least this many k-blocks per CTA
+    if (splits > MAX_SPLITS) splits = MAX_SPLITS;   // the splits of a tile form one thread-block cluster
     if (splits < 1) splits = 1;
   }
   pl.kb_per_split = static_cast<int>(ceil_div(KB, splits));
   pl.splits = static_cast<int>(ceil_div(KB, pl.kb_per_split));
-  pl.ws_pitch = pl.tiles_n * pl.bn;
   return pl;
+}
+
+Tc5Plan plan_tc5(int64_t M, int64_t N, int64_t K, bool glu = false) {
+  const int64_t tm = ceil_div(M, BM);
+  if (glu) return plan_for_bn(128, M, N, K);   // the gated epilogue pairs columns c and c+64 of a 128-wide tile
+  if (tm == 1 && prefer_bn128()) {
+    // weight streaming: a 128-wide tile re-reads the activations half as often; take it when
+    // split-K can still put (nearly) as many CTAs to work as 64-wide tiles would
+    const Tc5Plan wide = plan_for_bn(128, M, N, K), narrow = plan_for_bn(64, M, N, K);
+    const int64_t cw = wide.tiles_n * wide.splits, cn = narrow.tiles_n * narrow.splits;
+    return cw * 10 >= cn * 8 ? wide : narrow;
+  }
+  // 64-wide tiles whenever 128-wide ones would not give every SM a tile (148 SMs; fixed so that
+  // the workspace size does not depend on the device the plan is made on)
+  return plan_for_bn(ceil_div(N, 128) * tm < 148 ? 64 : 128, M, N, K);
 }
 
 template <typename T, int BN, bool CONV, int MODE = 0>
@@ -600,17 +775,35 @@ int launch(const Tc5Args& a, const Tc5Plan& pl, cudaStream_t st, const Tc5Conv* 
   p.x = a.A;
   p.g = g ? *g : Tc5Conv{};
   p.bias = a.bias; p.residual = a.residual; p.aux = a.aux; p.out = a.out;
-  p.M = a.M; p.N = a.N; p.K = a.K; p.ldo = a.ldo; p.ldr = a.ldr; p.ldaux = a.ldaux; p.ws_pitch = pl.ws_pitch;
+  p.M = a.M; p.N = a.N; p.K = a.K; p.ldo = a.ldo; p.ldr = a.ldr; p.ldaux = a.ldaux;
   p.bias_dtype = a.bias_dtype; p.epilogue = a.epilogue; p.splits = pl.splits; p.kb_per_split = pl.kb_per_split;
-  p.ws = nullptr; p.ctr = nullptr;
-  if (pl.splits > 1) {
-    const int64_t need = a.M * pl.ws_pitch * 4 + pl.tiles_n * pl.tiles_m * 4 + 256;
-    if (!a.workspace || a.workspace_bytes < need || !aligned16(a.workspace)) return B200_ENOTSUP;
-    p.ws = static_cast<float*>(a.workspace);
-    p.ctr = reinterpret_cast<unsigned int*>(static_cast<uint8_t*>(a.workspace) + a.M * pl.ws_pitch * 4);
+  p.trace_slot = 0;
+#ifdef B200NN_TC5_TRACE
+  p.trace_slot = g_trace_counter++ % TR_SLOTS;
+#endif
+  if (CONV && pl.splits != 1) return B200_ENOTSUP;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(pl.tiles_n), static_cast<unsigned>(pl.tiles_m), static_cast<unsigned>(pl.splits));
+  cfg.blockDim = dim3(192);
+  cfg.dynamicSmemBytes = SMEM;
+  cfg.stream = st;
+  cudaLaunchAttribute attrs[2];
+  int n_attrs = 0;
+  if (pdl_enabled()) {
+    attrs[n_attrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[n_attrs].val.programmaticStreamSerializationAllowed = 1;
+    ++n_attrs;
   }
-  dim3 grid(static_cast<unsigned>(pl.tiles_n), static_cast<unsigned>(pl.tiles_m), static_cast<unsigned>(pl.splits));
-  launch_pdl(gemm_tc5_kernel<T, BN, CONV, MODE>, grid, dim3(192), SMEM, st, ma, mw, p);
+  if (pl.splits > 1) {   // the split-K CTAs of one tile exchange partial sums through distributed shared memory
+    attrs[n_attrs].id = cudaLaunchAttributeClusterDimension;
+    attrs[n_attrs].val.clusterDim.x = 1;
+    attrs[n_attrs].val.clusterDim.y = 1;
+    attrs[n_attrs].val.clusterDim.z = static_cast<unsigned>(pl.splits);
+    ++n_attrs;
+  }
+  cfg.attrs = attrs;
+  cfg.numAttrs = n_attrs;
+  cudaLaunchKernelEx(&cfg, gemm_tc5_kernel<T, BN, CONV, MODE>, ma, mw, p);
   B200_CHECK_LAUNCH("gemm_tc5_kernel");
   return B200_OK;
 }
@@ -632,11 +825,11 @@ int launch_persistent(const Tc5Args& a, cudaStream_t st, const Tc5Conv* g = null
   else if (!make_map(&ma, a.A, a.M, a.K, a.lda, BM, a.dtype)) return B200_ENOTSUP;
   Tc5Params p;
   p.bias = a.bias; p.residual = a.residual; p.aux = a.aux; p.out = a.out;
-  p.M = a.M; p.N = a.N; p.K = a.K; p.ldo = a.ldo; p.ldr = a.ldr; p.ldaux = a.ldaux; p.ws_pitch = 0;
+  p.M = a.M; p.N = a.N; p.K = a.K; p.ldo = a.ldo; p.ldr = a.ldr; p.ldaux = a.ldaux;
   p.bias_dtype = a.bias_dtype; p.epilogue = a.epilogue; p.splits = 1; p.kb_per_split = static_cast<int>(ceil_div(a.K, BK));
-  p.ws = nullptr; p.ctr = nullptr;
   p.x = a.A;
   p.g = g ? *g : Tc5Conv{};
+  p.trace_slot = 0;
   const int64_t tiles_m = ceil_div(a.M, BM), tiles = tiles_m * ceil_div(a.N, BN);
   if (tiles >= (1ll << 31)) return B200_ENOTSUP;
   const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
@@ -684,18 +877,8 @@ bool tc5_enabled() {
   return state == 1;
 }
 
-int64_t linear_tc5_workspace_bytes(int64_t M, int64_t N, int64_t K) {
-  if (M <= 0 || N <= 0 || K <= 0) return 0;
-  int64_t need = 0;
-  for (int glu = 0; glu < 2; ++glu) {  // the caller does not say which epilogue it will ask for
-    if (glu && N % 128) continue;
-    const Tc5Plan pl = plan_tc5(M, N, K, glu != 0);
-    if (pl.splits <= 1) continue;
-    const int64_t b = M * pl.ws_pitch * 4 + pl.tiles_n * pl.tiles_m * 4 + 256;
-    need = b > need ? b : need;
-  }
-  return need;
-}
+// The tcgen05 path needs no global scratch: split-K partial sums meet in distributed shared memory.
+int64_t linear_tc5_workspace_bytes(int64_t, int64_t, int64_t) { return 0; }
 
 int linear_tc5(const Tc5Args& a, cudaStream_t st) {
   if (!tc5_enabled()) return B200_ENOTSUP;
@@ -735,13 +918,18 @@ int conv_tc5(const Tc5Args& a, const Tc5Conv& g, cudaStream_t st) {
   pl.tiles_m = ceil_div(a.M, BM);
   pl.splits = 1;
   pl.kb_per_split = static_cast<int>(a.K / BK);
-  pl.ws_pitch = pl.tiles_n * pl.bn;
   if (pl.tiles_m > 65535) return B200_ENOTSUP;
   if (a.dtype == B200_BF16) return pl.bn == 64 ? launch<__nv_bfloat16, 64, true, 0>(a, pl, st, &g) : launch<__nv_bfloat16, 128, true, 0>(a, pl, st, &g);
   return pl.bn == 64 ? launch<__half, 64, true, 0>(a, pl, st, &g) : launch<__half, 128, true, 0>(a, pl, st, &g);
 }
 
 }  // namespace b200
+
+#ifdef B200NN_TC5_TRACE
+extern "C" int b200_debug_tc5_trace(unsigned long long* host_out) {
+  return cudaMemcpyFromSymbol(host_out, b200::g_tc5_trace, sizeof(unsigned long long) * b200::TR_SLOTS * b200::TR_CTAS * b200::TR_N) == cudaSuccess ? B200_OK : B200_ELAUNCH;
+}
+#endif
 
 extern "C" int b200_debug_device_error(int* code, int clear) {
   int v = 0;

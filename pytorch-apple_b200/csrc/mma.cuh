@@ -65,4 +65,15 @@ template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, f
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
+// inverse of pack2
+template <typename T> __device__ __forceinline__ void unpack2(uint32_t raw, float& lo, float& hi);
+template <> __device__ __forceinline__ void unpack2<__half>(uint32_t raw, float& lo, float& hi) {
+  const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&raw));
+  lo = f.x; hi = f.y;
+}
+template <> __device__ __forceinline__ void unpack2<__nv_bfloat16>(uint32_t raw, float& lo, float& hi) {
+  lo = __uint_as_float(raw << 16);
+  hi = __uint_as_float(raw & 0xffff0000u);
+}
+
 }  // namespace b200
