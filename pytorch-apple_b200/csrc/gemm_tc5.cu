@@ -32,8 +32,13 @@ constexpr int BM = 128, BK = 64;
 template <int BN, int MODE> struct Cfg {
   static constexpr int AROWS = MODE >= 2 ? 64 : 128;
   static constexpr int A_STAGE = AROWS * BK * 2;
-  static constexpr int ST = MODE == 0 ? (BN == 128 ? 3 : 4) : MODE == 1 ? (BN == 128 ? 6 : 8) : MODE == 2 ? (BN == 128 ? 4 : 6) : (BN == 128 ? 8 : 12);
+  static constexpr int ST = MODE == 0 ? (BN == 128 ? 3 : 4) : MODE == 1 ? (BN == 128 ? 4 : 6) : MODE == 2 ? (BN == 128 ? 4 : 6) : (BN == 128 ? 7 : 12);
   static constexpr int CTAS = (MODE == 1 || MODE == 3) ? 1 : 2;
+  static constexpr int RING = ST * (A_STAGE + BN * BK * 2);
+  // split-K only: fp32 receive buffer for the partial-tile rows this CTA owns, one slot per
+  // cluster rank, behind the ring (peers write into it while this CTA may still be computing)
+  static constexpr int RECV_ROWS = (MODE >= 2 ? 64 : 128) + 8;
+  static constexpr int RECV = RECV_ROWS * (BN + 4) * 4;
 };
 
 int env_int(const char* name, int dflt) {
@@ -43,8 +48,8 @@ int env_int(const char* name, int dflt) {
 // decode (M <= 64) tuning: ring depth / CTAs per SM, and how many CTAs split-K aims for
 int decode_deep() { static int v = env_int("B200NN_TC5_DECODE_DEEP", 0); return v; }
 int split_target() { static int v = env_int("B200NN_TC5_SPLIT_CTAS", 148); return v; }
-int split_traffic_div() { static int v = env_int("B200NN_TC5_SPLIT_TRAFFIC", 8); return v; }
-int split_min_kb() { static int v = env_int("B200NN_TC5_SPLIT_MIN_KB", 4); return v; }
+int split_traffic_div() { static int v = env_int("B200NN_TC5_SPLIT_TRAFFIC", 2); return v; }
+int split_min_kb() { static int v = env_int("B200NN_TC5_SPLIT_MIN_KB", 2); return v; }
 int prefer_bn128() { static int v = env_int("B200NN_TC5_PREFER_BN128", 0); return v; }
 
 // Phase time stamps for tuning, compiled in only with -DB200NN_TC5_TRACE (never in the shipped
@@ -251,7 +256,13 @@ __global__ void __launch_bounds__(192, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(cons
   const bool glu = (p.epilogue & B200_EPI_GLU) != 0;       // host guarantees BN == 128 and N % 128 == 0
   const int rows_valid = static_cast<int>(p.M - m0 < BM ? p.M - m0 : BM);
   constexpr int PART_PITCH = BN + 4;                      // floats; rows 16 bytes apart in bank space
-  float* part = reinterpret_cast<float*>(smem);
+  // fp32 staging tile: the ring itself without split-K (it is free once the last MMA has completed);
+  // with split-K the receive buffer behind the ring.  Rows are handed out to the cluster ranks in
+  // blocks of `rpo`; slot s of a CTA's buffer holds rank s's partial sums for the rows it owns.
+  const int nsp = p.splits;
+  float* part = reinterpret_cast<float*>(nsp > 1 ? smem + Cfg<BN, MODE>::RING : smem);
+  const int rpo = (rows_valid + nsp - 1) / nsp;
+  const int rank = nsp > 1 ? static_cast<int>(tc5::cluster_ctarank()) : 0;
 
   if (threadIdx.x == 0) {
     TC5_STAMP(0);
@@ -269,19 +280,22 @@ __global__ void __launch_bounds__(192, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(cons
   const uint32_t tmem_base = tmem_holder;
   pdl_trigger();   // the next kernel in the stream may be scheduled (it waits for this one before reading)
 
+  // Weights that no kernel of this stream writes can be fetched before the predecessor has
+  // finished: fill the ring with weight tiles first, then wait, then add the activation tiles.
+  const int pre = (!CONV && (p.epilogue & B200_EPI_W_STATIC)) ? (nkb < ST ? nkb : ST) : 0;
+  if (threadIdx.x == 0) {
+    TC5_STAMP(1);
+    for (int i = 0; i < pre; ++i) {
+      tc5::mbar_arrive_expect_tx(&full_bar[i], STAGE);
+      tc5::tma_load_2d(smem + i * STAGE + A_STAGE, &map_w, &full_bar[i], (kb0 + i) * BK, n0);
+    }
+  }
+  // Every CTA of the cluster is running before any of them writes into a peer's shared memory.
+  // This barrier sits in the part of the kernel that overlaps the predecessor, so it costs nothing.
+  if (nsp > 1) { __syncwarp(); tc5::cluster_sync(); }
+
   if (warp == 0) {
     if (lane == 0) {
-      TC5_STAMP(1);
-      // Weights that no kernel of this stream writes can be fetched before the predecessor has
-      // finished: fill the ring with weight tiles first, then wait, then add the activation tiles.
-      int pre = 0;
-      if (!CONV && (p.epilogue & B200_EPI_W_STATIC)) {
-        pre = nkb < ST ? nkb : ST;
-        for (int i = 0; i < pre; ++i) {
-          tc5::mbar_arrive_expect_tx(&full_bar[i], STAGE);
-          tc5::tma_load_2d(smem + i * STAGE + A_STAGE, &map_w, &full_bar[i], (kb0 + i) * BK, n0);
-        }
-      }
       pdl_wait();
       TC5_STAMP(2);
       int issued = pre;
@@ -371,17 +385,24 @@ __global__ void __launch_bounds__(192, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(cons
     const int64_t m = m0 + q * 32 + lane;
     const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
     if (ok && staged) {
-      // ---- accumulator -> fp32 tile in shared memory (the ring is free: every stage was consumed) ----
+      // ---- accumulator row -> fp32 staging buffer of the CTA that owns the row ----
       tc5::tc_fence_after();
       if (q * 32 < rows_valid) {   // warp-uniform: this lane quarter holds rows that exist
-        float* prow = part + (q * 32 + lane) * PART_PITCH;
+        const int r = q * 32 + lane;
+        const bool row_ok = r < rows_valid;
+        const int owner = row_ok ? r / rpo : 0, lr = r - owner * rpo;
+        uint32_t dst = tc5::smem_addr(part + (rank * rpo + lr) * PART_PITCH);
+        if (nsp > 1) dst = tc5::map_to_rank(dst, owner);
 #pragma unroll 1
         for (int c = 0; c < BN; c += 16) {
           float v[16];
+          __syncwarp();
           tc5::tmem_ld_32x16(t_row + c, v);
           tc5::tmem_ld_wait();
+          if (row_ok) {
 #pragma unroll
-          for (int j = 0; j < 4; ++j) *reinterpret_cast<float4*>(prow + c + 4 * j) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            for (int j = 0; j < 4; ++j) tc5::st_cluster_f4(dst + (c + 4 * j) * 4, v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+          }
         }
       }
       tc5::tc_fence_before();
@@ -417,57 +438,48 @@ __global__ void __launch_bounds__(192, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(cons
     if (threadIdx.x == 64) TC5_STAMP(6);
   }
 
-  // ---- staged epilogue: the tile (or, with split-K, this CTA's partial tile) sits in shared
-  // memory as fp32.  The split-K CTAs of one output tile form a thread-block cluster along z:
-  // after a cluster barrier each CTA sums its share of the tile over all ranks through
-  // distributed shared memory, in rank order (deterministic), and finishes those outputs.
-  // No global scratch, no atomics.  Every thread of every CTA takes both cluster barriers.
+  // ---- staged epilogue.  The split-K CTAs of one output tile form a thread-block cluster along
+  // z.  Every accumulator row has been written, as fp32, into the staging buffer of the CTA that
+  // owns the row (remote shared-memory stores for the other ranks' rows); after ONE cluster
+  // barrier each CTA sums the slots of its rows in rank order (deterministic) from its own shared
+  // memory and finishes those outputs with coalesced stores.  No global scratch, no atomics;
+  // after the barrier nobody touches a peer's memory, so CTAs may exit independently.
   if (staged) {
     __syncwarp();
-    if (p.splits > 1) tc5::cluster_sync();
+    if (nsp > 1) tc5::cluster_sync();
     else __syncthreads();
     if (threadIdx.x == 64) TC5_STAMP(7);
     if (!*reinterpret_cast<volatile int*>(&failed)) {
-      if (threadIdx.x == 64) TC5_STAMP(11);
-      // All 192 threads walk the tile as float4 units in row-major order (coalesced stores).  The
-      // loop body is kept short: it runs a handful of times per thread, so its cost is mostly
-      // instruction count, not throughput.
+      // All 192 threads walk the owned rows as float4 units in row-major order.  The loop body is
+      // kept short: it runs a handful of times per thread, so its cost is instruction count.
       constexpr int LOG_UNITS = BN == 64 ? 4 : 5;              // float4 units per tile row (staged tiles are 64 or 128 wide)
       const int log_pr = glu ? 4 : LOG_UNITS;                  // gated: the 16 units of gate columns, each paired with +64
-      const int total = rows_valid << log_pr;
-      const int nsp = p.splits;
-      const int share = (total + nsp - 1) / nsp;
-      const int rank = nsp > 1 ? static_cast<int>(tc5::cluster_ctarank()) : 0;
-      const int end = min(total, (rank + 1) * share);
-      const uint32_t part_addr = tc5::smem_addr(part);
+      const int my_rows = max(0, min(rpo, rows_valid - rank * rpo));
+      const int total = my_rows << log_pr;
+      const int slot = rpo * PART_PITCH;                       // floats between the slots of two ranks
       T* const outp = static_cast<T*>(p.out);
       const T* const resp = static_cast<const T*>(p.residual);
       const bool relu = (p.epilogue & B200_EPI_RELU) != 0;
       const int bias_kind = !p.bias ? 0 : p.bias_dtype == B200_F32 ? 1 : p.bias_dtype == AbFormat<T>::value + 1 ? 2 : 3;
       const bool vec_ok = (reinterpret_cast<uintptr_t>(outp) & 7u) == 0 && (p.ldo & 3) == 0 && bias_kind < 3 &&
                           (!resp || ((reinterpret_cast<uintptr_t>(resp) & 7u) == 0 && (p.ldr & 3) == 0)) && !(p.epilogue & B200_EPI_SILU_MUL);
-      if (threadIdx.x == 64) TC5_STAMP(12);
 #pragma unroll 1
-      for (int idx = rank * share + static_cast<int>(threadIdx.x); idx < end; idx += 192) {
-        const int r = idx >> log_pr, col = (idx & ((1 << log_pr) - 1)) << 2;
-        const uint32_t off = part_addr + static_cast<uint32_t>(r * PART_PITCH + col) * 4u;
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f), up = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (nsp == 1) {
-          acc = *reinterpret_cast<const float4*>(part + r * PART_PITCH + col);
-          if (glu) up = *reinterpret_cast<const float4*>(part + r * PART_PITCH + col + 64);
-        } else {
+      for (int idx = static_cast<int>(threadIdx.x); idx < total; idx += 192) {
+        const int lr = idx >> log_pr, col = (idx & ((1 << log_pr) - 1)) << 2;
+        const float* src = part + lr * PART_PITCH + col;
+        float4 acc = *reinterpret_cast<const float4*>(src), up = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (glu) up = *reinterpret_cast<const float4*>(src + 64);
 #pragma unroll 1
-          for (int sidx = 0; sidx < nsp; ++sidx) {
-            const uint32_t ra = tc5::map_to_rank(off, sidx);
-            const float4 t = tc5::ld_cluster_f4(ra);
-            acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w;
-            if (glu) {
-              const float4 u = tc5::ld_cluster_f4(ra + 256);
-              up.x += u.x; up.y += u.y; up.z += u.z; up.w += u.w;
-            }
+        for (int s = 1; s < nsp; ++s) {
+          src += slot;
+          const float4 t = *reinterpret_cast<const float4*>(src);
+          acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w;
+          if (glu) {
+            const float4 u = *reinterpret_cast<const float4*>(src + 64);
+            up.x += u.x; up.y += u.y; up.z += u.z; up.w += u.w;
           }
         }
-        const int64_t mm = static_cast<int64_t>(m0) + r;
+        const int64_t mm = static_cast<int64_t>(m0) + rank * rpo + lr;
         const int64_t n = static_cast<int64_t>(n0) + col;
         if (glu) {
           finish_glu4<T>(p, acc, up, mm, n, n0 / 2 + col);
@@ -494,9 +506,6 @@ __global__ void __launch_bounds__(192, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(cons
       }
     }
     if (threadIdx.x == 64) TC5_STAMP(9);
-    __syncwarp();
-    if (p.splits > 1) tc5::cluster_sync();   // nobody leaves while a peer may still read its tile
-    if (threadIdx.x == 64) TC5_STAMP(10);
   }
   __syncthreads();
   if (threadIdx.x == 0) TC5_STAMP(8);
@@ -728,8 +737,8 @@ Tc5Plan plan_for_bn(int bn, int64_t M, int64_t N, int64_t K) {
   const int64_t tiles = pl.tiles_n * tm, KB = ceil_div(K, BK);
   int64_t splits = 1;
   if (tiles < 100) {
-    // one CTA per SM in the deep decode mode, otherwise two may share an SM
-    splits = (decode_deep() && M <= 64) ? split_target() / tiles : ceil_div(split_target(), tiles);
+    // a split-K CTA carries ring + receive buffer, so one fits per SM: never more CTAs than SMs
+    splits = split_target() / tiles;
     const int64_t by_traffic = K / (split_traffic_div() * (M < BM ? M : BM));   // partial sums stay below the weight bytes
     if (splits > by_traffic) splits = by_traffic;
     if (splits > KB / split_min_kb()) splits = KB / split_min_kb();             // at least this many k-blocks per CTA
@@ -757,16 +766,47 @@ Tc5Plan plan_tc5(int64_t M, int64_t N, int64_t K, bool glu = false) {
 }
 
 template <typename T, int BN, bool CONV, int MODE = 0>
-int launch(const Tc5Args& a, const Tc5Plan& pl, cudaStream_t st, const Tc5Conv* g = nullptr) {
-  constexpr int SMEM = Cfg<BN, MODE>::ST * (Cfg<BN, MODE>::A_STAGE + BN * BK * 2) + 1024;
+int launch(const Tc5Args& a, const Tc5Plan& plan, cudaStream_t st, const Tc5Conv* g = nullptr) {
+  Tc5Plan pl = plan;
+  constexpr int SMEM_RING = Cfg<BN, MODE>::RING + 1024, SMEM_SPLIT = SMEM_RING + Cfg<BN, MODE>::RECV;
+  static_assert(SMEM_SPLIT <= 227 * 1024, "ring + receive buffer exceed the shared memory of an SM");
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(gemm_tc5_kernel<T, BN, CONV, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) {
+    if (cudaFuncSetAttribute(gemm_tc5_kernel<T, BN, CONV, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_SPLIT) != cudaSuccess) {
       cudaGetLastError();
       return B200_ENOTSUP;
     }
     configured = true;
   }
+  // The clusters of one launch should all be resident at once (a second wave would double the
+  // time of these short kernels).  How many clusters of a given size fit depends on how the SMs
+  // are grouped, so ask the runtime, once per cluster size, and shrink the split until they fit.
+  if (pl.splits > 1) {
+    static int fit[MAX_SPLITS + 1] = {0};
+    const int64_t tiles = pl.tiles_n * pl.tiles_m;
+    int splits = pl.splits;
+    for (; splits > 1; --splits) {
+      if (fit[splits] == 0) {
+        cudaLaunchConfig_t q = {};
+        q.gridDim = dim3(static_cast<unsigned>(pl.tiles_n), static_cast<unsigned>(pl.tiles_m), static_cast<unsigned>(splits));
+        q.blockDim = dim3(192);
+        q.dynamicSmemBytes = SMEM_SPLIT;
+        cudaLaunchAttribute ca;
+        ca.id = cudaLaunchAttributeClusterDimension;
+        ca.val.clusterDim.x = 1; ca.val.clusterDim.y = 1; ca.val.clusterDim.z = static_cast<unsigned>(splits);
+        q.attrs = &ca;
+        q.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, gemm_tc5_kernel<T, BN, CONV, MODE>, &q) != cudaSuccess) { cudaGetLastError(); n = -1; }
+        fit[splits] = n > 0 ? n : -1;
+      }
+      if (fit[splits] >= tiles) break;
+    }
+    const int64_t KB = ceil_div(a.K, BK);
+    pl.kb_per_split = static_cast<int>(ceil_div(KB, splits));
+    pl.splits = static_cast<int>(ceil_div(KB, pl.kb_per_split));
+  }
+  const int SMEM = pl.splits > 1 ? SMEM_SPLIT : SMEM_RING;
   CUtensorMap ma, mw;
   if (!make_map(&mw, a.W, a.N, a.K, a.ldw, BN, a.dtype)) return B200_ENOTSUP;
   if (CONV) ma = mw;   // unused in implicit-GEMM mode
