@@ -13,6 +13,8 @@
 // for the second MMA, as the unfused graph rounds the probabilities.
 #include "mma.cuh"
 
+#include <stdlib.h>
+
 namespace b200 {
 
 constexpr int HD = 128;          // head dim
@@ -161,13 +163,29 @@ struct DecodeParams {
   int split_len, splits;
   float scale;
   int mask_dtype;
+  int l2_ahead;   // blocks per warp requested into L2 ahead of the shared-memory ring
 };
 
 constexpr int DEC_MAX_BLOCKS = 128;  // 16-key blocks per split (split_len <= 2048)
 
-constexpr int DEC_STAGES = 3;                  // per-warp cp.async ring depth
+// Phase time stamps for tuning, compiled in only with -DB200NN_TC5_TRACE (never in the shipped library).
+#ifdef B200NN_TC5_TRACE
+constexpr int ATR_CTAS = 1280, ATR_N = 8;
+__device__ unsigned long long g_attn_trace[ATR_CTAS][ATR_N];
+#define ATTN_STAMP(i)                                                                                   \
+  do {                                                                                                  \
+    const int cta_ = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);                    \
+    if (threadIdx.x == 0 && cta_ < ATR_CTAS) {                                                          \
+      unsigned long long t_;                                                                            \
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                            \
+      g_attn_trace[cta_][i] = t_;                                                                       \
+    }                                                                                                   \
+  } while (0)
+#else
+#define ATTN_STAMP(i)
+#endif
+
 constexpr int DEC_STAGE_BYTES = 2 * 16 * HD * 2;  // 16 keys of K and of V
-constexpr int DEC_SMEM = 4 * DEC_STAGES * DEC_STAGE_BYTES;
 constexpr int DEC_MAX_SPLIT = 512;             // keys per split (mask values of a split are staged in shared memory)
 constexpr int DEC_ACC_PITCH = HD + 4;          // row pitch of the cross-warp accumulator (spreads the heads over banks)
 
@@ -183,16 +201,21 @@ constexpr int DEC_ACC_PITCH = HD + 4;          // row pitch of the cross-warp ac
 // a per-thread partial (its keys only) until the end; the output accumulators are rescaled
 // only when some head's running max moved.
 //
-// Each warp streams its own 16-key blocks through a private 3-stage ring of shared memory
-// filled with cp.async (two blocks, 16 KB, in flight per warp while a third is consumed).
-// 16-byte chunk c of row r is stored at chunk c ^ (r & 7), which makes every ldmatrix
-// (8 rows x 16 bytes, rows 256 bytes apart) bank-conflict free.
-template <typename T>
-__global__ void __launch_bounds__(128, 2) attn_decode_kernel(const __grid_constant__ DecodeParams p) {
+// Each warp streams its own 16-key blocks (blocks warp, warp+4, ...) through a private ring of
+// STAGES shared-memory stages filled with cp.async.  16-byte chunk c of row r is stored at chunk
+// c ^ (r & 7), which makes every ldmatrix (8 rows x 16 bytes, rows 256 bytes apart)
+// bank-conflict free.  STAGES = 3: two blocks in flight while a third is consumed, two CTAs per
+// SM; STAGES = 2: one in flight, three CTAs per SM (more CTAs to cover each other's start-up
+// and wind-down).
+//
+// Nothing on the way into the main loop waits for the whole CTA: each warp looks only at the
+// mask entries of its own blocks (ballots into a register bit set: which blocks have an
+// unmasked key and need to be fetched at all), and reads the two mask values a lane needs per
+// block straight from global memory (L1 hits after the scan).  The four warps meet once, at
+// the end, to merge their partial results through the shared memory their rings occupied.
+template <typename T, int STAGES>
+__global__ void __launch_bounds__(128, STAGES == 2 ? 3 : 2) attn_decode_kernel(const __grid_constant__ DecodeParams p) {
   extern __shared__ __align__(1024) uint8_t dsm[];
-  __shared__ uint32_t valid[DEC_MAX_BLOCKS / 32];
-  __shared__ float s_mask[DEC_MAX_SPLIT];
-  __shared__ float s_acc[8][DEC_ACC_PITCH];
   __shared__ float s_m[4][8], s_l[4][8];
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
@@ -203,10 +226,10 @@ __global__ void __launch_bounds__(128, 2) attn_decode_kernel(const __grid_consta
   const int n_keys = static_cast<int>(s_end - s_begin);
   const int nblk = (n_keys + 15) / 16;
 
-  if (threadIdx.x < DEC_MAX_BLOCKS / 32) valid[threadIdx.x] = 0u;
-  for (int i = threadIdx.x; i < 8 * DEC_ACC_PITCH; i += 128) (&s_acc[0][0])[i] = 0.f;
+  ATTN_STAMP(0);
   pdl_trigger();
   pdl_wait();   // q, the new cache rows and the mask come from the kernels before this one
+  ATTN_STAMP(1);
 
   // ---- per-lane addressing -------------------------------------------------------------
   // cp.async: lane copies chunk (lane & 15) of rows 2i + (lane >> 4), i = 0..7
@@ -218,7 +241,7 @@ __global__ void __launch_bounds__(128, 2) attn_decode_kernel(const __grid_consta
   const int mi = lane >> 3, mr = lane & 7;
   const uint32_t k_off = (8 * (mi & 1) + mr) * 256 + (((mi >> 1) ^ mr) << 4);   // ^ (ks << 5) selects dims 16ks..16ks+15
   const uint32_t v_off = (8 * (mi >> 1) + mr) * 256 + (((mi & 1) ^ mr) << 4);   // ^ (j << 5) selects dims 16j..16j+15
-  const uint32_t ring = smem_u32(dsm) + warp * (DEC_STAGES * DEC_STAGE_BYTES);
+  const uint32_t ring = smem_u32(dsm) + warp * (STAGES * DEC_STAGE_BYTES);
 
   // copy block `blk` (16 keys x 256 B of K and of V) into ring stage `st`
   auto issue = [&](int blk, int st) {
@@ -234,7 +257,7 @@ __global__ void __launch_bounds__(128, 2) attn_decode_kernel(const __grid_consta
         cp_async16(d + 16 * HD * 2, vs + i * 2 * HD, 16);
       }
     } else {   // rows past the end are zero-filled (their probabilities are zero, but 0 * garbage must stay 0)
-#pragma unroll
+#pragma unroll 1
       for (int i = 0; i < 8; ++i) {
         const uint32_t d = (sk ^ (((2 * i) & 7) << 4)) + i * 512;
         const bool ok = 2 * i + hi < rows_left;
@@ -244,14 +267,50 @@ __global__ void __launch_bounds__(128, 2) attn_decode_kernel(const __grid_consta
     }
   };
 
-  // The first two blocks of every warp are fetched before the mask has been looked at (they
-  // are almost always needed); this hides the mask scan behind the first copies.
-  int cur = warp < nblk ? warp : -1, nxt = warp + 4 < nblk ? warp + 4 : -1;
+  // Ask for a block's K and V rows (two contiguous 4 KB runs) to be brought into L2.  The ring
+  // keeps at most one or two blocks per warp in flight (shared memory is the limit); requests
+  // into L2 cost no shared memory, so the DRAM latency is paid there and the ring copies that
+  // follow find their lines in L2.
+  const T* k_blk0 = static_cast<const T*>(p.k) + b * p.kv_bs + hk * p.kv_hs + s_begin * HD;
+  const T* v_blk0 = static_cast<const T*>(p.v) + b * p.kv_bs + hk * p.kv_hs + s_begin * HD;
+  auto l2_prefetch = [&](int blk) {
+    if (lane == 0 && blk < nblk) {
+      const int rows = min(16, n_keys - blk * 16);
+      const uint32_t bytes = static_cast<uint32_t>(rows) * HD * 2;
+      asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(k_blk0 + static_cast<int64_t>(blk) * 16 * HD), "r"(bytes) : "memory");
+      asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(v_blk0 + static_cast<int64_t>(blk) * 16 * HD), "r"(bytes) : "memory");
+    }
+  };
+
+  // The first blocks of every warp are fetched before the mask has been looked at (they are
+  // almost always needed): the mask scan and the query loads hide behind these copies.
+  int cur = warp < nblk ? warp : -1, nxt = -1;
   if (cur >= 0) issue(cur, 0);
   cp_async_commit();
-  if (nxt >= 0) issue(nxt, 1);
-  cp_async_commit();
-  int st_fetch = 2, st_use = 0;
+  if (STAGES > 2) {
+    nxt = warp + 4 < nblk ? warp + 4 : -1;
+    if (nxt >= 0) issue(nxt, 1);
+    cp_async_commit();
+  }
+  for (int dd = 0; dd < p.l2_ahead; ++dd) l2_prefetch(warp + 4 * (STAGES - 1 + dd));
+
+  // ---- which of this warp's blocks have an unmasked key: bit j <-> block warp + 4j ----
+  const char* mask_row = p.mask ? static_cast<const char*>(p.mask) : nullptr;
+  const int64_t mask_base = b * p.mask_bs + s_begin;
+  uint32_t vbits = 0;
+#pragma unroll
+  for (int i = 0; i < DEC_MAX_SPLIT / 128; ++i) {
+    const int idx = i * 32 + lane, blk = warp + 4 * (idx >> 4), key = blk * 16 + (idx & 15);
+    float mv = -INFINITY;
+    if (key < n_keys) mv = mask_row ? load_as_f32(mask_row, mask_base + key, p.mask_dtype) : 0.f;
+    const uint32_t bal = __ballot_sync(0xffffffffu, mv > MASKED);
+    vbits |= ((bal & 0xffffu) ? 1u : 0u) << (2 * i) | ((bal >> 16) ? 1u : 0u) << (2 * i + 1);
+  }
+  auto is_valid = [&](int blk) { return ((vbits >> ((blk - warp) >> 2)) & 1u) != 0u; };
+  auto next_valid = [&](int blk) {  // first valid block of this warp at or after blk (stride 4)
+    while (blk < nblk && !is_valid(blk)) blk += 4;
+    return blk;
+  };
 
   // Q^T fragments: head g, dims 16ks + 2t, +1 and 16ks + 2t + 8, +9
   uint32_t qf[8][2];
@@ -263,17 +322,7 @@ __global__ void __launch_bounds__(128, 2) attn_decode_kernel(const __grid_consta
       qf[ks][1] = g < p.G ? *reinterpret_cast<const uint32_t*>(qr + 16 * ks + 8) : 0u;
     }
   }
-
-  // ---- mask values of this split (log2 domain); which 16-key blocks have an unmasked key ----
-  __syncthreads();
-  for (int i = threadIdx.x; i < nblk * 16; i += 128) {
-    float mv = 0.f;
-    if (i >= n_keys) mv = -INFINITY;
-    else if (p.mask) mv = load_as_f32(p.mask, b * p.mask_bs + s_begin + i, p.mask_dtype);
-    s_mask[i] = mv * LOG2E;
-    if (mv > MASKED) atomicOr(&valid[i >> 9], 1u << ((i >> 4) & 31));
-  }
-  __syncthreads();
+  ATTN_STAMP(2);
 
   float o[8][4];   // [dim tile j][dims 16j+g (0,1) / 16j+g+8 (2,3)  x  heads 2t (0,2) / 2t+1 (1,3)]
 #pragma unroll
@@ -281,22 +330,46 @@ __global__ void __launch_bounds__(128, 2) attn_decode_kernel(const __grid_consta
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
   const float sl = p.scale * LOG2E;
 
-  auto is_valid = [&](int blk) { return ((valid[blk >> 5] >> (blk & 31)) & 1u) != 0u; };
-  auto next_valid = [&](int blk) {  // first valid block of this warp at or after blk (stride 4)
-    while (blk < nblk && !is_valid(blk)) blk += 4;
-    return blk;
+  // additive mask (log2 domain) of key `key` of this split for this lane's two score rows
+  auto mask_of = [&](int key) {
+    if (key >= n_keys) return -INFINITY;
+    return mask_row ? load_as_f32(mask_row, mask_base + key, p.mask_dtype) * LOG2E : 0.f;
   };
-  int fetch = next_valid(warp + 8);   // next block to copy
+
+  int fetch = next_valid(warp + (STAGES > 2 ? 8 : 4));   // next block to copy
+  int st_fetch = STAGES > 2 ? 2 : 1, st_use = 0;
   while (cur >= 0) {
-    cp_async_wait<DEC_STAGES - 2>();
-    __syncwarp();   // every lane's copies for this stage have landed; the stage consumed last time is free
     int fetched = -1;
-    if (fetch < nblk) { issue(fetch, st_fetch); fetched = fetch; fetch = next_valid(fetch + 4); }
-    cp_async_commit();
-    st_fetch = (st_fetch + 1) % DEC_STAGES;
+    if (STAGES > 2) {
+      cp_async_wait<1>();
+      __syncwarp();   // every lane's copies for this stage have landed; the stage consumed last time is free
+      if (fetch < nblk) {
+        issue(fetch, st_fetch);
+        fetched = fetch;
+        const int pb = fetch + 4 * p.l2_ahead;
+        if (p.l2_ahead && pb < nblk && is_valid(pb)) l2_prefetch(pb);
+        fetch = next_valid(fetch + 4);
+      }
+      cp_async_commit();
+      st_fetch = (st_fetch + 1) % STAGES;
+    } else {
+      __syncwarp();   // every lane has finished with the stage consumed last time
+      if (fetch < nblk) {
+        issue(fetch, st_fetch);
+        fetched = fetch;
+        const int pb = fetch + 4 * p.l2_ahead;
+        if (p.l2_ahead && pb < nblk && is_valid(pb)) l2_prefetch(pb);
+        fetch = next_valid(fetch + 4);
+      }
+      cp_async_commit();
+      st_fetch ^= 1;
+      cp_async_wait<1>();
+      __syncwarp();
+    }
 
     if (is_valid(cur)) {
       const uint32_t sk = ring + st_use * DEC_STAGE_BYTES, sv = sk + 16 * HD * 2;
+      const float mk0 = mask_of(cur * 16 + g), mk1 = mask_of(cur * 16 + g + 8);
       // ---- S^T = K Q^T (two accumulators halve the dependent chain) ----
       float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -307,7 +380,6 @@ __global__ void __launch_bounds__(128, 2) attn_decode_kernel(const __grid_consta
         MmaType<T>::mma(sa, a0, qf[ks]);
         MmaType<T>::mma(sb, a1, qf[ks + 1]);
       }
-      const float mk0 = s_mask[cur * 16 + g], mk1 = s_mask[cur * 16 + g + 8];
       const float v0 = fmaf(sa[0] + sb[0], sl, mk0), v1 = fmaf(sa[1] + sb[1], sl, mk0);   // key g:   heads 2t, 2t+1
       const float v2 = fmaf(sa[2] + sb[2], sl, mk1), v3 = fmaf(sa[3] + sb[3], sl, mk1);   // key g+8: heads 2t, 2t+1
       // ---- online softmax over the 16 keys (lanes that differ in g) ----
@@ -338,45 +410,60 @@ __global__ void __launch_bounds__(128, 2) attn_decode_kernel(const __grid_consta
         MmaType<T>::mma(o[j], a, pb);
       }
     }
-    st_use = (st_use + 1) % DEC_STAGES;
-    cur = nxt;
-    nxt = fetched;
+    st_use = (st_use + 1) % STAGES;
+    if (STAGES > 2) { cur = nxt; nxt = fetched; }
+    else cur = fetched;
   }
   cp_async_wait<0>();
+  ATTN_STAMP(3);
 
-  // ---- merge the four warps ------------------------------------------------------------
+  // ---- merge the four warps: every warp parks its accumulators (and running max / sum) in the
+  // shared memory its own ring occupied; after one barrier thread d adds up dim d of every head ----
 #pragma unroll
   for (int off = 4; off < 32; off <<= 1) {
     l0 += __shfl_xor_sync(0xffffffffu, l0, off);
     l1 += __shfl_xor_sync(0xffffffffu, l1, off);
   }
+  __syncwarp();   // all lanes are done reading the ring
+  float* slab = reinterpret_cast<float*>(dsm + warp * (STAGES * DEC_STAGE_BYTES));   // [8 heads][DEC_ACC_PITCH]
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    slab[(2 * t) * DEC_ACC_PITCH + 16 * j + g] = o[j][0];
+    slab[(2 * t + 1) * DEC_ACC_PITCH + 16 * j + g] = o[j][1];
+    slab[(2 * t) * DEC_ACC_PITCH + 16 * j + g + 8] = o[j][2];
+    slab[(2 * t + 1) * DEC_ACC_PITCH + 16 * j + g + 8] = o[j][3];
+  }
   if (g == 0) { s_m[warp][2 * t] = m0; s_m[warp][2 * t + 1] = m1; s_l[warp][2 * t] = l0; s_l[warp][2 * t + 1] = l1; }
   __syncthreads();
-  {
-    const int h0 = 2 * t, h1 = 2 * t + 1;
-    const float ma0 = fmaxf(fmaxf(s_m[0][h0], s_m[1][h0]), fmaxf(s_m[2][h0], s_m[3][h0]));
-    const float ma1 = fmaxf(fmaxf(s_m[0][h1], s_m[1][h1]), fmaxf(s_m[2][h1], s_m[3][h1]));
-    const float f0 = ex2_approx(m0 - (ma0 == -INFINITY ? 0.f : ma0)), f1 = ex2_approx(m1 - (ma1 == -INFINITY ? 0.f : ma1));
+  const int64_t pidx = ((b * p.Hkv + hk) * p.splits + split) * p.G;
+  const int d = threadIdx.x;
+#pragma unroll 1
+  for (int h = 0; h < p.G; ++h) {
+    const float ma = fmaxf(fmaxf(s_m[0][h], s_m[1][h]), fmaxf(s_m[2][h], s_m[3][h]));
+    const float mu = ma == -INFINITY ? 0.f : ma;
+    float acc = 0.f, lr = 0.f;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      if (h0 < p.G) { atomicAdd(&s_acc[h0][16 * j + g], o[j][0] * f0); atomicAdd(&s_acc[h0][16 * j + g + 8], o[j][2] * f0); }
-      if (h1 < p.G) { atomicAdd(&s_acc[h1][16 * j + g], o[j][1] * f1); atomicAdd(&s_acc[h1][16 * j + g + 8], o[j][3] * f1); }
+    for (int wi = 0; wi < 4; ++wi) {
+      const float f = ex2_approx(s_m[wi][h] - mu);
+      acc += reinterpret_cast<const float*>(dsm + wi * (STAGES * DEC_STAGE_BYTES))[h * DEC_ACC_PITCH + d] * f;
+      lr += s_l[wi][h] * f;
+    }
+    p.part_acc[(pidx + h) * HD + d] = acc;
+    if (d == 0) {
+      p.part_ml[(pidx + h) * 2] = ma;      // log2 domain
+      p.part_ml[(pidx + h) * 2 + 1] = lr;
     }
   }
-  __syncthreads();
-  const int64_t pidx = ((b * p.Hkv + hk) * p.splits + split) * p.G;
-  for (int i = threadIdx.x; i < p.G * HD; i += 128) p.part_acc[pidx * HD + i] = s_acc[i >> 7][i & (HD - 1)];
-  if (threadIdx.x < p.G) {
-    const int r = threadIdx.x;
-    const float mr_ = fmaxf(fmaxf(s_m[0][r], s_m[1][r]), fmaxf(s_m[2][r], s_m[3][r]));
-    const float mu = mr_ == -INFINITY ? 0.f : mr_;
-    float lr = 0.f;
-#pragma unroll
-    for (int wi = 0; wi < 4; ++wi) lr += s_l[wi][r] * ex2_approx(s_m[wi][r] - mu);
-    p.part_ml[(pidx + r) * 2] = mr_;      // log2 domain
-    p.part_ml[(pidx + r) * 2 + 1] = lr;
-  }
+  ATTN_STAMP(4);
 }
+
+#ifdef B200NN_TC5_TRACE
+}  // namespace b200
+extern "C" int b200_debug_attn_trace(unsigned long long* host_out) {
+  return cudaMemcpyFromSymbol(host_out, b200::g_attn_trace, sizeof(unsigned long long) * b200::ATR_CTAS * b200::ATR_N) == cudaSuccess ? 0 : -3;
+}
+namespace b200 {
+#endif
 
 // grid = B*Hq blocks of 128 threads (one per head dim)
 template <typename T>
@@ -522,14 +609,25 @@ extern "C" int b200_attn_decode(const void* q, const void* k, const void* v, con
   p.split_len = d.split_len; p.splits = d.splits; p.scale = scale; p.mask_dtype = dtype;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   dim3 grid(static_cast<unsigned>(d.splits), static_cast<unsigned>(Hkv), static_cast<unsigned>(B));
+  static int stages = 0, l2_ahead = 0;   // ring depth per warp: 2 (three CTAs per SM) or 3 (two CTAs per SM)
+  if (stages == 0) {
+    const char* e = getenv("B200NN_ATTN_STAGES");
+    stages = (e && e[0] == '3') ? 3 : 2;
+    const char* a = getenv("B200NN_ATTN_L2_AHEAD");
+    l2_ahead = a && a[0] ? atoi(a) : 0;   // measured: requests into L2 ahead of the ring only slow the kernel down
+    if (l2_ahead < 0 || l2_ahead > 8) l2_ahead = 0;
+  }
+  p.l2_ahead = l2_ahead;
   B200_DISPATCH_HALF(dtype, T, {
     static bool configured = false;
     if (!configured) {
-      cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM);
+      cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<T, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 4 * 3 * DEC_STAGE_BYTES);
+      if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_decode_kernel<T, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 4 * 2 * DEC_STAGE_BYTES);
       if (e != cudaSuccess) B200_FAIL(B200_ELAUNCH, "attn_decode_kernel attribute: %s", cudaGetErrorString(e));
       configured = true;
     }
-    launch_pdl(attn_decode_kernel<T>, grid, dim3(128), DEC_SMEM, st, p);
+    if (stages == 2) launch_pdl(attn_decode_kernel<T, 2>, grid, dim3(128), 4 * 2 * DEC_STAGE_BYTES, st, p);
+    else launch_pdl(attn_decode_kernel<T, 3>, grid, dim3(128), 4 * 3 * DEC_STAGE_BYTES, st, p);
     launch_pdl(attn_decode_merge_kernel<T>, dim3(static_cast<unsigned>(B * Hq)), dim3(128), 0, st, static_cast<const float*>(p.part_acc),
                static_cast<const float*>(p.part_ml), static_cast<T*>(out), Hq, Hkv, p.G, d.splits);
   });
