@@ -235,9 +235,12 @@ int b200_conv_weight_prep(const void* w, const void* conv_bias, const void* gamm
  * which calls cupy.matmul and a separate bias-add kernel):
  *   out[M,N] = epi( A[M,K] * W[N,K]^T + bias[N] + residual[M,N] )
  * A, W, out, residual share `dtype` (f16/bf16), fp32 accumulation; bias dtype is
- * `bias_dtype`.  lda/ldw/ldo/ldr are row strides in elements.  Any M; skinny M
- * (decode) takes a weight-streaming split-K path that uses `workspace`
- * (fp32 [M*N] + a counter block, see b200_linear_workspace_bytes). */
+ * `bias_dtype`.  lda/ldw/ldo/ldr are row strides in elements.  Any M.  Operands that
+ * meet the TMA rules (16-byte aligned, strides multiples of 8 elements) run on the
+ * tcgen05 path, which needs no scratch (split-K partial sums meet in distributed shared
+ * memory).  Other operands with M <= 64 fall back to a weight-streaming kernel whose
+ * split-K uses `workspace` (zero-initialised by the caller once, left zeroed by every
+ * call; b200_linear_workspace_bytes gives the size, 0 when none is needed). */
 int b200_linear(const void* A, const void* W, const void* bias, const void* residual, void* out,
                 int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldw, int64_t ldo, int64_t ldr,
                 int dtype, int bias_dtype, int epilogue, const void* aux, int64_t ldaux,

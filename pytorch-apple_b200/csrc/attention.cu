@@ -1,16 +1,9 @@
-// Fused attention for head_dim 128 on the warp-level tensor-core path.
-//
-// One warp owns a 16-row score tile: 16 query positions of one head (prefill) or
-// the group of query heads that share one KV head, padded to 16 (decode).  K and V
-// rows go from global memory straight into MMA fragments with 16-byte loads:
-//   * S = Q K^T: inside every 32-wide slice of the head dim, thread t of a quad owns
-//     dims 8t..8t+7 for both Q and K - a consistent permutation of the contraction
-//     index, so the dot products are unchanged;
-//   * O = P V: thread (g, t) loads dims 8g..8g+7 (+64) of keys {2t, 2t+1, 2t+8, 2t+9}
-//     and assembles the B fragments with byte permutes; output column "g" of MMA
-//     tile j therefore is head dim 8g + j, which the store undoes.
-// Softmax is the usual online form in fp32; P is rounded to the activation dtype
-// for the second MMA, as the unfused graph rounds the probabilities.
+// Fused attention for head_dim 128 on the warp-level tensor-core path (mma.sync m16n8k16,
+// fp32 accumulation, online softmax in the log2 domain).  K and V rows are staged in shared
+// memory with cp.async under an XOR swizzle and read with ldmatrix / ldmatrix.trans; the
+// probabilities are rounded to the activation dtype for the second MMA, as the unfused graph
+// rounds them.  Two kernels: prefill (64 query rows per CTA) and split-KV decode (one query
+// token, the query heads of a KV group on the N side of the MMA).
 #include "mma.cuh"
 
 #include <stdlib.h>
@@ -20,134 +13,6 @@ namespace b200 {
 constexpr int HD = 128;          // head dim
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float MASKED = -1e30f; // additive mask values at or below this are "masked out"
-
-template <typename T> struct AttnWarp {
-  uint32_t q[4][2][4];  // [32-dim slice][row half g / g+8][4 x 32-bit]
-  float o[2][8][4];     // [64-dim half][tile j][c0..c3]
-  float m[2], l[2];     // running max / sum for rows g and g+8
-
-  __device__ __forceinline__ void init() {
-#pragma unroll
-    for (int a = 0; a < 2; ++a)
-#pragma unroll
-      for (int j = 0; j < 8; ++j)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) o[a][j][e] = 0.f;
-    m[0] = m[1] = -INFINITY;
-    l[0] = l[1] = 0.f;
-  }
-
-  // q_lo / q_hi: rows g and g+8 (nullptr -> zero row)
-  __device__ __forceinline__ void load_q(const T* q_lo, const T* q_hi, int t) {
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      const uint4 lo = q_lo ? *reinterpret_cast<const uint4*>(q_lo + 32 * c + 8 * t) : make_uint4(0, 0, 0, 0);
-      const uint4 hi = q_hi ? *reinterpret_cast<const uint4*>(q_hi + 32 * c + 8 * t) : make_uint4(0, 0, 0, 0);
-      q[c][0][0] = lo.x; q[c][0][1] = lo.y; q[c][0][2] = lo.z; q[c][0][3] = lo.w;
-      q[c][1][0] = hi.x; q[c][1][1] = hi.y; q[c][1][2] = hi.z; q[c][1][3] = hi.w;
-    }
-  }
-
-  // One block of 16 keys starting at row `kb`.  k_base/v_base point at key 0 of this
-  // (batch, kv head); key stride in elements.  add[j][e]: additive mask (already in
-  // the score domain) for rows (g, g+8) x keys (8j+2t, 8j+2t+1): index [j][2*half+e].
-  __device__ __forceinline__ void step(const T* k_base, const T* v_base, int64_t k_stride, int64_t v_stride, int64_t kb,
-                                       int64_t n_keys, float scale, const float (&add)[2][4], int g, int t) {
-    const uint4 zero4 = make_uint4(0, 0, 0, 0);
-    // ---- issue all loads for this block -----------------------------------------
-    uint4 kf[2][4];  // [key tile][32-dim slice]
-#pragma unroll
-    for (int j = 0; j < 2; ++j) {
-      const int64_t key = kb + 8 * j + g;
-      const T* kr = k_base + key * k_stride + 8 * t;
-#pragma unroll
-      for (int c = 0; c < 4; ++c) kf[j][c] = key < n_keys ? ld_global_nc_v4(kr + 32 * c) : zero4;
-    }
-    uint4 vf[2][4];  // [64-dim half][key slot 2t, 2t+1, 2t+8, 2t+9]
-#pragma unroll
-    for (int s = 0; s < 4; ++s) {
-      const int64_t key = kb + 2 * t + (s & 1) + 8 * (s >> 1);
-      const T* vr = v_base + key * v_stride + 8 * g;
-#pragma unroll
-      for (int a = 0; a < 2; ++a) vf[a][s] = key < n_keys ? ld_global_nc_v4(vr + 64 * a) : zero4;
-    }
-    compute(kf, vf, kb, n_keys, scale, add, t);
-  }
-
-  // Same block, fragments already in registers (from global memory or from a shared-memory stage).
-  __device__ __forceinline__ void compute(const uint4 (&kf)[2][4], const uint4 (&vf)[2][4], int64_t kb, int64_t n_keys, float scale,
-                                          const float (&add)[2][4], int t) {
-    // ---- S = Q K^T ---------------------------------------------------------------
-    float s[2][4];
-#pragma unroll
-    for (int j = 0; j < 2; ++j) {
-      s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const uint32_t a1[4] = {q[c][0][0], q[c][1][0], q[c][0][1], q[c][1][1]};
-        const uint32_t a2[4] = {q[c][0][2], q[c][1][2], q[c][0][3], q[c][1][3]};
-        const uint32_t b1[2] = {kf[j][c].x, kf[j][c].y};
-        const uint32_t b2[2] = {kf[j][c].z, kf[j][c].w};
-        MmaType<T>::mma(s[j], a1, b1);
-        MmaType<T>::mma(s[j], a2, b2);
-      }
-    }
-    // ---- online softmax ------------------------------------------------------------
-    float mx[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-    for (int j = 0; j < 2; ++j)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int64_t key = kb + 8 * j + 2 * t + (e & 1);
-        const float v = key < n_keys ? s[j][e] * scale + add[j][e] : -INFINITY;
-        s[j][e] = v;
-        mx[e >> 1] = fmaxf(mx[e >> 1], v);
-      }
-    float corr[2];
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
-      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
-      const float m_new = fmaxf(m[h], mx[h]);
-      const float m_use = m_new == -INFINITY ? 0.f : m_new;
-      corr[h] = exp2f((m[h] - m_use) * LOG2E);  // m = -inf -> 0
-      m[h] = m_new;
-      float rs = 0.f;
-#pragma unroll
-      for (int j = 0; j < 2; ++j)
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const float p = exp2f((s[j][2 * h + e] - m_use) * LOG2E);
-          s[j][2 * h + e] = p;
-          rs += p;
-        }
-      rs += __shfl_xor_sync(0xffffffffu, rs, 1);
-      rs += __shfl_xor_sync(0xffffffffu, rs, 2);
-      l[h] = l[h] * corr[h] + rs;
-    }
-    // ---- O = O * corr + P V -----------------------------------------------------------
-    const uint32_t pa[4] = {pack2<T>(s[0][0], s[0][1]), pack2<T>(s[0][2], s[0][3]), pack2<T>(s[1][0], s[1][1]),
-                            pack2<T>(s[1][2], s[1][3])};
-#pragma unroll
-    for (int a = 0; a < 2; ++a) {
-      const uint32_t* r0 = reinterpret_cast<const uint32_t*>(&vf[a][0]);
-      const uint32_t* r1 = reinterpret_cast<const uint32_t*>(&vf[a][1]);
-      const uint32_t* r2 = reinterpret_cast<const uint32_t*>(&vf[a][2]);
-      const uint32_t* r3 = reinterpret_cast<const uint32_t*>(&vf[a][3]);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const uint32_t sel = (j & 1) ? 0x7632u : 0x5410u;
-        const uint32_t b[2] = {__byte_perm(r0[j >> 1], r1[j >> 1], sel), __byte_perm(r2[j >> 1], r3[j >> 1], sel)};
-        o[a][j][0] *= corr[0]; o[a][j][1] *= corr[0];
-        o[a][j][2] *= corr[1]; o[a][j][3] *= corr[1];
-        MmaType<T>::mma(o[a][j], pa, b);
-      }
-    }
-  }
-};
-
-// head dim held in o[a][j][2*h + e]  (h: row half) for thread (g, t)
-__device__ __forceinline__ int out_dim(int a, int j, int e, int t) { return 64 * a + 8 * (2 * t + e) + j; }
 
 // ===========================================================================
 // Decode: one query token, G = Hq / Hkv query heads share each KV head.
@@ -500,58 +365,175 @@ struct PrefillParams {
   int mask_dtype;
 };
 
+constexpr int PF_BK = 64;                              // keys per shared-memory tile
+constexpr int PF_STAGE_BYTES = 2 * PF_BK * HD * 2;     // K tile + V tile
+constexpr int PF_SMEM = 2 * PF_STAGE_BYTES;            // double buffer
+
+// One CTA = 64 query rows of one head (16 per warp).  K and V tiles of 64 keys are copied into
+// shared memory once per CTA with cp.async (double-buffered; chunk c of row r at c ^ (r & 7)) and
+// read by all four warps with ldmatrix: K rows as the B operand of S = Q K^T, V rows through
+// ldmatrix.trans as the B operand of O += P V; P goes from the score accumulators straight
+// into A fragments.  Online softmax in the log2 domain, lazy rescale, 64-key tiles whose mask
+// entries are all <= -1e30 for a warp's 16 rows are skipped by that warp.
 template <typename T>
 __global__ void __launch_bounds__(128) attn_prefill_kernel(const __grid_constant__ PrefillParams p) {
+  extern __shared__ __align__(1024) uint8_t psm[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
   const int h = blockIdx.y, hk = h / (p.Hq / p.Hkv);
   const int64_t b = blockIdx.z;
   const int64_t row0 = static_cast<int64_t>(blockIdx.x) * 64 + warp * 16;
-  if (row0 >= p.T) return;
   const int64_t r_lo = row0 + g, r_hi = row0 + g + 8;
-  const T* qb = static_cast<const T*>(p.q) + b * p.qs[0] + h * p.qs[1];
-  AttnWarp<T> w;
-  w.init();
-  w.load_q(r_lo < p.T ? qb + r_lo * p.qs[2] : nullptr, r_hi < p.T ? qb + r_hi * p.qs[2] : nullptr, t);
+  const bool warp_live = row0 < p.T;   // a warp past the end still copies tiles and meets the barriers
+
+  // Q as A fragments: slice ks covers dims 16ks..16ks+15
+  uint32_t qf[8][4];
+  {
+    const T* qb = static_cast<const T*>(p.q) + b * p.qs[0] + h * p.qs[1] + 2 * t;
+    const T* q0 = qb + r_lo * p.qs[2];
+    const T* q1 = qb + r_hi * p.qs[2];
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      qf[ks][0] = r_lo < p.T ? *reinterpret_cast<const uint32_t*>(q0 + 16 * ks) : 0u;
+      qf[ks][1] = r_hi < p.T ? *reinterpret_cast<const uint32_t*>(q1 + 16 * ks) : 0u;
+      qf[ks][2] = r_lo < p.T ? *reinterpret_cast<const uint32_t*>(q0 + 16 * ks + 8) : 0u;
+      qf[ks][3] = r_hi < p.T ? *reinterpret_cast<const uint32_t*>(q1 + 16 * ks + 8) : 0u;
+    }
+  }
   const T* kbase = static_cast<const T*>(p.k) + b * p.ks[0] + hk * p.ks[1];
   const T* vbase = static_cast<const T*>(p.v) + b * p.vs[0] + hk * p.vs[1];
+  const uint32_t sm0 = smem_u32(psm);
+
+  auto issue = [&](int64_t kb, int st) {   // tile of keys kb..kb+63 -> stage st
+    const uint32_t sk = sm0 + st * PF_STAGE_BYTES, sv = sk + PF_BK * HD * 2;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int idx = i * 128 + threadIdx.x, row = idx >> 4, ch = idx & 15;
+      const bool ok = kb + row < p.S;
+      const uint32_t off = row * 256 + ((ch ^ (row & 7)) << 4);
+      cp_async16(sk + off, ok ? static_cast<const void*>(kbase + (kb + row) * p.ks[2] + ch * 8) : static_cast<const void*>(kbase), ok ? 16 : 0);
+      cp_async16(sv + off, ok ? static_cast<const void*>(vbase + (kb + row) * p.vs[2] + ch * 8) : static_cast<const void*>(vbase), ok ? 16 : 0);
+    }
+  };
+
+  // ldmatrix lane addressing inside a tile
+  const int mi = lane >> 3, mr = lane & 7;
+  const uint32_t k_off = ((mi >> 1) * 8 + mr) * 256 + (((mi & 1) ^ mr) << 4);   // + 16-key group * 4096, ^ (dim slice << 5)
+  const uint32_t v_off = ((mi & 1) * 8 + mr) * 256 + (((mi >> 1) ^ mr) << 4);   // + 16-key group * 4096, ^ (dim pair << 5)
+
+  float o[16][4];
+#pragma unroll
+  for (int j = 0; j < 16; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  const float sl = p.scale * LOG2E;
   const int64_t mrow[2] = {b * p.mask_b + min(r_lo, p.T - 1) * p.mask_t, b * p.mask_b + min(r_hi, p.T - 1) * p.mask_t};
 
-  for (int64_t kb = 0; kb < p.S; kb += 16) {
-    float add[2][4];
-    bool any = !p.mask;
+  const int n_tiles = static_cast<int>((p.S + PF_BK - 1) / PF_BK);
+  issue(0, 0);
+  cp_async_commit();
+  for (int j = 0; j < n_tiles; ++j) {
+    const int64_t kb = static_cast<int64_t>(j) * PF_BK;
+    if (j + 1 < n_tiles) issue(kb + PF_BK, (j + 1) & 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();   // tile j has landed for every thread
+
+    // ---- additive mask (log2 domain) for rows g, g+8 x keys 8nt + 2t, +1 ----
+    float mk[8][4];
+    bool any = false;
 #pragma unroll
-    for (int j = 0; j < 2; ++j)
+    for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const int64_t key = kb + 8 * j + 2 * t + (e & 1);
+        const int64_t key = kb + 8 * nt + 2 * t + (e & 1);
         float mv = 0.f;
-        if (p.mask && key < p.S) {
-          mv = load_as_f32(p.mask, mrow[e >> 1] + key, p.mask_dtype);
-          any = any || mv > MASKED;
-        }
-        add[j][e] = mv;
+        if (key >= p.S) mv = -INFINITY;
+        else if (p.mask) mv = load_as_f32(p.mask, mrow[e >> 1] + key, p.mask_dtype);
+        any = any || mv > MASKED;
+        mk[nt][e] = mv * LOG2E;
       }
-    if (!__any_sync(0xffffffffu, any)) continue;  // whole 16x16 tile masked out
-    w.step(kbase, vbase, p.ks[2], p.vs[2], kb, p.S, p.scale, add, g, t);
+    if (warp_live && __any_sync(0xffffffffu, any)) {
+      const uint32_t sk = sm0 + (j & 1) * PF_STAGE_BYTES, sv = sk + PF_BK * HD * 2;
+      // ---- S = Q K^T ----
+      float sc[8][4];
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks)
+#pragma unroll
+        for (int np = 0; np < 4; ++np) {
+          uint32_t kf[4];
+          ldmatrix_x4(kf, sk + np * 4096 + (k_off ^ (ks << 5)));
+          const uint32_t b0[2] = {kf[0], kf[1]}, b1[2] = {kf[2], kf[3]};
+          MmaType<T>::mma(sc[2 * np], qf[ks], b0);
+          MmaType<T>::mma(sc[2 * np + 1], qf[ks], b1);
+        }
+      // ---- online softmax ----
+      float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          sc[nt][e] = fmaf(sc[nt][e], sl, mk[nt][e]);
+          mx[e >> 1] = fmaxf(mx[e >> 1], sc[nt][e]);
+        }
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        mx[hh] = fmaxf(mx[hh], __shfl_xor_sync(0xffffffffu, mx[hh], 1));
+        mx[hh] = fmaxf(mx[hh], __shfl_xor_sync(0xffffffffu, mx[hh], 2));
+        mx[hh] = fmaxf(mx[hh], m_run[hh]);
+      }
+      if (__any_sync(0xffffffffu, mx[0] > m_run[0] || mx[1] > m_run[1])) {
+        const float c0 = ex2_approx(m_run[0] - (mx[0] == -INFINITY ? 0.f : mx[0])), c1 = ex2_approx(m_run[1] - (mx[1] == -INFINITY ? 0.f : mx[1]));
+#pragma unroll
+        for (int jj = 0; jj < 16; ++jj) { o[jj][0] *= c0; o[jj][1] *= c0; o[jj][2] *= c1; o[jj][3] *= c1; }
+        l_run[0] *= c0; l_run[1] *= c1;
+        m_run[0] = mx[0]; m_run[1] = mx[1];
+      }
+      const float u0 = m_run[0] == -INFINITY ? 0.f : m_run[0], u1 = m_run[1] == -INFINITY ? 0.f : m_run[1];
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
+        sc[nt][0] = ex2_approx(sc[nt][0] - u0); sc[nt][1] = ex2_approx(sc[nt][1] - u0);
+        sc[nt][2] = ex2_approx(sc[nt][2] - u1); sc[nt][3] = ex2_approx(sc[nt][3] - u1);
+        l_run[0] += sc[nt][0] + sc[nt][1];
+        l_run[1] += sc[nt][2] + sc[nt][3];
+      }
+      // ---- O += P V ----
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) {
+        const uint32_t pa[4] = {pack2<T>(sc[2 * kk][0], sc[2 * kk][1]), pack2<T>(sc[2 * kk][2], sc[2 * kk][3]),
+                                pack2<T>(sc[2 * kk + 1][0], sc[2 * kk + 1][1]), pack2<T>(sc[2 * kk + 1][2], sc[2 * kk + 1][3])};
+#pragma unroll
+        for (int dp = 0; dp < 8; ++dp) {
+          uint32_t vf[4];
+          ldmatrix_x4_trans(vf, sv + kk * 4096 + (v_off ^ (dp << 5)));
+          const uint32_t b0[2] = {vf[0], vf[1]}, b1[2] = {vf[2], vf[3]};
+          MmaType<T>::mma(o[2 * dp], pa, b0);
+          MmaType<T>::mma(o[2 * dp + 1], pa, b1);
+        }
+      }
+    }
+    __syncthreads();   // every warp is done with stage j & 1 before tile j + 2 is copied into it
   }
+  cp_async_wait<0>();
 
+  if (!warp_live) return;
+  // row sums live as per-thread partials over the thread's key columns: finish them across the quad
+#pragma unroll
+  for (int hh = 0; hh < 2; ++hh) {
+    l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 1);
+    l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 2);
+  }
   // out[b][row][h][:]
-  T* ob = static_cast<T*>(p.out) + (b * p.T * p.Hq + h) * HD;
+  T* ob = static_cast<T*>(p.out) + (b * p.T * p.Hq + h) * HD + 2 * t;
 #pragma unroll
   for (int hh = 0; hh < 2; ++hh) {
     const int64_t row = hh ? r_hi : r_lo;
     if (row >= p.T) continue;
-    const float inv = w.l[hh] > 0.f ? 1.f / w.l[hh] : 0.f;
+    const float inv = l_run[hh] > 0.f ? 1.f / l_run[hh] : 0.f;
     T* orow = ob + row * p.Hq * HD;
 #pragma unroll
-    for (int a = 0; a < 2; ++a)
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        float vals[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) vals[j] = w.o[a][j][2 * hh + e] * inv;
-        *reinterpret_cast<uint4*>(orow + 64 * a + 8 * (2 * t + e)) = pack8<T>(vals);
-      }
+    for (int nt = 0; nt < 16; ++nt)
+      *reinterpret_cast<uint32_t*>(orow + 8 * nt) = pack2<T>(o[nt][2 * hh] * inv, o[nt][2 * hh + 1] * inv);
   }
 }
 
@@ -654,7 +636,15 @@ extern "C" int b200_attn_prefill(const void* q, const void* k, const void* v, co
   p.mask_b = mask_b; p.mask_t = mask_t; p.scale = scale; p.mask_dtype = dtype;
   dim3 grid(static_cast<unsigned>(ceil_div(T, 64)), static_cast<unsigned>(Hq), static_cast<unsigned>(B));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  B200_DISPATCH_HALF(dtype, T_, { attn_prefill_kernel<T_><<<grid, 128, 0, st>>>(p); });
+  B200_DISPATCH_HALF(dtype, T_, {
+    static bool configured = false;
+    if (!configured) {
+      cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<T_>, cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM);
+      if (e != cudaSuccess) B200_FAIL(B200_ELAUNCH, "attn_prefill_kernel attribute: %s", cudaGetErrorString(e));
+      configured = true;
+    }
+    attn_prefill_kernel<T_><<<grid, 128, PF_SMEM, st>>>(p);
+  });
   B200_CHECK_LAUNCH("attn_prefill_kernel");
   return B200_OK;
 }

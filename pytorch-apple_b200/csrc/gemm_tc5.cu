@@ -252,6 +252,7 @@ __global__ void __launch_bounds__(192, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(cons
   const int kb0 = blockIdx.z * p.kb_per_split;
   const int nkb = min(KB, kb0 + p.kb_per_split) - kb0;   // >= 1 by construction of the grid
   // single-row-tile shapes and split-K stage the accumulator through shared memory (see the end of the kernel)
+  const bool gather = CONV && !p.g.im2col;   // convolution A tile copied by the epilogue warps instead of TMA
   const bool staged = !CONV && (MODE >= 1 || p.splits > 1);   // MODE >= 1: known at compile time, the direct epilogue is dropped
   const bool glu = (p.epilogue & B200_EPI_GLU) != 0;       // host guarantees BN == 128 and N % 128 == 0
   const int rows_valid = static_cast<int>(p.M - m0 < BM ? p.M - m0 : BM);
@@ -267,7 +268,7 @@ __global__ void __launch_bounds__(192, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(cons
   if (threadIdx.x == 0) {
     TC5_STAMP(0);
     failed = 0;
-    for (int s = 0; s < ST; ++s) { tc5::mbar_init(&full_bar[s], CONV ? 129 : 1); tc5::mbar_init(&empty_bar[s], 1); }
+    for (int s = 0; s < ST; ++s) { tc5::mbar_init(&full_bar[s], gather ? 129 : 1); tc5::mbar_init(&empty_bar[s], 1); }
     tc5::mbar_init(&acc_bar, 1);
     tc5::fence_barrier_init();
     tc5::prefetch_tensormap(&map_a);
@@ -305,10 +306,17 @@ __global__ void __launch_bounds__(192, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(cons
         if (i >= pre) {
           if (!tc5::mbar_wait(&empty_bar[s], ph ^ 1)) { failed = 1; atomicExch(&g_tc5_error, 1); break; }
           if (*reinterpret_cast<volatile int*>(&failed)) break;
-          tc5::mbar_arrive_expect_tx(&full_bar[s], CONV ? B_STAGE : STAGE);
+          tc5::mbar_arrive_expect_tx(&full_bar[s], gather ? B_STAGE : STAGE);
           tc5::tma_load_2d(smem + s * STAGE + A_STAGE, &map_w, &full_bar[s], (kb0 + i) * BK, n0);
         }
-        if (!CONV) tc5::tma_load_2d(smem + s * STAGE, &map_a, &full_bar[s], (kb0 + i) * BK, m0);
+        if (!CONV) {
+          tc5::tma_load_2d(smem + s * STAGE, &map_a, &full_bar[s], (kb0 + i) * BK, m0);
+        } else if (!gather) {
+          const int cpb = p.g.C / BK, kb = kb0 + i, tap = kb / cpb, r = tap / p.g.KW;
+          const int img = m0 / (p.g.Ho * p.g.Wo), rem = m0 - img * (p.g.Ho * p.g.Wo), oh = rem / p.g.Wo, ow = rem - oh * p.g.Wo;
+          tc5::tma_load_im2col_4d(smem + s * STAGE, &map_a, &full_bar[s], (kb - tap * cpb) * BK, ow * p.g.sw - p.g.pw, oh * p.g.sh - p.g.ph, img,
+                                  tap - r * p.g.KW, r);
+        }
         if (i + 1 > issued) issued = i + 1;
       }
       if (*reinterpret_cast<volatile int*>(&failed)) {  // wait (bounded) for our own copies still in flight
@@ -337,7 +345,7 @@ __global__ void __launch_bounds__(192, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(cons
   } else {
     pdl_wait();   // residual, bias, split-K scratch and convolution inputs come from earlier kernels
     const int q = warp & 3;  // warps 2,3,4,5 -> TMEM lane quarters 2,3,0,1
-    if (CONV) {
+    if (gather) {
       // ---- A-operand gather: this thread owns tile row q*32+lane (the pixel it will also finish) ----
       constexpr int LAG = 2;   // k-blocks of copies kept in flight per thread
       const int row = q * 32 + lane;
@@ -523,20 +531,36 @@ __global__ void __launch_bounds__(192, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(cons
 // 128-wide tiles.  Roles: warp 0 TMA producer, warp 1 MMA issuer, warps 2-5 epilogue, and
 // for convolutions warps 6-9 gather the A tile (implicit GEMM) as in the kernel above.
 // ===========================================================================================
-template <int BN> struct PCfg {
+//
+// TS = true adds the bulk-copy epilogue for 16-bit outputs: the residual tile of tile i is
+// fetched by TMA into a shared-memory C buffer while tile i is still being multiplied; the
+// epilogue warps combine accumulator, bias and residual in that buffer (128-byte-swizzled
+// 64-column sub-tiles, conflict-free 16-byte accesses); a dedicated thread (warp 6) writes the
+// buffer out with TMA stores.  Residual reads and output writes are then large asynchronous
+// copies - what a memory-bound layer (1x1 convolution, K = 64..256) needs to keep enough
+// bytes in flight - instead of one dependent 32-byte access per thread and 16 columns.
+template <int BN, bool TS> struct PCfg {
   static constexpr int A_STAGE = BM * BK * 2, B_STAGE = BN * BK * 2, STAGE = A_STAGE + B_STAGE;
-  static constexpr int ST = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
-  static constexpr int SMEM = ST * STAGE + 1024;
+  static constexpr int ST = TS ? (BN == 256 ? 3 : (BN == 128 ? 4 : 6)) : (BN == 256 ? 4 : (BN == 128 ? 6 : 8));
+  static constexpr int CB = BM * BN * 2;               // one C buffer: BN/64 sub-tiles of [128 rows][128 bytes]
+  static constexpr int NCB = TS ? (BN == 256 ? 1 : 2) : 0;
+  static constexpr int SMEM = ST * STAGE + NCB * CB + 1024;
+  static constexpr int THREADS_LINEAR = TS ? 224 : 192;
 };
 
-template <typename T, int BN, bool CONV>
-__global__ void __launch_bounds__(CONV ? 320 : 192, 1) gemm_tc5p_kernel(const __grid_constant__ CUtensorMap map_a,
-                                                                       const __grid_constant__ CUtensorMap map_w, const Tc5Params p,
-                                                                       const int tiles_m, const int n_tiles) {
-  constexpr int ST = PCfg<BN>::ST, A_STAGE = PCfg<BN>::A_STAGE, B_STAGE = PCfg<BN>::B_STAGE, STAGE = PCfg<BN>::STAGE;
+template <typename T, int BN, bool CONV, bool TS>
+__global__ void __launch_bounds__(CONV ? 320 : PCfg<BN, TS>::THREADS_LINEAR, 1)
+    gemm_tc5p_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                     const __grid_constant__ CUtensorMap map_r, const __grid_constant__ CUtensorMap map_o, const Tc5Params p,
+                     const int tiles_m, const int n_tiles) {
+  constexpr int ST = PCfg<BN, TS>::ST, A_STAGE = PCfg<BN, TS>::A_STAGE, B_STAGE = PCfg<BN, TS>::B_STAGE, STAGE = PCfg<BN, TS>::STAGE;
+  constexpr int CB = PCfg<BN, TS>::CB, NCB = TS ? PCfg<BN, TS>::NCB : 1;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint8_t* cbuf = smem + ST * STAGE;
   __shared__ __align__(8) uint64_t full_bar[ST], empty_bar[ST], acc_full[2], acc_empty[2];
+  // C buffers: c_full = residual tile landed, c_ready = epilogue result written, c_free = store has read it
+  __shared__ __align__(8) uint64_t c_full[2], c_ready[2], c_free[2];
   __shared__ uint32_t tmem_holder;
   __shared__ int failed;
 
@@ -545,11 +569,13 @@ __global__ void __launch_bounds__(CONV ? 320 : 192, 1) gemm_tc5p_kernel(const __
 
   if (threadIdx.x == 0) {
     failed = 0;
-    for (int s = 0; s < ST; ++s) { tc5::mbar_init(&full_bar[s], CONV ? 129 : 1); tc5::mbar_init(&empty_bar[s], 1); }
+    for (int s = 0; s < ST; ++s) { tc5::mbar_init(&full_bar[s], (CONV && !p.g.im2col) ? 129 : 1); tc5::mbar_init(&empty_bar[s], 1); }
     for (int b = 0; b < 2; ++b) { tc5::mbar_init(&acc_full[b], 1); tc5::mbar_init(&acc_empty[b], 4); }
+    for (int b = 0; b < 2; ++b) { tc5::mbar_init(&c_full[b], 1); tc5::mbar_init(&c_ready[b], 4); tc5::mbar_init(&c_free[b], 1); }
     tc5::fence_barrier_init();
     tc5::prefetch_tensormap(&map_a);
     tc5::prefetch_tensormap(&map_w);
+    if (TS) { tc5::prefetch_tensormap(&map_o); if (p.residual) tc5::prefetch_tensormap(&map_r); }
   }
   if (warp == 1) { tc5::tmem_alloc(&tmem_holder, 2 * BN); tc5::tmem_relinquish(); }
   tc5::tc_fence_before();
@@ -562,14 +588,33 @@ __global__ void __launch_bounds__(CONV ? 320 : 192, 1) gemm_tc5p_kernel(const __
   if (warp == 0) {
     if (lane == 0) {
       pdl_wait();
-      int it = 0;
-      for (int tile = blockIdx.x; tile < n_tiles && !dead(); tile += gridDim.x) {
+      int it = 0, ti = 0;
+      for (int tile = blockIdx.x; tile < n_tiles && !dead(); tile += gridDim.x, ++ti) {
         const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+        if (TS && p.residual) {   // residual tile -> C buffer, once the store that last used the buffer has read it
+          const int cb = ti % NCB, u = ti / NCB;
+          if (!tc5::mbar_wait(&c_free[cb], (u & 1) ^ 1)) { failed = 1; atomicExch(&g_tc5_error, 16); break; }
+          tc5::mbar_arrive_expect_tx(&c_full[cb], CB);
+          for (int j = 0; j < BN / 64; ++j) tc5::tma_load_2d(cbuf + cb * CB + j * (BM * 128), &map_r, &c_full[cb], n0 + 64 * j, m0);
+        }
+        int cpb = 1, img = 0, base_w = 0, base_h = 0;   // convolution: first output pixel of the tile as a base position
+        if (CONV) {
+          cpb = p.g.C / BK;
+          img = m0 / (p.g.Ho * p.g.Wo);
+          const int rem = m0 - img * (p.g.Ho * p.g.Wo), oh = rem / p.g.Wo;
+          base_w = (rem - oh * p.g.Wo) * p.g.sw - p.g.pw;
+          base_h = oh * p.g.sh - p.g.ph;
+        }
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const int s = it % ST;
           if (!tc5::mbar_wait(&empty_bar[s], ((it / ST) & 1) ^ 1)) { failed = 1; atomicExch(&g_tc5_error, 11); break; }
-          tc5::mbar_arrive_expect_tx(&full_bar[s], CONV ? B_STAGE : STAGE);
-          if (!CONV) tc5::tma_load_2d(smem + s * STAGE, &map_a, &full_bar[s], kb * BK, m0);
+          tc5::mbar_arrive_expect_tx(&full_bar[s], (CONV && !p.g.im2col) ? B_STAGE : STAGE);
+          if (!CONV) {
+            tc5::tma_load_2d(smem + s * STAGE, &map_a, &full_bar[s], kb * BK, m0);
+          } else if (p.g.im2col) {
+            const int tap = kb / cpb, r = tap / p.g.KW;
+            tc5::tma_load_im2col_4d(smem + s * STAGE, &map_a, &full_bar[s], (kb - tap * cpb) * BK, base_w, base_h, img, tap - r * p.g.KW, r);
+          }
           tc5::tma_load_2d(smem + s * STAGE + A_STAGE, &map_w, &full_bar[s], kb * BK, n0);
         }
       }
@@ -617,7 +662,51 @@ __global__ void __launch_bounds__(CONV ? 320 : 192, 1) gemm_tc5p_kernel(const __
       tc5::tc_fence_after();
       const int64_t m = static_cast<int64_t>(m0) + q * 32 + lane;
       const uint32_t t_row = tmem_base + b * BN + (static_cast<uint32_t>(q * 32) << 16);
-      if (glu) {
+      if (TS) {
+        const int cb = ti % NCB, u = ti / NCB;
+        bool okc = true;   // residual landed / buffer free
+        if (lane == 0) okc = p.residual ? tc5::mbar_wait(&c_full[cb], u & 1) : tc5::mbar_wait(&c_free[cb], (u & 1) ^ 1);
+        okc = __shfl_sync(0xffffffffu, okc ? 1 : 0, 0) != 0;
+        if (!okc) { if (lane == 0) { failed = 1; atomicExch(&g_tc5_error, 17); } break; }
+        const int r = q * 32 + lane, swz = r & 7;
+        const uint32_t crow = tc5::smem_addr(cbuf + cb * CB) + r * 128;
+        const bool relu = (p.epilogue & B200_EPI_RELU) != 0, has_res = p.residual != nullptr;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 16) {
+          float v[16];
+          __syncwarp();
+          tc5::tmem_ld_32x16(t_row + c, v);
+          tc5::tmem_ld_wait();
+          const int64_t n = static_cast<int64_t>(n0) + c;
+          const int cnt = static_cast<int>(p.N - n < 16 ? (p.N - n < 0 ? 0 : p.N - n) : 16);
+          add_bias<16>(p, v, n, cnt);
+          const int k = (c & 63) >> 3;
+          const uint32_t a0 = crow + (c >> 6) * (BM * 128) + ((k ^ swz) << 4), a1 = crow + (c >> 6) * (BM * 128) + (((k + 1) ^ swz) << 4);
+          if (has_res) {
+            uint4 r0, r1;
+            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r0.x), "=r"(r0.y), "=r"(r0.z), "=r"(r0.w) : "r"(a0));
+            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r1.x), "=r"(r1.y), "=r"(r1.z), "=r"(r1.w) : "r"(a1));
+            float f0[8], f1[8];
+            unpack8<T>(r0, f0);
+            unpack8<T>(r1, f1);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { v[i] = round_as<T>(v[i]) + f0[i]; v[8 + i] = round_as<T>(v[8 + i]) + f1[i]; }
+          }
+          if (relu) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = fmaxf(v[i], 0.f);
+          }
+          float lo[8], hi[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) { lo[i] = v[i]; hi[i] = v[8 + i]; }
+          const uint4 o0 = pack8<T>(lo), o1 = pack8<T>(hi);
+          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a0), "r"(o0.x), "r"(o0.y), "r"(o0.z), "r"(o0.w) : "memory");
+          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a1), "r"(o1.x), "r"(o1.y), "r"(o1.z), "r"(o1.w) : "memory");
+        }
+        tc5::fence_proxy_async();   // the TMA store reads these generic-proxy writes
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&c_ready[cb]);
+      } else if (glu) {
 #pragma unroll 1
         for (int c = 0; c < BN / 2; c += 16) {   // c counts gate columns: block h = c / 64 of 128 merged columns
           float vg[16], vu[16];
@@ -644,7 +733,24 @@ __global__ void __launch_bounds__(CONV ? 320 : 192, 1) gemm_tc5p_kernel(const __
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[b]);   // this warp has drained its quarter of the accumulator
     }
-  } else if (CONV) {
+  } else if (TS) {
+    // ---- C-buffer store (one thread of warp 6) ----
+    if (warp == 6 && lane == 0) {
+      pdl_wait();   // the output buffer may still be read by the kernel before this one
+      int ti = 0;
+      for (int tile = blockIdx.x; tile < n_tiles && !dead(); tile += gridDim.x, ++ti) {
+        const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+        const int cb = ti % NCB, u = ti / NCB;
+        if (!tc5::mbar_wait(&c_ready[cb], u & 1)) { failed = 1; atomicExch(&g_tc5_error, 18); break; }
+        for (int j = 0; j < BN / 64; ++j)
+          if (n0 + 64 * j < p.N) tc5::tma_store_2d(&map_o, cbuf + cb * CB + j * (BM * 128), n0 + 64 * j, m0);
+        tc5::tma_store_commit();
+        tc5::tma_store_wait_read();
+        mbar_arrive(&c_free[cb]);
+      }
+      tc5::tma_store_wait_all();
+    }
+  } else if (CONV && !p.g.im2col) {
     // ---- A-operand gather (warps 6-9): thread r owns tile row r, i.e. one output pixel per tile ----
     constexpr int LAG = 2;
     const int row = (warp - 6) * 32 + lane;
@@ -721,6 +827,51 @@ bool make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t K, int64
   const cuuint32_t estr[2] = {1, 1};
   const CUtensorMapDataType dt = dtype == B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   return fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+typedef CUresult (*EncodeIm2colFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const int*,
+                                   const int*, cuuint32_t, cuuint32_t, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeIm2colFn encode_im2col_fn() {
+  static EncodeIm2colFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeIm2col", &p, 12000, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeIm2colFn>(p);
+  }
+  return fn;
+}
+
+bool conv_im2col_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("B200NN_CONV_IM2COL");
+    v = (e && e[0] == '0') ? 0 : 1;
+  }
+  return v == 1;
+}
+
+// NHWC activations [N, H, W, C] as an im2col-mode map: 64 channels x 128 output positions per
+// load, 128-byte swizzle, zero fill outside the image.  The bounding box of base positions runs
+// from -pad to (size - 1) + pad - (filter - 1) in each spatial dimension and is walked with the
+// convolution stride, so consecutive positions are consecutive output pixels.
+bool make_im2col_map(CUtensorMap* map, const void* x, const Tc5Conv& g, int dtype) {
+  EncodeIm2colFn fn = encode_im2col_fn();
+  if (!fn || !conv_im2col_enabled() || g.batch <= 0) return false;
+  if (g.ph > 127 || g.pw > 127 || g.KH > 128 || g.KW > 128 || g.sh > 8 || g.sw > 8) return false;
+  const cuuint64_t dims[4] = {static_cast<cuuint64_t>(g.C), static_cast<cuuint64_t>(g.W), static_cast<cuuint64_t>(g.H), static_cast<cuuint64_t>(g.batch)};
+  const cuuint64_t strides[3] = {static_cast<cuuint64_t>(g.C) * 2, static_cast<cuuint64_t>(g.W) * g.C * 2, static_cast<cuuint64_t>(g.H) * g.W * g.C * 2};
+  const int lower[2] = {-g.pw, -g.ph};
+  const int upper[2] = {g.pw - (g.KW - 1), g.ph - (g.KH - 1)};
+  const cuuint32_t estr[4] = {1, static_cast<cuuint32_t>(g.sw), static_cast<cuuint32_t>(g.sh), 1};
+  const CUtensorMapDataType dt = dtype == B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  return fn(map, dt, 4, const_cast<void*>(x), dims, strides, lower, upper, BK, BM, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -809,11 +960,15 @@ int launch(const Tc5Args& a, const Tc5Plan& plan, cudaStream_t st, const Tc5Conv
   const int SMEM = pl.splits > 1 ? SMEM_SPLIT : SMEM_RING;
   CUtensorMap ma, mw;
   if (!make_map(&mw, a.W, a.N, a.K, a.ldw, BN, a.dtype)) return B200_ENOTSUP;
-  if (CONV) ma = mw;   // unused in implicit-GEMM mode
-  else if (!make_map(&ma, a.A, a.M, a.K, a.lda, Cfg<BN, MODE>::AROWS, a.dtype)) return B200_ENOTSUP;
   Tc5Params p;
   p.x = a.A;
   p.g = g ? *g : Tc5Conv{};
+  if (CONV) {
+    p.g.im2col = make_im2col_map(&ma, a.A, p.g, a.dtype) ? 1 : 0;
+    if (!p.g.im2col) ma = mw;   // unused: the epilogue warps gather the A tile
+  } else if (!make_map(&ma, a.A, a.M, a.K, a.lda, Cfg<BN, MODE>::AROWS, a.dtype)) {
+    return B200_ENOTSUP;
+  }
   p.bias = a.bias; p.residual = a.residual; p.aux = a.aux; p.out = a.out;
   p.M = a.M; p.N = a.N; p.K = a.K; p.ldo = a.ldo; p.ldr = a.ldr; p.ldaux = a.ldaux;
   p.bias_dtype = a.bias_dtype; p.epilogue = a.epilogue; p.splits = pl.splits; p.kb_per_split = pl.kb_per_split;
@@ -848,40 +1003,53 @@ int launch(const Tc5Args& a, const Tc5Plan& plan, cudaStream_t st, const Tc5Conv
   return B200_OK;
 }
 
-template <typename T, int BN, bool CONV>
+template <typename T, int BN, bool CONV, bool TS>
 int launch_persistent(const Tc5Args& a, cudaStream_t st, const Tc5Conv* g = nullptr) {
-  constexpr int SMEM = PCfg<BN>::SMEM;
+  constexpr int SMEM = PCfg<BN, TS>::SMEM;
+  static_assert(SMEM <= 227 * 1024, "ring + C buffers exceed the shared memory of an SM");
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(gemm_tc5p_kernel<T, BN, CONV>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) {
+    if (cudaFuncSetAttribute(gemm_tc5p_kernel<T, BN, CONV, TS>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) {
       cudaGetLastError();
       return B200_ENOTSUP;
     }
     configured = true;
   }
-  CUtensorMap ma, mw;
+  CUtensorMap ma, mw, mr, mo;
   if (!make_map(&mw, a.W, a.N, a.K, a.ldw, BN, a.dtype)) return B200_ENOTSUP;
-  if (CONV) ma = mw;
-  else if (!make_map(&ma, a.A, a.M, a.K, a.lda, BM, a.dtype)) return B200_ENOTSUP;
   Tc5Params p;
+  p.g = g ? *g : Tc5Conv{};
+  if (CONV) {
+    p.g.im2col = make_im2col_map(&ma, a.A, p.g, a.dtype) ? 1 : 0;
+    if (!p.g.im2col) {
+      if (TS) return B200_ENOTSUP;   // warp 6 cannot both gather and store
+      ma = mw;
+    }
+  } else if (!make_map(&ma, a.A, a.M, a.K, a.lda, BM, a.dtype)) {
+    return B200_ENOTSUP;
+  }
+  mr = mw; mo = mw;
+  if (TS) {   // output (and residual) as [M, N] maps with 64-column x 128-row boxes
+    if (!make_map(&mo, a.out, a.M, a.N, a.ldo, BM, a.dtype)) return B200_ENOTSUP;
+    if (a.residual && !make_map(&mr, a.residual, a.M, a.N, a.ldr, BM, a.dtype)) return B200_ENOTSUP;
+  }
   p.bias = a.bias; p.residual = a.residual; p.aux = a.aux; p.out = a.out;
   p.M = a.M; p.N = a.N; p.K = a.K; p.ldo = a.ldo; p.ldr = a.ldr; p.ldaux = a.ldaux;
   p.bias_dtype = a.bias_dtype; p.epilogue = a.epilogue; p.splits = 1; p.kb_per_split = static_cast<int>(ceil_div(a.K, BK));
   p.x = a.A;
-  p.g = g ? *g : Tc5Conv{};
   p.trace_slot = 0;
   const int64_t tiles_m = ceil_div(a.M, BM), tiles = tiles_m * ceil_div(a.N, BN);
   if (tiles >= (1ll << 31)) return B200_ENOTSUP;
   const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
-  launch_pdl(gemm_tc5p_kernel<T, BN, CONV>, dim3(grid), dim3(CONV ? 320 : 192), SMEM, st, ma, mw, p, static_cast<int>(tiles_m),
-             static_cast<int>(tiles));
+  launch_pdl(gemm_tc5p_kernel<T, BN, CONV, TS>, dim3(grid), dim3(CONV ? 320 : PCfg<BN, TS>::THREADS_LINEAR), SMEM, st, ma, mw, mr, mo, p,
+             static_cast<int>(tiles_m), static_cast<int>(tiles));
   B200_CHECK_LAUNCH("gemm_tc5p_kernel");
   return B200_OK;
 }
 
 // Tile width of the persistent kernel for a shape, or 0 when the shape should stay on the
 // one-tile-per-CTA kernel (too few tiles to fill the SMs with wide tiles).
-int persistent_bn(int64_t M, int64_t N, bool glu) {
+int persistent_bn(int64_t M, int64_t N, int64_t K, bool glu) {
   static int enabled = -1;
   if (enabled < 0) {
     const char* e = getenv("B200NN_TC5_PERSISTENT");
@@ -889,21 +1057,40 @@ int persistent_bn(int64_t M, int64_t N, bool glu) {
   }
   const int64_t tm = ceil_div(M, BM);
   if (!enabled || tm < 2) return 0;
-  if (ceil_div(N, 256) * tm >= 2 * 148) return 256;
+  // short reductions are memory-bound: 128-wide tiles leave room for two C buffers (see PCfg)
+  if (K > 512 && ceil_div(N, 256) * tm >= 2 * 148) return 256;
   if (ceil_div(N, 128) * tm >= 148) return 128;
   if (!glu && ceil_div(N, 64) * tm >= 148) return 64;
   return 0;
 }
 
-template <bool CONV> int dispatch_persistent(int bn, const Tc5Args& a, cudaStream_t st, const Tc5Conv* g) {
-  if (a.dtype == B200_BF16) {
-    if (bn == 256) return launch_persistent<__nv_bfloat16, 256, CONV>(a, st, g);
-    if (bn == 128) return launch_persistent<__nv_bfloat16, 128, CONV>(a, st, g);
-    return launch_persistent<__nv_bfloat16, 64, CONV>(a, st, g);
+// The bulk-copy epilogue handles 16-bit outputs with bias, residual and ReLU.
+bool tma_store_ok(const Tc5Args& a) {
+  static int enabled = -1;
+  if (enabled < 0) {
+    const char* e = getenv("B200NN_TC5_TMA_STORE");
+    enabled = (e && e[0] == '0') ? 0 : 1;
   }
-  if (bn == 256) return launch_persistent<__half, 256, CONV>(a, st, g);
-  if (bn == 128) return launch_persistent<__half, 128, CONV>(a, st, g);
-  return launch_persistent<__half, 64, CONV>(a, st, g);
+  if (!enabled || (a.epilogue & (B200_EPI_GLU | B200_EPI_SILU_MUL))) return false;
+  if (!aligned16(a.out) || a.ldo % 8 || a.N % 8) return false;
+  if (a.residual && (!aligned16(a.residual) || a.ldr % 8)) return false;
+  return true;
+}
+
+template <typename T, bool CONV> int dispatch_persistent_t(int bn, bool ts, const Tc5Args& a, cudaStream_t st, const Tc5Conv* g) {
+  if (ts) {
+    int rc = bn == 256 ? launch_persistent<T, 256, CONV, true>(a, st, g) : bn == 128 ? launch_persistent<T, 128, CONV, true>(a, st, g)
+                                                                                     : launch_persistent<T, 64, CONV, true>(a, st, g);
+    if (rc != B200_ENOTSUP) return rc;
+  }
+  return bn == 256 ? launch_persistent<T, 256, CONV, false>(a, st, g) : bn == 128 ? launch_persistent<T, 128, CONV, false>(a, st, g)
+                                                                                  : launch_persistent<T, 64, CONV, false>(a, st, g);
+}
+
+template <bool CONV> int dispatch_persistent(int bn, const Tc5Args& a, cudaStream_t st, const Tc5Conv* g) {
+  const bool ts = tma_store_ok(a);
+  if (a.dtype == B200_BF16) return dispatch_persistent_t<__nv_bfloat16, CONV>(bn, ts, a, st, g);
+  return dispatch_persistent_t<__half, CONV>(bn, ts, a, st, g);
 }
 
 }  // namespace
@@ -927,7 +1114,7 @@ int linear_tc5(const Tc5Args& a, cudaStream_t st) {
   if (a.M >= (1ll << 31) || a.N >= (1ll << 31) || a.K >= (1ll << 31)) return B200_ENOTSUP;
   const bool glu = (a.epilogue & B200_EPI_GLU) != 0;
   if (glu && (a.N % 128 || (a.epilogue & ~(B200_EPI_GLU | B200_EPI_W_STATIC)) || a.residual)) return B200_ENOTSUP;
-  if (const int bn = persistent_bn(a.M, a.N, glu)) return dispatch_persistent<false>(bn, a, st, nullptr);
+  if (const int bn = persistent_bn(a.M, a.N, a.K, glu)) return dispatch_persistent<false>(bn, a, st, nullptr);
   const Tc5Plan pl = plan_tc5(a.M, a.N, a.K, glu);
   if (pl.tiles_m > 65535 || pl.splits > 65535) return B200_ENOTSUP;
   if (pl.tiles_m == 1 && a.M <= 64 && decode_deep()) {
@@ -951,7 +1138,7 @@ int conv_tc5(const Tc5Args& a, const Tc5Conv& g, cudaStream_t st) {
   if (a.dtype != B200_BF16 && a.dtype != B200_F16) return B200_ENOTSUP;
   if (g.C % BK || a.K != static_cast<int64_t>(g.KH) * g.KW * g.C || a.ldw % 8 || !aligned16(a.A) || !aligned16(a.W)) return B200_ENOTSUP;
   if (a.M >= (1ll << 31) || a.N >= (1ll << 31) || (a.epilogue & ~(B200_EPI_RELU | B200_EPI_W_STATIC))) return B200_ENOTSUP;
-  if (const int bn = persistent_bn(a.M, a.N, false)) return dispatch_persistent<true>(bn, a, st, &g);
+  if (const int bn = persistent_bn(a.M, a.N, a.K, false)) return dispatch_persistent<true>(bn, a, st, &g);
   Tc5Plan pl;
   pl.bn = a.N >= 128 ? 128 : 64;
   pl.tiles_n = ceil_div(a.N, pl.bn);

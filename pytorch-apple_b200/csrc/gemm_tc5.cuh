@@ -16,6 +16,8 @@ struct Tc5Args {
 // k runs over (filter row, filter column, channel)).
 struct Tc5Conv {
   int H, W, C, KH, KW, sh, sw, ph, pw, Ho, Wo;
+  int batch = 0;    // images
+  int im2col = 0;   // set by conv_tc5: the A tile comes from an im2col-mode tensor map (else gathered by threads)
 };
 
 // y = epi(conv(x, w) + bias + residual) on the tcgen05 path; needs C % 64 == 0.

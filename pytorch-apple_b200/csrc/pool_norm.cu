@@ -48,6 +48,37 @@ __global__ void __launch_bounds__(256) max_pool2d_kernel(const __grid_constant__
   store_from_f32(p.y, n * p.ys[0] + c * p.ys[1] + oh * p.ys[2] + ow * p.ys[3], p.y_dtype, best);
 }
 
+// Channels-last fast path: one thread owns 8 consecutive channels (16 bytes) of one output
+// pixel; every tap is one 128-bit load.  NaN propagates as in the generic kernel.
+template <typename T>
+__global__ void __launch_bounds__(256) max_pool2d_cl8_kernel(const __grid_constant__ Pool4D p) {
+  const int c8 = static_cast<int>(p.C / 8);
+  const int64_t total = p.N * p.OH * p.OW * c8;
+  int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int c = static_cast<int>(i % c8) * 8; i /= c8;
+  const int ow = static_cast<int>(i % p.OW); i /= p.OW;
+  const int oh = static_cast<int>(i % p.OH);
+  const int64_t n = i / p.OH;
+  const T* xb = static_cast<const T*>(p.x) + n * p.xs[0] + c;
+  float best[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) best[k] = -INFINITY;
+  for (int r = 0; r < p.kh; ++r) {
+    const int ih = oh * p.sh - p.ph + r;
+    if (ih < 0 || ih >= p.H) continue;
+    for (int s = 0; s < p.kw; ++s) {
+      const int iw = ow * p.sw - p.pw + s;
+      if (iw < 0 || iw >= p.W) continue;
+      float v[8];
+      unpack8<T>(ld_global_nc_v4(xb + ih * p.xs[2] + iw * p.xs[3]), v);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) best[k] = (v[k] > best[k] || v[k] != v[k]) ? v[k] : best[k];
+    }
+  }
+  *reinterpret_cast<uint4*>(static_cast<T*>(p.y) + n * p.ys[0] + oh * p.ys[2] + ow * p.ys[3] + c) = pack8<T>(best);
+}
+
 __global__ void __launch_bounds__(256) adaptive_avg_pool2d_kernel(const __grid_constant__ Pool4D p) {
   const int64_t total = p.N * p.C * p.OH * p.OW;
   const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -132,6 +163,15 @@ extern "C" int b200_max_pool2d(const b200_tensor* x, const b200_tensor* y, int k
   p.kh = kh; p.kw = kw; p.sh = sh; p.sw = sw; p.ph = ph; p.pw = pw;
   const int64_t total = p.N * p.C * p.OH * p.OW;
   if (total == 0) return B200_OK;
+  const bool half_types = p.x_dtype == p.y_dtype && (p.x_dtype == B200_F16 || p.x_dtype == B200_BF16);
+  if (half_types && p.channels_last && p.C % 8 == 0 && p.xs[1] == 1 && p.ys[1] == 1 && aligned16(p.x) && aligned16(p.y) &&
+      p.xs[0] % 8 == 0 && p.xs[2] % 8 == 0 && p.xs[3] % 8 == 0 && p.ys[0] % 8 == 0 && p.ys[2] % 8 == 0 && p.ys[3] % 8 == 0) {
+    const unsigned blocks = static_cast<unsigned>(ceil_div(total / 8, 256));
+    if (p.x_dtype == B200_F16) max_pool2d_cl8_kernel<__half><<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    else max_pool2d_cl8_kernel<__nv_bfloat16><<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    B200_CHECK_LAUNCH("max_pool2d_cl8_kernel");
+    return B200_OK;
+  }
   max_pool2d_kernel<<<static_cast<unsigned>(ceil_div(total, 256)), 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
   B200_CHECK_LAUNCH("max_pool2d_kernel");
   return B200_OK;

@@ -49,6 +49,27 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(smem_addr(smem_dst)), "l"(map), "r"(smem_addr(bar)), "r"(c0), "r"(c1) : "memory");
 }
+// Im2col-mode load of an NHWC tensor: `pixels` consecutive output positions (raster order over
+// W, H, N inside the bounding box of the map) starting at base position (w, h, n), each read at
+// offset (off_w, off_h) = filter tap; c is the first channel (c * elem_size a multiple of 16
+// bytes).  Positions outside the image read as zero.  The tile lands as [pixels][64 channels]
+// with the map's swizzle - the same layout the 2-D tiled load produces.
+__device__ __forceinline__ void tma_load_im2col_4d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c, int w, int h, int n,
+                                                   int off_w, int off_h) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};"
+      ::"r"(smem_addr(smem_dst)), "l"(map), "r"(smem_addr(bar)), "r"(c), "r"(w), "r"(h), "r"(n),
+        "h"(static_cast<unsigned short>(off_w)), "h"(static_cast<unsigned short>(off_h)) : "memory");
+}
+// 2-D tiled store shared -> global (bulk async group); rows / columns outside the tensor are clipped.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* smem_src, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(map), "r"(smem_addr(smem_src)), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// all committed stores have finished READING shared memory (the buffers may be overwritten)
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }

@@ -142,6 +142,9 @@ def test_linear_rejects_unaligned(lib):
     (2, 64, 56, 128, 1, 2, 0, False, False),
     (3, 256, 14, 1024, 1, 1, 0, True, True),
     (1, 512, 7, 512, 3, 1, 1, False, True),
+    (8, 64, 56, 64, 3, 1, 1, True, True),      # enough tiles for the persistent kernel, tiles cross image borders
+    (32, 64, 56, 128, 3, 2, 1, False, True),   # persistent, stride 2
+    (5, 128, 28, 128, 3, 1, 1, False, False),  # odd image count: the last tile runs past the tensor
 ])
 def test_conv2d_nhwc(lib, N, C, H, O, k, s, p, res, relu):
     dtype = torch.float16
