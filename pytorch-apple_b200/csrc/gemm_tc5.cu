@@ -69,8 +69,15 @@ __device__ __forceinline__ unsigned long long globaltimer_ns() {
     const int cta_ = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);              \
     if (cta_ < TR_CTAS) g_tc5_trace[p.trace_slot][cta_][i] = globaltimer_ns();                   \
   } while (0)
+constexpr int PTR_CTAS = 160, PTR_TILES = 12, PTR_N = 8;
+__device__ unsigned long long g_tc5p_trace[PTR_CTAS][PTR_TILES][PTR_N];
+#define TC5P_STAMP(ti_, i)                                                                              \
+  do {                                                                                                  \
+    if (blockIdx.x < PTR_CTAS && (ti_) < PTR_TILES) g_tc5p_trace[blockIdx.x][ti_][i] = globaltimer_ns(); \
+  } while (0)
 #else
 #define TC5_STAMP(i)
+#define TC5P_STAMP(ti_, i)
 #endif
 
 struct Tc5Params {
@@ -591,6 +598,7 @@ __global__ void __launch_bounds__(CONV ? 320 : PCfg<BN, TS>::THREADS_LINEAR, 1)
       int it = 0, ti = 0;
       for (int tile = blockIdx.x; tile < n_tiles && !dead(); tile += gridDim.x, ++ti) {
         const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+        TC5P_STAMP(ti, 5);   // producer: tile started
         if (TS && p.residual) {   // residual tile -> C buffer, once the store that last used the buffer has read it
           const int cb = ti % NCB, u = ti / NCB;
           if (!tc5::mbar_wait(&c_free[cb], (u & 1) ^ 1)) { failed = 1; atomicExch(&g_tc5_error, 16); break; }
@@ -643,6 +651,7 @@ __global__ void __launch_bounds__(CONV ? 320 : PCfg<BN, TS>::THREADS_LINEAR, 1)
         }
         if (dead()) break;
         tc5::umma_commit(&acc_full[b]);
+        TC5P_STAMP(ti, 6);   // MMA: all k-blocks of the tile issued
       }
     }
   } else if (warp < 6) {
@@ -662,50 +671,68 @@ __global__ void __launch_bounds__(CONV ? 320 : PCfg<BN, TS>::THREADS_LINEAR, 1)
       tc5::tc_fence_after();
       const int64_t m = static_cast<int64_t>(m0) + q * 32 + lane;
       const uint32_t t_row = tmem_base + b * BN + (static_cast<uint32_t>(q * 32) << 16);
+      if (warp == 2 && lane == 0) TC5P_STAMP(ti, 0);   // accumulator ready
       if (TS) {
         const int cb = ti % NCB, u = ti / NCB;
         bool okc = true;   // residual landed / buffer free
         if (lane == 0) okc = p.residual ? tc5::mbar_wait(&c_full[cb], u & 1) : tc5::mbar_wait(&c_free[cb], (u & 1) ^ 1);
         okc = __shfl_sync(0xffffffffu, okc ? 1 : 0, 0) != 0;
         if (!okc) { if (lane == 0) { failed = 1; atomicExch(&g_tc5_error, 17); } break; }
+        if (warp == 2 && lane == 0) TC5P_STAMP(ti, 1);   // C buffer ready
         const int r = q * 32 + lane, swz = r & 7;
         const uint32_t crow = tc5::smem_addr(cbuf + cb * CB) + r * 128;
         const bool relu = (p.epilogue & B200_EPI_RELU) != 0, has_res = p.residual != nullptr;
-#pragma unroll 1
-        for (int c = 0; c < BN; c += 16) {
-          float v[16];
-          __syncwarp();
-          tc5::tmem_ld_32x16(t_row + c, v);
-          tc5::tmem_ld_wait();
+        // one 16-column unit: bias in fp32, then packed 16-bit pairs (one conversion per pair; the
+        // residual add and the ReLU are exact in packed arithmetic) - conversions are quarter-rate
+        const bool bias_f32_vec = p.bias && p.bias_dtype == B200_F32 && (reinterpret_cast<uintptr_t>(p.bias) & 15u) == 0 && (n0 & 3) == 0;
+        auto unit = [&](float (&v)[16], int c) {
           const int64_t n = static_cast<int64_t>(n0) + c;
-          const int cnt = static_cast<int>(p.N - n < 16 ? (p.N - n < 0 ? 0 : p.N - n) : 16);
-          add_bias<16>(p, v, n, cnt);
+          if (bias_f32_vec && n + 16 <= p.N) {
+            const float4* bp = reinterpret_cast<const float4*>(static_cast<const float*>(p.bias) + n);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float4 bv = __ldg(bp + i);
+              v[4 * i] += bv.x; v[4 * i + 1] += bv.y; v[4 * i + 2] += bv.z; v[4 * i + 3] += bv.w;
+            }
+          } else {
+            const int cnt = static_cast<int>(p.N - n < 16 ? (p.N - n < 0 ? 0 : p.N - n) : 16);
+            add_bias<16>(p, v, n, cnt);
+          }
           const int k = (c & 63) >> 3;
           const uint32_t a0 = crow + (c >> 6) * (BM * 128) + ((k ^ swz) << 4), a1 = crow + (c >> 6) * (BM * 128) + (((k + 1) ^ swz) << 4);
-          if (has_res) {
-            uint4 r0, r1;
-            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r0.x), "=r"(r0.y), "=r"(r0.z), "=r"(r0.w) : "r"(a0));
-            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r1.x), "=r"(r1.y), "=r"(r1.z), "=r"(r1.w) : "r"(a1));
-            float f0[8], f1[8];
-            unpack8<T>(r0, f0);
-            unpack8<T>(r1, f1);
+          uint32_t o[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) { v[i] = round_as<T>(v[i]) + f0[i]; v[8 + i] = round_as<T>(v[8 + i]) + f1[i]; }
+          for (int i = 0; i < 8; ++i) o[i] = pack2<T>(v[2 * i], v[2 * i + 1]);
+          if (has_res) {
+            uint32_t r[8];
+            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a0));
+            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]) : "r"(a1));
+#pragma unroll
+            for (int i = 0; i < 8; ++i) o[i] = add2<T>(o[i], r[i]);
           }
           if (relu) {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) v[i] = fmaxf(v[i], 0.f);
+            for (int i = 0; i < 8; ++i) o[i] = relu2<T>(o[i]);
           }
-          float lo[8], hi[8];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) { lo[i] = v[i]; hi[i] = v[8 + i]; }
-          const uint4 o0 = pack8<T>(lo), o1 = pack8<T>(hi);
-          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a0), "r"(o0.x), "r"(o0.y), "r"(o0.z), "r"(o0.w) : "memory");
-          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a1), "r"(o1.x), "r"(o1.y), "r"(o1.z), "r"(o1.w) : "memory");
+          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a0), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
+          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a1), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]) : "memory");
+        };
+        float va[16], vb[16];   // two units in flight: the next tcgen05.ld runs under the current unit's math
+        __syncwarp();
+        tc5::tmem_ld_32x16(t_row, va);
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          tc5::tmem_ld_wait();
+          tc5::tmem_ld_32x16(t_row + c + 16, vb);
+          unit(va, c);
+          tc5::tmem_ld_wait();
+          if (c + 32 < BN) tc5::tmem_ld_32x16(t_row + c + 32, va);
+          unit(vb, c + 16);
         }
         tc5::fence_proxy_async();   // the TMA store reads these generic-proxy writes
         __syncwarp();
         if (lane == 0) mbar_arrive(&c_ready[cb]);
+        if (warp == 2 && lane == 0) TC5P_STAMP(ti, 2);   // tile written to the C buffer
       } else if (glu) {
 #pragma unroll 1
         for (int c = 0; c < BN / 2; c += 16) {   // c counts gate columns: block h = c / 64 of 128 merged columns
@@ -742,11 +769,13 @@ __global__ void __launch_bounds__(CONV ? 320 : PCfg<BN, TS>::THREADS_LINEAR, 1)
         const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
         const int cb = ti % NCB, u = ti / NCB;
         if (!tc5::mbar_wait(&c_ready[cb], u & 1)) { failed = 1; atomicExch(&g_tc5_error, 18); break; }
+        TC5P_STAMP(ti, 3);   // store thread: buffer complete
         for (int j = 0; j < BN / 64; ++j)
           if (n0 + 64 * j < p.N) tc5::tma_store_2d(&map_o, cbuf + cb * CB + j * (BM * 128), n0 + 64 * j, m0);
         tc5::tma_store_commit();
         tc5::tma_store_wait_read();
         mbar_arrive(&c_free[cb]);
+        TC5P_STAMP(ti, 4);   // store thread: buffer read out
       }
       tc5::tma_store_wait_all();
     }
@@ -1072,6 +1101,7 @@ bool tma_store_ok(const Tc5Args& a) {
     enabled = (e && e[0] == '0') ? 0 : 1;
   }
   if (!enabled || (a.epilogue & (B200_EPI_GLU | B200_EPI_SILU_MUL))) return false;
+  if (a.K > 2048) return false;   // long reductions hide the plain epilogue and prefer the deeper ring
   if (!aligned16(a.out) || a.ldo % 8 || a.N % 8) return false;
   if (a.residual && (!aligned16(a.residual) || a.ldr % 8)) return false;
   return true;
@@ -1153,6 +1183,9 @@ int conv_tc5(const Tc5Args& a, const Tc5Conv& g, cudaStream_t st) {
 }  // namespace b200
 
 #ifdef B200NN_TC5_TRACE
+extern "C" int b200_debug_tc5p_trace(unsigned long long* host_out) {
+  return cudaMemcpyFromSymbol(host_out, b200::g_tc5p_trace, sizeof(unsigned long long) * b200::PTR_CTAS * b200::PTR_TILES * b200::PTR_N) == cudaSuccess ? B200_OK : B200_ELAUNCH;
+}
 extern "C" int b200_debug_tc5_trace(unsigned long long* host_out) {
   return cudaMemcpyFromSymbol(host_out, b200::g_tc5_trace, sizeof(unsigned long long) * b200::TR_SLOTS * b200::TR_CTAS * b200::TR_N) == cudaSuccess ? B200_OK : B200_ELAUNCH;
 }

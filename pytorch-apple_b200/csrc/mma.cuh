@@ -65,6 +65,27 @@ template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, f
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
+// Packed 16-bit pair arithmetic on raw registers.  a + b rounds the exact sum once, which is
+// what adding two 16-bit tensors in fp32 and rounding the result gives; max is maxNum.
+template <typename T> __device__ __forceinline__ uint32_t add2(uint32_t a, uint32_t b);
+template <> __device__ __forceinline__ uint32_t add2<__half>(uint32_t a, uint32_t b) {
+  const __half2 r = __hadd2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+template <> __device__ __forceinline__ uint32_t add2<__nv_bfloat16>(uint32_t a, uint32_t b) {
+  const __nv_bfloat162 r = __hadd2(*reinterpret_cast<const __nv_bfloat162*>(&a), *reinterpret_cast<const __nv_bfloat162*>(&b));
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+template <typename T> __device__ __forceinline__ uint32_t relu2(uint32_t a);
+template <> __device__ __forceinline__ uint32_t relu2<__half>(uint32_t a) {
+  const __half2 r = __hmax2(*reinterpret_cast<const __half2*>(&a), __float2half2_rn(0.f));
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+template <> __device__ __forceinline__ uint32_t relu2<__nv_bfloat16>(uint32_t a) {
+  const __nv_bfloat162 r = __hmax2(*reinterpret_cast<const __nv_bfloat162*>(&a), __float2bfloat162_rn(0.f));
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+
 // inverse of pack2
 template <typename T> __device__ __forceinline__ void unpack2(uint32_t raw, float& lo, float& hi);
 template <> __device__ __forceinline__ void unpack2<__half>(uint32_t raw, float& lo, float& hi) {

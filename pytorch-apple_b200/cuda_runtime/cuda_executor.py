@@ -126,6 +126,44 @@ class CUDAExecutor:
         stream.synchronize()
         return [(name, a.elapsed_time(b)) for name, a, b in events]
 
+    def profile_entry(self, inputs: dict[str, Any], weights: dict[str, Any], entry: str, iters: int = 10) -> tuple[int, float]:
+        """Time only the calls of one entry point: they are captured, in program order, into a
+        CUDA graph of their own, and replays of that graph are timed with CUDA events on the
+        launching stream (no host time between the launches).  Returns ``(calls per replay,
+        mean milliseconds per call)``.  The calls read whatever their input buffers hold and
+        write their usual outputs, so run it after the measurement proper, not in between."""
+        if not self._on_gpu:
+            raise RuntimeError("profile_entry() needs a CUDA device")
+        if self._weights_id != id(weights) or len(weights) != self._weights_len:
+            self._load_weights(weights)
+        tensors = {n: inputs[n].native_handle for n in self._input_names if n in inputs}
+        plan = self._bind(tensors)
+        calls = [(fn, args) for fn, args in plan.launches if fn.__name__ == entry]
+        if not calls:
+            return 0, 0.0
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            for fn, args in calls:   # warm-up outside the capture (one-off set-up inside the library)
+                native.check(fn(*args, side.cuda_stream), entry)
+            side.synchronize()
+            with torch.cuda.graph(graph, stream=side):
+                for fn, args in calls:
+                    native.check(fn(*args, torch.cuda.current_stream().cuda_stream), entry)
+        torch.cuda.synchronize()
+        stream = torch.cuda.current_stream()
+        graph.replay()
+        times = []
+        for _ in range(iters):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            graph.replay()
+            b.record(stream)
+            stream.synchronize()
+            times.append(a.elapsed_time(b))
+        return len(calls), float(sum(times) / len(times) / len(calls))
+
     # --------------------------------------------------------------- launching
     def _stream_ptr(self) -> int:
         return torch.cuda.current_stream().cuda_stream if self._on_gpu else 0
