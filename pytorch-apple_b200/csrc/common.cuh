@@ -124,17 +124,51 @@ __device__ __forceinline__ int64_t load_index(const void* p, int64_t i, int dt) 
 // ---- 128-bit packs of 16-bit floats -------------------------------------------
 template <typename T> struct Pack8 { uint4 raw; };  // 8 x 16-bit
 
-template <typename T> __device__ __forceinline__ void unpack8(const uint4& raw, float (&f)[8]) {
-  const T* h = reinterpret_cast<const T*>(&raw);
+// Conversions run at a quarter of the ALU rate, so pairs go through the packed forms: one
+// cvt.rn.{f16x2,bf16x2}.f32 per two values on the way out; bf16 -> f32 is a shift / mask.
+template <typename T> __device__ __forceinline__ void unpack8(const uint4& raw, float (&f)[8]);
+template <> __device__ __forceinline__ void unpack8<__half>(const uint4& raw, float (&f)[8]) {
+  const __half2* h = reinterpret_cast<const __half2*>(&raw);
 #pragma unroll
-  for (int i = 0; i < 8; ++i) f[i] = to_f32<T>(h[i]);
+  for (int i = 0; i < 4; ++i) {
+    const float2 v = __half22float2(h[i]);
+    f[2 * i] = v.x; f[2 * i + 1] = v.y;
+  }
 }
-template <typename T> __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
-  uint4 raw;
-  T* h = reinterpret_cast<T*>(&raw);
+template <> __device__ __forceinline__ void unpack8<__nv_bfloat16>(const uint4& raw, float (&f)[8]) {
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
-  for (int i = 0; i < 8; ++i) h[i] = from_f32<T>(f[i]);
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __uint_as_float(w[i] << 16);
+    f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+template <typename T> __device__ __forceinline__ uint4 pack8(const float (&f)[8]);
+template <> __device__ __forceinline__ uint4 pack8<__half>(const float (&f)[8]) {
+  uint4 raw;
+  __half2* h = reinterpret_cast<__half2*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
   return raw;
+}
+template <> __device__ __forceinline__ uint4 pack8<__nv_bfloat16>(const float (&f)[8]) {
+  uint4 raw;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return raw;
+}
+// round two values to T and back (what storing them as T and reloading would give)
+template <typename T> __device__ __forceinline__ void round2(float& a, float& b);
+template <> __device__ __forceinline__ void round2<__half>(float& a, float& b) {
+  const float2 v = __half22float2(__floats2half2_rn(a, b));
+  a = v.x; b = v.y;
+}
+template <> __device__ __forceinline__ void round2<__nv_bfloat16>(float& a, float& b) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  const uint32_t w = *reinterpret_cast<const uint32_t*>(&h);
+  a = __uint_as_float(w << 16);
+  b = __uint_as_float(w & 0xffff0000u);
 }
 
 __device__ __forceinline__ uint4 ld_global_nc_v4(const void* p) {

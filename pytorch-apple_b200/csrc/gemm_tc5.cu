@@ -163,7 +163,10 @@ __device__ __forceinline__ void finish_cols(const Tc5Params& p, float (&v)[CNT],
     float r[CNT];
     load_cols<T, CNT>(static_cast<const T*>(p.residual), p.ldr, m, n, cnt, r);
 #pragma unroll
-    for (int i = 0; i < CNT; ++i) v[i] = round_as<T>(v[i]) + r[i];
+    for (int i = 0; i < CNT; i += 2) {
+      round2<T>(v[i], v[i + 1]);
+      v[i] += r[i]; v[i + 1] += r[i + 1];
+    }
   }
   if (p.epilogue & B200_EPI_RELU) {
 #pragma unroll
@@ -185,7 +188,14 @@ __device__ __forceinline__ void finish_glu_cols(const Tc5Params& p, float (&g)[C
   add_bias<CNT>(p, g, n_merged, CNT);
   add_bias<CNT>(p, u, n_merged + 64, CNT);
 #pragma unroll
-  for (int i = 0; i < CNT; ++i) g[i] = round_as<T>(silu_f32(round_as<T>(g[i]))) * round_as<T>(u[i]);
+  for (int i = 0; i < CNT; i += 2) {   // pairs: the three roundings to T go through packed conversions
+    float g0 = g[i], g1 = g[i + 1], u0 = u[i], u1 = u[i + 1];
+    round2<T>(g0, g1);
+    g0 = silu_f32(g0); g1 = silu_f32(g1);
+    round2<T>(g0, g1);
+    round2<T>(u0, u1);
+    g[i] = g0 * u0; g[i + 1] = g1 * u1;
+  }
   store_cols<T, CNT>(static_cast<T*>(p.out) + m * p.ldo + n_out, g, CNT);
 }
 
@@ -221,7 +231,14 @@ __device__ __forceinline__ void finish_glu4(const Tc5Params& p, const float4& ga
   add_bias<4>(p, g, n_merged, 4);
   add_bias<4>(p, u, n_merged + 64, 4);
 #pragma unroll
-  for (int i = 0; i < 4; ++i) g[i] = round_as<T>(silu_f32(round_as<T>(g[i]))) * round_as<T>(u[i]);
+  for (int i = 0; i < 4; i += 2) {
+    float g0 = g[i], g1 = g[i + 1], u0 = u[i], u1 = u[i + 1];
+    round2<T>(g0, g1);
+    g0 = silu_f32(g0); g1 = silu_f32(g1);
+    round2<T>(g0, g1);
+    round2<T>(u0, u1);
+    g[i] = g0 * u0; g[i + 1] = g1 * u1;
+  }
   T* o = static_cast<T*>(p.out) + m * p.ldo + n_out;
   if ((reinterpret_cast<uintptr_t>(o) & 7u) == 0) {
     *reinterpret_cast<uint2*>(o) = make_uint2(pack2<T>(g[0], g[1]), pack2<T>(g[2], g[3]));
@@ -933,16 +950,15 @@ Tc5Plan plan_for_bn(int bn, int64_t M, int64_t N, int64_t K) {
 Tc5Plan plan_tc5(int64_t M, int64_t N, int64_t K, bool glu = false) {
   const int64_t tm = ceil_div(M, BM);
   if (glu) return plan_for_bn(128, M, N, K);   // the gated epilogue pairs columns c and c+64 of a 128-wide tile
-  if (tm == 1 && prefer_bn128()) {
-    // weight streaming: a 128-wide tile re-reads the activations half as often; take it when
-    // split-K can still put (nearly) as many CTAs to work as 64-wide tiles would
+  if (tm >= 2 && ceil_div(N, 128) * tm >= 148) return plan_for_bn(128, M, N, K);   // enough 128-wide tiles for every SM
+  if (tm >= 2 || prefer_bn128()) {
+    // Too few wide tiles: either 64-wide tiles or wide tiles with split-K.  Take the wide ones when
+    // split-K can still put (nearly) as many CTAs to work - they re-read the activations half as often.
     const Tc5Plan wide = plan_for_bn(128, M, N, K), narrow = plan_for_bn(64, M, N, K);
-    const int64_t cw = wide.tiles_n * wide.splits, cn = narrow.tiles_n * narrow.splits;
+    const int64_t cw = wide.tiles_n * wide.tiles_m * wide.splits, cn = narrow.tiles_n * narrow.tiles_m * narrow.splits;
     return cw * 10 >= cn * 8 ? wide : narrow;
   }
-  // 64-wide tiles whenever 128-wide ones would not give every SM a tile (148 SMs; fixed so that
-  // the workspace size does not depend on the device the plan is made on)
-  return plan_for_bn(ceil_div(N, 128) * tm < 148 ? 64 : 128, M, N, K);
+  return plan_for_bn(64, M, N, K);   // decode (one row tile): measured best with 64-wide tiles
 }
 
 template <typename T, int BN, bool CONV, int MODE = 0>
