@@ -363,10 +363,12 @@ struct PrefillParams {
   int64_t mask_b, mask_t;
   float scale;
   int mask_dtype;
+  int mask_staged;   // the mask can travel through shared memory (activation dtype, 16-byte-aligned rows)
 };
 
 constexpr int PF_BK = 64;                              // keys per shared-memory tile
-constexpr int PF_STAGE_BYTES = 2 * PF_BK * HD * 2;     // K tile + V tile
+constexpr int PF_KV_BYTES = 2 * PF_BK * HD * 2;        // K tile + V tile
+constexpr int PF_STAGE_BYTES = PF_KV_BYTES + 64 * PF_BK * 2;   // + the 64 x 64 tile of a 16-bit mask
 constexpr int PF_SMEM = 2 * PF_STAGE_BYTES;            // double buffer
 
 // One CTA = 64 query rows of one head (16 per warp).  K and V tiles of 64 keys are copied into
@@ -402,6 +404,11 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const __grid_constant
   const T* kbase = static_cast<const T*>(p.k) + b * p.ks[0] + hk * p.ks[1];
   const T* vbase = static_cast<const T*>(p.v) + b * p.vs[0] + hk * p.vs[1];
   const uint32_t sm0 = smem_u32(psm);
+  // A mask in the activation dtype with 16-byte-aligned rows travels with the K/V tiles: its
+  // 64 x 64 tile is copied with cp.async (chunk c of row r at c ^ (r & 7)).  Reading the mask
+  // straight from global memory, two bytes at a time, cost three times the rest of the kernel.
+  const bool mask_staged = p.mask != nullptr && p.mask_staged;
+  const T* mask_t = static_cast<const T*>(p.mask);
 
   auto issue = [&](int64_t kb, int st) {   // tile of keys kb..kb+63 -> stage st
     const uint32_t sk = sm0 + st * PF_STAGE_BYTES, sv = sk + PF_BK * HD * 2;
@@ -412,6 +419,17 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const __grid_constant
       const uint32_t off = row * 256 + ((ch ^ (row & 7)) << 4);
       cp_async16(sk + off, ok ? static_cast<const void*>(kbase + (kb + row) * p.ks[2] + ch * 8) : static_cast<const void*>(kbase), ok ? 16 : 0);
       cp_async16(sv + off, ok ? static_cast<const void*>(vbase + (kb + row) * p.vs[2] + ch * 8) : static_cast<const void*>(vbase), ok ? 16 : 0);
+    }
+    if (mask_staged) {
+      const uint32_t smk = sk + PF_KV_BYTES;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int idx = i * 128 + threadIdx.x, row = idx >> 3, ch = idx & 7;   // 64 rows x 8 chunks of 8 keys
+        const int64_t qrow = min(static_cast<int64_t>(blockIdx.x) * 64 + row, p.T - 1);
+        const bool ok = kb + ch * 8 < p.S;   // S is a multiple of 8 here; chunks past the end are never read as valid keys
+        cp_async16(smk + row * 128 + ((ch ^ (row & 7)) << 4),
+                   ok ? static_cast<const void*>(mask_t + b * p.mask_b + qrow * p.mask_t + kb + ch * 8) : static_cast<const void*>(mask_t), ok ? 16 : 0);
+      }
     }
   };
 
@@ -440,17 +458,39 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const __grid_constant
     // ---- additive mask (log2 domain) for rows g, g+8 x keys 8nt + 2t, +1 ----
     float mk[8][4];
     bool any = false;
+    if (mask_staged) {
+      const uint32_t smk = sm0 + (j & 1) * PF_STAGE_BYTES + PF_KV_BYTES;
+      const int rl = warp * 16 + g;   // tile rows rl and rl + 8 ((rl + 8) & 7 == rl & 7)
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int64_t key = kb + 8 * nt + 2 * t + (e & 1);
-        float mv = 0.f;
-        if (key >= p.S) mv = -INFINITY;
-        else if (p.mask) mv = load_as_f32(p.mask, mrow[e >> 1] + key, p.mask_dtype);
-        any = any || mv > MASKED;
-        mk[nt][e] = mv * LOG2E;
+      for (int nt = 0; nt < 8; ++nt) {
+        uint32_t w0, w1;
+        const uint32_t off = ((nt ^ (rl & 7)) << 4) + 4 * t;
+        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w0) : "r"(smk + rl * 128 + off));
+        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w1) : "r"(smk + (rl + 8) * 128 + off));
+        unpack2<T>(w0, mk[nt][0], mk[nt][1]);
+        unpack2<T>(w1, mk[nt][2], mk[nt][3]);
       }
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          if (kb + 8 * nt + 2 * t + (e & 1) >= p.S) mk[nt][e] = -INFINITY;
+          any = any || mk[nt][e] > MASKED;
+          mk[nt][e] *= LOG2E;
+        }
+    } else {
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int64_t key = kb + 8 * nt + 2 * t + (e & 1);
+          float mv = 0.f;
+          if (key >= p.S) mv = -INFINITY;
+          else if (p.mask) mv = load_as_f32(p.mask, mrow[e >> 1] + key, p.mask_dtype);
+          any = any || mv > MASKED;
+          mk[nt][e] = mv * LOG2E;
+        }
+    }
     if (warp_live && __any_sync(0xffffffffu, any)) {
       const uint32_t sk = sm0 + (j & 1) * PF_STAGE_BYTES, sv = sk + PF_BK * HD * 2;
       // ---- S = Q K^T ----
@@ -634,6 +674,7 @@ extern "C" int b200_attn_prefill(const void* q, const void* k, const void* v, co
   p.q = q; p.k = k; p.v = v; p.mask = mask; p.out = out; p.B = B; p.T = T; p.S = S; p.Hq = Hq; p.Hkv = Hkv;
   for (int i = 0; i < 3; ++i) { p.qs[i] = q_strides[i]; p.ks[i] = k_strides[i]; p.vs[i] = v_strides[i]; }
   p.mask_b = mask_b; p.mask_t = mask_t; p.scale = scale; p.mask_dtype = dtype;
+  p.mask_staged = (mask && aligned16(mask) && mask_b % 8 == 0 && mask_t % 8 == 0 && S % 8 == 0) ? 1 : 0;   // mask dtype == activation dtype by contract
   dim3 grid(static_cast<unsigned>(ceil_div(T, 64)), static_cast<unsigned>(Hq), static_cast<unsigned>(B));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   B200_DISPATCH_HALF(dtype, T_, {
