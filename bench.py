@@ -270,10 +270,7 @@ def run_b200(args, rank: int, world: int, device):
     line = {
         "metric": METRIC, "value": whole_job_throughput(world, B, K, ms), "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
         "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"Qwen2.5-1.5B-arch greedy decode, {args.layers} layers, B={B} sequences per GPU, KV cache {CACHE_LEN} rows "
-                               f"with {PREFILLED} filled, lock-step positions from {PREFILLED}", "batch_per_gpu": B,
-                   "cache_len": CACHE_LEN, "prefilled": PREFILLED, "parallelism": f"replicas x{world}, batch sharded, no collective",
-                   "l2_policy": "inputs larger than L2: every step streams 3.1 GB of weights and the KV cache"},
+        "config": workload_config(args.layers, B, world),
         "e2e": {"value": whole_job_throughput(world, B, K, e2e_ms), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
                 "ms_per_step": e2e_ms / K, "api": "DAGExecutor.execute(host inputs) -> argmax -> to_numpy()"},
         "gpu_launches": int(launches_per_step * K),
@@ -313,11 +310,28 @@ def cpu_oracle_decode(cfg, sd_cpu, batch: int, steps: int, warmup: int):
     return batch * len(times) / sum(times), sum(times)
 
 
+def workload_config(layers: int, B: int, world: int) -> dict:
+    """The ``config`` object of the JSON line; both arms describe the same workload."""
+    return {"workload": f"Qwen2.5-1.5B-arch greedy decode, {layers} layers, B={B} sequences per GPU, KV cache {CACHE_LEN} rows "
+                        f"with {PREFILLED} filled, lock-step positions from {PREFILLED}", "batch_per_gpu": B,
+            "cache_len": CACHE_LEN, "prefilled": PREFILLED, "parallelism": f"replicas x{world}, batch sharded, no collective",
+            "l2_policy": "inputs larger than L2: every step streams 3.1 GB of weights and the KV cache"}
+
+
+def host_threads() -> int:
+    """All host cores this process may use (torchrun pins OMP_NUM_THREADS to 1; undo that for the CPU arm)."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
 def run_reference(args):
     """--impl reference: the reference's CPU execution of the same decode graph."""
+    torch.set_num_threads(host_threads())
     cfg = mz.qwen2_config(num_layers=args.layers)
     sd = mz.qwen2_weights(cfg, seed=0)
-    b = 1
+    b = min(args.cpu_sample_batch, args.batch)   # a bounded sample: this many of the step's sequences
     tps, total = cpu_oracle_decode(cfg, sd, b, args.steps, min(args.warmup, 2))
     threads = torch.get_num_threads()
     sample = f"{args.steps} decode steps of {b} sequence(s) (of the B={args.batch} workload), {args.layers} layers, cache {CACHE_LEN}/{PREFILLED}"
@@ -325,8 +339,7 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": tps, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
         "warmup": min(args.warmup, 2), "ms_per_step": total / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"Qwen2.5-1.5B-arch greedy decode, {args.layers} layers, KV cache {CACHE_LEN} rows with {PREFILLED} filled",
-                   "batch_per_gpu": args.batch, "cache_len": CACHE_LEN, "prefilled": PREFILLED},
+        "config": workload_config(args.layers, args.batch, max(1, args.gpus)),
         "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -355,6 +368,7 @@ def main():
 
             line["also"] = bench_extras.run(cfg, sd, device)
         if not args.no_cpu_baseline:
+            torch.set_num_threads(host_threads())
             sd_cpu = {k: v.cpu() for k, v in sd.items()}
             b = min(args.cpu_sample_batch, args.batch)
             tps, total = cpu_oracle_decode(cfg, sd_cpu, b, 3, 1)

@@ -624,7 +624,7 @@ __global__ void __launch_bounds__(CONV ? 320 : PCfg<BN, TS>::THREADS_LINEAR, 1)
         }
         int cpb = 1, img = 0, base_w = 0, base_h = 0;   // convolution: first output pixel of the tile as a base position
         if (CONV) {
-          cpb = p.g.C / BK;
+          cpb = p.g.c8 ? 1 : p.g.C / BK;
           img = m0 / (p.g.Ho * p.g.Wo);
           const int rem = m0 - img * (p.g.Ho * p.g.Wo), oh = rem / p.g.Wo;
           base_w = (rem - oh * p.g.Wo) * p.g.sw - p.g.pw;
@@ -634,6 +634,17 @@ __global__ void __launch_bounds__(CONV ? 320 : PCfg<BN, TS>::THREADS_LINEAR, 1)
           const int s = it % ST;
           if (!tc5::mbar_wait(&empty_bar[s], ((it / ST) & 1) ^ 1)) { failed = 1; atomicExch(&g_tc5_error, 11); break; }
           tc5::mbar_arrive_expect_tx(&full_bar[s], (CONV && !p.g.im2col) ? B_STAGE : STAGE);
+          if (CONV && p.g.c8) {
+            // 8-channel input: k-block = 8 filter taps, each a [128 pixels][16 B] box (A) and a
+            // [BN rows][16 B] box (W).  Taps past the filter read zero weights (outside the weight
+            // map), so the activation box they are paired with only has to be finite: tap 0 again.
+            for (int tt = 0; tt < 8; ++tt) {
+              const int tap = kb * 8 + tt, ta = tap < p.g.KH * p.g.KW ? tap : 0, r = ta / p.g.KW;
+              tc5::tma_load_im2col_4d(smem + s * STAGE + tt * (BM * 16), &map_a, &full_bar[s], 0, base_w, base_h, img, ta - r * p.g.KW, r);
+              tc5::tma_load_2d(smem + s * STAGE + A_STAGE + tt * (BN * 16), &map_w, &full_bar[s], tap * 8, n0);
+            }
+            continue;
+          }
           if (!CONV) {
             tc5::tma_load_2d(smem + s * STAGE, &map_a, &full_bar[s], kb * BK, m0);
           } else if (p.g.im2col) {
@@ -661,9 +672,18 @@ __global__ void __launch_bounds__(CONV ? 320 : PCfg<BN, TS>::THREADS_LINEAR, 1)
           if (!tc5::mbar_wait(&full_bar[s], (it / ST) & 1)) { failed = 1; atomicExch(&g_tc5_error, 13); break; }
           tc5::tc_fence_after();
           const uint32_t a_addr = tc5::smem_addr(smem + s * STAGE), b_addr = a_addr + A_STAGE;
-          const uint64_t da = tc5::umma_desc_sw128(a_addr), db = tc5::umma_desc_sw128(b_addr);
+          if (CONV && p.g.c8) {   // unswizzled operands: one MMA covers two taps (2 x 16 bytes of K)
+            const uint32_t ak = p.g.c8_swap ? 128u : BM * 16u, am = p.g.c8_swap ? BM * 16u : 128u;
+            const uint32_t bk = p.g.c8_swap ? 128u : BN * 16u, bm = p.g.c8_swap ? BN * 16u : 128u;
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k) tc5::umma_f16(acc, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+            for (int k = 0; k < BK / 16; ++k)
+              tc5::umma_f16(acc, tc5::umma_desc_nosw(a_addr + k * 2 * (BM * 16), ak, am), tc5::umma_desc_nosw(b_addr + k * 2 * (BN * 16), bk, bm), idesc,
+                            (kb | k) != 0);
+          } else {
+            const uint64_t da = tc5::umma_desc_sw128(a_addr), db = tc5::umma_desc_sw128(b_addr);
+#pragma unroll
+            for (int k = 0; k < BK / 16; ++k) tc5::umma_f16(acc, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+          }
           tc5::umma_commit(&empty_bar[s]);
         }
         if (dead()) break;
@@ -921,6 +941,33 @@ bool make_im2col_map(CUtensorMap* map, const void* x, const Tc5Conv& g, int dtyp
             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// 8-channel variants: no swizzle, 16-byte inner box (one filter tap of 8 channels)
+bool make_map_c8(CUtensorMap* map, const void* w, int64_t rows, int64_t K, int64_t ld, int box_rows, int dtype) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
+  const cuuint32_t box[2] = {8, static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUtensorMapDataType dt = dtype == B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  return fn(map, dt, 2, const_cast<void*>(w), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+bool make_im2col_map_c8(CUtensorMap* map, const void* x, const Tc5Conv& g, int dtype) {
+  EncodeIm2colFn fn = encode_im2col_fn();
+  if (!fn || !conv_im2col_enabled() || g.batch <= 0 || g.C != 8) return false;
+  if (g.ph > 127 || g.pw > 127 || g.KH > 128 || g.KW > 128 || g.sh > 8 || g.sw > 8) return false;
+  const cuuint64_t dims[4] = {8, static_cast<cuuint64_t>(g.W), static_cast<cuuint64_t>(g.H), static_cast<cuuint64_t>(g.batch)};
+  const cuuint64_t strides[3] = {16, static_cast<cuuint64_t>(g.W) * 16, static_cast<cuuint64_t>(g.H) * g.W * 16};
+  const int lower[2] = {-g.pw, -g.ph};
+  const int upper[2] = {g.pw - (g.KW - 1), g.ph - (g.KH - 1)};
+  const cuuint32_t estr[4] = {1, static_cast<cuuint32_t>(g.sw), static_cast<cuuint32_t>(g.sh), 1};
+  const CUtensorMapDataType dt = dtype == B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  return fn(map, dt, 4, const_cast<void*>(x), dims, strides, lower, upper, 8, BM, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 struct Tc5Plan { int bn, splits, kb_per_split; int64_t tiles_n, tiles_m; };
 
 constexpr int MAX_SPLITS = 8;   // portable cluster size
@@ -1061,10 +1108,14 @@ int launch_persistent(const Tc5Args& a, cudaStream_t st, const Tc5Conv* g = null
     configured = true;
   }
   CUtensorMap ma, mw, mr, mo;
-  if (!make_map(&mw, a.W, a.N, a.K, a.ldw, BN, a.dtype)) return B200_ENOTSUP;
   Tc5Params p;
   p.g = g ? *g : Tc5Conv{};
-  if (CONV) {
+  if (CONV && p.g.c8) {
+    if (!make_map_c8(&mw, a.W, a.N, a.K, a.ldw, BN, a.dtype) || !make_im2col_map_c8(&ma, a.A, p.g, a.dtype)) return B200_ENOTSUP;
+    p.g.im2col = 1;
+  } else if (!make_map(&mw, a.W, a.N, a.K, a.ldw, BN, a.dtype)) {
+    return B200_ENOTSUP;
+  } else if (CONV) {
     p.g.im2col = make_im2col_map(&ma, a.A, p.g, a.dtype) ? 1 : 0;
     if (!p.g.im2col) {
       if (TS) return B200_ENOTSUP;   // warp 6 cannot both gather and store
@@ -1182,8 +1233,22 @@ int linear_tc5(const Tc5Args& a, cudaStream_t st) {
 int conv_tc5(const Tc5Args& a, const Tc5Conv& g, cudaStream_t st) {
   if (!tc5_enabled()) return B200_ENOTSUP;
   if (a.dtype != B200_BF16 && a.dtype != B200_F16) return B200_ENOTSUP;
-  if (g.C % BK || a.K != static_cast<int64_t>(g.KH) * g.KW * g.C || a.ldw % 8 || !aligned16(a.A) || !aligned16(a.W)) return B200_ENOTSUP;
   if (a.M >= (1ll << 31) || a.N >= (1ll << 31) || (a.epilogue & ~(B200_EPI_RELU | B200_EPI_W_STATIC))) return B200_ENOTSUP;
+  if (g.C == 8) {   // stem convolution on the padded RGB input: persistent kernel, 64-wide tiles, bulk-copy epilogue
+    static int c8_mode = -1;   // B200NN_CONV_C8: 0 off, 1 on, 2 on with the descriptor offsets exchanged
+    if (c8_mode < 0) {
+      const char* e = getenv("B200NN_CONV_C8");
+      c8_mode = e && e[0] ? atoi(e) : 1;
+    }
+    if (!c8_mode || a.K != static_cast<int64_t>(g.KH) * g.KW * 8 || a.ldw % 8 || !aligned16(a.A) || !aligned16(a.W) || a.N > 64 || a.N % 8 ||
+        a.M < 2 * BM || !tma_store_ok(a))
+      return B200_ENOTSUP;
+    Tc5Conv g8 = g;
+    g8.c8 = 1;
+    g8.c8_swap = c8_mode == 2;
+    return a.dtype == B200_BF16 ? launch_persistent<__nv_bfloat16, 64, true, true>(a, st, &g8) : launch_persistent<__half, 64, true, true>(a, st, &g8);
+  }
+  if (g.C % BK || a.K != static_cast<int64_t>(g.KH) * g.KW * g.C || a.ldw % 8 || !aligned16(a.A) || !aligned16(a.W)) return B200_ENOTSUP;
   if (const int bn = persistent_bn(a.M, a.N, a.K, false)) return dispatch_persistent<true>(bn, a, st, &g);
   Tc5Plan pl;
   pl.bn = a.N >= 128 ? 128 : 64;

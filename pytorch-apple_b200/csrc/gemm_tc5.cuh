@@ -18,9 +18,12 @@ struct Tc5Conv {
   int H, W, C, KH, KW, sh, sw, ph, pw, Ho, Wo;
   int batch = 0;    // images
   int im2col = 0;   // set by conv_tc5: the A tile comes from an im2col-mode tensor map (else gathered by threads)
+  int c8 = 0;       // 8-channel input (the padded RGB stem): one filter tap per 16-byte K chunk, unswizzled operands
+  int c8_swap = 0;  // debugging switch: exchange the two byte offsets of the unswizzled descriptors
 };
 
-// y = epi(conv(x, w) + bias + residual) on the tcgen05 path; needs C % 64 == 0.
+// y = epi(conv(x, w) + bias + residual) on the tcgen05 path; needs C % 64 == 0, or C == 8
+// (stem convolution after channel padding) with O <= 64.
 // Args: A = x [N,H,W,C], W = packed weights [O, KH*KW*C], M = N*Ho*Wo, N = O, K = KH*KW*C.
 int conv_tc5(const Tc5Args& a, const Tc5Conv& g, cudaStream_t stream);
 

@@ -103,6 +103,18 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_byte_addr) {
   return d;
 }
 
+// Shared-memory operand, K-major, no swizzle: core matrices of 8 rows x 16 bytes stored
+// contiguously (row r at +16 r); `k_step_bytes` separates core matrices that are neighbours
+// along K (leading byte offset), `mn_step_bytes` those along M/N (stride byte offset).
+__device__ __forceinline__ uint64_t umma_desc_nosw(uint32_t smem_byte_addr, uint32_t k_step_bytes, uint32_t mn_step_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_byte_addr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>((k_step_bytes >> 4) & 0x3FFFu) << 16;
+  d |= static_cast<uint64_t>((mn_step_bytes >> 4) & 0x3FFFu) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  return d;
+}
+
 // Instruction descriptor for kind::f16 with fp32 accumulation, both operands K-major.
 //   [4,6) D format 1=f32   [7,10) A format (0 f16, 1 bf16)   [10,13) B format
 //   [15] A major 0=K  [16] B major 0=K   [17,23) N>>3   [24,29) M>>4
