@@ -584,7 +584,8 @@ extern "C" int b200_conv2d_nhwc(const void* x, const void* w, const float* bias,
     // implicit GEMM on the tcgen05 path: A rows fetched by the kernel itself
     const int64_t rows = static_cast<int64_t>(N) * Ho * Wo, K = static_cast<int64_t>(KH) * KW * C;
     Tc5Args t{x, w, bias, residual, nullptr, y, rows, O, K, 0, K, O, O, 0, dtype, B200_F32, epilogue, nullptr, 0};
-    const Tc5Conv g{H, W, C, KH, KW, sh, sw, ph, pw, Ho, Wo, N, 0};
+    Tc5Conv g{H, W, C, KH, KW, sh, sw, ph, pw, Ho, Wo};
+    g.batch = N;
     const int rc = conv_tc5(t, g, st);
     if (rc != B200_ENOTSUP) return rc;
   }

@@ -1,6 +1,9 @@
-// tcgen05 GEMM for large M:  out[M,N] = epi(A[M,K] * W[N,K]^T + bias + residual).
+// tcgen05 GEMM and implicit-GEMM convolution:  out[M,N] = epi(A[M,K] * W[N,K]^T + bias + residual).
 //
-// One CTA computes a 128 x BN tile.  Warp 0 streams 128x64 (A) and BNx64 (W) tiles
+// Two kernels share the building blocks: gemm_tc5_kernel computes one 128 x BN tile per CTA
+// (decode weight streaming with split-K inside a thread-block cluster, small and mid-size
+// shapes); gemm_tc5p_kernel is persistent (one CTA per SM walks the tile list, accumulator
+// double-buffered in tensor memory, optional bulk-copy epilogue).  In both, per tile:  Warp 0 streams 128x64 (A) and BNx64 (W) tiles
 // through a ring of shared-memory stages with TMA (128-byte swizzle, no multicast);
 // warp 1 issues tcgen05.mma (M=128, N=BN, K=16) from shared-memory descriptors into a
 // tensor-memory accumulator and releases stages with tcgen05.commit; warps 2-5 read the
@@ -71,6 +74,11 @@ __device__ __forceinline__ unsigned long long globaltimer_ns() {
   } while (0)
 constexpr int PTR_CTAS = 160, PTR_TILES = 12, PTR_N = 8;
 __device__ unsigned long long g_tc5p_trace[PTR_CTAS][PTR_TILES][PTR_N];
+__device__ unsigned long long g_tc5p_kb[2][PTR_CTAS][PTR_TILES][PTR_N];   // [0] producer: stage free, [1] MMA: stage full
+#define TC5P_KB(which, ti_, kb_)                                                                              \
+  do {                                                                                                        \
+    if (blockIdx.x < PTR_CTAS && (ti_) < PTR_TILES && (kb_) < PTR_N) g_tc5p_kb[which][blockIdx.x][ti_][kb_] = globaltimer_ns(); \
+  } while (0)
 #define TC5P_STAMP(ti_, i)                                                                              \
   do {                                                                                                  \
     if (blockIdx.x < PTR_CTAS && (ti_) < PTR_TILES) g_tc5p_trace[blockIdx.x][ti_][i] = globaltimer_ns(); \
@@ -78,6 +86,7 @@ __device__ unsigned long long g_tc5p_trace[PTR_CTAS][PTR_TILES][PTR_N];
 #else
 #define TC5_STAMP(i)
 #define TC5P_STAMP(ti_, i)
+#define TC5P_KB(which, ti_, kb_)
 #endif
 
 struct Tc5Params {
@@ -630,9 +639,22 @@ __global__ void __launch_bounds__(CONV ? 320 : PCfg<BN, TS>::THREADS_LINEAR, 1)
           base_w = (rem - oh * p.g.Wo) * p.g.sw - p.g.pw;
           base_h = oh * p.g.sh - p.g.ph;
         }
+        if (CONV && p.g.im2col && p.g.l2_ahead && tile + static_cast<int>(gridDim.x) < n_tiles) {
+          // The first read of a pixel comes from DRAM (measured 3-4 us to the barrier, 1.4 us for the
+          // later taps that find it in L2), and the ring holds only a few k-blocks: ask for the next
+          // tile's pixels now.  One box per filter row and channel block covers every tap's pixels
+          // up to a column or two at the row ends.
+          const int nt = tile + gridDim.x, nm0 = (nt % tiles_m) * BM;
+          const int nimg = nm0 / (p.g.Ho * p.g.Wo), nrem = nm0 - nimg * (p.g.Ho * p.g.Wo), noh = nrem / p.g.Wo;
+          const int nw = (nrem - noh * p.g.Wo) * p.g.sw - p.g.pw, nh = noh * p.g.sh - p.g.ph;
+          const int cblocks = p.g.c8 ? 1 : p.g.C / BK;
+          for (int r = 0; r < p.g.KH; ++r)
+            for (int cb2 = 0; cb2 < cblocks; ++cb2) tc5::tma_prefetch_im2col_4d(&map_a, cb2 * BK, nw, nh, nimg, p.g.KW / 2, r);
+        }
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const int s = it % ST;
           if (!tc5::mbar_wait(&empty_bar[s], ((it / ST) & 1) ^ 1)) { failed = 1; atomicExch(&g_tc5_error, 11); break; }
+          TC5P_KB(0, ti, kb);
           tc5::mbar_arrive_expect_tx(&full_bar[s], (CONV && !p.g.im2col) ? B_STAGE : STAGE);
           if (CONV && p.g.c8) {
             // 8-channel input: k-block = 8 filter taps, each a [128 pixels][16 B] box (A) and a
@@ -670,6 +692,7 @@ __global__ void __launch_bounds__(CONV ? 320 : PCfg<BN, TS>::THREADS_LINEAR, 1)
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const int s = it % ST;
           if (!tc5::mbar_wait(&full_bar[s], (it / ST) & 1)) { failed = 1; atomicExch(&g_tc5_error, 13); break; }
+          TC5P_KB(1, ti, kb);
           tc5::tc_fence_after();
           const uint32_t a_addr = tc5::smem_addr(smem + s * STAGE), b_addr = a_addr + A_STAGE;
           if (CONV && p.g.c8) {   // unswizzled operands: one MMA covers two taps (2 x 16 bytes of K)
@@ -914,6 +937,15 @@ EncodeIm2colFn encode_im2col_fn() {
   return fn;
 }
 
+int conv_l2_ahead() {   // B200NN_CONV_L2_AHEAD=1: L2 prefetch of the next tile's pixels (measured: no gain, off by default)
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("B200NN_CONV_L2_AHEAD");
+    v = (e && e[0] == '1') ? 1 : 0;
+  }
+  return v;
+}
+
 bool conv_im2col_enabled() {
   static int v = -1;
   if (v < 0) {
@@ -1117,6 +1149,7 @@ int launch_persistent(const Tc5Args& a, cudaStream_t st, const Tc5Conv* g = null
     return B200_ENOTSUP;
   } else if (CONV) {
     p.g.im2col = make_im2col_map(&ma, a.A, p.g, a.dtype) ? 1 : 0;
+    p.g.l2_ahead = conv_l2_ahead();
     if (!p.g.im2col) {
       if (TS) return B200_ENOTSUP;   // warp 6 cannot both gather and store
       ma = mw;
@@ -1244,6 +1277,7 @@ int conv_tc5(const Tc5Args& a, const Tc5Conv& g, cudaStream_t st) {
         a.M < 2 * BM || !tma_store_ok(a))
       return B200_ENOTSUP;
     Tc5Conv g8 = g;
+    g8.l2_ahead = conv_l2_ahead();
     g8.c8 = 1;
     g8.c8_swap = c8_mode == 2;
     return a.dtype == B200_BF16 ? launch_persistent<__nv_bfloat16, 64, true, true>(a, st, &g8) : launch_persistent<__half, 64, true, true>(a, st, &g8);
@@ -1264,6 +1298,9 @@ int conv_tc5(const Tc5Args& a, const Tc5Conv& g, cudaStream_t st) {
 }  // namespace b200
 
 #ifdef B200NN_TC5_TRACE
+extern "C" int b200_debug_tc5p_kb(unsigned long long* host_out) {
+  return cudaMemcpyFromSymbol(host_out, b200::g_tc5p_kb, sizeof(unsigned long long) * 2 * b200::PTR_CTAS * b200::PTR_TILES * b200::PTR_N) == cudaSuccess ? B200_OK : B200_ELAUNCH;
+}
 extern "C" int b200_debug_tc5p_trace(unsigned long long* host_out) {
   return cudaMemcpyFromSymbol(host_out, b200::g_tc5p_trace, sizeof(unsigned long long) * b200::PTR_CTAS * b200::PTR_TILES * b200::PTR_N) == cudaSuccess ? B200_OK : B200_ELAUNCH;
 }

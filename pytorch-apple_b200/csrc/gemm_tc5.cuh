@@ -8,7 +8,7 @@ struct Tc5Args {
   const void* A; const void* W; const void* bias; const void* residual; const void* aux; void* out;
   int64_t M, N, K, lda, ldw, ldo, ldr, ldaux;
   int dtype, bias_dtype, epilogue;
-  void* workspace;          // zero-initialised scratch for split-K (may be null when not needed)
+  void* workspace;          // unused by the tcgen05 path (split-K needs no global scratch); kept for the dispatcher's fallbacks
   int64_t workspace_bytes;
 };
 
@@ -18,6 +18,7 @@ struct Tc5Conv {
   int H, W, C, KH, KW, sh, sw, ph, pw, Ho, Wo;
   int batch = 0;    // images
   int im2col = 0;   // set by conv_tc5: the A tile comes from an im2col-mode tensor map (else gathered by threads)
+  int l2_ahead = 0; // persistent kernel: prefetch the next tile's pixels into L2
   int c8 = 0;       // 8-channel input (the padded RGB stem): one filter tap per 16-byte K chunk, unswizzled operands
   int c8_swap = 0;  // debugging switch: exchange the two byte offsets of the unswizzled descriptors
 };
@@ -31,7 +32,7 @@ int conv_tc5(const Tc5Args& a, const Tc5Conv& g, cudaStream_t stream);
 // operands do not meet the TMA alignment rules (the caller then uses the mma.sync tiles).
 int linear_tc5(const Tc5Args& a, cudaStream_t stream);
 bool tc5_enabled();
-// Scratch bytes linear_tc5 needs for (M, N, K); 0 when the plan does not split K.
+// Scratch bytes linear_tc5 needs for (M, N, K): always 0.
 int64_t linear_tc5_workspace_bytes(int64_t M, int64_t N, int64_t K);
 
 }  // namespace b200
