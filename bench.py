@@ -275,11 +275,11 @@ def run_b200(args, rank: int, world: int, device):
                 "ms_per_step": e2e_ms / K, "api": "DAGExecutor.execute(host inputs) -> argmax -> to_numpy()"},
         "gpu_launches": int(launches_per_step * K),
         "clocks": clocks.result,
-        "roofline": {"bound": "hbm", "kernel": "attn_decode_kernel (+merge)", "achieved": attn_bytes / (attn_ms * 1e-3) / 1e9 if attn_ms else None,
+        "roofline": {"bound": "hbm", "kernel": "attn_decode_kernel", "achieved": attn_bytes / (attn_ms * 1e-3) / 1e9 if attn_ms else None,
                      "peak": hbm, "unit": "GB/s", "frac": (attn_bytes / (attn_ms * 1e-3) / 1e9 / hbm) if attn_ms else None,
                      "peak_source": which, "traffic": ATTN_DRAM_BYTES_PER_LAUNCH if B == 64 else None,
                      "bytes_per_launch": int(attn_bytes), "ms_per_launch": attn_ms,
-                     "timing": f"CUDA events around replays of a graph holding the step's {attn_calls} attention launches (attention + merge kernel each)",
+                     "timing": f"CUDA events around replays of a graph holding the step's {attn_calls} attention launches",
                      "step": {"algorithmic_bytes": int(bts["total"]), "achieved_gbs": bts["total"] / (ms / K * 1e-3) / 1e9,
                               "frac": bts["total"] / (ms / K * 1e-3) / 1e9 / hbm}},
         "kernel_ms_one_step": {k: {"launches": len(v), "total_ms": float(np.sum(v))} for k, v in sorted(by_fn.items())},

@@ -5,6 +5,7 @@
 // rounds them.  Two kernels: prefill (64 query rows per CTA) and split-KV decode (one query
 // token, the query heads of a KV group on the N side of the MMA).
 #include "mma.cuh"
+#include "tc5.cuh"
 
 #include <stdlib.h>
 
@@ -29,6 +30,7 @@ struct DecodeParams {
   float scale;
   int mask_dtype;
   int l2_ahead;   // blocks per warp requested into L2 ahead of the shared-memory ring
+  void* out;      // cluster-merge mode: final output [B][Hq][HD] in the activation dtype
 };
 
 constexpr int DEC_MAX_BLOCKS = 128;  // 16-key blocks per split (split_len <= 2048)
@@ -51,7 +53,7 @@ __device__ unsigned long long g_attn_trace[ATR_CTAS][ATR_N];
 #endif
 
 constexpr int DEC_STAGE_BYTES = 2 * 16 * HD * 2;  // 16 keys of K and of V
-constexpr int DEC_MAX_SPLIT = 512;             // keys per split (mask values of a split are staged in shared memory)
+constexpr int DEC_MAX_SPLIT = 640;             // keys per split (mask values of a split are staged in shared memory)
 constexpr int DEC_ACC_PITCH = HD + 4;          // row pitch of the cross-warp accumulator (spreads the heads over banks)
 
 // The decode kernel works on the transposed problem, so that the (at most 8) query heads of a
@@ -78,10 +80,18 @@ constexpr int DEC_ACC_PITCH = HD + 4;          // row pitch of the cross-warp ac
 // unmasked key and need to be fetched at all), and reads the two mask values a lane needs per
 // block straight from global memory (L1 hits after the scan).  The four warps meet once, at
 // the end, to merge their partial results through the shared memory their rings occupied.
-template <typename T, int STAGES>
+//
+// CM = true ("cluster merge"): the splits of one (sequence, KV head) form a thread-block cluster
+// along x.  Instead of writing its partial result to global memory for a second kernel, every
+// CTA stores head h's partial (accumulator, max, sum) into the receive buffer of cluster rank h
+// (distributed shared memory); after one cluster barrier ranks 0..G-1 combine the splits of
+// their head and write the final output.  Needs G <= splits <= 8.
+template <typename T, int STAGES, bool CM>
 __global__ void __launch_bounds__(128, STAGES == 2 ? 3 : 2) attn_decode_kernel(const __grid_constant__ DecodeParams p) {
   extern __shared__ __align__(1024) uint8_t dsm[];
   __shared__ float s_m[4][8], s_l[4][8];
+  __shared__ __align__(16) float recv_acc[CM ? 8 : 1][HD];   // [source rank][dim] partials of the head this CTA owns
+  __shared__ float recv_ml[CM ? 8 : 1][2];
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
   const int split = blockIdx.x, hk = blockIdx.y;
@@ -93,6 +103,7 @@ __global__ void __launch_bounds__(128, STAGES == 2 ? 3 : 2) attn_decode_kernel(c
 
   ATTN_STAMP(0);
   pdl_trigger();
+  if (CM) tc5::cluster_sync();   // every CTA of the cluster runs before anyone writes into a peer (overlaps the predecessor)
   pdl_wait();   // q, the new cache rows and the mask come from the kernels before this one
   ATTN_STAMP(1);
 
@@ -313,10 +324,34 @@ __global__ void __launch_bounds__(128, STAGES == 2 ? 3 : 2) attn_decode_kernel(c
       acc += reinterpret_cast<const float*>(dsm + wi * (STAGES * DEC_STAGE_BYTES))[h * DEC_ACC_PITCH + d] * f;
       lr += s_l[wi][h] * f;
     }
-    p.part_acc[(pidx + h) * HD + d] = acc;
-    if (d == 0) {
-      p.part_ml[(pidx + h) * 2] = ma;      // log2 domain
-      p.part_ml[(pidx + h) * 2 + 1] = lr;
+    if (CM) {   // partial of head h -> slot `split` of the receive buffer of cluster rank h
+      const uint32_t dst = tc5::map_to_rank(smem_u32(&recv_acc[split][d]), h);
+      asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(dst), "f"(acc) : "memory");
+      if (d == 0) {
+        const uint32_t dml = tc5::map_to_rank(smem_u32(&recv_ml[split][0]), h);
+        asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};" ::"r"(dml), "f"(ma), "f"(lr) : "memory");
+      }
+    } else {
+      p.part_acc[(pidx + h) * HD + d] = acc;
+      if (d == 0) {
+        p.part_ml[(pidx + h) * 2] = ma;      // log2 domain
+        p.part_ml[(pidx + h) * 2 + 1] = lr;
+      }
+    }
+  }
+  if (CM) {
+    tc5::cluster_sync();   // all partials have landed; nobody touches a peer's memory afterwards
+    if (split < p.G) {     // this CTA owns head `split` of the group
+      float m_all = -INFINITY;
+      for (int r = 0; r < p.splits; ++r) m_all = fmaxf(m_all, recv_ml[r][0]);
+      const float m_use = m_all == -INFINITY ? 0.f : m_all;
+      float acc = 0.f, l = 0.f;
+      for (int r = 0; r < p.splits; ++r) {
+        const float f = ex2_approx(recv_ml[r][0] - m_use);
+        l += recv_ml[r][1] * f;
+        acc += recv_acc[r][d] * f;
+      }
+      static_cast<T*>(p.out)[((b * p.Hq) + static_cast<int64_t>(hk) * p.G + split) * HD + d] = from_f32<T>(l > 0.f ? acc / l : 0.f);
     }
   }
   ATTN_STAMP(4);
@@ -577,14 +612,32 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const __grid_constant
   }
 }
 
-struct DecodePlan { int split_len; int splits; };
+struct DecodePlan { int split_len; int splits; bool cluster; };
 
-static DecodePlan plan_decode(int64_t B, int Hkv, int64_t S) {
+static bool cluster_merge_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("B200NN_ATTN_CLUSTER");
+    v = (e && e[0] == '0') ? 0 : 1;
+  }
+  return v == 1;
+}
+
+static DecodePlan plan_decode(int64_t B, int Hkv, int64_t S, int G = 8) {
   const int64_t want = 2 * 148;  // fixed so that the workspace size does not depend on the device
+  // Plenty of sequences: eight splits per (sequence, KV head), merged inside the kernel by a cluster.
+  if (cluster_merge_enabled() && B * Hkv * 8 >= 4 * 148 && S >= 8 * 64 && S <= 8 * DEC_MAX_SPLIT && G <= 8) {
+    DecodePlan c;
+    c.split_len = static_cast<int>(ceil_div(ceil_div(S, 8), 16) * 16);
+    c.splits = static_cast<int>(ceil_div(S, c.split_len));
+    c.cluster = c.splits >= G && c.splits <= 8;
+    if (c.cluster) return c;
+  }
   if (B * Hkv * ceil_div(S, 512) >= 4 * 148) {  // plenty of work: longer splits amortise the per-split prologue
     DecodePlan big;
     big.split_len = 512;
     big.splits = static_cast<int>(ceil_div(S, 512));
+    big.cluster = false;
     return big;
   }
   int len = 256;
@@ -592,6 +645,7 @@ static DecodePlan plan_decode(int64_t B, int Hkv, int64_t S) {
   DecodePlan d;
   d.split_len = len;
   d.splits = static_cast<int>(ceil_div(S, len));
+  d.cluster = false;
   return d;
 }
 
@@ -601,8 +655,9 @@ using namespace b200;
 
 extern "C" int64_t b200_attn_decode_workspace_bytes(int64_t B, int Hq, int Hkv, int64_t S, int D) {
   if (B <= 0 || Hkv <= 0 || Hq <= 0 || S <= 0) return 0;
-  const DecodePlan d = plan_decode(B, Hkv, S);
   const int G = Hq / Hkv;
+  const DecodePlan d = plan_decode(B, Hkv, S, G);
+  if (d.cluster) return 0;   // the splits are merged inside the kernel through distributed shared memory
   return B * Hkv * d.splits * G * (static_cast<int64_t>(D) + 2) * 4;
 }
 
@@ -617,9 +672,9 @@ extern "C" int b200_attn_decode(const void* q, const void* k, const void* v, con
   if (B == 0) return B200_OK;
   if (!(aligned16(q) && aligned16(k) && aligned16(v) && q_batch_stride % 8 == 0 && kv_batch_stride % 8 == 0 && kv_head_stride % 8 == 0))
     B200_FAIL(B200_EALIGN, "b200_attn_decode: operands must be 16-byte aligned with strides multiple of 8");
-  const DecodePlan d = plan_decode(B, Hkv, S);
+  const DecodePlan d = plan_decode(B, Hkv, S, Hq / Hkv);
   const int64_t need = b200_attn_decode_workspace_bytes(B, Hq, Hkv, S, D);
-  if (!workspace || workspace_bytes < need)
+  if (need > 0 && (!workspace || workspace_bytes < need))
     B200_FAIL(B200_EINVAL, "b200_attn_decode: workspace of %lld bytes required (got %lld)", (long long)need, (long long)workspace_bytes);
   DecodeParams p;
   p.q = q; p.k = k; p.v = v; p.mask = mask;
@@ -629,6 +684,7 @@ extern "C" int b200_attn_decode(const void* q, const void* k, const void* v, con
   p.B = B; p.S = S; p.Hq = Hq; p.Hkv = Hkv;
   p.q_bs = q_batch_stride; p.kv_bs = kv_batch_stride; p.kv_hs = kv_head_stride; p.mask_bs = mask_batch_stride;
   p.split_len = d.split_len; p.splits = d.splits; p.scale = scale; p.mask_dtype = dtype;
+  p.out = out;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   dim3 grid(static_cast<unsigned>(d.splits), static_cast<unsigned>(Hkv), static_cast<unsigned>(B));
   static int stages = 0, l2_ahead = 0;   // ring depth per warp: 2 (three CTAs per SM) or 3 (two CTAs per SM)
@@ -643,15 +699,39 @@ extern "C" int b200_attn_decode(const void* q, const void* k, const void* v, con
   B200_DISPATCH_HALF(dtype, T, {
     static bool configured = false;
     if (!configured) {
-      cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<T, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 4 * 3 * DEC_STAGE_BYTES);
-      if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_decode_kernel<T, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 4 * 2 * DEC_STAGE_BYTES);
+      cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<T, 3, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 4 * 3 * DEC_STAGE_BYTES);
+      if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_decode_kernel<T, 2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 4 * 2 * DEC_STAGE_BYTES);
+      if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_decode_kernel<T, 2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 4 * 2 * DEC_STAGE_BYTES);
       if (e != cudaSuccess) B200_FAIL(B200_ELAUNCH, "attn_decode_kernel attribute: %s", cudaGetErrorString(e));
       configured = true;
     }
-    if (stages == 2) launch_pdl(attn_decode_kernel<T, 2>, grid, dim3(128), 4 * 2 * DEC_STAGE_BYTES, st, p);
-    else launch_pdl(attn_decode_kernel<T, 3>, grid, dim3(128), 4 * 3 * DEC_STAGE_BYTES, st, p);
-    launch_pdl(attn_decode_merge_kernel<T>, dim3(static_cast<unsigned>(B * Hq)), dim3(128), 0, st, static_cast<const float*>(p.part_acc),
-               static_cast<const float*>(p.part_ml), static_cast<T*>(out), Hq, Hkv, p.G, d.splits);
+    if (d.cluster) {   // one kernel: the splits of a (sequence, KV head) are a cluster along x and merge in shared memory
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = grid;
+      cfg.blockDim = dim3(128);
+      cfg.dynamicSmemBytes = 4 * 2 * DEC_STAGE_BYTES;
+      cfg.stream = st;
+      cudaLaunchAttribute attrs[2];
+      int n_attrs = 0;
+      attrs[n_attrs].id = cudaLaunchAttributeClusterDimension;
+      attrs[n_attrs].val.clusterDim.x = static_cast<unsigned>(d.splits);
+      attrs[n_attrs].val.clusterDim.y = 1;
+      attrs[n_attrs].val.clusterDim.z = 1;
+      ++n_attrs;
+      if (pdl_enabled()) {
+        attrs[n_attrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attrs[n_attrs].val.programmaticStreamSerializationAllowed = 1;
+        ++n_attrs;
+      }
+      cfg.attrs = attrs;
+      cfg.numAttrs = n_attrs;
+      cudaLaunchKernelEx(&cfg, attn_decode_kernel<T, 2, true>, p);
+    } else {
+      if (stages == 2) launch_pdl(attn_decode_kernel<T, 2, false>, grid, dim3(128), 4 * 2 * DEC_STAGE_BYTES, st, p);
+      else launch_pdl(attn_decode_kernel<T, 3, false>, grid, dim3(128), 4 * 3 * DEC_STAGE_BYTES, st, p);
+      launch_pdl(attn_decode_merge_kernel<T>, dim3(static_cast<unsigned>(B * Hq)), dim3(128), 0, st, static_cast<const float*>(p.part_acc),
+                 static_cast<const float*>(p.part_ml), static_cast<T*>(out), Hq, Hkv, p.G, d.splits);
+    }
   });
   B200_CHECK_LAUNCH("attn_decode_kernel");
   return B200_OK;
