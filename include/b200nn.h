@@ -275,7 +275,7 @@ int b200_conv2d_nhwc(const void* x, const void* w, const float* bias, const void
  *   k,v: [B, Hkv, S, D] caches, row stride D, head stride S*D
  *   mask:[B, S] additive (the graph's attention_mask [B,1,1,S]); NULL = none
  *   out: [B, Hq, D]
- * Split-KV: for big batches (B*Hkv*8 >= 592) of caches up to 5120 rows the eight splits of
+ * Split-KV: for caches of 512..5120 rows (and at most 8 query heads per KV head) the eight splits of
  * a (sequence, KV head) form a thread-block cluster and merge in distributed shared memory
  * (no workspace: b200_attn_decode_workspace_bytes returns 0); otherwise partial
  * (max, sum, acc) per split go to `workspace` and are merged by a second kernel.  Key blocks whose mask entries are all <= -1e30 are skipped, which
@@ -291,7 +291,7 @@ int64_t b200_attn_decode_workspace_bytes(int64_t B, int Hq, int Hkv, int64_t S, 
  * it was handed, code running where cudaMalloc is off limits).  This entry point has no
  * counterpart in the reference.  The split-KV partials go to an 8 MiB array that is part
  * of the library image (each GPU that loads the library holds it until exit); shapes whose
- * partials need more return B200_ELIMIT (big batches of caches up to 5120 rows need none:
+ * partials need more return B200_ELIMIT (caches up to 5120 rows need none:
  * their splits merge inside the kernel; Hq=12, Hkv=2, S=8192 is refused for B > 84).  No
  * cudaMalloc, cudaFree or allocating library call is made.  The first call on a device
  * looks up the array's device address; make that call before any stream capture.  All

@@ -614,19 +614,21 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const __grid_constant
 
 struct DecodePlan { int split_len; int splits; bool cluster; };
 
-static bool cluster_merge_enabled() {
+// B200NN_ATTN_CLUSTER: 0 = never merge in-kernel, 1 = only for big batches, 2 (default) = whenever the
+// shape allows (measured faster at every batch size: B=8 14.7 vs 19.6 us, B=1 12.2 vs 13.4 us)
+static int cluster_merge_mode() {
   static int v = -1;
   if (v < 0) {
     const char* e = getenv("B200NN_ATTN_CLUSTER");
-    v = (e && e[0] == '0') ? 0 : 1;
+    v = (e && e[0] >= '0' && e[0] <= '2') ? e[0] - '0' : 2;
   }
-  return v == 1;
+  return v;
 }
 
 static DecodePlan plan_decode(int64_t B, int Hkv, int64_t S, int G = 8) {
   const int64_t want = 2 * 148;  // fixed so that the workspace size does not depend on the device
   // Plenty of sequences: eight splits per (sequence, KV head), merged inside the kernel by a cluster.
-  if (cluster_merge_enabled() && B * Hkv * 8 >= 4 * 148 && S >= 8 * 64 && S <= 8 * DEC_MAX_SPLIT && G <= 8) {
+  if (cluster_merge_mode() && (B * Hkv * 8 >= 4 * 148 || cluster_merge_mode() == 2) && S >= 8 * 64 && S <= 8 * DEC_MAX_SPLIT && G <= 8) {
     DecodePlan c;
     c.split_len = static_cast<int>(ceil_div(ceil_div(S, 8), 16) * 16);
     c.splits = static_cast<int>(ceil_div(S, c.split_len));
