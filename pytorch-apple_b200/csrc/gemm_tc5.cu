@@ -578,11 +578,12 @@ template <int BN, bool TS> struct PCfg {
   static constexpr int CB = BM * BN * 2;               // one C buffer: BN/64 sub-tiles of [128 rows][128 bytes]
   static constexpr int NCB = TS ? (BN == 256 ? 1 : 2) : 0;
   static constexpr int SMEM = ST * STAGE + NCB * CB + 1024;
-  static constexpr int THREADS_LINEAR = TS ? 224 : 192;
+  static constexpr int THREADS = TS ? 352 : 192;        // TS: warps 2-5 and 7-10 share the epilogue (half the columns each), warp 6 stores
+  static constexpr int EPI_WARPS = TS ? 8 : 4;
 };
 
 template <typename T, int BN, bool CONV, bool TS>
-__global__ void __launch_bounds__(CONV ? 320 : PCfg<BN, TS>::THREADS_LINEAR, 1)
+__global__ void __launch_bounds__(CONV ? (TS ? 352 : 320) : PCfg<BN, TS>::THREADS, 1)
     gemm_tc5p_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                      const __grid_constant__ CUtensorMap map_r, const __grid_constant__ CUtensorMap map_o, const Tc5Params p,
                      const int tiles_m, const int n_tiles) {
@@ -603,8 +604,8 @@ __global__ void __launch_bounds__(CONV ? 320 : PCfg<BN, TS>::THREADS_LINEAR, 1)
   if (threadIdx.x == 0) {
     failed = 0;
     for (int s = 0; s < ST; ++s) { tc5::mbar_init(&full_bar[s], (CONV && !p.g.im2col) ? 129 : 1); tc5::mbar_init(&empty_bar[s], 1); }
-    for (int b = 0; b < 2; ++b) { tc5::mbar_init(&acc_full[b], 1); tc5::mbar_init(&acc_empty[b], 4); }
-    for (int b = 0; b < 2; ++b) { tc5::mbar_init(&c_full[b], 1); tc5::mbar_init(&c_ready[b], 4); tc5::mbar_init(&c_free[b], 1); }
+    for (int b = 0; b < 2; ++b) { tc5::mbar_init(&acc_full[b], 1); tc5::mbar_init(&acc_empty[b], PCfg<BN, TS>::EPI_WARPS); }
+    for (int b = 0; b < 2; ++b) { tc5::mbar_init(&c_full[b], 1); tc5::mbar_init(&c_ready[b], PCfg<BN, TS>::EPI_WARPS); tc5::mbar_init(&c_free[b], 1); }
     tc5::fence_barrier_init();
     tc5::prefetch_tensormap(&map_a);
     tc5::prefetch_tensormap(&map_w);
@@ -714,8 +715,10 @@ __global__ void __launch_bounds__(CONV ? 320 : PCfg<BN, TS>::THREADS_LINEAR, 1)
         TC5P_STAMP(ti, 6);   // MMA: all k-blocks of the tile issued
       }
     }
-  } else if (warp < 6) {
+  } else if (warp < 6 || (TS && warp >= 7 && warp < 11)) {
     const int q = warp & 3;  // TMEM lane quarter this warp may read
+    // bulk-copy epilogue: two warps per lane quarter, each takes half of the tile's columns
+    const int c_begin = (TS && warp >= 7) ? BN / 2 : 0, c_end = (TS && warp < 6) ? BN / 2 : BN;
     pdl_wait();
     const bool glu = (p.epilogue & B200_EPI_GLU) != 0;
     int ti = 0;
@@ -779,14 +782,14 @@ __global__ void __launch_bounds__(CONV ? 320 : PCfg<BN, TS>::THREADS_LINEAR, 1)
         };
         float va[16], vb[16];   // two units in flight: the next tcgen05.ld runs under the current unit's math
         __syncwarp();
-        tc5::tmem_ld_32x16(t_row, va);
+        tc5::tmem_ld_32x16(t_row + c_begin, va);
 #pragma unroll 1
-        for (int c = 0; c < BN; c += 32) {
+        for (int c = c_begin; c < c_end; c += 32) {
           tc5::tmem_ld_wait();
           tc5::tmem_ld_32x16(t_row + c + 16, vb);
           unit(va, c);
           tc5::tmem_ld_wait();
-          if (c + 32 < BN) tc5::tmem_ld_32x16(t_row + c + 32, va);
+          if (c + 32 < c_end) tc5::tmem_ld_32x16(t_row + c + 32, va);
           unit(vb, c + 16);
         }
         tc5::fence_proxy_async();   // the TMA store reads these generic-proxy writes
@@ -1170,7 +1173,7 @@ int launch_persistent(const Tc5Args& a, cudaStream_t st, const Tc5Conv* g = null
   const int64_t tiles_m = ceil_div(a.M, BM), tiles = tiles_m * ceil_div(a.N, BN);
   if (tiles >= (1ll << 31)) return B200_ENOTSUP;
   const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
-  launch_pdl(gemm_tc5p_kernel<T, BN, CONV, TS>, dim3(grid), dim3(CONV ? 320 : PCfg<BN, TS>::THREADS_LINEAR), SMEM, st, ma, mw, mr, mo, p,
+  launch_pdl(gemm_tc5p_kernel<T, BN, CONV, TS>, dim3(grid), dim3(CONV ? (TS ? 352 : 320) : PCfg<BN, TS>::THREADS), SMEM, st, ma, mw, mr, mo, p,
              static_cast<int>(tiles_m), static_cast<int>(tiles));
   B200_CHECK_LAUNCH("gemm_tc5p_kernel");
   return B200_OK;
@@ -1256,6 +1259,10 @@ int linear_tc5(const Tc5Args& a, cudaStream_t st) {
     return pl.bn == 64 ? launch<__half, 64, false, 2>(a, pl, st) : launch<__half, 128, false, 2>(a, pl, st);
   }
   if (pl.tiles_m == 1) {
+    if (a.dtype == B200_BF16) return pl.bn == 64 ? launch<__nv_bfloat16, 64, false, 1>(a, pl, st) : launch<__nv_bfloat16, 128, false, 1>(a, pl, st);
+    return pl.bn == 64 ? launch<__half, 64, false, 1>(a, pl, st) : launch<__half, 128, false, 1>(a, pl, st);
+  }
+  if (pl.splits > 1) {   // split-K CTAs sit alone on their SM (ring + receive buffer): give them the deeper ring of mode 1
     if (a.dtype == B200_BF16) return pl.bn == 64 ? launch<__nv_bfloat16, 64, false, 1>(a, pl, st) : launch<__nv_bfloat16, 128, false, 1>(a, pl, st);
     return pl.bn == 64 ? launch<__half, 64, false, 1>(a, pl, st) : launch<__half, 128, false, 1>(a, pl, st);
   }
