@@ -308,8 +308,15 @@ class CUDAExecutor:
                 continue
             p = step.params
             getattr(self, "_bind_" + p["op"])(plan, step, p)
-        plan.n_kernels = len(plan.launches) + sum(1 for s in self._program.steps
-                                                   if getattr(s, "params", None) and s.params.get("op") == "attention" and s.params["decode"])
+        # every library call is one kernel, except decode attention when its splits are merged by a
+        # second kernel (the library then asks for a workspace; with in-kernel merging it asks for none)
+        def _two_kernels(q) -> bool:
+            if not (q and q.get("op") == "attention" and q["decode"]):
+                return False
+            if not hasattr(self._lib, "b200_attn_decode_workspace_bytes"):
+                return True
+            return int(self._lib.b200_attn_decode_workspace_bytes(q["B"], q["Hq"], q["Hkv"], q["S"], q["D"])) > 0
+        plan.n_kernels = len(plan.launches) + sum(1 for s in self._program.steps if _two_kernels(getattr(s, "params", None)))
         for spec in self._program.output_specs:
             view = self._program.views.get(spec.name)
             if view is None:
