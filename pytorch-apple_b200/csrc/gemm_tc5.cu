@@ -1032,7 +1032,7 @@ Tc5Plan plan_for_bn(int bn, int64_t M, int64_t N, int64_t K) {
 Tc5Plan plan_tc5(int64_t M, int64_t N, int64_t K, bool glu = false) {
   const int64_t tm = ceil_div(M, BM);
   if (glu) return plan_for_bn(128, M, N, K);   // the gated epilogue pairs columns c and c+64 of a 128-wide tile
-  if (tm >= 2 && ceil_div(N, 128) * tm >= 148) return plan_for_bn(128, M, N, K);   // enough 128-wide tiles for every SM
+  if (ceil_div(N, 128) * tm >= 148) return plan_for_bn(128, M, N, K);   // enough 128-wide tiles for every SM
   if (tm >= 2 || prefer_bn128()) {
     // Too few wide tiles: either 64-wide tiles or wide tiles with split-K.  Take the wide ones when
     // split-K can still put (nearly) as many CTAs to work - they re-read the activations half as often.

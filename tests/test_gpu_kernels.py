@@ -184,7 +184,7 @@ def attn_ref(q, k, v, mask, scale, dtype):
     return torch.softmax(s, -1) @ v
 
 
-@pytest.mark.parametrize("B,S,valid", [(1, 4352, 4097), (8, 4352, 4100), (3, 80, 37), (2, 272, 272), (64, 512, 300)])
+@pytest.mark.parametrize("B,S,valid", [(1, 4352, 4097), (8, 4352, 4100), (3, 80, 37), (2, 272, 272), (64, 512, 300), (64, 4352, 4097), (5, 8192, 6000)])
 def test_attn_decode(lib, B, S, valid):
     import model_zoo as mz
 
