@@ -574,7 +574,7 @@ __global__ void __launch_bounds__(192, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(cons
 // bytes in flight - instead of one dependent 32-byte access per thread and 16 columns.
 template <int BN, bool TS> struct PCfg {
   static constexpr int A_STAGE = BM * BK * 2, B_STAGE = BN * BK * 2, STAGE = A_STAGE + B_STAGE;
-  static constexpr int ST = TS ? (BN == 256 ? 3 : (BN == 128 ? 4 : 6)) : (BN == 256 ? 4 : (BN == 128 ? 6 : 8));
+  static constexpr int ST = TS ? (BN == 256 ? 3 : (BN == 128 ? 5 : 8)) : (BN == 256 ? 4 : (BN == 128 ? 6 : 8));   // ring + C buffers fill the 227 KB
   static constexpr int CB = BM * BN * 2;               // one C buffer: BN/64 sub-tiles of [128 rows][128 bytes]
   static constexpr int NCB = TS ? (BN == 256 ? 1 : 2) : 0;
   static constexpr int SMEM = ST * STAGE + NCB * CB + 1024;

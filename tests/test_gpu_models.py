@@ -157,3 +157,23 @@ def test_unfused_generic_path_on_gpu():
     ref = to_f32(list(IRInterpreter(ir, sd).execute(ins).values())[0])
     out, _ = run_backend(ir, mz.state_dict_numpy(sd), np_inputs(ir, ins), {"fuse": False})
     assert np.abs(to_f32(out[ir["graph_outputs"][0]["name"]]) - ref).max() < 0.1
+
+
+def test_profile_entry_times_one_entry_point_in_a_graph():
+    """CUDAExecutor.profile_entry replays the calls of one entry point as a CUDA graph of their own."""
+    from golden.make_golden import tiny_qwen
+
+    from cuda_runtime import CUDABuffer
+
+    cfg, sd, model = tiny_qwen()
+    T = 16
+    ir = extract_ir(mz.QwenPrefillWrapper(model), mz.qwen2_example_inputs(cfg, 1, T, None, device="cpu"), "p")
+    g = torch.Generator().manual_seed(3)
+    ins = (torch.randint(0, cfg.vocab_size, (1, T), generator=g), mz.causal_mask(1, T, T, 0), torch.arange(T)[None], torch.arange(T))
+    _, dag = run_backend(ir, mz.state_dict_numpy(sd), np_inputs(ir, ins))
+    pid = next(iter(dag.npu_programs))
+    ex, w = dag._npu_executors[pid], dag._npu_weight_cache[pid]
+    feed = {s["name"]: CUDABuffer(t.cuda()) for s, t in zip(ir["graph_inputs"], ins)}
+    calls, ms = ex.profile_entry(feed, w, "b200_linear", iters=3)
+    assert calls > 0 and 0.0 < ms < 5.0
+    assert ex.profile_entry(feed, w, "b200_no_such_entry") == (0, 0.0)
