@@ -269,7 +269,7 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 // thread, 128 bytes of channels per k-block - with zero-filling cp.async into the same
 // 128-byte-swizzled layout TMA would produce, and signal the stage's barrier themselves.
 template <typename T, int BN, bool CONV, int MODE>
-__global__ void __launch_bounds__(192, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a,
+__global__ void __launch_bounds__(224, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a,
                                                           const __grid_constant__ CUtensorMap map_w, const Tc5Params p) {
   constexpr int ST = Cfg<BN, MODE>::ST, A_STAGE = Cfg<BN, MODE>::A_STAGE;
   constexpr int B_STAGE = BN * BK * 2, STAGE = A_STAGE + B_STAGE;
@@ -301,7 +301,8 @@ __global__ void __launch_bounds__(192, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(cons
   if (threadIdx.x == 0) {
     TC5_STAMP(0);
     failed = 0;
-    for (int s = 0; s < ST; ++s) { tc5::mbar_init(&full_bar[s], gather ? 129 : 1); tc5::mbar_init(&empty_bar[s], 1); }
+    // a stage is full when both producers' copies have landed (or the 128 gather threads have arrived)
+    for (int s = 0; s < ST; ++s) { tc5::mbar_init(&full_bar[s], gather ? 129 : 2); tc5::mbar_init(&empty_bar[s], 1); }
     tc5::mbar_init(&acc_bar, 1);
     tc5::fence_barrier_init();
     tc5::prefetch_tensormap(&map_a);
@@ -314,13 +315,17 @@ __global__ void __launch_bounds__(192, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(cons
   const uint32_t tmem_base = tmem_holder;
   pdl_trigger();   // the next kernel in the stream may be scheduled (it waits for this one before reading)
 
-  // Weights that no kernel of this stream writes can be fetched before the predecessor has
-  // finished: fill the ring with weight tiles first, then wait, then add the activation tiles.
-  const int pre = (!CONV && (p.epilogue & B200_EPI_W_STATIC)) ? (nkb < ST ? nkb : ST) : 0;
-  if (threadIdx.x == 0) {
+  // Two producer threads: one TMA-issuing thread sustains ~60 GB/s (measured: 0.26 us per 16 KB
+  // box whatever the ring depth; two threads issue twice that), so activations and weights each
+  // get their own - thread 0 of warp 0 the activation tiles, thread 0 of warp 6 the weight tiles.
+  // Weights that no kernel of this stream writes are fetched before the predecessor has finished:
+  // the weight producer simply runs ahead until the ring is full.
+  const bool w_static = (p.epilogue & B200_EPI_W_STATIC) != 0;
+  const int pre = w_static ? (nkb < ST ? nkb : ST) : 0;   // weight stages issued before the cluster start-up barrier
+  if (warp == 6 && lane == 0) {
     TC5_STAMP(1);
     for (int i = 0; i < pre; ++i) {
-      tc5::mbar_arrive_expect_tx(&full_bar[i], STAGE);
+      tc5::mbar_arrive_expect_tx(&full_bar[i], B_STAGE);
       tc5::tma_load_2d(smem + i * STAGE + A_STAGE, &map_w, &full_bar[i], (kb0 + i) * BK, n0);
     }
   }
@@ -328,32 +333,44 @@ __global__ void __launch_bounds__(192, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(cons
   // This barrier sits in the part of the kernel that overlaps the predecessor, so it costs nothing.
   if (nsp > 1) { __syncwarp(); tc5::cluster_sync(); }
 
-  if (warp == 0) {
-    if (lane == 0) {
+  if (warp == 6) {
+    if (lane == 0) {   // ---- weight producer ----
+      if (!w_static) pdl_wait();   // the weights may come from the kernel before this one
+      int issued = pre;
+      for (int i = pre; i < nkb; ++i) {
+        const int s = i % ST;
+        if (!tc5::mbar_wait(&empty_bar[s], ((i / ST) & 1) ^ 1)) { failed = 1; atomicExch(&g_tc5_error, 1); break; }
+        if (*reinterpret_cast<volatile int*>(&failed)) break;
+        tc5::mbar_arrive_expect_tx(&full_bar[s], B_STAGE);
+        tc5::tma_load_2d(smem + s * STAGE + A_STAGE, &map_w, &full_bar[s], (kb0 + i) * BK, n0);
+        issued = i + 1;
+      }
+      if (*reinterpret_cast<volatile int*>(&failed)) {  // wait (bounded) for our own copies still in flight
+        for (int i = issued > ST ? issued - ST : 0; i < issued; ++i) tc5::mbar_wait(&full_bar[i % ST], (i / ST) & 1, 1u << 16);
+      }
+    }
+  } else if (warp == 0) {
+    if (lane == 0 && !gather) {   // ---- activation producer (the gather variant fills the A tile with the epilogue warps) ----
       pdl_wait();
       TC5_STAMP(2);
-      int issued = pre;
+      int issued = 0;
       for (int i = 0; i < nkb; ++i) {
         const int s = i % ST;
-        const uint32_t ph = (i / ST) & 1;
-        if (i >= pre) {
-          if (!tc5::mbar_wait(&empty_bar[s], ph ^ 1)) { failed = 1; atomicExch(&g_tc5_error, 1); break; }
-          if (*reinterpret_cast<volatile int*>(&failed)) break;
-          tc5::mbar_arrive_expect_tx(&full_bar[s], gather ? B_STAGE : STAGE);
-          tc5::tma_load_2d(smem + s * STAGE + A_STAGE, &map_w, &full_bar[s], (kb0 + i) * BK, n0);
-        }
+        if (!tc5::mbar_wait(&empty_bar[s], ((i / ST) & 1) ^ 1)) { failed = 1; atomicExch(&g_tc5_error, 1); break; }
+        if (*reinterpret_cast<volatile int*>(&failed)) break;
+        tc5::mbar_arrive_expect_tx(&full_bar[s], A_STAGE);
         if (!CONV) {
           tc5::tma_load_2d(smem + s * STAGE, &map_a, &full_bar[s], (kb0 + i) * BK, m0);
-        } else if (!gather) {
+        } else {
           const int cpb = p.g.C / BK, kb = kb0 + i, tap = kb / cpb, r = tap / p.g.KW;
           const int img = m0 / (p.g.Ho * p.g.Wo), rem = m0 - img * (p.g.Ho * p.g.Wo), oh = rem / p.g.Wo, ow = rem - oh * p.g.Wo;
           tc5::tma_load_im2col_4d(smem + s * STAGE, &map_a, &full_bar[s], (kb - tap * cpb) * BK, ow * p.g.sw - p.g.pw, oh * p.g.sh - p.g.ph, img,
                                   tap - r * p.g.KW, r);
         }
-        if (i + 1 > issued) issued = i + 1;
+        issued = i + 1;
       }
-      if (*reinterpret_cast<volatile int*>(&failed)) {  // wait (bounded) for our own copies still in flight
-        for (int i = issued > ST ? issued - ST : 0; i < issued; ++i) tc5::mbar_wait(&full_bar[i % ST], (i / ST) & 1);
+      if (*reinterpret_cast<volatile int*>(&failed)) {
+        for (int i = issued > ST ? issued - ST : 0; i < issued; ++i) tc5::mbar_wait(&full_bar[i % ST], (i / ST) & 1, 1u << 16);
       }
     }
   } else if (warp == 1) {
@@ -491,7 +508,7 @@ __global__ void __launch_bounds__(192, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(cons
     else __syncthreads();
     if (threadIdx.x == 64) TC5_STAMP(7);
     if (!*reinterpret_cast<volatile int*>(&failed)) {
-      // All 192 threads walk the owned rows as float4 units in row-major order.  The loop body is
+      // All 224 threads walk the owned rows as float4 units in row-major order.  The loop body is
       // kept short: it runs a handful of times per thread, so its cost is instruction count.
       constexpr int LOG_UNITS = BN == 64 ? 4 : 5;              // float4 units per tile row (staged tiles are 64 or 128 wide)
       const int log_pr = glu ? 4 : LOG_UNITS;                  // gated: the 16 units of gate columns, each paired with +64
@@ -505,7 +522,7 @@ __global__ void __launch_bounds__(192, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(cons
       const bool vec_ok = (reinterpret_cast<uintptr_t>(outp) & 7u) == 0 && (p.ldo & 3) == 0 && bias_kind < 3 &&
                           (!resp || ((reinterpret_cast<uintptr_t>(resp) & 7u) == 0 && (p.ldr & 3) == 0)) && !(p.epilogue & B200_EPI_SILU_MUL);
 #pragma unroll 1
-      for (int idx = static_cast<int>(threadIdx.x); idx < total; idx += 192) {
+      for (int idx = static_cast<int>(threadIdx.x); idx < total; idx += 224) {
         const int lr = idx >> log_pr, col = (idx & ((1 << log_pr) - 1)) << 2;
         const float* src = part + lr * PART_PITCH + col;
         float4 acc = *reinterpret_cast<const float4*>(src), up = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -578,12 +595,17 @@ template <int BN, bool TS> struct PCfg {
   static constexpr int CB = BM * BN * 2;               // one C buffer: BN/64 sub-tiles of [128 rows][128 bytes]
   static constexpr int NCB = TS ? (BN == 256 ? 1 : 2) : 0;
   static constexpr int SMEM = ST * STAGE + NCB * CB + 1024;
-  static constexpr int THREADS = TS ? 352 : 192;        // TS: warps 2-5 and 7-10 share the epilogue (half the columns each), warp 6 stores
+  // warps: 0 activation producer, 1 MMA, 2-5 epilogue; TS adds 6 store, 7-10 second epilogue group
+  // (half the columns each); the gather variant adds 6-9 gather; the last warp is the weight producer
+  static constexpr int THREADS = TS ? 384 : 224;
+  static constexpr int THREADS_GATHER = 352;            // CONV without im2col (never TS)
+  static constexpr int W_WARP = TS ? 11 : 6;
+  static constexpr int W_WARP_GATHER = 10;
   static constexpr int EPI_WARPS = TS ? 8 : 4;
 };
 
 template <typename T, int BN, bool CONV, bool TS>
-__global__ void __launch_bounds__(CONV ? (TS ? 352 : 320) : PCfg<BN, TS>::THREADS, 1)
+__global__ void __launch_bounds__(TS ? 384 : (CONV ? 352 : 224), 1)
     gemm_tc5p_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                      const __grid_constant__ CUtensorMap map_r, const __grid_constant__ CUtensorMap map_o, const Tc5Params p,
                      const int tiles_m, const int n_tiles) {
@@ -603,7 +625,8 @@ __global__ void __launch_bounds__(CONV ? (TS ? 352 : 320) : PCfg<BN, TS>::THREAD
 
   if (threadIdx.x == 0) {
     failed = 0;
-    for (int s = 0; s < ST; ++s) { tc5::mbar_init(&full_bar[s], (CONV && !p.g.im2col) ? 129 : 1); tc5::mbar_init(&empty_bar[s], 1); }
+    // a stage is full when both producers' copies have landed (or the 128 gather threads have arrived)
+    for (int s = 0; s < ST; ++s) { tc5::mbar_init(&full_bar[s], (CONV && !p.g.im2col) ? 129 : 2); tc5::mbar_init(&empty_bar[s], 1); }
     for (int b = 0; b < 2; ++b) { tc5::mbar_init(&acc_full[b], 1); tc5::mbar_init(&acc_empty[b], PCfg<BN, TS>::EPI_WARPS); }
     for (int b = 0; b < 2; ++b) { tc5::mbar_init(&c_full[b], 1); tc5::mbar_init(&c_ready[b], PCfg<BN, TS>::EPI_WARPS); tc5::mbar_init(&c_free[b], 1); }
     tc5::fence_barrier_init();
@@ -656,28 +679,46 @@ __global__ void __launch_bounds__(CONV ? (TS ? 352 : 320) : PCfg<BN, TS>::THREAD
           const int s = it % ST;
           if (!tc5::mbar_wait(&empty_bar[s], ((it / ST) & 1) ^ 1)) { failed = 1; atomicExch(&g_tc5_error, 11); break; }
           TC5P_KB(0, ti, kb);
-          tc5::mbar_arrive_expect_tx(&full_bar[s], (CONV && !p.g.im2col) ? B_STAGE : STAGE);
+          if (CONV && !p.g.im2col) continue;   // gather variant: warps 6-9 fill the A tile
+          tc5::mbar_arrive_expect_tx(&full_bar[s], A_STAGE);
           if (CONV && p.g.c8) {
-            // 8-channel input: k-block = 8 filter taps, each a [128 pixels][16 B] box (A) and a
-            // [BN rows][16 B] box (W).  Taps past the filter read zero weights (outside the weight
-            // map), so the activation box they are paired with only has to be finite: tap 0 again.
+            // 8-channel input: k-block = 8 filter taps, each a [128 pixels][16 B] box.  Taps past the
+            // filter meet zero weights (outside the weight map), so their box only has to be finite: tap 0 again.
             for (int tt = 0; tt < 8; ++tt) {
               const int tap = kb * 8 + tt, ta = tap < p.g.KH * p.g.KW ? tap : 0, r = ta / p.g.KW;
               tc5::tma_load_im2col_4d(smem + s * STAGE + tt * (BM * 16), &map_a, &full_bar[s], 0, base_w, base_h, img, ta - r * p.g.KW, r);
-              tc5::tma_load_2d(smem + s * STAGE + A_STAGE + tt * (BN * 16), &map_w, &full_bar[s], tap * 8, n0);
             }
-            continue;
-          }
-          if (!CONV) {
+          } else if (!CONV) {
             tc5::tma_load_2d(smem + s * STAGE, &map_a, &full_bar[s], kb * BK, m0);
-          } else if (p.g.im2col) {
+          } else {
             const int tap = kb / cpb, r = tap / p.g.KW;
             tc5::tma_load_im2col_4d(smem + s * STAGE, &map_a, &full_bar[s], (kb - tap * cpb) * BK, base_w, base_h, img, tap - r * p.g.KW, r);
           }
-          tc5::tma_load_2d(smem + s * STAGE + A_STAGE, &map_w, &full_bar[s], kb * BK, n0);
         }
       }
       if (dead()) {  // wait (bounded) for our own copies still in flight
+        for (int i = it > ST ? it - ST : 0; i < it; ++i) tc5::mbar_wait(&full_bar[i % ST], (i / ST) & 1, 1u << 16);
+      }
+    }
+  } else if (warp == ((CONV && !TS && !p.g.im2col) ? PCfg<BN, TS>::W_WARP_GATHER : PCfg<BN, TS>::W_WARP)) {
+    // ---- weight producer: one TMA-issuing thread sustains ~60 GB/s, so weights get their own ----
+    if (lane == 0) {
+      if (!(p.epilogue & B200_EPI_W_STATIC)) pdl_wait();
+      int it = 0;
+      for (int tile = blockIdx.x; tile < n_tiles && !dead(); tile += gridDim.x) {
+        const int n0 = (tile / tiles_m) * BN;
+        for (int kb = 0; kb < KB; ++kb, ++it) {
+          const int s = it % ST;
+          if (!tc5::mbar_wait(&empty_bar[s], ((it / ST) & 1) ^ 1)) { failed = 1; atomicExch(&g_tc5_error, 19); break; }
+          tc5::mbar_arrive_expect_tx(&full_bar[s], B_STAGE);
+          if (CONV && p.g.c8) {
+            for (int tt = 0; tt < 8; ++tt) tc5::tma_load_2d(smem + s * STAGE + A_STAGE + tt * (BN * 16), &map_w, &full_bar[s], (kb * 8 + tt) * 8, n0);
+          } else {
+            tc5::tma_load_2d(smem + s * STAGE + A_STAGE, &map_w, &full_bar[s], kb * BK, n0);
+          }
+        }
+      }
+      if (dead()) {
         for (int i = it > ST ? it - ST : 0; i < it; ++i) tc5::mbar_wait(&full_bar[i % ST], (i / ST) & 1, 1u << 16);
       }
     }
@@ -1067,7 +1108,7 @@ int launch(const Tc5Args& a, const Tc5Plan& plan, cudaStream_t st, const Tc5Conv
       if (fit[splits] == 0) {
         cudaLaunchConfig_t q = {};
         q.gridDim = dim3(static_cast<unsigned>(pl.tiles_n), static_cast<unsigned>(pl.tiles_m), static_cast<unsigned>(splits));
-        q.blockDim = dim3(192);
+        q.blockDim = dim3(224);
         q.dynamicSmemBytes = SMEM_SPLIT;
         cudaLaunchAttribute ca;
         ca.id = cudaLaunchAttributeClusterDimension;
@@ -1106,7 +1147,7 @@ int launch(const Tc5Args& a, const Tc5Plan& plan, cudaStream_t st, const Tc5Conv
   if (CONV && pl.splits != 1) return B200_ENOTSUP;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(pl.tiles_n), static_cast<unsigned>(pl.tiles_m), static_cast<unsigned>(pl.splits));
-  cfg.blockDim = dim3(192);
+  cfg.blockDim = dim3(224);
   cfg.dynamicSmemBytes = SMEM;
   cfg.stream = st;
   cudaLaunchAttribute attrs[2];
@@ -1173,7 +1214,7 @@ int launch_persistent(const Tc5Args& a, cudaStream_t st, const Tc5Conv* g = null
   const int64_t tiles_m = ceil_div(a.M, BM), tiles = tiles_m * ceil_div(a.N, BN);
   if (tiles >= (1ll << 31)) return B200_ENOTSUP;
   const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
-  launch_pdl(gemm_tc5p_kernel<T, BN, CONV, TS>, dim3(grid), dim3(CONV ? (TS ? 352 : 320) : PCfg<BN, TS>::THREADS), SMEM, st, ma, mw, mr, mo, p,
+  launch_pdl(gemm_tc5p_kernel<T, BN, CONV, TS>, dim3(grid), dim3(TS ? 384 : ((CONV && !p.g.im2col) ? 352 : 224)), SMEM, st, ma, mw, mr, mo, p,
              static_cast<int>(tiles_m), static_cast<int>(tiles));
   B200_CHECK_LAUNCH("gemm_tc5p_kernel");
   return B200_OK;
