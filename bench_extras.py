@@ -1,7 +1,9 @@
 """Secondary workloads reported next to the headline decode number (``"also"`` in the
 benchmark's JSON line): Qwen2.5-1.5B-architecture decode at B=1 and B=8, prefill of a
-512-token prompt, and ResNet-50 fp16 inference at batch 1 / 32 / 256.  All are timed with
-CUDA events over device-resident inputs, after warm-up, as whole-graph replays.
+512-token prompt, ResNet-50 fp16 inference at batch 1 / 32 / 256, and the bandwidth
+kernels (RMSNorm, SiLU*up, masked softmax, RoPE) on their own at 128 / 2048 / 8192 tokens.
+All are timed with CUDA events over device-resident inputs, after warm-up, as whole-graph
+replays.
 """
 
 from __future__ import annotations
@@ -104,6 +106,73 @@ def resnet50(device, batch: int, tflops_peak: float) -> dict:
             "tensor_frac": flops / (ms * 1e-3) / 1e12 / tflops_peak, "launches": ex.last_launch_count}
 
 
+def ops(device, hbm_gbs: float, tokens=(128, 2048, 8192)) -> dict:
+    """The bandwidth kernels on their own, at Qwen2.5-1.5B widths and ``T`` tokens, bf16:
+    RMSNorm [T,1536]; SiLU(gate)*up [T,8960]; masked softmax over [1,12,T,T] scores with a
+    [1,1,T,T] additive mask; rotary embedding of q [1,12,T,128].  Each call is captured
+    into a CUDA graph that walks enough separate buffer sets to exceed the L2 (so every
+    call reads cold data), and the graph is timed with CUDA events.  ``gbs`` is the
+    algorithmic bytes of one call (inputs read once, outputs written once) over its share
+    of the graph's time."""
+    from cuda_compiler.cuda_codegen import EW_OPCODES
+    from cuda_runtime import native
+
+    lib = native.load()
+    BF = native.DTYPE_CODES["bfloat16"]
+    H, I, NH, D = 1536, 8960, 12, 128
+    gen = torch.Generator(device=device).manual_seed(3)
+
+    def rnd(*shape):
+        return torch.randn(*shape, device=device, generator=gen).bfloat16()
+
+    def timed(bytes_per_call, make_set, call):
+        n_sets = int(max(2, min(64, -(-400_000_000 // bytes_per_call))))
+        sets = [make_set() for _ in range(n_sets)]
+        side = torch.cuda.Stream(device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for s in sets:
+                call(s, side.cuda_stream)
+        side.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            for s in sets:
+                call(s, side.cuda_stream)
+        ms = _time_runs(graph.replay, 3, 15) / n_sets
+        return {"us": ms * 1e3, "gbs": bytes_per_call / (ms * 1e-3) / 1e9, "hbm_frac": bytes_per_call / (ms * 1e-3) / 1e9 / hbm_gbs,
+                "algorithmic_bytes": int(bytes_per_call), "buffer_sets": n_sets}
+
+    out = {}
+    for T in tokens:
+        res = {}
+        w = rnd(H)
+        res["rmsnorm"] = timed(2 * T * H * 2 + H * 2, lambda: (rnd(T, H), torch.empty(T, H, device=device, dtype=torch.bfloat16)),
+                               lambda s, st: native.check(lib.b200_rmsnorm(s[0].data_ptr(), w.data_ptr(), s[1].data_ptr(), T, H, H, H, 1e-6, BF, 1, st)))
+        chain = (native.EwOp * 2)(native.EwOp(EW_OPCODES["SILU"], 0, -1, BF, 0.0), native.EwOp(EW_OPCODES["MUL"], 4, 1, BF, 0.0))
+
+        def silu_mul(s, st):
+            ins = (native.Tensor * 2)(*[native.make_tensor(t.data_ptr(), "bfloat16", (T, I), (I, 1)) for t in s[:2]])
+            o = native.make_tensor(s[2].data_ptr(), "bfloat16", (T, I), (I, 1))
+            native.check(lib.b200_ew_chain(o, ins, 2, chain, 2, st))
+
+        res["silu_mul"] = timed(3 * T * I * 2, lambda: (rnd(T, I), rnd(T, I), torch.empty(T, I, device=device, dtype=torch.bfloat16)), silu_mul)
+        mask = torch.full((T, T), float("-inf"), device=device).triu(1).bfloat16()
+        res["masked_softmax"] = timed(2 * NH * T * T * 2 + T * T * 2,
+                                      lambda: (rnd(NH, T, T), torch.empty(NH, T, T, device=device, dtype=torch.bfloat16)),
+                                      lambda s, st: native.check(lib.b200_softmax(s[0].data_ptr(), mask.data_ptr(), s[1].data_ptr(), 1, NH, T, T,
+                                                                                   0, 0, T, D ** -0.5, BF, BF, BF, 1, st)))
+        cos, sin = rnd(T, D), rnd(T, D)
+
+        def rope(s, st):
+            x = native.make_tensor(s[0].data_ptr(), "bfloat16", (1, NH, T, D), (NH * T * D, T * D, D, 1))
+            native.check(lib.b200_rope_rotate(x, cos.data_ptr(), sin.data_ptr(), s[1].data_ptr(), None, None, 0, native.DTYPE_CODES["int64"], st))
+
+        res["rope"] = timed(2 * NH * T * D * 2 + 2 * T * D * 2, lambda: (rnd(NH, T, D), torch.empty(NH, T, D, device=device, dtype=torch.bfloat16)), rope)
+        out[f"t{T}"] = res
+        torch.cuda.empty_cache()
+    return out
+
+
 def run(cfg, sd, device) -> dict:
     from bench import measured_peaks
 
@@ -117,6 +186,7 @@ def run(cfg, sd, device) -> dict:
     for b in (1, 32, 256):
         out[f"resnet50_b{b}"] = resnet50(device, b, tf)
         torch.cuda.empty_cache()
+    out["ops"] = ops(device, hbm)
     return out
 
 
@@ -125,13 +195,14 @@ if __name__ == "__main__":
     #   python bench_extras.py qwen_prefill --layers 2
     #   python bench_extras.py resnet50 --batch 256
     #   python bench_extras.py qwen_decode --layers 2 --batch 1
+    #   python bench_extras.py ops
     import argparse
     import json
 
     from bench import measured_peaks
 
     ap = argparse.ArgumentParser()
-    ap.add_argument("workload", choices=["qwen_prefill", "qwen_decode", "resnet50"])
+    ap.add_argument("workload", choices=["qwen_prefill", "qwen_decode", "resnet50", "ops"])
     ap.add_argument("--layers", type=int, default=28)
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--tokens", type=int, default=512)
@@ -139,7 +210,9 @@ if __name__ == "__main__":
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
     hbm, tf, _ = measured_peaks()
-    if a.workload == "resnet50":
+    if a.workload == "ops":
+        print(json.dumps(ops(dev, hbm)))
+    elif a.workload == "resnet50":
         print(json.dumps(resnet50(dev, a.batch, tf)))
     else:
         cfg = mz.qwen2_config(num_layers=a.layers)

@@ -73,44 +73,61 @@ struct RopeParams {
   int pos_dtype;
 };
 
-// One thread per 8 consecutive head dims.
-template <typename T>
+// One thread per pair of 16-byte packs (dims d..d+7 and d+D/2..d+D/2+7): both halves of a
+// rotation are read once.  Products are rounded in pairs (one packed conversion per two
+// values; the conversion unit is the scarce one), index arithmetic in IDX (32-bit when the
+// tensor allows it).
+template <typename T, typename IDX>
 __global__ void __launch_bounds__(128) rope_rotate_kernel(const __grid_constant__ RopeParams p) {
-  const int packs = p.D >> 3, half_packs = packs >> 1;
-  const int64_t gid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  const int64_t total = p.B * p.H * p.T * packs;
+  const IDX half_packs = static_cast<IDX>(p.D >> 4);
+  const IDX gid = static_cast<IDX>(blockIdx.x) * 128 + threadIdx.x;
+  const IDX total = static_cast<IDX>(p.B * p.H * p.T) * half_packs;
   if (gid >= total) return;
-  const int pk = static_cast<int>(gid % packs);
-  int64_t r = gid / packs;
-  const int64_t t = r % p.T; r /= p.T;
-  const int64_t h = r % p.H;
-  const int64_t b = r / p.H;
-  const T* xr = static_cast<const T*>(p.x) + b * p.xs[0] + h * p.xs[1] + t * p.xs[2];
-  const int64_t tab = (b * p.T + t) * p.D;
-  float xv[8], ov[8], c[8], s[8];
-  unpack8<T>(*(reinterpret_cast<const uint4*>(xr) + pk), xv);
-  const int opk = pk < half_packs ? pk + half_packs : pk - half_packs;
-  unpack8<T>(*(reinterpret_cast<const uint4*>(xr) + opk), ov);
-  unpack8<T>(__ldg(reinterpret_cast<const uint4*>(static_cast<const T*>(p.cos_t) + tab) + pk), c);
-  unpack8<T>(__ldg(reinterpret_cast<const uint4*>(static_cast<const T*>(p.sin_t) + tab) + pk), s);
-  const float sign = pk < half_packs ? -1.f : 1.f;
-  float out[8];
+  const IDX row = gid / half_packs;
+  const int pk = static_cast<int>(gid - row * half_packs);
+  const IDX bh = row / static_cast<IDX>(p.T);
+  const int64_t t = static_cast<int64_t>(row - bh * static_cast<IDX>(p.T));
+  const IDX b = bh / static_cast<IDX>(p.H);
+  const int64_t h = static_cast<int64_t>(bh - b * static_cast<IDX>(p.H));
+  const uint4* xr = reinterpret_cast<const uint4*>(static_cast<const T*>(p.x) + static_cast<int64_t>(b) * p.xs[0] + h * p.xs[1] + t * p.xs[2]);
+  const int64_t tab = (static_cast<int64_t>(b) * p.T + t) * p.D;
+  const uint4* ct = reinterpret_cast<const uint4*>(static_cast<const T*>(p.cos_t) + tab);
+  const uint4* st = reinterpret_cast<const uint4*>(static_cast<const T*>(p.sin_t) + tab);
+  const int hp = static_cast<int>(half_packs);
+  const uint4 rlo = ld_global_nc_v4(xr + pk), rhi = ld_global_nc_v4(xr + pk + hp);
+  const uint4 rclo = __ldg(ct + pk), rchi = __ldg(ct + pk + hp), rslo = __ldg(st + pk), rshi = __ldg(st + pk + hp);
+  float lo[8], hi[8], c[8], s[8], olo[8], ohi[8];
+  unpack8<T>(rlo, lo);
+  unpack8<T>(rhi, hi);
+  unpack8<T>(rclo, c);
+  unpack8<T>(rslo, s);
 #pragma unroll
-  for (int k = 0; k < 8; ++k) {
-    const float a = round_as<T>(xv[k] * c[k]);
-    const float rb = round_as<T>(sign * ov[k] * s[k]);
-    out[k] = a + rb;
+  for (int k = 0; k < 8; k += 2) {   // first half: x1*cos + (-x2)*sin
+    float a0 = lo[k] * c[k], a1 = lo[k + 1] * c[k + 1], b0 = -hi[k] * s[k], b1 = -hi[k + 1] * s[k + 1];
+    round2<T>(a0, a1);
+    round2<T>(b0, b1);
+    olo[k] = a0 + b0; olo[k + 1] = a1 + b1;
+  }
+  unpack8<T>(rchi, c);
+  unpack8<T>(rshi, s);
+#pragma unroll
+  for (int k = 0; k < 8; k += 2) {   // second half: x2*cos + x1*sin
+    float a0 = hi[k] * c[k], a1 = hi[k + 1] * c[k + 1], b0 = lo[k] * s[k], b1 = lo[k + 1] * s[k + 1];
+    round2<T>(a0, a1);
+    round2<T>(b0, b1);
+    ohi[k] = a0 + b0; ohi[k + 1] = a1 + b1;
   }
   T* dst;
   if (p.cache) {
     int64_t pos = load_index(p.cache_pos, t, p.pos_dtype);
     if (pos < 0) pos += p.cache_len;
     if (pos < 0 || pos >= p.cache_len) return;
-    dst = static_cast<T*>(p.cache) + ((b * p.H + h) * p.cache_len + pos) * p.D;
+    dst = static_cast<T*>(p.cache) + (static_cast<int64_t>(bh) * p.cache_len + pos) * p.D;
   } else {
-    dst = static_cast<T*>(p.y) + ((b * p.H + h) * p.T + t) * p.D;
+    dst = static_cast<T*>(p.y) + static_cast<int64_t>(row) * p.D;
   }
-  reinterpret_cast<uint4*>(dst)[pk] = pack8<T>(out);
+  reinterpret_cast<uint4*>(dst)[pk] = pack8<T>(olo);
+  reinterpret_cast<uint4*>(dst)[pk + hp] = pack8<T>(ohi);
 }
 
 struct QkvPostParams {
@@ -272,11 +289,16 @@ extern "C" int b200_rope_rotate(const b200_tensor* x, const void* cos_t, const v
   const bool ok = aligned16(x->data) && aligned16(cos_t) && aligned16(sin_t) && aligned16(kv_cache ? kv_cache : y) &&
                   p.xs[0] % 8 == 0 && p.xs[1] % 8 == 0 && p.xs[2] % 8 == 0;
   if (!ok) B200_FAIL(B200_EALIGN, "b200_rope_rotate: operands must be 16-byte aligned with strides multiple of 8");
-  const int64_t total = p.B * p.H * p.T * (p.D >> 3);
+  const int64_t total = p.B * p.H * p.T * (p.D >> 4);
   if (total == 0) return B200_OK;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const unsigned grid = static_cast<unsigned>(ceil_div(total, 128));
-  B200_DISPATCH_HALF(x->dtype, T, { rope_rotate_kernel<T><<<grid, 128, 0, st>>>(p); });
+  const int64_t grid = ceil_div(total, 128);
+  B200_CHECK_ARG(grid < (1ll << 31), "b200_rope_rotate: tensor too large");
+  const bool small = total + 128 < (1ll << 32);
+  B200_DISPATCH_HALF(x->dtype, T, {
+    if (small) rope_rotate_kernel<T, uint32_t><<<static_cast<unsigned>(grid), 128, 0, st>>>(p);
+    else rope_rotate_kernel<T, int64_t><<<static_cast<unsigned>(grid), 128, 0, st>>>(p);
+  });
   B200_CHECK_LAUNCH("rope_rotate_kernel");
   return B200_OK;
 }

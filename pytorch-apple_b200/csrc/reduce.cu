@@ -87,73 +87,148 @@ struct SoftmaxParams {
   float scale;
   int round_steps;
   int mask_dtype;
+  int d1_inner;   // walk d1 fastest: blocks that share a mask row (mask broadcast over d1) run back to back
 };
 
 __device__ __forceinline__ float fast_exp(float x) { return exp2f(x * 1.4426950408889634f); }
+__device__ __forceinline__ float ex2_ftz(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
-// BLOCK threads cooperate on one row; each holds up to 4 packs of 8 elements.
+// True when rounding a and b to T would not change them (cheap test, may say false for
+// values that are in fact representable).  bf16 is the upper half of an fp32.
+template <typename T> __device__ __forceinline__ bool exact_in(const float (&f)[8]) { return false; }
+template <> __device__ __forceinline__ bool exact_in<__nv_bfloat16>(const float (&f)[8]) {
+  uint32_t low = 0;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) low |= __float_as_uint(f[k]);
+  return (low & 0xffffu) == 0;
+}
+
+// Block reduction with one barrier: every warp leaves its partial in `slot` and every
+// thread combines all partials itself.  Consecutive calls must alternate between two slots.
+template <bool IS_MAX, int BLOCK> __device__ __forceinline__ float block_combine(float v, float* slot) {
+  constexpr int NW = BLOCK / 32;
+  v = IS_MAX ? warp_max(v) : warp_sum(v);
+  if (NW == 1) return v;
+  if ((threadIdx.x & 31) == 0) slot[threadIdx.x >> 5] = v;
+  __syncthreads();
+  if (NW <= 8) {
+    float t = slot[0];
+#pragma unroll
+    for (int i = 1; i < NW; ++i) t = IS_MAX ? fmaxf(t, slot[i]) : t + slot[i];
+    return t;
+  }
+  const float t = slot[threadIdx.x & 31];  // NW == 32
+  return IS_MAX ? warp_max(t) : warp_sum(t);
+}
+
+// BLOCK threads cooperate on one row (one block per row); each holds up to 4 packs of 8
+// elements.  The special function unit that computes ex2 also does the float conversions, and
+// it is the unit this kernel can saturate before the memory system: values are rounded in pairs
+// (one packed conversion per two elements), and the rounding after the mask is added is skipped
+// for a pack whose sums are already representable (always so for masks of 0 / -inf).
+// (A persistent variant that prefetched its next row into registers ran 40 % slower: 80
+// registers instead of 56 cost more in resident threads than the prefetch gained.)
 template <typename TI, typename TO, int BLOCK>
 __global__ void __launch_bounds__(BLOCK) softmax_row_kernel(const __grid_constant__ SoftmaxParams p) {
-  __shared__ float scratch[33];
+  __shared__ float scratch[2][32];
   constexpr int MAXP = 4;
-  const int64_t row = blockIdx.x;
-  const int64_t i2 = row % p.d2, i1 = (row / p.d2) % p.d1, i0 = row / (p.d2 * p.d1);
-  const TI* xr = static_cast<const TI*>(p.x) + row * p.cols;
-  TO* yr = static_cast<TO*>(p.y) + row * p.cols;
-  const int64_t moff = i0 * p.ms0 + i1 * p.ms1 + i2 * p.ms2;
+  constexpr float LOG2E = 1.4426950408889634f;
   const int npack = static_cast<int>(p.cols >> 3);
-  float v[MAXP][8];
-  float mx = -INFINITY;
+  const bool scaled = p.scale != 1.f, rounded = p.round_steps != 0;
+  const bool mask16 = p.mask && p.mask_dtype != B200_F32;
+  uint4 raw[MAXP], mraw[MAXP];
+  // row index and mask offset of work item `idx`
+  auto locate = [&](int64_t idx, int64_t& row, int64_t& moff) {
+    int64_t i0, i1, i2;
+    if (p.d1_inner) {   // a mask row is then read from DRAM once and found in L2 by the other d1 - 1 blocks
+      i1 = idx % p.d1; i2 = (idx / p.d1) % p.d2; i0 = idx / (p.d2 * p.d1);
+    } else {
+      i2 = idx % p.d2; i1 = (idx / p.d2) % p.d1; i0 = idx / (p.d2 * p.d1);
+    }
+    row = (i0 * p.d1 + i1) * p.d2 + i2;
+    moff = i0 * p.ms0 + i1 * p.ms1 + i2 * p.ms2;
+  };
+  auto issue = [&](int64_t row, int64_t moff) {
+    const uint4* xr = reinterpret_cast<const uint4*>(static_cast<const TI*>(p.x) + row * p.cols);
 #pragma unroll
-  for (int i = 0; i < MAXP; ++i) {
-    const int pk = threadIdx.x + BLOCK * i;
-    if (pk < npack) {
-      unpack8<TI>(ld_global_nc_v4(reinterpret_cast<const uint4*>(xr) + pk), v[i]);
-      float m[8];
-      if (p.mask) {
-        if (p.mask_dtype == B200_F32) {
-          const float4* mp = reinterpret_cast<const float4*>(static_cast<const float*>(p.mask) + moff) + 2 * pk;
-          const float4 a = __ldg(mp), b = __ldg(mp + 1);
-          m[0] = a.x; m[1] = a.y; m[2] = a.z; m[3] = a.w; m[4] = b.x; m[5] = b.y; m[6] = b.z; m[7] = b.w;
-        } else {
-          unpack8<TI>(__ldg(reinterpret_cast<const uint4*>(static_cast<const TI*>(p.mask) + moff) + pk), m);
+    for (int i = 0; i < MAXP; ++i) {
+      const int pk = threadIdx.x + BLOCK * i;
+      if (pk < npack) {
+        raw[i] = ld_global_nc_v4(xr + pk);
+        if (mask16) mraw[i] = __ldg(reinterpret_cast<const uint4*>(static_cast<const TI*>(p.mask) + moff) + pk);
+      }
+    }
+  };
+  int64_t row, moff;
+  locate(blockIdx.x, row, moff);
+  issue(row, moff);
+  {
+    float v[MAXP][8];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < MAXP; ++i) {
+      const int pk = threadIdx.x + BLOCK * i;
+      if (pk < npack) {
+        unpack8<TI>(raw[i], v[i]);
+        if (scaled) {
+#pragma unroll
+          for (int k = 0; k < 8; k += 2) {
+            v[i][k] *= p.scale; v[i][k + 1] *= p.scale;
+            if (rounded) round2<TI>(v[i][k], v[i][k + 1]);
+          }
         }
-      }
+        if (p.mask) {
+          float m[8];
+          if (mask16) {
+            unpack8<TI>(mraw[i], m);
+          } else {
+            const float4* mp = reinterpret_cast<const float4*>(static_cast<const float*>(p.mask) + moff) + 2 * pk;
+            const float4 a = __ldg(mp), b = __ldg(mp + 1);
+            m[0] = a.x; m[1] = a.y; m[2] = a.z; m[3] = a.w; m[4] = b.x; m[5] = b.y; m[6] = b.z; m[7] = b.w;
+          }
 #pragma unroll
-      for (int k = 0; k < 8; ++k) {
-        float t = v[i][k];
-        if (p.scale != 1.f) { t *= p.scale; if (p.round_steps) t = round_as<TI>(t); }
-        if (p.mask) { t += m[k]; if (p.round_steps) t = round_as<TI>(t); }
-        v[i][k] = t;
-        mx = fmaxf(mx, t);
+          for (int k = 0; k < 8; ++k) v[i][k] += m[k];
+          if (rounded && !exact_in<TI>(v[i])) {
+#pragma unroll
+            for (int k = 0; k < 8; k += 2) round2<TI>(v[i][k], v[i][k + 1]);
+          }
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) mx = fmaxf(mx, v[i][k]);
       }
     }
-  }
-  if (BLOCK == 32) mx = warp_max(mx); else mx = block_reduce<true>(mx, scratch);
-  if (mx == -INFINITY) mx = 0.f;  // fully -inf row: exp(-inf - 0) = 0 everywhere, matches 0/0 guard below
-  float sum = 0.f;
+    TO* yr = static_cast<TO*>(p.y) + row * p.cols;
+    mx = block_combine<true, BLOCK>(mx, scratch[0]);
+    if (mx == -INFINITY) mx = 0.f;  // fully -inf row: every exp is 0, the row becomes 0 * inf = NaN as in ATen
+    const float mxl = mx * LOG2E;
+    float sum = 0.f;
 #pragma unroll
-  for (int i = 0; i < MAXP; ++i) {
-    const int pk = threadIdx.x + BLOCK * i;
-    if (pk < npack) {
+    for (int i = 0; i < MAXP; ++i) {
+      const int pk = threadIdx.x + BLOCK * i;
+      if (pk < npack) {
 #pragma unroll
-      for (int k = 0; k < 8; ++k) { v[i][k] = fast_exp(v[i][k] - mx); sum += v[i][k]; }
+        for (int k = 0; k < 8; ++k) { v[i][k] = ex2_ftz(fmaf(v[i][k], LOG2E, -mxl)); sum += v[i][k]; }
+      }
     }
-  }
-  if (BLOCK == 32) sum = warp_sum(sum); else sum = block_reduce<false>(sum, scratch);
-  const float inv = 1.f / sum;
+    sum = block_combine<false, BLOCK>(sum, scratch[1]);
+    const float inv = 1.f / sum;
 #pragma unroll
-  for (int i = 0; i < MAXP; ++i) {
-    const int pk = threadIdx.x + BLOCK * i;
-    if (pk < npack) {
+    for (int i = 0; i < MAXP; ++i) {
+      const int pk = threadIdx.x + BLOCK * i;
+      if (pk < npack) {
 #pragma unroll
-      for (int k = 0; k < 8; ++k) v[i][k] *= inv;
-      if (sizeof(TO) == 2) {
-        reinterpret_cast<uint4*>(yr)[pk] = pack8<TO>(v[i]);
-      } else {
-        float4* o = reinterpret_cast<float4*>(yr) + 2 * pk;
-        o[0] = make_float4(v[i][0], v[i][1], v[i][2], v[i][3]);
-        o[1] = make_float4(v[i][4], v[i][5], v[i][6], v[i][7]);
+        for (int k = 0; k < 8; ++k) v[i][k] *= inv;
+        if (sizeof(TO) == 2) {
+          reinterpret_cast<uint4*>(yr)[pk] = pack8<TO>(v[i]);
+        } else {
+          float4* o = reinterpret_cast<float4*>(yr) + 2 * pk;
+          o[0] = make_float4(v[i][0], v[i][1], v[i][2], v[i][3]);
+          o[1] = make_float4(v[i][4], v[i][5], v[i][6], v[i][7]);
+        }
       }
     }
   }
@@ -275,13 +350,18 @@ extern "C" int b200_rmsnorm(const void* x, const void* w, void* y, int64_t rows,
   return B200_OK;
 }
 
+template <typename TI, typename TO, int BLOCK>
+static void launch_softmax_block(const SoftmaxParams& p, int64_t rows, cudaStream_t st) {
+  softmax_row_kernel<TI, TO, BLOCK><<<static_cast<int>(rows), BLOCK, 0, st>>>(p);
+}
+
 template <typename TI, typename TO>
 static void launch_softmax_rows(const SoftmaxParams& p, int64_t rows, cudaStream_t st) {
-  const int grid = static_cast<int>(rows);
-  if (p.cols <= 1024) softmax_row_kernel<TI, TO, 32><<<grid, 32, 0, st>>>(p);
-  else if (p.cols <= 4096) softmax_row_kernel<TI, TO, 128><<<grid, 128, 0, st>>>(p);
-  else if (p.cols <= 8192) softmax_row_kernel<TI, TO, 256><<<grid, 256, 0, st>>>(p);
-  else softmax_row_kernel<TI, TO, 1024><<<grid, 1024, 0, st>>>(p);
+  if (p.cols <= 1024) launch_softmax_block<TI, TO, 32>(p, rows, st);
+  else if (p.cols <= 2048) launch_softmax_block<TI, TO, 64>(p, rows, st);
+  else if (p.cols <= 4096) launch_softmax_block<TI, TO, 128>(p, rows, st);
+  else if (p.cols <= 8192) launch_softmax_block<TI, TO, 256>(p, rows, st);
+  else launch_softmax_block<TI, TO, 1024>(p, rows, st);
 }
 
 extern "C" int b200_softmax(const void* x, const void* mask, void* y, int64_t d0, int64_t d1, int64_t d2, int64_t cols,
@@ -292,7 +372,7 @@ extern "C" int b200_softmax(const void* x, const void* mask, void* y, int64_t d0
   if (rows == 0) return B200_OK;
   B200_CHECK_ARG(rows < (1ll << 31), "b200_softmax: too many rows");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  SoftmaxParams p{x, mask, y, d1, d2, cols, ms0, ms1, ms2, scale, round_steps, mask_dtype};
+  SoftmaxParams p{x, mask, y, d1, d2, cols, ms0, ms1, ms2, scale, round_steps, mask_dtype, (mask && ms1 == 0 && d1 > 1) ? 1 : 0};
   const bool half_in = in_dtype == B200_BF16 || in_dtype == B200_F16;
   bool vec = half_in && cols % 8 == 0 && cols <= 32768 && aligned16(x) && aligned16(y) &&
              (out_dtype == in_dtype || out_dtype == B200_F32);

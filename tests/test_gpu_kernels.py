@@ -256,6 +256,27 @@ def test_masked_softmax(lib, T):
     close(Yf, torch.softmax(x.float() * 0.5, -1), rtol=1e-3, atol=1e-5)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("T", [96, 2048, 8192])
+def test_softmax_scale_and_finite_mask_round_like_the_unfused_ops(lib, T, dtype):
+    """scale, then an additive mask of arbitrary finite values: each step rounds to the
+    input dtype as the separate ATen ops would (the kernel may skip a rounding only where
+    it cannot change the value)."""
+    H, R = 2, 24
+    code = 2 if dtype == torch.bfloat16 else 1
+    x, mask = gen((1, H, R, T), dtype), gen((1, 1, R, T), dtype, 1)
+    mask[..., ::3] = 0
+    mask[..., 1::7] = float("-inf")
+    scale = 128 ** -0.5
+    ref = torch.softmax(((x.float() * scale).to(dtype).float() + mask.float()).to(dtype).float(), -1)
+    X, M = x.cuda(), mask.cuda()
+    Y = torch.empty_like(X)
+    ok(lib, lib.b200_softmax(X.data_ptr(), M.data_ptr(), Y.data_ptr(), 1, H, R, T, 0, 0, T, scale, code, code, code, 1, stream()))
+    close(Y, ref, rtol=1e-2, atol=1e-4)
+    if dtype == torch.bfloat16:      # fp16 outputs can sit at the edge of underflow
+        assert torch.equal(Y.cpu() == 0, ref.to(dtype) == 0)
+
+
 def test_softmax_full_size_properties(lib):
     """[12, 8192, 8192] causal: too large for the CPU oracle in a test, so check what must
     hold: rows sum to 1, masked columns are 0, row 0 is one-hot."""
