@@ -89,6 +89,15 @@ __device__ unsigned long long g_tc5p_kb[2][PTR_CTAS][PTR_TILES][PTR_N];   // [0]
 #define TC5P_KB(which, ti_, kb_)
 #endif
 
+// Ablation switches for tuning (only with -DB200NN_TC5_ABLATE, never in the shipped library):
+// a bit mask from the environment turns parts of the persistent kernel into no-ops so that the
+// cost of each part shows in the kernel's duration.  Results are garbage under ablation.
+#ifdef B200NN_TC5_ABLATE
+#define TC5_ABL(bit) ((p.trace_slot & (bit)) != 0)
+#else
+#define TC5_ABL(bit) false
+#endif
+
 struct Tc5Params {
   const void* bias; const void* residual; const void* aux; void* out;
   int64_t M, N, K, ldo, ldr, ldaux;
@@ -96,6 +105,10 @@ struct Tc5Params {
   const void* x;   // convolution input (implicit-GEMM mode only)
   Tc5Conv g;
   int trace_slot;  // used by the tracing build only
+  // persistent kernel: shared-memory plan chosen by the host (bytes from the aligned base)
+  int pst, pstage;      // ring stages and bytes per stage
+  int wr, w_off;        // weights resident: all k-blocks of the CTA's weight tile stay in shared memory at w_off
+  int pncb, c_off;      // C buffers (bulk-copy epilogue) and where they start
 };
 
 template <typename T> struct AbFormat;
@@ -595,10 +608,12 @@ template <int BN, bool TS> struct PCfg {
   static constexpr int CB = BM * BN * 2;               // one C buffer: BN/64 sub-tiles of [128 rows][128 bytes]
   static constexpr int NCB = TS ? (BN == 256 ? 1 : 2) : 0;
   static constexpr int SMEM = ST * STAGE + NCB * CB + 1024;
+  // Weights resident (short reductions whose whole weight tile fits): the ring holds activation
+  // tiles only, the rest goes to the weight tile and up to MAX_NCB C buffers.
+  static constexpr int MAX_ST = 12, MAX_NCB = 4;
+  static constexpr int SMEM_LIMIT = 227 * 1024 - 1024;   // dynamic part; the barriers are static shared memory
   // warps: 0 activation producer, 1 MMA, 2-5 epilogue; TS adds 6 store, 7-10 second epilogue group
   // (half the columns each); the gather variant adds 6-9 gather; the last warp is the weight producer
-  static constexpr int THREADS = TS ? 384 : 224;
-  static constexpr int THREADS_GATHER = 352;            // CONV without im2col (never TS)
   static constexpr int W_WARP = TS ? 11 : 6;
   static constexpr int W_WARP_GATHER = 10;
   static constexpr int EPI_WARPS = TS ? 8 : 4;
@@ -609,14 +624,19 @@ __global__ void __launch_bounds__(TS ? 384 : (CONV ? 352 : 224), 1)
     gemm_tc5p_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                      const __grid_constant__ CUtensorMap map_r, const __grid_constant__ CUtensorMap map_o, const Tc5Params p,
                      const int tiles_m, const int n_tiles) {
-  constexpr int ST = PCfg<BN, TS>::ST, A_STAGE = PCfg<BN, TS>::A_STAGE, B_STAGE = PCfg<BN, TS>::B_STAGE, STAGE = PCfg<BN, TS>::STAGE;
-  constexpr int CB = PCfg<BN, TS>::CB, NCB = TS ? PCfg<BN, TS>::NCB : 1;
+  constexpr int A_STAGE = PCfg<BN, TS>::A_STAGE, B_STAGE = PCfg<BN, TS>::B_STAGE, CB = PCfg<BN, TS>::CB;
+  constexpr int MAX_ST = PCfg<BN, TS>::MAX_ST, MAX_NCB = PCfg<BN, TS>::MAX_NCB;
+  const int ST = p.pst, STAGE = p.pstage, NCB = p.pncb;
+  const bool WR = p.wr != 0;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  uint8_t* cbuf = smem + ST * STAGE;
-  __shared__ __align__(8) uint64_t full_bar[ST], empty_bar[ST], acc_full[2], acc_empty[2];
+  uint8_t* cbuf = smem + p.c_off;
+  uint8_t* wres = smem + p.w_off;
+  __shared__ __align__(8) uint64_t full_bar[MAX_ST], empty_bar[MAX_ST], acc_full[2], acc_empty[2];
   // C buffers: c_full = residual tile landed, c_ready = epilogue result written, c_free = store has read it
-  __shared__ __align__(8) uint64_t c_full[2], c_ready[2], c_free[2];
+  __shared__ __align__(8) uint64_t c_full[MAX_NCB], c_ready[MAX_NCB], c_free[MAX_NCB];
+  // resident weights: w_full = the weight tile has landed, w_empty = every MMA that reads it has completed
+  __shared__ __align__(8) uint64_t w_full, w_empty;
   __shared__ uint32_t tmem_holder;
   __shared__ int failed;
 
@@ -626,9 +646,11 @@ __global__ void __launch_bounds__(TS ? 384 : (CONV ? 352 : 224), 1)
   if (threadIdx.x == 0) {
     failed = 0;
     // a stage is full when both producers' copies have landed (or the 128 gather threads have arrived)
-    for (int s = 0; s < ST; ++s) { tc5::mbar_init(&full_bar[s], (CONV && !p.g.im2col) ? 129 : 2); tc5::mbar_init(&empty_bar[s], 1); }
+    for (int s = 0; s < ST; ++s) { tc5::mbar_init(&full_bar[s], (CONV && !p.g.im2col) ? 129 : (WR ? 1 : 2)); tc5::mbar_init(&empty_bar[s], 1); }
     for (int b = 0; b < 2; ++b) { tc5::mbar_init(&acc_full[b], 1); tc5::mbar_init(&acc_empty[b], PCfg<BN, TS>::EPI_WARPS); }
-    for (int b = 0; b < 2; ++b) { tc5::mbar_init(&c_full[b], 1); tc5::mbar_init(&c_ready[b], PCfg<BN, TS>::EPI_WARPS); tc5::mbar_init(&c_free[b], 1); }
+    for (int b = 0; b < MAX_NCB; ++b) { tc5::mbar_init(&c_full[b], 1); tc5::mbar_init(&c_ready[b], PCfg<BN, TS>::EPI_WARPS); tc5::mbar_init(&c_free[b], 1); }
+    tc5::mbar_init(&w_full, 1);
+    tc5::mbar_init(&w_empty, 1);
     tc5::fence_barrier_init();
     tc5::prefetch_tensormap(&map_a);
     tc5::prefetch_tensormap(&map_w);
@@ -649,12 +671,6 @@ __global__ void __launch_bounds__(TS ? 384 : (CONV ? 352 : 224), 1)
       for (int tile = blockIdx.x; tile < n_tiles && !dead(); tile += gridDim.x, ++ti) {
         const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
         TC5P_STAMP(ti, 5);   // producer: tile started
-        if (TS && p.residual) {   // residual tile -> C buffer, once the store that last used the buffer has read it
-          const int cb = ti % NCB, u = ti / NCB;
-          if (!tc5::mbar_wait(&c_free[cb], (u & 1) ^ 1)) { failed = 1; atomicExch(&g_tc5_error, 16); break; }
-          tc5::mbar_arrive_expect_tx(&c_full[cb], CB);
-          for (int j = 0; j < BN / 64; ++j) tc5::tma_load_2d(cbuf + cb * CB + j * (BM * 128), &map_r, &c_full[cb], n0 + 64 * j, m0);
-        }
         int cpb = 1, img = 0, base_w = 0, base_h = 0;   // convolution: first output pixel of the tile as a base position
         if (CONV) {
           cpb = p.g.c8 ? 1 : p.g.C / BK;
@@ -680,6 +696,7 @@ __global__ void __launch_bounds__(TS ? 384 : (CONV ? 352 : 224), 1)
           if (!tc5::mbar_wait(&empty_bar[s], ((it / ST) & 1) ^ 1)) { failed = 1; atomicExch(&g_tc5_error, 11); break; }
           TC5P_KB(0, ti, kb);
           if (CONV && !p.g.im2col) continue;   // gather variant: warps 6-9 fill the A tile
+          if (TC5_ABL(16)) { mbar_arrive(&full_bar[s]); continue; }
           tc5::mbar_arrive_expect_tx(&full_bar[s], A_STAGE);
           if (CONV && p.g.c8) {
             // 8-channel input: k-block = 8 filter taps, each a [128 pixels][16 B] box.  Taps past the
@@ -704,30 +721,62 @@ __global__ void __launch_bounds__(TS ? 384 : (CONV ? 352 : 224), 1)
     // ---- weight producer: one TMA-issuing thread sustains ~60 GB/s, so weights get their own ----
     if (lane == 0) {
       if (!(p.epilogue & B200_EPI_W_STATIC)) pdl_wait();
-      int it = 0;
-      for (int tile = blockIdx.x; tile < n_tiles && !dead(); tile += gridDim.x) {
-        const int n0 = (tile / tiles_m) * BN;
-        for (int kb = 0; kb < KB; ++kb, ++it) {
-          const int s = it % ST;
-          if (!tc5::mbar_wait(&empty_bar[s], ((it / ST) & 1) ^ 1)) { failed = 1; atomicExch(&g_tc5_error, 19); break; }
-          tc5::mbar_arrive_expect_tx(&full_bar[s], B_STAGE);
-          if (CONV && p.g.c8) {
-            for (int tt = 0; tt < 8; ++tt) tc5::tma_load_2d(smem + s * STAGE + A_STAGE + tt * (BN * 16), &map_w, &full_bar[s], (kb * 8 + tt) * 8, n0);
+      auto load_w = [&](uint8_t* dst, uint64_t* bar, int kb, int n0) {
+        if (CONV && p.g.c8) {
+          for (int tt = 0; tt < 8; ++tt) tc5::tma_load_2d(dst + tt * (BN * 16), &map_w, bar, (kb * 8 + tt) * 8, n0);
+        } else {
+          tc5::tma_load_2d(dst, &map_w, bar, kb * BK, n0);
+        }
+      };
+      if (WR) {
+        // Resident weights: every CTA would otherwise fetch the same few lines of a small weight
+        // matrix from L2 for every tile, all at the same time (measured: those loads, not the
+        // activations, set the pace of a 3x3 convolution over 64 channels).  The tile is loaded
+        // once and again only when the CTA moves to another column tile.
+        int cur_n0 = -1, loads = 0;
+        for (int tile = blockIdx.x; tile < n_tiles && !dead(); tile += gridDim.x) {
+          const int n0 = (tile / tiles_m) * BN;
+          if (n0 == cur_n0) continue;
+          if (loads > 0 && !tc5::mbar_wait(&w_empty, (loads - 1) & 1)) { failed = 1; atomicExch(&g_tc5_error, 19); break; }
+          if (!TC5_ABL(32)) {
+            tc5::mbar_arrive_expect_tx(&w_full, KB * B_STAGE);
+            for (int kb = 0; kb < KB; ++kb) load_w(wres + kb * B_STAGE, &w_full, kb, n0);
           } else {
-            tc5::tma_load_2d(smem + s * STAGE + A_STAGE, &map_w, &full_bar[s], kb * BK, n0);
+            mbar_arrive(&w_full);
+          }
+          cur_n0 = n0;
+          ++loads;
+        }
+        if (dead() && loads > 0) tc5::mbar_wait(&w_full, (loads - 1) & 1, 1u << 16);
+      } else {
+        int it = 0;
+        for (int tile = blockIdx.x; tile < n_tiles && !dead(); tile += gridDim.x) {
+          const int n0 = (tile / tiles_m) * BN;
+          for (int kb = 0; kb < KB; ++kb, ++it) {
+            const int s = it % ST;
+            if (!tc5::mbar_wait(&empty_bar[s], ((it / ST) & 1) ^ 1)) { failed = 1; atomicExch(&g_tc5_error, 19); break; }
+            if (TC5_ABL(32)) { mbar_arrive(&full_bar[s]); continue; }
+            tc5::mbar_arrive_expect_tx(&full_bar[s], B_STAGE);
+            load_w(smem + s * STAGE + A_STAGE, &full_bar[s], kb, n0);
           }
         }
-      }
-      if (dead()) {
-        for (int i = it > ST ? it - ST : 0; i < it; ++i) tc5::mbar_wait(&full_bar[i % ST], (i / ST) & 1, 1u << 16);
+        if (dead()) {
+          for (int i = it > ST ? it - ST : 0; i < it; ++i) tc5::mbar_wait(&full_bar[i % ST], (i / ST) & 1, 1u << 16);
+        }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc = tc5::umma_idesc(BM, BN, AbFormat<T>::value);
-      int it = 0, ti = 0;
+      int it = 0, ti = 0, cur_n0 = -1, w_loads = 0;
       for (int tile = blockIdx.x; tile < n_tiles && !dead(); tile += gridDim.x, ++ti) {
         const int b = ti & 1;
+        const int n0 = (tile / tiles_m) * BN;
+        if (WR && n0 != cur_n0) {   // the resident weight tile of this column tile
+          if (!tc5::mbar_wait(&w_full, w_loads & 1)) { failed = 1; atomicExch(&g_tc5_error, 20); break; }
+          cur_n0 = n0;
+          ++w_loads;
+        }
         if (!tc5::mbar_wait(&acc_empty[b], ((ti >> 1) & 1) ^ 1)) { failed = 1; atomicExch(&g_tc5_error, 12); break; }
         tc5::tc_fence_after();
         const uint32_t acc = tmem_base + b * BN;
@@ -736,7 +785,7 @@ __global__ void __launch_bounds__(TS ? 384 : (CONV ? 352 : 224), 1)
           if (!tc5::mbar_wait(&full_bar[s], (it / ST) & 1)) { failed = 1; atomicExch(&g_tc5_error, 13); break; }
           TC5P_KB(1, ti, kb);
           tc5::tc_fence_after();
-          const uint32_t a_addr = tc5::smem_addr(smem + s * STAGE), b_addr = a_addr + A_STAGE;
+          const uint32_t a_addr = tc5::smem_addr(smem + s * STAGE), b_addr = WR ? tc5::smem_addr(wres + kb * B_STAGE) : a_addr + A_STAGE;
           if (CONV && p.g.c8) {   // unswizzled operands: one MMA covers two taps (2 x 16 bytes of K)
             const uint32_t ak = p.g.c8_swap ? 128u : BM * 16u, am = p.g.c8_swap ? BM * 16u : 128u;
             const uint32_t bk = p.g.c8_swap ? 128u : BN * 16u, bm = p.g.c8_swap ? BN * 16u : 128u;
@@ -744,7 +793,7 @@ __global__ void __launch_bounds__(TS ? 384 : (CONV ? 352 : 224), 1)
             for (int k = 0; k < BK / 16; ++k)
               tc5::umma_f16(acc, tc5::umma_desc_nosw(a_addr + k * 2 * (BM * 16), ak, am), tc5::umma_desc_nosw(b_addr + k * 2 * (BN * 16), bk, bm), idesc,
                             (kb | k) != 0);
-          } else {
+          } else if (!TC5_ABL(8)) {
             const uint64_t da = tc5::umma_desc_sw128(a_addr), db = tc5::umma_desc_sw128(b_addr);
 #pragma unroll
             for (int k = 0; k < BK / 16; ++k) tc5::umma_f16(acc, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
@@ -753,6 +802,10 @@ __global__ void __launch_bounds__(TS ? 384 : (CONV ? 352 : 224), 1)
         }
         if (dead()) break;
         tc5::umma_commit(&acc_full[b]);
+        if (WR) {   // last tile of this column tile: the weight producer may overwrite the tile once these MMAs are done
+          const int next = tile + static_cast<int>(gridDim.x);
+          if (next < n_tiles && (next / tiles_m) * BN != n0) tc5::umma_commit(&w_empty);
+        }
         TC5P_STAMP(ti, 6);   // MMA: all k-blocks of the tile issued
       }
     }
@@ -823,9 +876,9 @@ __global__ void __launch_bounds__(TS ? 384 : (CONV ? 352 : 224), 1)
         };
         float va[16], vb[16];   // two units in flight: the next tcgen05.ld runs under the current unit's math
         __syncwarp();
-        tc5::tmem_ld_32x16(t_row + c_begin, va);
+        if (!TC5_ABL(1)) tc5::tmem_ld_32x16(t_row + c_begin, va);
 #pragma unroll 1
-        for (int c = c_begin; c < c_end; c += 32) {
+        for (int c = c_begin; c < c_end && !TC5_ABL(1); c += 32) {
           tc5::tmem_ld_wait();
           tc5::tmem_ld_32x16(t_row + c + 16, vb);
           unit(va, c);
@@ -865,9 +918,22 @@ __global__ void __launch_bounds__(TS ? 384 : (CONV ? 352 : 224), 1)
       if (lane == 0) mbar_arrive(&acc_empty[b]);   // this warp has drained its quarter of the accumulator
     }
   } else if (TS) {
-    // ---- C-buffer store (one thread of warp 6) ----
+    // ---- C-buffer store and residual prefetch (one thread of warp 6) ----
+    // The thread that learns first that a buffer is free again (its store has been read out) is
+    // the one that refills it with the residual tile of the tile that will use it next.
     if (warp == 6 && lane == 0) {
       pdl_wait();   // the output buffer may still be read by the kernel before this one
+      const bool has_res = p.residual != nullptr;
+      const int my_tiles = static_cast<int>(blockIdx.x) < n_tiles ? (n_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x) : 0;
+      auto load_residual = [&](int ti) {
+        const int tile = blockIdx.x + ti * gridDim.x, cb = ti % NCB;
+        const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+        tc5::mbar_arrive_expect_tx(&c_full[cb], CB);
+        for (int j = 0; j < BN / 64; ++j) tc5::tma_load_2d(cbuf + cb * CB + j * (BM * 128), &map_r, &c_full[cb], n0 + 64 * j, m0);
+      };
+      int res_issued = 0;
+      if (has_res)
+        for (; res_issued < NCB && res_issued < my_tiles; ++res_issued) load_residual(res_issued);
       int ti = 0;
       for (int tile = blockIdx.x; tile < n_tiles && !dead(); tile += gridDim.x, ++ti) {
         const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
@@ -875,12 +941,15 @@ __global__ void __launch_bounds__(TS ? 384 : (CONV ? 352 : 224), 1)
         if (!tc5::mbar_wait(&c_ready[cb], u & 1)) { failed = 1; atomicExch(&g_tc5_error, 18); break; }
         TC5P_STAMP(ti, 3);   // store thread: buffer complete
         for (int j = 0; j < BN / 64; ++j)
-          if (n0 + 64 * j < p.N) tc5::tma_store_2d(&map_o, cbuf + cb * CB + j * (BM * 128), n0 + 64 * j, m0);
+          if (n0 + 64 * j < p.N && !TC5_ABL(4)) tc5::tma_store_2d(&map_o, cbuf + cb * CB + j * (BM * 128), n0 + 64 * j, m0);
         tc5::tma_store_commit();
         tc5::tma_store_wait_read();
-        mbar_arrive(&c_free[cb]);
+        if (!has_res) mbar_arrive(&c_free[cb]);
+        else if (res_issued < my_tiles) load_residual(res_issued++);   // == ti + NCB
         TC5P_STAMP(ti, 4);   // store thread: buffer read out
       }
+      if (dead())   // wait (bounded) for residual copies still in flight
+        for (int i = res_issued > NCB ? res_issued - NCB : 0; i < res_issued; ++i) tc5::mbar_wait(&c_full[i % NCB], (i / NCB) & 1, 1u << 16);
       tc5::tma_store_wait_all();
     }
   } else if (CONV && !p.g.im2col) {
@@ -1171,13 +1240,23 @@ int launch(const Tc5Args& a, const Tc5Plan& plan, cudaStream_t st, const Tc5Conv
   return B200_OK;
 }
 
+// Resident weight tiles in the persistent kernel (B200NN_TC5_W_RESIDENT=0 turns them off).
+bool weights_resident_enabled() {
+  static int enabled = -1;
+  if (enabled < 0) {
+    const char* e = getenv("B200NN_TC5_W_RESIDENT");
+    enabled = (e && e[0] == '0') ? 0 : 1;
+  }
+  return enabled == 1;
+}
+
 template <typename T, int BN, bool CONV, bool TS>
 int launch_persistent(const Tc5Args& a, cudaStream_t st, const Tc5Conv* g = nullptr) {
-  constexpr int SMEM = PCfg<BN, TS>::SMEM;
-  static_assert(SMEM <= 227 * 1024, "ring + C buffers exceed the shared memory of an SM");
+  using PC = PCfg<BN, TS>;
+  static_assert(PC::SMEM <= PC::SMEM_LIMIT, "ring + C buffers exceed the shared memory of an SM");
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(gemm_tc5p_kernel<T, BN, CONV, TS>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) {
+    if (cudaFuncSetAttribute(gemm_tc5p_kernel<T, BN, CONV, TS>, cudaFuncAttributeMaxDynamicSharedMemorySize, PC::SMEM_LIMIT) != cudaSuccess) {
       cudaGetLastError();
       return B200_ENOTSUP;
     }
@@ -1211,9 +1290,28 @@ int launch_persistent(const Tc5Args& a, cudaStream_t st, const Tc5Conv* g = null
   p.bias_dtype = a.bias_dtype; p.epilogue = a.epilogue; p.splits = 1; p.kb_per_split = static_cast<int>(ceil_div(a.K, BK));
   p.x = a.A;
   p.trace_slot = 0;
+#ifdef B200NN_TC5_ABLATE
+  { const char* e = getenv("B200NN_TC5P_ABLATE"); p.trace_slot = e ? atoi(e) : 0; }
+#endif
   const int64_t tiles_m = ceil_div(a.M, BM), tiles = tiles_m * ceil_div(a.N, BN);
   if (tiles >= (1ll << 31)) return B200_ENOTSUP;
   const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
+  // shared-memory plan
+  p.pst = PC::ST; p.pstage = PC::STAGE; p.wr = 0; p.w_off = 0; p.pncb = TS ? PC::NCB : 1; p.c_off = PC::ST * PC::STAGE;
+  int SMEM = PC::SMEM;
+  const int64_t w_bytes = ceil_div(a.K, BK) * PC::B_STAGE;
+  if (weights_resident_enabled() && (!CONV || p.g.im2col) && w_bytes <= 96 * 1024 && tiles >= 2 * grid) {
+    const int avail = PC::SMEM_LIMIT - 1024 - static_cast<int>(w_bytes);
+    for (int stages = (a.K <= BK ? 4 : 6); stages >= 4; stages -= 2) {
+      const int left = avail - stages * PC::A_STAGE;
+      const int ncb = TS ? (left / PC::CB < PC::MAX_NCB ? left / PC::CB : PC::MAX_NCB) : 0;
+      if (left < 0 || (TS && ncb < PC::NCB)) continue;
+      p.wr = 1; p.pst = stages; p.pstage = PC::A_STAGE; p.w_off = stages * PC::A_STAGE;
+      p.c_off = p.w_off + static_cast<int>(w_bytes); p.pncb = TS ? ncb : 1;
+      SMEM = p.c_off + (TS ? ncb : 0) * PC::CB + 1024;
+      break;
+    }
+  }
   launch_pdl(gemm_tc5p_kernel<T, BN, CONV, TS>, dim3(grid), dim3(TS ? 384 : ((CONV && !p.g.im2col) ? 352 : 224)), SMEM, st, ma, mw, mr, mo, p,
              static_cast<int>(tiles_m), static_cast<int>(tiles));
   B200_CHECK_LAUNCH("gemm_tc5p_kernel");
@@ -1231,8 +1329,9 @@ int persistent_bn(int64_t M, int64_t N, int64_t K, bool glu) {
   const int64_t tm = ceil_div(M, BM);
   if (!enabled || tm < 2) return 0;
   // short reductions are memory-bound: 128-wide tiles leave room for two C buffers (see PCfg)
-  if (K > 512 && ceil_div(N, 256) * tm >= 2 * 148) return 256;
-  if (ceil_div(N, 128) * tm >= 148) return 128;
+  // (a tile wider than N only multiplies and copies padding: 64 output channels take 64-wide tiles)
+  if (K > 512 && N > 128 && ceil_div(N, 256) * tm >= 2 * 148) return 256;
+  if ((N > 64 || glu) && ceil_div(N, 128) * tm >= 148) return 128;
   if (!glu && ceil_div(N, 64) * tm >= 148) return 64;
   return 0;
 }
