@@ -137,8 +137,8 @@ __device__ __forceinline__ void add_bias(const Tc5Params& p, float (&v)[CNT], in
 #pragma unroll
     for (int i = 0; i < CNT; ++i) if (i < cnt) v[i] += __half2float(bp[i]);
   } else {
-#pragma unroll 1
-    for (int i = 0; i < cnt; ++i) v[i] += load_as_f32(p.bias, n + i, p.bias_dtype);
+#pragma unroll
+    for (int i = 0; i < CNT; ++i) if (i < cnt) v[i] += load_as_f32(p.bias, n + i, p.bias_dtype);   // (static indices keep v in registers)
   }
 }
 
@@ -619,6 +619,14 @@ template <int BN, bool TS> struct PCfg {
   static constexpr int EPI_WARPS = TS ? 8 : 4;
 };
 
+// Position in the shared-memory ring (stage index and phase bit), stepped without a division:
+// the persistent kernel's ring depth is a run-time value.
+struct RingPos {
+  int s = 0;
+  uint32_t ph = 0;
+  __device__ __forceinline__ void next(int stages) { if (++s == stages) { s = 0; ph ^= 1u; } }
+};
+
 template <typename T, int BN, bool CONV, bool TS>
 __global__ void __launch_bounds__(TS ? 384 : (CONV ? 352 : 224), 1)
     gemm_tc5p_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
@@ -668,6 +676,7 @@ __global__ void __launch_bounds__(TS ? 384 : (CONV ? 352 : 224), 1)
     if (lane == 0) {
       pdl_wait();
       int it = 0, ti = 0;
+      RingPos rp;
       for (int tile = blockIdx.x; tile < n_tiles && !dead(); tile += gridDim.x, ++ti) {
         const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
         TC5P_STAMP(ti, 5);   // producer: tile started
@@ -691,9 +700,9 @@ __global__ void __launch_bounds__(TS ? 384 : (CONV ? 352 : 224), 1)
           for (int r = 0; r < p.g.KH; ++r)
             for (int cb2 = 0; cb2 < cblocks; ++cb2) tc5::tma_prefetch_im2col_4d(&map_a, cb2 * BK, nw, nh, nimg, p.g.KW / 2, r);
         }
-        for (int kb = 0; kb < KB; ++kb, ++it) {
-          const int s = it % ST;
-          if (!tc5::mbar_wait(&empty_bar[s], ((it / ST) & 1) ^ 1)) { failed = 1; atomicExch(&g_tc5_error, 11); break; }
+        for (int kb = 0; kb < KB; ++kb, ++it, rp.next(ST)) {
+          const int s = rp.s;
+          if (!tc5::mbar_wait(&empty_bar[s], rp.ph ^ 1u)) { failed = 1; atomicExch(&g_tc5_error, 11); break; }
           TC5P_KB(0, ti, kb);
           if (CONV && !p.g.im2col) continue;   // gather variant: warps 6-9 fill the A tile
           if (TC5_ABL(16)) { mbar_arrive(&full_bar[s]); continue; }
@@ -750,11 +759,12 @@ __global__ void __launch_bounds__(TS ? 384 : (CONV ? 352 : 224), 1)
         if (dead() && loads > 0) tc5::mbar_wait(&w_full, (loads - 1) & 1, 1u << 16);
       } else {
         int it = 0;
+        RingPos rp;
         for (int tile = blockIdx.x; tile < n_tiles && !dead(); tile += gridDim.x) {
           const int n0 = (tile / tiles_m) * BN;
-          for (int kb = 0; kb < KB; ++kb, ++it) {
-            const int s = it % ST;
-            if (!tc5::mbar_wait(&empty_bar[s], ((it / ST) & 1) ^ 1)) { failed = 1; atomicExch(&g_tc5_error, 19); break; }
+          for (int kb = 0; kb < KB; ++kb, ++it, rp.next(ST)) {
+            const int s = rp.s;
+            if (!tc5::mbar_wait(&empty_bar[s], rp.ph ^ 1u)) { failed = 1; atomicExch(&g_tc5_error, 19); break; }
             if (TC5_ABL(32)) { mbar_arrive(&full_bar[s]); continue; }
             tc5::mbar_arrive_expect_tx(&full_bar[s], B_STAGE);
             load_w(smem + s * STAGE + A_STAGE, &full_bar[s], kb, n0);
@@ -769,6 +779,7 @@ __global__ void __launch_bounds__(TS ? 384 : (CONV ? 352 : 224), 1)
     if (lane == 0) {
       constexpr uint32_t idesc = tc5::umma_idesc(BM, BN, AbFormat<T>::value);
       int it = 0, ti = 0, cur_n0 = -1, w_loads = 0;
+      RingPos rp;
       for (int tile = blockIdx.x; tile < n_tiles && !dead(); tile += gridDim.x, ++ti) {
         const int b = ti & 1;
         const int n0 = (tile / tiles_m) * BN;
@@ -780,9 +791,9 @@ __global__ void __launch_bounds__(TS ? 384 : (CONV ? 352 : 224), 1)
         if (!tc5::mbar_wait(&acc_empty[b], ((ti >> 1) & 1) ^ 1)) { failed = 1; atomicExch(&g_tc5_error, 12); break; }
         tc5::tc_fence_after();
         const uint32_t acc = tmem_base + b * BN;
-        for (int kb = 0; kb < KB; ++kb, ++it) {
-          const int s = it % ST;
-          if (!tc5::mbar_wait(&full_bar[s], (it / ST) & 1)) { failed = 1; atomicExch(&g_tc5_error, 13); break; }
+        for (int kb = 0; kb < KB; ++kb, ++it, rp.next(ST)) {
+          const int s = rp.s;
+          if (!tc5::mbar_wait(&full_bar[s], rp.ph)) { failed = 1; atomicExch(&g_tc5_error, 13); break; }
           TC5P_KB(1, ti, kb);
           tc5::tc_fence_after();
           const uint32_t a_addr = tc5::smem_addr(smem + s * STAGE), b_addr = WR ? tc5::smem_addr(wres + kb * B_STAGE) : a_addr + A_STAGE;
@@ -844,7 +855,8 @@ __global__ void __launch_bounds__(TS ? 384 : (CONV ? 352 : 224), 1)
         const bool bias_f32_vec = p.bias && p.bias_dtype == B200_F32 && (reinterpret_cast<uintptr_t>(p.bias) & 15u) == 0 && (n0 & 3) == 0;
         auto unit = [&](float (&v)[16], int c) {
           const int64_t n = static_cast<int64_t>(n0) + c;
-          if (bias_f32_vec && n + 16 <= p.N) {
+          if (TC5_ABL(64)) {
+          } else if (bias_f32_vec && n + 16 <= p.N) {
             const float4* bp = reinterpret_cast<const float4*>(static_cast<const float*>(p.bias) + n);
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -860,7 +872,7 @@ __global__ void __launch_bounds__(TS ? 384 : (CONV ? 352 : 224), 1)
           uint32_t o[8];
 #pragma unroll
           for (int i = 0; i < 8; ++i) o[i] = pack2<T>(v[2 * i], v[2 * i + 1]);
-          if (has_res) {
+          if (has_res && !TC5_ABL(128)) {
             uint32_t r[8];
             asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a0));
             asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]) : "r"(a1));
@@ -871,6 +883,7 @@ __global__ void __launch_bounds__(TS ? 384 : (CONV ? 352 : 224), 1)
 #pragma unroll
             for (int i = 0; i < 8; ++i) o[i] = relu2<T>(o[i]);
           }
+          if (TC5_ABL(256)) return;
           asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a0), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
           asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a1), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]) : "memory");
         };
@@ -880,10 +893,10 @@ __global__ void __launch_bounds__(TS ? 384 : (CONV ? 352 : 224), 1)
 #pragma unroll 1
         for (int c = c_begin; c < c_end && !TC5_ABL(1); c += 32) {
           tc5::tmem_ld_wait();
-          tc5::tmem_ld_32x16(t_row + c + 16, vb);
+          if (!TC5_ABL(512)) tc5::tmem_ld_32x16(t_row + c + 16, vb);
           unit(va, c);
           tc5::tmem_ld_wait();
-          if (c + 32 < c_end) tc5::tmem_ld_32x16(t_row + c + 32, va);
+          if (c + 32 < c_end && !TC5_ABL(512)) tc5::tmem_ld_32x16(t_row + c + 32, va);
           unit(vb, c + 16);
         }
         tc5::fence_proxy_async();   // the TMA store reads these generic-proxy writes
@@ -960,6 +973,7 @@ __global__ void __launch_bounds__(TS ? 384 : (CONV ? 352 : 224), 1)
     const uint32_t row_off = row * 128, swz = row & 7;
     pdl_wait();
     int it = 0;          // k-blocks issued
+    RingPos rp;
     int arrived = 0;     // k-blocks signalled
     bool alive = true;
     for (int tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x) {
@@ -970,9 +984,9 @@ __global__ void __launch_bounds__(TS ? 384 : (CONV ? 352 : 224), 1)
       const int64_t img = mm / (static_cast<int64_t>(p.g.Wo) * p.g.Ho);
       const int ih0 = oh * p.g.sh - p.g.ph, iw0 = ow * p.g.sw - p.g.pw;
       const T* xb = static_cast<const T*>(p.x) + img * p.g.H * p.g.W * p.g.C;
-      for (int kb = 0; kb < KB && alive; ++kb, ++it) {
-        const int s = it % ST;
-        if (!tc5::mbar_wait(&empty_bar[s], ((it / ST) & 1) ^ 1) || dead()) { failed = 1; atomicExch(&g_tc5_error, 15); alive = false; break; }
+      for (int kb = 0; kb < KB && alive; ++kb, ++it, rp.next(ST)) {
+        const int s = rp.s;
+        if (!tc5::mbar_wait(&empty_bar[s], rp.ph ^ 1u) || dead()) { failed = 1; atomicExch(&g_tc5_error, 15); alive = false; break; }
         const int tap = kb / cpb, c0 = (kb - tap * cpb) * BK;
         const int r = tap / p.g.KW, sx = tap - r * p.g.KW;
         const int ih = ih0 + r, iw = iw0 + sx;
