@@ -109,6 +109,7 @@ struct Tc5Params {
   int pst, pstage;      // ring stages and bytes per stage
   int wr, w_off;        // weights resident: all k-blocks of the CTA's weight tile stay in shared memory at w_off
   int pncb, c_off;      // C buffers (bulk-copy epilogue) and where they start
+  int a2;               // two activation producer threads take alternate k-blocks
 };
 
 template <typename T> struct AbFormat;
@@ -613,8 +614,11 @@ template <int BN, bool TS> struct PCfg {
   static constexpr int MAX_ST = 12, MAX_NCB = 4;
   static constexpr int SMEM_LIMIT = 227 * 1024 - 1024;   // dynamic part; the barriers are static shared memory
   // warps: 0 activation producer, 1 MMA, 2-5 epilogue; TS adds 6 store, 7-10 second epilogue group
-  // (half the columns each); the gather variant adds 6-9 gather; the last warp is the weight producer
+  // (half the columns each); the gather variant adds 6-9 gather; then the weight producer and,
+  // last, the second activation producer
   static constexpr int W_WARP = TS ? 11 : 6;
+  static constexpr int A2_WARP = TS ? 12 : 7;           // second activation producer
+  static constexpr int THREADS = TS ? 416 : 256;
   static constexpr int W_WARP_GATHER = 10;
   static constexpr int EPI_WARPS = TS ? 8 : 4;
 };
@@ -628,7 +632,7 @@ struct RingPos {
 };
 
 template <typename T, int BN, bool CONV, bool TS>
-__global__ void __launch_bounds__(TS ? 384 : (CONV ? 352 : 224), 1)
+__global__ void __launch_bounds__(TS ? 416 : (CONV ? 352 : 256), 1)
     gemm_tc5p_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                      const __grid_constant__ CUtensorMap map_r, const __grid_constant__ CUtensorMap map_o, const Tc5Params p,
                      const int tiles_m, const int n_tiles) {
@@ -672,14 +676,17 @@ __global__ void __launch_bounds__(TS ? 384 : (CONV ? 352 : 224), 1)
   pdl_trigger();
   auto dead = [&]() { return *reinterpret_cast<volatile int*>(&failed) != 0; };
 
-  if (warp == 0) {
+  if (warp == 0 || (p.a2 && warp == PCfg<BN, TS>::A2_WARP)) {
+    // ---- activation producer(s): with a2 the k-blocks alternate between two issuing threads
+    // (a 3x3 convolution is bound by how fast one thread gets its im2col boxes through) ----
     if (lane == 0) {
       pdl_wait();
+      const int mine = warp == 0 ? 0 : 1;
       int it = 0, ti = 0;
       RingPos rp;
       for (int tile = blockIdx.x; tile < n_tiles && !dead(); tile += gridDim.x, ++ti) {
-        const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
-        TC5P_STAMP(ti, 5);   // producer: tile started
+        const int m0 = (tile % tiles_m) * BM;
+        if (warp == 0) TC5P_STAMP(ti, 5);   // producer: tile started
         int cpb = 1, img = 0, base_w = 0, base_h = 0;   // convolution: first output pixel of the tile as a base position
         if (CONV) {
           cpb = p.g.c8 ? 1 : p.g.C / BK;
@@ -688,7 +695,7 @@ __global__ void __launch_bounds__(TS ? 384 : (CONV ? 352 : 224), 1)
           base_w = (rem - oh * p.g.Wo) * p.g.sw - p.g.pw;
           base_h = oh * p.g.sh - p.g.ph;
         }
-        if (CONV && p.g.im2col && p.g.l2_ahead && tile + static_cast<int>(gridDim.x) < n_tiles) {
+        if (CONV && p.g.im2col && p.g.l2_ahead && warp == 0 && tile + static_cast<int>(gridDim.x) < n_tiles) {
           // The first read of a pixel comes from DRAM (measured 3-4 us to the barrier, 1.4 us for the
           // later taps that find it in L2), and the ring holds only a few k-blocks: ask for the next
           // tile's pixels now.  One box per filter row and channel block covers every tap's pixels
@@ -702,6 +709,7 @@ __global__ void __launch_bounds__(TS ? 384 : (CONV ? 352 : 224), 1)
         }
         for (int kb = 0; kb < KB; ++kb, ++it, rp.next(ST)) {
           const int s = rp.s;
+          if (p.a2 && (it & 1) != mine) continue;
           if (!tc5::mbar_wait(&empty_bar[s], rp.ph ^ 1u)) { failed = 1; atomicExch(&g_tc5_error, 11); break; }
           TC5P_KB(0, ti, kb);
           if (CONV && !p.g.im2col) continue;   // gather variant: warps 6-9 fill the A tile
@@ -1264,6 +1272,17 @@ bool weights_resident_enabled() {
   return enabled == 1;
 }
 
+// Two activation producer threads in the persistent kernel: B200NN_TC5_A2 = 0 never, 1 for
+// convolutions (default), 2 for linear layers too.
+bool two_a_producers(bool conv) {
+  static int mode = -1;
+  if (mode < 0) {
+    const char* e = getenv("B200NN_TC5_A2");
+    mode = e && e[0] ? atoi(e) : 1;
+  }
+  return mode >= 2 || (mode == 1 && conv);
+}
+
 template <typename T, int BN, bool CONV, bool TS>
 int launch_persistent(const Tc5Args& a, cudaStream_t st, const Tc5Conv* g = nullptr) {
   using PC = PCfg<BN, TS>;
@@ -1310,6 +1329,7 @@ int launch_persistent(const Tc5Args& a, cudaStream_t st, const Tc5Conv* g = null
   const int64_t tiles_m = ceil_div(a.M, BM), tiles = tiles_m * ceil_div(a.N, BN);
   if (tiles >= (1ll << 31)) return B200_ENOTSUP;
   const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
+  p.a2 = two_a_producers(CONV) && (!CONV || p.g.im2col) && ceil_div(a.K, BK) >= 2 ? 1 : 0;
   // shared-memory plan
   p.pst = PC::ST; p.pstage = PC::STAGE; p.wr = 0; p.w_off = 0; p.pncb = TS ? PC::NCB : 1; p.c_off = PC::ST * PC::STAGE;
   int SMEM = PC::SMEM;
@@ -1326,7 +1346,7 @@ int launch_persistent(const Tc5Args& a, cudaStream_t st, const Tc5Conv* g = null
       break;
     }
   }
-  launch_pdl(gemm_tc5p_kernel<T, BN, CONV, TS>, dim3(grid), dim3(TS ? 384 : ((CONV && !p.g.im2col) ? 352 : 224)), SMEM, st, ma, mw, mr, mo, p,
+  launch_pdl(gemm_tc5p_kernel<T, BN, CONV, TS>, dim3(grid), dim3((CONV && !p.g.im2col) ? 352 : PC::THREADS), SMEM, st, ma, mw, mr, mo, p,
              static_cast<int>(tiles_m), static_cast<int>(tiles));
   B200_CHECK_LAUNCH("gemm_tc5p_kernel");
   return B200_OK;
