@@ -102,7 +102,11 @@ int b200_ew_chain(const b200_tensor* out, const b200_tensor* ins, int n_in,
  * Replaces transpose_kernel / slice_kernel / expand_kernel / cat_2_kernel
  * (cuda_compiler/cuda_templates.py:164-302), which the reference executor
  * substitutes with CuPy views and implicit copies
- * (cuda_runtime/cuda_executor.py:596-649). */
+ * (cuda_runtime/cuda_executor.py:596-649).
+ * A 16-bit [N, C<=8, H, W] output whose strides are (s0, 1, 8W, 8) is treated as a window
+ * of a channels-last buffer with 8-channel slots: each pixel's 16-byte slot is read,
+ * the C channels replaced and the slot written back, so all 8 channels of every slot
+ * must be addressable (they keep their contents). */
 int b200_strided_copy(const b200_tensor* out, const b200_tensor* in, void* stream);
 
 /* full_kernel (cuda_templates.py:304-313): fill `n` elements with `value`. */

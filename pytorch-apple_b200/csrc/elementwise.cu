@@ -227,6 +227,29 @@ struct CopyParams {
   int64_t total;
 };
 
+// Planar -> interleaved for up to 8 channels of a 16-bit type: in [N, C, H, W] contiguous,
+// out [N, C, H, W] viewed with strides (S0, 1, 8 W, 8) - channels-last with room for 8.  One
+// thread per pixel: C coalesced 2-byte reads (one per plane), then the pixel's 16-byte slot is
+// read, the C channels replaced and written back whole (channels C..7 keep their contents), so
+// DRAM sees full sectors instead of masked 2-byte writes.
+__global__ void __launch_bounds__(256) interleave8_kernel(const uint16_t* __restrict__ in, uint16_t* __restrict__ out, int64_t pixels,
+                                                          int64_t hw, int C, int64_t out_s0) {
+  const int64_t gid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (gid >= pixels) return;
+  const int64_t n = gid / hw, r = gid - n * hw;
+  const uint16_t* src = in + n * C * hw + r;
+  uint4* slot = reinterpret_cast<uint4*>(out + n * out_s0 + r * 8);
+  uint16_t v[8];
+#pragma unroll
+  for (int c = 0; c < 8; ++c) v[c] = c < C ? src[c * hw] : uint16_t(0);
+  uint4 cur = *slot;
+  uint32_t w[4] = {cur.x, cur.y, cur.z, cur.w};
+#pragma unroll
+  for (int c = 0; c < 8; ++c)
+    if (c < C) w[c >> 1] = (c & 1) ? ((w[c >> 1] & 0x0000ffffu) | (static_cast<uint32_t>(v[c]) << 16)) : ((w[c >> 1] & 0xffff0000u) | v[c]);
+  *slot = make_uint4(w[0], w[1], w[2], w[3]);
+}
+
 template <typename U>
 __global__ void __launch_bounds__(256) strided_copy_raw_kernel(const __grid_constant__ CopyParams p) {
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
@@ -341,6 +364,20 @@ extern "C" int b200_strided_copy(const b200_tensor* out, const b200_tensor* in, 
   B200_CHECK_ARG(check_tensor(out) && check_tensor(in) && in->ndim == out->ndim, "b200_strided_copy: bad tensors");
   for (int d = 0; d < out->ndim; ++d)
     B200_CHECK_ARG(in->shape[d] == out->shape[d], "b200_strided_copy: shape differs at dim %d", d);
+  if (out->ndim == 4 && out->dtype == in->dtype && dtype_size(out->dtype) == 2 && out->shape[1] >= 2 && out->shape[1] <= 8) {
+    // planar -> channels-last with 8-channel slots (the input repack of a convolution network)
+    const int64_t N = out->shape[0], C = out->shape[1], H = out->shape[2], W = out->shape[3], hw = H * W;
+    const bool planar = in->stride[3] == 1 && in->stride[2] == W && in->stride[1] == hw && (N == 1 || in->stride[0] == C * hw);
+    const bool slots = out->stride[1] == 1 && out->stride[3] == 8 && out->stride[2] == 8 * W && (N == 1 || out->stride[0] % 8 == 0) &&
+                       aligned16(out->data);
+    if (planar && slots && N * hw > 0) {
+      const int64_t pixels = N * hw;
+      interleave8_kernel<<<static_cast<unsigned>(ceil_div(pixels, 256)), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+          static_cast<const uint16_t*>(in->data), static_cast<uint16_t*>(out->data), pixels, hw, static_cast<int>(C), N == 1 ? 0 : out->stride[0]);
+      B200_CHECK_LAUNCH("interleave8_kernel");
+      return B200_OK;
+    }
+  }
   CopyParams p;
   const b200_tensor* inp[1] = {in};
   p.total = coalesce(out, inp, 1, &p.it);

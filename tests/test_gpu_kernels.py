@@ -428,6 +428,20 @@ def test_strided_copy_transpose_cast_and_pad(lib):
     assert torch.equal(z, y.transpose(0, 1).contiguous())
 
 
+@pytest.mark.parametrize("N,Cn,H,W", [(3, 3, 5, 7), (2, 8, 4, 6), (1, 2, 33, 31)])
+def test_strided_copy_planar_to_eight_channel_slots(lib, N, Cn, H, W):
+    """Same-dtype NCHW -> NHWC8 window (the input repack of a convolution network): the
+    channels of the window are replaced, the other channels of each slot keep their contents."""
+    x = gen((N, Cn, H, W), torch.float16)
+    X = x.cuda()
+    full = torch.full((N, H, W, 8), 7.0, dtype=torch.float16, device="cuda")
+    dst = full.permute(0, 3, 1, 2)[:, :Cn]
+    a, b = bt(dst), bt(X)
+    ok(lib, lib.b200_strided_copy(C.byref(a), C.byref(b), stream()))
+    assert torch.equal(full[..., :Cn].cpu(), x.permute(0, 2, 3, 1))
+    assert bool((full[..., Cn:] == 7.0).all())
+
+
 def test_pooling_and_batchnorm(lib):
     x = gen((2, 64, 112, 112), torch.float16)
     for cl in (True, False):
