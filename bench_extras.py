@@ -106,6 +106,53 @@ def resnet50(device, batch: int, tflops_peak: float) -> dict:
             "tensor_frac": flops / (ms * 1e-3) / 1e12 / tflops_peak, "launches": ex.last_launch_count}
 
 
+# (in channels, input size, out channels, kernel, stride, padding, residual, how many) - the
+# distinct convolutions of ResNet-50 at 224 x 224 (the stem with its input padded to 8 channels)
+RESNET50_CONVS = [
+    (8, 224, 64, 7, 2, 3, 0, 1),
+    (64, 56, 64, 1, 1, 0, 0, 1), (64, 56, 64, 3, 1, 1, 0, 3), (64, 56, 256, 1, 1, 0, 1, 3), (64, 56, 256, 1, 1, 0, 0, 1),
+    (256, 56, 64, 1, 1, 0, 0, 2), (256, 56, 128, 1, 1, 0, 0, 1), (128, 56, 128, 3, 2, 1, 0, 1), (128, 28, 512, 1, 1, 0, 1, 4),
+    (256, 56, 512, 1, 2, 0, 0, 1), (512, 28, 128, 1, 1, 0, 0, 3), (128, 28, 128, 3, 1, 1, 0, 3), (512, 28, 256, 1, 1, 0, 0, 1),
+    (256, 28, 256, 3, 2, 1, 0, 1), (256, 14, 1024, 1, 1, 0, 1, 6), (512, 28, 1024, 1, 2, 0, 0, 1), (1024, 14, 256, 1, 1, 0, 0, 5),
+    (256, 14, 256, 3, 1, 1, 0, 5), (1024, 14, 512, 1, 1, 0, 0, 1), (512, 14, 512, 3, 2, 1, 0, 1), (512, 7, 2048, 1, 1, 0, 1, 3),
+    (1024, 14, 2048, 1, 2, 0, 0, 1), (2048, 7, 512, 1, 1, 0, 0, 2), (512, 7, 512, 3, 1, 1, 0, 2)]
+
+
+def resnet50_layers(device, batch: int, hbm_gbs: float, tflops_peak: float) -> list:
+    """Every distinct convolution of ResNet-50 on its own through ``b200_conv2d_nhwc`` (fp16,
+    NHWC, bias + ReLU, residual where the network has one): microseconds per call (five calls
+    back to back, CUDA events) next to its roofline time = max(flops / tensor peak, bytes / HBM peak)."""
+    from cuda_runtime import native
+
+    lib = native.load()
+    st = torch.cuda.current_stream().cuda_stream
+    rows = []
+    for cin, h, o, k, s, p, res, count in RESNET50_CONVS:
+        ho = (h + 2 * p - k) // s + 1
+        x = torch.randn(batch, h, h, cin, device=device).half()
+        w = (torch.randn(o, k * k * cin, device=device) * 0.05).half()
+        bias = torch.zeros(o, device=device)
+        r = torch.randn(batch, ho, ho, o, device=device).half()
+        y = torch.empty(batch, ho, ho, o, device=device, dtype=torch.half)
+
+        def call():
+            native.check(lib.b200_conv2d_nhwc(x.data_ptr(), w.data_ptr(), bias.data_ptr(), r.data_ptr() if res else None, y.data_ptr(),
+                                              batch, h, h, cin, cin, o, k, k, s, s, p, p, ho, ho, 1, 1, st))
+
+        def five():
+            for _ in range(5):
+                call()
+
+        us = _time_runs(five, 2, 5) / 5 * 1e3
+        flops = 2 * batch * ho * ho * o * k * k * cin
+        nbytes = 2 * (batch * h * h * cin + batch * ho * ho * o * (2 if res else 1) + o * k * k * cin)
+        t_tensor, t_hbm = flops / (tflops_peak * 1e12) * 1e6, nbytes / (hbm_gbs * 1e9) * 1e6
+        rows.append({"conv": f"{cin}->{o} {k}x{k}/{s} @{h}" + (" +res" if res else ""), "count": count, "us": round(us, 1),
+                     "roofline_us": round(max(t_tensor, t_hbm), 1), "bound": "tensor" if t_tensor > t_hbm else "hbm",
+                     "frac": round(max(t_tensor, t_hbm) / us, 2)})
+    return rows
+
+
 def ops(device, hbm_gbs: float, tokens=(128, 2048, 8192)) -> dict:
     """The bandwidth kernels on their own, at Qwen2.5-1.5B widths and ``T`` tokens, bf16:
     RMSNorm [T,1536]; SiLU(gate)*up [T,8960]; masked softmax over [1,12,T,T] scores with a
@@ -196,13 +243,14 @@ if __name__ == "__main__":
     #   python bench_extras.py resnet50 --batch 256
     #   python bench_extras.py qwen_decode --layers 2 --batch 1
     #   python bench_extras.py ops
+    #   python bench_extras.py resnet50_layers --batch 256
     import argparse
     import json
 
     from bench import measured_peaks
 
     ap = argparse.ArgumentParser()
-    ap.add_argument("workload", choices=["qwen_prefill", "qwen_decode", "resnet50", "ops"])
+    ap.add_argument("workload", choices=["qwen_prefill", "qwen_decode", "resnet50", "resnet50_layers", "ops"])
     ap.add_argument("--layers", type=int, default=28)
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--tokens", type=int, default=512)
@@ -212,6 +260,12 @@ if __name__ == "__main__":
     hbm, tf, _ = measured_peaks()
     if a.workload == "ops":
         print(json.dumps(ops(dev, hbm)))
+    elif a.workload == "resnet50_layers":
+        rows = resnet50_layers(dev, a.batch, hbm, tf)
+        for row in rows:
+            print(json.dumps(row))
+        print(json.dumps({"sum_us": round(sum(r["us"] * r["count"] for r in rows)),
+                          "sum_roofline_us": round(sum(r["roofline_us"] * r["count"] for r in rows))}))
     elif a.workload == "resnet50":
         print(json.dumps(resnet50(dev, a.batch, tf)))
     else:
