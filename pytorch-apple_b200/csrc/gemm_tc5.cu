@@ -1022,6 +1022,192 @@ __global__ void __launch_bounds__(TS ? 416 : (CONV ? 352 : 256), 1)
   if (warp == 1) { tc5::tc_fence_after(); tc5::tmem_dealloc(tmem_base, 2 * BN); }
 }
 
+// ---- 7x7 / stride-2 stem convolution on the 8-channel padded input ------------------------------
+// The im2col route moves one 16-byte row per (pixel, tap): 7168 TMA rows per 128-pixel tile.  Here a
+// persistent CTA walks consecutive output rows of an image and keeps the input rows it needs in a
+// shared-memory window (16 row slots): stepping to the next output row loads only sh new input rows
+// (7 KB instead of 114 KB of boxes).  Each input row is stored de-interleaved - odd pixels in one
+// plane, even pixels in the other, 16 bytes per pixel - so that for a fixed filter tap the pixels of
+// consecutive output columns (stride 2 in the input) are consecutive 16-byte entries of one plane:
+// exactly the unswizzled K-major core-matrix layout (8 rows x 16 bytes contiguous), and the MMA reads
+// the A operand straight from the window.  One MMA (K = 16) covers taps (r, 2k) and (r, 2k+1): the
+// second tap sits in the other plane at a constant distance, which is the descriptor's K step.
+// Tile = one output row (Wo <= 128 pixels; accumulator rows beyond Wo are computed and never stored).
+struct StemParams {
+  const void* x; const void* bias; int bias_dtype, relu;
+  int batch, H, W, Ho, Wo, KH, sh, ph, N;
+  int tiles, tiles_per_cta;
+};
+constexpr int STEM_BN = 64, STEM_SLOTS = 16, STEM_ENTRIES = 132, STEM_PLANE = STEM_ENTRIES * 16, STEM_SLOT = 2 * STEM_PLANE;
+constexpr int STEM_W_STAGE = STEM_BN * 128;                  // one filter row: 8 taps x [64 rows][16 B]
+constexpr int STEM_CB = BM * STEM_BN * 2, STEM_NT = 4;       // C buffer; tiles the row loaders may run ahead
+constexpr int STEM_THREADS = 352;                            // warps: 0 weights, 1 MMA, 2-5 epilogue, 6 store, 7-10 row loaders
+
+template <typename T>
+__global__ void __launch_bounds__(STEM_THREADS, 1)
+    conv_stem_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_o, const StemParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint8_t* wres = smem;                                   // KH filter rows of weights, resident
+  uint8_t* cbuf = smem + 8 * STEM_W_STAGE;                // 2 C buffers
+  uint8_t* window = cbuf + 2 * STEM_CB;                   // 16 row slots
+  __shared__ __align__(8) uint64_t w_full, tile_full[STEM_NT], tile_done[STEM_NT], acc_full[2], acc_empty[2], c_ready[2], c_free[2];
+  __shared__ uint32_t tmem_holder;
+  __shared__ int failed;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int first = blockIdx.x * p.tiles_per_cta;
+  const int my_tiles = first >= p.tiles ? 0 : (p.tiles - first < p.tiles_per_cta ? p.tiles - first : p.tiles_per_cta);
+
+  if (threadIdx.x == 0) {
+    failed = 0;
+    tc5::mbar_init(&w_full, 1);
+    for (int s = 0; s < STEM_NT; ++s) { tc5::mbar_init(&tile_full[s], 128); tc5::mbar_init(&tile_done[s], 1); }
+    for (int b = 0; b < 2; ++b) {
+      tc5::mbar_init(&acc_full[b], 1); tc5::mbar_init(&acc_empty[b], 4);
+      tc5::mbar_init(&c_ready[b], 4); tc5::mbar_init(&c_free[b], 1);
+    }
+    tc5::fence_barrier_init();
+    tc5::prefetch_tensormap(&map_w);
+    tc5::prefetch_tensormap(&map_o);
+  }
+  // the window starts as zeros: the margins of every plane (pixels left and right of the image) stay zero
+  for (int i = threadIdx.x; i < STEM_SLOTS * STEM_SLOT / 16; i += STEM_THREADS) reinterpret_cast<uint4*>(window)[i] = make_uint4(0, 0, 0, 0);
+  if (warp == 1) { tc5::tmem_alloc(&tmem_holder, 2 * STEM_BN); tc5::tmem_relinquish(); }
+  tc5::fence_proxy_async();
+  tc5::tc_fence_before();
+  __syncthreads();
+  tc5::tc_fence_after();
+  const uint32_t tmem_base = tmem_holder;
+  pdl_trigger();
+  auto dead = [&]() { return *reinterpret_cast<volatile int*>(&failed) != 0; };
+  auto fail = [&](int code) { failed = 1; atomicExch(&g_tc5_error, code); };
+
+  if (warp == 0) {
+    // ---- weights: filter row r = 8 boxes of [64 channels][16 B]; the 8th tap lies outside the weight matrix (zeros) ----
+    if (lane == 0 && my_tiles > 0) {
+      tc5::mbar_arrive_expect_tx(&w_full, p.KH * STEM_W_STAGE);
+      for (int r = 0; r < p.KH; ++r)
+        for (int tt = 0; tt < 8; ++tt)
+          tc5::tma_load_2d(wres + r * STEM_W_STAGE + tt * (STEM_BN * 16), &map_w, &w_full, tt < 7 ? (r * 7 + tt) * 8 : p.KH * 7 * 8 + 8, 0);
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer ----
+    if (lane == 0 && my_tiles > 0) {
+      constexpr uint32_t idesc = tc5::umma_idesc(BM, STEM_BN, AbFormat<T>::value);
+      if (!tc5::mbar_wait(&w_full, 0)) fail(31);
+      for (int ti = 0; ti < my_tiles && !dead(); ++ti) {
+        const int b = ti & 1, st = ti % STEM_NT;
+        const int tile = first + ti, oh = tile % p.Ho, ih_lo = oh * p.sh - p.ph;
+        if (!tc5::mbar_wait(&acc_empty[b], ((ti >> 1) & 1) ^ 1)) { fail(32); break; }
+        if (!tc5::mbar_wait(&tile_full[st], (ti / STEM_NT) & 1)) { fail(33); break; }
+        tc5::tc_fence_after();
+        const uint32_t acc = tmem_base + b * STEM_BN;
+        for (int r = 0; r < p.KH; ++r) {
+          const uint32_t a_row = tc5::smem_addr(window + ((ih_lo + r + STEM_SLOTS) & (STEM_SLOTS - 1)) * STEM_SLOT);
+          const uint32_t b_row = tc5::smem_addr(wres + r * STEM_W_STAGE);
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            tc5::umma_f16(acc, tc5::umma_desc_nosw(a_row + k * 16, STEM_PLANE + 16, 128),
+                          tc5::umma_desc_nosw(b_row + k * 2 * (STEM_BN * 16), STEM_BN * 16, 128), idesc, (r | k) != 0);
+        }
+        tc5::umma_commit(&acc_full[b]);
+        tc5::umma_commit(&tile_done[st]);
+      }
+    }
+  } else if (warp < 6) {
+    // ---- epilogue warps 2-5: TMEM -> bias (+ReLU) -> packed 16-bit -> swizzled C buffer ----
+    const int q = warp & 3;
+    const int r = q * 32 + lane, swz = r & 7;
+    const bool relu = p.relu != 0;
+    Tc5Params bp{};   // add_bias reads bias, dtype and N from the GEMM parameter block
+    bp.bias = p.bias; bp.bias_dtype = p.bias_dtype; bp.N = p.N;
+    for (int ti = 0; ti < my_tiles; ++ti) {
+      const int b = ti & 1;
+      bool ok = true;
+      if (lane == 0) ok = tc5::mbar_wait(&acc_full[b], (ti >> 1) & 1) && tc5::mbar_wait(&c_free[b], ((ti >> 1) & 1) ^ 1);
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!ok && lane == 0) fail(34);
+      ok = __all_sync(0xffffffffu, ok && !dead());
+      if (!ok) break;
+      tc5::tc_fence_after();
+      const uint32_t t_row = tmem_base + b * STEM_BN + (static_cast<uint32_t>(q * 32) << 16);
+      const uint32_t crow = tc5::smem_addr(cbuf + b * STEM_CB) + r * 128;
+#pragma unroll 1
+      for (int c = 0; c < STEM_BN; c += 16) {
+        float v[16];
+        __syncwarp();
+        tc5::tmem_ld_32x16(t_row + c, v);
+        tc5::tmem_ld_wait();
+        const int cnt = p.N - c < 16 ? (p.N - c < 0 ? 0 : p.N - c) : 16;
+        add_bias<16>(bp, v, c, cnt);
+        uint32_t o[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = pack2<T>(v[2 * i], v[2 * i + 1]);
+        if (relu) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] = relu2<T>(o[i]);
+        }
+        const int k = c >> 3;
+        const uint32_t a0 = crow + ((k ^ swz) << 4), a1 = crow + (((k + 1) ^ swz) << 4);
+        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a0), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
+        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a1), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]) : "memory");
+      }
+      tc5::fence_proxy_async();
+      tc5::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) { mbar_arrive(&c_ready[b]); mbar_arrive(&acc_empty[b]); }
+    }
+  } else if (warp == 6) {
+    // ---- store thread: one bulk tensor store of [Wo pixels][64 channels] per tile ----
+    if (lane == 0) {
+      pdl_wait();   // the output buffer may still be read by the kernel before this one
+      for (int ti = 0; ti < my_tiles && !dead(); ++ti) {
+        const int b = ti & 1;
+        if (!tc5::mbar_wait(&c_ready[b], (ti >> 1) & 1)) { fail(35); break; }
+        tc5::tma_store_2d(&map_o, cbuf + b * STEM_CB, 0, (first + ti) * p.Wo);
+        tc5::tma_store_commit();
+        tc5::tma_store_wait_read();
+        mbar_arrive(&c_free[b]);
+      }
+      tc5::tma_store_wait_all();
+    }
+  } else {
+    // ---- row loaders (warps 7-10): de-interleave the new input rows of each tile into the window ----
+    const int t = threadIdx.x - 7 * 32;   // 0..127
+    pdl_wait();
+    int have_n = -1, have_hi = 0;          // image whose rows the window holds, highest row loaded
+    for (int ti = 0; ti < my_tiles; ++ti) {
+      const int tile = first + ti, n = tile / p.Ho, oh = tile - n * p.Ho;
+      const int ih_lo = oh * p.sh - p.ph, ih_hi = ih_lo + p.KH - 1;
+      const bool fresh = n != have_n;
+      // slots about to be overwritten were last read by tile ti-4 at the latest (16 slots, KH + 4 sh <= 16);
+      // a new image overwrites rows the previous tile may still be reading
+      bool ok = true;
+      if (fresh && ti >= 1) ok = tc5::mbar_wait(&tile_done[(ti - 1) % STEM_NT], ((ti - 1) / STEM_NT) & 1);
+      else if (ti >= STEM_NT) ok = tc5::mbar_wait(&tile_done[ti % STEM_NT], ((ti / STEM_NT) & 1) ^ 1);
+      if (!ok || dead()) { fail(36); break; }
+      const int from = fresh ? ih_lo : (have_hi + 1 > ih_lo ? have_hi + 1 : ih_lo);
+      for (int ih = from; ih <= ih_hi; ++ih) {
+        uint8_t* slot = window + ((ih + STEM_SLOTS) & (STEM_SLOTS - 1)) * STEM_SLOT;
+        const bool in = ih >= 0 && ih < p.H;
+        const T* src = static_cast<const T*>(p.x) + (static_cast<int64_t>(n) * p.H + (in ? ih : 0)) * p.W * 8;
+        for (int px = t; px < p.W; px += 128) {
+          const uint32_t dst = tc5::smem_addr(slot + ((px & 1) ? 0 : STEM_PLANE) + (((px - (px & 1)) >> 1) + 2) * 16);
+          cp_async16_zfill(dst, src + px * 8, in ? 16 : 0);
+        }
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+      tc5::fence_proxy_async();   // generic-proxy writes -> visible to the tensor core's async-proxy reads
+      mbar_arrive(&tile_full[ti % STEM_NT]);
+      have_n = n;
+      have_hi = ih_hi;
+    }
+  }
+  __syncthreads();
+  if (warp == 1) { tc5::tc_fence_after(); tc5::tmem_dealloc(tmem_base, 2 * STEM_BN); }
+}
+
 // ---- host side -----------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -1400,6 +1586,44 @@ template <bool CONV> int dispatch_persistent(int bn, const Tc5Args& a, cudaStrea
   return dispatch_persistent_t<__half, CONV>(bn, ts, a, st, g);
 }
 
+// The stem kernel takes 7-wide filters with stride 2 and padding 3 along W on an 8-channel input whose
+// output rows fit one tile (Wo <= 128); B200NN_CONV_STEM_ROWS=0 sends the stem through the im2col path.
+template <typename T>
+int launch_stem_rows(const Tc5Args& a, const Tc5Conv& g, cudaStream_t st) {
+  static int enabled = -1;
+  if (enabled < 0) {
+    const char* e = getenv("B200NN_CONV_STEM_ROWS");
+    enabled = (e && e[0] == '0') ? 0 : 1;
+  }
+  if (!enabled || g.C != 8 || g.KW != 7 || g.sw != 2 || g.pw != 3 || g.sh != 2 || g.KH < 1 || g.KH > 8 || g.Wo > BM || g.W > 256 ||
+      g.Wo != (g.W + 2 * g.pw - g.KW) / g.sw + 1 || g.batch <= 0 || a.residual || a.N > STEM_BN || a.N % 8 ||
+      a.K != static_cast<int64_t>(g.KH) * g.KW * 8 || a.ldw % 8 || !aligned16(a.A) || !aligned16(a.W) || !tma_store_ok(a))
+    return B200_ENOTSUP;
+  constexpr int SMEM = 8 * STEM_W_STAGE + 2 * STEM_CB + STEM_SLOTS * STEM_SLOT + 1024;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(conv_stem_rows_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) {
+      cudaGetLastError();
+      return B200_ENOTSUP;
+    }
+    configured = true;
+  }
+  CUtensorMap mw, mo;
+  if (!make_map_c8(&mw, a.W, a.N, a.K, a.ldw, STEM_BN, a.dtype) || !make_map(&mo, a.out, a.M, a.N, a.ldo, g.Wo, a.dtype)) return B200_ENOTSUP;
+  const int64_t tiles = static_cast<int64_t>(g.batch) * g.Ho;
+  if (tiles >= (1ll << 31) || a.M != tiles * g.Wo) return B200_ENOTSUP;
+  StemParams p;
+  p.x = a.A; p.bias = a.bias; p.bias_dtype = a.bias_dtype; p.relu = (a.epilogue & B200_EPI_RELU) ? 1 : 0;
+  p.batch = g.batch; p.H = g.H; p.W = g.W; p.Ho = g.Ho; p.Wo = g.Wo; p.KH = g.KH; p.sh = g.sh; p.ph = g.ph; p.N = static_cast<int>(a.N);
+  p.tiles = static_cast<int>(tiles);
+  const int sms = sm_count();
+  p.tiles_per_cta = static_cast<int>(ceil_div(tiles, tiles < sms ? tiles : sms));
+  const int grid = static_cast<int>(ceil_div(tiles, p.tiles_per_cta));
+  launch_pdl(conv_stem_rows_kernel<T>, dim3(grid), dim3(STEM_THREADS), SMEM, st, mw, mo, p);
+  B200_CHECK_LAUNCH("conv_stem_rows_kernel");
+  return B200_OK;
+}
+
 }  // namespace
 
 bool tc5_enabled() {
@@ -1448,6 +1672,10 @@ int conv_tc5(const Tc5Args& a, const Tc5Conv& g, cudaStream_t st) {
   if (!tc5_enabled()) return B200_ENOTSUP;
   if (a.dtype != B200_BF16 && a.dtype != B200_F16) return B200_ENOTSUP;
   if (a.M >= (1ll << 31) || a.N >= (1ll << 31) || (a.epilogue & ~(B200_EPI_RELU | B200_EPI_W_STATIC))) return B200_ENOTSUP;
+  if (g.C == 8 && !(a.epilogue & ~(B200_EPI_RELU | B200_EPI_W_STATIC))) {   // 7x7 stem: rows kept in a shared-memory window
+    const int rc = a.dtype == B200_BF16 ? launch_stem_rows<__nv_bfloat16>(a, g, st) : launch_stem_rows<__half>(a, g, st);
+    if (rc != B200_ENOTSUP) return rc;
+  }
   if (g.C == 8) {   // stem convolution on the padded RGB input: persistent kernel, 64-wide tiles, bulk-copy epilogue
     static int c8_mode = -1;   // B200NN_CONV_C8: 0 off, 1 on, 2 on with the descriptor offsets exchanged
     if (c8_mode < 0) {

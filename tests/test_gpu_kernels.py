@@ -137,6 +137,8 @@ def test_linear_rejects_unaligned(lib):
 # ------------------------------------------------------------------ conv
 @pytest.mark.parametrize("N,C,H,O,k,s,p,res,relu", [
     (2, 8, 56, 64, 7, 2, 3, False, True),     # stem after channel padding 3 -> 8
+    (3, 8, 224, 64, 7, 2, 3, False, True),    # full-size stem: several output rows per CTA, image borders inside a CTA's rows
+    (20, 8, 64, 48, 7, 2, 3, False, False),   # stem with fewer than 64 output channels, no ReLU
     (1, 64, 56, 64, 3, 1, 1, True, True),
     (2, 64, 56, 128, 3, 2, 1, False, True),
     (2, 64, 56, 128, 1, 2, 0, False, False),
