@@ -66,10 +66,17 @@ class ClockSampler:
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, device_index: int):
-        self.idx, self.proc = device_index, None
+    def __init__(self, device_index: int, enabled: bool = True):
+        self.idx, self.proc, self.enabled, self.t_mark, self.t_start = device_index, None, enabled, None, None
+
+    def mark(self):
+        """The timed region starts now: samples taken earlier are dropped."""
+        self.t_mark = time.perf_counter()
 
     def __enter__(self):
+        if not self.enabled:
+            return self
+        self.t_start = time.perf_counter()
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
                                           "-i", str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
@@ -89,7 +96,12 @@ class ClockSampler:
             self.proc.kill()
             text = ""
         sm, mx, reasons = [], [], set()
-        for line in text.splitlines():
+        lines = text.splitlines()
+        if self.t_mark is not None and self.t_start is not None and lines:
+            # samples arrive every 100 ms; keep those of the timed region (the last ones), at least three
+            timed = max(3, int((time.perf_counter() - self.t_mark) / 0.1) + 1)
+            lines = lines[-timed:]
+        for line in lines:
             f = [x.strip() for x in line.split(",")]
             if len(f) < 9:
                 continue
@@ -197,13 +209,19 @@ def run_b200(args, rank: int, world: int, device):
         bufs["input_ids"].native_handle.copy_(tok.native_handle.view(B, 1))
         return out
 
-    for i in range(W):
-        device_step(i)
-    if world > 1:
-        torch.distributed.barrier()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(device.index) as clocks:
+    # Clocks are sampled by rank 0 only, and the sampler is started before the warm-up: nvidia-smi
+    # initialises NVML for every GPU of the box when it starts, which stalls running kernels for a
+    # moment (with one sampler per rank inside the timed region, four ranks lost 9 % of a 32-step run).
+    with ClockSampler(device.index, enabled=rank == 0) as clocks:
+        if rank == 0:
+            time.sleep(1.0)   # let nvidia-smi finish starting up
+        for i in range(W):
+            device_step(i)
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        clocks.mark()
         e0.record()
         for i in range(W, n_total):
             device_step(i)
