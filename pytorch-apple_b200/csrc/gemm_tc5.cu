@@ -1540,7 +1540,7 @@ int launch_persistent(const Tc5Args& a, cudaStream_t st, const Tc5Conv* g = null
 
 // Tile width of the persistent kernel for a shape, or 0 when the shape should stay on the
 // one-tile-per-CTA kernel (too few tiles to fill the SMs with wide tiles).
-int persistent_bn(int64_t M, int64_t N, int64_t K, bool glu) {
+int persistent_bn(int64_t M, int64_t N, int64_t K, bool glu, bool residual) {
   static int enabled = -1;
   if (enabled < 0) {
     const char* e = getenv("B200NN_TC5_PERSISTENT");
@@ -1551,6 +1551,12 @@ int persistent_bn(int64_t M, int64_t N, int64_t K, bool glu) {
   // short reductions are memory-bound: 128-wide tiles leave room for two C buffers (see PCfg)
   // (a tile wider than N only multiplies and copies padding: 64 output channels take 64-wide tiles)
   if (K > 512 && N > 128 && ceil_div(N, 256) * tm >= 2 * 148) return 256;
+  // Short reductions are memory-bound and the column tiles of a row tile run far apart in time, so every
+  // column tile reads its activation tile from DRAM again: a 256-wide tile halves those reads.  It pays
+  // where two C buffers still fit beside the resident weights (K <= 64: 1x1 expansions 64 -> 256 went from
+  // 0.78 to 0.91 of their HBM time) or where no residual tile has to be prefetched into the one buffer.
+  static const int wide_short = env_int("B200NN_TC5_WIDE_SHORT", 1);
+  if (wide_short && N >= 256 && (K <= 64 || (K <= 256 && !residual)) && ceil_div(N, 256) * tm >= 2 * 148) return 256;
   if ((N > 64 || glu) && ceil_div(N, 128) * tm >= 148) return 128;
   if (!glu && ceil_div(N, 64) * tm >= 148) return 64;
   return 0;
@@ -1645,7 +1651,7 @@ int linear_tc5(const Tc5Args& a, cudaStream_t st) {
   if (a.M >= (1ll << 31) || a.N >= (1ll << 31) || a.K >= (1ll << 31)) return B200_ENOTSUP;
   const bool glu = (a.epilogue & B200_EPI_GLU) != 0;
   if (glu && (a.N % 128 || (a.epilogue & ~(B200_EPI_GLU | B200_EPI_W_STATIC)) || a.residual)) return B200_ENOTSUP;
-  if (const int bn = persistent_bn(a.M, a.N, a.K, glu)) return dispatch_persistent<false>(bn, a, st, nullptr);
+  if (const int bn = persistent_bn(a.M, a.N, a.K, glu, a.residual != nullptr)) return dispatch_persistent<false>(bn, a, st, nullptr);
   const Tc5Plan pl = plan_tc5(a.M, a.N, a.K, glu);
   if (pl.tiles_m > 65535 || pl.splits > 65535) return B200_ENOTSUP;
   if (pl.tiles_m == 1 && a.M <= 64 && decode_deep()) {
@@ -1692,7 +1698,7 @@ int conv_tc5(const Tc5Args& a, const Tc5Conv& g, cudaStream_t st) {
     return a.dtype == B200_BF16 ? launch_persistent<__nv_bfloat16, 64, true, true>(a, st, &g8) : launch_persistent<__half, 64, true, true>(a, st, &g8);
   }
   if (g.C % BK || a.K != static_cast<int64_t>(g.KH) * g.KW * g.C || a.ldw % 8 || !aligned16(a.A) || !aligned16(a.W)) return B200_ENOTSUP;
-  if (const int bn = persistent_bn(a.M, a.N, a.K, false)) return dispatch_persistent<true>(bn, a, st, &g);
+  if (const int bn = persistent_bn(a.M, a.N, a.K, false, a.residual != nullptr)) return dispatch_persistent<true>(bn, a, st, &g);
   Tc5Plan pl;
   pl.bn = a.N >= 128 ? 128 : 64;
   pl.tiles_n = ceil_div(a.N, pl.bn);

@@ -148,7 +148,8 @@ def test_linear_rejects_unaligned(lib):
     (32, 64, 56, 128, 3, 2, 1, False, True),   # persistent, stride 2
     (5, 128, 28, 128, 3, 1, 1, False, False),  # odd image count: the last tile runs past the tensor
     (16, 64, 56, 64, 3, 1, 1, False, True),    # several tiles per CTA: the 72 KB weight tile stays resident in shared memory
-    (16, 64, 56, 256, 1, 1, 0, True, True),    # resident weights, two column tiles: the weight tile is replaced mid-kernel
+    (16, 64, 56, 512, 1, 1, 0, True, True),    # resident weights, two 256-wide column tiles: the weight tile is replaced mid-kernel
+    (16, 128, 28, 256, 1, 1, 0, True, True),   # 128-wide tiles, two column tiles, residual
     (52, 256, 28, 64, 1, 1, 0, False, False),  # resident weights with four k-blocks per tile, ragged last tile
 ])
 def test_conv2d_nhwc(lib, N, C, H, O, k, s, p, res, relu):
