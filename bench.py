@@ -66,6 +66,8 @@ class ClockSampler:
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
+    PERIOD_MS = int(os.environ.get("B200NN_BENCH_CLOCK_MS", "100"))
+
     def __init__(self, device_index: int, enabled: bool = True):
         self.idx, self.proc, self.enabled, self.t_mark, self.t_start = device_index, None, enabled, None, None
 
@@ -78,7 +80,7 @@ class ClockSampler:
             return self
         self.t_start = time.perf_counter()
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", str(self.PERIOD_MS),
                                           "-i", str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -99,7 +101,7 @@ class ClockSampler:
         lines = text.splitlines()
         if self.t_mark is not None and self.t_start is not None and lines:
             # samples arrive every 100 ms; keep those of the timed region (the last ones), at least three
-            timed = max(3, int((time.perf_counter() - self.t_mark) / 0.1) + 1)
+            timed = max(3, int((time.perf_counter() - self.t_mark) * 1e3 / self.PERIOD_MS) + 1)
             lines = lines[-timed:]
         for line in lines:
             f = [x.strip() for x in line.split(",")]
