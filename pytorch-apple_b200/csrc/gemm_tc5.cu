@@ -110,6 +110,7 @@ struct Tc5Params {
   int wr, w_off;        // weights resident: all k-blocks of the CTA's weight tile stay in shared memory at w_off
   int pncb, c_off;      // C buffers (bulk-copy epilogue) and where they start
   int a2;               // two activation producer threads take alternate k-blocks
+  int nfast;            // persistent kernel: column tiles fastest in the tile order
 };
 
 template <typename T> struct AbFormat;
@@ -654,6 +655,13 @@ __global__ void __launch_bounds__(TS ? 416 : (CONV ? 352 : 256), 1)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int KB = static_cast<int>((p.K + BK - 1) / BK);
+  // Tile index -> row tile / column tile.  Rows fastest by default (the CTAs running together share
+  // weight tiles); columns fastest (p.nfast) for short reductions over large activations: the column
+  // tiles of one row tile then run together and share the activation tile in L2, and with a grid that
+  // is a multiple of the column-tile count every CTA keeps one column tile - its resident weights - for good.
+  const int tiles_n = static_cast<int>((p.N + BN - 1) / BN);
+  auto tile_m = [&](int tile) { return p.nfast ? tile / tiles_n : tile % tiles_m; };
+  auto tile_n = [&](int tile) { return p.nfast ? tile % tiles_n : tile / tiles_m; };
 
   if (threadIdx.x == 0) {
     failed = 0;
@@ -685,7 +693,7 @@ __global__ void __launch_bounds__(TS ? 416 : (CONV ? 352 : 256), 1)
       int it = 0, ti = 0;
       RingPos rp;
       for (int tile = blockIdx.x; tile < n_tiles && !dead(); tile += gridDim.x, ++ti) {
-        const int m0 = (tile % tiles_m) * BM;
+        const int m0 = tile_m(tile) * BM;
         if (warp == 0) TC5P_STAMP(ti, 5);   // producer: tile started
         int cpb = 1, img = 0, base_w = 0, base_h = 0;   // convolution: first output pixel of the tile as a base position
         if (CONV) {
@@ -700,7 +708,7 @@ __global__ void __launch_bounds__(TS ? 416 : (CONV ? 352 : 256), 1)
           // later taps that find it in L2), and the ring holds only a few k-blocks: ask for the next
           // tile's pixels now.  One box per filter row and channel block covers every tap's pixels
           // up to a column or two at the row ends.
-          const int nt = tile + gridDim.x, nm0 = (nt % tiles_m) * BM;
+          const int nt = tile + gridDim.x, nm0 = tile_m(nt) * BM;
           const int nimg = nm0 / (p.g.Ho * p.g.Wo), nrem = nm0 - nimg * (p.g.Ho * p.g.Wo), noh = nrem / p.g.Wo;
           const int nw = (nrem - noh * p.g.Wo) * p.g.sw - p.g.pw, nh = noh * p.g.sh - p.g.ph;
           const int cblocks = p.g.c8 ? 1 : p.g.C / BK;
@@ -752,7 +760,7 @@ __global__ void __launch_bounds__(TS ? 416 : (CONV ? 352 : 256), 1)
         // once and again only when the CTA moves to another column tile.
         int cur_n0 = -1, loads = 0;
         for (int tile = blockIdx.x; tile < n_tiles && !dead(); tile += gridDim.x) {
-          const int n0 = (tile / tiles_m) * BN;
+          const int n0 = tile_n(tile) * BN;
           if (n0 == cur_n0) continue;
           if (loads > 0 && !tc5::mbar_wait(&w_empty, (loads - 1) & 1)) { failed = 1; atomicExch(&g_tc5_error, 19); break; }
           if (!TC5_ABL(32)) {
@@ -769,7 +777,7 @@ __global__ void __launch_bounds__(TS ? 416 : (CONV ? 352 : 256), 1)
         int it = 0;
         RingPos rp;
         for (int tile = blockIdx.x; tile < n_tiles && !dead(); tile += gridDim.x) {
-          const int n0 = (tile / tiles_m) * BN;
+          const int n0 = tile_n(tile) * BN;
           for (int kb = 0; kb < KB; ++kb, ++it, rp.next(ST)) {
             const int s = rp.s;
             if (!tc5::mbar_wait(&empty_bar[s], rp.ph ^ 1u)) { failed = 1; atomicExch(&g_tc5_error, 19); break; }
@@ -790,7 +798,7 @@ __global__ void __launch_bounds__(TS ? 416 : (CONV ? 352 : 256), 1)
       RingPos rp;
       for (int tile = blockIdx.x; tile < n_tiles && !dead(); tile += gridDim.x, ++ti) {
         const int b = ti & 1;
-        const int n0 = (tile / tiles_m) * BN;
+        const int n0 = tile_n(tile) * BN;
         if (WR && n0 != cur_n0) {   // the resident weight tile of this column tile
           if (!tc5::mbar_wait(&w_full, w_loads & 1)) { failed = 1; atomicExch(&g_tc5_error, 20); break; }
           cur_n0 = n0;
@@ -823,7 +831,7 @@ __global__ void __launch_bounds__(TS ? 416 : (CONV ? 352 : 256), 1)
         tc5::umma_commit(&acc_full[b]);
         if (WR) {   // last tile of this column tile: the weight producer may overwrite the tile once these MMAs are done
           const int next = tile + static_cast<int>(gridDim.x);
-          if (next < n_tiles && (next / tiles_m) * BN != n0) tc5::umma_commit(&w_empty);
+          if (next < n_tiles && tile_n(next) * BN != n0) tc5::umma_commit(&w_empty);
         }
         TC5P_STAMP(ti, 6);   // MMA: all k-blocks of the tile issued
       }
@@ -837,7 +845,7 @@ __global__ void __launch_bounds__(TS ? 416 : (CONV ? 352 : 256), 1)
     int ti = 0;
     for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++ti) {
       const int b = ti & 1;
-      const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+      const int m0 = tile_m(tile) * BM, n0 = tile_n(tile) * BN;
       bool ok = true;
       if (lane == 0) ok = tc5::mbar_wait(&acc_full[b], (ti >> 1) & 1);
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
@@ -948,7 +956,7 @@ __global__ void __launch_bounds__(TS ? 416 : (CONV ? 352 : 256), 1)
       const int my_tiles = static_cast<int>(blockIdx.x) < n_tiles ? (n_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x) : 0;
       auto load_residual = [&](int ti) {
         const int tile = blockIdx.x + ti * gridDim.x, cb = ti % NCB;
-        const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+        const int m0 = tile_m(tile) * BM, n0 = tile_n(tile) * BN;
         tc5::mbar_arrive_expect_tx(&c_full[cb], CB);
         for (int j = 0; j < BN / 64; ++j) tc5::tma_load_2d(cbuf + cb * CB + j * (BM * 128), &map_r, &c_full[cb], n0 + 64 * j, m0);
       };
@@ -957,7 +965,7 @@ __global__ void __launch_bounds__(TS ? 416 : (CONV ? 352 : 256), 1)
         for (; res_issued < NCB && res_issued < my_tiles; ++res_issued) load_residual(res_issued);
       int ti = 0;
       for (int tile = blockIdx.x; tile < n_tiles && !dead(); tile += gridDim.x, ++ti) {
-        const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+        const int m0 = tile_m(tile) * BM, n0 = tile_n(tile) * BN;
         const int cb = ti % NCB, u = ti / NCB;
         if (!tc5::mbar_wait(&c_ready[cb], u & 1)) { failed = 1; atomicExch(&g_tc5_error, 18); break; }
         TC5P_STAMP(ti, 3);   // store thread: buffer complete
@@ -985,7 +993,7 @@ __global__ void __launch_bounds__(TS ? 416 : (CONV ? 352 : 256), 1)
     int arrived = 0;     // k-blocks signalled
     bool alive = true;
     for (int tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x) {
-      const int64_t mrow = static_cast<int64_t>(tile % tiles_m) * BM + row;
+      const int64_t mrow = static_cast<int64_t>(tile_m(tile)) * BM + row;
       const bool row_ok = mrow < p.M;
       const int64_t mm = row_ok ? mrow : 0;
       const int ow = static_cast<int>(mm % p.g.Wo), oh = static_cast<int>((mm / p.g.Wo) % p.g.Ho);
@@ -1458,6 +1466,12 @@ bool weights_resident_enabled() {
   return enabled == 1;
 }
 
+// Column-fastest tile order for reductions up to this length (B200NN_TC5_COLUMN_FASTEST=<K>, 0 turns it off).
+int column_fastest_max_k() {
+  static int v = env_int("B200NN_TC5_COLUMN_FASTEST", 256);
+  return v;
+}
+
 // Two activation producer threads in the persistent kernel: B200NN_TC5_A2 = 0 never, 1 for
 // convolutions (default), 2 for linear layers too.
 bool two_a_producers(bool conv) {
@@ -1514,7 +1528,13 @@ int launch_persistent(const Tc5Args& a, cudaStream_t st, const Tc5Conv* g = null
 #endif
   const int64_t tiles_m = ceil_div(a.M, BM), tiles = tiles_m * ceil_div(a.N, BN);
   if (tiles >= (1ll << 31)) return B200_ENOTSUP;
-  const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
+  int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
+  const int64_t tiles_n = ceil_div(a.N, BN);
+  p.nfast = 0;
+  if (a.K <= column_fastest_max_k() && tiles_n > 1 && tiles_n <= grid / 4 && tiles >= 2 * grid) {
+    p.nfast = 1;
+    grid -= grid % static_cast<int>(tiles_n);   // every CTA stays on one column tile
+  }
   p.a2 = two_a_producers(CONV) && (!CONV || p.g.im2col) && ceil_div(a.K, BK) >= 2 ? 1 : 0;
   // shared-memory plan
   p.pst = PC::ST; p.pstage = PC::STAGE; p.wr = 0; p.w_off = 0; p.pncb = TS ? PC::NCB : 1; p.c_off = PC::ST * PC::STAGE;

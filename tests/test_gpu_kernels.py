@@ -151,6 +151,8 @@ def test_linear_rejects_unaligned(lib):
     (16, 64, 56, 512, 1, 1, 0, True, True),    # resident weights, two 256-wide column tiles: the weight tile is replaced mid-kernel
     (16, 128, 28, 256, 1, 1, 0, True, True),   # 128-wide tiles, two column tiles, residual
     (52, 256, 28, 64, 1, 1, 0, False, False),  # resident weights with four k-blocks per tile, ragged last tile
+    (41, 128, 28, 512, 1, 1, 0, True, True),   # column tiles fastest: each CTA keeps one of four column tiles, ragged last row tile
+    (37, 256, 14, 1024, 1, 1, 0, True, False), # column tiles fastest with eight column tiles (grid trimmed to a multiple of 8)
 ])
 def test_conv2d_nhwc(lib, N, C, H, O, k, s, p, res, relu):
     dtype = torch.float16
