@@ -6,8 +6,8 @@ IR -> compile_subgraph -> CUDAExecutor (CUDA graph replay of hand-written kernel
 arg-max on the device.  Requests are independent, so with N GPUs every rank serves its
 own B sequences with replicated weights and no collective on the data path (weak scaling).
 
-Prints ONE JSON line (see README/DESIGN for the keys).  ``--impl reference`` times the
-reference's CPU path (ATen execution of the same IR) on the host cores instead.
+Prints ONE JSON line.  ``--impl reference`` times the reference's CPU path (ATen execution
+of the same IR, same batch) on the host cores instead.
 """
 
 from __future__ import annotations
@@ -33,8 +33,10 @@ from ir_export import extract_ir  # noqa: E402
 
 METRIC = "qwen2.5-1.5b_decode_tokens_per_s"
 CACHE_LEN, PREFILLED, LAYERS = 4352, 4096, 28
-# dram__bytes_read.sum + dram__bytes_write.sum of one attn_decode_kernel launch at B=64 (ncu capture
-# summarised under profiles/): 1.02 x the algorithmic bytes, i.e. nothing is read twice.
+# dram__bytes_read.sum + dram__bytes_write.sum of one attn_decode_kernel launch at B=64, L=4097, from an
+# ncu capture of that launch: 1.02 x the algorithmic bytes, i.e. nothing is read twice.  DRAM counters
+# cannot be read without the profiler, so the figure is carried as a constant and only reported for
+# the shape it was captured on.
 ATTN_DRAM_BYTES_PER_LAUNCH = 274_500_000
 
 
@@ -48,7 +50,7 @@ def parse():
     ap.add_argument("--layers", type=int, default=LAYERS)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary workloads (prefill, B=1/8 decode, ResNet-50)")
-    ap.add_argument("--cpu-sample-batch", type=int, default=8)
+    ap.add_argument("--cpu-sample-batch", type=int, default=8, help="sequences per step of the in-run cpu_baseline sample (b200 arm, N=1)")
     return ap.parse_args()
 
 
@@ -169,7 +171,7 @@ def build_decode(cfg, B: int, device):
 
 def run_b200(args, rank: int, world: int, device):
     from cuda_runtime import CUDABuffer
-    from oracle.ir_interpreter import torch_to_numpy  # dtype plumbing for host arrays only
+    from cuda_runtime.cuda_backend import torch_to_numpy
 
     cfg = mz.qwen2_config(num_layers=args.layers)
     B, K, W = args.batch, args.steps, args.warmup
@@ -347,17 +349,18 @@ def host_threads() -> int:
 
 
 def run_reference(args):
-    """--impl reference: the reference's CPU execution of the same decode graph."""
+    """--impl reference: the reference's CPU execution of the same decode graph, with the same
+    batch per step and the same warm-up count as the other arm."""
     torch.set_num_threads(host_threads())
     cfg = mz.qwen2_config(num_layers=args.layers)
     sd = mz.qwen2_weights(cfg, seed=0)
-    b = min(args.cpu_sample_batch, args.batch)   # a bounded sample: this many of the step's sequences
-    tps, total = cpu_oracle_decode(cfg, sd, b, args.steps, min(args.warmup, 2))
+    tps, total = cpu_oracle_decode(cfg, sd, args.batch, args.steps, args.warmup)
     threads = torch.get_num_threads()
-    sample = f"{args.steps} decode steps of {b} sequence(s) (of the B={args.batch} workload), {args.layers} layers, cache {CACHE_LEN}/{PREFILLED}"
+    sample = (f"{args.steps} whole decode steps of all B={args.batch} sequences after {args.warmup} warm-up steps, {args.layers} layers, "
+              f"cache {CACHE_LEN}/{PREFILLED}, {total:.1f} s of CPU time")
     return {
         "impl": "reference", "metric": METRIC, "value": tps, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": min(args.warmup, 2), "ms_per_step": total / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "warmup": args.warmup, "ms_per_step": total / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": workload_config(args.layers, args.batch, max(1, args.gpus)),
         "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
@@ -382,12 +385,17 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         torch.distributed.init_process_group("nccl", device_id=device)
     line, cfg, sd = run_b200(args, rank, world, device)
-    if rank == 0:
-        if not args.no_extras:
-            import bench_extras
+    if not args.no_extras:
+        import bench_extras
 
-            line["also"] = bench_extras.run(cfg, sd, device)
-        if not args.no_cpu_baseline:
+        # ResNet-50 fp16, 256 images per GPU, on every rank: aggregate images/s at this N
+        rn = bench_extras.resnet50_replicas(device, 256, world)
+        if rank == 0:
+            line["also"] = {"resnet50_b256": rn}
+            line["also"].update(bench_extras.run(cfg, sd, device))
+    if rank == 0:
+        if not args.no_cpu_baseline and world == 1:
+            # Only at N=1: under torchrun the other ranks would be spinning at the barrier on the same host cores.
             torch.set_num_threads(host_threads())
             sd_cpu = {k: v.cpu() for k, v in sd.items()}
             b = min(args.cpu_sample_batch, args.batch)

@@ -128,6 +128,17 @@ class IRInterpreter:
             t = val if isinstance(val, torch.Tensor) else numpy_to_torch(val)
             for n in names:
                 self.env0[n] = t
+        # Intermediates are dropped after their last reader (a 28-layer decode step at batch 64 would
+        # otherwise hold ~50 GB of repeated K/V); results are unaffected.
+        keep = {o["name"] for o in ir["graph_outputs"]}
+        last: dict[str, int] = {}
+        for i, node in enumerate(self.nodes):
+            for t in node.get("inputs", []):
+                last[t["name"]] = i
+        self._dead_after: dict[int, list[str]] = {}
+        for name, i in last.items():
+            if name not in keep and name not in self.env0:
+                self._dead_after.setdefault(i, []).append(name)
 
     def execute(self, inputs: dict[str, Any] | Sequence[Any], keep_all: bool = False) -> dict[str, torch.Tensor]:
         env = dict(self.env0)
@@ -136,8 +147,11 @@ class IRInterpreter:
         for k, v in inputs.items():
             env[k] = v if isinstance(v, torch.Tensor) else numpy_to_torch(v)
         with torch.no_grad():
-            for node in self.nodes:
+            for i, node in enumerate(self.nodes):
                 self._run_node(node, env)
+                if not keep_all:
+                    for name in self._dead_after.get(i, ()):
+                        env.pop(name, None)
         if keep_all:
             return env
         return {o["name"]: env[o["name"]] for o in self.ir["graph_outputs"]}

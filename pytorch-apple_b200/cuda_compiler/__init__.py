@@ -17,14 +17,23 @@ from cuda_compiler.subgraph_analyzer import analyze
 from npu_compiler.ir_reader import IRGraph, load_ir_from_dict
 
 
-def compile_subgraph(ir_dict: dict, compute_dtype: str = "float16", donate_inputs: bool = True, fuse: bool = True) -> CUDAProgram:
+def compile_subgraph(ir_dict: dict, compute_dtype: str = "float16", donate_inputs: bool = True, fuse: bool = True,
+                     keep_inputs=()) -> CUDAProgram:
     """Compile an IR dict.  ``compute_dtype`` applies to float32 graphs; a graph whose
-    weights or inputs are already float16/bfloat16 computes in that type."""
-    return compile_graph(load_ir_from_dict(ir_dict), compute_dtype=compute_dtype, donate_inputs=donate_inputs, fuse=fuse)
+    weights or inputs are already float16/bfloat16 computes in that type.
+
+    ``donate_inputs``: an ``index_copy`` into a graph input that nothing else in this graph
+    reads is done in place, in the caller's buffer (the KV cache of a decode step), instead of
+    into a fresh copy as the reference does (cuda_templates.py:134-162).  ``keep_inputs`` names
+    graph inputs that must keep their contents all the same - tensors that another partition
+    of the same plan, or the caller, reads after this program ran."""
+    return compile_graph(load_ir_from_dict(ir_dict), compute_dtype=compute_dtype, donate_inputs=donate_inputs, fuse=fuse,
+                         keep_inputs=keep_inputs)
 
 
-def compile_graph(graph: IRGraph, compute_dtype: str = "float16", donate_inputs: bool = True, fuse: bool = True) -> CUDAProgram:
-    an = analyze(graph, compute_dtype, donate=donate_inputs, fuse=fuse)
+def compile_graph(graph: IRGraph, compute_dtype: str = "float16", donate_inputs: bool = True, fuse: bool = True,
+                  keep_inputs=()) -> CUDAProgram:
+    an = analyze(graph, compute_dtype, donate=donate_inputs, fuse=fuse, keep_inputs=keep_inputs)
     input_specs, output_specs, weight_specs = list(graph.graph_inputs), list(graph.graph_outputs), list(graph.weights)
     allocations = plan_buffers(an.steps, input_specs, output_specs, weight_specs, an.compute_dtype, analysis=an)
     sources, seen = [], set()

@@ -78,10 +78,11 @@ class Analysis:
 
 
 class _Lowering:
-    def __init__(self, graph: IRGraph, compute_dtype: str, donate: bool = True, fuse: bool = True):
+    def __init__(self, graph: IRGraph, compute_dtype: str, donate: bool = True, fuse: bool = True, keep_inputs=()):
         self.graph = graph
         self.cd = compute_dtype
         self.donate = donate
+        self.keep_inputs = frozenset(keep_inputs)   # graph inputs somebody outside this graph still reads
         self.fuse = fuse
         self.out = Analysis(compute_dtype=compute_dtype)
         low_precision = any(s.dtype in ("bfloat16", "float16") for s in list(graph.weights) + list(graph.graph_inputs))
@@ -585,7 +586,7 @@ class _Lowering:
             src = self.contiguous(src)
             s3 = V.try_reshape(self.view(src), (outer, n_index, inner))
         idx = self.contiguous(index)
-        in_place = (self.donate and base in self.external and base not in self.weight_names
+        in_place = (self.donate and base in self.external and base not in self.weight_names and base not in self.keep_inputs
                     and len(self.gi.consumers.get(base, [])) == 1)
         if in_place:
             self.out.views[out.name] = TensorView(bv.buffer, bv.offset, tuple(out.shape), V.contiguous_strides(out.shape), bv.dtype)
@@ -631,8 +632,8 @@ class _Lowering:
 
         def donatable(c) -> bool:
             cvw = self.view(c.name)
-            return (self.donate and c.name in self.external and c.name not in self.weight_names and cvw.is_contiguous()
-                    and cvw.dtype == dt and len(self.gi.consumers.get(c.name, [])) == 1)
+            return (self.donate and c.name in self.external and c.name not in self.weight_names and c.name not in self.keep_inputs
+                    and cvw.is_contiguous() and cvw.dtype == dt and len(self.gi.consumers.get(c.name, [])) == 1)
 
         ok = dt in ("float16", "bfloat16") and D % 16 == 0 and table_ok(cv) and table_ok(sv) and donatable(cache_k) and donatable(cache_v)
         ok = ok and all(t.dtype == dt and t.strides[3] == 1 and t.offset % 8 == 0 and all(s % 8 == 0 for s in t.strides[:3]) for t in views)
@@ -879,9 +880,9 @@ class _Lowering:
         self.emit(CUBLASStep("attention", names, out.name, p), names + [out.name])
 
 
-def analyze(graph: IRGraph, compute_dtype: str | None = None, donate: bool = True, fuse: bool = True) -> Analysis:
+def analyze(graph: IRGraph, compute_dtype: str | None = None, donate: bool = True, fuse: bool = True, keep_inputs=()) -> Analysis:
     cd = infer_compute_dtype(graph, compute_dtype)
-    return _Lowering(graph, cd, donate=donate, fuse=fuse).run()
+    return _Lowering(graph, cd, donate=donate, fuse=fuse, keep_inputs=keep_inputs).run()
 
 
 def analyze_subgraph(graph: IRGraph, compute_dtype: str | None = None) -> list:

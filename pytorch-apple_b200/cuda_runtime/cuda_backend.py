@@ -55,6 +55,15 @@ def numpy_to_torch(data: np.ndarray, target: str | None = None):
     return t
 
 
+def torch_to_numpy(t) -> np.ndarray:
+    """Host-side counterpart of ``numpy_to_torch``: a tensor as a numpy array, bfloat16 as an
+    ``ml_dtypes.bfloat16`` view of the same bits (numpy has no native bfloat16)."""
+    t = t.detach().cpu().contiguous()
+    if t.dtype == torch.bfloat16:
+        return t.view(torch.uint16).numpy().view(_np_bf16())
+    return t.numpy()
+
+
 def _target_dtype(data: np.ndarray, spec) -> str | None:
     """Which dtype an upload should have on the device."""
     name = getattr(spec, "dtype", None) if spec is not None else None

@@ -91,6 +91,29 @@ def build_sub_ir_dict(part: Partition, original_ir: dict) -> dict:
 _build_sub_ir_dict = build_sub_ir_dict
 
 
+def tensors_read_elsewhere(part: Partition, plan: PartitionPlan) -> set[str]:
+    """External operands of ``part`` that something outside it also needs: another partition
+    (device or host) reads them, or they are results of the whole graph.  A compiler that
+    updates inputs in place (KV-cache ``index_copy``) must leave these alone."""
+    made = {t["name"] for n in part.nodes for t in n.get("outputs", [])}
+    mine = {t["name"] for n in part.nodes for t in n.get("inputs", [])} - made
+    others: set[str] = {t["name"] for t in plan.original_ir.get("graph_outputs", [])}
+    for step in plan.steps:
+        if isinstance(step, Partition) and step is not part:
+            others |= {t["name"] for n in step.nodes for t in n.get("inputs", [])}
+    return mine & others
+
+
+def _accepts_keyword(fn, name: str) -> bool:
+    import inspect
+
+    try:
+        params = inspect.signature(fn).parameters
+    except (TypeError, ValueError):
+        return False
+    return name in params or any(p.kind is inspect.Parameter.VAR_KEYWORD for p in params.values())
+
+
 def _torch_ir_cpu_factory(nodes: list[dict], weights: dict[str, np.ndarray], mapping: dict[str, str] | None):
     """Default host-partition runner: the third-party ``torch_ir`` ATen executor,
     driven the way the reference's npu_runtime/cpu_fallback.py:136-175 does."""
@@ -134,7 +157,11 @@ class DAGExecutor:
             if not isinstance(step, Partition):
                 continue
             if step.target == "npu":
-                program = self._compile_fn(build_sub_ir_dict(step, ir))
+                shared = tensors_read_elsewhere(step, plan)
+                if shared and _accepts_keyword(self._compile_fn, "keep_inputs"):
+                    program = self._compile_fn(build_sub_ir_dict(step, ir), keep_inputs=shared)
+                else:
+                    program = self._compile_fn(build_sub_ir_dict(step, ir))
                 self.npu_programs[step.partition_id] = program
                 self._npu_executors[step.partition_id] = backend.create_executor(program)
             else:

@@ -173,3 +173,54 @@ def test_cpu_partition_without_interpreter_raises(fake_native):
     dag = DAGExecutor(partition(ir, lambda *a: False), CUDABackend(), compile_subgraph)
     with pytest.raises(RuntimeError, match="torch_ir"):
         dag.execute({"x": np.zeros(2, np.float32)}, weights={})
+
+
+def test_replacing_one_weight_buffer_in_the_same_dict_is_noticed(fake_native):
+    """The executor keeps prepared copies and bound pointers per weight set; swapping one buffer
+    inside the dict it was given (same dict object, same length) must rebuild them."""
+    from cuda_compiler import compile_subgraph
+    from cuda_runtime import CUDABackend
+
+    n = [node("y", "aten.linear.default", [ts("x", [2, 8], "bfloat16"), ts("w", [4, 8], "bfloat16")], [ts("y", [2, 4], "bfloat16")])]
+    ir = graph(n, [ts("x", [2, 8], "bfloat16")], [ts("y", [2, 4], "bfloat16")], [ts("w", [4, 8], "bfloat16")])
+    backend = CUDABackend()
+    ex = backend.create_executor(compile_subgraph(ir))
+    x, w1, w2 = rand((2, 8)), rand((4, 8), seed=1), rand((4, 8), seed=2)
+    weights = {"w": backend.allocate_buffer(torch_to_numpy(w1))}
+    feed = {"x": backend.allocate_buffer(torch_to_numpy(x))}
+    y1 = to_f32(ex.run(feed, weights)["y"])
+    np.testing.assert_allclose(y1, (x.float() @ w1.float().T).numpy(), rtol=2e-2, atol=2e-2)
+    weights["w"] = backend.allocate_buffer(torch_to_numpy(w2))      # same dict, one entry replaced
+    y2 = to_f32(ex.run(feed, weights)["y"])
+    np.testing.assert_allclose(y2, (x.float() @ w2.float().T).numpy(), rtol=2e-2, atol=2e-2)
+    assert np.abs(y2 - y1).max() > 0.1
+
+
+def test_cache_read_by_a_later_partition_is_not_updated_in_place(fake_native):
+    """index_copy into a graph input is normally done in the caller's buffer.  When another partition of
+    the plan reads the same input afterwards it must still see the old contents, as with the reference's
+    out-of-place kernel (cuda_templates.py:134-162)."""
+    from cuda_compiler import compile_subgraph
+    from cuda_runtime import CUDABackend
+    from npu_compiler import partition
+    from npu_runtime import DAGExecutor
+
+    S, D = 8, 16
+    c, src, pos = ts("cache", [1, 1, S, D], "bfloat16"), ts("src", [1, 1, 1, D], "bfloat16"), ts("pos", [1], "int64")
+    n = [node("upd", "aten.index_copy.default", [c, pos, src], [ts("upd", [1, 1, S, D], "bfloat16")], dim=2),
+         node("old", "aten.neg.default", [c], [ts("old", [1, 1, S, D], "bfloat16")]),           # forced to the host: reads the cache after the update
+         node("sum", "aten.add.Tensor", [ts("upd", [1, 1, S, D], "bfloat16"), ts("old", [1, 1, S, D], "bfloat16")], [ts("sum", [1, 1, S, D], "bfloat16")])]
+    ir = graph(n, [c, pos, src], [ts("sum", [1, 1, S, D], "bfloat16"), ts("upd", [1, 1, S, D], "bfloat16")])
+    plan = partition(ir, lambda op, attrs=None: op != "aten.neg.default")
+    dag = DAGExecutor(plan, CUDABackend(), compile_subgraph, cpu_executor_factory=cpu_executor_factory)
+    first = next(iter(dag.npu_programs.values()))
+    assert not first.donated_inputs
+    cache, row = rand((1, 1, S, D)), rand((1, 1, 1, D), seed=1)
+    feed = {"cache": torch_to_numpy(cache), "pos": np.array([3]), "src": torch_to_numpy(row)}
+    out = dag.execute(feed, weights={})
+    ref = oracle(ir, {}, {"cache": cache, "pos": torch.tensor([3]), "src": row})
+    np.testing.assert_allclose(to_f32(out["sum"]), ref["sum"], rtol=0, atol=1e-6)
+    # alone in its plan the same update is done in place
+    solo = graph(n[:1], [c, pos, src], [ts("upd", [1, 1, S, D], "bfloat16")])
+    assert compile_subgraph(solo).donated_inputs == {"upd": "cache"}
+    assert not compile_subgraph(solo, keep_inputs={"cache"}).donated_inputs

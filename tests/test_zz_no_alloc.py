@@ -26,30 +26,58 @@ def _case(B, S, valid, seed):
     return q, k, v, mask, Hq, Hkv, D
 
 
-def test_noalloc_matches_workspace_entry_point_twice(native_lib):
+def _attn_ref(q, k, v, mask, scale):
+    """fp32 statement of the op on the host: softmax(q k^T * scale + mask) v with shared KV heads."""
+    G = q.shape[1] // k.shape[1]
+    kf, vf = k.float().cpu().repeat_interleave(G, 1), v.float().cpu().repeat_interleave(G, 1)
+    s = torch.einsum("bhd,bhsd->bhs", q.float().cpu(), kf) * scale + mask.float().cpu()[:, None, :]
+    return torch.einsum("bhs,bhsd->bhd", torch.softmax(s, -1), vf)
+
+
+def _run_pair(lib, B, S, valid, seed):
+    stream = torch.cuda.current_stream().cuda_stream
+    q, k, v, mask, Hq, Hkv, D = _case(B, S, valid, seed)
+    scale = D ** -0.5
+    need = lib.b200_attn_decode_workspace_bytes(B, Hq, Hkv, S, D)
+    ws = torch.empty(max(need, 16), dtype=torch.uint8, device="cuda")
+    want = torch.empty(B, Hq, D, dtype=torch.bfloat16, device="cuda")
+    got = torch.full_like(want, float("nan"))
+    rc = lib.b200_attn_decode(q.data_ptr(), k.data_ptr(), v.data_ptr(), mask.data_ptr(), want.data_ptr(), B, Hq, Hkv, S, D, Hq * D,
+                              Hkv * S * D, S * D, S, scale, 2, ws.data_ptr(), ws.numel(), stream)
+    assert rc == 0, lib.b200_last_error().decode()
+    rc = lib.b200_attn_decode_noalloc(q.data_ptr(), k.data_ptr(), v.data_ptr(), mask.data_ptr(), got.data_ptr(), B, Hq, Hkv, S, D,
+                                      Hq * D, Hkv * S * D, S * D, S, scale, 2, stream)
+    assert rc == 0, lib.b200_last_error().decode()
+    torch.cuda.synchronize()
+    torch.testing.assert_close(got.float(), want.float(), rtol=2e-2, atol=5e-3)
+    torch.testing.assert_close(got.float().cpu(), _attn_ref(q, k, v, mask, scale), rtol=2e-2, atol=5e-3)
+    return need
+
+
+def test_noalloc_uses_the_builtin_scratch_twice_in_a_row(native_lib):
+    """Shapes whose split-KV partials go through global scratch (caches longer than the in-kernel
+    merge covers, or too short for it): the built-in array is what the kernels read and write.  Two
+    calls in a row with different layouts of the partials - the second finds the first one's data
+    in the array - must both equal the workspace entry point and the fp32 host statement."""
     lib = native_lib
     torch.cuda.set_device(0)
-    stream = torch.cuda.current_stream().cuda_stream
-    for B, S, valid, seed in ((8, 4352, 4100, 0), (3, 1024, 700, 1)):   # two calls in a row, different shapes
-        q, k, v, mask, Hq, Hkv, D = _case(B, S, valid, seed)
-        scale = D ** -0.5
-        ws = torch.empty(lib.b200_attn_decode_workspace_bytes(B, Hq, Hkv, S, D), dtype=torch.uint8, device="cuda")
-        want = torch.empty(B, Hq, D, dtype=torch.bfloat16, device="cuda")
-        got = torch.full_like(want, float("nan"))
-        rc = lib.b200_attn_decode(q.data_ptr(), k.data_ptr(), v.data_ptr(), mask.data_ptr(), want.data_ptr(), B, Hq, Hkv, S, D, Hq * D,
-                                  Hkv * S * D, S * D, S, scale, 2, ws.data_ptr(), ws.numel(), stream)
-        assert rc == 0, lib.b200_last_error().decode()
-        rc = lib.b200_attn_decode_noalloc(q.data_ptr(), k.data_ptr(), v.data_ptr(), mask.data_ptr(), got.data_ptr(), B, Hq, Hkv, S, D,
-                                          Hq * D, Hkv * S * D, S * D, S, scale, 2, stream)
-        assert rc == 0, lib.b200_last_error().decode()
-        torch.cuda.synchronize()
-        torch.testing.assert_close(got.float(), want.float(), rtol=2e-2, atol=5e-3)
+    for B, S, valid, seed in ((8, 6144, 6000, 0), (3, 8192, 5000, 1), (3, 80, 37, 2)):
+        need = _run_pair(lib, B, S, valid, seed)
+        assert 0 < need <= 8 << 20, f"B={B} S={S} no longer plans to the scratch path (needs {need} bytes)"
+
+
+def test_noalloc_shapes_that_need_no_scratch(native_lib):
+    """Caches of 512..5120 rows merge their splits inside the kernel; the entry point must serve them too."""
+    lib = native_lib
+    torch.cuda.set_device(0)
+    for B, S, valid, seed in ((8, 4352, 4100, 0), (3, 1024, 700, 1)):
+        _run_pair(lib, B, S, valid, seed)
 
 
 def test_noalloc_rejects_shapes_beyond_the_builtin_scratch(native_lib):
     lib = native_lib
     # A cache longer than eight in-kernel splits can cover falls back to the two-kernel split-KV path,
-    # whose partials (~38 MB here) do not fit the 8 MiB array.
+    # whose partials (~20 MB here) do not fit the 8 MiB array.
     B, S = 200, 8192
     dummy = torch.zeros(16, dtype=torch.bfloat16, device="cuda")
     rc = lib.b200_attn_decode_noalloc(dummy.data_ptr(), dummy.data_ptr(), dummy.data_ptr(), None, dummy.data_ptr(), B, 12, 2, S, 128,
