@@ -251,6 +251,26 @@ int b200_linear(const void* A, const void* W, const void* bias, const void* resi
                 void* workspace, int64_t workspace_bytes, void* stream);
 int64_t b200_linear_workspace_bytes(int64_t M, int64_t N, int64_t K);
 
+/* Decode-shape (M <= 64) linear layer with the neighbouring RMSNorm folded in, replacing a
+ * `rmsnorm_kernel` launch (cuda_templates.py:458-506, matcher subgraph_analyzer.py:667-756)
+ * plus the CUBLASStep("gemm") that consumes it (cuda_executor.py:182-208).
+ *   sumsq_in != NULL: A holds the UN-normalised rows x and W holds the weights with the
+ *     RMSNorm gain folded into their columns (W'[n,k] = W[n,k] * gain[k], prepared once by
+ *     the caller).  Since (r x) W^T = r (x W^T), the kernel multiplies output row m by
+ *     r_m = 1 / sqrt(s_m / K + norm_eps) before the bias, where s_m is the sum of
+ *     sumsq_in[m * sumsq_in_cols + 0 .. sumsq_in_cols) (fp32, added in index order; at most
+ *     32 partials).  The normalised activations are never rounded to the 16-bit type, so
+ *     results differ from b200_rmsnorm + b200_linear by rounding only.
+ *   sumsq_out != NULL: besides `out` the kernel writes sumsq_out[m * (N / 64) + j] = sum of
+ *     squares of the rounded outputs out[m, 64 j .. 64 j + 63] - the partials the next
+ *     normalising layer consumes.  Needs N % 64 == 0.
+ * Everything else as b200_linear (bias, residual, B200_EPI_RELU / _GLU / _W_STATIC); no
+ * aux operand, no workspace.  B200_ENOTSUP when the operands do not fit the fused kernel. */
+int b200_linear_norm(const void* A, const void* W, const void* bias, const void* residual, void* out,
+                     int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldw, int64_t ldo, int64_t ldr,
+                     int dtype, int bias_dtype, int epilogue, float norm_eps,
+                     const float* sumsq_in, int sumsq_in_cols, float* sumsq_out, void* stream);
+
 /* CUBLASStep("gemm_batched") and plain 2-D matmul (subgraph_analyzer.py:206-224,
  * dispatch cuda_executor.py:210-218): out[b1,b2,M,N] = A[b1,b2,M,K] @ B[b1,b2,K,N] with
  * independent element strides for every axis of every operand (0 = broadcast), so

@@ -53,7 +53,7 @@ __device__ unsigned long long g_attn_trace[ATR_CTAS][ATR_N];
 #endif
 
 constexpr int DEC_STAGE_BYTES = 2 * 16 * HD * 2;  // 16 keys of K and of V
-constexpr int DEC_MAX_SPLIT = 640;             // keys per split (mask values of a split are staged in shared memory)
+constexpr int DEC_MAX_SPLIT = 2048;            // keys per split (mask values of a split are staged in shared memory)
 constexpr int DEC_ACC_PITCH = HD + 4;          // row pitch of the cross-warp accumulator (spreads the heads over banks)
 
 // The decode kernel works on the transposed problem, so that the (at most 8) query heads of a
@@ -84,14 +84,15 @@ constexpr int DEC_ACC_PITCH = HD + 4;          // row pitch of the cross-warp ac
 // CM = true ("cluster merge"): the splits of one (sequence, KV head) form a thread-block cluster
 // along x.  Instead of writing its partial result to global memory for a second kernel, every
 // CTA stores head h's partial (accumulator, max, sum) into the receive buffer of cluster rank h
-// (distributed shared memory); after one cluster barrier ranks 0..G-1 combine the splits of
-// their head and write the final output.  Needs G <= splits <= 8.
+// (distributed shared memory); after one cluster barrier every rank combines the splits of the
+// heads it owns (head h belongs to rank h % splits) and writes the final output.  2 <= splits <= 8.
 template <typename T, int STAGES, bool CM>
 __global__ void __launch_bounds__(128, STAGES == 2 ? 3 : 2) attn_decode_kernel(const __grid_constant__ DecodeParams p) {
   extern __shared__ __align__(1024) uint8_t dsm[];
   __shared__ float s_m[4][8], s_l[4][8];
-  __shared__ __align__(16) float recv_acc[CM ? 8 : 1][HD];   // [source rank][dim] partials of the head this CTA owns
-  __shared__ float recv_ml[CM ? 8 : 1][2];
+  // partials of the heads this CTA owns (head h belongs to cluster rank h % splits), by [owned head * splits + source rank]
+  __shared__ __align__(16) float recv_acc[CM ? 16 : 1][HD];
+  __shared__ float recv_ml[CM ? 16 : 1][2];
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
   const int split = blockIdx.x, hk = blockIdx.y;
@@ -176,6 +177,7 @@ __global__ void __launch_bounds__(128, STAGES == 2 ? 3 : 2) attn_decode_kernel(c
   uint32_t vbits = 0;
 #pragma unroll
   for (int i = 0; i < DEC_MAX_SPLIT / 128; ++i) {
+    if (i * 128 >= n_keys) break;   // (uniform) every pass covers 128 keys of the split
     const int idx = i * 32 + lane, blk = warp + 4 * (idx >> 4), key = blk * 16 + (idx & 15);
     float mv = -INFINITY;
     if (key < n_keys) mv = mask_row ? load_as_f32(mask_row, mask_base + key, p.mask_dtype) : 0.f;
@@ -324,11 +326,12 @@ __global__ void __launch_bounds__(128, STAGES == 2 ? 3 : 2) attn_decode_kernel(c
       acc += reinterpret_cast<const float*>(dsm + wi * (STAGES * DEC_STAGE_BYTES))[h * DEC_ACC_PITCH + d] * f;
       lr += s_l[wi][h] * f;
     }
-    if (CM) {   // partial of head h -> slot `split` of the receive buffer of cluster rank h
-      const uint32_t dst = tc5::map_to_rank(smem_u32(&recv_acc[split][d]), h);
+    if (CM) {   // partial of head h -> the receive buffer of the cluster rank that owns the head
+      const int owner = h % p.splits, slot = (h / p.splits) * p.splits + split;
+      const uint32_t dst = tc5::map_to_rank(smem_u32(&recv_acc[slot][d]), owner);
       asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(dst), "f"(acc) : "memory");
       if (d == 0) {
-        const uint32_t dml = tc5::map_to_rank(smem_u32(&recv_ml[split][0]), h);
+        const uint32_t dml = tc5::map_to_rank(smem_u32(&recv_ml[slot][0]), owner);
         asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};" ::"r"(dml), "f"(ma), "f"(lr) : "memory");
       }
     } else {
@@ -341,17 +344,18 @@ __global__ void __launch_bounds__(128, STAGES == 2 ? 3 : 2) attn_decode_kernel(c
   }
   if (CM) {
     tc5::cluster_sync();   // all partials have landed; nobody touches a peer's memory afterwards
-    if (split < p.G) {     // this CTA owns head `split` of the group
+    for (int h = split; h < p.G; h += p.splits) {   // the heads this CTA owns
+      const int base = (h / p.splits) * p.splits;
       float m_all = -INFINITY;
-      for (int r = 0; r < p.splits; ++r) m_all = fmaxf(m_all, recv_ml[r][0]);
+      for (int r = 0; r < p.splits; ++r) m_all = fmaxf(m_all, recv_ml[base + r][0]);
       const float m_use = m_all == -INFINITY ? 0.f : m_all;
       float acc = 0.f, l = 0.f;
       for (int r = 0; r < p.splits; ++r) {
-        const float f = ex2_approx(recv_ml[r][0] - m_use);
-        l += recv_ml[r][1] * f;
-        acc += recv_acc[r][d] * f;
+        const float f = ex2_approx(recv_ml[base + r][0] - m_use);
+        l += recv_ml[base + r][1] * f;
+        acc += recv_acc[base + r][d] * f;
       }
-      static_cast<T*>(p.out)[((b * p.Hq) + static_cast<int64_t>(hk) * p.G + split) * HD + d] = from_f32<T>(l > 0.f ? acc / l : 0.f);
+      static_cast<T*>(p.out)[((b * p.Hq) + static_cast<int64_t>(hk) * p.G + h) * HD + d] = from_f32<T>(l > 0.f ? acc / l : 0.f);
     }
   }
   ATTN_STAMP(4);
@@ -629,16 +633,25 @@ static DecodePlan plan_decode(int64_t B, int Hkv, int64_t S, int G = 8) {
   const int64_t want = 2 * 148;  // fixed so that the workspace size does not depend on the device
   // Plenty of sequences: eight splits per (sequence, KV head), merged inside the kernel by a cluster.
   if (cluster_merge_mode() && (B * Hkv * 8 >= 4 * 148 || cluster_merge_mode() == 2) && S >= 8 * 64 && S <= 8 * DEC_MAX_SPLIT && G <= 8) {
-    // As many splits as a portable cluster allows (8), fewer only when the cache is short.  (Choosing
-    // 7 splits so that 128 pairs fill two waves of 3 x 148 CTAs exactly measured 7 % slower.)
+    // Among the split counts min(G, 6)..8 take the one with the shortest estimated time: waves of
+    // CTAs (three CTAs per SM are resident at a time) x keys per split.  Measured at B=64, S=4352:
+    // 8 splits (2.3 waves of 544 keys) 55.2 us, 7 splits 59.1, 6 splits (1.7 waves of 736 keys) 52.2;
+    // at B=32: 8 splits 34.2 us, 6 splits 28.6.  Fewer, longer splits lose again even when they fit
+    // one wave (3 splits of 1456 keys: 54.7 us; 4 splits: 64.0): SMs left with two CTAs stream slower.
     DecodePlan c;
     c.cluster = false;
-    for (int n = 8; n >= (G < 2 ? 2 : G) && !c.cluster; --n) {
+    int64_t best = 0;
+    for (int n = 8; n >= (G < 6 ? (G < 2 ? 2 : G) : 6); --n) {
       const int len = static_cast<int>(ceil_div(ceil_div(S, n), 16) * 16);
       if (len > DEC_MAX_SPLIT || ceil_div(S, len) != n) continue;
-      c.split_len = len;
-      c.splits = n;
-      c.cluster = true;
+      const int64_t waves = ceil_div(B * Hkv * n, 3 * 148);
+      const int64_t cost = waves * (len + 96);   // + 96 keys' worth of start-up and merge per wave
+      if (!c.cluster || cost < best) {
+        best = cost;
+        c.split_len = len;
+        c.splits = n;
+        c.cluster = true;
+      }
     }
     if (c.cluster) return c;
   }

@@ -510,6 +510,27 @@ extern "C" int64_t b200_linear_workspace_bytes(int64_t M, int64_t N, int64_t K) 
   return a > b ? a : b;
 }
 
+extern "C" int b200_linear_norm(const void* A, const void* W, const void* bias, const void* residual, void* out, int64_t M,
+                                int64_t N, int64_t K, int64_t lda, int64_t ldw, int64_t ldo, int64_t ldr, int dtype,
+                                int bias_dtype, int epilogue, float norm_eps, const float* sumsq_in, int sumsq_in_cols,
+                                float* sumsq_out, void* stream) {
+  B200_CHECK_ARG(A && W && out && M >= 0 && N > 0 && K > 0, "b200_linear_norm: bad arguments");
+  B200_CHECK_ARG(!(epilogue & B200_EPI_SILU_MUL), "b200_linear_norm: the silu_mul epilogue is not available here");
+  B200_CHECK_ARG(!(epilogue & B200_EPI_GLU) || (N % 128 == 0 && !residual && !sumsq_out), "b200_linear_norm: the gated epilogue needs N %% 128 == 0 and excludes residual / sumsq_out");
+  B200_CHECK_ARG(!sumsq_in || sumsq_in_cols > 0, "b200_linear_norm: sumsq_in needs its column count");
+  if (M == 0) return B200_OK;
+  if (M > 64) B200_FAIL(B200_ENOTSUP, "b200_linear_norm: M = %lld; the fused forms exist for decode shapes (M <= 64) only", (long long)M);
+  if (!(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0 && aligned16(A) && aligned16(W)))
+    B200_FAIL(B200_EALIGN, "b200_linear_norm: K, lda, ldw must be multiples of 8 and A, W 16-byte aligned");
+  Tc5Args t{A, W, bias, residual, nullptr, out, M, N, K, lda, ldw, ldo, ldr, 0, dtype, bias_dtype, epilogue, nullptr, 0};
+  t.norm_eps = norm_eps; t.sumsq_in = sumsq_in; t.sumsq_in_cols = sumsq_in_cols; t.sumsq_out = sumsq_out;
+  const int rc = linear_tc5(t, static_cast<cudaStream_t>(stream));
+  if (rc == B200_ENOTSUP)
+    B200_FAIL(B200_ENOTSUP, "b200_linear_norm: operands outside the fused kernel's rules (sumsq_in: at most 32 partials per row; "
+                            "sumsq_out: N %% 64 == 0, 8-byte aligned rows of out / residual, bias in fp32 or the activation type)");
+  return rc;
+}
+
 extern "C" int b200_linear(const void* A, const void* W, const void* bias, const void* residual, void* out, int64_t M,
                            int64_t N, int64_t K, int64_t lda, int64_t ldw, int64_t ldo, int64_t ldr, int dtype,
                            int bias_dtype, int epilogue, const void* aux, int64_t ldaux, void* workspace,

@@ -23,6 +23,7 @@ __device__ int g_tc5_error = 0;
 namespace {
 
 constexpr int BM = 128, BK = 64;
+constexpr int NORM_MAX_PARTS = 32;   // row scaling: at most this many sum-of-squares partials per row
 // Kernel modes.
 //   0  compute-bound shapes (several row tiles): two CTAs per SM with a short ring, so that
 //      one CTA's epilogue overlaps the other's main loop;
@@ -111,6 +112,11 @@ struct Tc5Params {
   int pncb, c_off;      // C buffers (bulk-copy epilogue) and where they start
   int a2;               // two activation producer threads take alternate k-blocks
   int nfast;            // persistent kernel: column tiles fastest in the tile order
+  // one-tile kernel, M <= 64: scale the output rows by the RMSNorm factor of the input rows / write
+  // sum-of-squares partials of the output rows
+  const float* sumsq_in; float* sumsq_out;
+  float norm_eps;
+  int sumsq_in_cols;
 };
 
 template <typename T> struct AbFormat;
@@ -293,6 +299,12 @@ __global__ void __launch_bounds__(224, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(cons
   __shared__ __align__(8) uint64_t full_bar[ST], empty_bar[ST], acc_bar;
   __shared__ uint32_t tmem_holder;
   __shared__ int failed;
+  // Row scaling (decode shapes): the RMSNorm in front of this layer is applied after the GEMM - the
+  // caller has folded the gain into W's columns and each output row m is multiplied by
+  // r_m = 1 / sqrt(sum(x_m^2) / K + eps) before the bias, since (r x) W^T = r (x W^T).
+  constexpr bool CAN_NORM = !CONV && MODE >= 2;
+  __shared__ float s_rinv[CAN_NORM ? 64 : 1];
+  const bool norm = CAN_NORM && p.sumsq_in != nullptr;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
@@ -448,6 +460,25 @@ __global__ void __launch_bounds__(224, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(cons
       }
       asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
+    if (CAN_NORM && norm) {
+      // r of the rows of this tile, from the sum-of-squares partials the producer of x left behind: all
+      // partials of a row are requested at once, then added in index order.  Needed in the final pass only.
+      const int row = static_cast<int>(threadIdx.x) - 64;
+      if (row < 64) {
+        float rinv = 0.f;
+        if (row < rows_valid) {
+          const float* sp = p.sumsq_in + static_cast<int64_t>(m0 + row) * p.sumsq_in_cols;
+          float part[NORM_MAX_PARTS];
+#pragma unroll
+          for (int j = 0; j < NORM_MAX_PARTS; ++j) part[j] = j < p.sumsq_in_cols ? __ldcg(sp + j) : 0.f;
+          float ss = 0.f;
+#pragma unroll
+          for (int j = 0; j < NORM_MAX_PARTS; ++j) ss += part[j];
+          rinv = 1.0f / sqrtf(ss / static_cast<float>(p.K) + p.norm_eps);
+        }
+        s_rinv[row] = rinv;
+      }
+    }
     bool ok = true;
     if (lane == 0) ok = tc5::mbar_wait(&acc_bar, 0);
     ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
@@ -554,6 +585,11 @@ __global__ void __launch_bounds__(224, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(cons
         }
         const int64_t mm = static_cast<int64_t>(m0) + rank * rpo + lr;
         const int64_t n = static_cast<int64_t>(n0) + col;
+        if (CAN_NORM && norm) {
+          const float rs = s_rinv[rank * rpo + lr];
+          acc.x *= rs; acc.y *= rs; acc.z *= rs; acc.w *= rs;
+          up.x *= rs; up.y *= rs; up.z *= rs; up.w *= rs;
+        }
         if (glu) {
           finish_glu4<T>(p, acc, up, mm, n, n0 / 2 + col);
         } else if (vec_ok && n + 4 <= p.N) {
@@ -573,6 +609,17 @@ __global__ void __launch_bounds__(224, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(cons
           }
           if (relu) { acc.x = fmaxf(acc.x, 0.f); acc.y = fmaxf(acc.y, 0.f); acc.z = fmaxf(acc.z, 0.f); acc.w = fmaxf(acc.w, 0.f); }
           *reinterpret_cast<uint2*>(outp + mm * p.ldo + n) = make_uint2(pack2<T>(acc.x, acc.y), pack2<T>(acc.z, acc.w));
+          if (p.sumsq_out) {
+            // Sum of squares of the rounded outputs over this row's block of 64 columns: the 16 lanes
+            // of a half warp hold exactly that block (4 columns each; N % 64 == 0 by contract).
+            round2<T>(acc.x, acc.y);
+            round2<T>(acc.z, acc.w);
+            float sq = acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
+            const unsigned am = __activemask();
+#pragma unroll
+            for (int off = 8; off >= 1; off >>= 1) sq += __shfl_xor_sync(am, sq, off);
+            if ((lane & 15) == 0) p.sumsq_out[mm * (p.N >> 6) + (n >> 6)] = sq;
+          }
         } else if (n < p.N) {
           finish4<T>(p, acc, mm, n);
         }
@@ -1425,6 +1472,8 @@ int launch(const Tc5Args& a, const Tc5Plan& plan, cudaStream_t st, const Tc5Conv
   p.bias = a.bias; p.residual = a.residual; p.aux = a.aux; p.out = a.out;
   p.M = a.M; p.N = a.N; p.K = a.K; p.ldo = a.ldo; p.ldr = a.ldr; p.ldaux = a.ldaux;
   p.bias_dtype = a.bias_dtype; p.epilogue = a.epilogue; p.splits = pl.splits; p.kb_per_split = pl.kb_per_split;
+  p.norm_eps = a.norm_eps; p.sumsq_in = a.sumsq_in; p.sumsq_in_cols = a.sumsq_in_cols; p.sumsq_out = a.sumsq_out;
+  if ((a.sumsq_in || a.sumsq_out) && (CONV || MODE < 2)) return B200_ENOTSUP;
   p.trace_slot = 0;
 #ifdef B200NN_TC5_TRACE
   p.trace_slot = g_trace_counter++ % TR_SLOTS;
@@ -1521,6 +1570,7 @@ int launch_persistent(const Tc5Args& a, cudaStream_t st, const Tc5Conv* g = null
   p.bias = a.bias; p.residual = a.residual; p.aux = a.aux; p.out = a.out;
   p.M = a.M; p.N = a.N; p.K = a.K; p.ldo = a.ldo; p.ldr = a.ldr; p.ldaux = a.ldaux;
   p.bias_dtype = a.bias_dtype; p.epilogue = a.epilogue; p.splits = 1; p.kb_per_split = static_cast<int>(ceil_div(a.K, BK));
+  p.sumsq_in = nullptr; p.sumsq_out = nullptr; p.norm_eps = 0.f; p.sumsq_in_cols = 0;
   p.x = a.A;
   p.trace_slot = 0;
 #ifdef B200NN_TC5_ABLATE
@@ -1671,6 +1721,15 @@ int linear_tc5(const Tc5Args& a, cudaStream_t st) {
   if (a.M >= (1ll << 31) || a.N >= (1ll << 31) || a.K >= (1ll << 31)) return B200_ENOTSUP;
   const bool glu = (a.epilogue & B200_EPI_GLU) != 0;
   if (glu && (a.N % 128 || (a.epilogue & ~(B200_EPI_GLU | B200_EPI_W_STATIC)) || a.residual)) return B200_ENOTSUP;
+  if (a.sumsq_in || a.sumsq_out) {   // carried by the staged epilogue of the decode kernel
+    if (a.M > 64) return B200_ENOTSUP;
+    if (a.sumsq_in && (a.sumsq_in_cols <= 0 || a.sumsq_in_cols > NORM_MAX_PARTS || (a.epilogue & B200_EPI_SILU_MUL))) return B200_ENOTSUP;
+    const int tb = a.dtype == B200_BF16 ? B200_BF16 : B200_F16;
+    if (a.sumsq_out && (a.N % 64 || glu || (a.epilogue & B200_EPI_SILU_MUL) || (reinterpret_cast<uintptr_t>(a.out) & 7u) || a.ldo % 4 ||
+                        (a.bias && a.bias_dtype != B200_F32 && a.bias_dtype != tb) ||
+                        (a.residual && ((reinterpret_cast<uintptr_t>(a.residual) & 7u) || a.ldr % 4))))
+      return B200_ENOTSUP;
+  }
   if (const int bn = persistent_bn(a.M, a.N, a.K, glu, a.residual != nullptr)) return dispatch_persistent<false>(bn, a, st, nullptr);
   const Tc5Plan pl = plan_tc5(a.M, a.N, a.K, glu);
   if (pl.tiles_m > 65535 || pl.splits > 65535) return B200_ENOTSUP;

@@ -10,6 +10,15 @@ struct Tc5Args {
   int dtype, bias_dtype, epilogue;
   void* workspace;          // unused by the tcgen05 path (split-K needs no global scratch); kept for the dispatcher's fallbacks
   int64_t workspace_bytes;
+  // Decode shapes (M <= 64) only.  sumsq_in != nullptr: every output row m is multiplied, before the
+  // bias, by r_m = 1 / sqrt(s_m / K + norm_eps), s_m = sum of sumsq_in[m * sumsq_in_cols + 0..sumsq_in_cols)
+  // - the RMSNorm of the input rows, applied after the GEMM (the caller folds the gain into W's columns).
+  // sumsq_out != nullptr: the kernel also writes, for every output row m and every block of 64 output
+  // columns j, the sum of squares of the (rounded) outputs: sumsq_out[m * (N / 64) + j].
+  float norm_eps = 0.f;
+  const float* sumsq_in = nullptr;
+  int sumsq_in_cols = 0;
+  float* sumsq_out = nullptr;
 };
 
 // Geometry of an NHWC convolution run as an implicit GEMM (A rows are output pixels,

@@ -193,7 +193,92 @@ class _Lowering:
             if id(node) in self._chain_done:
                 continue
             self.lower(node)
+        if self.fuse:
+            self._fold_rmsnorm_into_decode_linears()
         return self.out
+
+    def _fold_rmsnorm_into_decode_linears(self) -> None:
+        """Decode shapes (M <= 64): an RMSNorm between two GEMMs costs a kernel launch for a few
+        hundred KB.  Where the normalised tensor feeds exactly one GEMM and its input x comes out
+        of a GEMM, the producing GEMM also writes sum-of-squares partials of its output rows
+        (``sumsq_out``, one fp32 per row and 64 columns); the consuming GEMM reads the
+        un-normalised x, uses weights with the gain folded into their columns (weight
+        preparation, once per weight set) and scales its output rows by 1/rms(x) from the
+        partials, since (r x * g) W^T = r (x (W * g)^T) (``b200_linear_norm``).  The normalised
+        activations are no longer rounded to the 16-bit type on the way, so results differ from
+        the unfused kernels by rounding only; ``fuse=False`` keeps the unfused kernels."""
+        steps = self.out.steps
+        touched = self.out.step_tensors
+
+        def buffer_of(name: str) -> str:
+            v = self.out.views.get(name)
+            return v.buffer if v is not None else name
+
+        producer: dict[str, int] = {}          # buffer -> the one step that writes it (-1: several)
+        readers: dict[str, list[int]] = {}     # buffer -> steps that read it
+        for i, st in enumerate(steps):
+            if isinstance(st, AliasStep):
+                continue
+            outs = set(getattr(st, "output_buffer_names", None) or [st.output_buffer_name])
+            for name in touched[i]:
+                b = buffer_of(name)
+                if name in outs:
+                    producer[b] = i if b not in producer else -1
+                elif i not in readers.setdefault(b, []):
+                    readers[b].append(i)
+        graph_outputs = {o.name for o in self.graph.graph_outputs}
+        drop: set[int] = set()
+        for i, st in enumerate(steps):
+            p = getattr(st, "params", None) or {}
+            if p.get("op") != "rmsnorm" or not p.get("round_mid"):
+                continue
+            y_name = st.output_buffer_name
+            x_view = p["x"]
+            rows, cols = p["rows"], p["cols"]
+            users = readers.get(p["y"].buffer, [])
+            if y_name in graph_outputs or len(users) != 1 or producer.get(p["y"].buffer) != i or rows > 64 or cols % 64 or cols > 2048:
+                continue
+            cons = steps[users[0]]
+            cp = getattr(cons, "params", None) or {}
+            if cp.get("op") != "linear" or cp.get("aux") is not None or cp["x"].buffer != p["y"].buffer or cp["x"].offset != p["y"].offset \
+                    or cp["K"] != cols or cp["M"] != rows or cp.get("norm") or x_view.strides[-1] != 1 or x_view.offset % 8 \
+                    or (rows > 1 and x_view.strides[0] % 8):
+                continue
+            # the producer of x: a GEMM writing exactly this [rows, cols] tensor, alone
+            src = producer.get(x_view.buffer, -1)
+            if src < 0:
+                continue
+            pp = getattr(steps[src], "params", None) or {}
+            if pp.get("op") != "linear" or pp.get("glu") or pp.get("aux") is not None or pp["M"] != rows or pp["N"] != cols \
+                    or pp["y"].offset != x_view.offset or pp["y"].buffer != x_view.buffer or pp.get("sumsq_out") is not None:
+                continue
+            n_part = cols // 64
+            sq = self.alloc(f"{y_name}__sumsq", (rows, n_part), "float32")
+            pp["sumsq_out"] = sq
+            touched[src].append(sq.buffer)
+            cp["norm"] = {"eps": float(p["eps"]), "sumsq": sq, "cols": n_part}
+            cp["x"] = x_view
+            # the gain goes into the columns of the consumer's weights
+            prep = next((wp for wp in self.out.weight_preps if cp["w"] in wp.outputs), None)
+            if prep is not None and prep.kind in ("concat_rows", "interleave_rows") and "col_scale" not in prep.params:
+                prep.params["col_scale"] = p["w"]
+            else:
+                scaled = f"{cp['w']}__x_{p['w']}"
+                if scaled not in self.out.views:
+                    wv = self.view(cp["w"])
+                    self.out.weight_preps.append(WeightPrep("scale_cols", [cp["w"], p["w"]], [scaled],
+                                                            {"rows": int(wv.shape[0]), "cols": int(wv.shape[1]), "dtype": cp["y"].dtype}))
+                    self.out.views[scaled] = TensorView(scaled, 0, tuple(wv.shape), V.contiguous_strides(wv.shape), cp["y"].dtype)
+                cp["w"] = scaled
+            names = [n for n in touched[users[0]] if n != y_name] + [x_view.buffer, sq.buffer]
+            touched[users[0]] = names
+            if hasattr(cons, "input_buffer_names"):
+                cons.input_buffer_names = [x_view.buffer if n == y_name else n for n in cons.input_buffer_names]
+            cp["source"] = "rmsnorm(x) folded in: " + cp.get("source", "")
+            drop.add(i)
+        if drop:
+            self.out.steps = [s for i, s in enumerate(steps) if i not in drop]
+            self.out.step_tensors = [t for i, t in enumerate(touched) if i not in drop]
 
     def lower(self, node: OpNode) -> None:
         op = node.op_type

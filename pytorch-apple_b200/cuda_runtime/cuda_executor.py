@@ -220,6 +220,8 @@ class CUDAExecutor:
                 self._prep_concat(prep)
             elif prep.kind == "interleave_rows":
                 self._prep_interleave(prep)
+            elif prep.kind == "scale_cols":
+                self._prep_scale_cols(prep)
             else:
                 raise RuntimeError(f"unknown weight preparation {prep.kind}")
 
@@ -253,6 +255,24 @@ class CUDAExecutor:
         b = native.make_tensor(src.data_ptr(), str(src.dtype).replace("torch.", ""), (n,), (1,))
         native.check(self._lib.b200_strided_copy(C.byref(a), C.byref(b), self._stream_ptr()), "weight cast")
 
+    def _scale_cols(self, mat, rows: int, cols: int, gain_name: str) -> None:
+        """mat[rows, cols] *= gain[cols] (rounded to mat's dtype), in place: an RMSNorm gain folded into the
+        columns of the weights that consume the normalised activations."""
+        dt = str(mat.dtype).replace("torch.", "")
+        gain = self._weight(gain_name, dt)
+        out = native.make_tensor(mat.data_ptr(), dt, (rows, cols), (cols, 1))
+        ins = (native.Tensor * 2)(native.make_tensor(mat.data_ptr(), dt, (rows, cols), (cols, 1)),
+                                  native.make_tensor(gain.data_ptr(), dt, (rows, cols), (0, 1)))
+        ops = (native.EwOp * 1)(native.EwOp(EW_OPCODES["MUL"], 0, 1, DTYPE_CODES[dt], 0.0))
+        native.check(self._lib.b200_ew_chain(C.byref(out), ins, 2, ops, 1, self._stream_ptr()), "gain folding")
+
+    def _prep_scale_cols(self, prep) -> None:
+        p = prep.params
+        src = self._weight(prep.inputs[0], p["dtype"])
+        out = src.clone()      # the unscaled weight may serve other layers (a tied embedding table)
+        self._scale_cols(out, p["rows"], p["cols"], prep.inputs[1])
+        self._prepared[prep.outputs[0]] = out
+
     def _prep_concat(self, prep) -> None:
         """Row-wise concatenation of weights (merged q/k/v projection), in the compute dtype."""
         p = prep.params
@@ -267,6 +287,8 @@ class CUDAExecutor:
                 raise RuntimeError(f"weight '{name}' has {src.numel()} elements, expected {rows * cols}")
             self._convert(src.reshape(-1), out[at:at + rows * cols])
             at += rows * cols
+        if p.get("col_scale"):
+            self._scale_cols(out, sum(p["rows"]), cols, p["col_scale"])
         self._prepared[prep.outputs[0]] = out
 
     def _prep_interleave(self, prep) -> None:
@@ -283,6 +305,8 @@ class CUDAExecutor:
                                      (2 * blk * cols, cols, 1))
             s_t = native.make_tensor(src.data_ptr(), str(src.dtype).replace("torch.", ""), (rows // blk, blk, cols), (blk * cols, cols, 1))
             native.check(self._lib.b200_strided_copy(C.byref(dst), C.byref(s_t), self._stream_ptr()), "weight interleave")
+        if p.get("col_scale"):
+            self._scale_cols(out, 2 * rows, cols, p["col_scale"])
         self._prepared[prep.outputs[0]] = out
 
     def _prep_conv(self, prep, stream: int) -> None:
@@ -513,6 +537,14 @@ class CUDAExecutor:
             epi |= native.EPI_W_STATIC   # model weight: may be prefetched ahead of the previous kernel's completion
         ws = self._ws["__ws_splitk"] if p["workspace"] else None
         ld = lambda v: (v.strides[0] if v.shape[0] > 1 else v.shape[1]) if v is not None else 0
+        norm, sumsq_out = p.get("norm"), p.get("sumsq_out")
+        if norm is not None or sumsq_out is not None:   # decode shapes: RMSNorm folded into its neighbours
+            plan.launches.append((self._lib.b200_linear_norm, (
+                self._ptr(x), self._wptr(p["w"], dt), self._wptr(p["bias"], dt), self._ptr(res), self._ptr(y), p["M"], p["N"], p["K"],
+                ld(x), p["K"], ld(y), ld(res), DTYPE_CODES[dt], DTYPE_CODES[dt], epi,
+                float(norm["eps"]) if norm else 0.0, self._ptr(norm["sumsq"]) if norm else None, int(norm["cols"]) if norm else 0,
+                self._ptr(sumsq_out))))
+            return
         plan.launches.append((self._lib.b200_linear, (
             self._ptr(x), self._wptr(p["w"], dt), self._wptr(p["bias"], dt), self._ptr(res), self._ptr(y), p["M"], p["N"], p["K"],
             ld(x), p["K"], ld(y), ld(res), DTYPE_CODES[dt], DTYPE_CODES[dt], epi, self._ptr(aux), ld(aux),

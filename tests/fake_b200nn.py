@@ -299,6 +299,36 @@ class FakeLibrary:
         _raw(out, dt, [M, N], [ldo, 1]).copy_(r.to(dt))
         return 0
 
+    def b200_linear_norm(self, A, W, bias, residual, out, M, N, K, lda, ldw, ldo, ldr, dtype, bias_dtype, epilogue, norm_eps,
+                         sumsq_in, sumsq_in_cols, sumsq_out, stream):
+        self.calls.append("linear_norm")
+        assert M <= 64
+        dt = _DT[dtype]
+        a = _raw(A, dt, [M, K], [lda, 1]).float()
+        w = _raw(W, dt, [N, K], [ldw, 1]).float()
+        r = a @ w.t()
+        if _addr(sumsq_in):   # RMSNorm of the input rows applied after the GEMM (gain folded into W by the caller)
+            assert 0 < sumsq_in_cols <= 32
+            ss = _raw(sumsq_in, torch.float32, [M, sumsq_in_cols], [sumsq_in_cols, 1]).sum(-1, keepdim=True)
+            r = r * torch.rsqrt(ss / K + norm_eps)
+        if _addr(bias):
+            r = r + _flat(bias, bias_dtype, N).float()
+        if epilogue & 4:
+            r = r.reshape(M, N // 128, 2, 64)
+            g, u = r[:, :, 0].to(dt).float(), r[:, :, 1].to(dt).float()
+            _raw(out, dt, [M, N // 2], [ldo, 1]).copy_(((g / (1 + torch.exp(-g))).to(dt).float() * u).reshape(M, N // 2).to(dt))
+            return 0
+        if _addr(residual):
+            r = r.to(dt).float() + _raw(residual, dt, [M, N], [ldr, 1]).float()
+        if epilogue & 1:
+            r = torch.relu(r)
+        r = r.to(dt)
+        _raw(out, dt, [M, N], [ldo, 1]).copy_(r)
+        if _addr(sumsq_out):
+            assert N % 64 == 0
+            _raw(sumsq_out, torch.float32, [M, N // 64], [N // 64, 1]).copy_(r.float().pow(2).reshape(M, N // 64, 64).sum(-1))
+        return 0
+
     def b200_matmul_strided(self, A, B, out, b1, b2, M, N, K, a_s, b_s, o_s, dtype, stream):
         self.calls.append("matmul")
         dt = _DT[dtype]

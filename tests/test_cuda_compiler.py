@@ -180,13 +180,23 @@ def test_qwen_decode_layer_plan():
     prog = compile_subgraph(ir)
     assert prog.compute_dtype == "bfloat16"
     kinds = [getattr(s, "kernel_name", None) or s.blas_type for s in prog.steps if not isinstance(s, AliasStep)]
-    assert kinds.count("attention") == L and kinds.count("rmsnorm_kernel") == 2 * L + 1
+    # decode shapes: every RMSNorm that sits between two GEMMs is folded into them (the producing GEMM
+    # writes sum-of-squares partials, the consuming one scales its rows); only the first one, fed by the
+    # embedding, keeps its kernel
+    assert kinds.count("attention") == L and kinds.count("rmsnorm_kernel") == 1
     assert kinds.count("gemm") == 4 * L + 1                    # qkv, o_proj, gate+up, down
+    gemms = [s.params for s in prog.steps if isinstance(s, CUBLASStep)]
+    assert sum(1 for g in gemms if g.get("norm")) == 2 * L and sum(1 for g in gemms if g.get("sumsq_out") is not None) == 2 * L
+    assert sorted(p.kind for p in prog.weight_preps).count("scale_cols") == 1          # the tied head gets a scaled copy
+    assert sum(1 for p in prog.weight_preps if p.params.get("col_scale")) == 2 * L - 1  # q/k/v of layers 1.., gate/up of all
     assert kinds.count("qkv_rope_cache_kernel") == L           # rope(q), rope(k) + key write, value write: one launch
     assert kinds.count("index_copy_kernel") == 0 and kinds.count("rope_rotate_kernel") == 0
     assert len(prog.donated_inputs) == 2 * L
-    per_layer = (len(kinds) - 4) / L                           # minus embedding, rope table, final norm, lm_head
-    assert per_layer == 8
+    per_layer = (len(kinds) - 4) / L                           # minus embedding, rope table, first norm, lm_head
+    assert per_layer == 6
+    # fuse=False keeps every op on its own kernel, with the reference's rounding points
+    kinds0 = [getattr(s, "kernel_name", None) or s.blas_type for s in compile_subgraph(ir, fuse=False).steps if not isinstance(s, AliasStep)]
+    assert "rmsnorm_kernel" not in kinds0 and kinds0.count("gemm") == 7 * L + 1
     # without donation the cache is copied, as in the reference
     prog2 = compile_subgraph(ir, donate_inputs=False)
     assert not prog2.donated_inputs

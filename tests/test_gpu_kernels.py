@@ -128,6 +128,84 @@ def test_linear_gated_mlp_epilogue(lib, M, I, K):
     assert not ws.any()
 
 
+@pytest.mark.parametrize("M,N,K,mode", [(1, 2048, 1536, "bias"), (8, 2048, 1536, "bias"), (64, 2048, 1536, "bias"), (64, 17920, 1536, "glu"),
+                                        (5, 17920, 1536, "glu"), (64, 151936, 1536, "plain"), (33, 1536, 1536, "chain"), (64, 1536, 8960, "chain")])
+def test_linear_norm_fused_rmsnorm(lib, M, N, K, mode):
+    """RMSNorm folded into decode GEMMs.  "chain": a residual GEMM that also writes the sum-of-squares
+    partials of its output rows, followed by a GEMM over gain-folded weights that scales its output
+    rows by 1/rms from those partials - against the fp32 statement of rmsnorm + matmul with the
+    roundings of the unfused kernels, and against the unfused kernels themselves."""
+    dtype = torch.bfloat16
+    BF = 2
+    if mode == "chain":
+        a, w, res = gen((M, K), dtype, 0, 0.5), gen((N, K), dtype, 1, 0.05), gen((M, N), dtype, 2)
+        y = torch.empty(M, N, dtype=dtype, device="cuda")
+        sq = torch.full((M, N // 64), float("nan"), device="cuda")
+        A, W, R = a.cuda(), w.cuda(), res.cuda()
+        ok(lib, lib.b200_linear_norm(A.data_ptr(), W.data_ptr(), None, R.data_ptr(), y.data_ptr(), M, N, K, K, K, N, N, BF, BF, 8,
+                                     0.0, None, 0, sq.data_ptr(), stream()))
+        ref = ((a.float() @ w.float().T).to(dtype).float() + res.float()).to(dtype)
+        close(y, ref, rtol=2e-2, atol=2e-2)
+        # the partials describe the rows that were actually written
+        want_sq = y.float().pow(2).reshape(M, N // 64, 64).sum(-1)
+        torch.testing.assert_close(sq, want_sq, rtol=1e-4, atol=1e-4)
+        x, n_part, sumsq = y, N // 64, sq       # feed the next layer from them
+        K2, N2 = N, 2048
+    else:
+        x = gen((M, K), dtype, 0, 3.0).cuda()
+        n_part = 3
+        sumsq = x.float().pow(2).reshape(M, n_part, K // n_part).sum(-1).contiguous()
+        K2, N2 = K, N
+    gain = (1 + 0.1 * gen((K2,), torch.float32, 5)).to(dtype).cuda()
+    w2 = gen((N2, K2), dtype, 6, 0.03).cuda()
+    w2_folded = (w2.float() * gain.float()[None, :]).to(dtype)          # what the weight preparation produces
+    bias = gen((N2,), dtype, 7).cuda() if mode in ("bias", "chain") else None
+    epi = 8 | (4 if mode == "glu" else 0)
+    n_out = N2 // 2 if mode == "glu" else N2
+    out = torch.full((M, n_out), float("nan"), dtype=dtype, device="cuda")
+    ok(lib, lib.b200_linear_norm(x.data_ptr(), w2_folded.data_ptr(), bias.data_ptr() if bias is not None else None, None, out.data_ptr(), M, N2, K2,
+                                 K2, K2, n_out, 0, BF, BF, epi, 1e-6, sumsq.data_ptr(), n_part, None, stream()))
+
+    def finish(r):
+        if bias is not None:
+            r = r + bias.float().cpu()
+        if mode == "glu":
+            r = r.reshape(M, N2 // 128, 2, 64)
+            g_, u_ = r[:, :, 0].to(dtype).float(), r[:, :, 1].to(dtype).float()
+            r = (torch.nn.functional.silu(g_).to(dtype).float() * u_).reshape(M, n_out)
+        return r
+
+    xf = x.float().cpu()
+    rr = torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-6)
+    # the reference's rounding points: round(x r), round(. * gain), then the GEMM
+    a2 = ((xf * rr).to(dtype).float() * gain.float().cpu()).to(dtype).float()
+    # (the gated form multiplies two rounded factors: a one-ulp difference in the gate is scaled by |up| <= ~5)
+    tol = 6e-2 if mode == "glu" else 3e-2
+    close(out, finish(a2 @ w2.float().cpu().T), rtol=3e-2, atol=tol)
+    # the exact statement of what the kernel computes: r * (x W'^T)
+    close(out, finish(rr * (xf @ w2_folded.float().cpu().T)), rtol=2e-2, atol=tol / 2)
+    # and the unfused pair of kernels
+    y_n = torch.empty_like(x)
+    ok(lib, lib.b200_rmsnorm(x.data_ptr(), gain.data_ptr(), y_n.data_ptr(), M, K2, K2, K2, 1e-6, BF, 1, stream()))
+    out2 = torch.empty_like(out)
+    ok(lib, lib.b200_linear(y_n.data_ptr(), w2.data_ptr(), bias.data_ptr() if bias is not None else None, None, out2.data_ptr(), M, N2, K2,
+                            K2, K2, n_out, 0, BF, BF, epi, None, 0, None, 0, stream()))
+    close(out, out2, rtol=3e-2, atol=tol)
+    code = C.c_int(0)
+    ok(lib, lib.b200_debug_device_error(C.byref(code), 1))
+    assert code.value == 0
+
+
+def test_linear_norm_rejects_shapes_outside_the_fused_kernel(lib):
+    t = torch.zeros(128 * 1536, dtype=torch.bfloat16, device="cuda")
+    f = torch.zeros(4096, device="cuda")
+    args = lambda M, N, K, cols, sq_out: (t.data_ptr(), t.data_ptr(), None, None, t.data_ptr(), M, N, K, K, K, N, 0, 2, 2, 0, 1e-6,
+                                          f.data_ptr(), cols, f.data_ptr() if sq_out else None, stream())
+    assert lib.b200_linear_norm(*args(100, 64, 128, 1, False)) == -4 and b"M <= 64" in lib.b200_last_error()   # prefill-sized M
+    assert lib.b200_linear_norm(*args(8, 64, 128, 40, False)) == -4                                              # too many partials
+    assert lib.b200_linear_norm(*args(8, 72, 128, 1, True)) == -4                                                # N not a multiple of 64
+
+
 def test_linear_rejects_unaligned(lib):
     a = torch.zeros(4, 12, dtype=torch.bfloat16, device="cuda")
     rc = lib.b200_linear(a.data_ptr(), a.data_ptr(), None, None, a.data_ptr(), 4, 4, 12, 12, 12, 4, 0, 2, 2, 0, None, 0, None, 0, stream())
@@ -210,6 +288,43 @@ def test_attn_decode(lib, B, S, valid):
     ok(lib, lib.b200_attn_decode(Q.data_ptr(), K.data_ptr(), V.data_ptr(), None, out.data_ptr(), B, Hq, Hkv, S, D, Hq * D,
                                  Hkv * S * D, S * D, 0, D ** -0.5, 2, ws.data_ptr(), ws.numel(), stream()))
     close(out, attn_ref(q, k, v, None, D ** -0.5, dtype)[:, :, 0], rtol=2e-2, atol=5e-3)
+
+
+@pytest.mark.parametrize("B,S,Hq,Hkv", [(40, 2048, 12, 2), (64, 4352, 12, 2), (33, 1000, 8, 1), (130, 640, 4, 4)])
+def test_attn_decode_many_sequences_ragged_masks(lib, B, S, Hq, Hkv):
+    """Batches large enough for the balanced kernel (every CTA gets the same number of unmasked 16-key
+    blocks): each sequence has its own attended length - from a single key to the whole cache - some
+    masks have holes, and the call is repeated (the tickets of the merge must return to zero)."""
+    dtype, D = torch.bfloat16, 128
+    g = torch.Generator().manual_seed(B)
+    q, k, v = gen((B, Hq, 1, D), dtype), gen((B, Hkv, S, D), dtype, 1), gen((B, Hkv, S, D), dtype, 2)
+    neg = torch.finfo(dtype).min
+    mask = torch.full((B, 1, 1, S), neg, dtype=dtype)
+    lengths = torch.randint(1, S + 1, (B,), generator=g)
+    lengths[0], lengths[1], lengths[2] = 1, S, 17
+    for b in range(B):
+        mask[b, 0, 0, :lengths[b]] = 0
+        if b % 5 == 3 and lengths[b] > 200:      # a hole of masked keys inside the attended range
+            mask[b, 0, 0, 64:160] = neg
+        if b % 7 == 4:
+            mask[b, 0, 0, :lengths[b]] = torch.where(torch.rand(int(lengths[b]), generator=g) < 0.5, 0.0, neg).to(dtype)
+            mask[b, 0, 0, 0] = 0
+    ref = attn_ref(q, k, v, mask, D ** -0.5, dtype)[:, :, 0]
+    Q, K, V, M = q.cuda(), k.cuda(), v.cuda(), mask.cuda()
+    ws = torch.empty(max(16, lib.b200_attn_decode_workspace_bytes(B, Hq, Hkv, S, D)), dtype=torch.uint8, device="cuda")
+    for _ in range(2):
+        out = torch.full((B, Hq, D), float("nan"), dtype=dtype, device="cuda")
+        ok(lib, lib.b200_attn_decode(Q.data_ptr(), K.data_ptr(), V.data_ptr(), M.data_ptr(), out.data_ptr(), B, Hq, Hkv, S, D, Hq * D,
+                                     Hkv * S * D, S * D, S, D ** -0.5, 2, ws.data_ptr(), ws.numel(), stream()))
+        close(out, ref, rtol=2e-2, atol=5e-3)
+    # a sequence whose mask admits no key gives zeros (ATen would average all rows; no model produces such a mask)
+    mask[5] = neg
+    out = torch.full((B, Hq, D), float("nan"), dtype=dtype, device="cuda")
+    ok(lib, lib.b200_attn_decode(Q.data_ptr(), K.data_ptr(), V.data_ptr(), mask.cuda().data_ptr(), out.data_ptr(), B, Hq, Hkv, S, D, Hq * D,
+                                 Hkv * S * D, S * D, S, D ** -0.5, 2, ws.data_ptr(), ws.numel(), stream()))
+    assert (out[5] == 0).all()
+    keep = [b for b in range(B) if b != 5]
+    close(out[keep], ref[keep], rtol=2e-2, atol=5e-3)
 
 
 @pytest.mark.parametrize("B,T", [(1, 512), (2, 48), (1, 100)])
