@@ -23,7 +23,7 @@ INCLUDE = ROOT.parent / "include"
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
-    "-Xcompiler", "-fPIC", "--use_fast_math=false", "-I", str(INCLUDE),
+    "-Xcompiler", "-fPIC", "-I", str(INCLUDE),
 ]
 
 
@@ -43,7 +43,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     OBJ_DIR.mkdir(parents=True, exist_ok=True)
     headers = list(CSRC.glob("*.cuh")) + list(INCLUDE.glob("*.h"))
     newest_header = max((h.stat().st_mtime for h in headers), default=0.0)
-    flags = [f for f in NVCC_FLAGS if f != "--use_fast_math=false"]
+    flags = list(NVCC_FLAGS)
 
     def compile_one(src: Path) -> Path:
         obj = OBJ_DIR / (src.stem + ".o")

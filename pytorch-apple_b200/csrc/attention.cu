@@ -29,28 +29,9 @@ struct DecodeParams {
   int split_len, splits;
   float scale;
   int mask_dtype;
-  int l2_ahead;   // blocks per warp requested into L2 ahead of the shared-memory ring
   void* out;      // cluster-merge mode: final output [B][Hq][HD] in the activation dtype
 };
 
-constexpr int DEC_MAX_BLOCKS = 128;  // 16-key blocks per split (split_len <= 2048)
-
-// Phase time stamps for tuning, compiled in only with -DB200NN_TC5_TRACE (never in the shipped library).
-#ifdef B200NN_TC5_TRACE
-constexpr int ATR_CTAS = 1280, ATR_N = 8;
-__device__ unsigned long long g_attn_trace[ATR_CTAS][ATR_N];
-#define ATTN_STAMP(i)                                                                                   \
-  do {                                                                                                  \
-    const int cta_ = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);                    \
-    if (threadIdx.x == 0 && cta_ < ATR_CTAS) {                                                          \
-      unsigned long long t_;                                                                            \
-      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                            \
-      g_attn_trace[cta_][i] = t_;                                                                       \
-    }                                                                                                   \
-  } while (0)
-#else
-#define ATTN_STAMP(i)
-#endif
 
 constexpr int DEC_STAGE_BYTES = 2 * 16 * HD * 2;  // 16 keys of K and of V
 constexpr int DEC_MAX_SPLIT = 2048;            // keys per split (mask values of a split are staged in shared memory)
@@ -102,11 +83,9 @@ __global__ void __launch_bounds__(128, STAGES == 2 ? 3 : 2) attn_decode_kernel(c
   const int n_keys = static_cast<int>(s_end - s_begin);
   const int nblk = (n_keys + 15) / 16;
 
-  ATTN_STAMP(0);
   pdl_trigger();
   if (CM) tc5::cluster_sync();   // every CTA of the cluster runs before anyone writes into a peer (overlaps the predecessor)
   pdl_wait();   // q, the new cache rows and the mask come from the kernels before this one
-  ATTN_STAMP(1);
 
   // ---- per-lane addressing -------------------------------------------------------------
   // cp.async: lane copies chunk (lane & 15) of rows 2i + (lane >> 4), i = 0..7
@@ -144,21 +123,6 @@ __global__ void __launch_bounds__(128, STAGES == 2 ? 3 : 2) attn_decode_kernel(c
     }
   };
 
-  // Ask for a block's K and V rows (two contiguous 4 KB runs) to be brought into L2.  The ring
-  // keeps at most one or two blocks per warp in flight (shared memory is the limit); requests
-  // into L2 cost no shared memory, so the DRAM latency is paid there and the ring copies that
-  // follow find their lines in L2.
-  const T* k_blk0 = static_cast<const T*>(p.k) + b * p.kv_bs + hk * p.kv_hs + s_begin * HD;
-  const T* v_blk0 = static_cast<const T*>(p.v) + b * p.kv_bs + hk * p.kv_hs + s_begin * HD;
-  auto l2_prefetch = [&](int blk) {
-    if (lane == 0 && blk < nblk) {
-      const int rows = min(16, n_keys - blk * 16);
-      const uint32_t bytes = static_cast<uint32_t>(rows) * HD * 2;
-      asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(k_blk0 + static_cast<int64_t>(blk) * 16 * HD), "r"(bytes) : "memory");
-      asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(v_blk0 + static_cast<int64_t>(blk) * 16 * HD), "r"(bytes) : "memory");
-    }
-  };
-
   // The first blocks of every warp are fetched before the mask has been looked at (they are
   // almost always needed): the mask scan and the query loads hide behind these copies.
   int cur = warp < nblk ? warp : -1, nxt = -1;
@@ -169,7 +133,6 @@ __global__ void __launch_bounds__(128, STAGES == 2 ? 3 : 2) attn_decode_kernel(c
     if (nxt >= 0) issue(nxt, 1);
     cp_async_commit();
   }
-  for (int dd = 0; dd < p.l2_ahead; ++dd) l2_prefetch(warp + 4 * (STAGES - 1 + dd));
 
   // ---- which of this warp's blocks have an unmasked key: bit j <-> block warp + 4j ----
   const char* mask_row = p.mask ? static_cast<const char*>(p.mask) : nullptr;
@@ -200,7 +163,6 @@ __global__ void __launch_bounds__(128, STAGES == 2 ? 3 : 2) attn_decode_kernel(c
       qf[ks][1] = g < p.G ? *reinterpret_cast<const uint32_t*>(qr + 16 * ks + 8) : 0u;
     }
   }
-  ATTN_STAMP(2);
 
   float o[8][4];   // [dim tile j][dims 16j+g (0,1) / 16j+g+8 (2,3)  x  heads 2t (0,2) / 2t+1 (1,3)]
 #pragma unroll
@@ -224,8 +186,6 @@ __global__ void __launch_bounds__(128, STAGES == 2 ? 3 : 2) attn_decode_kernel(c
       if (fetch < nblk) {
         issue(fetch, st_fetch);
         fetched = fetch;
-        const int pb = fetch + 4 * p.l2_ahead;
-        if (p.l2_ahead && pb < nblk && is_valid(pb)) l2_prefetch(pb);
         fetch = next_valid(fetch + 4);
       }
       cp_async_commit();
@@ -235,8 +195,6 @@ __global__ void __launch_bounds__(128, STAGES == 2 ? 3 : 2) attn_decode_kernel(c
       if (fetch < nblk) {
         issue(fetch, st_fetch);
         fetched = fetch;
-        const int pb = fetch + 4 * p.l2_ahead;
-        if (p.l2_ahead && pb < nblk && is_valid(pb)) l2_prefetch(pb);
         fetch = next_valid(fetch + 4);
       }
       cp_async_commit();
@@ -293,7 +251,6 @@ __global__ void __launch_bounds__(128, STAGES == 2 ? 3 : 2) attn_decode_kernel(c
     else cur = fetched;
   }
   cp_async_wait<0>();
-  ATTN_STAMP(3);
 
   // ---- merge the four warps: every warp parks its accumulators (and running max / sum) in the
   // shared memory its own ring occupied; after one barrier thread d adds up dim d of every head ----
@@ -358,16 +315,7 @@ __global__ void __launch_bounds__(128, STAGES == 2 ? 3 : 2) attn_decode_kernel(c
       static_cast<T*>(p.out)[((b * p.Hq) + static_cast<int64_t>(hk) * p.G + h) * HD + d] = from_f32<T>(l > 0.f ? acc / l : 0.f);
     }
   }
-  ATTN_STAMP(4);
 }
-
-#ifdef B200NN_TC5_TRACE
-}  // namespace b200
-extern "C" int b200_debug_attn_trace(unsigned long long* host_out) {
-  return cudaMemcpyFromSymbol(host_out, b200::g_attn_trace, sizeof(unsigned long long) * b200::ATR_CTAS * b200::ATR_N) == cudaSuccess ? 0 : -3;
-}
-namespace b200 {
-#endif
 
 // grid = B*Hq blocks of 128 threads (one per head dim)
 template <typename T>
@@ -618,21 +566,11 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const __grid_constant
 
 struct DecodePlan { int split_len; int splits; bool cluster; };
 
-// B200NN_ATTN_CLUSTER: 0 = never merge in-kernel, 1 = only for big batches, 2 (default) = whenever the
-// shape allows (measured faster at every batch size: B=8 14.7 vs 19.6 us, B=1 12.2 vs 13.4 us)
-static int cluster_merge_mode() {
-  static int v = -1;
-  if (v < 0) {
-    const char* e = getenv("B200NN_ATTN_CLUSTER");
-    v = (e && e[0] >= '0' && e[0] <= '2') ? e[0] - '0' : 2;
-  }
-  return v;
-}
-
 static DecodePlan plan_decode(int64_t B, int Hkv, int64_t S, int G = 8) {
   const int64_t want = 2 * 148;  // fixed so that the workspace size does not depend on the device
-  // Plenty of sequences: eight splits per (sequence, KV head), merged inside the kernel by a cluster.
-  if (cluster_merge_mode() && (B * Hkv * 8 >= 4 * 148 || cluster_merge_mode() == 2) && S >= 8 * 64 && S <= 8 * DEC_MAX_SPLIT && G <= 8) {
+  // Caches of 512 .. 16384 rows: up to eight splits per (sequence, KV head), merged inside the kernel by a cluster
+  // (measured faster than the two-kernel form at every batch size: B=8 14.7 vs 19.6 us, B=1 12.2 vs 13.4 us).
+  if (S >= 8 * 64 && S <= 8 * DEC_MAX_SPLIT && G <= 8) {
     // Among the split counts min(G, 6)..8 take the one with the shortest estimated time: waves of
     // CTAs (three CTAs per SM are resident at a time) x keys per split.  Measured at B=64, S=4352:
     // 8 splits (2.3 waves of 544 keys) 55.2 us, 7 splits 59.1, 6 splits (1.7 waves of 736 keys) 52.2;
@@ -709,20 +647,10 @@ extern "C" int b200_attn_decode(const void* q, const void* k, const void* v, con
   p.out = out;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   dim3 grid(static_cast<unsigned>(d.splits), static_cast<unsigned>(Hkv), static_cast<unsigned>(B));
-  static int stages = 0, l2_ahead = 0;   // ring depth per warp: 2 (three CTAs per SM) or 3 (two CTAs per SM)
-  if (stages == 0) {
-    const char* e = getenv("B200NN_ATTN_STAGES");
-    stages = (e && e[0] == '3') ? 3 : 2;
-    const char* a = getenv("B200NN_ATTN_L2_AHEAD");
-    l2_ahead = a && a[0] ? atoi(a) : 0;   // measured: requests into L2 ahead of the ring only slow the kernel down
-    if (l2_ahead < 0 || l2_ahead > 8) l2_ahead = 0;
-  }
-  p.l2_ahead = l2_ahead;
   B200_DISPATCH_HALF(dtype, T, {
     static bool configured = false;
     if (!configured) {
-      cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<T, 3, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 4 * 3 * DEC_STAGE_BYTES);
-      if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_decode_kernel<T, 2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 4 * 2 * DEC_STAGE_BYTES);
+      cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<T, 2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 4 * 2 * DEC_STAGE_BYTES);
       if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_decode_kernel<T, 2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 4 * 2 * DEC_STAGE_BYTES);
       if (e != cudaSuccess) B200_FAIL(B200_ELAUNCH, "attn_decode_kernel attribute: %s", cudaGetErrorString(e));
       configured = true;
@@ -749,8 +677,7 @@ extern "C" int b200_attn_decode(const void* q, const void* k, const void* v, con
       cfg.numAttrs = n_attrs;
       cudaLaunchKernelEx(&cfg, attn_decode_kernel<T, 2, true>, p);
     } else {
-      if (stages == 2) launch_pdl(attn_decode_kernel<T, 2, false>, grid, dim3(128), 4 * 2 * DEC_STAGE_BYTES, st, p);
-      else launch_pdl(attn_decode_kernel<T, 3, false>, grid, dim3(128), 4 * 3 * DEC_STAGE_BYTES, st, p);
+      launch_pdl(attn_decode_kernel<T, 2, false>, grid, dim3(128), 4 * 2 * DEC_STAGE_BYTES, st, p);
       launch_pdl(attn_decode_merge_kernel<T>, dim3(static_cast<unsigned>(B * Hq)), dim3(128), 0, st, static_cast<const float*>(p.part_acc),
                  static_cast<const float*>(p.part_ml), static_cast<T*>(out), Hq, Hkv, p.G, d.splits);
     }

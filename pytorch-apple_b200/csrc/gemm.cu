@@ -491,20 +491,6 @@ static int64_t skinny_workspace_bytes(int64_t M, int64_t N, int64_t K) {
   return s.row_blocks * SK_ROWS * s.mpad * 4 + s.row_blocks * 4 + 256;
 }
 
-// Which kernel family serves a linear of M rows: up to 16 rows the register-streaming
-// split-K kernel, above that the tcgen05 tiles (which also split K for narrow outputs).
-static bool prefers_skinny(int64_t M) {
-  // Rows up to which the mma.sync weight-streaming kernel is tried before the tcgen05 path.
-  // Default 0: the tcgen05 kernel (activation rows padded into its 64-row tile) measured faster
-  // for every decode batch size; the skinny kernel remains the fallback for unaligned operands.
-  static int limit = -1;
-  if (limit < 0) {
-    const char* e = getenv("B200NN_SKINNY_MAX_M");
-    limit = e && e[0] ? atoi(e) : 0;
-  }
-  return M <= limit;
-}
-
 extern "C" int64_t b200_linear_workspace_bytes(int64_t M, int64_t N, int64_t K) {
   const int64_t a = skinny_workspace_bytes(M, N, K), b = linear_tc5_workspace_bytes(M, N, K);
   return a > b ? a : b;
@@ -543,7 +529,7 @@ extern "C" int b200_linear(const void* A, const void* W, const void* bias, const
   if (!(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0 && aligned16(A) && aligned16(W)))
     B200_FAIL(B200_EALIGN, "b200_linear: K, lda, ldw must be multiples of 8 and A, W 16-byte aligned");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (!prefers_skinny(M)) {
+  {   // the tcgen05 kernels first (measured faster for every batch size); what follows are the fallbacks for operands they cannot take
     Tc5Args t{A, W, bias, residual, aux, out, M, N, K, lda, ldw, ldo, ldr, ldaux, dtype, bias_dtype, epilogue, workspace, workspace_bytes};
     const int rc = linear_tc5(t, st);
     if (rc != B200_ENOTSUP) return rc;

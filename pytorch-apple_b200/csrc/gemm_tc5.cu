@@ -30,14 +30,14 @@ constexpr int NORM_MAX_PARTS = 32;   // row scaling: at most this many sum-of-sq
 //   1  a single row tile with 64 < M <= 128: pure weight streaming, one CTA per SM, deep ring;
 //   2  M <= 64 (decode): the activation tile is loaded 64 rows high (the MMA still reads 128
 //      rows; the upper half is whatever follows in shared memory and only feeds accumulator
-//      rows that are never stored), which halves the stage size: two CTAs per SM, so the
-//      next GEMM in the stream can already sit on the SM and prefetch its weights.
-//   3  as 2, but one CTA per SM with a ring twice as deep (more bytes in flight per CTA).
+//      rows that are never stored), which halves the stage size; one CTA per SM with a ring of
+//      7 (128-wide tiles) or 12 (64-wide) stages - weight streaming is bound by the bytes a
+//      CTA keeps in flight (two CTAs per SM with rings half as deep measured 4 % slower).
 template <int BN, int MODE> struct Cfg {
   static constexpr int AROWS = MODE >= 2 ? 64 : 128;
   static constexpr int A_STAGE = AROWS * BK * 2;
-  static constexpr int ST = MODE == 0 ? (BN == 128 ? 3 : 4) : MODE == 1 ? (BN == 128 ? 4 : 6) : MODE == 2 ? (BN == 128 ? 4 : 6) : (BN == 128 ? 7 : 12);
-  static constexpr int CTAS = (MODE == 1 || MODE == 3) ? 1 : 2;
+  static constexpr int ST = MODE == 0 ? (BN == 128 ? 3 : 4) : MODE == 1 ? (BN == 128 ? 4 : 6) : (BN == 128 ? 7 : 12);
+  static constexpr int CTAS = MODE == 0 ? 2 : 1;
   static constexpr int RING = ST * (A_STAGE + BN * BK * 2);
   // split-K only: fp32 receive buffer for the partial-tile rows this CTA owns, one slot per
   // cluster rank, behind the ring (peers write into it while this CTA may still be computing)
@@ -45,59 +45,10 @@ template <int BN, int MODE> struct Cfg {
   static constexpr int RECV = RECV_ROWS * (BN + 4) * 4;
 };
 
-int env_int(const char* name, int dflt) {
-  const char* e = getenv(name);
-  return e && e[0] ? atoi(e) : dflt;
-}
-// decode (M <= 64) tuning: ring depth / CTAs per SM, and how many CTAs split-K aims for
-int decode_deep() { static int v = env_int("B200NN_TC5_DECODE_DEEP", 0); return v; }
-int split_target() { static int v = env_int("B200NN_TC5_SPLIT_CTAS", 148); return v; }
-int split_traffic_div() { static int v = env_int("B200NN_TC5_SPLIT_TRAFFIC", 2); return v; }
-int split_min_kb() { static int v = env_int("B200NN_TC5_SPLIT_MIN_KB", 2); return v; }
-int prefer_bn128() { static int v = env_int("B200NN_TC5_PREFER_BN128", 0); return v; }
-
-// Phase time stamps for tuning, compiled in only with -DB200NN_TC5_TRACE (never in the shipped
-// library): every CTA of the one-tile kernel records %globaltimer at fixed points into
-// g_tc5_trace[launch slot][CTA][point]; b200_debug_tc5_trace copies the table to the host.
-#ifdef B200NN_TC5_TRACE
-constexpr int TR_SLOTS = 64, TR_CTAS = 320, TR_N = 14;
-__device__ unsigned long long g_tc5_trace[TR_SLOTS][TR_CTAS][TR_N];
-int g_trace_counter = 0;   // host side: launches so far
-__device__ __forceinline__ unsigned long long globaltimer_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-#define TC5_STAMP(i)                                                                              \
-  do {                                                                                            \
-    const int cta_ = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);              \
-    if (cta_ < TR_CTAS) g_tc5_trace[p.trace_slot][cta_][i] = globaltimer_ns();                   \
-  } while (0)
-constexpr int PTR_CTAS = 160, PTR_TILES = 12, PTR_N = 8;
-__device__ unsigned long long g_tc5p_trace[PTR_CTAS][PTR_TILES][PTR_N];
-__device__ unsigned long long g_tc5p_kb[2][PTR_CTAS][PTR_TILES][PTR_N];   // [0] producer: stage free, [1] MMA: stage full
-#define TC5P_KB(which, ti_, kb_)                                                                              \
-  do {                                                                                                        \
-    if (blockIdx.x < PTR_CTAS && (ti_) < PTR_TILES && (kb_) < PTR_N) g_tc5p_kb[which][blockIdx.x][ti_][kb_] = globaltimer_ns(); \
-  } while (0)
-#define TC5P_STAMP(ti_, i)                                                                              \
-  do {                                                                                                  \
-    if (blockIdx.x < PTR_CTAS && (ti_) < PTR_TILES) g_tc5p_trace[blockIdx.x][ti_][i] = globaltimer_ns(); \
-  } while (0)
-#else
-#define TC5_STAMP(i)
-#define TC5P_STAMP(ti_, i)
-#define TC5P_KB(which, ti_, kb_)
-#endif
-
-// Ablation switches for tuning (only with -DB200NN_TC5_ABLATE, never in the shipped library):
-// a bit mask from the environment turns parts of the persistent kernel into no-ops so that the
-// cost of each part shows in the kernel's duration.  Results are garbage under ablation.
-#ifdef B200NN_TC5_ABLATE
-#define TC5_ABL(bit) ((p.trace_slot & (bit)) != 0)
-#else
-#define TC5_ABL(bit) false
-#endif
+// Decode (M <= 64) plan, settled by measurement on the Qwen2.5-1.5B shapes (a layer's four GEMMs, B = 1..64):
+// split-K aims for one CTA per SM, keeps the partial sums below half the weight bytes and at least two
+// k-blocks per CTA; the deep single-CTA ring (mode 3) gained 4 % and is used.
+constexpr int SPLIT_TARGET_CTAS = 148, SPLIT_TRAFFIC_DIV = 2, SPLIT_MIN_KB = 2;
 
 struct Tc5Params {
   const void* bias; const void* residual; const void* aux; void* out;
@@ -105,7 +56,6 @@ struct Tc5Params {
   int bias_dtype, epilogue, splits, kb_per_split;
   const void* x;   // convolution input (implicit-GEMM mode only)
   Tc5Conv g;
-  int trace_slot;  // used by the tracing build only
   // persistent kernel: shared-memory plan chosen by the host (bytes from the aligned base)
   int pst, pstage;      // ring stages and bytes per stage
   int wr, w_off;        // weights resident: all k-blocks of the CTA's weight tile stay in shared memory at w_off
@@ -326,7 +276,6 @@ __global__ void __launch_bounds__(224, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(cons
   const int rank = nsp > 1 ? static_cast<int>(tc5::cluster_ctarank()) : 0;
 
   if (threadIdx.x == 0) {
-    TC5_STAMP(0);
     failed = 0;
     // a stage is full when both producers' copies have landed (or the 128 gather threads have arrived)
     for (int s = 0; s < ST; ++s) { tc5::mbar_init(&full_bar[s], gather ? 129 : 2); tc5::mbar_init(&empty_bar[s], 1); }
@@ -350,7 +299,6 @@ __global__ void __launch_bounds__(224, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(cons
   const bool w_static = (p.epilogue & B200_EPI_W_STATIC) != 0;
   const int pre = w_static ? (nkb < ST ? nkb : ST) : 0;   // weight stages issued before the cluster start-up barrier
   if (warp == 6 && lane == 0) {
-    TC5_STAMP(1);
     for (int i = 0; i < pre; ++i) {
       tc5::mbar_arrive_expect_tx(&full_bar[i], B_STAGE);
       tc5::tma_load_2d(smem + i * STAGE + A_STAGE, &map_w, &full_bar[i], (kb0 + i) * BK, n0);
@@ -379,7 +327,6 @@ __global__ void __launch_bounds__(224, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(cons
   } else if (warp == 0) {
     if (lane == 0 && !gather) {   // ---- activation producer (the gather variant fills the A tile with the epilogue warps) ----
       pdl_wait();
-      TC5_STAMP(2);
       int issued = 0;
       for (int i = 0; i < nkb; ++i) {
         const int s = i % ST;
@@ -407,7 +354,6 @@ __global__ void __launch_bounds__(224, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(cons
         const int s = i % ST;
         const uint32_t ph = (i / ST) & 1;
         if (!tc5::mbar_wait(&full_bar[s], ph)) { failed = 1; atomicExch(&g_tc5_error, 2); break; }
-        if (i == 0) TC5_STAMP(3);
         tc5::tc_fence_after();
         const uint32_t a_addr = tc5::smem_addr(smem + s * STAGE), b_addr = a_addr + A_STAGE;
         const uint64_t da = tc5::umma_desc_sw128(a_addr), db = tc5::umma_desc_sw128(b_addr);
@@ -417,7 +363,6 @@ __global__ void __launch_bounds__(224, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(cons
         tc5::umma_commit(&empty_bar[s]);
       }
       tc5::umma_commit(&acc_bar);
-      TC5_STAMP(4);
     }
   } else {
     pdl_wait();   // residual, bias, split-K scratch and convolution inputs come from earlier kernels
@@ -485,7 +430,6 @@ __global__ void __launch_bounds__(224, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(cons
     if (!ok && lane == 0) { failed = 1; atomicExch(&g_tc5_error, 3); }
     ok = ok && !*reinterpret_cast<volatile int*>(&failed);
     ok = __all_sync(0xffffffffu, ok);
-    if (threadIdx.x == 64) TC5_STAMP(5);
     const int64_t m = m0 + q * 32 + lane;
     const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
     if (ok && staged) {
@@ -539,7 +483,6 @@ __global__ void __launch_bounds__(224, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(cons
       }
       tc5::tc_fence_before();
     }
-    if (threadIdx.x == 64) TC5_STAMP(6);
   }
 
   // ---- staged epilogue.  The split-K CTAs of one output tile form a thread-block cluster along
@@ -552,7 +495,6 @@ __global__ void __launch_bounds__(224, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(cons
     __syncwarp();
     if (nsp > 1) tc5::cluster_sync();
     else __syncthreads();
-    if (threadIdx.x == 64) TC5_STAMP(7);
     if (!*reinterpret_cast<volatile int*>(&failed)) {
       // All 224 threads walk the owned rows as float4 units in row-major order.  The loop body is
       // kept short: it runs a handful of times per thread, so its cost is instruction count.
@@ -625,10 +567,8 @@ __global__ void __launch_bounds__(224, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(cons
         }
       }
     }
-    if (threadIdx.x == 64) TC5_STAMP(9);
   }
   __syncthreads();
-  if (threadIdx.x == 0) TC5_STAMP(8);
   if (warp == 1) { tc5::tc_fence_after(); tc5::tmem_dealloc(tmem_base, BN); }
 }
 
@@ -741,7 +681,6 @@ __global__ void __launch_bounds__(TS ? 416 : (CONV ? 352 : 256), 1)
       RingPos rp;
       for (int tile = blockIdx.x; tile < n_tiles && !dead(); tile += gridDim.x, ++ti) {
         const int m0 = tile_m(tile) * BM;
-        if (warp == 0) TC5P_STAMP(ti, 5);   // producer: tile started
         int cpb = 1, img = 0, base_w = 0, base_h = 0;   // convolution: first output pixel of the tile as a base position
         if (CONV) {
           cpb = p.g.c8 ? 1 : p.g.C / BK;
@@ -750,25 +689,11 @@ __global__ void __launch_bounds__(TS ? 416 : (CONV ? 352 : 256), 1)
           base_w = (rem - oh * p.g.Wo) * p.g.sw - p.g.pw;
           base_h = oh * p.g.sh - p.g.ph;
         }
-        if (CONV && p.g.im2col && p.g.l2_ahead && warp == 0 && tile + static_cast<int>(gridDim.x) < n_tiles) {
-          // The first read of a pixel comes from DRAM (measured 3-4 us to the barrier, 1.4 us for the
-          // later taps that find it in L2), and the ring holds only a few k-blocks: ask for the next
-          // tile's pixels now.  One box per filter row and channel block covers every tap's pixels
-          // up to a column or two at the row ends.
-          const int nt = tile + gridDim.x, nm0 = tile_m(nt) * BM;
-          const int nimg = nm0 / (p.g.Ho * p.g.Wo), nrem = nm0 - nimg * (p.g.Ho * p.g.Wo), noh = nrem / p.g.Wo;
-          const int nw = (nrem - noh * p.g.Wo) * p.g.sw - p.g.pw, nh = noh * p.g.sh - p.g.ph;
-          const int cblocks = p.g.c8 ? 1 : p.g.C / BK;
-          for (int r = 0; r < p.g.KH; ++r)
-            for (int cb2 = 0; cb2 < cblocks; ++cb2) tc5::tma_prefetch_im2col_4d(&map_a, cb2 * BK, nw, nh, nimg, p.g.KW / 2, r);
-        }
         for (int kb = 0; kb < KB; ++kb, ++it, rp.next(ST)) {
           const int s = rp.s;
           if (p.a2 && (it & 1) != mine) continue;
           if (!tc5::mbar_wait(&empty_bar[s], rp.ph ^ 1u)) { failed = 1; atomicExch(&g_tc5_error, 11); break; }
-          TC5P_KB(0, ti, kb);
           if (CONV && !p.g.im2col) continue;   // gather variant: warps 6-9 fill the A tile
-          if (TC5_ABL(16)) { mbar_arrive(&full_bar[s]); continue; }
           tc5::mbar_arrive_expect_tx(&full_bar[s], A_STAGE);
           if (CONV && p.g.c8) {
             // 8-channel input: k-block = 8 filter taps, each a [128 pixels][16 B] box.  Taps past the
@@ -810,12 +735,8 @@ __global__ void __launch_bounds__(TS ? 416 : (CONV ? 352 : 256), 1)
           const int n0 = tile_n(tile) * BN;
           if (n0 == cur_n0) continue;
           if (loads > 0 && !tc5::mbar_wait(&w_empty, (loads - 1) & 1)) { failed = 1; atomicExch(&g_tc5_error, 19); break; }
-          if (!TC5_ABL(32)) {
-            tc5::mbar_arrive_expect_tx(&w_full, KB * B_STAGE);
-            for (int kb = 0; kb < KB; ++kb) load_w(wres + kb * B_STAGE, &w_full, kb, n0);
-          } else {
-            mbar_arrive(&w_full);
-          }
+          tc5::mbar_arrive_expect_tx(&w_full, KB * B_STAGE);
+          for (int kb = 0; kb < KB; ++kb) load_w(wres + kb * B_STAGE, &w_full, kb, n0);
           cur_n0 = n0;
           ++loads;
         }
@@ -828,7 +749,6 @@ __global__ void __launch_bounds__(TS ? 416 : (CONV ? 352 : 256), 1)
           for (int kb = 0; kb < KB; ++kb, ++it, rp.next(ST)) {
             const int s = rp.s;
             if (!tc5::mbar_wait(&empty_bar[s], rp.ph ^ 1u)) { failed = 1; atomicExch(&g_tc5_error, 19); break; }
-            if (TC5_ABL(32)) { mbar_arrive(&full_bar[s]); continue; }
             tc5::mbar_arrive_expect_tx(&full_bar[s], B_STAGE);
             load_w(smem + s * STAGE + A_STAGE, &full_bar[s], kb, n0);
           }
@@ -857,17 +777,15 @@ __global__ void __launch_bounds__(TS ? 416 : (CONV ? 352 : 256), 1)
         for (int kb = 0; kb < KB; ++kb, ++it, rp.next(ST)) {
           const int s = rp.s;
           if (!tc5::mbar_wait(&full_bar[s], rp.ph)) { failed = 1; atomicExch(&g_tc5_error, 13); break; }
-          TC5P_KB(1, ti, kb);
           tc5::tc_fence_after();
           const uint32_t a_addr = tc5::smem_addr(smem + s * STAGE), b_addr = WR ? tc5::smem_addr(wres + kb * B_STAGE) : a_addr + A_STAGE;
           if (CONV && p.g.c8) {   // unswizzled operands: one MMA covers two taps (2 x 16 bytes of K)
-            const uint32_t ak = p.g.c8_swap ? 128u : BM * 16u, am = p.g.c8_swap ? BM * 16u : 128u;
-            const uint32_t bk = p.g.c8_swap ? 128u : BN * 16u, bm = p.g.c8_swap ? BN * 16u : 128u;
+            const uint32_t ak = BM * 16u, am = 128u, bk = BN * 16u, bm = 128u;
 #pragma unroll
             for (int k = 0; k < BK / 16; ++k)
               tc5::umma_f16(acc, tc5::umma_desc_nosw(a_addr + k * 2 * (BM * 16), ak, am), tc5::umma_desc_nosw(b_addr + k * 2 * (BN * 16), bk, bm), idesc,
                             (kb | k) != 0);
-          } else if (!TC5_ABL(8)) {
+          } else {
             const uint64_t da = tc5::umma_desc_sw128(a_addr), db = tc5::umma_desc_sw128(b_addr);
 #pragma unroll
             for (int k = 0; k < BK / 16; ++k) tc5::umma_f16(acc, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
@@ -880,7 +798,6 @@ __global__ void __launch_bounds__(TS ? 416 : (CONV ? 352 : 256), 1)
           const int next = tile + static_cast<int>(gridDim.x);
           if (next < n_tiles && tile_n(next) * BN != n0) tc5::umma_commit(&w_empty);
         }
-        TC5P_STAMP(ti, 6);   // MMA: all k-blocks of the tile issued
       }
     }
   } else if (warp < 6 || (TS && warp >= 7 && warp < 11)) {
@@ -902,14 +819,12 @@ __global__ void __launch_bounds__(TS ? 416 : (CONV ? 352 : 256), 1)
       tc5::tc_fence_after();
       const int64_t m = static_cast<int64_t>(m0) + q * 32 + lane;
       const uint32_t t_row = tmem_base + b * BN + (static_cast<uint32_t>(q * 32) << 16);
-      if (warp == 2 && lane == 0) TC5P_STAMP(ti, 0);   // accumulator ready
       if (TS) {
         const int cb = ti % NCB, u = ti / NCB;
         bool okc = true;   // residual landed / buffer free
         if (lane == 0) okc = p.residual ? tc5::mbar_wait(&c_full[cb], u & 1) : tc5::mbar_wait(&c_free[cb], (u & 1) ^ 1);
         okc = __shfl_sync(0xffffffffu, okc ? 1 : 0, 0) != 0;
         if (!okc) { if (lane == 0) { failed = 1; atomicExch(&g_tc5_error, 17); } break; }
-        if (warp == 2 && lane == 0) TC5P_STAMP(ti, 1);   // C buffer ready
         const int r = q * 32 + lane, swz = r & 7;
         const uint32_t crow = tc5::smem_addr(cbuf + cb * CB) + r * 128;
         const bool relu = (p.epilogue & B200_EPI_RELU) != 0, has_res = p.residual != nullptr;
@@ -918,8 +833,7 @@ __global__ void __launch_bounds__(TS ? 416 : (CONV ? 352 : 256), 1)
         const bool bias_f32_vec = p.bias && p.bias_dtype == B200_F32 && (reinterpret_cast<uintptr_t>(p.bias) & 15u) == 0 && (n0 & 3) == 0;
         auto unit = [&](float (&v)[16], int c) {
           const int64_t n = static_cast<int64_t>(n0) + c;
-          if (TC5_ABL(64)) {
-          } else if (bias_f32_vec && n + 16 <= p.N) {
+          if (bias_f32_vec && n + 16 <= p.N) {
             const float4* bp = reinterpret_cast<const float4*>(static_cast<const float*>(p.bias) + n);
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -935,7 +849,7 @@ __global__ void __launch_bounds__(TS ? 416 : (CONV ? 352 : 256), 1)
           uint32_t o[8];
 #pragma unroll
           for (int i = 0; i < 8; ++i) o[i] = pack2<T>(v[2 * i], v[2 * i + 1]);
-          if (has_res && !TC5_ABL(128)) {
+          if (has_res) {
             uint32_t r[8];
             asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a0));
             asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]) : "r"(a1));
@@ -946,26 +860,24 @@ __global__ void __launch_bounds__(TS ? 416 : (CONV ? 352 : 256), 1)
 #pragma unroll
             for (int i = 0; i < 8; ++i) o[i] = relu2<T>(o[i]);
           }
-          if (TC5_ABL(256)) return;
           asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a0), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
           asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a1), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]) : "memory");
         };
         float va[16], vb[16];   // two units in flight: the next tcgen05.ld runs under the current unit's math
         __syncwarp();
-        if (!TC5_ABL(1)) tc5::tmem_ld_32x16(t_row + c_begin, va);
+        tc5::tmem_ld_32x16(t_row + c_begin, va);
 #pragma unroll 1
-        for (int c = c_begin; c < c_end && !TC5_ABL(1); c += 32) {
+        for (int c = c_begin; c < c_end; c += 32) {
           tc5::tmem_ld_wait();
-          if (!TC5_ABL(512)) tc5::tmem_ld_32x16(t_row + c + 16, vb);
+          tc5::tmem_ld_32x16(t_row + c + 16, vb);
           unit(va, c);
           tc5::tmem_ld_wait();
-          if (c + 32 < c_end && !TC5_ABL(512)) tc5::tmem_ld_32x16(t_row + c + 32, va);
+          if (c + 32 < c_end) tc5::tmem_ld_32x16(t_row + c + 32, va);
           unit(vb, c + 16);
         }
         tc5::fence_proxy_async();   // the TMA store reads these generic-proxy writes
         __syncwarp();
         if (lane == 0) mbar_arrive(&c_ready[cb]);
-        if (warp == 2 && lane == 0) TC5P_STAMP(ti, 2);   // tile written to the C buffer
       } else if (glu) {
 #pragma unroll 1
         for (int c = 0; c < BN / 2; c += 16) {   // c counts gate columns: block h = c / 64 of 128 merged columns
@@ -1015,14 +927,12 @@ __global__ void __launch_bounds__(TS ? 416 : (CONV ? 352 : 256), 1)
         const int m0 = tile_m(tile) * BM, n0 = tile_n(tile) * BN;
         const int cb = ti % NCB, u = ti / NCB;
         if (!tc5::mbar_wait(&c_ready[cb], u & 1)) { failed = 1; atomicExch(&g_tc5_error, 18); break; }
-        TC5P_STAMP(ti, 3);   // store thread: buffer complete
         for (int j = 0; j < BN / 64; ++j)
-          if (n0 + 64 * j < p.N && !TC5_ABL(4)) tc5::tma_store_2d(&map_o, cbuf + cb * CB + j * (BM * 128), n0 + 64 * j, m0);
+          if (n0 + 64 * j < p.N) tc5::tma_store_2d(&map_o, cbuf + cb * CB + j * (BM * 128), n0 + 64 * j, m0);
         tc5::tma_store_commit();
         tc5::tma_store_wait_read();
         if (!has_res) mbar_arrive(&c_free[cb]);
         else if (res_issued < my_tiles) load_residual(res_issued++);   // == ti + NCB
-        TC5P_STAMP(ti, 4);   // store thread: buffer read out
       }
       if (dead())   // wait (bounded) for residual copies still in flight
         for (int i = res_issued > NCB ? res_issued - NCB : 0; i < res_issued; ++i) tc5::mbar_wait(&c_full[i % NCB], (i / NCB) & 1, 1u << 16);
@@ -1313,31 +1223,13 @@ EncodeIm2colFn encode_im2col_fn() {
   return fn;
 }
 
-int conv_l2_ahead() {   // B200NN_CONV_L2_AHEAD=1: L2 prefetch of the next tile's pixels (measured: no gain, off by default)
-  static int v = -1;
-  if (v < 0) {
-    const char* e = getenv("B200NN_CONV_L2_AHEAD");
-    v = (e && e[0] == '1') ? 1 : 0;
-  }
-  return v;
-}
-
-bool conv_im2col_enabled() {
-  static int v = -1;
-  if (v < 0) {
-    const char* e = getenv("B200NN_CONV_IM2COL");
-    v = (e && e[0] == '0') ? 0 : 1;
-  }
-  return v == 1;
-}
-
 // NHWC activations [N, H, W, C] as an im2col-mode map: 64 channels x 128 output positions per
 // load, 128-byte swizzle, zero fill outside the image.  The bounding box of base positions runs
 // from -pad to (size - 1) + pad - (filter - 1) in each spatial dimension and is walked with the
 // convolution stride, so consecutive positions are consecutive output pixels.
 bool make_im2col_map(CUtensorMap* map, const void* x, const Tc5Conv& g, int dtype) {
   EncodeIm2colFn fn = encode_im2col_fn();
-  if (!fn || !conv_im2col_enabled() || g.batch <= 0) return false;
+  if (!fn || g.batch <= 0) return false;
   if (g.ph > 127 || g.pw > 127 || g.KH > 128 || g.KW > 128 || g.sh > 8 || g.sw > 8) return false;
   const cuuint64_t dims[4] = {static_cast<cuuint64_t>(g.C), static_cast<cuuint64_t>(g.W), static_cast<cuuint64_t>(g.H), static_cast<cuuint64_t>(g.batch)};
   const cuuint64_t strides[3] = {static_cast<cuuint64_t>(g.C) * 2, static_cast<cuuint64_t>(g.W) * g.C * 2, static_cast<cuuint64_t>(g.H) * g.W * g.C * 2};
@@ -1364,7 +1256,7 @@ bool make_map_c8(CUtensorMap* map, const void* w, int64_t rows, int64_t K, int64
 
 bool make_im2col_map_c8(CUtensorMap* map, const void* x, const Tc5Conv& g, int dtype) {
   EncodeIm2colFn fn = encode_im2col_fn();
-  if (!fn || !conv_im2col_enabled() || g.batch <= 0 || g.C != 8) return false;
+  if (!fn || g.batch <= 0 || g.C != 8) return false;
   if (g.ph > 127 || g.pw > 127 || g.KH > 128 || g.KW > 128 || g.sh > 8 || g.sw > 8) return false;
   const cuuint64_t dims[4] = {8, static_cast<cuuint64_t>(g.W), static_cast<cuuint64_t>(g.H), static_cast<cuuint64_t>(g.batch)};
   const cuuint64_t strides[3] = {16, static_cast<cuuint64_t>(g.W) * 16, static_cast<cuuint64_t>(g.H) * g.W * 16};
@@ -1390,10 +1282,10 @@ Tc5Plan plan_for_bn(int bn, int64_t M, int64_t N, int64_t K) {
   int64_t splits = 1;
   if (tiles < 100) {
     // a split-K CTA carries ring + receive buffer, so one fits per SM: never more CTAs than SMs
-    splits = split_target() / tiles;
-    const int64_t by_traffic = K / (split_traffic_div() * (M < BM ? M : BM));   // partial sums stay below the weight bytes
+    splits = SPLIT_TARGET_CTAS / tiles;
+    const int64_t by_traffic = K / (SPLIT_TRAFFIC_DIV * (M < BM ? M : BM));   // partial sums stay below the weight bytes
     if (splits > by_traffic) splits = by_traffic;
-    if (splits > KB / split_min_kb()) splits = KB / split_min_kb();             // at least this many k-blocks per CTA
+    if (splits > KB / SPLIT_MIN_KB) splits = KB / SPLIT_MIN_KB;             // at least this many k-blocks per CTA
     if (splits > MAX_SPLITS) splits = MAX_SPLITS;   // the splits of a tile form one thread-block cluster
     if (splits < 1) splits = 1;
   }
@@ -1406,7 +1298,7 @@ Tc5Plan plan_tc5(int64_t M, int64_t N, int64_t K, bool glu = false) {
   const int64_t tm = ceil_div(M, BM);
   if (glu) return plan_for_bn(128, M, N, K);   // the gated epilogue pairs columns c and c+64 of a 128-wide tile
   if (ceil_div(N, 128) * tm >= 148) return plan_for_bn(128, M, N, K);   // enough 128-wide tiles for every SM
-  if (tm >= 2 || prefer_bn128()) {
+  if (tm >= 2) {
     // Too few wide tiles: either 64-wide tiles or wide tiles with split-K.  Take the wide ones when
     // split-K can still put (nearly) as many CTAs to work - they re-read the activations half as often.
     const Tc5Plan wide = plan_for_bn(128, M, N, K), narrow = plan_for_bn(64, M, N, K);
@@ -1474,10 +1366,6 @@ int launch(const Tc5Args& a, const Tc5Plan& plan, cudaStream_t st, const Tc5Conv
   p.bias_dtype = a.bias_dtype; p.epilogue = a.epilogue; p.splits = pl.splits; p.kb_per_split = pl.kb_per_split;
   p.norm_eps = a.norm_eps; p.sumsq_in = a.sumsq_in; p.sumsq_in_cols = a.sumsq_in_cols; p.sumsq_out = a.sumsq_out;
   if ((a.sumsq_in || a.sumsq_out) && (CONV || MODE < 2)) return B200_ENOTSUP;
-  p.trace_slot = 0;
-#ifdef B200NN_TC5_TRACE
-  p.trace_slot = g_trace_counter++ % TR_SLOTS;
-#endif
   if (CONV && pl.splits != 1) return B200_ENOTSUP;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(pl.tiles_n), static_cast<unsigned>(pl.tiles_m), static_cast<unsigned>(pl.splits));
@@ -1505,32 +1393,10 @@ int launch(const Tc5Args& a, const Tc5Plan& plan, cudaStream_t st, const Tc5Conv
   return B200_OK;
 }
 
-// Resident weight tiles in the persistent kernel (B200NN_TC5_W_RESIDENT=0 turns them off).
-bool weights_resident_enabled() {
-  static int enabled = -1;
-  if (enabled < 0) {
-    const char* e = getenv("B200NN_TC5_W_RESIDENT");
-    enabled = (e && e[0] == '0') ? 0 : 1;
-  }
-  return enabled == 1;
-}
-
-// Column-fastest tile order for reductions up to this length (B200NN_TC5_COLUMN_FASTEST=<K>, 0 turns it off).
-int column_fastest_max_k() {
-  static int v = env_int("B200NN_TC5_COLUMN_FASTEST", 256);
-  return v;
-}
-
-// Two activation producer threads in the persistent kernel: B200NN_TC5_A2 = 0 never, 1 for
-// convolutions (default), 2 for linear layers too.
-bool two_a_producers(bool conv) {
-  static int mode = -1;
-  if (mode < 0) {
-    const char* e = getenv("B200NN_TC5_A2");
-    mode = e && e[0] ? atoi(e) : 1;
-  }
-  return mode >= 2 || (mode == 1 && conv);
-}
+// Persistent-kernel choices settled by measurement on ResNet-50 at batch 256 and Qwen prefill:
+// column tiles fastest for reductions up to K = 256, a second activation producer thread for
+// convolutions only, weight tiles resident whenever they fit.
+constexpr int COLUMN_FASTEST_MAX_K = 256;
 
 template <typename T, int BN, bool CONV, bool TS>
 int launch_persistent(const Tc5Args& a, cudaStream_t st, const Tc5Conv* g = nullptr) {
@@ -1554,7 +1420,6 @@ int launch_persistent(const Tc5Args& a, cudaStream_t st, const Tc5Conv* g = null
     return B200_ENOTSUP;
   } else if (CONV) {
     p.g.im2col = make_im2col_map(&ma, a.A, p.g, a.dtype) ? 1 : 0;
-    p.g.l2_ahead = conv_l2_ahead();
     if (!p.g.im2col) {
       if (TS) return B200_ENOTSUP;   // warp 6 cannot both gather and store
       ma = mw;
@@ -1572,25 +1437,21 @@ int launch_persistent(const Tc5Args& a, cudaStream_t st, const Tc5Conv* g = null
   p.bias_dtype = a.bias_dtype; p.epilogue = a.epilogue; p.splits = 1; p.kb_per_split = static_cast<int>(ceil_div(a.K, BK));
   p.sumsq_in = nullptr; p.sumsq_out = nullptr; p.norm_eps = 0.f; p.sumsq_in_cols = 0;
   p.x = a.A;
-  p.trace_slot = 0;
-#ifdef B200NN_TC5_ABLATE
-  { const char* e = getenv("B200NN_TC5P_ABLATE"); p.trace_slot = e ? atoi(e) : 0; }
-#endif
   const int64_t tiles_m = ceil_div(a.M, BM), tiles = tiles_m * ceil_div(a.N, BN);
   if (tiles >= (1ll << 31)) return B200_ENOTSUP;
   int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
   const int64_t tiles_n = ceil_div(a.N, BN);
   p.nfast = 0;
-  if (a.K <= column_fastest_max_k() && tiles_n > 1 && tiles_n <= grid / 4 && tiles >= 2 * grid) {
+  if (a.K <= COLUMN_FASTEST_MAX_K && tiles_n > 1 && tiles_n <= grid / 4 && tiles >= 2 * grid) {
     p.nfast = 1;
     grid -= grid % static_cast<int>(tiles_n);   // every CTA stays on one column tile
   }
-  p.a2 = two_a_producers(CONV) && (!CONV || p.g.im2col) && ceil_div(a.K, BK) >= 2 ? 1 : 0;
+  p.a2 = CONV && p.g.im2col && ceil_div(a.K, BK) >= 2 ? 1 : 0;
   // shared-memory plan
   p.pst = PC::ST; p.pstage = PC::STAGE; p.wr = 0; p.w_off = 0; p.pncb = TS ? PC::NCB : 1; p.c_off = PC::ST * PC::STAGE;
   int SMEM = PC::SMEM;
   const int64_t w_bytes = ceil_div(a.K, BK) * PC::B_STAGE;
-  if (weights_resident_enabled() && (!CONV || p.g.im2col) && w_bytes <= 96 * 1024 && tiles >= 2 * grid) {
+  if ((!CONV || p.g.im2col) && w_bytes <= 96 * 1024 && tiles >= 2 * grid) {
     const int avail = PC::SMEM_LIMIT - 1024 - static_cast<int>(w_bytes);
     for (int stages = (a.K <= BK ? 4 : 6); stages >= 4; stages -= 2) {
       const int left = avail - stages * PC::A_STAGE;
@@ -1611,13 +1472,8 @@ int launch_persistent(const Tc5Args& a, cudaStream_t st, const Tc5Conv* g = null
 // Tile width of the persistent kernel for a shape, or 0 when the shape should stay on the
 // one-tile-per-CTA kernel (too few tiles to fill the SMs with wide tiles).
 int persistent_bn(int64_t M, int64_t N, int64_t K, bool glu, bool residual) {
-  static int enabled = -1;
-  if (enabled < 0) {
-    const char* e = getenv("B200NN_TC5_PERSISTENT");
-    enabled = (e && e[0] == '0') ? 0 : 1;
-  }
   const int64_t tm = ceil_div(M, BM);
-  if (!enabled || tm < 2) return 0;
+  if (tm < 2) return 0;
   // short reductions are memory-bound: 128-wide tiles leave room for two C buffers (see PCfg)
   // (a tile wider than N only multiplies and copies padding: 64 output channels take 64-wide tiles)
   if (K > 512 && N > 128 && ceil_div(N, 256) * tm >= 2 * 148) return 256;
@@ -1625,8 +1481,7 @@ int persistent_bn(int64_t M, int64_t N, int64_t K, bool glu, bool residual) {
   // column tile reads its activation tile from DRAM again: a 256-wide tile halves those reads.  It pays
   // where two C buffers still fit beside the resident weights (K <= 64: 1x1 expansions 64 -> 256 went from
   // 0.78 to 0.91 of their HBM time) or where no residual tile has to be prefetched into the one buffer.
-  static const int wide_short = env_int("B200NN_TC5_WIDE_SHORT", 1);
-  if (wide_short && N >= 256 && (K <= 64 || (K <= 256 && !residual)) && ceil_div(N, 256) * tm >= 2 * 148) return 256;
+  if (N >= 256 && (K <= 64 || (K <= 256 && !residual)) && ceil_div(N, 256) * tm >= 2 * 148) return 256;
   if ((N > 64 || glu) && ceil_div(N, 128) * tm >= 148) return 128;
   if (!glu && ceil_div(N, 64) * tm >= 148) return 64;
   return 0;
@@ -1634,12 +1489,7 @@ int persistent_bn(int64_t M, int64_t N, int64_t K, bool glu, bool residual) {
 
 // The bulk-copy epilogue handles 16-bit outputs with bias, residual and ReLU.
 bool tma_store_ok(const Tc5Args& a) {
-  static int enabled = -1;
-  if (enabled < 0) {
-    const char* e = getenv("B200NN_TC5_TMA_STORE");
-    enabled = (e && e[0] == '0') ? 0 : 1;
-  }
-  if (!enabled || (a.epilogue & (B200_EPI_GLU | B200_EPI_SILU_MUL))) return false;
+  if (a.epilogue & (B200_EPI_GLU | B200_EPI_SILU_MUL)) return false;
   if (a.K > 2048) return false;   // long reductions hide the plain epilogue and prefer the deeper ring
   if (!aligned16(a.out) || a.ldo % 8 || a.N % 8) return false;
   if (a.residual && (!aligned16(a.residual) || a.ldr % 8)) return false;
@@ -1663,15 +1513,10 @@ template <bool CONV> int dispatch_persistent(int bn, const Tc5Args& a, cudaStrea
 }
 
 // The stem kernel takes 7-wide filters with stride 2 and padding 3 along W on an 8-channel input whose
-// output rows fit one tile (Wo <= 128); B200NN_CONV_STEM_ROWS=0 sends the stem through the im2col path.
+// output rows fit one tile (Wo <= 128); other stems go through the im2col path.
 template <typename T>
 int launch_stem_rows(const Tc5Args& a, const Tc5Conv& g, cudaStream_t st) {
-  static int enabled = -1;
-  if (enabled < 0) {
-    const char* e = getenv("B200NN_CONV_STEM_ROWS");
-    enabled = (e && e[0] == '0') ? 0 : 1;
-  }
-  if (!enabled || g.C != 8 || g.KW != 7 || g.sw != 2 || g.pw != 3 || g.sh != 2 || g.KH < 1 || g.KH > 8 || g.Wo > BM || g.W > 256 ||
+  if (g.C != 8 || g.KW != 7 || g.sw != 2 || g.pw != 3 || g.sh != 2 || g.KH < 1 || g.KH > 8 || g.Wo > BM || g.W > 256 ||
       g.Wo != (g.W + 2 * g.pw - g.KW) / g.sw + 1 || g.batch <= 0 || a.residual || a.N > STEM_BN || a.N % 8 ||
       a.K != static_cast<int64_t>(g.KH) * g.KW * 8 || a.ldw % 8 || !aligned16(a.A) || !aligned16(a.W) || !tma_store_ok(a))
     return B200_ENOTSUP;
@@ -1733,10 +1578,6 @@ int linear_tc5(const Tc5Args& a, cudaStream_t st) {
   if (const int bn = persistent_bn(a.M, a.N, a.K, glu, a.residual != nullptr)) return dispatch_persistent<false>(bn, a, st, nullptr);
   const Tc5Plan pl = plan_tc5(a.M, a.N, a.K, glu);
   if (pl.tiles_m > 65535 || pl.splits > 65535) return B200_ENOTSUP;
-  if (pl.tiles_m == 1 && a.M <= 64 && decode_deep()) {
-    if (a.dtype == B200_BF16) return pl.bn == 64 ? launch<__nv_bfloat16, 64, false, 3>(a, pl, st) : launch<__nv_bfloat16, 128, false, 3>(a, pl, st);
-    return pl.bn == 64 ? launch<__half, 64, false, 3>(a, pl, st) : launch<__half, 128, false, 3>(a, pl, st);
-  }
   if (pl.tiles_m == 1 && a.M <= 64) {
     if (a.dtype == B200_BF16) return pl.bn == 64 ? launch<__nv_bfloat16, 64, false, 2>(a, pl, st) : launch<__nv_bfloat16, 128, false, 2>(a, pl, st);
     return pl.bn == 64 ? launch<__half, 64, false, 2>(a, pl, st) : launch<__half, 128, false, 2>(a, pl, st);
@@ -1762,18 +1603,11 @@ int conv_tc5(const Tc5Args& a, const Tc5Conv& g, cudaStream_t st) {
     if (rc != B200_ENOTSUP) return rc;
   }
   if (g.C == 8) {   // stem convolution on the padded RGB input: persistent kernel, 64-wide tiles, bulk-copy epilogue
-    static int c8_mode = -1;   // B200NN_CONV_C8: 0 off, 1 on, 2 on with the descriptor offsets exchanged
-    if (c8_mode < 0) {
-      const char* e = getenv("B200NN_CONV_C8");
-      c8_mode = e && e[0] ? atoi(e) : 1;
-    }
-    if (!c8_mode || a.K != static_cast<int64_t>(g.KH) * g.KW * 8 || a.ldw % 8 || !aligned16(a.A) || !aligned16(a.W) || a.N > 64 || a.N % 8 ||
+    if (a.K != static_cast<int64_t>(g.KH) * g.KW * 8 || a.ldw % 8 || !aligned16(a.A) || !aligned16(a.W) || a.N > 64 || a.N % 8 ||
         a.M < 2 * BM || !tma_store_ok(a))
       return B200_ENOTSUP;
     Tc5Conv g8 = g;
-    g8.l2_ahead = conv_l2_ahead();
     g8.c8 = 1;
-    g8.c8_swap = c8_mode == 2;
     return a.dtype == B200_BF16 ? launch_persistent<__nv_bfloat16, 64, true, true>(a, st, &g8) : launch_persistent<__half, 64, true, true>(a, st, &g8);
   }
   if (g.C % BK || a.K != static_cast<int64_t>(g.KH) * g.KW * g.C || a.ldw % 8 || !aligned16(a.A) || !aligned16(a.W)) return B200_ENOTSUP;
@@ -1790,18 +1624,6 @@ int conv_tc5(const Tc5Args& a, const Tc5Conv& g, cudaStream_t st) {
 }
 
 }  // namespace b200
-
-#ifdef B200NN_TC5_TRACE
-extern "C" int b200_debug_tc5p_kb(unsigned long long* host_out) {
-  return cudaMemcpyFromSymbol(host_out, b200::g_tc5p_kb, sizeof(unsigned long long) * 2 * b200::PTR_CTAS * b200::PTR_TILES * b200::PTR_N) == cudaSuccess ? B200_OK : B200_ELAUNCH;
-}
-extern "C" int b200_debug_tc5p_trace(unsigned long long* host_out) {
-  return cudaMemcpyFromSymbol(host_out, b200::g_tc5p_trace, sizeof(unsigned long long) * b200::PTR_CTAS * b200::PTR_TILES * b200::PTR_N) == cudaSuccess ? B200_OK : B200_ELAUNCH;
-}
-extern "C" int b200_debug_tc5_trace(unsigned long long* host_out) {
-  return cudaMemcpyFromSymbol(host_out, b200::g_tc5_trace, sizeof(unsigned long long) * b200::TR_SLOTS * b200::TR_CTAS * b200::TR_N) == cudaSuccess ? B200_OK : B200_ELAUNCH;
-}
-#endif
 
 extern "C" int b200_debug_device_error(int* code, int clear) {
   int v = 0;

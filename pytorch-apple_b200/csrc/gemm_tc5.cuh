@@ -27,9 +27,7 @@ struct Tc5Conv {
   int H, W, C, KH, KW, sh, sw, ph, pw, Ho, Wo;
   int batch = 0;    // images
   int im2col = 0;   // set by conv_tc5: the A tile comes from an im2col-mode tensor map (else gathered by threads)
-  int l2_ahead = 0; // persistent kernel: prefetch the next tile's pixels into L2
   int c8 = 0;       // 8-channel input (the padded RGB stem): one filter tap per 16-byte K chunk, unswizzled operands
-  int c8_swap = 0;  // debugging switch: exchange the two byte offsets of the unswizzled descriptors
 };
 
 // y = epi(conv(x, w) + bias + residual) on the tcgen05 path; needs C % 64 == 0, or C == 8

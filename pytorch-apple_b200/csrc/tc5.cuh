@@ -70,11 +70,6 @@ __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk
 // all committed stores have finished READING shared memory (the buffers may be overwritten)
 __device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-// Same addressing as tma_load_im2col_4d, but the box is only brought into L2 (no shared memory, no barrier).
-__device__ __forceinline__ void tma_prefetch_im2col_4d(const CUtensorMap* map, int c, int w, int h, int n, int off_w, int off_h) {
-  asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.im2col [%0, {%1, %2, %3, %4}], {%5, %6};"
-               ::"l"(map), "r"(c), "r"(w), "r"(h), "r"(n), "h"(static_cast<unsigned short>(off_w)), "h"(static_cast<unsigned short>(off_h)) : "memory");
-}
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }

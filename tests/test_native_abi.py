@@ -33,7 +33,8 @@ def test_host_only_entry_points(native_lib):
     assert native_lib.b200_linear_workspace_bytes(1, 1536, 1536) > 0
     assert native_lib.b200_linear_workspace_bytes(512, 1536, 1536) == 0
     assert native_lib.b200_attn_decode_workspace_bytes(64, 12, 2, 4352, 128) == 0   # the splits merge inside the kernel
-    assert native_lib.b200_attn_decode_workspace_bytes(64, 12, 2, 8192, 128) == 64 * 2 * 16 * 6 * 130 * 4   # long cache: 512-key splits + merge kernel
+    assert native_lib.b200_attn_decode_workspace_bytes(64, 12, 2, 8192, 128) == 0      # up to 16384 rows likewise
+    assert native_lib.b200_attn_decode_workspace_bytes(64, 12, 2, 32768, 128) == 64 * 2 * 64 * 6 * 130 * 4   # longer caches: 512-key splits + merge kernel
 
 
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):
