@@ -4,6 +4,8 @@
 // probabilities are rounded to the activation dtype for the second MMA, as the unfused graph
 // rounds them.  Two kernels: prefill (64 query rows per CTA) and split-KV decode (one query
 // token, the query heads of a KV group on the N side of the MMA).
+#include "attention.cuh"
+#include "gemm_tc5.cuh"
 #include "mma.cuh"
 #include "tc5.cuh"
 
@@ -342,16 +344,6 @@ __global__ void __launch_bounds__(128) attn_decode_merge_kernel(const float* __r
 // ===========================================================================
 // Prefill: grid = (ceil(T/64), Hq, B), 4 warps x 16 query rows, all keys streamed.
 // ===========================================================================
-struct PrefillParams {
-  const void* q; const void* k; const void* v; const void* mask; void* out;
-  int64_t B, T, S;
-  int Hq, Hkv;
-  int64_t qs[3], ks[3], vs[3];
-  int64_t mask_b, mask_t;
-  float scale;
-  int mask_dtype;
-  int mask_staged;   // the mask can travel through shared memory (activation dtype, 16-byte-aligned rows)
-};
 
 constexpr int PF_BK = 64;                              // keys per shared-memory tile
 constexpr int PF_KV_BYTES = 2 * PF_BK * HD * 2;        // K tile + V tile
@@ -704,8 +696,13 @@ extern "C" int b200_attn_prefill(const void* q, const void* k, const void* v, co
   for (int i = 0; i < 3; ++i) { p.qs[i] = q_strides[i]; p.ks[i] = k_strides[i]; p.vs[i] = v_strides[i]; }
   p.mask_b = mask_b; p.mask_t = mask_t; p.scale = scale; p.mask_dtype = dtype;
   p.mask_staged = (mask && aligned16(mask) && mask_b % 8 == 0 && mask_t % 8 == 0 && S % 8 == 0) ? 1 : 0;   // mask dtype == activation dtype by contract
-  dim3 grid(static_cast<unsigned>(ceil_div(T, 64)), static_cast<unsigned>(Hq), static_cast<unsigned>(B));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (tc5_enabled()) {   // tcgen05 kernel first; the mma.sync kernel below takes what it cannot (odd strides, other mask types)
+    const int rc = attn_prefill_tc5(p, dtype, st);
+    if (rc == B200_ELAUNCH) B200_FAIL(B200_ELAUNCH, "attn_prefill_tc5_kernel: launch failed");
+    if (rc != B200_ENOTSUP) return rc;
+  }
+  dim3 grid(static_cast<unsigned>(ceil_div(T, 64)), static_cast<unsigned>(Hq), static_cast<unsigned>(B));
   B200_DISPATCH_HALF(dtype, T_, {
     static bool configured = false;
     if (!configured) {

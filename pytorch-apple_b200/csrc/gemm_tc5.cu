@@ -10,6 +10,7 @@
 // accumulator back with tcgen05.ld (each warp owns the 32 TMEM lanes of its quarter),
 // apply the epilogue in fp32 and store.  Every barrier wait is bounded: on a timeout the
 // CTA records an error code in `g_tc5_error`, drains its own copies and exits.
+#include "attention.cuh"
 #include "gemm_tc5.cuh"
 #include "mma.cuh"
 #include "tc5.cuh"
@@ -1205,6 +1206,25 @@ bool make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t K, int64
             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+}  // namespace
+
+// Tiled tensor map of up to five dimensions with a 128-byte swizzle (dims / box innermost first,
+// strides in bytes for dimensions 1..rank-1).  Used by kernels outside this file.
+bool tma_encode_sw128(CUtensorMap* map, int dtype, int rank, const void* base, const uint64_t* dims, const uint64_t* strides_bytes,
+                      const uint32_t* box) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn || rank < 1 || rank > 5) return false;
+  cuuint64_t d[5], st[4];
+  cuuint32_t bx[5], es[5];
+  for (int i = 0; i < rank; ++i) { d[i] = dims[i]; bx[i] = box[i]; es[i] = 1; }
+  for (int i = 0; i + 1 < rank; ++i) st[i] = strides_bytes[i];
+  const CUtensorMapDataType dt = dtype == B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  return fn(map, dt, static_cast<cuuint32_t>(rank), const_cast<void*>(base), d, st, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+namespace {
+
 typedef CUresult (*EncodeIm2colFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const int*,
                                    const int*, cuuint32_t, cuuint32_t, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -1629,7 +1649,8 @@ extern "C" int b200_debug_device_error(int* code, int clear) {
   int v = 0;
   cudaError_t e = cudaMemcpyFromSymbol(&v, b200::g_tc5_error, sizeof(int));
   if (e != cudaSuccess) B200_FAIL(B200_ELAUNCH, "b200_debug_device_error: %s", cudaGetErrorString(e));
-  if (code) *code = v;
+  const int att = b200::attn_prefill_tc5_error(clear != 0);
+  if (code) *code = v ? v : (att > 0 ? att : 0);
   if (clear && v) {
     v = 0;
     cudaMemcpyToSymbol(b200::g_tc5_error, &v, sizeof(int));

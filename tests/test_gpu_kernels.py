@@ -327,7 +327,7 @@ def test_attn_decode_many_sequences_ragged_masks(lib, B, S, Hq, Hkv):
     close(out[keep], ref[keep], rtol=2e-2, atol=5e-3)
 
 
-@pytest.mark.parametrize("B,T", [(1, 512), (2, 48), (1, 100)])
+@pytest.mark.parametrize("B,T", [(1, 512), (2, 48), (1, 100), (1, 2048), (2, 328)])
 def test_attn_prefill(lib, B, T):
     import model_zoo as mz
 
@@ -338,11 +338,47 @@ def test_attn_prefill(lib, B, T):
     ref = attn_ref(q, k, v, mask, D ** -0.5, dtype).transpose(1, 2)
     Q, K, V, M = (t.cuda() for t in (q.transpose(1, 2).contiguous(), k, v.transpose(1, 2).contiguous(), mask))
     Q, V = Q.transpose(1, 2), V.transpose(1, 2)
-    out = torch.empty(B, T, Hq, D, dtype=dtype, device="cuda")
+    out = torch.full((B, T, Hq, D), float("nan"), dtype=dtype, device="cuda")
     st = lambda t: (C.c_int64 * 3)(*t.stride()[:3])
     ok(lib, lib.b200_attn_prefill(Q.data_ptr(), K.data_ptr(), V.data_ptr(), M.data_ptr(), out.data_ptr(), B, Hq, Hkv, T, T, D,
                                   st(Q), st(K), st(V), 0, T, D ** -0.5, 2, stream()))
     close(out, ref, rtol=2e-2, atol=5e-3)
+    code = C.c_int(0)
+    ok(lib, lib.b200_debug_device_error(C.byref(code), 1))
+    assert code.value == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_attn_prefill_arbitrary_masks_and_no_mask(lib, dtype):
+    """Nothing in the kernels assumes a causal mask: a per-sequence mask with windows, holes and key
+    tiles that are masked for a whole block of query rows (those tiles are skipped), S != T, and no
+    mask at all."""
+    B, T, S, Hq, Hkv, D = 2, 200, 456, 4, 2, 128
+    g = torch.Generator().manual_seed(11)
+    q, k, v = gen((B, Hq, T, D), dtype), gen((B, Hkv, S, D), dtype, 1), gen((B, Hkv, S, D), dtype, 2)
+    neg = torch.finfo(dtype).min
+    mask = torch.full((B, 1, T, S), neg, dtype=dtype)
+    for b in range(B):
+        for t in range(T):
+            lo = (37 * t + 11 * b) % 300
+            mask[b, 0, t, lo:lo + 40 + (t % 64)] = 0          # a sliding window; far tiles are fully masked
+        mask[b, 0, :, 128:192] = neg                          # one key tile masked for every row
+        mask[b, 0, :, 130 + b] = 0                            # ... except a single key
+    mask[1, 0, 150:, 192:256] = torch.where(torch.rand(T - 150, 64, generator=g) < 0.3, 0.0, neg).to(dtype)
+    ref = attn_ref(q, k, v, mask, D ** -0.5, dtype).transpose(1, 2)
+    Q, K, V, M = q.cuda(), k.cuda(), v.cuda(), mask.cuda()
+    out = torch.full((B, T, Hq, D), float("nan"), dtype=dtype, device="cuda")
+    st = lambda t: (C.c_int64 * 3)(*t.stride()[:3])
+    dt = DT[dtype]
+    ok(lib, lib.b200_attn_prefill(Q.data_ptr(), K.data_ptr(), V.data_ptr(), M.data_ptr(), out.data_ptr(), B, Hq, Hkv, T, S, D,
+                                  st(Q), st(K), st(V), T * S, S, D ** -0.5, dt, stream()))
+    close(out, ref, rtol=2e-2, atol=5e-3)
+    ok(lib, lib.b200_attn_prefill(Q.data_ptr(), K.data_ptr(), V.data_ptr(), None, out.data_ptr(), B, Hq, Hkv, T, S, D,
+                                  st(Q), st(K), st(V), 0, 0, D ** -0.5, dt, stream()))
+    close(out, attn_ref(q, k, v, None, D ** -0.5, dtype).transpose(1, 2), rtol=2e-2, atol=5e-3)
+    code = C.c_int(0)
+    ok(lib, lib.b200_debug_device_error(C.byref(code), 1))
+    assert code.value == 0
 
 
 # ------------------------------------------------------------------ bandwidth kernels
