@@ -236,6 +236,80 @@ def ops(device, hbm_gbs: float, tokens=(128, 2048, 8192)) -> dict:
     return out
 
 
+def log_scale_steps(max_steps: int) -> list[int]:
+    """1, 2, 4, ... and max_steps itself: the cache positions the reference's scaling benchmark visits
+    (benchmarks/benchmark_qwen.py:50-58)."""
+    steps, v = [], 1
+    while v < max_steps:
+        steps.append(v)
+        v *= 2
+    return steps + [max_steps]
+
+
+def decode_sweep(cfg, sd, device, prefill_len: int = 128, max_cache_len: int = 32768, repeats: int = 3) -> dict:
+    """The reference's CUDA scaling benchmark (benchmarks/benchmark_qwen.py:650-809) on this backend:
+    batch 1, a prefill graph of ``prefill_len`` tokens and a decode graph over a ``max_cache_len``-row
+    cache holding random values on the device; for each cache position 1, 2, 4, ... the time of ONE
+    decode step through ``DAGExecutor.execute`` with host inputs (ids, mask, positions uploaded every
+    call), median of ``repeats``.  One difference, on purpose: the reference reads the clock after the
+    call returns without waiting for the GPU (it times the enqueue, :788-793); here the device is
+    synchronised before the clock is read, and the device time between two CUDA events is reported too."""
+    import time
+
+    from cuda_runtime import CUDABuffer
+    from cuda_runtime.cuda_backend import torch_to_numpy
+
+    L = cfg.num_hidden_layers
+    weights = {k: CUDABuffer(v) for k, v in sd.items()}
+    ir_p = extract_ir(mz.QwenPrefillWrapper(mz.qwen2_model(cfg)), mz.qwen2_example_inputs(cfg, 1, prefill_len, None), "qwen2_prefill")
+    ir_d = extract_ir(mz.QwenDecodeWrapper(mz.qwen2_model(cfg), L), mz.qwen2_example_inputs(cfg, 1, 1, max_cache_len), "qwen2_decode")
+    dag_p, _, _ = _dag(ir_p, weights, device)
+    dag_d, _, _ = _dag(ir_d, weights, device)
+    g = torch.Generator().manual_seed(11)
+    ids = torch.randint(0, cfg.vocab_size, (1, prefill_len), generator=g)
+    pre_in = {"input_ids": ids.numpy(), "attention_mask": torch_to_numpy(mz.causal_mask(1, prefill_len, prefill_len, 0)),
+              "position_ids": np.arange(prefill_len, dtype=np.int64)[None], "cache_position": np.arange(prefill_len, dtype=np.int64)}
+
+    def timed(fn, n):
+        out = []
+        for _ in range(n):
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0 = time.perf_counter()
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            out.append(((time.perf_counter() - t0) * 1e3, a.elapsed_time(b)))
+        wall, dev = zip(*out)
+        return float(np.median(wall)), float(np.median(dev)), float(np.std(wall))
+
+    for _ in range(3):
+        dag_p.execute(pre_in)
+    ttft_ms, ttft_dev, _ = timed(lambda: dag_p.execute(pre_in), max(repeats, 7))
+    gd = torch.Generator(device=device).manual_seed(12)
+    names = [s_["name"] for s_ in ir_d["graph_inputs"]]
+    kv = {n: CUDABuffer(torch.randn(1, cfg.num_key_value_heads, max_cache_len, 128, generator=gd, device=device).bfloat16()) for n in names[4:]}
+
+    def step_inputs(cur_pos):
+        d = {"input_ids": np.array([[1]], np.int64), "attention_mask": torch_to_numpy(mz.causal_mask(1, 1, max_cache_len, cur_pos)),
+             "position_ids": np.array([[cur_pos]], np.int64), "cache_position": np.array([cur_pos], np.int64)}
+        d.update(kv)
+        return d
+
+    warm = step_inputs(prefill_len)
+    for _ in range(3):
+        dag_d.execute(warm)
+    rows = []
+    for pos in log_scale_steps(max_cache_len - prefill_len):
+        feed = step_inputs(prefill_len + pos - 1)
+        wall, dev, std = timed(lambda: dag_d.execute(feed), repeats)
+        rows.append({"position": pos, "step_ms": round(wall, 4), "step_ms_std": round(std, 4), "device_ms": round(dev, 4), "tps": round(1e3 / wall, 1)})
+    return {"protocol": f"batch 1, prefill graph {prefill_len} tokens, decode graph over a {max_cache_len}-row cache (random values), "
+                        f"median of {repeats} single steps per position, host inputs uploaded per call, device synchronised before the clock is read",
+            "layers": L, "ttft_ms": round(ttft_ms, 3), "ttft_device_ms": round(ttft_dev, 3), "points": rows}
+
+
 def run(cfg, sd, device) -> dict:
     from bench import measured_peaks
 
@@ -260,13 +334,14 @@ if __name__ == "__main__":
     #   python bench_extras.py qwen_decode --layers 2 --batch 1
     #   python bench_extras.py ops
     #   python bench_extras.py resnet50_layers --batch 256
+    #   python bench_extras.py decode_sweep            (the reference's cache-position scaling protocol)
     import argparse
     import json
 
     from bench import measured_peaks
 
     ap = argparse.ArgumentParser()
-    ap.add_argument("workload", choices=["qwen_prefill", "qwen_decode", "resnet50", "resnet50_layers", "ops"])
+    ap.add_argument("workload", choices=["qwen_prefill", "qwen_decode", "resnet50", "resnet50_layers", "ops", "decode_sweep"])
     ap.add_argument("--layers", type=int, default=28)
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--tokens", type=int, default=512)
@@ -284,6 +359,13 @@ if __name__ == "__main__":
                           "sum_roofline_us": round(sum(r["roofline_us"] * r["count"] for r in rows))}))
     elif a.workload == "resnet50":
         print(json.dumps(resnet50(dev, a.batch, tf)))
+    elif a.workload == "decode_sweep":
+        cfg = mz.qwen2_config(num_layers=a.layers)
+        sd = mz.qwen2_weights(cfg, seed=0, device=str(dev))
+        res = decode_sweep(cfg, sd, dev)
+        for row in res["points"]:
+            print(json.dumps(row))
+        print(json.dumps({k: v for k, v in res.items() if k != "points"}))
     else:
         cfg = mz.qwen2_config(num_layers=a.layers)
         sd = mz.qwen2_weights(cfg, seed=0, device=str(dev))

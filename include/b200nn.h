@@ -62,6 +62,12 @@ const char* b200_last_error(void);
  * non-zero code in a device variable when they give up instead of hanging.  Reads (and
  * optionally clears) it; this call synchronises the device. */
 int b200_debug_device_error(int* code, int clear);
+/* Self-test of the time-out path, for hosts that want to see it work: launches a one-thread
+ * kernel that waits on a barrier nobody will ever arrive at, with the library's bounded wait
+ * limited to `probes` polls.  The wait gives up, the kernel records code 99 and returns
+ * normally; b200_debug_device_error then reports 99 and the context stays usable.
+ * No counterpart in the reference (its kernels never wait on one another). */
+int b200_debug_wait_timeout(int probes, void* stream);
 /* sm count, compute capability and opt-in shared memory of device `dev`. */
 int b200_device_info(int dev, int* sm_count, int* cc_major, int* cc_minor, int64_t* smem_optin_bytes);
 

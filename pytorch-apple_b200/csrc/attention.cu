@@ -328,15 +328,19 @@ __global__ void __launch_bounds__(128) attn_decode_merge_kernel(const float* __r
   pdl_wait();
   pdl_trigger();
   const int64_t base = (b * Hkv + hk) * splits;
+  // (the loads of different splits are independent: unrolled, they overlap instead of queueing up one
+  // L2 round trip each - 256 splits of a 32768-row cache took 20 us that way)
   float m_all = -INFINITY;
-  for (int s = 0; s < splits; ++s) m_all = fmaxf(m_all, part_ml[((base + s) * G + r) * 2]);
+#pragma unroll 8
+  for (int s = 0; s < splits; ++s) m_all = fmaxf(m_all, __ldg(&part_ml[((base + s) * G + r) * 2]));
   const float m_use = m_all == -INFINITY ? 0.f : m_all;
   float acc = 0.f, l = 0.f;
+#pragma unroll 8
   for (int s = 0; s < splits; ++s) {
     const int64_t i = (base + s) * G + r;
-    const float f = ex2_approx(part_ml[i * 2] - m_use);   // maxima are stored in the log2 domain
-    l += part_ml[i * 2 + 1] * f;
-    acc += part_acc[i * HD + threadIdx.x] * f;
+    const float f = ex2_approx(__ldg(&part_ml[i * 2]) - m_use);   // maxima are stored in the log2 domain
+    l += __ldg(&part_ml[i * 2 + 1]) * f;
+    acc += __ldg(&part_acc[i * HD + threadIdx.x]) * f;
   }
   out[bh * HD + threadIdx.x] = from_f32<T>(l > 0.f ? acc / l : 0.f);
 }

@@ -1645,6 +1645,22 @@ int conv_tc5(const Tc5Args& a, const Tc5Conv& g, cudaStream_t st) {
 
 }  // namespace b200
 
+namespace b200 {
+__global__ void wait_timeout_selftest_kernel(uint32_t probes) {
+  __shared__ __align__(8) uint64_t bar;
+  tc5::mbar_init(&bar, 1);
+  tc5::fence_barrier_init();
+  if (!tc5::mbar_wait(&bar, 0, probes)) atomicExch(&g_tc5_error, 99);   // nobody arrives: the bounded wait must give up
+}
+}  // namespace b200
+
+extern "C" int b200_debug_wait_timeout(int probes, void* stream) {
+  B200_CHECK_ARG(probes > 0 && probes <= (1 << 20), "b200_debug_wait_timeout: probes must be in 1..2^20");
+  b200::wait_timeout_selftest_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<uint32_t>(probes));
+  B200_CHECK_LAUNCH("wait_timeout_selftest_kernel");
+  return B200_OK;
+}
+
 extern "C" int b200_debug_device_error(int* code, int clear) {
   int v = 0;
   cudaError_t e = cudaMemcpyFromSymbol(&v, b200::g_tc5_error, sizeof(int));

@@ -12,7 +12,10 @@ executor needs to bind the call: operand tensor names resolve through
 
 from __future__ import annotations
 
+import dataclasses
+import json
 from dataclasses import dataclass, field
+from pathlib import Path
 
 from npu_compiler.ir_reader import TensorSpec
 
@@ -145,3 +148,73 @@ class CUDAProgram:
     def kernel_calls(self):
         """Reference-compatible alias for ``steps``."""
         return self.steps
+
+    # -- serialisation ------------------------------------------------------------------
+    # The reference can store a compiled Metal program (``CompiledProgram.save / load``,
+    # npu_compiler/compiled_program.py:49-117: a JSON file tagged with format and version); its
+    # CUDA program has no such pair.  Same idea here: everything the executor needs - steps with
+    # their resolved views, the arena plan, weight preparations - as one JSON document, so that a
+    # serving process can skip export, pattern matching and planning.
+    FORMAT, VERSION = "b200prog", 1
+
+    def to_dict(self) -> dict:
+        return {"format": self.FORMAT, "version": self.VERSION, "program": _encode(self)}
+
+    def save(self, path: str) -> None:
+        Path(path).write_text(json.dumps(self.to_dict()))
+
+    @classmethod
+    def from_dict(cls, data: dict) -> "CUDAProgram":
+        if data.get("format") != cls.FORMAT:
+            raise ValueError(f"not a {cls.FORMAT} document (format = {data.get('format')!r})")
+        if data.get("version") != cls.VERSION:
+            raise ValueError(f"{cls.FORMAT} version {data.get('version')} is not supported (this build reads version {cls.VERSION})")
+        prog = _decode(data["program"])
+        if not isinstance(prog, cls):
+            raise ValueError("document does not hold a CUDAProgram")
+        return prog
+
+    @classmethod
+    def load(cls, path: str) -> "CUDAProgram":
+        return cls.from_dict(json.loads(Path(path).read_text()))
+
+
+_SERIALISABLE = {c.__name__: c for c in (TensorView, BufferAllocation, CUDAKernelSource, CUBLASStep, FusedKernelStep, ReductionKernelStep,
+                                         AliasStep, SpecialKernelStep, WeightPrep, CUDAProgram, TensorSpec)}
+
+
+def _encode(obj):
+    """JSON form of a program tree: dataclasses and tuples are tagged so that ``_decode`` restores them exactly."""
+    if dataclasses.is_dataclass(obj) and not isinstance(obj, type):
+        name = type(obj).__name__
+        if name not in _SERIALISABLE:
+            raise TypeError(f"cannot serialise {name}")
+        return {"__dc__": name, **{f.name: _encode(getattr(obj, f.name)) for f in dataclasses.fields(obj)}}
+    if isinstance(obj, tuple):
+        return {"__tuple__": [_encode(v) for v in obj]}
+    if isinstance(obj, list):
+        return [_encode(v) for v in obj]
+    if isinstance(obj, dict):
+        if not all(isinstance(k, str) for k in obj):
+            raise TypeError("only string keys can be serialised")
+        return {k: _encode(v) for k, v in obj.items()}
+    if isinstance(obj, (set, frozenset)):
+        return {"__set__": sorted(_encode(v) for v in obj)}
+    if obj is None or isinstance(obj, (bool, int, float, str)):
+        return obj
+    raise TypeError(f"cannot serialise a value of type {type(obj).__name__}")
+
+
+def _decode(obj):
+    if isinstance(obj, list):
+        return [_decode(v) for v in obj]
+    if isinstance(obj, dict):
+        if "__tuple__" in obj:
+            return tuple(_decode(v) for v in obj["__tuple__"])
+        if "__set__" in obj:
+            return set(_decode(v) for v in obj["__set__"])
+        if "__dc__" in obj:
+            cls = _SERIALISABLE[obj["__dc__"]]
+            return cls(**{k: _decode(v) for k, v in obj.items() if k != "__dc__"})
+        return {k: _decode(v) for k, v in obj.items()}
+    return obj

@@ -64,6 +64,68 @@ def torch_to_numpy(t) -> np.ndarray:
     return t.numpy()
 
 
+class PinnedStaging:
+    """Page-locked host buffers for the transfers at partition boundaries and for step inputs.
+
+    The reference moves tensors between host and device partitions with ``cp.asarray`` /
+    ``cp.asnumpy`` on pageable memory (cuda_backend.py:52-71, dag_executor.py:316-329).  Here uploads
+    go host array -> pinned buffer -> device (asynchronous, DMA at full PCIe rate) and downloads come
+    back through a pinned buffer as well.  One buffer per (dtype, element count), reused; a buffer is
+    only rewritten after the copy that last read it has finished (an event per buffer)."""
+
+    MIN_BYTES = 1 << 16   # smaller transfers are latency-bound either way
+    MAX_BYTES = 64 << 20  # larger ones (whole weight matrices at load time) are not worth keeping a pinned twin for
+
+    def __init__(self):
+        self._up: dict[tuple, tuple[Any, Any]] = {}
+        self._down: dict[tuple, Any] = {}
+        self.uploads = self.downloads = 0
+
+    def upload(self, host, dst) -> None:
+        """dst (device tensor) <- host (CPU tensor of the same dtype / element count)."""
+        nbytes = host.numel() * host.element_size()
+        if not dst.is_cuda or nbytes < self.MIN_BYTES or nbytes > self.MAX_BYTES or host.is_pinned():
+            dst.copy_(host.reshape(dst.shape), non_blocking=True)   # (a caller's own pinned array is copied straight from where it is)
+            return
+        key = (host.dtype, host.numel())
+        entry = self._up.get(key)
+        if entry is None:
+            entry = (torch.empty(host.numel(), dtype=host.dtype).pin_memory(), torch.cuda.Event())
+            self._up[key] = entry
+        else:
+            entry[1].synchronize()
+        pinned, event = entry
+        pinned.copy_(host.reshape(-1))
+        dst.copy_(pinned.view(dst.shape), non_blocking=True)
+        event.record()
+        self.uploads += 1
+
+    def download(self, src):
+        """CPU tensor holding a copy of src (device tensor, contiguous)."""
+        nbytes = src.numel() * src.element_size()
+        if not src.is_cuda or nbytes < self.MIN_BYTES or nbytes > self.MAX_BYTES:
+            return src.cpu()
+        key = (src.dtype, src.numel())
+        pinned = self._down.get(key)
+        if pinned is None:
+            pinned = torch.empty(src.numel(), dtype=src.dtype).pin_memory()
+            self._down[key] = pinned
+        pinned.copy_(src.reshape(-1), non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        self.downloads += 1
+        return pinned.view(src.shape).clone()
+
+
+_staging: PinnedStaging | None = None
+
+
+def staging() -> PinnedStaging:
+    global _staging
+    if _staging is None:
+        _staging = PinnedStaging()
+    return _staging
+
+
 def _target_dtype(data: np.ndarray, spec) -> str | None:
     """Which dtype an upload should have on the device."""
     name = getattr(spec, "dtype", None) if spec is not None else None
@@ -106,7 +168,7 @@ class CUDABuffer(DeviceBuffer):
         t = self._data.detach()
         if not t.is_contiguous():
             t = t.contiguous()
-        t = t.cpu()
+        t = staging().download(t) if t.is_cuda else t.cpu()
         if t.dtype == torch.bfloat16:
             arr = t.view(torch.uint16).numpy().view(_np_bf16())
         else:
@@ -124,7 +186,9 @@ class CUDABuffer(DeviceBuffer):
         if dtype is not None:
             target = "bfloat16" if getattr(np.dtype(dtype), "name", "") == "bfloat16" else np.dtype(dtype).name
         host = numpy_to_torch(data, target)
-        return cls(host.to(device or native.device_string(), non_blocking=True))
+        dev = torch.empty(host.shape, dtype=host.dtype, device=device or native.device_string())
+        staging().upload(host, dev)
+        return cls(dev)
 
     @classmethod
     def zeros(cls, shape: tuple[int, ...], dtype=np.dtype(np.float16), device: str | None = None) -> "CUDABuffer":
@@ -136,7 +200,7 @@ class CUDABuffer(DeviceBuffer):
         if host.dtype != self._data.dtype or tuple(host.shape) != tuple(self._data.shape):
             # first write after the fp16-zeros pre-allocation: adopt the real dtype/shape
             self._data = torch.empty(tuple(host.shape), dtype=host.dtype, device=self._data.device)
-        self._data.copy_(host, non_blocking=True)
+        staging().upload(host, self._data)
         self._logical_shape = tuple(data.shape)
 
 
@@ -162,7 +226,9 @@ class CUDABackend(Backend):
 
     def allocate_buffer(self, data: np.ndarray, alloc_shape=None, spec=None) -> CUDABuffer:
         host = numpy_to_torch(data, _target_dtype(np.asarray(data), spec))
-        return CUDABuffer(host.to(self._device, non_blocking=True))
+        dev = torch.empty(host.shape, dtype=host.dtype, device=self._device)
+        staging().upload(host, dev)
+        return CUDABuffer(dev)
 
     def allocate_zeros(self, shape, dtype=np.dtype(np.float16), alloc_shape=None) -> CUDABuffer:
         return CUDABuffer.zeros(tuple(shape), dtype=dtype, device=self._device)

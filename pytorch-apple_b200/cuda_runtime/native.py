@@ -48,6 +48,7 @@ SIGNATURES = {
     "b200_last_error": (C.c_char_p, []),
     "b200_device_info": (_i, [_i, C.POINTER(_i), C.POINTER(_i), C.POINTER(_i), C.POINTER(_i64)]),
     "b200_debug_device_error": (_i, [C.POINTER(_i), _i]),
+    "b200_debug_wait_timeout": (_i, [_i, _vp]),
     "b200_ew_chain": (_i, [_TP, _TP, _i, C.POINTER(EwOp), _i, _vp]),
     "b200_strided_copy": (_i, [_TP, _TP, _vp]),
     "b200_fill": (_i, [_vp, _i64, C.c_double, _i, _vp]),

@@ -73,6 +73,9 @@ class FakeLibrary:
     def b200_last_error(self):
         return self._err
 
+    def b200_debug_wait_timeout(self, probes, stream):
+        return 0
+
     def b200_linear_workspace_bytes(self, M, N, K):
         return 256 if M <= 128 else 0
 

@@ -206,6 +206,26 @@ def test_linear_norm_rejects_shapes_outside_the_fused_kernel(lib):
     assert lib.b200_linear_norm(*args(8, 72, 128, 1, True)) == -4                                                # N not a multiple of 64
 
 
+def test_bounded_wait_runs_out_and_the_context_survives(lib):
+    """A barrier wait that can never be satisfied: the kernel's bounded wait gives up after the probe limit,
+    leaves code 99 in the device error word and returns; the next kernels run normally."""
+    code = C.c_int(-1)
+    ok(lib, lib.b200_debug_device_error(C.byref(code), 1))
+    assert code.value == 0
+    ok(lib, lib.b200_debug_wait_timeout(2000, stream()))
+    ok(lib, lib.b200_debug_device_error(C.byref(code), 0))
+    assert code.value == 99
+    ok(lib, lib.b200_debug_device_error(C.byref(code), 1))     # reads 99 again and clears
+    ok(lib, lib.b200_debug_device_error(C.byref(code), 0))
+    assert code.value == 0
+    a, w = gen((4, 256)), gen((128, 256), seed=1)
+    out = torch.empty(4, 128, dtype=torch.bfloat16, device="cuda")
+    A, W = a.cuda(), w.cuda()
+    ok(lib, lib.b200_linear(A.data_ptr(), W.data_ptr(), None, None, out.data_ptr(), 4, 128, 256, 256, 256, 128, 0, 2, 2, 0, None, 0, None, 0, stream()))
+    close(out, a.float() @ w.float().T, rtol=2e-2, atol=2e-2)
+    assert lib.b200_debug_wait_timeout(0, stream()) == -1
+
+
 def test_linear_rejects_unaligned(lib):
     a = torch.zeros(4, 12, dtype=torch.bfloat16, device="cuda")
     rc = lib.b200_linear(a.data_ptr(), a.data_ptr(), None, None, a.data_ptr(), 4, 4, 12, 12, 12, 4, 0, 2, 2, 0, None, 0, None, 0, stream())

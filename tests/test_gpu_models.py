@@ -402,3 +402,32 @@ def test_resnet50_batch_32_vs_fp32_oracle():
     overlap = [len(set(np.argsort(-got[b])[:5]) & set(np.argsort(-ref[b])[:5])) for b in range(32)]
     assert min(overlap) >= 4, overlap
     print(f"ResNet-50 b32: max|d|/max|ref| = {rel:.5f} (max|ref| {np.abs(ref).max():.1f}), min top-5 overlap {min(overlap)}")
+
+
+def test_mixed_device_and_host_partitions_with_pinned_transfers():
+    """An op forced to the host (docs/partitioning.md:33-40 of the reference) splits the plan into device -
+    host - device partitions; tensors cross the boundaries through page-locked staging buffers.  The mixed
+    plan must give what the all-device plan gives."""
+    from cuda_compiler import compile_subgraph, is_cuda_op_supported
+    from cuda_runtime import CUDABackend
+    from cuda_runtime.cuda_backend import staging
+    from npu_compiler import partition
+    from npu_runtime import DAGExecutor
+    from oracle.ir_interpreter import cpu_executor_factory   # stands in for the third-party host interpreter
+
+    m = mz.resnet(18, seed=0)
+    x = torch.randn(4, 3, 224, 224, generator=torch.Generator().manual_seed(3))
+    ir = extract_ir(m, (x,), "resnet18")
+    w = mz.state_dict_numpy(m.state_dict())
+    name = ir["graph_outputs"][0]["name"]
+    all_dev, _ = run_backend(ir, w, {"x": x.numpy()})
+    plan = partition(ir, lambda op, attrs=None: op != "aten.max_pool2d.default" and is_cuda_op_supported(op, attrs))
+    kinds = [getattr(s, "target", "transfer") for s in plan.steps]
+    assert kinds.count("cpu") == 1 and kinds.count("npu") == 2
+    dag = DAGExecutor(plan, CUDABackend(), compile_subgraph, cpu_executor_factory=cpu_executor_factory)
+    before = (staging().uploads, staging().downloads)
+    out = dag.execute({"x": x.numpy()}, weights=w)
+    got = to_f32(out[name])
+    assert staging().uploads > before[0] and staging().downloads > before[1]
+    ref = to_f32(all_dev[name])
+    assert np.abs(got - ref).max() <= 2e-2 * np.abs(ref).max() and (got.argmax(-1) == ref.argmax(-1)).all()

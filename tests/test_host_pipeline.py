@@ -224,3 +224,41 @@ def test_cache_read_by_a_later_partition_is_not_updated_in_place(fake_native):
     solo = graph(n[:1], [c, pos, src], [ts("upd", [1, 1, S, D], "bfloat16")])
     assert compile_subgraph(solo).donated_inputs == {"upd": "cache"}
     assert not compile_subgraph(solo, keep_inputs={"cache"}).donated_inputs
+
+
+def test_program_save_and_load_round_trip(fake_native, tmp_path):
+    """A compiled program written to disk and read back drives the executor to the same result
+    (the reference has save / load for its Metal programs only, npu_compiler/compiled_program.py:49-117)."""
+    from golden.make_golden import tiny_qwen
+
+    from cuda_compiler import compile_subgraph
+    from cuda_compiler.cuda_program import CUDAProgram
+    from cuda_runtime import CUDABackend
+
+    cfg, sd, model = tiny_qwen()
+    L, B, S, P = cfg.num_hidden_layers, 2, 40, 17
+    ir = extract_ir(mz.QwenDecodeWrapper(model, L), mz.qwen2_example_inputs(cfg, B, 1, S, device="cpu"), "d")
+    prog = compile_subgraph(ir)
+    path = tmp_path / "decode.b200prog"
+    prog.save(str(path))
+    back = CUDAProgram.load(str(path))
+    assert back.to_dict() == prog.to_dict()
+    assert type(back.steps[0]) is type(prog.steps[0]) and back.views.keys() == prog.views.keys()
+    assert [a.offset for a in back.buffer_allocations] == [a.offset for a in prog.buffer_allocations] and back.arena_bytes == prog.arena_bytes
+    g = torch.Generator().manual_seed(2)
+    ins = (torch.randint(0, cfg.vocab_size, (B, 1), generator=g), mz.causal_mask(B, 1, S, P), torch.full((B, 1), P), torch.tensor([P]),
+           *[(torch.randn(B, 1, S, 128, generator=g) * 0.5).bfloat16() for _ in range(2 * L)])
+    backend = CUDABackend()
+    w = mz.state_dict_numpy(sd)
+    outs = []
+    for program in (prog, back):
+        ex = backend.create_executor(program)
+        key_to_ph = {k: ph for ph, k in program.weight_name_mapping.items()}
+        weights = {key_to_ph.get(s.name, s.name): backend.allocate_buffer(w[s.name], spec=s) for s in program.weight_specs if s.name in w}
+        feed = {s["name"]: backend.allocate_buffer(torch_to_numpy(t)) for s, t in zip(ir["graph_inputs"], ins)}
+        outs.append(to_f32(ex.run(feed, weights)[ir["graph_outputs"][0]["name"]]))
+    np.testing.assert_array_equal(outs[0], outs[1])
+    ref = oracle(ir, sd, ins)[ir["graph_outputs"][0]["name"]]
+    assert np.abs(outs[1] - ref).max() < 0.1
+    with pytest.raises(ValueError, match="version"):
+        CUDAProgram.from_dict({**prog.to_dict(), "version": 99})
