@@ -130,6 +130,59 @@ __global__ void __launch_bounds__(128) rope_rotate_kernel(const __grid_constant_
   reinterpret_cast<uint4*>(dst)[pk + hp] = pack8<T>(ohi);
 }
 
+// Many positions (prefill): one thread per (sequence, position, pack pair) walks ALL heads.  The
+// cos / sin values of a position are the same for every head, so they are loaded once per thread
+// instead of once per head, and the loads of four heads are in flight together.
+template <typename T>
+__global__ void __launch_bounds__(128) rope_rotate_heads_kernel(const __grid_constant__ RopeParams p) {
+  const int hp = p.D >> 4;
+  const int64_t gid = static_cast<int64_t>(blockIdx.x) * 128 + threadIdx.x;
+  if (gid >= p.B * p.T * hp) return;
+  const int pk = static_cast<int>(gid % hp);
+  const int64_t bt = gid / hp, b = bt / p.T, t = bt - b * p.T;
+  const int64_t tab = (b * p.T + t) * p.D;
+  const uint4* ct = reinterpret_cast<const uint4*>(static_cast<const T*>(p.cos_t) + tab);
+  const uint4* st = reinterpret_cast<const uint4*>(static_cast<const T*>(p.sin_t) + tab);
+  float clo[8], chi[8], slo[8], shi[8];
+  unpack8<T>(__ldg(ct + pk), clo);
+  unpack8<T>(__ldg(ct + pk + hp), chi);
+  unpack8<T>(__ldg(st + pk), slo);
+  unpack8<T>(__ldg(st + pk + hp), shi);
+  const T* xb = static_cast<const T*>(p.x) + b * p.xs[0] + t * p.xs[2];
+  constexpr int U = 4;
+  for (int64_t h0 = 0; h0 < p.H; h0 += U) {
+    uint4 rlo[U], rhi[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+      if (h0 + u < p.H) {
+        const uint4* xr = reinterpret_cast<const uint4*>(xb + (h0 + u) * p.xs[1]);
+        rlo[u] = ld_global_nc_v4(xr + pk);
+        rhi[u] = ld_global_nc_v4(xr + pk + hp);
+      }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (h0 + u >= p.H) break;
+      float lo[8], hi[8], olo[8], ohi[8];
+      unpack8<T>(rlo[u], lo);
+      unpack8<T>(rhi[u], hi);
+#pragma unroll
+      for (int k = 0; k < 8; k += 2) {
+        float a0 = lo[k] * clo[k], a1 = lo[k + 1] * clo[k + 1], b0 = -hi[k] * slo[k], b1 = -hi[k + 1] * slo[k + 1];
+        round2<T>(a0, a1);
+        round2<T>(b0, b1);
+        olo[k] = a0 + b0; olo[k + 1] = a1 + b1;
+        float c0 = hi[k] * chi[k], c1 = hi[k + 1] * chi[k + 1], d0 = lo[k] * shi[k], d1 = lo[k + 1] * shi[k + 1];
+        round2<T>(c0, c1);
+        round2<T>(d0, d1);
+        ohi[k] = c0 + d0; ohi[k + 1] = c1 + d1;
+      }
+      T* dst = static_cast<T*>(p.y) + ((b * p.H + h0 + u) * p.T + t) * p.D;
+      reinterpret_cast<uint4*>(dst)[pk] = pack8<T>(olo);
+      reinterpret_cast<uint4*>(dst)[pk + hp] = pack8<T>(ohi);
+    }
+  }
+}
+
 struct QkvPostParams {
   const void* x[3];     // q, k, v: [B, H, T, D] views, D contiguous
   int64_t xs[3][3];     // element strides over (b, h, t)
@@ -295,8 +348,11 @@ extern "C" int b200_rope_rotate(const b200_tensor* x, const void* cos_t, const v
   const int64_t grid = ceil_div(total, 128);
   B200_CHECK_ARG(grid < (1ll << 31), "b200_rope_rotate: tensor too large");
   const bool small = total + 128 < (1ll << 32);
+  const int64_t per_head = p.B * p.T * (p.D >> 4);
   B200_DISPATCH_HALF(x->dtype, T, {
-    if (small) rope_rotate_kernel<T, uint32_t><<<static_cast<unsigned>(grid), 128, 0, st>>>(p);
+    if (!kv_cache && p.H >= 2 && per_head >= 64 * 148)   // enough positions to fill the GPU with one thread per (position, pack pair)
+      rope_rotate_heads_kernel<T><<<static_cast<unsigned>(ceil_div(per_head, 128)), 128, 0, st>>>(p);
+    else if (small) rope_rotate_kernel<T, uint32_t><<<static_cast<unsigned>(grid), 128, 0, st>>>(p);
     else rope_rotate_kernel<T, int64_t><<<static_cast<unsigned>(grid), 128, 0, st>>>(p);
   });
   B200_CHECK_LAUNCH("rope_rotate_kernel");

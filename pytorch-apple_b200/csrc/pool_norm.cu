@@ -64,6 +64,30 @@ __global__ void __launch_bounds__(256) max_pool2d_cl8_kernel(const __grid_consta
   float best[8];
 #pragma unroll
   for (int k = 0; k < 8; ++k) best[k] = -INFINITY;
+  if (p.kh == 3 && p.kw == 3) {
+    // The ResNet stem pool: all nine taps are requested before the first comparison (nine loads in
+    // flight per thread instead of one after the other: 0.44 -> of the copy peak before).
+    uint4 tap[9];
+    bool in[9];
+#pragma unroll
+    for (int r = 0; r < 3; ++r)
+#pragma unroll
+      for (int s = 0; s < 3; ++s) {
+        const int ih = oh * p.sh - p.ph + r, iw = ow * p.sw - p.pw + s;
+        in[3 * r + s] = ih >= 0 && ih < p.H && iw >= 0 && iw < p.W;
+        if (in[3 * r + s]) tap[3 * r + s] = ld_global_nc_v4(xb + ih * p.xs[2] + iw * p.xs[3]);
+      }
+#pragma unroll
+    for (int j = 0; j < 9; ++j) {
+      if (!in[j]) continue;
+      float v[8];
+      unpack8<T>(tap[j], v);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) best[k] = (v[k] > best[k] || v[k] != v[k]) ? v[k] : best[k];
+    }
+    *reinterpret_cast<uint4*>(static_cast<T*>(p.y) + n * p.ys[0] + oh * p.ys[2] + ow * p.ys[3] + c) = pack8<T>(best);
+    return;
+  }
   for (int r = 0; r < p.kh; ++r) {
     const int ih = oh * p.sh - p.ph + r;
     if (ih < 0 || ih >= p.H) continue;

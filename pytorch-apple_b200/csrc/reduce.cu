@@ -20,13 +20,25 @@ __global__ void __launch_bounds__(128) rmsnorm_warp_kernel(const T* __restrict__
   if (row >= rows) return;
   const int npack = cols >> 3;
   const uint4* xr = reinterpret_cast<const uint4*>(x + row * xs);
-  uint4 raw[MAXP];
+  const uint4* wv = reinterpret_cast<const uint4*>(w);
+  uint4 raw[MAXP], gain[MAXP];
+  // every load of the row and of the gains is in flight before anything waits: the kernel lives for
+  // about two memory round trips, and asking for the gains only after the reduction made it three
+#pragma unroll
+  for (int i = 0; i < MAXP; ++i) {
+    const int pk = lane + 32 * i;
+    if (pk < npack) raw[i] = ld_global_nc_v4(xr + pk);
+  }
+#pragma unroll
+  for (int i = 0; i < MAXP; ++i) {
+    const int pk = lane + 32 * i;
+    if (pk < npack) gain[i] = __ldg(wv + pk);
+  }
   float ss = 0.f;
 #pragma unroll
   for (int i = 0; i < MAXP; ++i) {
     const int pk = lane + 32 * i;
     if (pk < npack) {
-      raw[i] = ld_global_nc_v4(xr + pk);
       float f[8];
       unpack8<T>(raw[i], f);
 #pragma unroll
@@ -35,7 +47,6 @@ __global__ void __launch_bounds__(128) rmsnorm_warp_kernel(const T* __restrict__
   }
   ss = warp_sum(ss);
   const float r = 1.0f / sqrtf(ss / static_cast<float>(cols) + eps);
-  const uint4* wv = reinterpret_cast<const uint4*>(w);
   uint4* yr = reinterpret_cast<uint4*>(y + row * ys);
 #pragma unroll
   for (int i = 0; i < MAXP; ++i) {
@@ -43,7 +54,7 @@ __global__ void __launch_bounds__(128) rmsnorm_warp_kernel(const T* __restrict__
     if (pk < npack) {
       float f[8], g[8];
       unpack8<T>(raw[i], f);
-      unpack8<T>(__ldg(wv + pk), g);
+      unpack8<T>(gain[i], g);
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
         float n = f[k] * r;
