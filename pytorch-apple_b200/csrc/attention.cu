@@ -644,12 +644,14 @@ extern "C" int b200_attn_decode(const void* q, const void* k, const void* v, con
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   dim3 grid(static_cast<unsigned>(d.splits), static_cast<unsigned>(Hkv), static_cast<unsigned>(B));
   B200_DISPATCH_HALF(dtype, T, {
-    static bool configured = false;
-    if (!configured) {
+    static PerDevice<bool> configured_on;
+    bool* configured = configured_on.slot();
+    if (!configured) B200_FAIL(B200_ELAUNCH, "attn_decode_kernel: no current device");
+    if (!*configured) {
       cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<T, 2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 4 * 2 * DEC_STAGE_BYTES);
       if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_decode_kernel<T, 2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 4 * 2 * DEC_STAGE_BYTES);
       if (e != cudaSuccess) B200_FAIL(B200_ELAUNCH, "attn_decode_kernel attribute: %s", cudaGetErrorString(e));
-      configured = true;
+      *configured = true;
     }
     if (d.cluster) {   // one kernel: the splits of a (sequence, KV head) are a cluster along x and merge in shared memory
       cudaLaunchConfig_t cfg = {};
@@ -708,11 +710,13 @@ extern "C" int b200_attn_prefill(const void* q, const void* k, const void* v, co
   }
   dim3 grid(static_cast<unsigned>(ceil_div(T, 64)), static_cast<unsigned>(Hq), static_cast<unsigned>(B));
   B200_DISPATCH_HALF(dtype, T_, {
-    static bool configured = false;
-    if (!configured) {
+    static PerDevice<bool> configured_on;
+    bool* configured = configured_on.slot();
+    if (!configured) B200_FAIL(B200_ELAUNCH, "attn_prefill_kernel: no current device");
+    if (!*configured) {
       cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<T_>, cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM);
       if (e != cudaSuccess) B200_FAIL(B200_ELAUNCH, "attn_prefill_kernel attribute: %s", cudaGetErrorString(e));
-      configured = true;
+      *configured = true;
     }
     attn_prefill_kernel<T_><<<grid, 128, PF_SMEM, st>>>(p);
   });

@@ -380,15 +380,15 @@ __global__ void __launch_bounds__(480, 1)
 
 template <typename T>
 int launch_prefill_tc5(const PrefillParams& p, int dtype, cudaStream_t st) {
-  static bool configured[64] = {false};
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return B200_ENOTSUP;
-  if (!configured[dev]) {
+  static PerDevice<bool> configured_on;
+  bool* configured = configured_on.slot();
+  if (!configured) return B200_ENOTSUP;
+  if (!*configured) {
     if (cudaFuncSetAttribute(attn_prefill_tc5_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, PF5_SMEM) != cudaSuccess) {
       cudaGetLastError();
       return B200_ENOTSUP;
     }
-    configured[dev] = true;
+    *configured = true;
   }
   CUtensorMap mq, mk, mv, mm;
   auto st_of = [](int64_t elems, uint64_t fallback) { return elems > 0 ? static_cast<uint64_t>(elems) * 2 : fallback; };

@@ -60,6 +60,18 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
     if (e__ != cudaSuccess) B200_FAIL(B200_ELAUNCH, "%s: %s", name, cudaGetErrorString(e__)); \
   } while (0)
 
+// Function attributes and occupancy answers belong to one device; a cache of them is indexed by the
+// device current at the call.  slot() is nullptr when the device cannot be read or lies outside the table.
+constexpr int B200_MAX_DEVICES = 64;
+template <typename V> struct PerDevice {
+  V v[B200_MAX_DEVICES] = {};
+  V* slot() {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= B200_MAX_DEVICES) return nullptr;
+    return &v[dev];
+  }
+};
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 inline int dtype_size(int dt) {

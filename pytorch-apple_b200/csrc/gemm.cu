@@ -443,11 +443,13 @@ __global__ void __launch_bounds__(256) matmul_strided_kernel(const __grid_consta
 template <typename T, int MT, bool IS_CONV> static int launch_tile(const GemmParams& p, cudaStream_t st) {
   constexpr int BM = MT * 32;
   constexpr int SMEM = STAGES * (BM * BK * 2 + BN * BK * 2);
-  static bool configured = false;  // per instantiation; attribute is per-function and idempotent
-  if (!configured) {
+  static PerDevice<bool> configured_on;  // per instantiation and device
+  bool* configured = configured_on.slot();
+  if (!configured) B200_FAIL(B200_ELAUNCH, "gemm_tile_kernel: no current device");
+  if (!*configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tile_kernel<T, MT, IS_CONV>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     if (e != cudaSuccess) B200_FAIL(B200_ELAUNCH, "gemm_tile_kernel attribute: %s", cudaGetErrorString(e));
-    configured = true;
+    *configured = true;
   }
   dim3 grid(static_cast<unsigned>(ceil_div(p.N, BN)), static_cast<unsigned>(ceil_div(p.M, BM)));
   gemm_tile_kernel<T, MT, IS_CONV><<<grid, 256, SMEM, st>>>(p);

@@ -1333,19 +1333,22 @@ int launch(const Tc5Args& a, const Tc5Plan& plan, cudaStream_t st, const Tc5Conv
   Tc5Plan pl = plan;
   constexpr int SMEM_RING = Cfg<BN, MODE>::RING + 1024, SMEM_SPLIT = SMEM_RING + Cfg<BN, MODE>::RECV;
   static_assert(SMEM_SPLIT <= 227 * 1024, "ring + receive buffer exceed the shared memory of an SM");
-  static bool configured = false;
-  if (!configured) {
+  struct DeviceState { bool configured; int fit[MAX_SPLITS + 1]; };
+  static PerDevice<DeviceState> state_on;
+  DeviceState* ds = state_on.slot();
+  if (!ds) return B200_ENOTSUP;
+  if (!ds->configured) {
     if (cudaFuncSetAttribute(gemm_tc5_kernel<T, BN, CONV, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_SPLIT) != cudaSuccess) {
       cudaGetLastError();
       return B200_ENOTSUP;
     }
-    configured = true;
+    ds->configured = true;
   }
   // The clusters of one launch should all be resident at once (a second wave would double the
   // time of these short kernels).  How many clusters of a given size fit depends on how the SMs
   // are grouped, so ask the runtime, once per cluster size, and shrink the split until they fit.
   if (pl.splits > 1) {
-    static int fit[MAX_SPLITS + 1] = {0};
+    int* fit = ds->fit;
     const int64_t tiles = pl.tiles_n * pl.tiles_m;
     int splits = pl.splits;
     for (; splits > 1; --splits) {
@@ -1422,13 +1425,15 @@ template <typename T, int BN, bool CONV, bool TS>
 int launch_persistent(const Tc5Args& a, cudaStream_t st, const Tc5Conv* g = nullptr) {
   using PC = PCfg<BN, TS>;
   static_assert(PC::SMEM <= PC::SMEM_LIMIT, "ring + C buffers exceed the shared memory of an SM");
-  static bool configured = false;
-  if (!configured) {
+  static PerDevice<bool> configured_on;
+  bool* configured = configured_on.slot();
+  if (!configured) return B200_ENOTSUP;
+  if (!*configured) {
     if (cudaFuncSetAttribute(gemm_tc5p_kernel<T, BN, CONV, TS>, cudaFuncAttributeMaxDynamicSharedMemorySize, PC::SMEM_LIMIT) != cudaSuccess) {
       cudaGetLastError();
       return B200_ENOTSUP;
     }
-    configured = true;
+    *configured = true;
   }
   CUtensorMap ma, mw, mr, mo;
   Tc5Params p;
@@ -1541,13 +1546,15 @@ int launch_stem_rows(const Tc5Args& a, const Tc5Conv& g, cudaStream_t st) {
       a.K != static_cast<int64_t>(g.KH) * g.KW * 8 || a.ldw % 8 || !aligned16(a.A) || !aligned16(a.W) || !tma_store_ok(a))
     return B200_ENOTSUP;
   constexpr int SMEM = 8 * STEM_W_STAGE + 2 * STEM_CB + STEM_SLOTS * STEM_SLOT + 1024;
-  static bool configured = false;
-  if (!configured) {
+  static PerDevice<bool> configured_on;
+  bool* configured = configured_on.slot();
+  if (!configured) return B200_ENOTSUP;
+  if (!*configured) {
     if (cudaFuncSetAttribute(conv_stem_rows_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) {
       cudaGetLastError();
       return B200_ENOTSUP;
     }
-    configured = true;
+    *configured = true;
   }
   CUtensorMap mw, mo;
   if (!make_map_c8(&mw, a.W, a.N, a.K, a.ldw, STEM_BN, a.dtype) || !make_map(&mo, a.out, a.M, a.N, a.ldo, g.Wo, a.dtype)) return B200_ENOTSUP;

@@ -24,6 +24,7 @@ pool the same way, cuda_executor.py:90-95).  Not re-entrant; one executor per GP
 
 from __future__ import annotations
 
+import contextlib
 import ctypes as C
 from typing import Any
 
@@ -85,11 +86,26 @@ class CUDAExecutor:
         self.last_launch_count = 0
 
     # ------------------------------------------------------------------ public
+    def _device_guard(self):
+        """The library launches on the current device; make it this executor's for the call."""
+        return torch.cuda.device(self._device) if self._on_gpu else contextlib.nullcontext()
+
+    def _input_tensors(self, inputs: dict[str, Any]) -> dict[str, Any]:
+        tensors = {n: inputs[n].native_handle for n in self._input_names if n in inputs}
+        for n, t in tensors.items():
+            if str(t.device) != self._device and not (self._device == "cuda:0" and str(t.device) == "cuda"):
+                raise ValueError(f"input '{n}' lives on {t.device}, this executor runs on {self._device}")
+        return tensors
+
     def run(self, inputs: dict[str, Any], weights: dict[str, Any]) -> dict[str, Any]:
+        with self._device_guard():
+            return self._run(inputs, weights)
+
+    def _run(self, inputs: dict[str, Any], weights: dict[str, Any]) -> dict[str, Any]:
         from cuda_runtime.cuda_backend import CUDABuffer
 
         self._check_weights(weights)
-        tensors = {n: inputs[n].native_handle for n in self._input_names if n in inputs}
+        tensors = self._input_tensors(inputs)
         key = tuple((n, t.data_ptr(), t.dtype) for n, t in tensors.items())
         plan = self._plans.get(key)
         if plan is None:
