@@ -39,6 +39,7 @@ template <int BN, int MODE> struct Cfg {
   static constexpr int A_STAGE = AROWS * BK * 2;
   static constexpr int ST = MODE == 0 ? (BN == 128 ? 3 : 4) : MODE == 1 ? (BN == 128 ? 4 : 6) : (BN == 128 ? 7 : 12);
   static constexpr int CTAS = MODE == 0 ? 2 : 1;
+  static constexpr int ISSUE_GROUP = ST >= 12 ? 4 : ST >= 6 ? 3 : ST >= 4 ? 2 : 1;   // ring stages a producer thread fills per barrier wait
   static constexpr int RING = ST * (A_STAGE + BN * BK * 2);
   // split-K only: fp32 receive buffer for the partial-tile rows this CTA owns, one slot per
   // cluster rank, behind the ring (peers write into it while this CTA may still be computing)
@@ -243,7 +244,7 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 template <typename T, int BN, bool CONV, int MODE>
 __global__ void __launch_bounds__(224, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a,
                                                           const __grid_constant__ CUtensorMap map_w, const Tc5Params p) {
-  constexpr int ST = Cfg<BN, MODE>::ST, A_STAGE = Cfg<BN, MODE>::A_STAGE;
+  constexpr int ST = Cfg<BN, MODE>::ST, A_STAGE = Cfg<BN, MODE>::A_STAGE, ISSUE_GROUP = Cfg<BN, MODE>::ISSUE_GROUP;
   constexpr int B_STAGE = BN * BK * 2, STAGE = A_STAGE + B_STAGE;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -292,9 +293,10 @@ __global__ void __launch_bounds__(224, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(cons
   const uint32_t tmem_base = tmem_holder;
   pdl_trigger();   // the next kernel in the stream may be scheduled (it waits for this one before reading)
 
-  // Two producer threads: one TMA-issuing thread sustains ~60 GB/s (measured: 0.26 us per 16 KB
-  // box whatever the ring depth; two threads issue twice that), so activations and weights each
-  // get their own - thread 0 of warp 0 the activation tiles, thread 0 of warp 6 the weight tiles.
+  // Two producer threads - thread 0 of warp 0 the activation tiles, thread 0 of warp 6 the weight
+  // tiles.  A barrier wait that follows a TMA instruction costs the thread ~0.3 us whatever it waits
+  // for (measured: one wait-then-copy per iteration issues 3 boxes per us, copies alone 30), so a
+  // producer waits once per ISSUE_GROUP stages and then issues that many copies back to back.
   // Weights that no kernel of this stream writes are fetched before the predecessor has finished:
   // the weight producer simply runs ahead until the ring is full.
   const bool w_static = (p.epilogue & B200_EPI_W_STATIC) != 0;
@@ -313,13 +315,24 @@ __global__ void __launch_bounds__(224, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(cons
     if (lane == 0) {   // ---- weight producer ----
       if (!w_static) pdl_wait();   // the weights may come from the kernel before this one
       int issued = pre;
-      for (int i = pre; i < nkb; ++i) {
-        const int s = i % ST;
-        if (!tc5::mbar_wait(&empty_bar[s], ((i / ST) & 1) ^ 1)) { failed = 1; atomicExch(&g_tc5_error, 1); break; }
-        if (*reinterpret_cast<volatile int*>(&failed)) break;
-        tc5::mbar_arrive_expect_tx(&full_bar[s], B_STAGE);
-        tc5::tma_load_2d(smem + s * STAGE + A_STAGE, &map_w, &full_bar[s], (kb0 + i) * BK, n0);
-        issued = i + 1;
+      const int first = nkb < ST ? nkb : ST;   // the first pass over the ring finds every stage free: no waits
+      for (int i = pre; i < first; ++i) {
+        tc5::mbar_arrive_expect_tx(&full_bar[i], B_STAGE);
+        tc5::tma_load_2d(smem + i * STAGE + A_STAGE, &map_w, &full_bar[i], (kb0 + i) * BK, n0);
+      }
+      issued = first;
+      bool alive = true;
+      for (int i = first; i < nkb && alive; i += ISSUE_GROUP) {
+        const int g = nkb - i < ISSUE_GROUP ? nkb - i : ISSUE_GROUP;
+        for (int j = g - 1; j >= 0 && alive; --j)   // the stage freed last first: the others then answer at once
+          if (!tc5::mbar_wait(&empty_bar[(i + j) % ST], (((i + j) / ST) & 1) ^ 1)) { failed = 1; atomicExch(&g_tc5_error, 1); alive = false; }
+        if (!alive || *reinterpret_cast<volatile int*>(&failed)) break;
+        for (int j = 0; j < g; ++j) {
+          const int s = (i + j) % ST;
+          tc5::mbar_arrive_expect_tx(&full_bar[s], B_STAGE);
+          tc5::tma_load_2d(smem + s * STAGE + A_STAGE, &map_w, &full_bar[s], (kb0 + i + j) * BK, n0);
+        }
+        issued = i + g;
       }
       if (*reinterpret_cast<volatile int*>(&failed)) {  // wait (bounded) for our own copies still in flight
         for (int i = issued > ST ? issued - ST : 0; i < issued; ++i) tc5::mbar_wait(&full_bar[i % ST], (i / ST) & 1, 1u << 16);
@@ -329,10 +342,8 @@ __global__ void __launch_bounds__(224, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(cons
     if (lane == 0 && !gather) {   // ---- activation producer (the gather variant fills the A tile with the epilogue warps) ----
       pdl_wait();
       int issued = 0;
-      for (int i = 0; i < nkb; ++i) {
+      auto load_a = [&](int i) {
         const int s = i % ST;
-        if (!tc5::mbar_wait(&empty_bar[s], ((i / ST) & 1) ^ 1)) { failed = 1; atomicExch(&g_tc5_error, 1); break; }
-        if (*reinterpret_cast<volatile int*>(&failed)) break;
         tc5::mbar_arrive_expect_tx(&full_bar[s], A_STAGE);
         if (!CONV) {
           tc5::tma_load_2d(smem + s * STAGE, &map_a, &full_bar[s], (kb0 + i) * BK, m0);
@@ -342,7 +353,18 @@ __global__ void __launch_bounds__(224, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(cons
           tc5::tma_load_im2col_4d(smem + s * STAGE, &map_a, &full_bar[s], (kb - tap * cpb) * BK, ow * p.g.sw - p.g.pw, oh * p.g.sh - p.g.ph, img,
                                   tap - r * p.g.KW, r);
         }
-        issued = i + 1;
+      };
+      const int first = nkb < ST ? nkb : ST;   // the first pass over the ring finds every stage free: no waits
+      for (int i = 0; i < first; ++i) load_a(i);
+      issued = first;
+      bool alive = true;
+      for (int i = first; i < nkb && alive; i += ISSUE_GROUP) {
+        const int g = nkb - i < ISSUE_GROUP ? nkb - i : ISSUE_GROUP;
+        for (int j = g - 1; j >= 0 && alive; --j)
+          if (!tc5::mbar_wait(&empty_bar[(i + j) % ST], (((i + j) / ST) & 1) ^ 1)) { failed = 1; atomicExch(&g_tc5_error, 1); alive = false; }
+        if (!alive || *reinterpret_cast<volatile int*>(&failed)) break;
+        for (int j = 0; j < g; ++j) load_a(i + j);
+        issued = i + g;
       }
       if (*reinterpret_cast<volatile int*>(&failed)) {
         for (int i = issued > ST ? issued - ST : 0; i < issued; ++i) tc5::mbar_wait(&full_bar[i % ST], (i / ST) & 1, 1u << 16);
