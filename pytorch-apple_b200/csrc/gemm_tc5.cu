@@ -62,7 +62,7 @@ struct Tc5Params {
   int pst, pstage;      // ring stages and bytes per stage
   int wr, w_off;        // weights resident: all k-blocks of the CTA's weight tile stay in shared memory at w_off
   int pncb, c_off;      // C buffers (bulk-copy epilogue) and where they start
-  int a2;               // two activation producer threads take alternate k-blocks
+  int npa, npw;         // persistent kernel: activation / weight producer threads (1, 2 or 4), k-blocks dealt round-robin
   int nfast;            // persistent kernel: column tiles fastest in the tile order
   // one-tile kernel, M <= 64: scale the output rows by the RMSNorm factor of the input rows / write
   // sum-of-squares partials of the output rows
@@ -301,89 +301,90 @@ __global__ void __launch_bounds__(224, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(cons
   // the weight producer simply runs ahead until the ring is full.
   const bool w_static = (p.epilogue & B200_EPI_W_STATIC) != 0;
   const int pre = w_static ? (nkb < ST ? nkb : ST) : 0;   // weight stages issued before the cluster start-up barrier
+  const uint32_t ring_addr = tc5::smem_addr(smem), full0 = tc5::smem_addr(&full_bar[0]), empty0 = tc5::smem_addr(&empty_bar[0]);
   if (warp == 6 && lane == 0) {
     for (int i = 0; i < pre; ++i) {
-      tc5::mbar_arrive_expect_tx(&full_bar[i], B_STAGE);
-      tc5::tma_load_2d(smem + i * STAGE + A_STAGE, &map_w, &full_bar[i], (kb0 + i) * BK, n0);
+      tc5::mbar_arrive_expect_tx_a(full0 + 8u * i, B_STAGE);
+      tc5::tma_load_2d_a(ring_addr + i * STAGE + A_STAGE, &map_w, full0 + 8u * i, (kb0 + i) * BK, n0);
     }
   }
   // Every CTA of the cluster is running before any of them writes into a peer's shared memory.
   // This barrier sits in the part of the kernel that overlaps the predecessor, so it costs nothing.
   if (nsp > 1) { __syncwarp(); tc5::cluster_sync(); }
 
+  // Both producers: the first pass over the ring finds every stage free and waits for nothing; after
+  // that a group of stages is waited for (the first wait is the long one, the rest answer at once) and
+  // filled back to back.  `load(i, s)` issues k-block i into stage s.
+  auto produce = [&](int from, auto&& load) {
+    const int first = nkb < ST ? nkb : ST;
+    for (int i = from; i < first; ++i) load(i, i);
+    int i = first, st = 0;
+    uint32_t par = 0;   // k-block ST reuses stage 0 once the first phase of its barrier has completed
+    while (i < nkb) {
+      const int g = nkb - i < ISSUE_GROUP ? nkb - i : ISSUE_GROUP;
+      int ss = st;
+      uint32_t pp = par;
+      for (int j = 0; j < g; ++j) {
+        if (!tc5::mbar_wait_a(empty0 + 8u * ss, pp)) { failed = 1; atomicExch(&g_tc5_error, 1); return i; }
+        if (++ss == ST) { ss = 0; pp ^= 1u; }
+      }
+      if (*reinterpret_cast<volatile int*>(&failed)) return i;
+      for (int j = 0; j < g; ++j, ++i) {
+        load(i, st);
+        if (++st == ST) { st = 0; par ^= 1u; }
+      }
+    }
+    return i;
+  };
+  auto drain = [&](int issued) {   // after a failure: wait (bounded) for this thread's own copies still in flight
+    if (*reinterpret_cast<volatile int*>(&failed))
+      for (int i = issued > ST ? issued - ST : 0; i < issued; ++i) tc5::mbar_wait(&full_bar[i % ST], (i / ST) & 1, 1u << 16);
+  };
+
   if (warp == 6) {
     if (lane == 0) {   // ---- weight producer ----
       if (!w_static) pdl_wait();   // the weights may come from the kernel before this one
-      int issued = pre;
-      const int first = nkb < ST ? nkb : ST;   // the first pass over the ring finds every stage free: no waits
-      for (int i = pre; i < first; ++i) {
-        tc5::mbar_arrive_expect_tx(&full_bar[i], B_STAGE);
-        tc5::tma_load_2d(smem + i * STAGE + A_STAGE, &map_w, &full_bar[i], (kb0 + i) * BK, n0);
-      }
-      issued = first;
-      bool alive = true;
-      for (int i = first; i < nkb && alive; i += ISSUE_GROUP) {
-        const int g = nkb - i < ISSUE_GROUP ? nkb - i : ISSUE_GROUP;
-        for (int j = g - 1; j >= 0 && alive; --j)   // the stage freed last first: the others then answer at once
-          if (!tc5::mbar_wait(&empty_bar[(i + j) % ST], (((i + j) / ST) & 1) ^ 1)) { failed = 1; atomicExch(&g_tc5_error, 1); alive = false; }
-        if (!alive || *reinterpret_cast<volatile int*>(&failed)) break;
-        for (int j = 0; j < g; ++j) {
-          const int s = (i + j) % ST;
-          tc5::mbar_arrive_expect_tx(&full_bar[s], B_STAGE);
-          tc5::tma_load_2d(smem + s * STAGE + A_STAGE, &map_w, &full_bar[s], (kb0 + i + j) * BK, n0);
-        }
-        issued = i + g;
-      }
-      if (*reinterpret_cast<volatile int*>(&failed)) {  // wait (bounded) for our own copies still in flight
-        for (int i = issued > ST ? issued - ST : 0; i < issued; ++i) tc5::mbar_wait(&full_bar[i % ST], (i / ST) & 1, 1u << 16);
-      }
+      drain(produce(pre, [&](int i, int st) {
+        tc5::mbar_arrive_expect_tx_a(full0 + 8u * st, B_STAGE);
+        tc5::tma_load_2d_a(ring_addr + st * STAGE + A_STAGE, &map_w, full0 + 8u * st, (kb0 + i) * BK, n0);
+      }));
     }
   } else if (warp == 0) {
     if (lane == 0 && !gather) {   // ---- activation producer (the gather variant fills the A tile with the epilogue warps) ----
       pdl_wait();
-      int issued = 0;
-      auto load_a = [&](int i) {
-        const int s = i % ST;
-        tc5::mbar_arrive_expect_tx(&full_bar[s], A_STAGE);
-        if (!CONV) {
-          tc5::tma_load_2d(smem + s * STAGE, &map_a, &full_bar[s], (kb0 + i) * BK, m0);
-        } else {
-          const int cpb = p.g.C / BK, kb = kb0 + i, tap = kb / cpb, r = tap / p.g.KW;
-          const int img = m0 / (p.g.Ho * p.g.Wo), rem = m0 - img * (p.g.Ho * p.g.Wo), oh = rem / p.g.Wo, ow = rem - oh * p.g.Wo;
-          tc5::tma_load_im2col_4d(smem + s * STAGE, &map_a, &full_bar[s], (kb - tap * cpb) * BK, ow * p.g.sw - p.g.pw, oh * p.g.sh - p.g.ph, img,
-                                  tap - r * p.g.KW, r);
-        }
-      };
-      const int first = nkb < ST ? nkb : ST;   // the first pass over the ring finds every stage free: no waits
-      for (int i = 0; i < first; ++i) load_a(i);
-      issued = first;
-      bool alive = true;
-      for (int i = first; i < nkb && alive; i += ISSUE_GROUP) {
-        const int g = nkb - i < ISSUE_GROUP ? nkb - i : ISSUE_GROUP;
-        for (int j = g - 1; j >= 0 && alive; --j)
-          if (!tc5::mbar_wait(&empty_bar[(i + j) % ST], (((i + j) / ST) & 1) ^ 1)) { failed = 1; atomicExch(&g_tc5_error, 1); alive = false; }
-        if (!alive || *reinterpret_cast<volatile int*>(&failed)) break;
-        for (int j = 0; j < g; ++j) load_a(i + j);
-        issued = i + g;
-      }
-      if (*reinterpret_cast<volatile int*>(&failed)) {
-        for (int i = issued > ST ? issued - ST : 0; i < issued; ++i) tc5::mbar_wait(&full_bar[i % ST], (i / ST) & 1, 1u << 16);
+      if (!CONV) {
+        drain(produce(0, [&](int i, int st) {
+          tc5::mbar_arrive_expect_tx_a(full0 + 8u * st, A_STAGE);
+          tc5::tma_load_2d_a(ring_addr + st * STAGE, &map_a, full0 + 8u * st, (kb0 + i) * BK, m0);
+        }));
+      } else {
+        // implicit GEMM: k-block = 64 channels of one filter tap; tap row / column / channel block are stepped
+        const int cpb = p.g.C / BK;
+        const int img = m0 / (p.g.Ho * p.g.Wo), rem = m0 - img * (p.g.Ho * p.g.Wo), oh = rem / p.g.Wo, ow = rem - oh * p.g.Wo;
+        const int base_w = ow * p.g.sw - p.g.pw, base_h = oh * p.g.sh - p.g.ph;
+        int cb = 0, sx = 0, r = 0;
+        drain(produce(0, [&](int, int st) {
+          tc5::mbar_arrive_expect_tx_a(full0 + 8u * st, A_STAGE);
+          tc5::tma_load_im2col_4d_a(ring_addr + st * STAGE, &map_a, full0 + 8u * st, cb * BK, base_w, base_h, img, sx, r);
+          if (++cb == cpb) { cb = 0; if (++sx == p.g.KW) { sx = 0; ++r; } }
+        }));
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc = tc5::umma_idesc(BM, BN, AbFormat<T>::value);
+      // this thread's scalar instructions set the pace of a decode GEMM (8 KB of weights per k-block): barrier
+      // addresses and descriptor words are stepped by single additions; a stage that no later k-block
+      // reuses is not handed back (a commit costs the thread ~50 cycles)
+      const uint32_t ring_lo = tc5::desc_sw128_lo(ring_addr);
+      uint32_t a_lo = ring_lo, ph = 0;
+      int s = 0;
       for (int i = 0; i < nkb; ++i) {
-        const int s = i % ST;
-        const uint32_t ph = (i / ST) & 1;
-        if (!tc5::mbar_wait(&full_bar[s], ph)) { failed = 1; atomicExch(&g_tc5_error, 2); break; }
-        tc5::tc_fence_after();
-        const uint32_t a_addr = tc5::smem_addr(smem + s * STAGE), b_addr = a_addr + A_STAGE;
-        const uint64_t da = tc5::umma_desc_sw128(a_addr), db = tc5::umma_desc_sw128(b_addr);
-#pragma unroll
-        for (int k = 0; k < BK / 16; ++k)  // 16 elements = 32 bytes = 2 descriptor address units
-          tc5::umma_f16(tmem_base, da + 2 * k, db + 2 * k, idesc, (i | k) != 0);
-        tc5::umma_commit(&empty_bar[s]);
+        if (!tc5::mbar_wait_a(full0 + 8u * s, ph)) { failed = 1; atomicExch(&g_tc5_error, 2); break; }
+        tc5::umma_f16_kblock(tmem_base, a_lo, a_lo + (A_STAGE >> 4), idesc, i);
+        if (i + ST < nkb) tc5::umma_commit_a(empty0 + 8u * s);
+        a_lo += STAGE >> 4;
+        if (++s == ST) { s = 0; ph ^= 1u; a_lo = ring_lo; }
       }
       tc5::umma_commit(&acc_bar);
     }
@@ -625,11 +626,13 @@ template <int BN, bool TS> struct PCfg {
   static constexpr int MAX_ST = 12, MAX_NCB = 4;
   static constexpr int SMEM_LIMIT = 227 * 1024 - 1024;   // dynamic part; the barriers are static shared memory
   // warps: 0 activation producer, 1 MMA, 2-5 epilogue; TS adds 6 store, 7-10 second epilogue group
-  // (half the columns each); the gather variant adds 6-9 gather; then the weight producer and,
-  // last, the second activation producer
+  // (half the columns each); the gather variant adds 6-9 gather; then the weight producer, the second
+  // activation producer and, last, five more producers (activation 3 and 4, weight 2 to 4): a producer
+  // thread gets one copy through per ~0.3 us, a 128-wide k-block of MMAs takes 0.13 us
   static constexpr int W_WARP = TS ? 11 : 6;
   static constexpr int A2_WARP = TS ? 12 : 7;           // second activation producer
-  static constexpr int THREADS = TS ? 416 : 256;
+  static constexpr int X_WARP = A2_WARP + 1;            // first of the five extra producers
+  static constexpr int THREADS = (X_WARP + 5) * 32;
   static constexpr int W_WARP_GATHER = 10;
   static constexpr int EPI_WARPS = TS ? 8 : 4;
 };
@@ -643,7 +646,7 @@ struct RingPos {
 };
 
 template <typename T, int BN, bool CONV, bool TS>
-__global__ void __launch_bounds__(TS ? 416 : (CONV ? 352 : 256), 1)
+__global__ void __launch_bounds__(PCfg<BN, TS>::THREADS, 1)
     gemm_tc5p_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                      const __grid_constant__ CUtensorMap map_r, const __grid_constant__ CUtensorMap map_o, const Tc5Params p,
                      const int tiles_m, const int n_tiles) {
@@ -694,51 +697,63 @@ __global__ void __launch_bounds__(TS ? 416 : (CONV ? 352 : 256), 1)
   pdl_trigger();
   auto dead = [&]() { return *reinterpret_cast<volatile int*>(&failed) != 0; };
 
-  if (warp == 0 || (p.a2 && warp == PCfg<BN, TS>::A2_WARP)) {
-    // ---- activation producer(s): with a2 the k-blocks alternate between two issuing threads
-    // (a 3x3 convolution is bound by how fast one thread gets its im2col boxes through) ----
+  // producer number of this warp among the activation / weight producers (-1: not one)
+  constexpr int XW = PCfg<BN, TS>::X_WARP;
+  const bool gather_variant = CONV && !TS && !p.g.im2col;   // launched with 352 threads: no extra producers
+  const int a_id = warp == 0 ? 0 : warp == PCfg<BN, TS>::A2_WARP ? 1 : (warp == XW || warp == XW + 1) ? warp - XW + 2 : -1;
+  const int w_id = warp == (gather_variant ? PCfg<BN, TS>::W_WARP_GATHER : PCfg<BN, TS>::W_WARP) ? 0 : (warp >= XW + 2 && warp <= XW + 4) ? warp - XW - 1 : -1;
+  if (a_id >= 0 && a_id < p.npa) {
+    // ---- activation producers: the k-blocks are dealt round-robin to p.npa issuing threads ----
     if (lane == 0) {
       pdl_wait();
-      const int mine = warp == 0 ? 0 : 1;
-      int it = 0, ti = 0;
-      RingPos rp;
-      for (int tile = blockIdx.x; tile < n_tiles && !dead(); tile += gridDim.x, ++ti) {
+      const int mine = a_id, deal = p.npa - 1;
+      const bool c8 = CONV && p.g.c8, gathered = CONV && !p.g.im2col;
+      const uint32_t ring_addr = tc5::smem_addr(smem), full0 = tc5::smem_addr(&full_bar[0]), empty0 = tc5::smem_addr(&empty_bar[0]);
+      const int cpb = CONV ? (c8 ? 1 : p.g.C / BK) : 1;
+      int it = 0, ti = 0, s = 0;
+      uint32_t ph = 0, dst = ring_addr;
+      bool alive = true;
+      for (int tile = blockIdx.x; tile < n_tiles && alive && !dead(); tile += gridDim.x, ++ti) {
         const int m0 = tile_m(tile) * BM;
-        int cpb = 1, img = 0, base_w = 0, base_h = 0;   // convolution: first output pixel of the tile as a base position
+        int img = 0, base_w = 0, base_h = 0;   // convolution: first output pixel of the tile as a base position
         if (CONV) {
-          cpb = p.g.c8 ? 1 : p.g.C / BK;
           img = m0 / (p.g.Ho * p.g.Wo);
           const int rem = m0 - img * (p.g.Ho * p.g.Wo), oh = rem / p.g.Wo;
           base_w = (rem - oh * p.g.Wo) * p.g.sw - p.g.pw;
           base_h = oh * p.g.sh - p.g.ph;
         }
-        for (int kb = 0; kb < KB; ++kb, ++it, rp.next(ST)) {
-          const int s = rp.s;
-          if (p.a2 && (it & 1) != mine) continue;
-          if (!tc5::mbar_wait(&empty_bar[s], rp.ph ^ 1u)) { failed = 1; atomicExch(&g_tc5_error, 11); break; }
-          if (CONV && !p.g.im2col) continue;   // gather variant: warps 6-9 fill the A tile
-          tc5::mbar_arrive_expect_tx(&full_bar[s], A_STAGE);
-          if (CONV && p.g.c8) {
-            // 8-channel input: k-block = 8 filter taps, each a [128 pixels][16 B] box.  Taps past the
-            // filter meet zero weights (outside the weight map), so their box only has to be finite: tap 0 again.
-            for (int tt = 0; tt < 8; ++tt) {
-              const int tap = kb * 8 + tt, ta = tap < p.g.KH * p.g.KW ? tap : 0, r = ta / p.g.KW;
-              tc5::tma_load_im2col_4d(smem + s * STAGE + tt * (BM * 16), &map_a, &full_bar[s], 0, base_w, base_h, img, ta - r * p.g.KW, r);
+        int cb = 0, sx = 0, r = 0;   // convolution: channel block within the filter tap, tap column, tap row - stepped, not divided
+        for (int kb = 0; kb < KB; ++kb, ++it) {
+          if ((it & deal) == mine) {
+            if (!tc5::mbar_wait_a(empty0 + 8u * s, ph ^ 1u)) { failed = 1; atomicExch(&g_tc5_error, 11); alive = false; break; }
+            if (!gathered) {   // (gather variant: warps 6-9 fill the A tile)
+              const uint32_t fb = full0 + 8u * s;
+              tc5::mbar_arrive_expect_tx_a(fb, A_STAGE);
+              if (c8) {
+                // 8-channel input: k-block = 8 filter taps, each a [128 pixels][16 B] box.  Taps past the
+                // filter meet zero weights (outside the weight map), so their box only has to be finite: tap 0 again.
+                for (int tt = 0; tt < 8; ++tt) {
+                  const int tap = kb * 8 + tt, ta = tap < p.g.KH * p.g.KW ? tap : 0, rr = ta / p.g.KW;
+                  tc5::tma_load_im2col_4d_a(dst + tt * (BM * 16), &map_a, fb, 0, base_w, base_h, img, ta - rr * p.g.KW, rr);
+                }
+              } else if (!CONV) {
+                tc5::tma_load_2d_a(dst, &map_a, fb, kb * BK, m0);
+              } else {
+                tc5::tma_load_im2col_4d_a(dst, &map_a, fb, cb * BK, base_w, base_h, img, sx, r);
+              }
             }
-          } else if (!CONV) {
-            tc5::tma_load_2d(smem + s * STAGE, &map_a, &full_bar[s], kb * BK, m0);
-          } else {
-            const int tap = kb / cpb, r = tap / p.g.KW;
-            tc5::tma_load_im2col_4d(smem + s * STAGE, &map_a, &full_bar[s], (kb - tap * cpb) * BK, base_w, base_h, img, tap - r * p.g.KW, r);
           }
+          dst += STAGE;
+          if (++s == ST) { s = 0; ph ^= 1u; dst = ring_addr; }
+          if (CONV && ++cb == cpb) { cb = 0; if (++sx == p.g.KW) { sx = 0; ++r; } }
         }
       }
       if (dead()) {  // wait (bounded) for our own copies still in flight
         for (int i = it > ST ? it - ST : 0; i < it; ++i) tc5::mbar_wait(&full_bar[i % ST], (i / ST) & 1, 1u << 16);
       }
     }
-  } else if (warp == ((CONV && !TS && !p.g.im2col) ? PCfg<BN, TS>::W_WARP_GATHER : PCfg<BN, TS>::W_WARP)) {
-    // ---- weight producer: one TMA-issuing thread sustains ~60 GB/s, so weights get their own ----
+  } else if (w_id >= 0 && w_id < (WR ? 1 : p.npw)) {
+    // ---- weight producers (one when the weights are resident) ----
     if (lane == 0) {
       if (!(p.epilogue & B200_EPI_W_STATIC)) pdl_wait();
       auto load_w = [&](uint8_t* dst, uint64_t* bar, int kb, int n0) {
@@ -765,15 +780,22 @@ __global__ void __launch_bounds__(TS ? 416 : (CONV ? 352 : 256), 1)
         }
         if (dead() && loads > 0) tc5::mbar_wait(&w_full, (loads - 1) & 1, 1u << 16);
       } else {
-        int it = 0;
-        RingPos rp;
-        for (int tile = blockIdx.x; tile < n_tiles && !dead(); tile += gridDim.x) {
+        const bool c8 = CONV && p.g.c8;
+        const uint32_t ring_addr = tc5::smem_addr(smem) + A_STAGE, full0 = tc5::smem_addr(&full_bar[0]), empty0 = tc5::smem_addr(&empty_bar[0]);
+        int it = 0, s = 0;
+        uint32_t ph = 0, dst = ring_addr;
+        bool alive = true;
+        for (int tile = blockIdx.x; tile < n_tiles && alive && !dead(); tile += gridDim.x) {
           const int n0 = tile_n(tile) * BN;
-          for (int kb = 0; kb < KB; ++kb, ++it, rp.next(ST)) {
-            const int s = rp.s;
-            if (!tc5::mbar_wait(&empty_bar[s], rp.ph ^ 1u)) { failed = 1; atomicExch(&g_tc5_error, 19); break; }
-            tc5::mbar_arrive_expect_tx(&full_bar[s], B_STAGE);
-            load_w(smem + s * STAGE + A_STAGE, &full_bar[s], kb, n0);
+          for (int kb = 0; kb < KB; ++kb, ++it) {
+            if ((it & (p.npw - 1)) == w_id) {
+              if (!tc5::mbar_wait_a(empty0 + 8u * s, ph ^ 1u)) { failed = 1; atomicExch(&g_tc5_error, 19); alive = false; break; }
+              tc5::mbar_arrive_expect_tx_a(full0 + 8u * s, B_STAGE);
+              if (c8) load_w(smem + s * STAGE + A_STAGE, &full_bar[s], kb, n0);
+              else tc5::tma_load_2d_a(dst, &map_w, full0 + 8u * s, kb * BK, n0);
+            }
+            dst += STAGE;
+            if (++s == ST) { s = 0; ph ^= 1u; dst = ring_addr; }
           }
         }
         if (dead()) {
@@ -784,9 +806,16 @@ __global__ void __launch_bounds__(TS ? 416 : (CONV ? 352 : 256), 1)
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc = tc5::umma_idesc(BM, BN, AbFormat<T>::value);
-      int it = 0, ti = 0, cur_n0 = -1, w_loads = 0;
-      RingPos rp;
-      for (int tile = blockIdx.x; tile < n_tiles && !dead(); tile += gridDim.x, ++ti) {
+      // Everything the loop needs per k-block is kept as a 32-bit value stepped by one addition: barrier
+      // addresses, the operand descriptors' low words, the phase bit.
+      const bool c8 = CONV && p.g.c8;
+      const uint32_t ring_addr = tc5::smem_addr(smem), full0 = tc5::smem_addr(&full_bar[0]), empty0 = tc5::smem_addr(&empty_bar[0]);
+      const uint32_t ring_lo = tc5::desc_sw128_lo(ring_addr), wres_lo = tc5::desc_sw128_lo(tc5::smem_addr(wres));
+      const uint32_t stage_lo = static_cast<uint32_t>(STAGE) >> 4;
+      int ti = 0, cur_n0 = -1, w_loads = 0, s = 0;
+      uint32_t ph = 0, a_lo = ring_lo;
+      bool alive = true;
+      for (int tile = blockIdx.x; tile < n_tiles && alive && !dead(); tile += gridDim.x, ++ti) {
         const int b = ti & 1;
         const int n0 = tile_n(tile) * BN;
         if (WR && n0 != cur_n0) {   // the resident weight tile of this column tile
@@ -797,25 +826,25 @@ __global__ void __launch_bounds__(TS ? 416 : (CONV ? 352 : 256), 1)
         if (!tc5::mbar_wait(&acc_empty[b], ((ti >> 1) & 1) ^ 1)) { failed = 1; atomicExch(&g_tc5_error, 12); break; }
         tc5::tc_fence_after();
         const uint32_t acc = tmem_base + b * BN;
-        for (int kb = 0; kb < KB; ++kb, ++it, rp.next(ST)) {
-          const int s = rp.s;
-          if (!tc5::mbar_wait(&full_bar[s], rp.ph)) { failed = 1; atomicExch(&g_tc5_error, 13); break; }
-          tc5::tc_fence_after();
-          const uint32_t a_addr = tc5::smem_addr(smem + s * STAGE), b_addr = WR ? tc5::smem_addr(wres + kb * B_STAGE) : a_addr + A_STAGE;
-          if (CONV && p.g.c8) {   // unswizzled operands: one MMA covers two taps (2 x 16 bytes of K)
+        uint32_t w_lo = wres_lo;
+        for (int kb = 0; kb < KB; ++kb) {
+          if (!tc5::mbar_wait_a(full0 + 8u * s, ph)) { failed = 1; atomicExch(&g_tc5_error, 13); alive = false; break; }
+          if (c8) {   // unswizzled operands: one MMA covers two taps (2 x 16 bytes of K)
+            const uint32_t a_addr = ring_addr + s * STAGE, b_addr = WR ? tc5::smem_addr(wres + kb * B_STAGE) : a_addr + A_STAGE;
             const uint32_t ak = BM * 16u, am = 128u, bk = BN * 16u, bm = 128u;
 #pragma unroll
             for (int k = 0; k < BK / 16; ++k)
               tc5::umma_f16(acc, tc5::umma_desc_nosw(a_addr + k * 2 * (BM * 16), ak, am), tc5::umma_desc_nosw(b_addr + k * 2 * (BN * 16), bk, bm), idesc,
                             (kb | k) != 0);
           } else {
-            const uint64_t da = tc5::umma_desc_sw128(a_addr), db = tc5::umma_desc_sw128(b_addr);
-#pragma unroll
-            for (int k = 0; k < BK / 16; ++k) tc5::umma_f16(acc, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+            tc5::umma_f16_kblock(acc, a_lo, WR ? w_lo : a_lo + (A_STAGE >> 4), idesc, kb);
           }
-          tc5::umma_commit(&empty_bar[s]);
+          tc5::umma_commit_a(empty0 + 8u * s);
+          w_lo += B_STAGE >> 4;
+          a_lo += stage_lo;
+          if (++s == ST) { s = 0; ph ^= 1u; a_lo = ring_lo; }
         }
-        if (dead()) break;
+        if (!alive) break;
         tc5::umma_commit(&acc_full[b]);
         if (WR) {   // last tile of this column tile: the weight producer may overwrite the tile once these MMAs are done
           const int next = tile + static_cast<int>(gridDim.x);
@@ -1493,7 +1522,7 @@ int launch_persistent(const Tc5Args& a, cudaStream_t st, const Tc5Conv* g = null
     p.nfast = 1;
     grid -= grid % static_cast<int>(tiles_n);   // every CTA stays on one column tile
   }
-  p.a2 = CONV && p.g.im2col && ceil_div(a.K, BK) >= 2 ? 1 : 0;
+
   // shared-memory plan
   p.pst = PC::ST; p.pstage = PC::STAGE; p.wr = 0; p.w_off = 0; p.pncb = TS ? PC::NCB : 1; p.c_off = PC::ST * PC::STAGE;
   int SMEM = PC::SMEM;
@@ -1510,7 +1539,17 @@ int launch_persistent(const Tc5Args& a, cudaStream_t st, const Tc5Conv* g = null
       break;
     }
   }
-  launch_pdl(gemm_tc5p_kernel<T, BN, CONV, TS>, dim3(grid), dim3((CONV && !p.g.im2col) ? 352 : PC::THREADS), SMEM, st, ma, mw, mr, mo, p,
+  // Producer threads (none extra for the gather variant): a power of two, at most the k-blocks of a tile
+  // and at most the ring depth.  The depth bound is a correctness condition: a producer learns how far the
+  // MMAs have got only from its own waits, one ring pass back at a time; dealt more than `depth` apart it
+  // could meet a barrier two phases behind, which a parity wait cannot tell from the phase it expects.
+  p.npa = p.npw = 1;
+  if (!CONV || p.g.im2col) {
+    const int64_t kbs = ceil_div(a.K, BK);
+    const int64_t cap = kbs < p.pst ? kbs : p.pst;
+    p.npa = p.npw = cap >= 4 ? 4 : cap >= 2 ? 2 : 1;
+  }
+  launch_pdl(gemm_tc5p_kernel<T, BN, CONV, TS>, dim3(grid), dim3((CONV && !TS && !p.g.im2col) ? 352 : PC::THREADS), SMEM, st, ma, mw, mr, mo, p,
              static_cast<int>(tiles_m), static_cast<int>(tiles));
   B200_CHECK_LAUNCH("gemm_tc5p_kernel");
   return B200_OK;

@@ -170,6 +170,66 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar)) : "memory");
 }
 
+// ---- forms for the single-thread issue loops ---------------------------------------------------
+// One thread issues every copy or MMA of a CTA, so the scalar instructions around them set the pace
+// (measured on sm_100a: four 64x64x16 MMAs plus a commit plus one barrier probe take ~300 cycles when
+// nothing else is executed; an MMA takes max(45, N/2) cycles whatever M).  These forms take 32-bit
+// shared-memory addresses and descriptor halves that the caller steps with single additions instead of
+// rebuilding generic pointers and 64-bit descriptors per k-block.
+__device__ __forceinline__ bool mbar_try_wait_a(uint32_t bar_addr, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(done) : "r"(bar_addr), "r"(parity) : "memory");
+  return done != 0;
+}
+__device__ __forceinline__ bool mbar_wait_a(uint32_t bar_addr, uint32_t parity, uint32_t limit = (1u << 22)) {
+  for (uint32_t i = 0; i < limit; ++i)
+    if (mbar_try_wait_a(bar_addr, parity)) return true;
+  return false;
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx_a(uint32_t bar_addr, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar_addr), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_a(uint32_t dst_addr, const CUtensorMap* map, uint32_t bar_addr, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst_addr), "l"(map), "r"(bar_addr), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tma_load_im2col_4d_a(uint32_t dst_addr, const CUtensorMap* map, uint32_t bar_addr, int c, int w, int h, int n,
+                                                     int off_w, int off_h) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};"
+      ::"r"(dst_addr), "l"(map), "r"(bar_addr), "r"(c), "r"(w), "r"(h), "r"(n),
+        "h"(static_cast<unsigned short>(off_w)), "h"(static_cast<unsigned short>(off_h)) : "memory");
+}
+__device__ __forceinline__ void umma_commit_a(uint32_t bar_addr) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_addr) : "memory");
+}
+// Halves of the K-major 128-byte-swizzle operand descriptor (see umma_desc_sw128): the low word holds
+// the start address (16-byte units; step it by bytes >> 4) and the leading offset, the high word is constant.
+constexpr uint32_t DESC_SW128_HI = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t desc_sw128_lo(uint32_t smem_byte_addr) { return ((smem_byte_addr & 0x3FFFFu) >> 4) | (1u << 16); }
+// The four MMAs of one 64-element k-block (K = 16 each, 32 bytes = 2 address units apart); `first_acc`
+// is the accumulate flag of the first one, the others always accumulate.
+__device__ __forceinline__ void umma_f16_kblock(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint32_t first_acc) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t.reg .b64 da, db;\n\t.reg .b32 al, bl;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "setp.eq.b32 q, 0, 0;\n\t"
+      "mov.b64 da, {%1, %5};\n\tmov.b64 db, {%2, %5};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, p;\n\t"
+      "add.u32 al, %1, 2;\n\tadd.u32 bl, %2, 2;\n\tmov.b64 da, {al, %5};\n\tmov.b64 db, {bl, %5};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, q;\n\t"
+      "add.u32 al, %1, 4;\n\tadd.u32 bl, %2, 4;\n\tmov.b64 da, {al, %5};\n\tmov.b64 db, {bl, %5};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, q;\n\t"
+      "add.u32 al, %1, 6;\n\tadd.u32 bl, %2, 6;\n\tmov.b64 da, {al, %5};\n\tmov.b64 db, {bl, %5};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, q;\n\t}"
+      ::"r"(tmem_d), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(first_acc), "r"(DESC_SW128_HI) : "memory");
+}
+
 // 32 lanes x 32 consecutive fp32 columns: thread i of the warp receives row (lane base + i).
 __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, float (&v)[32]) {
   uint32_t r[32];
