@@ -1039,6 +1039,158 @@ __global__ void __launch_bounds__(PCfg<BN, TS>::THREADS, 1)
   if (warp == 1) { tc5::tc_fence_after(); tc5::tmem_dealloc(tmem_base, 2 * BN); }
 }
 
+// ---- CTA-pair kernel: 256 x 256 tiles on two SMs (cta_group::2) ------------------------------------
+// A 128 x 256 tile per CTA needs 48 KB of operands per 4.2 MFLOP; at the rate the L2 feeds the SMs
+// (measured ~11 TB/s over all SMs) that bounds the persistent kernel at ~1 PFLOP/s.  Here the two CTAs
+// of a cluster share one 256 x 256 tile: each loads its own 128 rows of A and its own 128 of the 256 B
+// rows (32 KB per k-block and CTA for the same 4.2 MFLOP), rank 0 issues M = 256 MMAs that read both
+// CTAs' shared memory and write both CTAs' tensor memory.  Linear layers only; the epilogue is the plain
+// one (accumulator rows -> registers -> global), overlapped with the next tile through the two accumulators.
+// warps: 0 / 7 activation producers, 6 / 8 weight producers, 1 MMA (rank 0) and TMEM, 2-5 epilogue.
+constexpr int PAIR_BN = 256, PAIR_ST = 6, PAIR_THREADS = 288;
+constexpr int PAIR_A_STAGE = BM * BK * 2, PAIR_B_STAGE = (PAIR_BN / 2) * BK * 2, PAIR_STAGE = PAIR_A_STAGE + PAIR_B_STAGE;
+constexpr int PAIR_SMEM = PAIR_ST * PAIR_STAGE + 1024;
+
+template <typename T>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
+    gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, const Tc5Params p, const int tiles_m,
+                     const int n_tiles) {
+  constexpr int ST = PAIR_ST, BN = PAIR_BN;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  // full_bar / acc_empty are used in rank 0 only (its MMA thread waits on them); empty_bar / acc_full in both
+  __shared__ __align__(8) uint64_t full_bar[ST], empty_bar[ST], acc_full[2], acc_empty[2];
+  __shared__ uint32_t tmem_holder;
+  __shared__ int failed;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = tc5::cluster_ctarank();
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  const int KB = static_cast<int>((p.K + BK - 1) / BK);
+  if (threadIdx.x == 0) {
+    failed = 0;
+    for (int s = 0; s < ST; ++s) { tc5::mbar_init(&full_bar[s], 2); tc5::mbar_init(&empty_bar[s], 1); }   // full: rank 0's two producers of the k-block
+    for (int b = 0; b < 2; ++b) { tc5::mbar_init(&acc_full[b], 1); tc5::mbar_init(&acc_empty[b], 8); }     // empty: four epilogue warps of each CTA
+    tc5::fence_barrier_init();
+    tc5::prefetch_tensormap(&map_a);
+    tc5::prefetch_tensormap(&map_w);
+  }
+  if (warp == 1) { tc5::tmem_alloc_pair(&tmem_holder, 2 * BN); tc5::tmem_relinquish_pair(); }
+  tc5::tc_fence_before();
+  __syncthreads();
+  tc5::cluster_sync();   // the peer's barriers exist before anything arrives on them
+  tc5::tc_fence_after();
+  const uint32_t tmem_base = tmem_holder;
+  pdl_trigger();
+  auto dead = [&]() { return *reinterpret_cast<volatile int*>(&failed) != 0; };
+  const uint32_t ring_addr = tc5::smem_addr(smem), full0 = tc5::smem_addr(&full_bar[0]), empty0 = tc5::smem_addr(&empty_bar[0]);
+
+  const int a_id = warp == 0 ? 0 : warp == 7 ? 1 : -1, b_id = warp == 6 ? 0 : warp == 8 ? 1 : -1;
+  if (a_id >= 0 || b_id >= 0) {
+    // ---- producers: k-blocks alternate between the two threads of an operand (2 <= ring depth) ----
+    if (lane == 0) {
+      const bool is_a = a_id >= 0;
+      const int mine = is_a ? a_id : b_id;
+      if (is_a || !(p.epilogue & B200_EPI_W_STATIC)) pdl_wait();
+      const CUtensorMap* map = is_a ? &map_a : &map_w;
+      const uint32_t lead_full0 = tc5::map_to_rank(full0, 0);
+      int it = 0, s = 0;
+      uint32_t ph = 0, dst = ring_addr + (is_a ? 0 : PAIR_A_STAGE);
+      const uint32_t dst0 = dst;
+      bool alive = true;
+      for (int tile = pair; tile < n_tiles && alive && !dead(); tile += n_pairs) {
+        const int row0 = (is_a ? (tile % tiles_m) : (tile / tiles_m)) * 256 + static_cast<int>(rank) * 128;   // this CTA's half
+        for (int kb = 0; kb < KB; ++kb, ++it) {
+          if ((it & 1) == mine) {
+            if (!tc5::mbar_wait_a(empty0 + 8u * s, ph ^ 1u)) { failed = 1; atomicExch(&g_tc5_error, 40); alive = false; break; }
+            if (rank == 0) tc5::mbar_arrive_expect_tx_a(full0 + 8u * s, 2 * PAIR_A_STAGE);   // both CTAs' halves of this operand
+            tc5::tma_load_2d_pair(dst, map, lead_full0 + 8u * s, kb * BK, row0);
+          }
+          dst += PAIR_STAGE;
+          if (++s == ST) { s = 0; ph ^= 1u; dst = dst0; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      // ---- MMA issuer (rank 0 only) ----
+      constexpr uint32_t idesc = tc5::umma_idesc(256, BN, AbFormat<T>::value);
+      const uint32_t ring_lo = tc5::desc_sw128_lo(ring_addr);
+      const uint32_t acc_full0 = tc5::smem_addr(&acc_full[0]), acc_empty0 = tc5::smem_addr(&acc_empty[0]);
+      int ti = 0, s = 0;
+      uint32_t ph = 0, a_lo = ring_lo;
+      bool alive = true;
+      for (int tile = pair; tile < n_tiles && alive && !dead(); tile += n_pairs, ++ti) {
+        const int b = ti & 1;
+        if (!tc5::mbar_wait_a(acc_empty0 + 8u * b, ((ti >> 1) & 1) ^ 1)) { failed = 1; atomicExch(&g_tc5_error, 41); break; }
+        tc5::tc_fence_after();
+        const uint32_t acc = tmem_base + b * BN;
+        for (int kb = 0; kb < KB; ++kb) {
+          if (!tc5::mbar_wait_a(full0 + 8u * s, ph)) { failed = 1; atomicExch(&g_tc5_error, 42); alive = false; break; }
+          tc5::umma_f16_kblock_pair(acc, a_lo, a_lo + (PAIR_A_STAGE >> 4), idesc, kb);
+          tc5::umma_commit_pair(empty0 + 8u * s);   // frees the stage in both CTAs
+          a_lo += PAIR_STAGE >> 4;
+          if (++s == ST) { s = 0; ph ^= 1u; a_lo = ring_lo; }
+        }
+        if (!alive) break;
+        tc5::umma_commit_pair(acc_full0 + 8u * b);
+      }
+    }
+  } else if (warp < 6) {
+    // ---- epilogue: this CTA's 128 accumulator rows ----
+    const int q = warp & 3;
+    pdl_wait();
+    const bool glu = (p.epilogue & B200_EPI_GLU) != 0;
+    const uint32_t lead_acc_empty0 = tc5::map_to_rank(tc5::smem_addr(&acc_empty[0]), 0);
+    int ti = 0;
+    for (int tile = pair; tile < n_tiles; tile += n_pairs, ++ti) {
+      const int b = ti & 1;
+      const int64_t m = static_cast<int64_t>(tile % tiles_m) * 256 + rank * 128 + q * 32 + lane;
+      const int64_t n0 = static_cast<int64_t>(tile / tiles_m) * BN;
+      bool ok = true;
+      if (lane == 0) ok = tc5::mbar_wait(&acc_full[b], (ti >> 1) & 1);
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!ok && lane == 0) { failed = 1; atomicExch(&g_tc5_error, 43); }
+      ok = __all_sync(0xffffffffu, ok && !dead());
+      if (!ok) break;
+      tc5::tc_fence_after();
+      const uint32_t t_row = tmem_base + b * BN + (static_cast<uint32_t>(q * 32) << 16);
+      if (glu) {
+#pragma unroll 1
+        for (int c = 0; c < BN / 2; c += 16) {   // c counts gate columns: block c / 64 of 128 merged columns
+          float vg[16], vu[16];
+          const int col = (c >> 6) * 128 + (c & 63);
+          __syncwarp();
+          tc5::tmem_ld_32x16(t_row + col, vg);
+          tc5::tmem_ld_32x16(t_row + col + 64, vu);
+          tc5::tmem_ld_wait();
+          const int64_t nm = n0 + col;
+          if (m < p.M && nm < p.N) finish_glu_cols<T, 16>(p, vg, vu, m, nm, (n0 + (c >> 6) * 128) / 2 + (c & 63));
+        }
+      } else {
+        float va[16], vb[16];   // two units in flight: the next tcgen05.ld runs under the current unit's math
+        __syncwarp();
+        tc5::tmem_ld_32x16(t_row, va);
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          tc5::tmem_ld_wait();
+          tc5::tmem_ld_32x16(t_row + c + 16, vb);
+          if (m < p.M && n0 + c < p.N) finish_cols<T, 16>(p, va, m, n0 + c);
+          tc5::tmem_ld_wait();
+          if (c + 32 < BN) tc5::tmem_ld_32x16(t_row + c + 32, va);
+          if (m < p.M && n0 + c + 16 < p.N) finish_cols<T, 16>(p, vb, m, n0 + c + 16);
+        }
+      }
+      tc5::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) tc5::mbar_arrive_cluster(lead_acc_empty0 + 8u * b);   // this warp has drained its quarter of the accumulator
+    }
+  }
+  tc5::tc_fence_before();
+  __syncthreads();
+  tc5::cluster_sync();   // neither CTA leaves while the other may still signal its barriers or read its shared memory
+  if (warp == 1) { tc5::tc_fence_after(); tc5::tmem_dealloc_pair(tmem_base, 2 * BN); }
+}
+
 // ---- 7x7 / stride-2 stem convolution on the 8-channel padded input ------------------------------
 // The im2col route moves one 16-byte row per (pixel, tap): 7168 TMA rows per 128-pixel tile.  Here a
 // persistent CTA walks consecutive output rows of an image and keeps the input rows it needs in a
@@ -1555,6 +1707,39 @@ int launch_persistent(const Tc5Args& a, cudaStream_t st, const Tc5Conv* g = null
   return B200_OK;
 }
 
+// The CTA-pair kernel takes a linear layer when its 256 x 256 tiles give at least half of the 74 pairs a tile
+// (even half empty it beats 128-wide tiles on every SM) and the reduction is long enough to hide the plain epilogue.
+bool pair_shape(const Tc5Args& a) {
+  if (a.M <= 128 || a.N < 256 || a.K < 1024) return false;
+  return ceil_div(a.M, 256) * ceil_div(a.N, 256) >= 37;
+}
+
+template <typename T> int launch_pair(const Tc5Args& a, cudaStream_t st) {
+  static PerDevice<bool> configured_on;
+  bool* configured = configured_on.slot();
+  if (!configured) return B200_ENOTSUP;
+  if (!*configured) {
+    if (cudaFuncSetAttribute(gemm_pair_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM) != cudaSuccess) {
+      cudaGetLastError();
+      return B200_ENOTSUP;
+    }
+    *configured = true;
+  }
+  CUtensorMap ma, mw;
+  if (!make_map(&ma, a.A, a.M, a.K, a.lda, BM, a.dtype) || !make_map(&mw, a.W, a.N, a.K, a.ldw, PAIR_BN / 2, a.dtype)) return B200_ENOTSUP;
+  Tc5Params p = {};
+  p.bias = a.bias; p.residual = a.residual; p.aux = a.aux; p.out = a.out;
+  p.M = a.M; p.N = a.N; p.K = a.K; p.ldo = a.ldo; p.ldr = a.ldr; p.ldaux = a.ldaux;
+  p.bias_dtype = a.bias_dtype; p.epilogue = a.epilogue; p.splits = 1; p.kb_per_split = static_cast<int>(ceil_div(a.K, BK));
+  p.x = a.A;
+  const int64_t tiles_m = ceil_div(a.M, 256), tiles = tiles_m * ceil_div(a.N, PAIR_BN);
+  if (tiles >= (1ll << 30)) return B200_ENOTSUP;
+  const int pairs = static_cast<int>(tiles < sm_count() / 2 ? tiles : sm_count() / 2);
+  launch_pdl(gemm_pair_kernel<T>, dim3(2 * pairs), dim3(PAIR_THREADS), PAIR_SMEM, st, ma, mw, p, static_cast<int>(tiles_m), static_cast<int>(tiles));
+  B200_CHECK_LAUNCH("gemm_pair_kernel");
+  return B200_OK;
+}
+
 // Tile width of the persistent kernel for a shape, or 0 when the shape should stay on the
 // one-tile-per-CTA kernel (too few tiles to fill the SMs with wide tiles).
 int persistent_bn(int64_t M, int64_t N, int64_t K, bool glu, bool residual) {
@@ -1662,6 +1847,10 @@ int linear_tc5(const Tc5Args& a, cudaStream_t st) {
                         (a.bias && a.bias_dtype != B200_F32 && a.bias_dtype != tb) ||
                         (a.residual && ((reinterpret_cast<uintptr_t>(a.residual) & 7u) || a.ldr % 4))))
       return B200_ENOTSUP;
+  }
+  if (pair_shape(a)) {
+    const int rc = a.dtype == B200_BF16 ? launch_pair<__nv_bfloat16>(a, st) : launch_pair<__half>(a, st);
+    if (rc != B200_ENOTSUP) return rc;
   }
   if (const int bn = persistent_bn(a.M, a.N, a.K, glu, a.residual != nullptr)) return dispatch_persistent<false>(bn, a, st, nullptr);
   const Tc5Plan pl = plan_tc5(a.M, a.N, a.K, glu);

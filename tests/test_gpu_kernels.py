@@ -58,6 +58,10 @@ def close(got, ref, rtol=2e-2, atol=1e-2):
     (512, 8960, 1536, False, False, False, True),
     (300, 1000, 2048, True, False, True, False),
     (128, 151936 // 8, 1536, False, False, False, False),
+    # 256 x 256 tiles on CTA pairs: row tail (640 = 2 * 256 + 128), column tail, K tail, every epilogue term
+    (640, 8200, 1088, True, True, True, False),
+    (300, 16384, 1024, True, False, False, False),
+    (512, 8960, 1536, True, True, False, True),
 ])
 def test_linear(lib, dtype, M, N, K, bias, res, relu, silu):
     a, w = gen((M, K), dtype), gen((N, K), dtype, 1, 0.05)
