@@ -69,6 +69,8 @@ struct Tc5Params {
   const float* sumsq_in; float* sumsq_out;
   float norm_eps;
   int sumsq_in_cols;
+  // CTA-pair kernel with split-K (p.splits > 1): fp32 partial sums [split][M][N] instead of outputs
+  float* partial;
 };
 
 template <typename T> struct AbFormat;
@@ -161,6 +163,30 @@ __device__ __forceinline__ void finish_cols(const Tc5Params& p, float (&v)[CNT],
     for (int i = 0; i < CNT; ++i) v[i] = round_as<T>(silu_f32(round_as<T>(v[i]))) * x[i];
   }
   store_cols<T, CNT>(static_cast<T*>(p.out) + m * p.ldo + n, v, cnt);
+}
+
+// finish_cols with the residual already in registers (16 values as two 16-byte words); no silu_mul term
+template <typename T>
+__device__ __forceinline__ void finish_cols_res(const Tc5Params& p, float (&v)[16], int64_t m, int64_t n, const uint4& r0, const uint4& r1) {
+  const int cnt = static_cast<int>(p.N - n < 16 ? p.N - n : 16);
+  add_bias<16>(p, v, n, cnt);
+  float r[16], t[8];
+  unpack8<T>(r0, t);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) r[i] = t[i];
+  unpack8<T>(r1, t);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) r[8 + i] = t[i];
+#pragma unroll
+  for (int i = 0; i < 16; i += 2) {
+    round2<T>(v[i], v[i + 1]);
+    v[i] += r[i]; v[i + 1] += r[i + 1];
+  }
+  if (p.epilogue & B200_EPI_RELU) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = fmaxf(v[i], 0.f);
+  }
+  store_cols<T, 16>(static_cast<T*>(p.out) + m * p.ldo + n, v, cnt);
 }
 
 // gated-MLP epilogue: CNT gate accumulators (merged columns n_merged..) and the matching up
@@ -1066,6 +1092,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
   const uint32_t rank = tc5::cluster_ctarank();
   const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
   const int KB = static_cast<int>((p.K + BK - 1) / BK);
+  // Work units: (tile, split).  With split-K (few tiles, long reduction) a unit covers p.kb_per_split
+  // k-blocks of its tile and leaves fp32 partial sums in p.partial; a second kernel adds them up.
+  const int n_units = n_tiles * p.splits;
+  auto unit_kb0 = [&](int unit) { return (unit / n_tiles) * p.kb_per_split; };
+  auto unit_nkb = [&](int unit) { const int k0 = unit_kb0(unit); return (KB - k0 < p.kb_per_split ? KB - k0 : p.kb_per_split); };
   if (threadIdx.x == 0) {
     failed = 0;
     for (int s = 0; s < ST; ++s) { tc5::mbar_init(&full_bar[s], 2); tc5::mbar_init(&empty_bar[s], 1); }   // full: rank 0's two producers of the k-block
@@ -1097,9 +1128,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
       uint32_t ph = 0, dst = ring_addr + (is_a ? 0 : PAIR_A_STAGE);
       const uint32_t dst0 = dst;
       bool alive = true;
-      for (int tile = pair; tile < n_tiles && alive && !dead(); tile += n_pairs) {
+      for (int unit = pair; unit < n_units && alive && !dead(); unit += n_pairs) {
+        const int tile = unit % n_tiles;
         const int row0 = (is_a ? (tile % tiles_m) : (tile / tiles_m)) * 256 + static_cast<int>(rank) * 128;   // this CTA's half
-        for (int kb = 0; kb < KB; ++kb, ++it) {
+        const int kb0 = unit_kb0(unit), kb1 = kb0 + unit_nkb(unit);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           if ((it & 1) == mine) {
             if (!tc5::mbar_wait_a(empty0 + 8u * s, ph ^ 1u)) { failed = 1; atomicExch(&g_tc5_error, 40); alive = false; break; }
             if (rank == 0) tc5::mbar_arrive_expect_tx_a(full0 + 8u * s, 2 * PAIR_A_STAGE);   // both CTAs' halves of this operand
@@ -1119,12 +1152,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
       int ti = 0, s = 0;
       uint32_t ph = 0, a_lo = ring_lo;
       bool alive = true;
-      for (int tile = pair; tile < n_tiles && alive && !dead(); tile += n_pairs, ++ti) {
+      for (int unit = pair; unit < n_units && alive && !dead(); unit += n_pairs, ++ti) {
         const int b = ti & 1;
         if (!tc5::mbar_wait_a(acc_empty0 + 8u * b, ((ti >> 1) & 1) ^ 1)) { failed = 1; atomicExch(&g_tc5_error, 41); break; }
         tc5::tc_fence_after();
         const uint32_t acc = tmem_base + b * BN;
-        for (int kb = 0; kb < KB; ++kb) {
+        const int nkb = unit_nkb(unit);
+        for (int kb = 0; kb < nkb; ++kb) {
           if (!tc5::mbar_wait_a(full0 + 8u * s, ph)) { failed = 1; atomicExch(&g_tc5_error, 42); alive = false; break; }
           tc5::umma_f16_kblock_pair(acc, a_lo, a_lo + (PAIR_A_STAGE >> 4), idesc, kb);
           tc5::umma_commit_pair(empty0 + 8u * s);   // frees the stage in both CTAs
@@ -1140,12 +1174,26 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
     const int q = warp & 3;
     pdl_wait();
     const bool glu = (p.epilogue & B200_EPI_GLU) != 0;
+    const bool res_fast = p.splits == 1 && !glu && p.residual && !(p.epilogue & B200_EPI_SILU_MUL) && p.ldr % 8 == 0 && p.N % 8 == 0 &&
+                          (reinterpret_cast<uintptr_t>(p.residual) & 15u) == 0;
     const uint32_t lead_acc_empty0 = tc5::map_to_rank(tc5::smem_addr(&acc_empty[0]), 0);
     int ti = 0;
-    for (int tile = pair; tile < n_tiles; tile += n_pairs, ++ti) {
+    for (int unit = pair; unit < n_units; unit += n_pairs, ++ti) {
       const int b = ti & 1;
+      const int tile = unit % n_tiles;
       const int64_t m = static_cast<int64_t>(tile % tiles_m) * 256 + rank * 128 + q * 32 + lane;
       const int64_t n0 = static_cast<int64_t>(tile / tiles_m) * BN;
+      // Residual rows are read 32 columns (four 16-byte words) at a time, one step ahead of their use and the
+      // first step before the accumulator is waited for: a load per step issued and consumed in place would
+      // put an L2 round trip between any two steps of this thread's row.
+      uint4 rc[4], rn[4];
+      const T* rrow = res_fast && m < p.M ? static_cast<const T*>(p.residual) + m * p.ldr + n0 : nullptr;
+      auto fetch = [&](int c, uint4 (&r)[4]) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          r[j] = (rrow && n0 + c + 8 * j < p.N) ? __ldg(reinterpret_cast<const uint4*>(rrow + c) + j) : make_uint4(0u, 0u, 0u, 0u);
+      };
+      if (res_fast) fetch(0, rc);
       bool ok = true;
       if (lane == 0) ok = tc5::mbar_wait(&acc_full[b], (ti >> 1) & 1);
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
@@ -1154,7 +1202,35 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
       if (!ok) break;
       tc5::tc_fence_after();
       const uint32_t t_row = tmem_base + b * BN + (static_cast<uint32_t>(q * 32) << 16);
-      if (glu) {
+      if (res_fast) {
+        float va[16], vb[16];
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          __syncwarp();
+          tc5::tmem_ld_32x16(t_row + c, va);
+          tc5::tmem_ld_32x16(t_row + c + 16, vb);
+          if (c + 32 < BN) fetch(c + 32, rn);
+          tc5::tmem_ld_wait();
+          if (m < p.M && n0 + c < p.N) finish_cols_res<T>(p, va, m, n0 + c, rc[0], rc[1]);
+          if (m < p.M && n0 + c + 16 < p.N) finish_cols_res<T>(p, vb, m, n0 + c + 16, rc[2], rc[3]);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) rc[j] = rn[j];
+        }
+      } else if (p.splits > 1) {   // raw partial sums of this unit's k-range (N % 4 == 0: whole float4s inside the row)
+        float* dst = p.partial + (static_cast<int64_t>(unit / n_tiles) * p.M + m) * p.N + n0;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 16) {
+          float v[16];
+          __syncwarp();
+          tc5::tmem_ld_32x16(t_row + c, v);
+          tc5::tmem_ld_wait();
+          if (m < p.M) {
+#pragma unroll
+            for (int i = 0; i < 16; i += 4)
+              if (n0 + c + i < p.N) *reinterpret_cast<float4*>(dst + c + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+          }
+        }
+      } else if (glu) {
 #pragma unroll 1
         for (int c = 0; c < BN / 2; c += 16) {   // c counts gate columns: block c / 64 of 128 merged columns
           float vg[16], vu[16];
@@ -1189,6 +1265,29 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
   __syncthreads();
   tc5::cluster_sync();   // neither CTA leaves while the other may still signal its barriers or read its shared memory
   if (warp == 1) { tc5::tc_fence_after(); tc5::tmem_dealloc_pair(tmem_base, 2 * BN); }
+}
+
+// Second half of the pair kernel's split-K: out = epilogue(sum over splits of the fp32 partial sums), eight
+// consecutive columns per thread, splits added in index order (the result does not depend on timing); the
+// partial sums are zeroed behind the read, as every user of the shared split-K workspace leaves it.
+template <typename T>
+__global__ void __launch_bounds__(256) pair_splitk_reduce_kernel(const Tc5Params p) {
+  pdl_trigger();
+  pdl_wait();
+  const int64_t per_row = p.N / 8, total = p.M * per_row;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total; i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t m = i / per_row, n = (i - m * per_row) * 8;
+    const float* src = p.partial + m * p.N + n;
+    float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int s = 0; s < p.splits; ++s, src += p.M * p.N) {
+      float4* q = reinterpret_cast<float4*>(const_cast<float*>(src));
+      const float4 a = __ldcg(q), b = __ldcg(q + 1);
+      v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w; v[4] += b.x; v[5] += b.y; v[6] += b.z; v[7] += b.w;
+      q[0] = make_float4(0.f, 0.f, 0.f, 0.f);   // the workspace is shared with kernels that expect it zeroed
+      q[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    finish_cols<T, 8>(p, v, m, n);
+  }
 }
 
 // ---- 7x7 / stride-2 stem convolution on the 8-channel padded input ------------------------------
@@ -1714,7 +1813,23 @@ bool pair_shape(const Tc5Args& a) {
   return ceil_div(a.M, 256) * ceil_div(a.N, 256) >= 37;
 }
 
-template <typename T> int launch_pair(const Tc5Args& a, cudaStream_t st) {
+// Few tiles but a long reduction (the down projection of a 1024-token prompt: 24 tiles, K = 8960): the pairs
+// split K among themselves and leave fp32 partial sums in the caller's workspace.  Returns the split count (1: none).
+int pair_splits(int64_t M, int64_t N, int64_t K) {
+  if (M <= 128 || N < 256 || K < 4096 || N % 8) return 1;
+  const int64_t tiles = ceil_div(M, 256) * ceil_div(N, 256), KB = ceil_div(K, BK);
+  if (tiles >= 37 || tiles < 16) return 1;   // (fewer tiles: measured no better than the one-tile kernel's cluster split-K)
+  int64_t s = 74 / tiles;
+  if (s > KB / 16) s = KB / 16;   // at least 16 k-blocks per unit
+  if (s > 8) s = 8;
+  if (s < 2) return 1;
+  const int64_t per = ceil_div(KB, s);
+  return static_cast<int>(ceil_div(KB, per));
+}
+
+int64_t pair_splitk_bytes(int64_t M, int64_t N, int splits) { return splits > 1 ? splits * M * N * 4 : 0; }
+
+template <typename T> int launch_pair(const Tc5Args& a, cudaStream_t st, int splits = 1) {
   static PerDevice<bool> configured_on;
   bool* configured = configured_on.slot();
   if (!configured) return B200_ENOTSUP;
@@ -1730,13 +1845,23 @@ template <typename T> int launch_pair(const Tc5Args& a, cudaStream_t st) {
   Tc5Params p = {};
   p.bias = a.bias; p.residual = a.residual; p.aux = a.aux; p.out = a.out;
   p.M = a.M; p.N = a.N; p.K = a.K; p.ldo = a.ldo; p.ldr = a.ldr; p.ldaux = a.ldaux;
-  p.bias_dtype = a.bias_dtype; p.epilogue = a.epilogue; p.splits = 1; p.kb_per_split = static_cast<int>(ceil_div(a.K, BK));
+  p.bias_dtype = a.bias_dtype; p.epilogue = a.epilogue;
+  p.splits = splits; p.kb_per_split = static_cast<int>(ceil_div(ceil_div(a.K, BK), splits));
+  p.partial = static_cast<float*>(a.workspace);
   p.x = a.A;
-  const int64_t tiles_m = ceil_div(a.M, 256), tiles = tiles_m * ceil_div(a.N, PAIR_BN);
-  if (tiles >= (1ll << 30)) return B200_ENOTSUP;
-  const int pairs = static_cast<int>(tiles < sm_count() / 2 ? tiles : sm_count() / 2);
+  const int64_t tiles_m = ceil_div(a.M, 256), tiles = tiles_m * ceil_div(a.N, PAIR_BN), units = tiles * splits;
+  if (units >= (1ll << 30)) return B200_ENOTSUP;
+  if (splits > 1 && (!a.workspace || a.workspace_bytes < pair_splitk_bytes(a.M, a.N, splits) || (reinterpret_cast<uintptr_t>(a.workspace) & 15u)))
+    return B200_ENOTSUP;
+  const int pairs = static_cast<int>(units < sm_count() / 2 ? units : sm_count() / 2);
   launch_pdl(gemm_pair_kernel<T>, dim3(2 * pairs), dim3(PAIR_THREADS), PAIR_SMEM, st, ma, mw, p, static_cast<int>(tiles_m), static_cast<int>(tiles));
   B200_CHECK_LAUNCH("gemm_pair_kernel");
+  if (splits > 1) {
+    const int64_t work = a.M * (a.N / 8);
+    const int blocks = static_cast<int>(ceil_div(work, 256) < 4 * sm_count() ? ceil_div(work, 256) : 4 * sm_count());
+    launch_pdl(pair_splitk_reduce_kernel<T>, dim3(blocks), dim3(256), 0, st, p);
+    B200_CHECK_LAUNCH("pair_splitk_reduce_kernel");
+  }
   return B200_OK;
 }
 
@@ -1829,8 +1954,9 @@ bool tc5_enabled() {
   return state == 1;
 }
 
-// The tcgen05 path needs no global scratch: split-K partial sums meet in distributed shared memory.
-int64_t linear_tc5_workspace_bytes(int64_t, int64_t, int64_t) { return 0; }
+// Scratch of the tcgen05 path: none for the cluster split-K of the one-tile kernel (partial sums meet in
+// distributed shared memory); fp32 partial sums for the split-K of the CTA-pair kernel.
+int64_t linear_tc5_workspace_bytes(int64_t M, int64_t N, int64_t K) { return pair_splitk_bytes(M, N, pair_splits(M, N, K)); }
 
 int linear_tc5(const Tc5Args& a, cudaStream_t st) {
   if (!tc5_enabled()) return B200_ENOTSUP;
@@ -1850,6 +1976,10 @@ int linear_tc5(const Tc5Args& a, cudaStream_t st) {
   }
   if (pair_shape(a)) {
     const int rc = a.dtype == B200_BF16 ? launch_pair<__nv_bfloat16>(a, st) : launch_pair<__half>(a, st);
+    if (rc != B200_ENOTSUP) return rc;
+  }
+  if (const int ps = pair_splits(a.M, a.N, a.K); ps > 1 && !glu) {   // (falls through when the caller gave no workspace)
+    const int rc = a.dtype == B200_BF16 ? launch_pair<__nv_bfloat16>(a, st, ps) : launch_pair<__half>(a, st, ps);
     if (rc != B200_ENOTSUP) return rc;
   }
   if (const int bn = persistent_bn(a.M, a.N, a.K, glu, a.residual != nullptr)) return dispatch_persistent<false>(bn, a, st, nullptr);

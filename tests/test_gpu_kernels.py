@@ -62,6 +62,9 @@ def close(got, ref, rtol=2e-2, atol=1e-2):
     (640, 8200, 1088, True, True, True, False),
     (300, 16384, 1024, True, False, False, False),
     (512, 8960, 1536, True, True, False, True),
+    # few 256 x 256 tiles, long reduction: the pairs split K, a second kernel adds the fp32 partial sums
+    (1024, 1536, 8960, True, True, False, False),
+    (1000, 1200, 4104, False, False, True, False),
 ])
 def test_linear(lib, dtype, M, N, K, bias, res, relu, silu):
     a, w = gen((M, K), dtype), gen((N, K), dtype, 1, 0.05)
