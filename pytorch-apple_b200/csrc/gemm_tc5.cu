@@ -1809,7 +1809,9 @@ int launch_persistent(const Tc5Args& a, cudaStream_t st, const Tc5Conv* g = null
 // The CTA-pair kernel takes a linear layer when its 256 x 256 tiles give at least half of the 74 pairs a tile
 // (even half empty it beats 128-wide tiles on every SM) and the reduction is long enough to hide the plain epilogue.
 bool pair_shape(const Tc5Args& a) {
-  if (a.M <= 128 || a.N < 256 || a.K < 1024) return false;
+  // (N >= 1024: a tall activation matrix against one or two column tiles - the 1x1 convolutions 1024 -> 256 / 512
+  // over 50176 pixels - measured slower here than with the bulk-copy epilogue of the persistent kernel)
+  if (a.M <= 128 || a.N < 1024 || a.K < 1024) return false;
   return ceil_div(a.M, 256) * ceil_div(a.N, 256) >= 37;
 }
 
