@@ -62,7 +62,7 @@ struct Tc5Params {
   int pst, pstage;      // ring stages and bytes per stage
   int wr, w_off;        // weights resident: all k-blocks of the CTA's weight tile stay in shared memory at w_off
   int pncb, c_off;      // C buffers (bulk-copy epilogue) and where they start
-  int npa, npw;         // persistent kernel: activation / weight producer threads (1, 2 or 4), k-blocks dealt round-robin
+  int npa;              // persistent kernel: activation producer threads (1 or 2), k-blocks dealt round-robin
   int nfast;            // persistent kernel: column tiles fastest in the tile order
   // one-tile kernel, M <= 64: scale the output rows by the RMSNorm factor of the input rows / write
   // sum-of-squares partials of the output rows
@@ -652,13 +652,11 @@ template <int BN, bool TS> struct PCfg {
   static constexpr int MAX_ST = 12, MAX_NCB = 4;
   static constexpr int SMEM_LIMIT = 227 * 1024 - 1024;   // dynamic part; the barriers are static shared memory
   // warps: 0 activation producer, 1 MMA, 2-5 epilogue; TS adds 6 store, 7-10 second epilogue group
-  // (half the columns each); the gather variant adds 6-9 gather; then the weight producer, the second
-  // activation producer and, last, five more producers (activation 3 and 4, weight 2 to 4): a producer
-  // thread gets one copy through per ~0.3 us, a 128-wide k-block of MMAs takes 0.13 us
+  // (half the columns each); the gather variant adds 6-9 gather; then the weight producer and,
+  // last, the second activation producer
   static constexpr int W_WARP = TS ? 11 : 6;
   static constexpr int A2_WARP = TS ? 12 : 7;           // second activation producer
-  static constexpr int X_WARP = A2_WARP + 1;            // first of the five extra producers
-  static constexpr int THREADS = (X_WARP + 5) * 32;
+  static constexpr int THREADS = (A2_WARP + 1) * 32;
   static constexpr int W_WARP_GATHER = 10;
   static constexpr int EPI_WARPS = TS ? 8 : 4;
 };
@@ -723,13 +721,11 @@ __global__ void __launch_bounds__(PCfg<BN, TS>::THREADS, 1)
   pdl_trigger();
   auto dead = [&]() { return *reinterpret_cast<volatile int*>(&failed) != 0; };
 
-  // producer number of this warp among the activation / weight producers (-1: not one)
-  constexpr int XW = PCfg<BN, TS>::X_WARP;
-  const bool gather_variant = CONV && !TS && !p.g.im2col;   // launched with 352 threads: no extra producers
-  const int a_id = warp == 0 ? 0 : warp == PCfg<BN, TS>::A2_WARP ? 1 : (warp == XW || warp == XW + 1) ? warp - XW + 2 : -1;
-  const int w_id = warp == (gather_variant ? PCfg<BN, TS>::W_WARP_GATHER : PCfg<BN, TS>::W_WARP) ? 0 : (warp >= XW + 2 && warp <= XW + 4) ? warp - XW - 1 : -1;
+  const bool gather_variant = CONV && !TS && !p.g.im2col;   // launched with 352 threads
+  const int a_id = warp == 0 ? 0 : warp == PCfg<BN, TS>::A2_WARP ? 1 : -1;   // producer number among the activation producers (-1: not one)
   if (a_id >= 0 && a_id < p.npa) {
-    // ---- activation producers: the k-blocks are dealt round-robin to p.npa issuing threads ----
+    // ---- activation producers: with two, the k-blocks alternate between them (a 3x3 convolution is bound
+    // by how fast one thread gets its im2col boxes through; more than two measured no better) ----
     if (lane == 0) {
       pdl_wait();
       const int mine = a_id, deal = p.npa - 1;
@@ -778,8 +774,8 @@ __global__ void __launch_bounds__(PCfg<BN, TS>::THREADS, 1)
         for (int i = it > ST ? it - ST : 0; i < it; ++i) tc5::mbar_wait(&full_bar[i % ST], (i / ST) & 1, 1u << 16);
       }
     }
-  } else if (w_id >= 0 && w_id < (WR ? 1 : p.npw)) {
-    // ---- weight producers (one when the weights are resident) ----
+  } else if (warp == (gather_variant ? PCfg<BN, TS>::W_WARP_GATHER : PCfg<BN, TS>::W_WARP)) {
+    // ---- weight producer ----
     if (lane == 0) {
       if (!(p.epilogue & B200_EPI_W_STATIC)) pdl_wait();
       auto load_w = [&](uint8_t* dst, uint64_t* bar, int kb, int n0) {
@@ -814,12 +810,10 @@ __global__ void __launch_bounds__(PCfg<BN, TS>::THREADS, 1)
         for (int tile = blockIdx.x; tile < n_tiles && alive && !dead(); tile += gridDim.x) {
           const int n0 = tile_n(tile) * BN;
           for (int kb = 0; kb < KB; ++kb, ++it) {
-            if ((it & (p.npw - 1)) == w_id) {
-              if (!tc5::mbar_wait_a(empty0 + 8u * s, ph ^ 1u)) { failed = 1; atomicExch(&g_tc5_error, 19); alive = false; break; }
-              tc5::mbar_arrive_expect_tx_a(full0 + 8u * s, B_STAGE);
-              if (c8) load_w(smem + s * STAGE + A_STAGE, &full_bar[s], kb, n0);
-              else tc5::tma_load_2d_a(dst, &map_w, full0 + 8u * s, kb * BK, n0);
-            }
+            if (!tc5::mbar_wait_a(empty0 + 8u * s, ph ^ 1u)) { failed = 1; atomicExch(&g_tc5_error, 19); alive = false; break; }
+            tc5::mbar_arrive_expect_tx_a(full0 + 8u * s, B_STAGE);
+            if (c8) load_w(smem + s * STAGE + A_STAGE, &full_bar[s], kb, n0);
+            else tc5::tma_load_2d_a(dst, &map_w, full0 + 8u * s, kb * BK, n0);
             dst += STAGE;
             if (++s == ST) { s = 0; ph ^= 1u; dst = ring_addr; }
           }
@@ -1790,16 +1784,11 @@ int launch_persistent(const Tc5Args& a, cudaStream_t st, const Tc5Conv* g = null
       break;
     }
   }
-  // Producer threads (none extra for the gather variant): a power of two, at most the k-blocks of a tile
-  // and at most the ring depth.  The depth bound is a correctness condition: a producer learns how far the
-  // MMAs have got only from its own waits, one ring pass back at a time; dealt more than `depth` apart it
-  // could meet a barrier two phases behind, which a parity wait cannot tell from the phase it expects.
-  p.npa = p.npw = 1;
-  if (!CONV || p.g.im2col) {
-    const int64_t kbs = ceil_div(a.K, BK);
-    const int64_t cap = kbs < p.pst ? kbs : p.pst;
-    p.npa = p.npw = cap >= 4 ? 4 : cap >= 2 ? 2 : 1;
-  }
+  // Two activation producers for convolutions through im2col boxes.  (Dealing k-blocks to more threads than the
+  // ring has stages would be wrong, not just useless: a producer learns how far the MMAs have got only from its
+  // own waits, one ring pass back at a time, and a parity wait cannot tell a barrier two phases behind from the
+  // phase it expects.  Two is below every ring depth used here.)
+  p.npa = CONV && p.g.im2col && ceil_div(a.K, BK) >= 2 ? 2 : 1;
   launch_pdl(gemm_tc5p_kernel<T, BN, CONV, TS>, dim3(grid), dim3((CONV && !TS && !p.g.im2col) ? 352 : PC::THREADS), SMEM, st, ma, mw, mr, mo, p,
              static_cast<int>(tiles_m), static_cast<int>(tiles));
   B200_CHECK_LAUNCH("gemm_tc5p_kernel");
@@ -1871,7 +1860,9 @@ template <typename T> int launch_pair(const Tc5Args& a, cudaStream_t st, int spl
 // one-tile-per-CTA kernel (too few tiles to fill the SMs with wide tiles).
 int persistent_bn(int64_t M, int64_t N, int64_t K, bool glu, bool residual) {
   const int64_t tm = ceil_div(M, BM);
-  if (tm < 2) return 0;
+  // One row tile: the one-tile kernel, except for a very wide N (the vocabulary projection of a decode step:
+  // 1187 one-tile CTAs run in eight waves and pay their start-up eight times; measured 123 us for 467 MB).
+  if (tm < 2) return (K > 512 && ceil_div(N, 256) >= 2 * 148) ? 256 : 0;
   // short reductions are memory-bound: 128-wide tiles leave room for two C buffers (see PCfg)
   // (a tile wider than N only multiplies and copies padding: 64 output channels take 64-wide tiles)
   if (K > 512 && N > 128 && ceil_div(N, 256) * tm >= 2 * 148) return 256;
@@ -1984,7 +1975,8 @@ int linear_tc5(const Tc5Args& a, cudaStream_t st) {
     const int rc = a.dtype == B200_BF16 ? launch_pair<__nv_bfloat16>(a, st, ps) : launch_pair<__half>(a, st, ps);
     if (rc != B200_ENOTSUP) return rc;
   }
-  if (const int bn = persistent_bn(a.M, a.N, a.K, glu, a.residual != nullptr)) return dispatch_persistent<false>(bn, a, st, nullptr);
+  if (const int bn = (a.sumsq_in || a.sumsq_out) ? 0 : persistent_bn(a.M, a.N, a.K, glu, a.residual != nullptr))
+    return dispatch_persistent<false>(bn, a, st, nullptr);
   const Tc5Plan pl = plan_tc5(a.M, a.N, a.K, glu);
   if (pl.tiles_m > 65535 || pl.splits > 65535) return B200_ENOTSUP;
   if (pl.tiles_m == 1 && a.M <= 64) {
