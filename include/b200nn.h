@@ -247,10 +247,15 @@ int b200_conv_weight_prep(const void* w, const void* conv_bias, const void* gamm
  * A, W, out, residual share `dtype` (f16/bf16), fp32 accumulation; bias dtype is
  * `bias_dtype`.  lda/ldw/ldo/ldr are row strides in elements.  Any M.  Operands that
  * meet the TMA rules (16-byte aligned, strides multiples of 8 elements) run on the
- * tcgen05 path, which needs no scratch (split-K partial sums meet in distributed shared
- * memory).  Other operands with M <= 64 fall back to a weight-streaming kernel whose
- * split-K uses `workspace` (zero-initialised by the caller once, left zeroed by every
- * call; b200_linear_workspace_bytes gives the size, 0 when none is needed). */
+ * tcgen05 path: one tile per CTA with split-K inside a thread-block cluster (partial sums
+ * meet in distributed shared memory, no scratch) for M <= 128 and for shapes with few
+ * tiles, a persistent kernel with 128 x 64..256 tiles, or 256 x 256 tiles on pairs of CTAs
+ * (cta_group::2) for M > 128, N >= 1024, K >= 1024.  `workspace` (zero-initialised by the
+ * caller once, left zeroed by every call; b200_linear_workspace_bytes gives the size, 0
+ * when none is needed) serves two cases: the pair kernel's split-K for 16..36 tiles with
+ * K >= 4096 (fp32 partial sums, added in index order by a second kernel; without a
+ * workspace the shape takes the cluster split-K instead), and the weight-streaming
+ * fallback for operands with M <= 64 that miss the TMA rules. */
 int b200_linear(const void* A, const void* W, const void* bias, const void* residual, void* out,
                 int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldw, int64_t ldo, int64_t ldr,
                 int dtype, int bias_dtype, int epilogue, const void* aux, int64_t ldaux,
@@ -305,8 +310,8 @@ int b200_conv2d_nhwc(const void* x, const void* w, const float* bias, const void
  *   k,v: [B, Hkv, S, D] caches, row stride D, head stride S*D
  *   mask:[B, S] additive (the graph's attention_mask [B,1,1,S]); NULL = none
  *   out: [B, Hq, D]
- * Split-KV: for caches of 512..5120 rows (and at most 8 query heads per KV head) the eight splits of
- * a (sequence, KV head) form a thread-block cluster and merge in distributed shared memory
+ * Split-KV: for caches of 512..16384 rows (and at most 8 query heads per KV head) the up to eight splits
+ * of a (sequence, KV head) form a thread-block cluster and merge in distributed shared memory
  * (no workspace: b200_attn_decode_workspace_bytes returns 0); otherwise partial
  * (max, sum, acc) per split go to `workspace` and are merged by a second kernel.  Key blocks whose mask entries are all <= -1e30 are skipped, which
  * leaves the result unchanged because their softmax weight underflows to 0. */
@@ -321,8 +326,8 @@ int64_t b200_attn_decode_workspace_bytes(int64_t B, int Hq, int Hkv, int64_t S, 
  * it was handed, code running where cudaMalloc is off limits).  This entry point has no
  * counterpart in the reference.  The split-KV partials go to an 8 MiB array that is part
  * of the library image (each GPU that loads the library holds it until exit); shapes whose
- * partials need more return B200_ELIMIT (caches up to 5120 rows need none:
- * their splits merge inside the kernel; Hq=12, Hkv=2, S=8192 is refused for B > 84).  No
+ * partials need more return B200_ELIMIT (caches of 512..16384 rows need none: their splits
+ * merge inside the kernel; Hq=12, Hkv=2, S=32768 is refused for B > 21).  No
  * cudaMalloc, cudaFree or allocating library call is made.  The first call on a device
  * looks up the array's device address; make that call before any stream capture.  All
  * calls share the array: two calls whose kernels overlap on the GPU (different streams)
