@@ -282,6 +282,28 @@ int b200_linear_norm(const void* A, const void* W, const void* bias, const void*
                      int dtype, int bias_dtype, int epilogue, float norm_eps,
                      const float* sumsq_in, int sumsq_in_cols, float* sumsq_out, void* stream);
 
+/* The merged q/k/v projection of a decode step (one token per sequence, M = sequences <= 64)
+ * with everything that follows it before attention: replaces the three CUBLASStep("gemm")
+ * projections (cuda_executor.py:182-208), the `rope_kernel` launches on q and k
+ * (cuda_templates.py:114-132) and the two `index_copy_kernel` KV-cache writes
+ * (cuda_templates.py:134-162).  W holds the q, k and v weight rows one after the other,
+ * N = (Hq + 2 Hkv) * 128 (head dimension 128); columns [128 h, 128 h + 128) are head h.
+ * The kernel's final pass adds the bias, rounds to the 16-bit type as the linear layer's
+ * output is rounded, applies x * cos + rotate_half(x) * sin to query and key heads with the
+ * roundings of the unfused operators (both products, then the sum) and stores
+ *   rope(q) to q_out [M, Hq, 128],
+ *   rope(k) and v to row cache_pos[0] of k_cache / v_cache [M, Hkv, cache_len, 128] (in place;
+ *   a negative position counts from the end, a position outside the cache writes nothing).
+ * cos_t / sin_t: [M, 128] tables of the rows' positions in the activation type.  sumsq_in /
+ * sumsq_in_cols / norm_eps as in b200_linear_norm (NULL: no row scaling).  epilogue: 0 or
+ * B200_EPI_W_STATIC.  Results are bit-identical to b200_linear_norm followed by
+ * b200_qkv_rope_cache.  B200_ENOTSUP when the operands do not fit the fused kernel. */
+int b200_linear_qkv_rope(const void* A, const void* W, const void* bias, int64_t M, int64_t N, int64_t K,
+                         int64_t lda, int64_t ldw, int dtype, int bias_dtype, int epilogue, float norm_eps,
+                         const float* sumsq_in, int sumsq_in_cols, const void* cos_t, const void* sin_t,
+                         void* q_out, void* k_cache, void* v_cache, const void* cache_pos, int64_t cache_len,
+                         int pos_dtype, int Hq, int Hkv, void* stream);
+
 /* CUBLASStep("gemm_batched") and plain 2-D matmul (subgraph_analyzer.py:206-224,
  * dispatch cuda_executor.py:210-218): out[b1,b2,M,N] = A[b1,b2,M,K] @ B[b1,b2,K,N] with
  * independent element strides for every axis of every operand (0 = broadcast), so

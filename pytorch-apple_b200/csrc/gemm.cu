@@ -608,6 +608,31 @@ extern "C" int b200_conv2d_nhwc(const void* x, const void* w, const float* bias,
   return B200_OK;
 }
 
+extern "C" int b200_linear_qkv_rope(const void* A, const void* W, const void* bias, int64_t M, int64_t N, int64_t K, int64_t lda,
+                                    int64_t ldw, int dtype, int bias_dtype, int epilogue, float norm_eps, const float* sumsq_in,
+                                    int sumsq_in_cols, const void* cos_t, const void* sin_t, void* q_out, void* k_cache,
+                                    void* v_cache, const void* cache_pos, int64_t cache_len, int pos_dtype, int Hq, int Hkv,
+                                    void* stream) {
+  B200_CHECK_ARG(A && W && cos_t && sin_t && q_out && k_cache && v_cache && cache_pos && M >= 0 && N > 0 && K > 0 && Hq > 0 && Hkv > 0 &&
+                 cache_len > 0, "b200_linear_qkv_rope: bad arguments");
+  B200_CHECK_ARG(N == static_cast<int64_t>(Hq + 2 * Hkv) * 128, "b200_linear_qkv_rope: N must be (Hq + 2 Hkv) * 128 (head dimension 128)");
+  B200_CHECK_ARG(!(epilogue & ~B200_EPI_W_STATIC), "b200_linear_qkv_rope: no epilogue terms besides the bias");
+  B200_CHECK_ARG(!sumsq_in || sumsq_in_cols > 0, "b200_linear_qkv_rope: sumsq_in needs its column count");
+  if (M == 0) return B200_OK;
+  if (M > 64) B200_FAIL(B200_ENOTSUP, "b200_linear_qkv_rope: M = %lld; one token per sequence and at most 64 sequences", (long long)M);
+  if (!(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0 && aligned16(A) && aligned16(W)))
+    B200_FAIL(B200_EALIGN, "b200_linear_qkv_rope: K, lda, ldw must be multiples of 8 and A, W 16-byte aligned");
+  Tc5Args t{A, W, bias, nullptr, nullptr, nullptr, M, N, K, lda, ldw, 0, 0, 0, dtype, bias_dtype, epilogue, nullptr, 0};
+  t.norm_eps = norm_eps; t.sumsq_in = sumsq_in; t.sumsq_in_cols = sumsq_in_cols;
+  t.rope.cos = cos_t; t.rope.sin = sin_t; t.rope.q_out = q_out; t.rope.k_cache = k_cache; t.rope.v_cache = v_cache;
+  t.rope.cache_pos = cache_pos; t.rope.cache_len = cache_len; t.rope.Hq = Hq; t.rope.Hkv = Hkv; t.rope.pos_dtype = pos_dtype;
+  const int rc = linear_tc5(t, static_cast<cudaStream_t>(stream));
+  if (rc == B200_ENOTSUP)
+    B200_FAIL(B200_ENOTSUP, "b200_linear_qkv_rope: operands outside the fused kernel's rules (16-byte aligned tables and destinations, "
+                            "int32 / int64 position, at most 32 sum-of-squares partials per row)");
+  return rc;
+}
+
 extern "C" int b200_matmul_strided(const void* A, const void* B, void* out, int64_t b1, int64_t b2, int64_t M, int64_t N,
                                    int64_t K, const int64_t a_strides[4], const int64_t b_strides[4],
                                    const int64_t o_strides[4], int dtype, void* stream) {

@@ -71,6 +71,8 @@ struct Tc5Params {
   int sumsq_in_cols;
   // CTA-pair kernel with split-K (p.splits > 1): fp32 partial sums [split][M][N] instead of outputs
   float* partial;
+  // one-tile kernel, M <= 64, 128-wide tiles: rotary embedding + q / KV-cache destinations in the final pass
+  Tc5Args::Rope rope;
 };
 
 template <typename T> struct AbFormat;
@@ -207,6 +209,50 @@ __device__ __forceinline__ void finish_glu_cols(const Tc5Params& p, float (&g)[C
   store_cols<T, CNT>(static_cast<T*>(p.out) + m * p.ldo + n_out, g, CNT);
 }
 
+// Final pass of the merged q/k/v projection of a decode step: `lo` / `hi` are columns col..col+3 and
+// col+64..col+67 of head `head` (a 128-wide tile) for sequence b.  Adds the bias, rounds to T as the linear
+// layer's output is rounded, applies x*cos + rotate_half(x)*sin with the roundings of the unfused
+// operators (both products, then the sum) to query and key heads, and stores to rope(q) / the cache rows.
+template <typename T>
+__device__ __forceinline__ void finish_rope4(const Tc5Params& p, const float4& lo4, const float4& hi4, int64_t b, int head, int col) {
+  float lo[4] = {lo4.x, lo4.y, lo4.z, lo4.w}, hi[4] = {hi4.x, hi4.y, hi4.z, hi4.w};
+  const int64_t n = static_cast<int64_t>(head) * 128 + col;
+  add_bias<4>(p, lo, n, 4);
+  add_bias<4>(p, hi, n + 64, 4);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { lo[i] = round_as<T>(lo[i]); hi[i] = round_as<T>(hi[i]); }
+  const Tc5Args::Rope& r = p.rope;
+  const int which = head < r.Hq ? 0 : (head < r.Hq + r.Hkv ? 1 : 2);
+  if (which != 2) {
+    const T* cs = static_cast<const T*>(r.cos) + b * 128 + col;
+    const T* sn = static_cast<const T*>(r.sin) + b * 128 + col;
+    float c0, c1, c2, c3, s0, s1, s2, s3, d0, d1, d2, d3, t0, t1, t2, t3;
+    const uint2 cl = *reinterpret_cast<const uint2*>(cs), ch = *reinterpret_cast<const uint2*>(cs + 64);
+    const uint2 sl = *reinterpret_cast<const uint2*>(sn), sh = *reinterpret_cast<const uint2*>(sn + 64);
+    unpack2<T>(cl.x, c0, c1); unpack2<T>(cl.y, c2, c3); unpack2<T>(sl.x, s0, s1); unpack2<T>(sl.y, s2, s3);
+    unpack2<T>(ch.x, d0, d1); unpack2<T>(ch.y, d2, d3); unpack2<T>(sh.x, t0, t1); unpack2<T>(sh.y, t2, t3);
+    const float cl4[4] = {c0, c1, c2, c3}, sl4[4] = {s0, s1, s2, s3}, ch4[4] = {d0, d1, d2, d3}, sh4[4] = {t0, t1, t2, t3};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float a = lo[i], h = hi[i];
+      lo[i] = round_as<T>(a * cl4[i]) + round_as<T>(-h * sl4[i]);
+      hi[i] = round_as<T>(h * ch4[i]) + round_as<T>(a * sh4[i]);
+    }
+  }
+  T* dst;
+  if (which == 0) {
+    dst = static_cast<T*>(r.q_out) + (b * r.Hq + head) * 128;
+  } else {
+    int64_t pos = load_index(r.cache_pos, 0, r.pos_dtype);
+    if (pos < 0) pos += r.cache_len;
+    if (pos < 0 || pos >= r.cache_len) return;
+    const int hk = head - r.Hq - (which == 2 ? r.Hkv : 0);
+    dst = static_cast<T*>(which == 1 ? r.k_cache : r.v_cache) + ((b * r.Hkv + hk) * r.cache_len + pos) * 128;
+  }
+  *reinterpret_cast<uint2*>(dst + col) = make_uint2(pack2<T>(lo[0], lo[1]), pack2<T>(lo[2], lo[3]));
+  *reinterpret_cast<uint2*>(dst + col + 64) = make_uint2(pack2<T>(hi[0], hi[1]), pack2<T>(hi[2], hi[3]));
+}
+
 // four consecutive outputs of row m starting at column n (split-K final pass)
 template <typename T>
 __device__ __forceinline__ void finish4(const Tc5Params& p, const float4& acc, int64_t m, int64_t n) {
@@ -293,6 +339,7 @@ __global__ void __launch_bounds__(224, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(cons
   const bool gather = CONV && !p.g.im2col;   // convolution A tile copied by the epilogue warps instead of TMA
   const bool staged = !CONV && (MODE >= 1 || p.splits > 1);   // MODE >= 1: known at compile time, the direct epilogue is dropped
   const bool glu = (p.epilogue & B200_EPI_GLU) != 0;       // host guarantees BN == 128 and N % 128 == 0
+  const bool rope = CAN_NORM && BN == 128 && p.rope.cos != nullptr;   // tile = one attention head (host: BN == 128, N % 128 == 0)
   const int rows_valid = static_cast<int>(p.M - m0 < BM ? p.M - m0 : BM);
   constexpr int PART_PITCH = BN + 4;                      // floats; rows 16 bytes apart in bank space
   // fp32 staging tile: the ring itself without split-K (it is free once the last MMA has completed);
@@ -549,7 +596,8 @@ __global__ void __launch_bounds__(224, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(cons
       // All 224 threads walk the owned rows as float4 units in row-major order.  The loop body is
       // kept short: it runs a handful of times per thread, so its cost is instruction count.
       constexpr int LOG_UNITS = BN == 64 ? 4 : 5;              // float4 units per tile row (staged tiles are 64 or 128 wide)
-      const int log_pr = glu ? 4 : LOG_UNITS;                  // gated: the 16 units of gate columns, each paired with +64
+      const bool paired = glu || rope;
+      const int log_pr = paired ? 4 : LOG_UNITS;               // gated / rotary: the 16 units of columns 0..63, each paired with +64
       const int my_rows = max(0, min(rpo, rows_valid - rank * rpo));
       const int total = my_rows << log_pr;
       const int slot = rpo * PART_PITCH;                       // floats between the slots of two ranks
@@ -564,13 +612,13 @@ __global__ void __launch_bounds__(224, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(cons
         const int lr = idx >> log_pr, col = (idx & ((1 << log_pr) - 1)) << 2;
         const float* src = part + lr * PART_PITCH + col;
         float4 acc = *reinterpret_cast<const float4*>(src), up = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (glu) up = *reinterpret_cast<const float4*>(src + 64);
+        if (paired) up = *reinterpret_cast<const float4*>(src + 64);
 #pragma unroll 1
         for (int s = 1; s < nsp; ++s) {
           src += slot;
           const float4 t = *reinterpret_cast<const float4*>(src);
           acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w;
-          if (glu) {
+          if (paired) {
             const float4 u = *reinterpret_cast<const float4*>(src + 64);
             up.x += u.x; up.y += u.y; up.z += u.z; up.w += u.w;
           }
@@ -584,6 +632,8 @@ __global__ void __launch_bounds__(224, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(cons
         }
         if (glu) {
           finish_glu4<T>(p, acc, up, mm, n, n0 / 2 + col);
+        } else if (rope) {
+          finish_rope4<T>(p, acc, up, mm, n0 >> 7, col);
         } else if (vec_ok && n + 4 <= p.N) {
           if (bias_kind == 1) {
             const float* bp = static_cast<const float*>(p.bias) + n;
@@ -1687,6 +1737,8 @@ int launch(const Tc5Args& a, const Tc5Plan& plan, cudaStream_t st, const Tc5Conv
   p.bias_dtype = a.bias_dtype; p.epilogue = a.epilogue; p.splits = pl.splits; p.kb_per_split = pl.kb_per_split;
   p.norm_eps = a.norm_eps; p.sumsq_in = a.sumsq_in; p.sumsq_in_cols = a.sumsq_in_cols; p.sumsq_out = a.sumsq_out;
   if ((a.sumsq_in || a.sumsq_out) && (CONV || MODE < 2)) return B200_ENOTSUP;
+  p.rope = a.rope;
+  if (a.rope.cos && (CONV || MODE < 2 || BN != 128 || a.N % 128)) return B200_ENOTSUP;
   if (CONV && pl.splits != 1) return B200_ENOTSUP;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(pl.tiles_n), static_cast<unsigned>(pl.tiles_m), static_cast<unsigned>(pl.splits));
@@ -1968,6 +2020,17 @@ int linear_tc5(const Tc5Args& a, cudaStream_t st) {
                         (a.bias && a.bias_dtype != B200_F32 && a.bias_dtype != tb) ||
                         (a.residual && ((reinterpret_cast<uintptr_t>(a.residual) & 7u) || a.ldr % 4))))
       return B200_ENOTSUP;
+  }
+  if (a.rope.cos) {   // merged q/k/v projection with rotary embedding and cache write: decode shapes, one head per 128-wide tile
+    const Tc5Args::Rope& r = a.rope;
+    const bool aligned = aligned16(r.cos) && aligned16(r.sin) && aligned16(r.q_out) && aligned16(r.k_cache) && aligned16(r.v_cache);
+    if (a.M > 64 || !r.sin || !r.q_out || !r.k_cache || !r.v_cache || !r.cache_pos || !aligned || r.Hq <= 0 || r.Hkv <= 0 ||
+        a.N != static_cast<int64_t>(r.Hq + 2 * r.Hkv) * 128 || a.residual || a.sumsq_out || glu || (a.epilogue & ~B200_EPI_W_STATIC) ||
+        (r.pos_dtype != B200_I64 && r.pos_dtype != B200_I32) || r.cache_len <= 0)
+      return B200_ENOTSUP;
+    const Tc5Plan pl = plan_tc5(a.M, a.N, a.K, false);
+    if (pl.bn != 128 || pl.tiles_m != 1) return B200_ENOTSUP;
+    return a.dtype == B200_BF16 ? launch<__nv_bfloat16, 128, false, 2>(a, pl, st) : launch<__half, 128, false, 2>(a, pl, st);
   }
   if (pair_shape(a)) {
     const int rc = a.dtype == B200_BF16 ? launch_pair<__nv_bfloat16>(a, st) : launch_pair<__half>(a, st);

@@ -19,6 +19,17 @@ struct Tc5Args {
   const float* sumsq_in = nullptr;
   int sumsq_in_cols = 0;
   float* sumsq_out = nullptr;
+  // Decode shapes only, out == nullptr: the GEMM is the merged q/k/v projection of one token per row
+  // (N = (Hq + 2 Hkv) * 128, head h = columns [128 h, 128 h + 128)) and its final pass applies the rotary
+  // embedding and writes the destinations of the three groups itself: rope(q) to q_out [M, Hq, 128],
+  // rope(k) and v into row cache_pos[0] of the caches [M, Hkv, cache_len, 128].
+  struct Rope {
+    const void* cos = nullptr; const void* sin = nullptr;   // [M, 128] tables of the rows' positions
+    void* q_out = nullptr; void* k_cache = nullptr; void* v_cache = nullptr;
+    const void* cache_pos = nullptr;
+    int64_t cache_len = 0;
+    int Hq = 0, Hkv = 0, pos_dtype = 0;
+  } rope;
 };
 
 // Geometry of an NHWC convolution run as an implicit GEMM (A rows are output pixels,

@@ -195,7 +195,65 @@ class _Lowering:
             self.lower(node)
         if self.fuse:
             self._fold_rmsnorm_into_decode_linears()
+            self._fuse_rope_into_qkv_linear()
         return self.out
+
+    def _fuse_rope_into_qkv_linear(self) -> None:
+        """Decode shapes (one token per sequence, at most 64 sequences, head dimension 128): the merged
+        q/k/v projection is followed by one small kernel that rotates q and k and writes the new K / V
+        rows into the caches.  With 128-wide GEMM tiles a tile is one head, so the GEMM's final pass
+        can do that itself (``b200_linear_qkv_rope``): same roundings, one launch less per layer.  The
+        fused step takes the place of the rope / cache step (its table and index operands may be
+        produced after the projection's position in the step list)."""
+        steps, touched = self.out.steps, self.out.step_tensors
+        producer: dict[str, int] = {}
+        readers: dict[str, set[int]] = {}
+        for i, st in enumerate(steps):
+            if isinstance(st, AliasStep):
+                continue
+            outs = set(getattr(st, "output_buffer_names", None) or [st.output_buffer_name])
+            for name in touched[i]:
+                v = self.out.views.get(name)
+                b = v.buffer if v is not None else name
+                if name in outs:
+                    producer[b] = i if b not in producer else -1
+                else:
+                    readers.setdefault(b, set()).add(i)
+        drop: set[int] = set()
+        for i, st in enumerate(steps):
+            p = getattr(st, "params", None) or {}
+            if p.get("op") != "qkv_post" or not p.get("in_place"):
+                continue
+            q, k, v = p["q"], p["k"], p["v"]
+            B, Hq, T, D = q.shape
+            Hkv = k.shape[1]
+            N = (Hq + 2 * Hkv) * D
+            if T != 1 or D != 128 or B > 64 or not (q.buffer == k.buffer == v.buffer) or v.shape[1] != Hkv:
+                continue
+            src = producer.get(q.buffer, -1)
+            if src < 0 or src >= i or src in drop or readers.get(q.buffer, set()) != {i}:
+                continue
+            lp = getattr(steps[src], "params", None) or {}
+            if lp.get("op") != "linear" or lp.get("glu") or lp.get("relu") or lp.get("residual") is not None or lp.get("aux") is not None \
+                    or lp.get("sumsq_out") is not None or lp["M"] != B or lp["N"] != N or lp["y"].buffer != q.buffer:
+                continue
+            y = lp["y"]
+            head_major = all(t.strides[1] == D and t.strides[3] == 1 and (B == 1 or t.strides[0] == N) for t in (q, k, v))
+            if not head_major or not y.is_contiguous() or q.offset != y.offset or k.offset != y.offset + Hq * D or v.offset != y.offset + (Hq + Hkv) * D:
+                continue
+            # nothing between the projection and the rope step may depend on the move: the projection's output has no other reader
+            params = dict(lp)
+            params.update(op="linear_qkv_rope", rope={k_: p[k_] for k_ in ("cos", "sin", "q_out", "k_cache", "v_cache", "index", "cache_len")},
+                          Hq=Hq, Hkv=Hkv, source="rope(q), cache writes folded in: " + lp.get("source", ""))
+            names = list(dict.fromkeys(list(steps[src].input_buffer_names) + [n for n in st.input_buffer_names if self.out.views.get(n) is None
+                                                                                or self.out.views[n].buffer != q.buffer]))
+            steps[i] = SpecialKernelStep("gemm_tc5_kernel", "q/k/v projection -> rope(q); key cache[pos] = rope(k); value cache[pos] = v  (in place)",
+                                         names, st.output_buffer_name, output_buffer_names=list(st.output_buffer_names), params=params)
+            touched[i] = list(dict.fromkeys([n for n in touched[src]] + [n for n in touched[i]]))
+            drop.add(src)
+        if drop:
+            self.out.steps = [s for i, s in enumerate(steps) if i not in drop]
+            self.out.step_tensors = [t for i, t in enumerate(touched) if i not in drop]
 
     def _fold_rmsnorm_into_decode_linears(self) -> None:
         """Decode shapes (M <= 64): an RMSNorm between two GEMMs costs a kernel launch for a few

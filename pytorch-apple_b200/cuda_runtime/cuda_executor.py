@@ -528,6 +528,19 @@ class CUDAExecutor:
                                                               self._ptr(p["q_out"]), self._ptr(p["k_cache"]), self._ptr(p["v_cache"]), iptr,
                                                               p["cache_len"], idt)))
 
+    def _bind_linear_qkv_rope(self, plan, step, p):
+        x, r = p["x"], p["rope"]
+        dt = p["y"].dtype
+        epi = native.EPI_W_STATIC if (p["w"] in self._weight_tensors or p["w"] in self._prepared) else 0
+        ld = lambda v: v.strides[0] if v.shape[0] > 1 else v.shape[1]
+        norm = p.get("norm")
+        iptr, idt = self._index_ptr(r["index"])
+        plan.launches.append((self._lib.b200_linear_qkv_rope, (
+            self._ptr(x), self._wptr(p["w"], dt), self._wptr(p["bias"], dt), p["M"], p["N"], p["K"], ld(x), p["K"], DTYPE_CODES[dt], DTYPE_CODES[dt],
+            epi, float(norm["eps"]) if norm else 0.0, self._ptr(norm["sumsq"]) if norm else None, int(norm["cols"]) if norm else 0,
+            self._ptr(r["cos"]), self._ptr(r["sin"]), self._ptr(r["q_out"]), self._ptr(r["k_cache"]), self._ptr(r["v_cache"]), iptr,
+            int(r["cache_len"]), idt, int(p["Hq"]), int(p["Hkv"]))))
+
     def _bind_max_pool2d(self, plan, step, p):
         x, y = self._tensor(plan, p["x"]), self._tensor(plan, p["y"])
         plan.launches.append((self._lib.b200_max_pool2d, (C.byref(x), C.byref(y), p["kernel_h"], p["kernel_w"], p["stride_h"],

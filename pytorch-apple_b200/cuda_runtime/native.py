@@ -68,6 +68,8 @@ SIGNATURES = {
     "b200_linear": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _vp, _i64, _vp, _i64, _vp]),
     "b200_linear_workspace_bytes": (_i64, [_i64, _i64, _i64]),
     "b200_linear_norm": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _f, _vp, _i, _vp, _vp]),
+    "b200_linear_qkv_rope": (_i, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _f, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i,
+                                  _vp]),
     "b200_matmul_strided": (_i, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _I64P, _I64P, _I64P, _i, _vp]),
     "b200_conv2d_nhwc": (_i, [_vp, _vp, _vp, _vp, _vp] + [_i] * 16 + [_vp]),
     "b200_attn_decode": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i64, _i, _i64, _i64, _i64, _i64, _f, _i, _vp, _i64, _vp]),

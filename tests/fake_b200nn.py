@@ -332,6 +332,36 @@ class FakeLibrary:
             _raw(sumsq_out, torch.float32, [M, N // 64], [N // 64, 1]).copy_(r.float().pow(2).reshape(M, N // 64, 64).sum(-1))
         return 0
 
+    def b200_linear_qkv_rope(self, A, W, bias, M, N, K, lda, ldw, dtype, bias_dtype, epilogue, norm_eps, sumsq_in, sumsq_in_cols,
+                             cos_t, sin_t, q_out, k_cache, v_cache, cache_pos, cache_len, pos_dtype, Hq, Hkv, stream):
+        self.calls.append("linear_qkv_rope")
+        assert M <= 64 and N == (Hq + 2 * Hkv) * 128 and not (epilogue & ~8)
+        dt = _DT[dtype]
+        D = 128
+        r = _raw(A, dt, [M, K], [lda, 1]).float() @ _raw(W, dt, [N, K], [ldw, 1]).float().t()
+        if _addr(sumsq_in):
+            ss = _raw(sumsq_in, torch.float32, [M, sumsq_in_cols], [sumsq_in_cols, 1]).sum(-1, keepdim=True)
+            r = r * torch.rsqrt(ss / K + norm_eps)
+        if _addr(bias):
+            r = r + _flat(bias, bias_dtype, N).float()
+        r = r.to(dt).reshape(M, Hq + 2 * Hkv, D)
+        c = _raw(cos_t, dt, [M, 1, D], [D, D, 1]).float()
+        s = _raw(sin_t, dt, [M, 1, D], [D, D, 1]).float()
+
+        def rope(x):
+            xf = x.float()
+            rot = torch.cat([-xf[..., D // 2:], xf[..., :D // 2]], -1)
+            return ((xf * c).to(dt).float() + (rot * s).to(dt).float()).to(dt)
+
+        _raw(q_out, dt, [M, Hq, D], [Hq * D, D, 1]).copy_(rope(r[:, :Hq]))
+        pos = int(_flat(cache_pos, pos_dtype, 1)[0])
+        pos = pos + cache_len if pos < 0 else pos
+        if 0 <= pos < cache_len:
+            cs = [Hkv * cache_len * D, cache_len * D, D, 1]
+            _raw(k_cache, dt, [M, Hkv, cache_len, D], cs)[:, :, pos] = rope(r[:, Hq:Hq + Hkv])
+            _raw(v_cache, dt, [M, Hkv, cache_len, D], cs)[:, :, pos] = r[:, Hq + Hkv:]
+        return 0
+
     def b200_matmul_strided(self, A, B, out, b1, b2, M, N, K, a_s, b_s, o_s, dtype, stream):
         self.calls.append("matmul")
         dt = _DT[dtype]

@@ -573,6 +573,58 @@ def test_qkv_rope_cache_fused(lib, B, T):
     assert torch.equal(qo.cpu(), ref_q) and torch.equal(KC.cpu(), ref_k) and torch.equal(VC.cpu(), ref_v)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("B,norm,pos", [(1, True, 17), (8, True, 4100), (64, True, 4351), (5, False, -3), (64, False, 0)])
+def test_linear_qkv_rope_equals_the_two_kernels(lib, dtype, B, norm, pos):
+    """The merged q/k/v projection whose final pass rotates q and k and writes the cache rows is
+    bit-identical to the projection followed by the rope / cache kernel - q, both caches whole."""
+    Hq, Hkv, D, S, K = 12, 2, 128, 4352, 1536
+    N = (Hq + 2 * Hkv) * D
+    DTC = DT[dtype]
+    x = gen((B, K), dtype, 0, 2.0).cuda()
+    w, bias = gen((N, K), dtype, 1, 0.03).cuda(), gen((N,), dtype, 2).cuda()
+    sumsq = x.float().pow(2).reshape(B, 24, K // 24).sum(-1).contiguous() if norm else None
+    p_abs = pos if pos >= 0 else S + pos
+    inv = 1.0 / (1e6 ** (torch.arange(0, D, 2).float() / D))
+    ang = torch.cat([torch.full((B, 1), float(p_abs)) * inv[None]] * 2, -1)
+    CO, SI = ang.cos().to(dtype).cuda().contiguous(), ang.sin().to(dtype).cuda().contiguous()
+    kc0, vc0 = gen((B, Hkv, S, D), dtype, 3).cuda(), gen((B, Hkv, S, D), dtype, 4).cuda()
+    P = torch.tensor([pos], dtype=torch.int64, device="cuda")
+    sq_ptr, n_part = (sumsq.data_ptr(), 24) if norm else (None, 0)
+    # two kernels
+    qkv = torch.empty(B, N, dtype=dtype, device="cuda")
+    ok(lib, lib.b200_linear_norm(x.data_ptr(), w.data_ptr(), bias.data_ptr(), None, qkv.data_ptr(), B, N, K, K, K, N, 0, DTC, DTC, 8,
+                                 1e-6, sq_ptr, n_part, None, stream()))
+    dv = lambda lo, n: qkv[:, None, lo:lo + n * D].view(B, 1, n, D).transpose(1, 2)
+    tq, tk, tv = bt(dv(0, Hq)), bt(dv(Hq * D, Hkv)), bt(dv((Hq + Hkv) * D, Hkv))
+    q_ref, k_ref, v_ref = torch.empty(B, Hq, 1, D, dtype=dtype, device="cuda"), kc0.clone(), vc0.clone()
+    ok(lib, lib.b200_qkv_rope_cache(C.byref(tq), C.byref(tk), C.byref(tv), CO.data_ptr(), SI.data_ptr(), q_ref.data_ptr(), k_ref.data_ptr(),
+                                    v_ref.data_ptr(), P.data_ptr(), S, 4, stream()))
+    # one kernel
+    q_out, kc, vc = torch.full((B, Hq, 1, D), float("nan"), dtype=dtype, device="cuda"), kc0.clone(), vc0.clone()
+    ok(lib, lib.b200_linear_qkv_rope(x.data_ptr(), w.data_ptr(), bias.data_ptr(), B, N, K, K, K, DTC, DTC, 8, 1e-6, sq_ptr, n_part,
+                                     CO.data_ptr(), SI.data_ptr(), q_out.data_ptr(), kc.data_ptr(), vc.data_ptr(), P.data_ptr(), S, 4, Hq, Hkv,
+                                     stream()))
+    torch.cuda.synchronize()
+    as_bits = lambda t: t.cpu().view(torch.int16)
+    assert torch.equal(as_bits(q_out), as_bits(q_ref))
+    assert torch.equal(as_bits(kc), as_bits(k_ref)) and torch.equal(as_bits(vc), as_bits(v_ref))
+    assert not torch.equal(as_bits(kc[:, :, p_abs]), as_bits(kc0[:, :, p_abs]))       # the row was written
+    code = C.c_int(-1)
+    ok(lib, lib.b200_debug_device_error(C.byref(code), 1))
+    assert code.value == 0
+
+
+def test_linear_qkv_rope_rejects_what_it_cannot_fuse(lib):
+    x, w = gen((65, 1536), torch.bfloat16).cuda(), gen((2048, 1536), torch.bfloat16, 1).cuda()
+    t = torch.zeros(65 * 12 * 128, dtype=torch.bfloat16, device="cuda")
+    P = torch.zeros(1, dtype=torch.int64, device="cuda")
+    args = lambda M, N, Hq: (x.data_ptr(), w.data_ptr(), None, M, N, 1536, 1536, 1536, 2, 2, 8, 0.0, None, 0, t.data_ptr(), t.data_ptr(),
+                             t.data_ptr(), t.data_ptr(), t.data_ptr(), P.data_ptr(), 16, 4, Hq, 2, stream())
+    assert lib.b200_linear_qkv_rope(*args(65, 2048, 12)) == -4      # more than 64 rows: B200_ENOTSUP
+    assert lib.b200_linear_qkv_rope(*args(8, 2048, 10)) == -1       # N != (Hq + 2 Hkv) * 128: B200_EINVAL
+
+
 def test_embedding_is_bit_exact(lib):
     V, D = 151936, 1536
     table = torch.randn(V, D, generator=torch.Generator().manual_seed(0)).bfloat16()
