@@ -589,27 +589,51 @@ __global__ void __launch_bounds__(224, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(cons
   // memory and finishes those outputs with coalesced stores.  No global scratch, no atomics;
   // after the barrier nobody touches a peer's memory, so CTAs may exit independently.
   if (staged) {
+    // All 224 threads walk the owned rows as float4 units in row-major order.  The loop body is
+    // kept short: it runs a handful of times per thread, so its cost is instruction count.
+    constexpr int LOG_UNITS = BN == 64 ? 4 : 5;              // float4 units per tile row (staged tiles are 64 or 128 wide)
+    const bool paired = glu || rope;
+    const int log_pr = paired ? 4 : LOG_UNITS;               // gated / rotary: the 16 units of columns 0..63, each paired with +64
+    const int my_rows = max(0, min(rpo, rows_valid - rank * rpo));
+    const int total = my_rows << log_pr;
+    const int slot = rpo * PART_PITCH;                       // floats between the slots of two ranks
+    T* const outp = static_cast<T*>(p.out);
+    const T* const resp = static_cast<const T*>(p.residual);
+    const bool relu = (p.epilogue & B200_EPI_RELU) != 0;
+    const int bias_kind = !p.bias ? 0 : p.bias_dtype == B200_F32 ? 1 : p.bias_dtype == AbFormat<T>::value + 1 ? 2 : 3;
+    const bool vec_ok = (reinterpret_cast<uintptr_t>(outp) & 7u) == 0 && (p.ldo & 3) == 0 && bias_kind < 3 &&
+                        (!resp || ((reinterpret_cast<uintptr_t>(resp) & 7u) == 0 && (p.ldr & 3) == 0)) && !(p.epilogue & B200_EPI_SILU_MUL);
+    // A thread meets the same four columns in every iteration (224 is a multiple of the units per row), so
+    // their bias - a constant of the stream - is fetched once, before the barrier that the thread waits at anyway.
+    const int my_col = (static_cast<int>(threadIdx.x) & ((1 << log_pr) - 1)) << 2;
+    float4 bias4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (!paired && vec_ok && static_cast<int64_t>(n0) + my_col + 4 <= p.N) {
+      if (bias_kind == 1) {
+        const float* bp = static_cast<const float*>(p.bias) + n0 + my_col;
+        bias4 = make_float4(__ldg(bp), __ldg(bp + 1), __ldg(bp + 2), __ldg(bp + 3));
+      } else if (bias_kind == 2) {
+        const T* bp = static_cast<const T*>(p.bias) + n0 + my_col;
+        bias4 = make_float4(to_f32<T>(bp[0]), to_f32<T>(bp[1]), to_f32<T>(bp[2]), to_f32<T>(bp[3]));
+      }
+    }
     __syncwarp();
     if (nsp > 1) tc5::cluster_sync();
     else __syncthreads();
     if (!*reinterpret_cast<volatile int*>(&failed)) {
-      // All 224 threads walk the owned rows as float4 units in row-major order.  The loop body is
-      // kept short: it runs a handful of times per thread, so its cost is instruction count.
-      constexpr int LOG_UNITS = BN == 64 ? 4 : 5;              // float4 units per tile row (staged tiles are 64 or 128 wide)
-      const bool paired = glu || rope;
-      const int log_pr = paired ? 4 : LOG_UNITS;               // gated / rotary: the 16 units of columns 0..63, each paired with +64
-      const int my_rows = max(0, min(rpo, rows_valid - rank * rpo));
-      const int total = my_rows << log_pr;
-      const int slot = rpo * PART_PITCH;                       // floats between the slots of two ranks
-      T* const outp = static_cast<T*>(p.out);
-      const T* const resp = static_cast<const T*>(p.residual);
-      const bool relu = (p.epilogue & B200_EPI_RELU) != 0;
-      const int bias_kind = !p.bias ? 0 : p.bias_dtype == B200_F32 ? 1 : p.bias_dtype == AbFormat<T>::value + 1 ? 2 : 3;
-      const bool vec_ok = (reinterpret_cast<uintptr_t>(outp) & 7u) == 0 && (p.ldo & 3) == 0 && bias_kind < 3 &&
-                          (!resp || ((reinterpret_cast<uintptr_t>(resp) & 7u) == 0 && (p.ldr & 3) == 0)) && !(p.epilogue & B200_EPI_SILU_MUL);
+      // the residual of a unit is requested one iteration ahead of its use
+      const bool res_ahead = resp && vec_ok && !paired;
+      auto residual_of = [&](int idx) {
+        const int lr = idx >> log_pr;
+        const int64_t n = static_cast<int64_t>(n0) + my_col;
+        if (idx >= total || n + 4 > p.N) return make_uint2(0u, 0u);
+        return *reinterpret_cast<const uint2*>(resp + (static_cast<int64_t>(m0) + rank * rpo + lr) * p.ldr + n);
+      };
+      uint2 res_next = res_ahead ? residual_of(static_cast<int>(threadIdx.x)) : make_uint2(0u, 0u);
 #pragma unroll 1
       for (int idx = static_cast<int>(threadIdx.x); idx < total; idx += 224) {
-        const int lr = idx >> log_pr, col = (idx & ((1 << log_pr) - 1)) << 2;
+        const uint2 res_cur = res_next;
+        if (res_ahead) res_next = residual_of(idx + 224);
+        const int lr = idx >> log_pr, col = my_col;
         const float* src = part + lr * PART_PITCH + col;
         float4 acc = *reinterpret_cast<const float4*>(src), up = make_float4(0.f, 0.f, 0.f, 0.f);
         if (paired) up = *reinterpret_cast<const float4*>(src + 64);
@@ -635,15 +659,9 @@ __global__ void __launch_bounds__(224, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(cons
         } else if (rope) {
           finish_rope4<T>(p, acc, up, mm, n0 >> 7, col);
         } else if (vec_ok && n + 4 <= p.N) {
-          if (bias_kind == 1) {
-            const float* bp = static_cast<const float*>(p.bias) + n;
-            acc.x += bp[0]; acc.y += bp[1]; acc.z += bp[2]; acc.w += bp[3];
-          } else if (bias_kind == 2) {
-            const T* bp = static_cast<const T*>(p.bias) + n;
-            acc.x += to_f32<T>(bp[0]); acc.y += to_f32<T>(bp[1]); acc.z += to_f32<T>(bp[2]); acc.w += to_f32<T>(bp[3]);
-          }
+          acc.x += bias4.x; acc.y += bias4.y; acc.z += bias4.z; acc.w += bias4.w;
           if (resp) {
-            const uint2 raw = *reinterpret_cast<const uint2*>(resp + mm * p.ldr + n);
+            const uint2 raw = res_cur;
             float r0, r1, r2, r3;
             unpack2<T>(raw.x, r0, r1);
             unpack2<T>(raw.y, r2, r3);
