@@ -381,9 +381,10 @@ __global__ void __launch_bounds__(224, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(cons
       tc5::tma_load_2d_a(ring_addr + i * STAGE + A_STAGE, &map_w, full0 + 8u * i, (kb0 + i) * BK, n0);
     }
   }
-  // Every CTA of the cluster is running before any of them writes into a peer's shared memory.
-  // This barrier sits in the part of the kernel that overlaps the predecessor, so it costs nothing.
-  if (nsp > 1) { __syncwarp(); tc5::cluster_sync(); }
+  // Every CTA of the cluster must be running before any of them writes into a peer's shared memory, which
+  // happens in the epilogue only: arrive here, wait there (by then the peers have long arrived; a full
+  // barrier at this point was ~1 us on the critical path of every split-K GEMM).
+  if (nsp > 1) { __syncwarp(); tc5::cluster_arrive(); }
 
   // Both producers: the first pass over the ring finds every stage free and waits for nothing; after
   // that a group of stages is waited for (the first wait is the long one, the rest answer at once) and
@@ -529,6 +530,7 @@ __global__ void __launch_bounds__(224, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(cons
     ok = __all_sync(0xffffffffu, ok);
     const int64_t m = m0 + q * 32 + lane;
     const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+    if (nsp > 1) { __syncwarp(); tc5::cluster_wait(); }   // (every epilogue warp, whatever `ok`: pairs with the arrive at start-up)
     if (ok && staged) {
       // ---- accumulator row -> fp32 staging buffer of the CTA that owns the row ----
       tc5::tc_fence_after();
@@ -617,8 +619,12 @@ __global__ void __launch_bounds__(224, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(cons
       }
     }
     __syncwarp();
-    if (nsp > 1) tc5::cluster_sync();
-    else __syncthreads();
+    if (nsp > 1) {
+      if (warp < 2 || warp > 5) tc5::cluster_wait();   // the producer and MMA warps complete the start-up barrier here
+      tc5::cluster_sync();
+    } else {
+      __syncthreads();
+    }
     if (!*reinterpret_cast<volatile int*>(&failed)) {
       // the residual of a unit is requested one iteration ahead of its use
       const bool res_ahead = resp && vec_ok && !paired;

@@ -282,6 +282,10 @@ __device__ __forceinline__ uint32_t cluster_ctarank() {
 __device__ __forceinline__ void cluster_sync() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+// The two halves of cluster_sync: a thread that has arrived may go on with work that touches no peer and
+// wait later; every arrive needs its wait before the thread arrives again.
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 // address of this CTA's shared-memory location `smem_addr` in the CTA with rank `rank` of the cluster
 __device__ __forceinline__ uint32_t map_to_rank(uint32_t smem_addr, uint32_t rank) {
   uint32_t r;
