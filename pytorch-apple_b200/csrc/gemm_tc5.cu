@@ -62,7 +62,8 @@ struct Tc5Params {
   int pst, pstage;      // ring stages and bytes per stage
   int wr, w_off;        // weights resident: all k-blocks of the CTA's weight tile stay in shared memory at w_off
   int pncb, c_off;      // C buffers (bulk-copy epilogue) and where they start
-  int npa;              // persistent kernel: activation producer threads (1 or 2), k-blocks dealt round-robin
+  int npa;              // persistent kernel: activation producer threads (1 or 2), ring stages dealt round-robin
+  int kps;              // persistent kernel: k-blocks per ring stage (1 or 2): one barrier hand-off covers that many
   int nfast;            // persistent kernel: column tiles fastest in the tile order
   // one-tile kernel, M <= 64: scale the output rows by the RMSNorm factor of the input rows / write
   // sum-of-squares partials of the output rows
@@ -743,7 +744,7 @@ struct RingPos {
   __device__ __forceinline__ void next(int stages) { if (++s == stages) { s = 0; ph ^= 1u; } }
 };
 
-template <typename T, int BN, bool CONV, bool TS>
+template <typename T, int BN, bool CONV, bool TS, int KPS>
 __global__ void __launch_bounds__(PCfg<BN, TS>::THREADS, 1)
     gemm_tc5p_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                      const __grid_constant__ CUtensorMap map_r, const __grid_constant__ CUtensorMap map_o, const Tc5Params p,
@@ -803,6 +804,7 @@ __global__ void __launch_bounds__(PCfg<BN, TS>::THREADS, 1)
     if (lane == 0) {
       pdl_wait();
       const int mine = a_id, deal = p.npa - 1;
+      constexpr int kps = KPS;
       const bool c8 = CONV && p.g.c8, gathered = CONV && !p.g.im2col;
       const uint32_t ring_addr = tc5::smem_addr(smem), full0 = tc5::smem_addr(&full_bar[0]), empty0 = tc5::smem_addr(&empty_bar[0]);
       const int cpb = CONV ? (c8 ? 1 : p.g.C / BK) : 1;
@@ -819,29 +821,35 @@ __global__ void __launch_bounds__(PCfg<BN, TS>::THREADS, 1)
           base_h = oh * p.g.sh - p.g.ph;
         }
         int cb = 0, sx = 0, r = 0;   // convolution: channel block within the filter tap, tap column, tap row - stepped, not divided
-        for (int kb = 0; kb < KB; ++kb, ++it) {
-          if ((it & deal) == mine) {
-            if (!tc5::mbar_wait_a(empty0 + 8u * s, ph ^ 1u)) { failed = 1; atomicExch(&g_tc5_error, 11); alive = false; break; }
-            if (!gathered) {   // (gather variant: warps 6-9 fill the A tile)
-              const uint32_t fb = full0 + 8u * s;
-              tc5::mbar_arrive_expect_tx_a(fb, A_STAGE);
+        for (int kb0 = 0; kb0 < KB; kb0 += kps, ++it) {
+          const int cnt = KB - kb0 < kps ? KB - kb0 : kps;   // k-blocks of this stage
+          const bool own = (it & deal) == mine;
+          if (own && !tc5::mbar_wait_a(empty0 + 8u * s, ph ^ 1u)) { failed = 1; atomicExch(&g_tc5_error, 11); alive = false; break; }
+          const uint32_t fb = full0 + 8u * s;
+          if (own && !gathered) tc5::mbar_arrive_expect_tx_a(fb, cnt * A_STAGE);   // (gather variant: warps 6-9 fill the A tile)
+#pragma unroll
+          for (int j = 0; j < kps; ++j) {
+            if (j >= cnt) break;
+            const int kb = kb0 + j;
+            if (own && !gathered) {
+              const uint32_t dj = dst + j * A_STAGE;
               if (c8) {
                 // 8-channel input: k-block = 8 filter taps, each a [128 pixels][16 B] box.  Taps past the
                 // filter meet zero weights (outside the weight map), so their box only has to be finite: tap 0 again.
                 for (int tt = 0; tt < 8; ++tt) {
                   const int tap = kb * 8 + tt, ta = tap < p.g.KH * p.g.KW ? tap : 0, rr = ta / p.g.KW;
-                  tc5::tma_load_im2col_4d_a(dst + tt * (BM * 16), &map_a, fb, 0, base_w, base_h, img, ta - rr * p.g.KW, rr);
+                  tc5::tma_load_im2col_4d_a(dj + tt * (BM * 16), &map_a, fb, 0, base_w, base_h, img, ta - rr * p.g.KW, rr);
                 }
               } else if (!CONV) {
-                tc5::tma_load_2d_a(dst, &map_a, fb, kb * BK, m0);
+                tc5::tma_load_2d_a(dj, &map_a, fb, kb * BK, m0);
               } else {
-                tc5::tma_load_im2col_4d_a(dst, &map_a, fb, cb * BK, base_w, base_h, img, sx, r);
+                tc5::tma_load_im2col_4d_a(dj, &map_a, fb, cb * BK, base_w, base_h, img, sx, r);
               }
             }
+            if (CONV && ++cb == cpb) { cb = 0; if (++sx == p.g.KW) { sx = 0; ++r; } }
           }
           dst += STAGE;
           if (++s == ST) { s = 0; ph ^= 1u; dst = ring_addr; }
-          if (CONV && ++cb == cpb) { cb = 0; if (++sx == p.g.KW) { sx = 0; ++r; } }
         }
       }
       if (dead()) {  // wait (bounded) for our own copies still in flight
@@ -877,17 +885,23 @@ __global__ void __launch_bounds__(PCfg<BN, TS>::THREADS, 1)
         if (dead() && loads > 0) tc5::mbar_wait(&w_full, (loads - 1) & 1, 1u << 16);
       } else {
         const bool c8 = CONV && p.g.c8;
-        const uint32_t ring_addr = tc5::smem_addr(smem) + A_STAGE, full0 = tc5::smem_addr(&full_bar[0]), empty0 = tc5::smem_addr(&empty_bar[0]);
+        constexpr int kps = KPS;
+        const uint32_t ring_addr = tc5::smem_addr(smem) + kps * A_STAGE, full0 = tc5::smem_addr(&full_bar[0]), empty0 = tc5::smem_addr(&empty_bar[0]);
         int it = 0, s = 0;
         uint32_t ph = 0, dst = ring_addr;
         bool alive = true;
         for (int tile = blockIdx.x; tile < n_tiles && alive && !dead(); tile += gridDim.x) {
           const int n0 = tile_n(tile) * BN;
-          for (int kb = 0; kb < KB; ++kb, ++it) {
+          for (int kb0 = 0; kb0 < KB; kb0 += kps, ++it) {
+            const int cnt = KB - kb0 < kps ? KB - kb0 : kps;
             if (!tc5::mbar_wait_a(empty0 + 8u * s, ph ^ 1u)) { failed = 1; atomicExch(&g_tc5_error, 19); alive = false; break; }
-            tc5::mbar_arrive_expect_tx_a(full0 + 8u * s, B_STAGE);
-            if (c8) load_w(smem + s * STAGE + A_STAGE, &full_bar[s], kb, n0);
-            else tc5::tma_load_2d_a(dst, &map_w, full0 + 8u * s, kb * BK, n0);
+            tc5::mbar_arrive_expect_tx_a(full0 + 8u * s, cnt * B_STAGE);
+#pragma unroll
+            for (int j = 0; j < kps; ++j) {
+              if (j >= cnt) break;
+              if (c8) load_w(smem + s * STAGE + A_STAGE, &full_bar[s], kb0 + j, n0);   // (c8: one k-block per stage)
+              else tc5::tma_load_2d_a(dst + j * B_STAGE, &map_w, full0 + 8u * s, (kb0 + j) * BK, n0);
+            }
             dst += STAGE;
             if (++s == ST) { s = 0; ph ^= 1u; dst = ring_addr; }
           }
@@ -906,6 +920,7 @@ __global__ void __launch_bounds__(PCfg<BN, TS>::THREADS, 1)
       const uint32_t ring_addr = tc5::smem_addr(smem), full0 = tc5::smem_addr(&full_bar[0]), empty0 = tc5::smem_addr(&empty_bar[0]);
       const uint32_t ring_lo = tc5::desc_sw128_lo(ring_addr), wres_lo = tc5::desc_sw128_lo(tc5::smem_addr(wres));
       const uint32_t stage_lo = static_cast<uint32_t>(STAGE) >> 4;
+      constexpr int kps = KPS;
       int ti = 0, cur_n0 = -1, w_loads = 0, s = 0;
       uint32_t ph = 0, a_lo = ring_lo;
       bool alive = true;
@@ -921,9 +936,10 @@ __global__ void __launch_bounds__(PCfg<BN, TS>::THREADS, 1)
         tc5::tc_fence_after();
         const uint32_t acc = tmem_base + b * BN;
         uint32_t w_lo = wres_lo;
-        for (int kb = 0; kb < KB; ++kb) {
+        for (int kb = 0; kb < KB; kb += kps) {
+          const int cnt = KB - kb < kps ? KB - kb : kps;
           if (!tc5::mbar_wait_a(full0 + 8u * s, ph)) { failed = 1; atomicExch(&g_tc5_error, 13); alive = false; break; }
-          if (c8) {   // unswizzled operands: one MMA covers two taps (2 x 16 bytes of K)
+          if (c8) {   // unswizzled operands: one MMA covers two taps (2 x 16 bytes of K); one k-block per stage
             const uint32_t a_addr = ring_addr + s * STAGE, b_addr = WR ? tc5::smem_addr(wres + kb * B_STAGE) : a_addr + A_STAGE;
             const uint32_t ak = BM * 16u, am = 128u, bk = BN * 16u, bm = 128u;
 #pragma unroll
@@ -931,10 +947,13 @@ __global__ void __launch_bounds__(PCfg<BN, TS>::THREADS, 1)
               tc5::umma_f16(acc, tc5::umma_desc_nosw(a_addr + k * 2 * (BM * 16), ak, am), tc5::umma_desc_nosw(b_addr + k * 2 * (BN * 16), bk, bm), idesc,
                             (kb | k) != 0);
           } else {
-            tc5::umma_f16_kblock(acc, a_lo, WR ? w_lo : a_lo + (A_STAGE >> 4), idesc, kb);
+#pragma unroll
+            for (int j = 0; j < kps; ++j)
+              if (j < cnt)
+                tc5::umma_f16_kblock(acc, a_lo + j * (A_STAGE >> 4), WR ? w_lo + j * (B_STAGE >> 4) : a_lo + ((kps * A_STAGE + j * B_STAGE) >> 4), idesc, kb + j);
           }
           tc5::umma_commit_a(empty0 + 8u * s);
-          w_lo += B_STAGE >> 4;
+          w_lo += cnt * (B_STAGE >> 4);
           a_lo += stage_lo;
           if (++s == ST) { s = 0; ph ^= 1u; a_lo = ring_lo; }
         }
@@ -1803,7 +1822,9 @@ int launch_persistent(const Tc5Args& a, cudaStream_t st, const Tc5Conv* g = null
   bool* configured = configured_on.slot();
   if (!configured) return B200_ENOTSUP;
   if (!*configured) {
-    if (cudaFuncSetAttribute(gemm_tc5p_kernel<T, BN, CONV, TS>, cudaFuncAttributeMaxDynamicSharedMemorySize, PC::SMEM_LIMIT) != cudaSuccess) {
+    if (cudaFuncSetAttribute(gemm_tc5p_kernel<T, BN, CONV, TS, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, PC::SMEM_LIMIT) != cudaSuccess ||
+        (BN <= 128 && cudaFuncSetAttribute(gemm_tc5p_kernel<T, BN, CONV, TS, BN <= 128 ? 2 : 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           PC::SMEM_LIMIT) != cudaSuccess)) {
       cudaGetLastError();
       return B200_ENOTSUP;
     }
@@ -1862,13 +1883,31 @@ int launch_persistent(const Tc5Args& a, cudaStream_t st, const Tc5Conv* g = null
       break;
     }
   }
+  // Two k-blocks per ring stage where a k-block of MMAs is short (tiles up to 128 wide: 0.05-0.13 us against
+  // ~0.3 us for a barrier hand-off between the single-thread roles): half as many hand-offs per tile.  From
+  // nine k-blocks per tile - the 3x3 convolutions and long reductions (ResNet-50 at batch 256: 3x3 over 64
+  // channels 178 -> 146 us, over 512 channels 90 -> 68 us) - and from four where the ring has an even number
+  // of stages; shorter, memory-bound reductions on an odd ring keep it (pairing would lose a k-block of
+  // buffering: 1x1/2 512 -> 1024 went 88 -> 109 us).
+  // A compile-time parameter of the kernel: with a run-time count the longer issue loops cost what the
+  // halved hand-offs gained.  (Not for the unswizzled 8-channel operands and the gathered A tile.)
+  p.kps = 1;
+  if (BN <= 128 && (!CONV || (p.g.im2col && !p.g.c8)) && p.pst >= 4 && (ceil_div(a.K, BK) >= 9 || (ceil_div(a.K, BK) >= 4 && p.pst % 2 == 0))) {
+    p.kps = 2;
+    p.pst /= 2;
+    p.pstage *= 2;
+  }
   // Two activation producers for convolutions through im2col boxes.  (Dealing k-blocks to more threads than the
   // ring has stages would be wrong, not just useless: a producer learns how far the MMAs have got only from its
   // own waits, one ring pass back at a time, and a parity wait cannot tell a barrier two phases behind from the
   // phase it expects.  Two is below every ring depth used here.)
   p.npa = CONV && p.g.im2col && ceil_div(a.K, BK) >= 2 ? 2 : 1;
-  launch_pdl(gemm_tc5p_kernel<T, BN, CONV, TS>, dim3(grid), dim3((CONV && !TS && !p.g.im2col) ? 352 : PC::THREADS), SMEM, st, ma, mw, mr, mo, p,
-             static_cast<int>(tiles_m), static_cast<int>(tiles));
+  const dim3 block((CONV && !TS && !p.g.im2col) ? 352 : PC::THREADS);
+  if (p.kps == 2)
+    launch_pdl(gemm_tc5p_kernel<T, BN, CONV, TS, BN <= 128 ? 2 : 1>, dim3(grid), block, SMEM, st, ma, mw, mr, mo, p, static_cast<int>(tiles_m),
+               static_cast<int>(tiles));
+  else
+    launch_pdl(gemm_tc5p_kernel<T, BN, CONV, TS, 1>, dim3(grid), block, SMEM, st, ma, mw, mr, mo, p, static_cast<int>(tiles_m), static_cast<int>(tiles));
   B200_CHECK_LAUNCH("gemm_tc5p_kernel");
   return B200_OK;
 }
