@@ -37,10 +37,12 @@ constexpr int NORM_MAX_PARTS = 32;   // row scaling: at most this many sum-of-sq
 template <int BN, int MODE> struct Cfg {
   static constexpr int AROWS = MODE >= 2 ? 64 : 128;
   static constexpr int A_STAGE = AROWS * BK * 2;
-  static constexpr int ST = MODE == 0 ? (BN == 128 ? 3 : 4) : MODE == 1 ? (BN == 128 ? 4 : 6) : (BN == 128 ? 7 : 12);
+  // k-blocks per ring stage: the decode shapes pair them (one barrier hand-off per two k-blocks of MMAs)
+  static constexpr int KPS = MODE >= 2 ? 2 : 1;
+  static constexpr int ST = MODE == 0 ? (BN == 128 ? 3 : 4) : MODE == 1 ? (BN == 128 ? 4 : 6) : (BN == 128 ? 3 : 6);
   static constexpr int CTAS = MODE == 0 ? 2 : 1;
   static constexpr int ISSUE_GROUP = ST >= 12 ? 4 : ST >= 6 ? 3 : ST >= 4 ? 2 : 1;   // ring stages a producer thread fills per barrier wait
-  static constexpr int RING = ST * (A_STAGE + BN * BK * 2);
+  static constexpr int RING = ST * KPS * (A_STAGE + BN * BK * 2);
   // split-K only: fp32 receive buffer for the partial-tile rows this CTA owns, one slot per
   // cluster rank, behind the ring (peers write into it while this CTA may still be computing)
   static constexpr int RECV_ROWS = (MODE >= 2 ? 64 : 128) + 8;
@@ -317,8 +319,8 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 template <typename T, int BN, bool CONV, int MODE>
 __global__ void __launch_bounds__(224, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a,
                                                           const __grid_constant__ CUtensorMap map_w, const Tc5Params p) {
-  constexpr int ST = Cfg<BN, MODE>::ST, A_STAGE = Cfg<BN, MODE>::A_STAGE, ISSUE_GROUP = Cfg<BN, MODE>::ISSUE_GROUP;
-  constexpr int B_STAGE = BN * BK * 2, STAGE = A_STAGE + B_STAGE;
+  constexpr int ST = Cfg<BN, MODE>::ST, A_STAGE = Cfg<BN, MODE>::A_STAGE, ISSUE_GROUP = Cfg<BN, MODE>::ISSUE_GROUP, KPS = Cfg<BN, MODE>::KPS;
+  constexpr int B_STAGE = BN * BK * 2, STAGE = KPS * (A_STAGE + B_STAGE);   // a stage: KPS activation tiles, then KPS weight tiles
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   __shared__ __align__(8) uint64_t full_bar[ST], empty_bar[ST], acc_bar;
@@ -336,6 +338,8 @@ __global__ void __launch_bounds__(224, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(cons
   const int KB = static_cast<int>((p.K + BK - 1) / BK);
   const int kb0 = blockIdx.z * p.kb_per_split;
   const int nkb = min(KB, kb0 + p.kb_per_split) - kb0;   // >= 1 by construction of the grid
+  const int nstg = (nkb + KPS - 1) / KPS;                // ring stages this CTA fills
+  auto stage_cnt = [&](int i) { return nkb - i * KPS < KPS ? nkb - i * KPS : KPS; };   // k-blocks of stage i
   // single-row-tile shapes and split-K stage the accumulator through shared memory (see the end of the kernel)
   const bool gather = CONV && !p.g.im2col;   // convolution A tile copied by the epilogue warps instead of TMA
   const bool staged = !CONV && (MODE >= 1 || p.splits > 1);   // MODE >= 1: known at compile time, the direct epilogue is dropped
@@ -374,13 +378,17 @@ __global__ void __launch_bounds__(224, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(cons
   // Weights that no kernel of this stream writes are fetched before the predecessor has finished:
   // the weight producer simply runs ahead until the ring is full.
   const bool w_static = (p.epilogue & B200_EPI_W_STATIC) != 0;
-  const int pre = w_static ? (nkb < ST ? nkb : ST) : 0;   // weight stages issued before the cluster start-up barrier
+  const int pre = w_static ? (nstg < ST ? nstg : ST) : 0;   // weight stages issued before the cluster start-up barrier
   const uint32_t ring_addr = tc5::smem_addr(smem), full0 = tc5::smem_addr(&full_bar[0]), empty0 = tc5::smem_addr(&empty_bar[0]);
+  auto load_w_stage = [&](int i, int st) {   // the weight tiles of stage i into ring slot st
+    const int cnt = stage_cnt(i);
+    tc5::mbar_arrive_expect_tx_a(full0 + 8u * st, cnt * B_STAGE);
+#pragma unroll
+    for (int j = 0; j < KPS; ++j)
+      if (j < cnt) tc5::tma_load_2d_a(ring_addr + st * STAGE + KPS * A_STAGE + j * B_STAGE, &map_w, full0 + 8u * st, (kb0 + i * KPS + j) * BK, n0);
+  };
   if (warp == 6 && lane == 0) {
-    for (int i = 0; i < pre; ++i) {
-      tc5::mbar_arrive_expect_tx_a(full0 + 8u * i, B_STAGE);
-      tc5::tma_load_2d_a(ring_addr + i * STAGE + A_STAGE, &map_w, full0 + 8u * i, (kb0 + i) * BK, n0);
-    }
+    for (int i = 0; i < pre; ++i) load_w_stage(i, i);
   }
   // Every CTA of the cluster must be running before any of them writes into a peer's shared memory, which
   // happens in the epilogue only: arrive here, wait there (by then the peers have long arrived; a full
@@ -391,12 +399,12 @@ __global__ void __launch_bounds__(224, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(cons
   // that a group of stages is waited for (the first wait is the long one, the rest answer at once) and
   // filled back to back.  `load(i, s)` issues k-block i into stage s.
   auto produce = [&](int from, auto&& load) {
-    const int first = nkb < ST ? nkb : ST;
+    const int first = nstg < ST ? nstg : ST;
     for (int i = from; i < first; ++i) load(i, i);
     int i = first, st = 0;
-    uint32_t par = 0;   // k-block ST reuses stage 0 once the first phase of its barrier has completed
-    while (i < nkb) {
-      const int g = nkb - i < ISSUE_GROUP ? nkb - i : ISSUE_GROUP;
+    uint32_t par = 0;   // stage ST reuses slot 0 once the first phase of its barrier has completed
+    while (i < nstg) {
+      const int g = nstg - i < ISSUE_GROUP ? nstg - i : ISSUE_GROUP;
       int ss = st;
       uint32_t pp = par;
       for (int j = 0; j < g; ++j) {
@@ -419,18 +427,18 @@ __global__ void __launch_bounds__(224, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(cons
   if (warp == 6) {
     if (lane == 0) {   // ---- weight producer ----
       if (!w_static) pdl_wait();   // the weights may come from the kernel before this one
-      drain(produce(pre, [&](int i, int st) {
-        tc5::mbar_arrive_expect_tx_a(full0 + 8u * st, B_STAGE);
-        tc5::tma_load_2d_a(ring_addr + st * STAGE + A_STAGE, &map_w, full0 + 8u * st, (kb0 + i) * BK, n0);
-      }));
+      drain(produce(pre, load_w_stage));
     }
   } else if (warp == 0) {
     if (lane == 0 && !gather) {   // ---- activation producer (the gather variant fills the A tile with the epilogue warps) ----
       pdl_wait();
       if (!CONV) {
         drain(produce(0, [&](int i, int st) {
-          tc5::mbar_arrive_expect_tx_a(full0 + 8u * st, A_STAGE);
-          tc5::tma_load_2d_a(ring_addr + st * STAGE, &map_a, full0 + 8u * st, (kb0 + i) * BK, m0);
+          const int cnt = stage_cnt(i);
+          tc5::mbar_arrive_expect_tx_a(full0 + 8u * st, cnt * A_STAGE);
+#pragma unroll
+          for (int j = 0; j < KPS; ++j)
+            if (j < cnt) tc5::tma_load_2d_a(ring_addr + st * STAGE + j * A_STAGE, &map_a, full0 + 8u * st, (kb0 + i * KPS + j) * BK, m0);
         }));
       } else {
         // implicit GEMM: k-block = 64 channels of one filter tap; tap row / column / channel block are stepped
@@ -454,10 +462,13 @@ __global__ void __launch_bounds__(224, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(cons
       const uint32_t ring_lo = tc5::desc_sw128_lo(ring_addr);
       uint32_t a_lo = ring_lo, ph = 0;
       int s = 0;
-      for (int i = 0; i < nkb; ++i) {
+      for (int i = 0; i < nstg; ++i) {
         if (!tc5::mbar_wait_a(full0 + 8u * s, ph)) { failed = 1; atomicExch(&g_tc5_error, 2); break; }
-        tc5::umma_f16_kblock(tmem_base, a_lo, a_lo + (A_STAGE >> 4), idesc, i);
-        if (i + ST < nkb) tc5::umma_commit_a(empty0 + 8u * s);
+        const int cnt = stage_cnt(i);
+#pragma unroll
+        for (int j = 0; j < KPS; ++j)
+          if (j < cnt) tc5::umma_f16_kblock(tmem_base, a_lo + j * (A_STAGE >> 4), a_lo + ((KPS * A_STAGE + j * B_STAGE) >> 4), idesc, i * KPS + j);
+        if (i + ST < nstg) tc5::umma_commit_a(empty0 + 8u * s);
         a_lo += STAGE >> 4;
         if (++s == ST) { s = 0; ph ^= 1u; a_lo = ring_lo; }
       }
