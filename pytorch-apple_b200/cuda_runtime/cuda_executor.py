@@ -26,6 +26,7 @@ from __future__ import annotations
 
 import contextlib
 import ctypes as C
+import operator
 from typing import Any
 
 from cuda_compiler.cuda_codegen import EW_OPCODES
@@ -39,6 +40,9 @@ except ImportError:  # pragma: no cover
     torch = None
 
 
+_HANDLE = operator.attrgetter("native_handle")
+
+
 class _Plan:
     """Launch list bound to one set of buffer addresses."""
 
@@ -46,6 +50,7 @@ class _Plan:
         self.launches: list[tuple[Any, tuple]] = []   # (cfunc, args without the trailing stream)
         self.keepalive: list[Any] = []
         self.outputs: dict[str, Any] = {}
+        self.out_buffers: dict[str, Any] | None = None
         self.graph = None
         self.runs = 0
         self.n_kernels = 0
@@ -57,6 +62,7 @@ class CUDAExecutor:
             raise RuntimeError("PyTorch is not installed; it provides device memory for the CUDA executor")
         self._lib = native.load()
         self._device = native.device_string(device_id)
+        self._torch_device = torch.device(self._device)
         self._on_gpu = self._device.startswith("cuda")
         if self._on_gpu and not torch.cuda.is_available():
             raise RuntimeError("no CUDA device is available")
@@ -92,8 +98,9 @@ class CUDAExecutor:
 
     def _input_tensors(self, inputs: dict[str, Any]) -> dict[str, Any]:
         tensors = {n: inputs[n].native_handle for n in self._input_names if n in inputs}
-        for n, t in tensors.items():
-            if str(t.device) != self._device and not (self._device == "cuda:0" and str(t.device) == "cuda"):
+        dev = self._torch_device
+        for n, t in tensors.items():   # (device objects compare in C; a decode step passes 60 buffers per call)
+            if t.device != dev and not (dev.type == "cuda" and t.device.type == "cuda" and t.device.index in (None, dev.index)):
                 raise ValueError(f"input '{n}' lives on {t.device}, this executor runs on {self._device}")
         return tensors
 
@@ -115,7 +122,11 @@ class CUDAExecutor:
             self._plans[key] = plan
         self._launch(plan)
         self.last_launch_count = plan.n_kernels
-        return {name: CUDABuffer(t, logical_shape=tuple(t.shape)) for name, t in plan.outputs.items()}
+        # the same arena views on every replay of this plan: wrapped once (and again if a caller re-pointed a wrapper)
+        cached = plan.out_buffers
+        if cached is None or not all(map(operator.is_, map(_HANDLE, cached.values()), plan.outputs.values())):
+            cached = plan.out_buffers = {name: CUDABuffer(t, logical_shape=tuple(t.shape)) for name, t in plan.outputs.items()}
+        return dict(cached)
 
     def profile(self, inputs: dict[str, Any], weights: dict[str, Any]) -> list[tuple[str, float]]:
         """Run once without a CUDA graph, bracketing every library call with CUDA events on
@@ -210,15 +221,15 @@ class CUDAExecutor:
         (same names, same device tensors) - swapping one buffer inside the same dict counts."""
         seen = self._weights_seen
         if seen is not None and len(seen) == len(weights):
-            for (name, tensor), (n, buf) in zip(seen, weights.items()):
-                if name != n or tensor is not buf.native_handle:
-                    break
-            else:
+            # names as one list comparison, tensors by identity through C-level iterators: this runs before every launch
+            if list(weights) == self._weights_names and all(map(operator.is_, self._weights_handles, map(_HANDLE, weights.values()))):
                 return
         self._load_weights(weights)
 
     def _load_weights(self, weights: dict[str, Any]) -> None:
         self._weights_seen = [(n, b.native_handle) for n, b in weights.items()]
+        self._weights_names = [n for n, _ in self._weights_seen]
+        self._weights_handles = [t for _, t in self._weights_seen]
         self._weight_tensors = {n: b.native_handle for n, b in weights.items()}
         self._weight_cache.clear()
         self._prepared.clear()
