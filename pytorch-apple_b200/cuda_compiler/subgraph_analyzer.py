@@ -302,6 +302,8 @@ class _Lowering:
                     or cp["K"] != cols or cp["M"] != rows or cp.get("norm") or x_view.strides[-1] != 1 or x_view.offset % 8 \
                     or (rows > 1 and x_view.strides[0] % 8):
                 continue
+            if cp["N"] >= 2 * 148 * 256:
+                continue   # a vocabulary-sized projection runs on the persistent kernel, which carries no row scaling (91 against 115 us)
             # the producer of x: a GEMM writing exactly this [rows, cols] tensor, alone
             src = producer.get(x_view.buffer, -1)
             if src < 0:

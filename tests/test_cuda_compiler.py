@@ -181,20 +181,21 @@ def test_qwen_decode_layer_plan():
     assert prog.compute_dtype == "bfloat16"
     kinds = [getattr(s, "kernel_name", None) or s.blas_type for s in prog.steps if not isinstance(s, AliasStep)]
     # decode shapes: every RMSNorm that sits between two GEMMs is folded into them (the producing GEMM
-    # writes sum-of-squares partials, the consuming one scales its rows); only the first one, fed by the
-    # embedding, keeps its kernel
-    assert kinds.count("attention") == L and kinds.count("rmsnorm_kernel") == 1
+    # writes sum-of-squares partials, the consuming one scales its rows); the first one, fed by the
+    # embedding, and the last one, in front of the vocabulary projection (which runs on the persistent
+    # kernel), keep their kernels
+    assert kinds.count("attention") == L and kinds.count("rmsnorm_kernel") == 2
     # the q/k/v projection of every layer also rotates q and k and writes the new cache rows (its step replaces the rope / cache step)
     fused_qkv = [s.params for s in prog.steps if isinstance(s, SpecialKernelStep) and s.params.get("op") == "linear_qkv_rope"]
     assert len(fused_qkv) == L and all(f["Hq"] == cfg.num_attention_heads and f["Hkv"] == cfg.num_key_value_heads for f in fused_qkv)
     assert kinds.count("gemm") == 3 * L + 1                    # o_proj, gate+up, down (+ lm_head)
     gemms = [s.params for s in prog.steps if isinstance(s, CUBLASStep)] + fused_qkv
-    assert sum(1 for g in gemms if g.get("norm")) == 2 * L and sum(1 for g in gemms if g.get("sumsq_out") is not None) == 2 * L
-    assert sorted(p.kind for p in prog.weight_preps).count("scale_cols") == 1          # the tied head gets a scaled copy
+    assert sum(1 for g in gemms if g.get("norm")) == 2 * L - 1 and sum(1 for g in gemms if g.get("sumsq_out") is not None) == 2 * L - 1
+    assert sorted(p.kind for p in prog.weight_preps).count("scale_cols") == 0          # (the tied head stays as it is)
     assert sum(1 for p in prog.weight_preps if p.params.get("col_scale")) == 2 * L - 1  # q/k/v of layers 1.., gate/up of all
     assert kinds.count("qkv_rope_cache_kernel") == 0 and kinds.count("index_copy_kernel") == 0 and kinds.count("rope_rotate_kernel") == 0
     assert len(prog.donated_inputs) == 2 * L
-    per_layer = (len(kinds) - 4) / L                           # minus embedding, rope table, first norm, lm_head
+    per_layer = (len(kinds) - 5) / L                           # minus embedding, rope table, first and last norm, lm_head
     assert per_layer == 5                                      # q/k/v + rope + cache, attention, o_proj, gate/up, down
     # fuse=False keeps every op on its own kernel, with the reference's rounding points
     kinds0 = [getattr(s, "kernel_name", None) or s.blas_type for s in compile_subgraph(ir, fuse=False).steps if not isinstance(s, AliasStep)]
