@@ -647,8 +647,46 @@ __global__ void __launch_bounds__(224, Cfg<BN, MODE>::CTAS) gemm_tc5_kernel(cons
         return *reinterpret_cast<const uint2*>(resp + (static_cast<int64_t>(m0) + rank * rpo + lr) * p.ldr + n);
       };
       uint2 res_next = res_ahead ? residual_of(static_cast<int>(threadIdx.x)) : make_uint2(0u, 0u);
+      // The plain case (bias / residual / ReLU on whole float4 units, no row scale, no sum of squares) as a loop of
+      // its own: every decision is made outside, the pointers step by a constant number of rows, two units in flight.
+      const bool plain = !paired && vec_ok && static_cast<int64_t>(n0) + my_col + 4 <= p.N && !p.sumsq_out && !(CAN_NORM && norm);
+      if (plain) {
+        constexpr int ROWS_PER_STEP = 224 >> LOG_UNITS;   // 224 threads cover this many whole rows per iteration
+        const int lr0 = static_cast<int>(threadIdx.x) >> LOG_UNITS;
+        const float* src0 = part + lr0 * PART_PITCH + my_col;
+        const int64_t row0 = static_cast<int64_t>(m0) + rank * rpo + lr0;
+        T* o = outp + row0 * p.ldo + n0 + my_col;
+        const T* r = resp ? resp + row0 * p.ldr + n0 + my_col : nullptr;
+        const int64_t o_step = static_cast<int64_t>(ROWS_PER_STEP) * p.ldo, r_step = static_cast<int64_t>(ROWS_PER_STEP) * p.ldr;
+        const int iters = lr0 < my_rows ? (my_rows - lr0 + ROWS_PER_STEP - 1) / ROWS_PER_STEP : 0;
+        uint2 rn = (r && iters > 0) ? *reinterpret_cast<const uint2*>(r) : make_uint2(0u, 0u);
+#pragma unroll 2
+        for (int it = 0; it < iters; ++it) {
+          const uint2 rc = rn;
+          if (r && it + 1 < iters) rn = *reinterpret_cast<const uint2*>(r + r_step);
+          const float* sp = src0;
+          float4 acc = *reinterpret_cast<const float4*>(sp);
+          for (int sl = 1; sl < nsp; ++sl) {
+            sp += slot;
+            const float4 t = *reinterpret_cast<const float4*>(sp);
+            acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w;
+          }
+          acc.x += bias4.x; acc.y += bias4.y; acc.z += bias4.z; acc.w += bias4.w;
+          if (r) {
+            float r0, r1, r2, r3;
+            unpack2<T>(rc.x, r0, r1);
+            unpack2<T>(rc.y, r2, r3);
+            acc.x = round_as<T>(acc.x) + r0; acc.y = round_as<T>(acc.y) + r1; acc.z = round_as<T>(acc.z) + r2; acc.w = round_as<T>(acc.w) + r3;
+            r += r_step;
+          }
+          if (relu) { acc.x = fmaxf(acc.x, 0.f); acc.y = fmaxf(acc.y, 0.f); acc.z = fmaxf(acc.z, 0.f); acc.w = fmaxf(acc.w, 0.f); }
+          *reinterpret_cast<uint2*>(o) = make_uint2(pack2<T>(acc.x, acc.y), pack2<T>(acc.z, acc.w));
+          o += o_step;
+          src0 += ROWS_PER_STEP * PART_PITCH;
+        }
+      }
 #pragma unroll 1
-      for (int idx = static_cast<int>(threadIdx.x); idx < total; idx += 224) {
+      for (int idx = plain ? total : static_cast<int>(threadIdx.x); idx < total; idx += 224) {
         const uint2 res_cur = res_next;
         if (res_ahead) res_next = residual_of(idx + 224);
         const int lr = idx >> log_pr, col = my_col;
