@@ -1352,19 +1352,29 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
 #pragma unroll
           for (int j = 0; j < 4; ++j) rc[j] = rn[j];
         }
-      } else if (p.splits > 1) {   // raw partial sums of this unit's k-range (N % 4 == 0: whole float4s inside the row)
+      } else if (p.splits > 1) {
+        // raw partial sums of this unit's k-range (N % 8 == 0: 32-byte units stay inside the row); two 16-column
+        // units in flight, 256-bit stores (a lane's store is one whole sector)
         float* dst = p.partial + (static_cast<int64_t>(unit / n_tiles) * p.M + m) * p.N + n0;
+        float va[16], vb[16];
+        __syncwarp();
+        tc5::tmem_ld_32x16(t_row, va);
 #pragma unroll 1
-        for (int c = 0; c < BN; c += 16) {
-          float v[16];
-          __syncwarp();
-          tc5::tmem_ld_32x16(t_row + c, v);
+        for (int c = 0; c < BN; c += 32) {
           tc5::tmem_ld_wait();
+          tc5::tmem_ld_32x16(t_row + c + 16, vb);
           if (m < p.M) {
-#pragma unroll
-            for (int i = 0; i < 16; i += 4)
-              if (n0 + c + i < p.N) *reinterpret_cast<float4*>(dst + c + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+            if (n0 + c < p.N) tc5::st_global_f8(dst + c, va);
+            if (n0 + c + 8 < p.N) tc5::st_global_f8(dst + c + 8, va + 8);
           }
+          __syncwarp();
+          tc5::tmem_ld_wait();
+          if (c + 32 < BN) tc5::tmem_ld_32x16(t_row + c + 32, va);
+          if (m < p.M) {
+            if (n0 + c + 16 < p.N) tc5::st_global_f8(dst + c + 16, vb);
+            if (n0 + c + 24 < p.N) tc5::st_global_f8(dst + c + 24, vb + 8);
+          }
+          __syncwarp();
         }
       } else if (glu) {
 #pragma unroll 1
@@ -1404,23 +1414,32 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
 }
 
 // Second half of the pair kernel's split-K: out = epilogue(sum over splits of the fp32 partial sums), eight
-// consecutive columns per thread, splits added in index order (the result does not depend on timing); the
-// partial sums are zeroed behind the read, as every user of the shared split-K workspace leaves it.
+// consecutive columns per thread.  The partial sums of all splits (at most PAIR_MAX_SPLITS) are requested before
+// the first is used - one memory round trip per output instead of one per split, which is what this kernel's
+// time consists of - and added in index order (the result does not depend on timing); they are zeroed behind
+// the read, as every user of the shared split-K workspace leaves it.
+constexpr int PAIR_MAX_SPLITS = 8;
 template <typename T>
 __global__ void __launch_bounds__(256) pair_splitk_reduce_kernel(const Tc5Params p) {
   pdl_trigger();
   pdl_wait();
-  const int64_t per_row = p.N / 8, total = p.M * per_row;
+  const int64_t per_row = p.N / 8, total = p.M * per_row, plane = p.M * p.N;
   for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total; i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
     const int64_t m = i / per_row, n = (i - m * per_row) * 8;
-    const float* src = p.partial + m * p.N + n;
+    float* const q = p.partial + m * p.N + n;
+    float a[PAIR_MAX_SPLITS][8];
+#pragma unroll
+    for (int s = 0; s < PAIR_MAX_SPLITS; ++s)
+      if (s < p.splits) tc5::ld_global_cg_f8(q + s * plane, a[s]);
     float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    for (int s = 0; s < p.splits; ++s, src += p.M * p.N) {
-      float4* q = reinterpret_cast<float4*>(const_cast<float*>(src));
-      const float4 a = __ldcg(q), b = __ldcg(q + 1);
-      v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w; v[4] += b.x; v[5] += b.y; v[6] += b.z; v[7] += b.w;
-      q[0] = make_float4(0.f, 0.f, 0.f, 0.f);   // the workspace is shared with kernels that expect it zeroed
-      q[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float zero[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int s = 0; s < PAIR_MAX_SPLITS; ++s) {
+      if (s < p.splits) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] += a[s][i];
+        tc5::st_global_f8(q + s * plane, zero);   // the workspace is shared with kernels that expect it zeroed
+      }
     }
     finish_cols<T, 8>(p, v, m, n);
   }
@@ -1970,15 +1989,17 @@ bool pair_shape(const Tc5Args& a) {
   return ceil_div(a.M, 256) * ceil_div(a.N, 256) >= 37;
 }
 
-// Few tiles but a long reduction (the down projection of a 1024-token prompt: 24 tiles, K = 8960): the pairs
-// split K among themselves and leave fp32 partial sums in the caller's workspace.  Returns the split count (1: none).
+// Few tiles but a long reduction (the down projection of a 512- or 1024-token prompt: 12 or 24 tiles, K = 8960): the
+// pairs split K among themselves and leave fp32 partial sums in the caller's workspace; measured 21.8 us (512 rows)
+// and 30.7 us (1024) against 33.9 and 70.5 us for 128 x 128 tiles with split-K inside a cluster.  Returns the split
+// count (1: none).
 int pair_splits(int64_t M, int64_t N, int64_t K) {
   if (M <= 128 || N < 256 || K < 4096 || N % 8) return 1;
   const int64_t tiles = ceil_div(M, 256) * ceil_div(N, 256), KB = ceil_div(K, BK);
-  if (tiles >= 37 || tiles < 16) return 1;   // (fewer tiles: measured no better than the one-tile kernel's cluster split-K)
+  if (tiles >= 37 || tiles < 12) return 1;   // (fewer than 12 tiles: up to 256 rows, left to the one-tile kernel)
   int64_t s = 74 / tiles;
   if (s > KB / 16) s = KB / 16;   // at least 16 k-blocks per unit
-  if (s > 8) s = 8;
+  if (s > PAIR_MAX_SPLITS) s = PAIR_MAX_SPLITS;
   if (s < 2) return 1;
   const int64_t per = ceil_div(KB, s);
   return static_cast<int>(ceil_div(KB, per));
@@ -2007,8 +2028,8 @@ template <typename T> int launch_pair(const Tc5Args& a, cudaStream_t st, int spl
   p.partial = static_cast<float*>(a.workspace);
   p.x = a.A;
   const int64_t tiles_m = ceil_div(a.M, 256), tiles = tiles_m * ceil_div(a.N, PAIR_BN), units = tiles * splits;
-  if (units >= (1ll << 30)) return B200_ENOTSUP;
-  if (splits > 1 && (!a.workspace || a.workspace_bytes < pair_splitk_bytes(a.M, a.N, splits) || (reinterpret_cast<uintptr_t>(a.workspace) & 15u)))
+  if (units >= (1ll << 30) || splits > PAIR_MAX_SPLITS) return B200_ENOTSUP;
+  if (splits > 1 && (!a.workspace || a.workspace_bytes < pair_splitk_bytes(a.M, a.N, splits) || (reinterpret_cast<uintptr_t>(a.workspace) & 31u)))   // 256-bit accesses
     return B200_ENOTSUP;
   const int pairs = static_cast<int>(units < sm_count() / 2 ? units : sm_count() / 2);
   launch_pdl(gemm_pair_kernel<T>, dim3(2 * pairs), dim3(PAIR_THREADS), PAIR_SMEM, st, ma, mw, p, static_cast<int>(tiles_m), static_cast<int>(tiles));

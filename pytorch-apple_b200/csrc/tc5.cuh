@@ -301,6 +301,16 @@ __device__ __forceinline__ float4 ld_cluster_f4(uint32_t cluster_addr) {
   return v;
 }
 
+// 256-bit global accesses (32-byte aligned): one full sector per lane and instruction
+__device__ __forceinline__ void st_global_f8(float* gptr, const float* v) {
+  asm volatile("st.global.v8.f32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(gptr), "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]), "f"(v[4]),
+               "f"(v[5]), "f"(v[6]), "f"(v[7]) : "memory");
+}
+__device__ __forceinline__ void ld_global_cg_f8(const float* gptr, float* v) {   // through L2 only
+  asm volatile("ld.global.cg.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];" : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]), "=f"(v[4]), "=f"(v[5]),
+               "=f"(v[6]), "=f"(v[7]) : "l"(gptr) : "memory");
+}
+
 
 // ---- CTA pairs (cta_group::2) --------------------------------------------------------------------
 // Two CTAs of a cluster (ranks 0 and 1) work on one 256-row tile: each holds its own 128 rows of A and

@@ -64,6 +64,7 @@ def close(got, ref, rtol=2e-2, atol=1e-2):
     (512, 8960, 1536, True, True, False, True),
     # few 256 x 256 tiles, long reduction: the pairs split K, a second kernel adds the fp32 partial sums
     (1024, 1536, 8960, True, True, False, False),
+    (512, 1536, 8960, False, True, False, False),
     (1000, 1200, 4104, False, False, True, False),
 ])
 def test_linear(lib, dtype, M, N, K, bias, res, relu, silu):
