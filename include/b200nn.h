@@ -193,6 +193,15 @@ int b200_rope_rotate(const b200_tensor* x, const void* cos_t, const void* sin_t,
                      void* kv_cache, const void* cache_pos, int64_t cache_len, int pos_dtype,
                      void* stream);
 
+/* b200_rope_rotate on q and k of one attention layer (same batch, positions, head_dim and
+ * tables; their own head counts and strides) to dense q_out / k_out, in one launch where
+ * one thread per (head, position) is the faster form (up to ~4700 positions; longer prompts
+ * run the two rotations one after the other).  Same roundings as two b200_rope_rotate calls.
+ * Replaces the two rotate chains of a prefill layer (metal_kernels/rope_rotate.metal:41-61;
+ * steps subgraph_analyzer.py:395-428). */
+int b200_rope_rotate_pair(const b200_tensor* q, const b200_tensor* k, const void* cos_t,
+                          const void* sin_t, void* q_out, void* k_out, void* stream);
+
 /* The three per-token steps between the QKV projection and decode attention in one
  * launch: RoPE on q -> q_out [B,Hq,T,D] dense; RoPE on k -> key cache row cache_pos[t];
  * v -> value cache row cache_pos[t] (caches [B,Hkv,cache_len,D], updated in place).

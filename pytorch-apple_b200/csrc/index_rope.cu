@@ -78,9 +78,9 @@ struct RopeParams {
 // values; the conversion unit is the scarce one), index arithmetic in IDX (32-bit when the
 // tensor allows it).
 template <typename T, typename IDX>
-__global__ void __launch_bounds__(128) rope_rotate_kernel(const __grid_constant__ RopeParams p) {
+__device__ __forceinline__ void rope_rotate_block(const RopeParams& p, unsigned block) {
   const IDX half_packs = static_cast<IDX>(p.D >> 4);
-  const IDX gid = static_cast<IDX>(blockIdx.x) * 128 + threadIdx.x;
+  const IDX gid = static_cast<IDX>(block) * 128 + threadIdx.x;
   const IDX total = static_cast<IDX>(p.B * p.H * p.T) * half_packs;
   if (gid >= total) return;
   const IDX row = gid / half_packs;
@@ -128,6 +128,21 @@ __global__ void __launch_bounds__(128) rope_rotate_kernel(const __grid_constant_
   }
   reinterpret_cast<uint4*>(dst)[pk] = pack8<T>(olo);
   reinterpret_cast<uint4*>(dst)[pk + hp] = pack8<T>(ohi);
+}
+
+template <typename T, typename IDX>
+__global__ void __launch_bounds__(128) rope_rotate_kernel(const __grid_constant__ RopeParams p) {
+  rope_rotate_block<T, IDX>(p, blockIdx.x);
+}
+
+// q and k of one attention layer in one launch: the first `q_blocks` blocks rotate q, the rest k.
+template <typename T>
+__global__ void __launch_bounds__(128) rope_rotate_pair_kernel(const __grid_constant__ RopeParams pq, const __grid_constant__ RopeParams pk,
+                                                               const unsigned q_blocks) {
+  pdl_wait();
+  pdl_trigger();
+  if (blockIdx.x < q_blocks) rope_rotate_block<T, uint32_t>(pq, blockIdx.x);
+  else rope_rotate_block<T, uint32_t>(pk, blockIdx.x - q_blocks);
 }
 
 // Many positions (prefill): one thread per (sequence, position, pack pair) walks ALL heads.  The
@@ -329,32 +344,64 @@ extern "C" int b200_rope_table(const float* inv_freq, const void* positions, voi
   return B200_OK;
 }
 
-extern "C" int b200_rope_rotate(const b200_tensor* x, const void* cos_t, const void* sin_t, void* y, void* kv_cache,
-                                const void* cache_pos, int64_t cache_len, int pos_dtype, void* stream) {
-  B200_CHECK_ARG(x && x->data && x->ndim == 4 && cos_t && sin_t && (y || kv_cache), "b200_rope_rotate: bad arguments");
-  B200_CHECK_ARG(x->stride[3] == 1 && x->shape[3] % 16 == 0, "b200_rope_rotate: head_dim must be contiguous and a multiple of 16");
-  B200_CHECK_ARG(!kv_cache || cache_pos, "b200_rope_rotate: cache write needs cache_pos");
-  RopeParams p;
+namespace {
+// Fills `p` from the operands of one rotation; B200_OK or the error code (message set).
+int rope_params(RopeParams& p, const char* who, const b200_tensor* x, const void* cos_t, const void* sin_t, void* y, void* kv_cache,
+                const void* cache_pos, int64_t cache_len, int pos_dtype) {
+  B200_CHECK_ARG(x && x->data && x->ndim == 4 && cos_t && sin_t && (y || kv_cache), "%s: bad arguments", who);
+  B200_CHECK_ARG(x->stride[3] == 1 && x->shape[3] % 16 == 0, "%s: head_dim must be contiguous and a multiple of 16", who);
+  B200_CHECK_ARG(!kv_cache || cache_pos, "%s: cache write needs cache_pos", who);
   p.x = x->data; p.cos_t = cos_t; p.sin_t = sin_t; p.y = y; p.cache = kv_cache; p.cache_pos = cache_pos;
   p.B = x->shape[0]; p.H = x->shape[1]; p.T = x->shape[2]; p.D = static_cast<int>(x->shape[3]);
   for (int i = 0; i < 3; ++i) p.xs[i] = x->stride[i];
   p.cache_len = cache_len; p.pos_dtype = pos_dtype;
   const bool ok = aligned16(x->data) && aligned16(cos_t) && aligned16(sin_t) && aligned16(kv_cache ? kv_cache : y) &&
                   p.xs[0] % 8 == 0 && p.xs[1] % 8 == 0 && p.xs[2] % 8 == 0;
-  if (!ok) B200_FAIL(B200_EALIGN, "b200_rope_rotate: operands must be 16-byte aligned with strides multiple of 8");
+  if (!ok) B200_FAIL(B200_EALIGN, "%s: operands must be 16-byte aligned with strides multiple of 8", who);
+  return B200_OK;
+}
+
+int rope_launch(const RopeParams& p, int dtype, bool to_cache, cudaStream_t st) {
   const int64_t total = p.B * p.H * p.T * (p.D >> 4);
   if (total == 0) return B200_OK;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int64_t grid = ceil_div(total, 128);
   B200_CHECK_ARG(grid < (1ll << 31), "b200_rope_rotate: tensor too large");
   const bool small = total + 128 < (1ll << 32);
   const int64_t per_head = p.B * p.T * (p.D >> 4);
-  B200_DISPATCH_HALF(x->dtype, T, {
-    if (!kv_cache && p.H >= 2 && per_head >= 4 * 64 * 148)   // enough positions to fill the GPU with one thread per (position, pack pair): below that (2048 tokens: 6.2 against 5.2 us) one thread per head wins
+  B200_DISPATCH_HALF(dtype, T, {
+    if (!to_cache && p.H >= 2 && per_head >= 4 * 64 * 148)   // enough positions to fill the GPU with one thread per (position, pack pair): below that (2048 tokens: 6.2 against 5.2 us) one thread per head wins
       rope_rotate_heads_kernel<T><<<static_cast<unsigned>(ceil_div(per_head, 128)), 128, 0, st>>>(p);
     else if (small) rope_rotate_kernel<T, uint32_t><<<static_cast<unsigned>(grid), 128, 0, st>>>(p);
     else rope_rotate_kernel<T, int64_t><<<static_cast<unsigned>(grid), 128, 0, st>>>(p);
   });
   B200_CHECK_LAUNCH("rope_rotate_kernel");
+  return B200_OK;
+}
+}  // namespace
+
+extern "C" int b200_rope_rotate(const b200_tensor* x, const void* cos_t, const void* sin_t, void* y, void* kv_cache,
+                                const void* cache_pos, int64_t cache_len, int pos_dtype, void* stream) {
+  RopeParams p;
+  if (const int rc = rope_params(p, "b200_rope_rotate", x, cos_t, sin_t, y, kv_cache, cache_pos, cache_len, pos_dtype)) return rc;
+  return rope_launch(p, x->dtype, kv_cache != nullptr, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int b200_rope_rotate_pair(const b200_tensor* q, const b200_tensor* k, const void* cos_t, const void* sin_t, void* q_out,
+                                     void* k_out, void* stream) {
+  RopeParams pq, pk;
+  if (const int rc = rope_params(pq, "b200_rope_rotate_pair", q, cos_t, sin_t, q_out, nullptr, nullptr, 0, 0)) return rc;
+  if (const int rc = rope_params(pk, "b200_rope_rotate_pair", k, cos_t, sin_t, k_out, nullptr, nullptr, 0, 0)) return rc;
+  B200_CHECK_ARG(q->dtype == k->dtype && pq.B == pk.B && pq.T == pk.T && pq.D == pk.D, "b200_rope_rotate_pair: q and k differ in dtype, batch, positions or head_dim");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t tq = pq.B * pq.H * pq.T * (pq.D >> 4), tk = pk.B * pk.H * pk.T * (pk.D >> 4);
+  const int64_t per_head = pq.B * pq.T * (pq.D >> 4);
+  // long prompts take the kernel that walks the heads of a position (two launches); an empty side needs none
+  if (tq == 0 || tk == 0 || per_head >= 4 * 64 * 148 || tq + tk + 256 >= (1ll << 32)) {
+    if (const int rc = rope_launch(pq, q->dtype, false, st)) return rc;
+    return rope_launch(pk, k->dtype, false, st);
+  }
+  const unsigned qb = static_cast<unsigned>(ceil_div(tq, 128)), kb = static_cast<unsigned>(ceil_div(tk, 128));
+  B200_DISPATCH_HALF(q->dtype, T, { launch_pdl(rope_rotate_pair_kernel<T>, dim3(qb + kb), dim3(128), 0, st, pq, pk, qb); });
+  B200_CHECK_LAUNCH("rope_rotate_pair_kernel");
   return B200_OK;
 }

@@ -8,6 +8,7 @@ what a decode step is made of:
 
 * ``b200.rmsnorm``     cast/pow/mean/add/rsqrt/mul/cast/mul            -> one kernel
 * ``b200.rope_rotate`` mul/slice/slice/neg/cat/mul/add                 -> one kernel
+* ``b200.rope_pair``   rope(q) + rope(k) of a prefill layer                  -> one launch
 * ``b200.attention``   repeat_kv + QK^T + scale + mask + softmax + PV + transpose/reshape
 * ``b200.softmax``     [scale] + mask add + softmax [+ cast]
 * ``b200.linear``      linear + {residual add, relu, silu*up} epilogues
@@ -549,6 +550,38 @@ def fuse_qkv_post(nodes: list[OpNode], graph: IRGraph) -> list[OpNode]:
             continue
         replace[id(matched[-1])] = macro
         drop.update(id(n) for n in matched[:-1])
+    if not replace:
+        return nodes
+    return [replace.get(id(n), n) for n in nodes if id(n) not in drop]
+
+
+
+def fuse_rope_pair(nodes: list[OpNode], graph: IRGraph) -> list[OpNode]:
+    """rope(q) and rope(k) of one attention layer (same cos / sin tables, batch, positions and
+    head dimension) that ``fuse_qkv_post`` left alone - a prefill layer, whose keys go to a
+    graph output instead of a cache: one launch for both.  The pair sits where the later of the
+    two was."""
+    gi = GraphIndex.build(nodes, graph)
+    replace: dict[int, OpNode] = {}
+    drop: set[int] = set()
+    ropes = [n for n in nodes if n.op_type == "b200.rope_rotate"]
+    for a in ropes:
+        if id(a) in drop or id(a) in replace:
+            continue
+        xa, cos_u, sin_u = a.inputs
+        b = next((n for n in ropes if n is not a and id(n) not in drop and id(n) not in replace
+                  and gi.position[id(n)] > gi.position[id(a)]
+                  and n.inputs[1].name == cos_u.name and n.inputs[2].name == sin_u.name and n.inputs[0].dtype == xa.dtype
+                  and len(n.inputs[0].shape) == 4 and len(xa.shape) == 4
+                  and n.inputs[0].shape[0] == xa.shape[0] and list(n.inputs[0].shape[2:]) == list(xa.shape[2:])), None)
+        if b is None:
+            continue
+        matched = [a, b]
+        macro = _macro("b200.rope_pair", b, [xa, b.inputs[0], cos_u, sin_u], [a.outputs[0], b.outputs[0]], {}, matched)
+        if not _acceptable(gi, matched, macro):
+            continue
+        replace[id(b)] = macro
+        drop.add(id(a))
     if not replace:
         return nodes
     return [replace.get(id(n), n) for n in nodes if id(n) not in drop]

@@ -45,6 +45,7 @@ from cuda_compiler.patterns import (
     GraphIndex,
     apply_patterns,
     fuse_qkv_post,
+    fuse_rope_pair,
     group_linears,
 )
 from npu_compiler.ir_reader import IRGraph, OpNode, TensorSpec
@@ -187,6 +188,7 @@ class _Lowering:
             nodes = apply_patterns(nodes, self.graph, DEFAULT_FAMILIES)
             nodes = group_linears(nodes, self.graph)
             nodes = fuse_qkv_post(nodes, self.graph)
+            nodes = fuse_rope_pair(nodes, self.graph)
         self.gi = GraphIndex.build(nodes, self.graph)
         self._chain_done: set[int] = set()
         for node in nodes:
@@ -763,6 +765,28 @@ class _Lowering:
         self.emit(SpecialKernelStep("rope_rotate_kernel", "x*cos + rotate_half(x)*sin", [x.name, cos_u.name, sin_u.name], out.name,
                                     params={"op": "rope_rotate", "x": xv, "cos": cv, "sin": sv, "y": o}),
                   [x.name, cos_u.name, sin_u.name, out.name])
+
+    def lower_rope_pair(self, node: OpNode) -> None:
+        q, k, cos_u, sin_u = node.inputs
+        q_out, k_out = node.outputs
+        qv, kv, cv, sv = (self.view(t.name) for t in (q, k, cos_u, sin_u))
+        B, _, T, D = qv.shape
+        dt = self.sd(q_out.dtype)
+
+        def table_ok(v: TensorView) -> bool:  # [B,1,T,D] dense over (b, t, d)
+            return v.dtype == dt and v.strides[3] == 1 and (T == 1 or v.strides[2] == D) and (B == 1 or v.strides[0] == T * D) and v.offset % 8 == 0
+
+        ok = dt in ("float16", "bfloat16") and self.sd(k_out.dtype) == dt and D % 16 == 0 and table_ok(cv) and table_ok(sv)
+        ok = ok and all(t.dtype == dt and t.strides[3] == 1 and t.offset % 8 == 0 and all(s % 8 == 0 for s in t.strides[:3]) for t in (qv, kv))
+        if not ok:
+            return self.lower_original(node)
+        qo = self.alloc(q_out.name, q_out.shape, dt)
+        ko = self.alloc(k_out.name, k_out.shape, dt)
+        names = [q.name, k.name, cos_u.name, sin_u.name]
+        self.emit(SpecialKernelStep("rope_rotate_pair_kernel", "q*cos + rotate_half(q)*sin; k*cos + rotate_half(k)*sin", names, q_out.name,
+                                    output_buffer_names=[q_out.name, k_out.name],
+                                    params={"op": "rope_rotate_pair", "q": qv, "k": kv, "cos": cv, "sin": sv, "q_out": qo, "k_out": ko}),
+                  names + [q_out.name, k_out.name])
 
     def lower_qkv_post(self, node: OpNode) -> None:
         q, k, v, cos_u, sin_u, cache_k, cache_v, index = node.inputs

@@ -532,6 +532,11 @@ class CUDAExecutor:
         plan.launches.append((self._lib.b200_rope_rotate, (C.byref(x), self._ptr(p["cos"]), self._ptr(p["sin"]), self._ptr(p["y"]),
                                                            None, None, 0, 0)))
 
+    def _bind_rope_rotate_pair(self, plan, step, p):
+        q, k = self._tensor(plan, p["q"]), self._tensor(plan, p["k"])
+        plan.launches.append((self._lib.b200_rope_rotate_pair, (C.byref(q), C.byref(k), self._ptr(p["cos"]), self._ptr(p["sin"]),
+                                                                self._ptr(p["q_out"]), self._ptr(p["k_out"]))))
+
     def _bind_qkv_post(self, plan, step, p):
         q, k, v = (self._tensor(plan, p[n]) for n in ("q", "k", "v"))
         iptr, idt = self._index_ptr(p["index"])

@@ -60,6 +60,7 @@ SIGNATURES = {
     "b200_argmax_rows": (_i, [_vp, _vp, _i64, _i64, _i64, _i, _vp]),
     "b200_rope_table": (_i, [_vp, _vp, _vp, _vp, _i64, _i, _i, _i, _vp]),
     "b200_rope_rotate": (_i, [_TP, _vp, _vp, _vp, _vp, _vp, _i64, _i, _vp]),
+    "b200_rope_rotate_pair": (_i, [_TP, _TP, _vp, _vp, _vp, _vp, _vp]),
     "b200_qkv_rope_cache": (_i, [_TP, _TP, _TP, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i, _vp]),
     "b200_max_pool2d": (_i, [_TP, _TP, _i, _i, _i, _i, _i, _i, _vp]),
     "b200_adaptive_avg_pool2d": (_i, [_TP, _TP, _vp]),

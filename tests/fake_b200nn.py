@@ -217,6 +217,12 @@ class FakeLibrary:
         _raw(y, dt, [B, H, T, D], [H * T * D, T * D, D, 1]).copy_(r)
         return 0
 
+    def b200_rope_rotate_pair(self, q, k, cos_t, sin_t, q_out, k_out, stream):
+        self.b200_rope_rotate(q, cos_t, sin_t, q_out, None, None, 0, 0, stream)
+        self.b200_rope_rotate(k, cos_t, sin_t, k_out, None, None, 0, 0, stream)
+        self.calls[-2:] = ["rope_rotate_pair"]
+        return 0
+
     def b200_qkv_rope_cache(self, q, k, v, cos_t, sin_t, q_out, k_cache, v_cache, cache_pos, cache_len, pos_dtype, stream):
         self.calls.append("qkv_rope_cache")
         Q, K, Vv = _t(q), _t(k), _t(v)

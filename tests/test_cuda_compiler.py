@@ -173,6 +173,23 @@ def test_qwen_mlp_pattern_at_real_sizes():
     assert not [s for s in prog.steps if isinstance(s, FusedKernelStep)]
 
 
+def test_qwen_prefill_layer_plan():
+    L = 2
+    cfg = mz.qwen2_config(num_layers=L)
+    ir = extract_ir(mz.QwenPrefillWrapper(mz.qwen2_model(cfg)), mz.qwen2_example_inputs(cfg, 1, 128, None), "qp")   # 128 rows: past the decode shapes, whose norms fold into the GEMMs
+    prog = compile_subgraph(ir)
+    kinds = [getattr(s, "kernel_name", None) or s.blas_type for s in prog.steps if not isinstance(s, AliasStep)]
+    # a prefill layer: norm, q/k/v, rope on q and k in one launch, attention, o_proj, norm, gate/up, down
+    assert kinds.count("rope_rotate_pair_kernel") == L and kinds.count("rope_rotate_kernel") == 0
+    assert kinds.count("attention") == L and kinds.count("rmsnorm_kernel") == 2 * L + 1 and kinds.count("gemm") == 4 * L + 1
+    assert (len(kinds) - 4) / L == 8                           # minus embedding, rope table, last norm, lm_head
+    pair = next(s for s in prog.steps if getattr(s, "kernel_name", None) == "rope_rotate_pair_kernel")
+    assert list(pair.output_buffer_names) == [pair.params["q_out"].buffer, pair.params["k_out"].buffer]
+    assert pair.params["q"].buffer == pair.params["k"].buffer   # both are slices of the merged projection's output
+    kinds0 = [getattr(s, "kernel_name", None) or s.blas_type for s in compile_subgraph(ir, fuse=False).steps if not isinstance(s, AliasStep)]
+    assert "rope_rotate_pair_kernel" not in kinds0
+
+
 def test_qwen_decode_layer_plan():
     L = 2
     cfg = mz.qwen2_config(num_layers=L)

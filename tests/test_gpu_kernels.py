@@ -538,6 +538,35 @@ def test_rope_table_and_rotate(lib, T):
     assert torch.equal(Y.cpu(), ref)
 
 
+@pytest.mark.parametrize("B,T", [(1, 512), (2, 37), (1, 5000)])
+def test_rope_rotate_pair_equals_two_rotations(lib, B, T):
+    """rope(q) and rope(k) of a prefill layer in one call, from column slices of the merged projection's
+    output: bit-identical to two b200_rope_rotate calls (5000 positions: the two-launch form inside)."""
+    dtype, Hq, Hkv, D = torch.bfloat16, 12, 2, 128
+    N = (Hq + 2 * Hkv) * D
+    qkv = gen((B, T, N), dtype).cuda()
+    inv = 1.0 / (1e6 ** (torch.arange(0, D, 2).float() / D))
+    ang = torch.cat([(torch.arange(T) + 3).float()[:, None] * inv[None]] * 2, -1)
+    cos = ang.cos().to(dtype)[None].expand(B, T, D).contiguous().cuda()
+    sin = ang.sin().to(dtype)[None].expand(B, T, D).contiguous().cuda()
+    q = qkv[..., :Hq * D].view(B, T, Hq, D).transpose(1, 2)
+    k = qkv[..., Hq * D:(Hq + Hkv) * D].view(B, T, Hkv, D).transpose(1, 2)
+    qo, ko = torch.empty(B, Hq, T, D, dtype=dtype, device="cuda"), torch.empty(B, Hkv, T, D, dtype=dtype, device="cuda")
+    qr, kr = torch.empty_like(qo), torch.empty_like(ko)
+    qs, ks = bt(q), bt(k)
+    ok(lib, lib.b200_rope_rotate_pair(C.byref(qs), C.byref(ks), cos.data_ptr(), sin.data_ptr(), qo.data_ptr(), ko.data_ptr(), stream()))
+    ok(lib, lib.b200_rope_rotate(C.byref(qs), cos.data_ptr(), sin.data_ptr(), qr.data_ptr(), None, None, 0, 0, stream()))
+    ok(lib, lib.b200_rope_rotate(C.byref(ks), cos.data_ptr(), sin.data_ptr(), kr.data_ptr(), None, None, 0, 0, stream()))
+    assert torch.equal(qo, qr) and torch.equal(ko, kr)
+    xf = k.float().cpu()
+    rot = torch.cat([-xf[..., D // 2:], xf[..., : D // 2]], -1)
+    c, s_ = cos.cpu().float()[:, None], sin.cpu().float()[:, None]
+    assert torch.equal(ko.cpu(), ((xf * c).to(dtype).float() + (rot * s_).to(dtype).float()).to(dtype))
+    # mismatched positions are refused
+    k_bad = bt(k[:, :, : T - 1])
+    assert lib.b200_rope_rotate_pair(C.byref(qs), C.byref(k_bad), cos.data_ptr(), sin.data_ptr(), qo.data_ptr(), ko.data_ptr(), stream()) == -1   # B200_EINVAL
+
+
 @pytest.mark.parametrize("B,T", [(1, 1), (8, 1), (2, 5)])
 def test_qkv_rope_cache_fused(lib, B, T):
     """rope(q), rope(k) -> key cache row, v -> value cache row in one launch, from column

@@ -121,6 +121,7 @@ def test_qwen_tiny_golden_prefill_then_decode(fake_native):
     irp = extract_ir(mz.QwenPrefillWrapper(model), mz.qwen2_example_inputs(cfg, 1, T, None, device="cpu"), "p")
     ins = np_inputs(irp, (torch.from_numpy(fx["ids"]), mz.causal_mask(1, T, T, 0), torch.arange(T)[None], torch.arange(T)))
     pre, _ = run_backend(irp, w, ins)
+    assert fake_native.calls.count("rope_rotate_pair") == L and "rope_rotate" not in fake_native.calls
     names = [o["name"] for o in irp["graph_outputs"]]
     gold = torch.from_numpy(fx["prefill_logits"]).view(torch.bfloat16).float().numpy()
     got = to_f32(pre[names[0]])
