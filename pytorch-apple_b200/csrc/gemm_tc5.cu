@@ -1208,8 +1208,10 @@ __global__ void __launch_bounds__(PCfg<BN, TS>::THREADS, 1)
 // rows (32 KB per k-block and CTA for the same 4.2 MFLOP), rank 0 issues M = 256 MMAs that read both
 // CTAs' shared memory and write both CTAs' tensor memory.  Linear layers only; the epilogue is the plain
 // one (accumulator rows -> registers -> global), overlapped with the next tile through the two accumulators.
-// warps: 0 / 7 activation producers, 6 / 8 weight producers, 1 MMA (rank 0) and TMEM, 2-5 epilogue.
-constexpr int PAIR_BN = 256, PAIR_ST = 6, PAIR_THREADS = 288;
+// warps: 0 / 7 activation producers, 6 / 8 weight producers, 1 MMA (rank 0) and TMEM, 2-5 epilogue of columns
+// 0..127, 9-12 epilogue of columns 128..255 (a tile that nothing follows - the last of a CTA, every split-K unit -
+// is drained in half the time).
+constexpr int PAIR_BN = 256, PAIR_ST = 6, PAIR_THREADS = 416;
 constexpr int PAIR_A_STAGE = BM * BK * 2, PAIR_B_STAGE = (PAIR_BN / 2) * BK * 2, PAIR_STAGE = PAIR_A_STAGE + PAIR_B_STAGE;
 constexpr int PAIR_SMEM = PAIR_ST * PAIR_STAGE + 1024;
 
@@ -1236,7 +1238,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
   if (threadIdx.x == 0) {
     failed = 0;
     for (int s = 0; s < ST; ++s) { tc5::mbar_init(&full_bar[s], 2); tc5::mbar_init(&empty_bar[s], 1); }   // full: rank 0's two producers of the k-block
-    for (int b = 0; b < 2; ++b) { tc5::mbar_init(&acc_full[b], 1); tc5::mbar_init(&acc_empty[b], 8); }     // empty: four epilogue warps of each CTA
+    for (int b = 0; b < 2; ++b) { tc5::mbar_init(&acc_full[b], 1); tc5::mbar_init(&acc_empty[b], 16); }    // empty: eight epilogue warps of each CTA
     tc5::fence_barrier_init();
     tc5::prefetch_tensormap(&map_a);
     tc5::prefetch_tensormap(&map_w);
@@ -1305,9 +1307,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
         tc5::umma_commit_pair(acc_full0 + 8u * b);
       }
     }
-  } else if (warp < 6) {
-    // ---- epilogue: this CTA's 128 accumulator rows ----
+  } else {
+    // ---- epilogue (warps 2-5 and 9-12): this CTA's 128 accumulator rows, columns c_lo .. c_lo + 127 ----
     const int q = warp & 3;
+    const int c_lo = warp >= 9 ? BN / 2 : 0, c_hi = c_lo + BN / 2;
     pdl_wait();
     const bool glu = (p.epilogue & B200_EPI_GLU) != 0;
     const bool res_fast = p.splits == 1 && !glu && p.residual && !(p.epilogue & B200_EPI_SILU_MUL) && p.ldr % 8 == 0 && p.N % 8 == 0 &&
@@ -1329,7 +1332,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
         for (int j = 0; j < 4; ++j)
           r[j] = (rrow && n0 + c + 8 * j < p.N) ? __ldg(reinterpret_cast<const uint4*>(rrow + c) + j) : make_uint4(0u, 0u, 0u, 0u);
       };
-      if (res_fast) fetch(0, rc);
+      if (res_fast) fetch(c_lo, rc);
       bool ok = true;
       if (lane == 0) ok = tc5::mbar_wait(&acc_full[b], (ti >> 1) & 1);
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
@@ -1341,11 +1344,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
       if (res_fast) {
         float va[16], vb[16];
 #pragma unroll 1
-        for (int c = 0; c < BN; c += 32) {
+        for (int c = c_lo; c < c_hi; c += 32) {
           __syncwarp();
           tc5::tmem_ld_32x16(t_row + c, va);
           tc5::tmem_ld_32x16(t_row + c + 16, vb);
-          if (c + 32 < BN) fetch(c + 32, rn);
+          if (c + 32 < c_hi) fetch(c + 32, rn);
           tc5::tmem_ld_wait();
           if (m < p.M && n0 + c < p.N) finish_cols_res<T>(p, va, m, n0 + c, rc[0], rc[1]);
           if (m < p.M && n0 + c + 16 < p.N) finish_cols_res<T>(p, vb, m, n0 + c + 16, rc[2], rc[3]);
@@ -1358,9 +1361,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
         float* dst = p.partial + (static_cast<int64_t>(unit / n_tiles) * p.M + m) * p.N + n0;
         float va[16], vb[16];
         __syncwarp();
-        tc5::tmem_ld_32x16(t_row, va);
+        tc5::tmem_ld_32x16(t_row + c_lo, va);
 #pragma unroll 1
-        for (int c = 0; c < BN; c += 32) {
+        for (int c = c_lo; c < c_hi; c += 32) {
           tc5::tmem_ld_wait();
           tc5::tmem_ld_32x16(t_row + c + 16, vb);
           if (m < p.M) {
@@ -1369,7 +1372,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
           }
           __syncwarp();
           tc5::tmem_ld_wait();
-          if (c + 32 < BN) tc5::tmem_ld_32x16(t_row + c + 32, va);
+          if (c + 32 < c_hi) tc5::tmem_ld_32x16(t_row + c + 32, va);
           if (m < p.M) {
             if (n0 + c + 16 < p.N) tc5::st_global_f8(dst + c + 16, vb);
             if (n0 + c + 24 < p.N) tc5::st_global_f8(dst + c + 24, vb + 8);
@@ -1378,7 +1381,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
         }
       } else if (glu) {
 #pragma unroll 1
-        for (int c = 0; c < BN / 2; c += 16) {   // c counts gate columns: block c / 64 of 128 merged columns
+        for (int c = c_lo / 2; c < c_hi / 2; c += 16) {   // c counts gate columns: block c / 64 of 128 merged columns
           float vg[16], vu[16];
           const int col = (c >> 6) * 128 + (c & 63);
           __syncwarp();
@@ -1391,14 +1394,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
       } else {
         float va[16], vb[16];   // two units in flight: the next tcgen05.ld runs under the current unit's math
         __syncwarp();
-        tc5::tmem_ld_32x16(t_row, va);
+        tc5::tmem_ld_32x16(t_row + c_lo, va);
 #pragma unroll 1
-        for (int c = 0; c < BN; c += 32) {
+        for (int c = c_lo; c < c_hi; c += 32) {
           tc5::tmem_ld_wait();
           tc5::tmem_ld_32x16(t_row + c + 16, vb);
           if (m < p.M && n0 + c < p.N) finish_cols<T, 16>(p, va, m, n0 + c);
           tc5::tmem_ld_wait();
-          if (c + 32 < BN) tc5::tmem_ld_32x16(t_row + c + 32, va);
+          if (c + 32 < c_hi) tc5::tmem_ld_32x16(t_row + c + 32, va);
           if (m < p.M && n0 + c + 16 < p.N) finish_cols<T, 16>(p, vb, m, n0 + c + 16);
         }
       }
