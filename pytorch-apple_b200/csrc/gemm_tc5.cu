@@ -37,9 +37,10 @@ constexpr int NORM_MAX_PARTS = 32;   // row scaling: at most this many sum-of-sq
 template <int BN, int MODE> struct Cfg {
   static constexpr int AROWS = MODE >= 2 ? 64 : 128;
   static constexpr int A_STAGE = AROWS * BK * 2;
-  // k-blocks per ring stage: the decode shapes pair them (one barrier hand-off per two k-blocks of MMAs)
-  static constexpr int KPS = MODE >= 2 ? 2 : 1;
-  static constexpr int ST = MODE == 0 ? (BN == 128 ? 3 : 4) : MODE == 1 ? (BN == 128 ? 4 : 6) : (BN == 128 ? 3 : 6);
+  // k-blocks per ring stage: the linear shapes with staged epilogues pair them (one barrier hand-off per two
+  // k-blocks of MMAs; decode step 2.83 -> 2.76 ms, projections of a 512-token prompt 11.2 -> 10.7 us)
+  static constexpr int KPS = MODE >= 1 ? 2 : 1;
+  static constexpr int ST = MODE == 0 ? (BN == 128 ? 3 : 4) : MODE == 1 ? (BN == 128 ? 2 : 3) : (BN == 128 ? 3 : 6);
   static constexpr int CTAS = MODE == 0 ? 2 : 1;
   static constexpr int ISSUE_GROUP = ST >= 12 ? 4 : ST >= 6 ? 3 : ST >= 4 ? 2 : 1;   // ring stages a producer thread fills per barrier wait
   static constexpr int RING = ST * KPS * (A_STAGE + BN * BK * 2);
