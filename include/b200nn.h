@@ -262,7 +262,7 @@ int b200_conv_weight_prep(const void* w, const void* conv_bias, const void* gamm
  * (cta_group::2) for M > 128, N >= 1024, K >= 1024.  `workspace` (zero-initialised by the
  * caller once, left zeroed by every call; b200_linear_workspace_bytes gives the size, 0
  * when none is needed) serves two cases: the pair kernel's split-K for 12..36 tiles with
- * K >= 4096 (fp32 partial sums, added in index order by a second kernel; without a
+ * K >= 4096 (fp32 partial sums in a 32-byte aligned workspace, added in index order by a second kernel; without a
  * workspace the shape takes the cluster split-K instead), and the weight-streaming
  * fallback for operands with M <= 64 that miss the TMA rules. */
 int b200_linear(const void* A, const void* W, const void* bias, const void* residual, void* out,
