@@ -173,6 +173,45 @@ def test_qwen_mlp_pattern_at_real_sizes():
     assert not [s for s in prog.steps if isinstance(s, FusedKernelStep)]
 
 
+def _two_rope_graph(T=16, D=128, dtype="bfloat16", reader_between=False):
+    """rope(q [1,12,T,D]) and rope(k [1,2,T,D]) over the same cos / sin tables; with ``reader_between`` a neg of
+    the rotated q sits before the k chain in node order."""
+    inv, pos = ts("inv_freq", [D // 2], "float32"), ts("position_ids", [1, T], "int64")
+    cs = lambda n: ts(n, [1, T, D], dtype)
+    u = lambda n: ts(n, [1, 1, T, D], dtype)
+    n = [node("hop", "wrap_with_set_grad_enabled", [inv, pos], [cs("hop_0"), cs("hop_1")]),
+         node("cos", "<built-in function getitem>", [cs("hop_0"), cs("hop_1")], [cs("cos")], index=0),
+         node("sin", "<built-in function getitem>", [cs("hop_0"), cs("hop_1")], [cs("sin")], index=1),
+         node("cos_u", "aten.unsqueeze.default", [cs("cos")], [u("cos_u")], dim=1),
+         node("sin_u", "aten.unsqueeze.default", [cs("sin")], [u("sin_u")], dim=1)]
+    outs = []
+    for tag, H in (("q", 12), ("k", 2)):
+        x = ts(tag, [1, H, T, D], dtype)
+        h = lambda nm: ts(f"{tag}_{nm}", [1, H, T, D // 2], dtype)
+        f = lambda nm: ts(f"{tag}_{nm}", [1, H, T, D], dtype)
+        n += [node(f"{tag}_mul_c", "aten.mul.Tensor", [x, u("cos_u")], [f("mul_c")]),
+              node(f"{tag}_lo", "aten.slice.Tensor", [x], [h("lo")], dim=3, start=0, end=D // 2),
+              node(f"{tag}_hi", "aten.slice.Tensor", [x], [h("hi")], dim=3, start=D // 2, end=9223372036854775807),
+              node(f"{tag}_neg", "aten.neg.default", [h("hi")], [h("neg")]),
+              node(f"{tag}_cat", "aten.cat.default", [h("neg"), h("lo")], [f("cat")], dim=-1),
+              node(f"{tag}_mul_s", "aten.mul.Tensor", [f("cat"), u("sin_u")], [f("mul_s")]),
+              node(f"{tag}_y", "aten.add.Tensor", [f("mul_c"), f("mul_s")], [f("y")])]
+        outs.append(f("y"))
+        if tag == "q" and reader_between:
+            n.append(node("q_after", "aten.neg.default", [f("y")], [f("after")]))
+            outs.append(f("after"))
+    return graph(n, [ts("q", [1, 12, T, D], dtype), ts("k", [1, 2, T, D], dtype), pos], outs, [inv])
+
+
+def test_two_ropes_over_the_same_tables_share_a_launch():
+    kinds = [getattr(s, "kernel_name", None) for s in analyze_subgraph(load_ir_from_dict(_two_rope_graph()))]
+    assert kinds.count("rope_rotate_pair_kernel") == 1 and kinds.count("rope_rotate_kernel") == 0
+    # a reader of the first result that comes before the second rotation keeps the two apart (the pair runs where
+    # the later rotation was, which would be after that reader)
+    kinds = [getattr(s, "kernel_name", None) for s in analyze_subgraph(load_ir_from_dict(_two_rope_graph(reader_between=True)))]
+    assert kinds.count("rope_rotate_pair_kernel") == 0 and kinds.count("rope_rotate_kernel") == 2
+
+
 def test_qwen_prefill_layer_plan():
     L = 2
     cfg = mz.qwen2_config(num_layers=L)
