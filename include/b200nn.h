@@ -271,6 +271,20 @@ int b200_linear(const void* A, const void* W, const void* bias, const void* resi
                 void* workspace, int64_t workspace_bytes, void* stream);
 int64_t b200_linear_workspace_bytes(int64_t M, int64_t N, int64_t K);
 
+/* b200_linear followed by b200_rmsnorm of its output rows: out as b200_linear (bias,
+ * residual, B200_EPI_RELU / _W_STATIC; no aux, no gated epilogue), norm_out[m, :] =
+ * rmsnorm(out[m, :]) * norm_weight with the roundings of b200_rmsnorm (round_mid as there),
+ * row stride ldn.  Replaces a CUBLASStep("gemm") (cuda_executor.py:182-208) and the
+ * `rmsnorm_kernel` launch that reads its result (cuda_templates.py:458-506).  Where the GEMM
+ * takes the CTA-pair split-K path (see b200_linear) and N <= 2048 the kernel that adds up the
+ * partial sums also normalises the finished row - one launch less; every other shape runs
+ * the two kernels one after the other inside this call. */
+int b200_linear_rmsnorm(const void* A, const void* W, const void* bias, const void* residual,
+                        void* out, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldw,
+                        int64_t ldo, int64_t ldr, int dtype, int bias_dtype, int epilogue,
+                        void* workspace, int64_t workspace_bytes, const void* norm_weight,
+                        void* norm_out, int64_t ldn, float norm_eps, int round_mid, void* stream);
+
 /* Decode-shape (M <= 64) linear layer with the neighbouring RMSNorm folded in, replacing a
  * `rmsnorm_kernel` launch (cuda_templates.py:458-506, matcher subgraph_analyzer.py:667-756)
  * plus the CUBLASStep("gemm") that consumes it (cuda_executor.py:182-208).

@@ -572,6 +572,30 @@ extern "C" int b200_linear(const void* A, const void* W, const void* bias, const
   return B200_OK;
 }
 
+extern "C" int b200_rmsnorm(const void* x, const void* w, void* y, int64_t rows, int64_t cols, int64_t x_row_stride,
+                            int64_t y_row_stride, float eps, int dtype, int round_mid, void* stream);
+
+extern "C" int b200_linear_rmsnorm(const void* A, const void* W, const void* bias, const void* residual, void* out, int64_t M,
+                                   int64_t N, int64_t K, int64_t lda, int64_t ldw, int64_t ldo, int64_t ldr, int dtype,
+                                   int bias_dtype, int epilogue, void* workspace, int64_t workspace_bytes, const void* norm_weight,
+                                   void* norm_out, int64_t ldn, float norm_eps, int round_mid, void* stream) {
+  B200_CHECK_ARG(A && W && out && norm_weight && norm_out && M >= 0 && N > 0 && K > 0, "b200_linear_rmsnorm: bad arguments");
+  B200_CHECK_ARG(!(epilogue & (B200_EPI_SILU_MUL | B200_EPI_GLU)), "b200_linear_rmsnorm: gated epilogues are not supported");
+  if (M == 0) return B200_OK;
+  int done = 0;
+  int rc = B200_ENOTSUP;
+  if (K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0 && aligned16(A) && aligned16(W)) {
+    Tc5Args t{A, W, bias, residual, nullptr, out, M, N, K, lda, ldw, ldo, ldr, 0, dtype, bias_dtype, epilogue, workspace, workspace_bytes};
+    t.norm_tail.gain = norm_weight; t.norm_tail.out = norm_out; t.norm_tail.ld = ldn; t.norm_tail.eps = norm_eps;
+    t.norm_tail.round_mid = round_mid; t.norm_tail.done = &done;
+    rc = linear_tc5(t, static_cast<cudaStream_t>(stream));
+  }
+  if (rc == B200_ENOTSUP)
+    rc = b200_linear(A, W, bias, residual, out, M, N, K, lda, ldw, ldo, ldr, dtype, bias_dtype, epilogue, nullptr, 0, workspace, workspace_bytes, stream);
+  if (rc != B200_OK || done) return rc;
+  return b200_rmsnorm(out, norm_weight, norm_out, M, N, ldo, ldn, norm_eps, dtype, round_mid, stream);
+}
+
 extern "C" int b200_conv2d_nhwc(const void* x, const void* w, const float* bias, const void* residual, void* y, int N, int H,
                                 int W, int C, int C_pad, int O, int KH, int KW, int sh, int sw, int ph, int pw, int Ho, int Wo,
                                 int dtype, int epilogue, void* stream) {

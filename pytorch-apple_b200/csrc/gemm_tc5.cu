@@ -1449,6 +1449,62 @@ __global__ void __launch_bounds__(256) pair_splitk_reduce_kernel(const Tc5Params
   }
 }
 
+// The same with the RMSNorm of the finished row as a tail: one block per output row (N / 8 threads, N <= 2048), so
+// that the row's sum of squares can be formed inside the block.  norm_out[m, :] = rmsnorm(out[m, :]) * gain with the
+// roundings of the stand-alone kernel: the sum runs over the outputs as stored (rounded to T), x * r is rounded to T
+// before the gain when round_mid is set.
+struct NormTailParams { const void* gain; void* out; int64_t ld; float eps; int round_mid; };
+
+template <typename T>
+__global__ void __launch_bounds__(256) pair_splitk_reduce_norm_kernel(const Tc5Params p, const NormTailParams nt) {
+  __shared__ float warp_ss[8];
+  pdl_trigger();
+  pdl_wait();
+  const int64_t m = blockIdx.x, plane = p.M * p.N;
+  const int64_t n = static_cast<int64_t>(threadIdx.x) * 8;
+  const bool act = n < p.N;
+  float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  uint4 graw = make_uint4(0u, 0u, 0u, 0u);
+  float ss = 0.f;
+  if (act) {
+    float* const q = p.partial + m * p.N + n;
+    float a[PAIR_MAX_SPLITS][8];
+#pragma unroll
+    for (int s = 0; s < PAIR_MAX_SPLITS; ++s)
+      if (s < p.splits) tc5::ld_global_cg_f8(q + s * plane, a[s]);
+    graw = __ldg(reinterpret_cast<const uint4*>(static_cast<const T*>(nt.gain) + n));
+    const float zero[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int s = 0; s < PAIR_MAX_SPLITS; ++s) {
+      if (s < p.splits) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] += a[s][i];
+        tc5::st_global_f8(q + s * plane, zero);
+      }
+    }
+    finish_cols<T, 8>(p, v, m, n);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { v[i] = round_as<T>(v[i]); ss += v[i] * v[i]; }
+  }
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+  if ((threadIdx.x & 31) == 0) warp_ss[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+  for (int w = 0; w < static_cast<int>(blockDim.x >> 5); ++w) tot += warp_ss[w];
+  if (!act) return;
+  const float r = 1.0f / sqrtf(tot / static_cast<float>(p.N) + nt.eps);
+  float g[8];
+  unpack8<T>(graw, g);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    float x = v[i] * r;
+    if (nt.round_mid) x = round_as<T>(x);
+    v[i] = x * g[i];
+  }
+  *reinterpret_cast<uint4*>(static_cast<T*>(nt.out) + m * nt.ld + n) = pack8<T>(v);
+}
+
 // ---- 7x7 / stride-2 stem convolution on the 8-channel padded input ------------------------------
 // The im2col route moves one 16-byte row per (pixel, tap): 7168 TMA rows per 128-pixel tile.  Here a
 // persistent CTA walks consecutive output rows of an image and keeps the input rows it needs in a
@@ -2039,10 +2095,21 @@ template <typename T> int launch_pair(const Tc5Args& a, cudaStream_t st, int spl
   launch_pdl(gemm_pair_kernel<T>, dim3(2 * pairs), dim3(PAIR_THREADS), PAIR_SMEM, st, ma, mw, p, static_cast<int>(tiles_m), static_cast<int>(tiles));
   B200_CHECK_LAUNCH("gemm_pair_kernel");
   if (splits > 1) {
-    const int64_t work = a.M * (a.N / 8);
-    const int blocks = static_cast<int>(ceil_div(work, 256) < 4 * sm_count() ? ceil_div(work, 256) : 4 * sm_count());
-    launch_pdl(pair_splitk_reduce_kernel<T>, dim3(blocks), dim3(256), 0, st, p);
-    B200_CHECK_LAUNCH("pair_splitk_reduce_kernel");
+    const Tc5Args::NormTail& t = a.norm_tail;
+    const bool tail = t.out && t.gain && t.done && a.N <= 2048 && a.M < (1ll << 31) && t.ld % 8 == 0 && aligned16(t.out) && aligned16(t.gain) &&
+                      !(a.epilogue & B200_EPI_SILU_MUL);
+    if (tail) {
+      const NormTailParams nt{t.gain, t.out, t.ld, t.eps, t.round_mid};
+      const int threads = static_cast<int>(ceil_div(a.N / 8, 32) * 32);
+      launch_pdl(pair_splitk_reduce_norm_kernel<T>, dim3(static_cast<unsigned>(a.M)), dim3(threads), 0, st, p, nt);
+      B200_CHECK_LAUNCH("pair_splitk_reduce_norm_kernel");
+      *t.done = 1;
+    } else {
+      const int64_t work = a.M * (a.N / 8);
+      const int blocks = static_cast<int>(ceil_div(work, 256) < 4 * sm_count() ? ceil_div(work, 256) : 4 * sm_count());
+      launch_pdl(pair_splitk_reduce_kernel<T>, dim3(blocks), dim3(256), 0, st, p);
+      B200_CHECK_LAUNCH("pair_splitk_reduce_kernel");
+    }
   }
   return B200_OK;
 }

@@ -30,6 +30,17 @@ struct Tc5Args {
     int64_t cache_len = 0;
     int Hq = 0, Hkv = 0, pos_dtype = 0;
   } rope;
+  // RMSNorm of the output rows as a tail of the GEMM (b200_linear_rmsnorm): norm_out[m, :] =
+  // rmsnorm(out[m, :]) * gain, same roundings as b200_rmsnorm.  Only the split-K reduce kernel of the
+  // CTA-pair path can take it (one block per output row); it sets *done, otherwise the caller runs the
+  // RMSNorm kernel after the GEMM.
+  struct NormTail {
+    const void* gain = nullptr; void* out = nullptr;
+    int64_t ld = 0;
+    float eps = 0.f;
+    int round_mid = 0;
+    int* done = nullptr;
+  } norm_tail;
 };
 
 // Geometry of an NHWC convolution run as an implicit GEMM (A rows are output pixels,

@@ -198,6 +198,7 @@ class _Lowering:
         if self.fuse:
             self._fold_rmsnorm_into_decode_linears()
             self._fuse_rope_into_qkv_linear()
+            self._append_rmsnorm_to_splitk_linears()
         return self.out
 
     def _fuse_rope_into_qkv_linear(self) -> None:
@@ -338,6 +339,52 @@ class _Lowering:
                 cons.input_buffer_names = [x_view.buffer if n == y_name else n for n in cons.input_buffer_names]
             cp["source"] = "rmsnorm(x) folded in: " + cp.get("source", "")
             drop.add(i)
+        if drop:
+            self.out.steps = [s for i, s in enumerate(steps) if i not in drop]
+            self.out.step_tensors = [t for i, t in enumerate(touched) if i not in drop]
+
+    @staticmethod
+    def _pair_splitk_shape(M: int, N: int, K: int) -> bool:
+        """The shapes the library runs on 256 x 256 CTA-pair tiles with split-K and a reduce kernel (few
+        tiles, long reduction: the down projection of a 512- or 1024-token prompt), and whose rows that
+        kernel can normalise.  A wrong guess costs nothing but a plan that promises a fusion the library
+        then runs as two kernels."""
+        tiles = -(-M // 256) * -(-N // 256)
+        return M > 128 and 256 <= N <= 2048 and N % 8 == 0 and K >= 4096 and 12 <= tiles < 37
+
+    def _append_rmsnorm_to_splitk_linears(self) -> None:
+        """A GEMM whose partial sums are added up by a second kernel, followed directly by the RMSNorm
+        of its result (down projection + residual -> the next layer's input norm at prefill): the
+        adding kernel normalises the finished row as well (``b200_linear_rmsnorm``), same roundings,
+        one launch less.  The GEMM result itself is still written - the residual stream reads it."""
+        steps, touched = self.out.steps, self.out.step_tensors
+        drop: set[int] = set()
+        last = -1   # the last step that is not an alias
+        for i, st in enumerate(steps):
+            if isinstance(st, AliasStep):
+                continue
+            prev, last = last, i
+            p = getattr(st, "params", None) or {}
+            if p.get("op") != "rmsnorm" or prev < 0 or prev in drop:
+                continue
+            lp = getattr(steps[prev], "params", None) or {}
+            if lp.get("op") != "linear" or lp.get("glu") or lp.get("aux") is not None or lp.get("norm") or lp.get("sumsq_out") is not None \
+                    or lp.get("norm_tail") or not isinstance(steps[prev], CUBLASStep):
+                continue
+            x, y, ly = p["x"], p["y"], lp["y"]
+            M, N, K = lp["M"], lp["N"], lp["K"]
+            if p["rows"] != M or p["cols"] != N or not self._pair_splitk_shape(M, N, K):
+                continue
+            row = lambda v: v.strides[-2] if len(v.shape) >= 2 and v.shape[-2] > 1 else v.shape[-1]
+            if x.buffer != ly.buffer or x.offset != ly.offset or x.dtype != ly.dtype or x.strides[-1] != 1 or row(x) != row(ly) \
+                    or y.strides[-1] != 1 or row(y) % 8 or y.offset % 8 or row(y) != N:
+                continue
+            lp["norm_tail"] = {"w": p["w"], "y": y, "eps": float(p["eps"]), "round_mid": bool(p["round_mid"])}
+            lp["source"] = lp.get("source", "") + " ; rmsnorm(result) * gain"
+            steps[prev].input_buffer_names = list(dict.fromkeys(list(steps[prev].input_buffer_names) + [p["w"]]))
+            touched[prev] = list(dict.fromkeys(list(touched[prev]) + [n for n in touched[i]]))
+            drop.add(i)
+            last = prev
         if drop:
             self.out.steps = [s for i, s in enumerate(steps) if i not in drop]
             self.out.step_tensors = [t for i, t in enumerate(touched) if i not in drop]

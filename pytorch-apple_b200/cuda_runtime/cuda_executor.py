@@ -590,6 +590,14 @@ class CUDAExecutor:
                 float(norm["eps"]) if norm else 0.0, self._ptr(norm["sumsq"]) if norm else None, int(norm["cols"]) if norm else 0,
                 self._ptr(sumsq_out))))
             return
+        tail = p.get("norm_tail")
+        if tail is not None:   # the RMSNorm of the result rides on the kernel that adds up the split-K partial sums
+            plan.launches.append((self._lib.b200_linear_rmsnorm, (
+                self._ptr(x), self._wptr(p["w"], dt), self._wptr(p["bias"], dt), self._ptr(res), self._ptr(y), p["M"], p["N"], p["K"],
+                ld(x), p["K"], ld(y), ld(res), DTYPE_CODES[dt], DTYPE_CODES[dt], epi,
+                ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,
+                self._wptr(tail["w"], dt), self._ptr(tail["y"]), p["N"], float(tail["eps"]), int(tail["round_mid"]))))
+            return
         plan.launches.append((self._lib.b200_linear, (
             self._ptr(x), self._wptr(p["w"], dt), self._wptr(p["bias"], dt), self._ptr(res), self._ptr(y), p["M"], p["N"], p["K"],
             ld(x), p["K"], ld(y), ld(res), DTYPE_CODES[dt], DTYPE_CODES[dt], epi, self._ptr(aux), ld(aux),

@@ -68,6 +68,7 @@ SIGNATURES = {
     "b200_conv_weight_prep": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _i, _vp]),
     "b200_linear": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _vp, _i64, _vp, _i64, _vp]),
     "b200_linear_workspace_bytes": (_i64, [_i64, _i64, _i64]),
+    "b200_linear_rmsnorm": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _vp, _i64, _vp, _vp, _i64, _f, _i, _vp]),
     "b200_linear_norm": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _f, _vp, _i, _vp, _vp]),
     "b200_linear_qkv_rope": (_i, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _f, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i,
                                   _vp]),

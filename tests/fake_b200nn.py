@@ -308,6 +308,14 @@ class FakeLibrary:
         _raw(out, dt, [M, N], [ldo, 1]).copy_(r.to(dt))
         return 0
 
+    def b200_linear_rmsnorm(self, A, W, bias, residual, out, M, N, K, lda, ldw, ldo, ldr, dtype, bias_dtype, epilogue, workspace,
+                            workspace_bytes, norm_weight, norm_out, ldn, norm_eps, round_mid, stream):
+        self.b200_linear(A, W, bias, residual, out, M, N, K, lda, ldw, ldo, ldr, dtype, bias_dtype, epilogue, None, 0, workspace,
+                         workspace_bytes, stream)
+        self.b200_rmsnorm(out, norm_weight, norm_out, M, N, ldo, ldn, norm_eps, dtype, round_mid, stream)
+        self.calls[-2:] = ["linear_rmsnorm"]
+        return 0
+
     def b200_linear_norm(self, A, W, bias, residual, out, M, N, K, lda, ldw, ldo, ldr, dtype, bias_dtype, epilogue, norm_eps,
                          sumsq_in, sumsq_in_cols, sumsq_out, stream):
         self.calls.append("linear_norm")

@@ -227,6 +227,14 @@ def test_qwen_prefill_layer_plan():
     assert pair.params["q"].buffer == pair.params["k"].buffer   # both are slices of the merged projection's output
     kinds0 = [getattr(s, "kernel_name", None) or s.blas_type for s in compile_subgraph(ir, fuse=False).steps if not isinstance(s, AliasStep)]
     assert "rope_rotate_pair_kernel" not in kinds0
+    # 512 tokens: the down projection (12 tiles of 256 x 256, K = 8960) is split over CTA pairs, and the kernel that adds up
+    # its partial sums also applies the RMSNorm that follows (the next layer's input norm, the final norm)
+    ir512 = extract_ir(mz.QwenPrefillWrapper(mz.qwen2_model(cfg)), mz.qwen2_example_inputs(cfg, 1, 512, None), "qp512")
+    prog512 = compile_subgraph(ir512)
+    kinds512 = [getattr(s, "kernel_name", None) or s.blas_type for s in prog512.steps if not isinstance(s, AliasStep)]
+    tails = [s.params for s in prog512.steps if isinstance(s, CUBLASStep) and s.params.get("norm_tail")]
+    assert len(tails) == L and all(t["K"] == cfg.intermediate_size and t["residual"] is not None for t in tails)
+    assert kinds512.count("rmsnorm_kernel") == L + 1 and kinds512.count("gemm") == 4 * L + 1
 
 
 def test_qwen_decode_layer_plan():

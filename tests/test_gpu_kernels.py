@@ -538,6 +538,38 @@ def test_rope_table_and_rotate(lib, T):
     assert torch.equal(Y.cpu(), ref)
 
 
+@pytest.mark.parametrize("M,N,K,fused", [(512, 1536, 8960, True), (1000, 1200, 4104, True), (300, 1536, 1024, False), (64, 1536, 8960, False)])
+def test_linear_rmsnorm_equals_the_two_kernels(lib, M, N, K, fused):
+    """b200_linear_rmsnorm = b200_linear then b200_rmsnorm.  On the CTA-pair split-K shapes the reduce kernel normalises the
+    rows itself (the sum of squares is added in another order: last-bit differences); elsewhere the two kernels run as they are."""
+    dtype = torch.bfloat16
+    a, w, r = gen((M, K), dtype).cuda(), gen((N, K), dtype, 1, 0.05).cuda(), gen((M, N), dtype, 2).cuda()
+    b, g = gen((N,), dtype, 3).cuda(), (1 + 0.1 * gen((N,), dtype, 4).float()).to(dtype).cuda()
+    nb = lib.b200_linear_workspace_bytes(M, N, K)
+    assert nb > 0 or not fused
+    ws = torch.zeros(max(nb, 32), dtype=torch.uint8, device="cuda")
+    h1, n1, h2, n2 = (torch.empty(M, N, dtype=dtype, device="cuda") for _ in range(4))
+    for round_mid in (1, 0):
+        ok(lib, lib.b200_linear_rmsnorm(a.data_ptr(), w.data_ptr(), b.data_ptr(), r.data_ptr(), h1.data_ptr(), M, N, K, K, K, N, N, 2, 2, 0,
+                                        ws.data_ptr(), ws.numel(), g.data_ptr(), n1.data_ptr(), N, 1e-6, round_mid, stream()))
+        ok(lib, lib.b200_linear(a.data_ptr(), w.data_ptr(), b.data_ptr(), r.data_ptr(), h2.data_ptr(), M, N, K, K, K, N, N, 2, 2, 0, None, 0,
+                                ws.data_ptr(), ws.numel(), stream()))
+        ok(lib, lib.b200_rmsnorm(h2.data_ptr(), g.data_ptr(), n2.data_ptr(), M, N, N, N, 1e-6, 2, round_mid, stream()))
+        torch.cuda.synchronize()
+        assert torch.equal(h1, h2)
+        assert int(ws.count_nonzero()) == 0                     # the split-K workspace is left zeroed
+        if fused:
+            ulp = (n1.view(torch.int16).int() - n2.view(torch.int16).int()).abs()
+            assert int(ulp.max()) <= 1 and float((ulp != 0).float().mean()) < 0.01
+        else:
+            assert torch.equal(n1, n2)
+        hf = h2.float()
+        x = hf * torch.rsqrt(hf.pow(2).mean(-1, keepdim=True) + 1e-6)
+        if round_mid:
+            x = x.to(dtype).float()
+        close(n1, (x * g.float()).cpu(), rtol=2e-2, atol=2e-2)
+
+
 @pytest.mark.parametrize("B,T", [(1, 512), (2, 37), (1, 5000)])
 def test_rope_rotate_pair_equals_two_rotations(lib, B, T):
     """rope(q) and rope(k) of a prefill layer in one call, from column slices of the merged projection's

@@ -43,6 +43,41 @@ def test_rmsnorm_graph(fake_native, rows):
     assert fake_native.calls == ["rmsnorm"]
 
 
+def _linear_residual_rmsnorm_graph(M, N, K, dtype="bfloat16", eps=1e-6):
+    """h = a @ W^T + r;  y = rmsnorm(h) * g  - the down projection of a layer and the next layer's input norm."""
+    f32 = "float32"
+    a, r, w, g = ts("a", [M, K], dtype), ts("r", [M, N], dtype), ts("w_down", [N, K], dtype), ts("g", [N], dtype)
+    t = lambda n, d=dtype, c=N: ts(n, [M, c], d)
+    n = [node("lin", "aten.linear.default", [a, w], [t("lin")]),
+         node("h", "aten.add.Tensor", [r, t("lin")], [t("h")]),
+         node("to_a", "aten.to.dtype", [t("h")], [t("to_a", f32)], dtype="torch.float32"),
+         node("pow_1", "aten.pow.Tensor_Scalar", [t("to_a", f32)], [t("pow_1", f32)], exponent=2),
+         node("mean", "aten.mean.dim", [t("pow_1", f32)], [t("mean", f32, 1)], dim=[-1], keepdim=True),
+         node("add", "aten.add.Tensor", [t("mean", f32, 1)], [t("add", f32, 1)], other=eps),
+         node("rsqrt", "aten.rsqrt.default", [t("add", f32, 1)], [t("rsqrt", f32, 1)]),
+         node("mul_a", "aten.mul.Tensor", [t("to_a", f32), t("rsqrt", f32, 1)], [t("mul_a", f32)]),
+         node("to_b", "aten.to.dtype", [t("mul_a", f32)], [t("to_b")], dtype="torch." + dtype),
+         node("y", "aten.mul.Tensor", [g, t("to_b")], [t("y")])]
+    return graph(n, [a, r], [t("h"), t("y")], [w, g])
+
+
+def test_rmsnorm_rides_on_the_splitk_reduction_of_a_prefill_down_projection(fake_native):
+    M, N, K = 512, 1536, 4096   # 12 tiles of 256 x 256, long reduction: the shape class the library splits over CTA pairs
+    ir = _linear_residual_rmsnorm_graph(M, N, K)
+    a, r = rand((M, K)), rand((M, N), seed=1)
+    w, g = (0.02 * rand((N, K), seed=2).float()).bfloat16(), (1 + 0.02 * rand((N,), seed=3).float()).bfloat16()
+    out, _ = run_backend(ir, {"w_down": torch_to_numpy(w), "g": torch_to_numpy(g)}, {"a": torch_to_numpy(a), "r": torch_to_numpy(r)})
+    ref = oracle(ir, {"w_down": w, "g": g}, {"a": a, "r": r})
+    np.testing.assert_allclose(to_f32(out["h"]), ref["h"], rtol=2e-2, atol=2e-2)
+    np.testing.assert_allclose(to_f32(out["y"]), ref["y"], rtol=2e-2, atol=2e-2)
+    assert fake_native.calls == ["linear_rmsnorm"]
+    # a shape the library does not split keeps the two steps
+    fake_native.calls.clear()
+    ir2 = _linear_residual_rmsnorm_graph(128, 1536, 4096)
+    run_backend(ir2, {"w_down": torch_to_numpy(w), "g": torch_to_numpy(g)}, {"a": torch_to_numpy(a[:128]), "r": torch_to_numpy(r[:128])})
+    assert fake_native.calls == ["linear", "rmsnorm"]
+
+
 def test_silu_mul_graph(fake_native):
     ir = silu_mul_graph(7, 8960)
     g, u = rand((7, 8960)), rand((7, 8960), seed=1)
