@@ -89,7 +89,8 @@ def qwen_prefill(cfg, sd, device, T: int, tflops_peak: float) -> dict:
     kvd = cfg.num_key_value_heads * 128
     flops = 2 * T * (L * (H * H * 2 + 2 * kvd * H + 3 * H * I) + V * H) + L * cfg.num_attention_heads * 4 * T * T * 128
     return {"ms": ms, "tflops": flops / (ms * 1e-3) / 1e12, "tensor_frac": flops / (ms * 1e-3) / 1e12 / tflops_peak,
-            "algorithmic_flops": int(flops), "launches": ex.last_launch_count, "tokens": T}
+            "algorithmic_flops": int(flops), "launches": ex.last_launch_count, "tokens": T,
+            "launches_are": "library calls (a down projection split over CTA pairs is two kernels inside one call)"}
 
 
 def resnet50(device, batch: int, tflops_peak: float) -> dict:
