@@ -356,7 +356,7 @@ int b200_conv2d_nhwc(const void* x, const void* w, const float* bias, const void
  *   mask:[B, S] additive (the graph's attention_mask [B,1,1,S]); NULL = none
  *   out: [B, Hq, D]
  * Split-KV: for caches of 512..16384 rows (and at most 8 query heads per KV head) the up to eight splits
- * of a (sequence, KV head) form a thread-block cluster and merge in distributed shared memory
+ * (sixteen for batches whose clusters are all resident at once) of a (sequence, KV head) form a thread-block cluster and merge in distributed shared memory
  * (no workspace: b200_attn_decode_workspace_bytes returns 0); otherwise partial
  * (max, sum, acc) per split go to `workspace` and are merged by a second kernel.  Key blocks whose mask entries are all <= -1e30 are skipped, which
  * leaves the result unchanged because their softmax weight underflows to 0. */

@@ -68,7 +68,7 @@ constexpr int DEC_ACC_PITCH = HD + 4;          // row pitch of the cross-warp ac
 // along x.  Instead of writing its partial result to global memory for a second kernel, every
 // CTA stores head h's partial (accumulator, max, sum) into the receive buffer of cluster rank h
 // (distributed shared memory); after one cluster barrier every rank combines the splits of the
-// heads it owns (head h belongs to rank h % splits) and writes the final output.  2 <= splits <= 8.
+// heads it owns (head h belongs to rank h % splits) and writes the final output.  2 <= splits <= 16.
 template <typename T, int STAGES, bool CM>
 __global__ void __launch_bounds__(128, STAGES == 2 ? 3 : 2) attn_decode_kernel(const __grid_constant__ DecodeParams p) {
   extern __shared__ __align__(1024) uint8_t dsm[];
@@ -562,7 +562,7 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const __grid_constant
 
 struct DecodePlan { int split_len; int splits; bool cluster; };
 
-static DecodePlan plan_decode(int64_t B, int Hkv, int64_t S, int G = 8) {
+static DecodePlan plan_decode(int64_t B, int Hkv, int64_t S, int G = 8, int resident16 = 0) {
   const int64_t want = 2 * 148;  // fixed so that the workspace size does not depend on the device
   // Caches of 512 .. 16384 rows: up to eight splits per (sequence, KV head), merged inside the kernel by a cluster
   // (measured faster than the two-kernel form at every batch size: B=8 14.7 vs 19.6 us, B=1 12.2 vs 13.4 us).
@@ -575,7 +575,11 @@ static DecodePlan plan_decode(int64_t B, int Hkv, int64_t S, int G = 8) {
     DecodePlan c;
     c.cluster = false;
     int64_t best = 0;
-    for (int n = 8; n >= (G < 6 ? (G < 2 ? 2 : G) : 6); --n) {
+    // Small batches, where eight splits per KV head leave SMs idle, use clusters of 16 (a non-portable size) as long
+    // as all of them are resident at once (`resident16`, asked of the device): B=1 12.2 -> 8.0 us, B=8 13.1 -> 10.8,
+    // B=10 12.0; with a second wave of clusters they lose (B=12: 20.4 us).
+    const int n_hi = (resident16 > 0 && B * Hkv <= resident16) ? 16 : 8;
+    for (int n = n_hi; n >= (G < 6 ? (G < 2 ? 2 : G) : 6); --n) {
       const int len = static_cast<int>(ceil_div(ceil_div(S, n), 16) * 16);
       if (len > DEC_MAX_SPLIT || ceil_div(S, len) != n) continue;
       const int64_t waves = ceil_div(B * Hkv * n, 3 * 148);
@@ -628,7 +632,35 @@ extern "C" int b200_attn_decode(const void* q, const void* k, const void* v, con
   if (B == 0) return B200_OK;
   if (!(aligned16(q) && aligned16(k) && aligned16(v) && q_batch_stride % 8 == 0 && kv_batch_stride % 8 == 0 && kv_head_stride % 8 == 0))
     B200_FAIL(B200_EALIGN, "b200_attn_decode: operands must be 16-byte aligned with strides multiple of 8");
-  const DecodePlan d = plan_decode(B, Hkv, S, Hq / Hkv);
+  // clusters of 16 CTAs are a non-portable size: how many the device keeps resident at once is asked once per device
+  // (0 = not asked yet, -1 = not available)
+  static PerDevice<int> resident16_on;
+  int* resident16 = resident16_on.slot();
+  if (!resident16) B200_FAIL(B200_ELAUNCH, "attn_decode_kernel: no current device");
+  if (*resident16 == 0) {
+    *resident16 = -1;
+    int n16 = 0;
+    bool ok16 = true;
+    B200_DISPATCH_HALF(dtype, T, {
+      ok16 = cudaFuncSetAttribute(attn_decode_kernel<T, 2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 4 * 2 * DEC_STAGE_BYTES) == cudaSuccess &&
+             cudaFuncSetAttribute(attn_decode_kernel<T, 2, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
+      if (ok16) {
+        cudaLaunchConfig_t qc = {};
+        qc.gridDim = dim3(16, 1, 1);
+        qc.blockDim = dim3(128);
+        qc.dynamicSmemBytes = 4 * 2 * DEC_STAGE_BYTES;
+        cudaLaunchAttribute ca;
+        ca.id = cudaLaunchAttributeClusterDimension;
+        ca.val.clusterDim.x = 16; ca.val.clusterDim.y = 1; ca.val.clusterDim.z = 1;
+        qc.attrs = &ca;
+        qc.numAttrs = 1;
+        ok16 = cudaOccupancyMaxActiveClusters(&n16, attn_decode_kernel<T, 2, true>, &qc) == cudaSuccess && n16 >= 1;
+      }
+    });
+    cudaGetLastError();
+    if (ok16) *resident16 = n16;
+  }
+  const DecodePlan d = plan_decode(B, Hkv, S, Hq / Hkv, *resident16);
   const int64_t need = b200_attn_decode_workspace_bytes(B, Hq, Hkv, S, D);
   if (need > 0 && (!workspace || workspace_bytes < need))
     B200_FAIL(B200_EINVAL, "b200_attn_decode: workspace of %lld bytes required (got %lld)", (long long)need, (long long)workspace_bytes);
