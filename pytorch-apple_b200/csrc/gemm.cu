@@ -572,9 +572,6 @@ extern "C" int b200_linear(const void* A, const void* W, const void* bias, const
   return B200_OK;
 }
 
-extern "C" int b200_rmsnorm(const void* x, const void* w, void* y, int64_t rows, int64_t cols, int64_t x_row_stride,
-                            int64_t y_row_stride, float eps, int dtype, int round_mid, void* stream);
-
 extern "C" int b200_linear_rmsnorm(const void* A, const void* W, const void* bias, const void* residual, void* out, int64_t M,
                                    int64_t N, int64_t K, int64_t lda, int64_t ldw, int64_t ldo, int64_t ldr, int dtype,
                                    int bias_dtype, int epilogue, void* workspace, int64_t workspace_bytes, const void* norm_weight,
