@@ -37,6 +37,26 @@ def test_host_only_entry_points(native_lib):
     assert native_lib.b200_attn_decode_workspace_bytes(64, 12, 2, 32768, 128) == 64 * 2 * 64 * 6 * 130 * 4   # longer caches: 512-key splits + merge kernel
 
 
+def test_compiler_and_library_agree_on_the_splitk_shapes(native_lib):
+    """The compiler appends an RMSNorm to a GEMM only for the shapes it expects the library to split over CTA pairs
+    (`_pair_splitk_shape` of the lowering pass).  The library's own rule shows in its workspace sizing: for rows > 64 a
+    non-zero size means exactly that path.  The two are kept in step here (a mismatch would not be wrong, only a
+    fusion promised and not delivered, or missed)."""
+    from cuda_compiler.subgraph_analyzer import _Lowering as SubgraphAnalyzer
+
+    for M in (65, 128, 129, 256, 300, 512, 1000, 1024, 2048, 4096):
+        for N in (256, 1024, 1200, 1536, 2048, 2056, 4096):
+            for K in (1536, 4096, 4104, 8960):
+                mirror = SubgraphAnalyzer._pair_splitk_shape(M, N, K)
+                lib_splits = native_lib.b200_linear_workspace_bytes(M, N, K) > 0
+                if mirror:
+                    assert lib_splits, (M, N, K)
+                elif lib_splits:   # shapes the library splits but whose rows it cannot normalise in the reduce kernel
+                    assert N > 2048 or N % 8, (M, N, K)
+    assert SubgraphAnalyzer._pair_splitk_shape(512, 1536, 8960) and SubgraphAnalyzer._pair_splitk_shape(1024, 1536, 8960)
+    assert not SubgraphAnalyzer._pair_splitk_shape(2048, 1536, 8960) and not SubgraphAnalyzer._pair_splitk_shape(512, 1536, 1536)
+
+
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     from cuda_runtime import native
 
