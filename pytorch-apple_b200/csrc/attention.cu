@@ -641,9 +641,11 @@ extern "C" int b200_attn_decode(const void* q, const void* k, const void* v, con
     *resident16 = -1;
     int n16 = 0;
     bool ok16 = true;
+    // (the attribute is per kernel instantiation: both activation types get it, whichever asks first)
+    ok16 = cudaFuncSetAttribute(attn_decode_kernel<__nv_bfloat16, 2, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess &&
+           cudaFuncSetAttribute(attn_decode_kernel<__half, 2, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
     B200_DISPATCH_HALF(dtype, T, {
-      ok16 = cudaFuncSetAttribute(attn_decode_kernel<T, 2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 4 * 2 * DEC_STAGE_BYTES) == cudaSuccess &&
-             cudaFuncSetAttribute(attn_decode_kernel<T, 2, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
+      ok16 = ok16 && cudaFuncSetAttribute(attn_decode_kernel<T, 2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 4 * 2 * DEC_STAGE_BYTES) == cudaSuccess;
       if (ok16) {
         cudaLaunchConfig_t qc = {};
         qc.gridDim = dim3(16, 1, 1);

@@ -318,6 +318,26 @@ def test_attn_decode(lib, B, S, valid):
     close(out, attn_ref(q, k, v, None, D ** -0.5, dtype)[:, :, 0], rtol=2e-2, atol=5e-3)
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("B", [2, 12])
+def test_attn_decode_small_batches_in_both_dtypes(lib, dtype, B):
+    """Small batches take clusters of 16 splits (a non-portable cluster size that every kernel instantiation has to
+    be allowed separately), B=12 the portable eight: both activation types, in one process, against the fp32 reference."""
+    import model_zoo as mz
+
+    S, valid, Hq, Hkv, D = 1024, 700, 12, 2, 128
+    q, k, v = gen((B, Hq, 1, D), dtype), gen((B, Hkv, S, D), dtype, 1), gen((B, Hkv, S, D), dtype, 2)
+    mask = mz.causal_mask(B, 1, S, valid - 1).to(dtype)
+    ref = attn_ref(q, k, v, mask, D ** -0.5, dtype)[:, :, 0]
+    Q, K, V, M = q.cuda(), k.cuda(), v.cuda(), mask.cuda()
+    out = torch.empty(B, Hq, D, dtype=dtype, device="cuda")
+    ws = torch.empty(max(16, lib.b200_attn_decode_workspace_bytes(B, Hq, Hkv, S, D)), dtype=torch.uint8, device="cuda")
+    code = 2 if dtype == torch.bfloat16 else 1
+    ok(lib, lib.b200_attn_decode(Q.data_ptr(), K.data_ptr(), V.data_ptr(), M.data_ptr(), out.data_ptr(), B, Hq, Hkv, S, D, Hq * D,
+                                 Hkv * S * D, S * D, S, D ** -0.5, code, ws.data_ptr(), ws.numel(), stream()))
+    close(out, ref, rtol=2e-2, atol=5e-3)
+
+
 @pytest.mark.parametrize("B,S,Hq,Hkv", [(40, 2048, 12, 2), (64, 4352, 12, 2), (33, 1000, 8, 1), (130, 640, 4, 4)])
 def test_attn_decode_many_sequences_ragged_masks(lib, B, S, Hq, Hkv):
     """Batches large enough for the balanced kernel (every CTA gets the same number of unmasked 16-key
