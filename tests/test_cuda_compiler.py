@@ -237,6 +237,44 @@ def test_qwen_prefill_layer_plan():
     assert kinds512.count("rmsnorm_kernel") == L + 1 and kinds512.count("gemm") == 4 * L + 1
 
 
+def _assert_arena_is_consistent(prog):
+    """Every tensor a step touches lives in a buffer whose live range covers that step (the peepholes move and merge
+    steps after lowering), and no two such buffers that are live at the same step share a byte of the arena.
+    (Buffers that no step touches any more - the output of a folded RMSNorm - keep a placeholder offset.)"""
+    by_name = {a.name: a for a in prog.buffer_allocations}
+    used: dict[str, object] = {}
+    for i, st in enumerate(prog.steps):
+        p = getattr(st, "params", None) or {}
+        views = [v for v in p.values() if hasattr(v, "buffer")] + [v for d in p.values() if isinstance(d, dict) for v in d.values() if hasattr(v, "buffer")]
+        for v in views:
+            a = by_name.get(v.buffer)
+            if a is None or a.size_bytes == 0:
+                continue
+            used[a.name] = a
+            if not a.persistent:
+                assert a.first_step <= i <= a.last_step, (i, type(st).__name__, p.get("op"), v.buffer, a.first_step, a.last_step)
+    placed = list(used.values())
+    assert placed
+    for i, a in enumerate(placed):
+        assert a.offset % 256 == 0 and a.offset + a.size_bytes <= prog.arena_bytes, a.name
+        for b in placed[i + 1:]:
+            if a.last_step < b.first_step or b.last_step < a.first_step:
+                continue
+            assert a.offset + a.size_bytes <= b.offset or b.offset + b.size_bytes <= a.offset, (a.name, b.name)
+
+
+def test_arena_plans_stay_consistent_after_the_peepholes():
+    L = 2
+    cfg = mz.qwen2_config(num_layers=L)
+    for T in (128, 512):
+        ir = extract_ir(mz.QwenPrefillWrapper(mz.qwen2_model(cfg)), mz.qwen2_example_inputs(cfg, 1, T, None), f"qp{T}")
+        _assert_arena_is_consistent(compile_subgraph(ir))
+    ird = extract_ir(mz.QwenDecodeWrapper(mz.qwen2_model(cfg), L), mz.qwen2_example_inputs(cfg, 2, 1, 256), "qd")
+    _assert_arena_is_consistent(compile_subgraph(ird))
+    _assert_arena_is_consistent(compile_subgraph(ird, fuse=False))
+    _assert_arena_is_consistent(compile_subgraph(extract_ir(mz.resnet(18, device="meta"), (torch.zeros(1, 3, 64, 64, device="meta"),), "r18")))
+
+
 def test_qwen_decode_layer_plan():
     L = 2
     cfg = mz.qwen2_config(num_layers=L)
