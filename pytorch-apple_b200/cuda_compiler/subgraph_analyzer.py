@@ -379,9 +379,14 @@ class _Lowering:
             if x.buffer != ly.buffer or x.offset != ly.offset or x.dtype != ly.dtype or x.strides[-1] != 1 or row(x) != row(ly) \
                     or y.strides[-1] != 1 or row(y) % 8 or y.offset % 8 or row(y) != N:
                 continue
-            lp["norm_tail"] = {"w": p["w"], "y": y, "eps": float(p["eps"]), "round_mid": bool(p["round_mid"])}
-            lp["source"] = lp.get("source", "") + " ; rmsnorm(result) * gain"
-            steps[prev].input_buffer_names = list(dict.fromkeys(list(steps[prev].input_buffer_names) + [p["w"]]))
+            params = dict(lp)
+            params["norm_tail"] = {"w": p["w"], "y": y, "eps": float(p["eps"]), "round_mid": bool(p["round_mid"])}
+            params["source"] = lp.get("source", "") + " ; rmsnorm(result) * gain"
+            names = list(dict.fromkeys(list(steps[prev].input_buffer_names) + [p["w"]]))
+            # one step with two results: the GEMM's own and the normalised rows
+            steps[prev] = SpecialKernelStep("gemm_pair_kernel", "x @ W^T (+ b, + residual) split over CTA pairs; the kernel that adds up the "
+                                            "partial sums also writes rmsnorm(result) * gain", names, steps[prev].output_buffer_name,
+                                            output_buffer_names=[steps[prev].output_buffer_name, st.output_buffer_name], params=params)
             touched[prev] = list(dict.fromkeys(list(touched[prev]) + [n for n in touched[i]]))
             drop.add(i)
             last = prev

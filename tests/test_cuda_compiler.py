@@ -232,9 +232,10 @@ def test_qwen_prefill_layer_plan():
     ir512 = extract_ir(mz.QwenPrefillWrapper(mz.qwen2_model(cfg)), mz.qwen2_example_inputs(cfg, 1, 512, None), "qp512")
     prog512 = compile_subgraph(ir512)
     kinds512 = [getattr(s, "kernel_name", None) or s.blas_type for s in prog512.steps if not isinstance(s, AliasStep)]
-    tails = [s.params for s in prog512.steps if isinstance(s, CUBLASStep) and s.params.get("norm_tail")]
-    assert len(tails) == L and all(t["K"] == cfg.intermediate_size and t["residual"] is not None for t in tails)
-    assert kinds512.count("rmsnorm_kernel") == L + 1 and kinds512.count("gemm") == 4 * L + 1
+    tails = [s for s in prog512.steps if isinstance(s, SpecialKernelStep) and s.params.get("norm_tail")]
+    assert len(tails) == L and all(t.params["K"] == cfg.intermediate_size and t.params["residual"] is not None for t in tails)
+    assert all(t.kernel_name == "gemm_pair_kernel" and len(t.output_buffer_names) == 2 and t.params["op"] == "linear" for t in tails)
+    assert kinds512.count("rmsnorm_kernel") == L + 1 and kinds512.count("gemm") == 3 * L + 1
 
 
 def _assert_arena_is_consistent(prog):
@@ -253,6 +254,20 @@ def _assert_arena_is_consistent(prog):
             used[a.name] = a
             if not a.persistent:
                 assert a.first_step <= i <= a.last_step, (i, type(st).__name__, p.get("op"), v.buffer, a.first_step, a.last_step)
+    # every arena buffer a step reads has been written by an earlier step (donated inputs and persistent buffers aside)
+    produced: set[str] = set()
+    for i, st in enumerate(prog.steps):
+        if isinstance(st, AliasStep):
+            continue
+        outs = list(getattr(st, "output_buffer_names", None) or [st.output_buffer_name])
+        out_bufs = {prog.views[n].buffer if n in prog.views else n for n in outs}
+        for n in st.input_buffer_names:
+            b = prog.views[n].buffer if n in prog.views else n
+            a = by_name.get(b)
+            if a is None or a.persistent or a.size_bytes == 0 or b in out_bufs:
+                continue
+            assert b in produced, (i, getattr(st, "kernel_name", None) or st.blas_type, n, b)
+        produced |= out_bufs
     placed = list(used.values())
     assert placed
     for i, a in enumerate(placed):
